@@ -1,0 +1,310 @@
+"""Model geometry and deployment descriptions.
+
+A `ModelSpec` is the single description every layer of the framework consumes: the
+CPU oracle, the weight initialiser, the planner/placement solver, the engine and the
+benchmarks.  The reference derives the same facts from a snapshot's `config.json`
+(reference: rust/crates/cuteafd-loader/src/plan/family.rs, cuteafd-core/src/constants.rs);
+here they are plain dataclasses plus a `from_hf_config` reader.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Optional
+
+
+@dataclass(frozen=True)
+class AttentionSpec:
+    kind: str = "gqa"              # "gqa" | "mla"
+    n_heads: int = 8
+    n_kv_heads: int = 2
+    head_dim: int = 32
+    rope_theta: float = 10000.0
+    rope_interleaved: bool = True   # pair (2i, 2i+1) rotation; False = half-split (HF llama style)
+    qk_norm: bool = False           # per-head RMSNorm on q and k (Qwen3)
+    # MLA (DeepSeek-V3 style); ignored for gqa
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    window: int = 0                 # sliding window (0 = full)
+    sink: bool = False              # learned attention sink logit per head
+
+    @property
+    def q_dim(self) -> int:
+        if self.kind == "mla":
+            return self.n_heads * (self.qk_nope_head_dim + self.qk_rope_head_dim)
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_token_elems(self) -> int:
+        """Cached elements per token per layer."""
+        if self.kind == "mla":
+            return self.kv_lora_rank + self.qk_rope_head_dim
+        return 2 * self.n_kv_heads * self.head_dim
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    n_experts: int = 16
+    top_k: int = 4
+    intermediate: int = 128
+    n_shared: int = 1
+    shared_intermediate: int = 0    # 0 -> n_shared * intermediate
+    scoring: str = "sigmoid"        # sigmoid | softmax | sqrtsoftplus | hash
+    normalize: bool = True
+    route_scale: float = 1.0
+    use_bias: bool = False          # noaux_tc selection bias (affects choice only)
+    n_group: int = 1
+    topk_group: int = 1
+    first_dense: int = 0            # leading dense layers
+    dense_intermediate: int = 0
+    swiglu_limit: float = 0.0       # clamp on gate/up (0 = off)
+
+    @property
+    def shared_inter(self) -> int:
+        return self.shared_intermediate or self.n_shared * self.intermediate
+
+
+@dataclass(frozen=True)
+class QuantSpec:
+    """Weight formats as shipped in the checkpoint (no repacking on disk)."""
+    experts: str = "bf16"           # bf16 | fp8_block128 | mxfp4 | nvfp4 | exl3
+    dense: str = "bf16"             # bf16 | fp8_block128 | fp8_block32 | nvfp4
+    kv: str = "bf16"                # bf16 | fp8
+    exl3_bits: int = 4
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    name: str = "tiny"
+    family: str = "tiny"
+    vocab: int = 1024
+    hidden: int = 256
+    n_layers: int = 2
+    rms_eps: float = 1e-5
+    attn: AttentionSpec = field(default_factory=AttentionSpec)
+    moe: MoESpec = field(default_factory=MoESpec)
+    quant: QuantSpec = field(default_factory=QuantSpec)
+    mtp_layers: int = 0             # native next-n (MTP) draft layers
+    init_std: float = 0.02
+    tie_embeddings: bool = False
+    max_context: int = 1 << 20
+
+    def replace(self, **kw) -> "ModelSpec":
+        return dataclasses.replace(self, **kw)
+
+    # ---- derived sizes -------------------------------------------------
+    def is_moe_layer(self, layer: int) -> bool:
+        return layer >= self.moe.first_dense
+
+    def expert_params(self) -> int:
+        return 3 * self.hidden * self.moe.intermediate
+
+    def attn_params(self) -> int:
+        a, h = self.attn, self.hidden
+        if a.kind == "mla":
+            qk = a.qk_nope_head_dim + a.qk_rope_head_dim
+            q = h * a.q_lora_rank + a.q_lora_rank * a.n_heads * qk if a.q_lora_rank else h * a.n_heads * qk
+            kv = h * (a.kv_lora_rank + a.qk_rope_head_dim) + a.kv_lora_rank * a.n_heads * (a.qk_nope_head_dim + a.v_head_dim)
+            return q + kv + a.n_heads * a.v_head_dim * h
+        return h * (a.n_heads + 2 * a.n_kv_heads) * a.head_dim + a.n_heads * a.head_dim * h
+
+    def bits(self, fmt: str) -> float:
+        return {"bf16": 16.0, "fp8_block128": 8.0 + 32.0 / (128 * 128), "fp8_block32": 8.0 + 8.0 / (32 * 32),
+                "mxfp4": 4.25, "nvfp4": 4.5, "exl3": float(self.quant.exl3_bits)}[fmt]
+
+    def weight_bytes(self) -> dict:
+        """Bytes per category for the whole model (planner input)."""
+        moe_layers = self.n_layers - self.moe.first_dense
+        eb = self.bits(self.quant.experts) / 8
+        db = self.bits(self.quant.dense) / 8
+        routed = moe_layers * self.moe.n_experts * self.expert_params() * eb
+        shared = moe_layers * 3 * self.hidden * self.moe.shared_inter * db
+        dense_ffn = self.moe.first_dense * 3 * self.hidden * self.moe.dense_intermediate * db
+        attn = self.n_layers * self.attn_params() * db
+        router = moe_layers * self.moe.n_experts * self.hidden * 2
+        embed = self.vocab * self.hidden * 2 * (1 if self.tie_embeddings else 2)
+        return {"routed_experts": routed, "shared_experts": shared, "dense_ffn": dense_ffn,
+                "attention": attn, "router": router, "embed_head": embed}
+
+    def kv_bytes_per_token(self) -> float:
+        per = 1.0 if self.quant.kv == "fp8" else 2.0
+        return self.n_layers * self.attn.kv_token_elems * per
+
+
+# ---------------------------------------------------------------------------
+# Named configurations
+# ---------------------------------------------------------------------------
+
+def tiny_spec() -> ModelSpec:
+    """Tiny synthetic MoE decoder (CPU oracle config): vocab 1024, hidden 256, 2 layers,
+    GQA 8q/2kv/32, 16 experts sigmoid-normalised top-4 + 1 shared, SwiGLU I=128."""
+    return ModelSpec()
+
+
+def deepseek_v3_spec(n_layers: int = 61) -> ModelSpec:
+    """DeepSeek-V3-shape: 61 layers, hidden 7168, MLA 128 heads (q_lora 1536, kv_lora 512,
+    rope 64), 256 experts top-8 + 1 shared, I=2048, vocab 129280; FP8 128x128 dense, MXFP4 experts."""
+    return ModelSpec(
+        name="deepseek-v3-shape", family="deepseek_v3", vocab=129280, hidden=7168, n_layers=n_layers,
+        rms_eps=1e-6,
+        attn=AttentionSpec(kind="mla", n_heads=128, n_kv_heads=128, head_dim=192, rope_theta=10000.0,
+                           q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                           qk_rope_head_dim=64, v_head_dim=128),
+        moe=MoESpec(n_experts=256, top_k=8, intermediate=2048, n_shared=1, scoring="sigmoid",
+                    normalize=True, route_scale=2.5, use_bias=True, n_group=8, topk_group=4,
+                    first_dense=min(3, n_layers), dense_intermediate=18432),
+        quant=QuantSpec(experts="mxfp4", dense="fp8_block128", kv="bf16"),
+        mtp_layers=1)
+
+
+def qwen3_235b_spec(n_layers: int = 94) -> ModelSpec:
+    """Qwen3-235B-A22B-shape with NVFP4 weights: 94 layers, hidden 4096, GQA 64q/4kv/128,
+    128 experts top-8, I=1536, vocab 151936."""
+    return ModelSpec(
+        name="qwen3-235b-a22b-shape", family="qwen3_moe", vocab=151936, hidden=4096, n_layers=n_layers,
+        rms_eps=1e-6,
+        attn=AttentionSpec(kind="gqa", n_heads=64, n_kv_heads=4, head_dim=128, rope_theta=1e6,
+                           rope_interleaved=False, qk_norm=True),
+        moe=MoESpec(n_experts=128, top_k=8, intermediate=1536, n_shared=0, scoring="softmax",
+                    normalize=True),
+        quant=QuantSpec(experts="nvfp4", dense="nvfp4", kv="bf16"))
+
+
+def ep_microbench_spec() -> ModelSpec:
+    """EP dispatch -> grouped GEMM -> combine microbench layer: hidden 7168, 256 experts, top-8,
+    I=2048, MXFP4 weights."""
+    return ModelSpec(name="ep-microbench", family="microbench", hidden=7168, n_layers=1, vocab=1024,
+                     moe=MoESpec(n_experts=256, top_k=8, intermediate=2048, n_shared=0,
+                                 scoring="softmax", normalize=True),
+                     quant=QuantSpec(experts="mxfp4"))
+
+
+NAMED_SPECS = {
+    "tiny": tiny_spec,
+    "deepseek-v3": deepseek_v3_spec,
+    "qwen3-235b": qwen3_235b_spec,
+    "ep-microbench": ep_microbench_spec,
+}
+
+
+def spec_by_name(name: str, **kw) -> ModelSpec:
+    if name not in NAMED_SPECS:
+        raise KeyError(f"unknown model spec {name!r}; known: {sorted(NAMED_SPECS)}")
+    return NAMED_SPECS[name](**kw)
+
+
+# ---------------------------------------------------------------------------
+# HF config.json -> ModelSpec (family detection, reference: commands/family.rs)
+# ---------------------------------------------------------------------------
+
+FAMILY_BY_ARCH = {
+    "DeepseekV3ForCausalLM": "deepseek_v3",
+    "DeepseekV32ForCausalLM": "deepseek_v3",
+    "DeepseekV4ForCausalLM": "deepseek_v4",
+    "Qwen3MoeForCausalLM": "qwen3_moe",
+    "Qwen3ForCausalLM": "qwen3_dense",
+    "Glm4MoeForCausalLM": "glm_moe",
+    "GlmMoeDsaForCausalLM": "glm_moe",
+    "MiMoV2FlashForCausalLM": "mimo_v2",
+    "MixtralForCausalLM": "mixtral",
+}
+
+
+def detect_quant(cfg: dict) -> QuantSpec:
+    q = cfg.get("quantization_config") or {}
+    method = (q.get("quant_method") or q.get("quant_algo") or "").lower()
+    fmt = (q.get("fmt") or q.get("format") or "").lower()
+    if method == "fp8":
+        blk = q.get("weight_block_size") or [128, 128]
+        dense = "fp8_block32" if list(blk) == [32, 32] else "fp8_block128"
+        experts = "mxfp4" if "mxfp4" in json.dumps(q).lower() else dense
+        return QuantSpec(experts=experts, dense=dense)
+    if method in ("mxfp4",):
+        return QuantSpec(experts="mxfp4", dense="bf16")
+    if method in ("modelopt", "nvfp4") or "nvfp4" in fmt or q.get("quant_algo", "").upper() == "NVFP4":
+        return QuantSpec(experts="nvfp4", dense="nvfp4")
+    if method in ("exl3",) or "exl3" in fmt:
+        return QuantSpec(experts="exl3", dense="bf16", exl3_bits=int(round(float(q.get("bits", 4)))))
+    return QuantSpec()
+
+
+def from_hf_config(cfg: dict | str | Path) -> ModelSpec:
+    """Build a ModelSpec from a Hugging Face `config.json` (dict or path)."""
+    if not isinstance(cfg, dict):
+        p = Path(cfg)
+        p = p / "config.json" if p.is_dir() else p
+        cfg = json.loads(p.read_text())
+    archs = cfg.get("architectures") or ["?"]
+    family = FAMILY_BY_ARCH.get(archs[0])
+    if family is None:
+        raise ValueError(f"unsupported architecture {archs[0]!r} (supported: {sorted(FAMILY_BY_ARCH)})")
+    hidden = cfg["hidden_size"]
+    heads = cfg["num_attention_heads"]
+    if "kv_lora_rank" in cfg:
+        attn = AttentionSpec(kind="mla", n_heads=heads, n_kv_heads=heads,
+                             head_dim=cfg["qk_nope_head_dim"] + cfg["qk_rope_head_dim"],
+                             rope_theta=cfg.get("rope_theta", 1e4),
+                             q_lora_rank=cfg.get("q_lora_rank") or 0, kv_lora_rank=cfg["kv_lora_rank"],
+                             qk_nope_head_dim=cfg["qk_nope_head_dim"], qk_rope_head_dim=cfg["qk_rope_head_dim"],
+                             v_head_dim=cfg["v_head_dim"])
+    else:
+        attn = AttentionSpec(kind="gqa", n_heads=heads, n_kv_heads=cfg.get("num_key_value_heads", heads),
+                             head_dim=cfg.get("head_dim") or hidden // heads,
+                             rope_theta=cfg.get("rope_theta", 1e4), rope_interleaved=False,
+                             qk_norm=family in ("qwen3_moe", "qwen3_dense"),
+                             window=cfg.get("sliding_window") or 0)
+    n_exp = cfg.get("n_routed_experts") or cfg.get("num_experts") or cfg.get("num_local_experts") or 0
+    moe = MoESpec(
+        n_experts=n_exp, top_k=cfg.get("num_experts_per_tok", 1),
+        intermediate=cfg.get("moe_intermediate_size") or cfg.get("intermediate_size", 0),
+        n_shared=cfg.get("n_shared_experts") or 0,
+        scoring=cfg.get("scoring_func", "softmax"), normalize=cfg.get("norm_topk_prob", True),
+        route_scale=cfg.get("routed_scaling_factor", 1.0),
+        use_bias=cfg.get("topk_method") == "noaux_tc", n_group=cfg.get("n_group") or 1,
+        topk_group=cfg.get("topk_group") or 1, first_dense=cfg.get("first_k_dense_replace", 0),
+        dense_intermediate=cfg.get("intermediate_size", 0))
+    return ModelSpec(name=cfg.get("_name_or_path") or family, family=family, vocab=cfg["vocab_size"],
+                     hidden=hidden, n_layers=cfg["num_hidden_layers"], rms_eps=cfg.get("rms_norm_eps", 1e-6),
+                     attn=attn, moe=moe, quant=detect_quant(cfg),
+                     mtp_layers=cfg.get("num_nextn_predict_layers", 0),
+                     tie_embeddings=cfg.get("tie_word_embeddings", False),
+                     max_context=cfg.get("max_position_embeddings", 1 << 20))
+
+
+@dataclass(frozen=True)
+class Deployment:
+    """How ranks of one node are used (reference: SparkWorld / placement decisions).
+
+    attention ranks run attention + dense backbone + router + shared expert (+ head);
+    expert ranks hold routed experts, expert-parallel.  With `colocated=True` every rank does both."""
+    world: int = 1
+    attn_ranks: tuple = (0,)
+    expert_ranks: tuple = (0,)
+    colocated: bool = True
+
+    @property
+    def tp(self) -> int:
+        return len(self.attn_ranks)
+
+    @property
+    def ep(self) -> int:
+        return len(self.expert_ranks)
+
+    def describe(self) -> str:
+        if self.world == 1:
+            return "single"
+        return f"attn-tp{self.tp}+ep{self.ep}" if not self.colocated else f"tp{self.tp}-ep{self.ep}-colocated"
+
+
+def default_deployment(world: int) -> Deployment:
+    """North-star split: attention TP2 on ranks 0-1, experts EP on the rest (8 GPUs -> TP2 + EP6)."""
+    if world == 1:
+        return Deployment()
+    if world == 2:
+        return Deployment(world=2, attn_ranks=(0,), expert_ranks=(1,), colocated=False)
+    return Deployment(world=world, attn_ranks=(0, 1), expert_ranks=tuple(range(2, world)), colocated=False)

@@ -1,0 +1,160 @@
+"""fp32 CPU oracle for every operator the engine runs.
+
+Behaviour follows the reference's tiny CPU path (python/reference/cuteafd_reference/
+rmsnorm_ref.py:6-9, rope_ref.py:6-25, attention_ref.py:8-21, router_ref.py:6-23, moe_ref.py:16-36)
+and its router kernels (native/shared/cuda/expert_router.cu:73-171): all math in fp32, outputs cast
+back to the input dtype.  These functions are the comparison target of each CUDA kernel test.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y * weight.float()).to(x.dtype)
+
+
+def rope_angles(dim: int, positions: torch.Tensor, theta: float = 10000.0) -> torch.Tensor:
+    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    return torch.outer(positions.float(), inv)          # [T, dim/2]
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, theta: float = 10000.0,
+               interleaved: bool = True) -> torch.Tensor:
+    """x: [T, heads, dim].  interleaved rotates pairs (2i, 2i+1); otherwise (i, i+dim/2)."""
+    dim = x.shape[-1]
+    ang = rope_angles(dim, positions, theta)
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xf = x.float()
+    out = torch.empty_like(xf)
+    if interleaved:
+        a, b = xf[..., 0::2], xf[..., 1::2]
+        out[..., 0::2] = a * cos - b * sin
+        out[..., 1::2] = a * sin + b * cos
+    else:
+        h = dim // 2
+        a, b = xf[..., :h], xf[..., h:]
+        out[..., :h] = a * cos - b * sin
+        out[..., h:] = a * sin + b * cos
+    return out.to(x.dtype)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor,
+              k_pos: torch.Tensor, scale: float | None = None, window: int = 0,
+              sink: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention by absolute position.  q: [Tq, Hq, D], k: [Tk, Hkv, D], v: [Tk, Hkv, Dv].
+    Query at position p sees keys with position <= p (and > p - window when window > 0).
+    `sink` ([Hq]) adds one extra softmax logit per head whose value contribution is zero."""
+    Tq, Hq, D = q.shape
+    Hkv = k.shape[1]
+    g = Hq // Hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    kf = k.float().repeat_interleave(g, 1)
+    vf = v.float().repeat_interleave(g, 1)
+    s = torch.einsum("qhd,khd->hqk", q.float(), kf) * scale
+    mask = k_pos[None, :] > q_pos[:, None]
+    if window > 0:
+        mask |= k_pos[None, :] <= (q_pos[:, None] - window)
+    s = s.masked_fill(mask[None], float("-inf"))
+    if sink is not None:
+        s = torch.cat([s, sink.float()[:, None, None].expand(Hq, Tq, 1)], -1)
+    p = torch.softmax(s, -1)
+    if sink is not None:
+        p = p[..., :-1]
+    return torch.einsum("hqk,khd->qhd", p, vf).to(q.dtype)
+
+
+def router_scores(logits: torch.Tensor, scoring: str) -> torch.Tensor:
+    lf = logits.float()
+    if scoring == "sigmoid":
+        return torch.sigmoid(lf)
+    if scoring == "softmax":
+        return torch.softmax(lf, -1)
+    if scoring == "sqrtsoftplus":
+        return torch.sqrt(F.softplus(lf))
+    raise ValueError(f"unsupported scoring {scoring!r}")
+
+
+def route_topk(hidden: torch.Tensor, router_weight: torch.Tensor, top_k: int, scoring: str = "sigmoid",
+               normalize: bool = True, route_scale: float = 1.0, bias: torch.Tensor | None = None,
+               n_group: int = 1, topk_group: int = 1):
+    """Returns (indices [T, k] int64, weights [T, k] fp32).
+
+    `bias` (noaux_tc) only influences the choice; gate weights come from unbiased scores.
+    Group-limited routing keeps the `topk_group` groups whose top-2 biased scores sum highest.
+    Ties pick the lowest expert id; selected experts are ordered by descending choice score."""
+    logits = hidden.float() @ router_weight.float().T
+    scores = router_scores(logits, scoring)
+    choice = scores + bias.float() if bias is not None else scores
+    T, E = scores.shape
+    if n_group > 1 and topk_group < n_group:
+        grp = choice.reshape(T, n_group, E // n_group)
+        gscore = grp.topk(2, -1).values.sum(-1)
+        keep = torch.zeros(T, n_group, dtype=torch.bool)
+        keep.scatter_(1, _stable_topk(gscore, topk_group), True)
+        choice = choice.masked_fill(~keep.repeat_interleave(E // n_group, 1), float("-inf"))
+    idx = _stable_topk(choice, top_k)
+    w = scores.gather(1, idx)
+    if normalize:
+        w = w / w.sum(-1, keepdim=True).clamp_min(1e-12)
+    return idx, w * route_scale
+
+
+def _stable_topk(x: torch.Tensor, k: int) -> torch.Tensor:
+    """top-k indices, descending value, lowest index first among equals."""
+    order = torch.sort(x, dim=-1, descending=True, stable=True).indices
+    return order[..., :k]
+
+
+def hash_route(token_ids: torch.Tensor, tid2eid: torch.Tensor):
+    """Hash routing: a per-token-id table names the experts (reference select_hash_kernel)."""
+    return tid2eid[token_ids.long()]
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor, limit: float = 0.0) -> torch.Tensor:
+    g, u = gate.float(), up.float()
+    if limit > 0:
+        g = g.clamp(max=limit)
+        u = u.clamp(-limit, limit)
+    return F.silu(g) * u
+
+
+def expert_ffn(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+               limit: float = 0.0) -> torch.Tensor:
+    xf = x.float()
+    return swiglu(xf @ w_gate.float().T, xf @ w_up.float().T, limit) @ w_down.float().T
+
+
+def moe_forward(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                idx: torch.Tensor, weights: torch.Tensor, limit: float = 0.0) -> torch.Tensor:
+    """Routed experts.  w_*: [E, ...].  Accumulates routes in slot order in fp32 (the combine
+    contract: fixed order fp32 sum, one final rounding)."""
+    out = torch.zeros(x.shape, dtype=torch.float32)
+    for e in idx.unique().tolist():
+        rows, slots = (idx == e).nonzero(as_tuple=True)
+        y = expert_ffn(x[rows], w_gate[e], w_up[e], w_down[e], limit)
+        out.index_put_((rows,), y * weights[rows, slots].float()[:, None], accumulate=True)
+    return out
+
+
+def greedy_verify(inputs: list[int], target_next: list[int], eos: int | None, remaining: int):
+    """Lossless greedy verification (reference: cuteafd-core/src/dspark_verify.rs:21-69).
+    inputs = anchor followed by drafts; target_next[i] = target argmax after input row i.
+    Returns (accepted_inputs, emitted, hit_eos, hit_length)."""
+    assert inputs and len(inputs) == len(target_next) and remaining > 0
+    accepted, emitted, hit_eos, hit_len = 1, [], False, False
+    for i, tok in enumerate(target_next):
+        matched = i + 1 < len(inputs) and inputs[i + 1] == tok
+        emitted.append(tok)
+        if matched:
+            accepted += 1
+        hit_eos = eos is not None and tok == eos
+        hit_len = len(emitted) == remaining
+        if not matched or hit_eos or hit_len:
+            break
+    return accepted, emitted, hit_eos, hit_len
