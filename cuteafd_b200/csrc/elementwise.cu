@@ -1,0 +1,293 @@
+// Memory-bound glue kernels (one pass over the activations each, fused where one op feeds the next):
+// embedding gather, (residual add +) RMSNorm, q/k head-norm + RoPE + paged KV write, activation
+// quantisation to NVFP4 / MXFP4 / FP8 wire rows (optionally gathering rows into expert order), SiLU*up.
+// Reference counterparts: native/shared/cuda/norm.cu:5-114, embedding.cu:6-105, attention.cu:88-135
+// (rope), kv_cache.cu:142 (norm+RoPE+store), nvfp4_payload.cu:35-117, residual.cu:170-296 (gather +
+// quantise on dispatch), mlp.cu:83 (silu_mul).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+__global__ void embed_gather_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ out,
+                                    int H, int vocab, int* status) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  if (tok < 0 || tok >= vocab) { ca_dev_fail(status, CA_DEV_BAD_INDEX, t); tok = 0; }
+  const uint4* src = (const uint4*)(table + (size_t)tok * H);
+  uint4* dst = (uint4*)(out + (size_t)t * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int cuteafd_embed_gather(const int* tokens, const void* table, void* out, int T, int H, int vocab, int* status,
+                                    cudaStream_t s) {
+  CA_REQUIRE(H % 8 == 0, "embed_gather: hidden must be a multiple of 8");
+  if (T <= 0) return CA_OK;
+  embed_gather_kernel<<<T, 128, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, H, vocab, status);
+  CA_CHECK_LAUNCH("embed_gather");
+  return CA_OK;
+}
+
+// ---------------------------------------------------------------- (add +) rmsnorm
+// x_out = x (+ delta)  [written back when delta != null];  y = rmsnorm(x_out) * w.
+// One block per row; the row is kept in registers between the two passes (H <= 8 * 1024 elements at 1024 threads).
+template <int VEC>
+__global__ void add_rmsnorm_kernel(bf16* __restrict__ x, const bf16* __restrict__ delta, const float* __restrict__ w,
+                                   bf16* __restrict__ y, int H, float eps) {
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  float v[VEC * 8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      uint4 q = *(const uint4*)(x + base + i);
+      const bf16* e = (const bf16*)&q;
+      if (delta) {
+        uint4 dq = *(const uint4*)(delta + base + i);
+        const bf16* de = (const bf16*)&dq;
+        bf16 o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { o[j] = __float2bfloat16(__bfloat162float(e[j]) + __bfloat162float(de[j])); v[k * 8 + j] = __bfloat162float(o[j]); }
+        *(uint4*)(x + base + i) = *(uint4*)o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[k * 8 + j] = __bfloat162float(e[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[k * 8 + j] * v[k * 8 + j];
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / H + eps);
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      bf16 o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16(v[k * 8 + j] * inv * w[i + j]);
+      *(uint4*)(y + base + i) = *(uint4*)o;
+    }
+  }
+}
+
+extern "C" int cuteafd_add_rmsnorm(void* x, const void* delta, const float* w, void* y, int T, int H, float eps, cudaStream_t s) {
+  CA_REQUIRE(H % 8 == 0 && H <= 32768, "add_rmsnorm: hidden %d unsupported", H);
+  if (T <= 0) return CA_OK;
+  const int vecs = H / 8;
+  int threads = vecs >= 1024 ? 1024 : ((vecs + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  const int per = (vecs + threads - 1) / threads;
+  if (per == 1) add_rmsnorm_kernel<1><<<T, threads, 0, s>>>((bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
+  else if (per == 2) add_rmsnorm_kernel<2><<<T, threads, 0, s>>>((bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
+  else add_rmsnorm_kernel<4><<<T, threads, 0, s>>>((bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
+  CA_CHECK_LAUNCH("add_rmsnorm");
+  return CA_OK;
+}
+
+// ---------------------------------------------------------------- head-norm + RoPE + paged KV write (GQA)
+// qkv: [T, (Hq + 2*Hkv) * D] bf16, q in place.  One warp per (token, head).  K and V rows go to
+// kv_cache[slot] with slot = slot_map[t] (page * page_size + offset): layout [slots, 2, Hkv, D].
+__global__ void qk_norm_rope_kvwrite_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                            const int* __restrict__ slot_map, const float* __restrict__ q_norm,
+                                            const float* __restrict__ k_norm, bf16* __restrict__ kv_cache, int T, int Hq,
+                                            int Hkv, int D, float theta, int interleaved, float eps, int n_slots, int* status) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int heads = Hq + 2 * Hkv;
+  if (warp >= T * heads) return;
+  const int t = warp / heads, h = warp % heads;
+  bf16* row = qkv + (size_t)t * heads * D + (size_t)h * D;
+  const bool is_q = h < Hq, is_k = !is_q && h < Hq + Hkv;
+  // Each lane owns up to 4 rotation pairs.  Pair p is (2p, 2p+1) when interleaved, (p, p + D/2) otherwise.
+  const int n_pairs = D / 2, ppl = (n_pairs + 31) / 32;
+  float a[4], b[4];
+  int ia[4], ib[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int p = lane * ppl + j;
+    const bool on = j < ppl && p < n_pairs;
+    ia[j] = on ? (interleaved ? 2 * p : p) : -1;
+    ib[j] = on ? (interleaved ? 2 * p + 1 : p + n_pairs) : -1;
+    a[j] = on ? __bfloat162float(row[ia[j]]) : 0.f;
+    b[j] = on ? __bfloat162float(row[ib[j]]) : 0.f;
+  }
+  if (is_q || is_k) {
+    const float* nw = is_q ? q_norm : k_norm;
+    if (nw) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss += a[j] * a[j] + b[j] * b[j];
+      const float inv = rsqrtf(warp_sum(ss) / D + eps);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) if (ia[j] >= 0) { a[j] *= inv * nw[ia[j]]; b[j] *= inv * nw[ib[j]]; }
+    }
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) if (ia[j] >= 0) {
+      const int p = lane * ppl + j;
+      const float ang = pos * powf(theta, -2.f * (float)p / (float)D);
+      const float sn = sinf(ang), cs = cosf(ang);
+      const float x0 = a[j], x1 = b[j];
+      a[j] = x0 * cs - x1 * sn;
+      b[j] = x0 * sn + x1 * cs;
+    }
+  }
+  bf16* dst = row;
+  if (!is_q) {
+    const int slot = slot_map[t];
+    if (slot < 0 || slot >= n_slots) { if (lane == 0) ca_dev_fail(status, CA_DEV_BAD_INDEX, t); return; }
+    dst = kv_cache + ((size_t)slot * 2 + (is_k ? 0 : 1)) * Hkv * D + (size_t)(h - Hq - (is_k ? 0 : Hkv)) * D;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) if (ia[j] >= 0) { dst[ia[j]] = __float2bfloat16(a[j]); dst[ib[j]] = __float2bfloat16(b[j]); }
+}
+
+extern "C" int cuteafd_qk_norm_rope_kvwrite(void* qkv, const int* positions, const int* slot_map, const float* q_norm,
+                                            const float* k_norm, void* kv_cache, int T, int Hq, int Hkv, int D, float theta,
+                                            int interleaved, float eps, int n_slots, int* status, cudaStream_t s) {
+  CA_REQUIRE(D == 32 || D == 64 || D == 128 || D == 256, "qk_norm_rope_kvwrite: head_dim %d unsupported", D);
+  if (T <= 0) return CA_OK;
+  const long long warps = (long long)T * (Hq + 2 * Hkv);
+  const int blocks = (int)((warps * 32 + 255) / 256);
+  qk_norm_rope_kvwrite_kernel<<<blocks, 256, 0, s>>>((bf16*)qkv, positions, slot_map, q_norm, k_norm, (bf16*)kv_cache, T, Hq,
+                                                     Hkv, D, theta, interleaved, eps, n_slots, status);
+  CA_CHECK_LAUNCH("qk_norm_rope_kvwrite");
+  return CA_OK;
+}
+
+// ---------------------------------------------------------------- FP4 activation quantisation (+ gather)
+// One thread quantises 16 consecutive elements.  NVFP4: E4M3 scale per 16 with a static global scale
+// (inv_gs = 1 / global_scale); MXFP4: UE8M0 scale per 32 (two threads cooperate through a shuffle).
+// dst row i takes src row (src_rows ? src_rows[i] : i); rows with a negative source are zero-filled.
+template <bool MX>
+__global__ void quant_fp4_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ src_rows, const int* __restrict__ n_rows_dev,
+                                      uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int rows, int K, int ldx, int ldsf,
+                                      const float* __restrict__ inv_gs_ptr) {
+  const int per_row = K / 16;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int n_rows = n_rows_dev ? min(*n_rows_dev, rows) : rows;
+  const int r = (int)(gid / per_row), c = (int)(gid % per_row);
+  const bool active = r < n_rows;
+  float v[16];
+  int src = active ? (src_rows ? src_rows[r] : r) : -1;
+  if (src >= 0) {
+    const uint4* p = (const uint4*)(x + (size_t)src * ldx + c * 16);
+    uint4 a = p[0], b = p[1];
+    const bf16* ea = (const bf16*)&a; const bf16* eb = (const bf16*)&b;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[j] = __bfloat162float(ea[j]); v[8 + j] = __bfloat162float(eb[j]); }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  float eff;   // value of one FP4 unit
+  uint8_t sb;
+  if (MX) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    // OCP MX: shared exponent = floor(log2(amax)) - 2
+    int e = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xFF) - 2 : 0;
+    e = max(e, 0); e = min(e, 254);
+    sb = (uint8_t)e;
+    eff = ue8m0_to_float(sb);
+  } else {
+    const float inv_gs = inv_gs_ptr ? *inv_gs_ptr : 1.f;
+    const float target = fminf(amax * inv_gs / 6.f, 448.f);
+    sb = float_to_e4m3(target);
+    eff = e4m3_to_float(sb) / inv_gs;
+  }
+  if (!active) return;
+  const float inv = eff > 0.f ? 1.f / eff : 0.f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { lo |= float_to_e2m1(v[j] * inv) << (4 * j); hi |= float_to_e2m1(v[8 + j] * inv) << (4 * j); }
+  *(uint2*)(q + (size_t)r * (K / 2) + c * 8) = make_uint2(lo, hi);
+  if (MX) { if (!(c & 1)) sf[(size_t)r * ldsf + (c >> 1)] = sb; }
+  else sf[(size_t)r * ldsf + c] = sb;
+}
+
+extern "C" int cuteafd_quant_fp4_rows(int mx, const void* x, const int* src_rows, const int* n_rows_dev, void* q, void* sf,
+                                      int rows, int K, int ldx, int ldsf, const float* inv_gs, cudaStream_t s) {
+  CA_REQUIRE(K % 32 == 0 && ldx % 8 == 0, "quant_fp4_rows: K must be a multiple of 32");
+  if (rows <= 0) return CA_OK;
+  const long long n = (long long)rows * (K / 16);
+  const int blocks = (int)((n + 255) / 256);
+  if (mx) quant_fp4_rows_kernel<true><<<blocks, 256, 0, s>>>((const bf16*)x, src_rows, n_rows_dev, (uint8_t*)q, (uint8_t*)sf, rows, K, ldx, ldsf, inv_gs);
+  else quant_fp4_rows_kernel<false><<<blocks, 256, 0, s>>>((const bf16*)x, src_rows, n_rows_dev, (uint8_t*)q, (uint8_t*)sf, rows, K, ldx, ldsf, inv_gs);
+  CA_CHECK_LAUNCH("quant_fp4_rows");
+  return CA_OK;
+}
+
+// Gather bf16 rows into expert order (BF16 expert path).
+__global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ src_rows, const int* __restrict__ n_rows_dev,
+                                   bf16* __restrict__ out, int rows, int K) {
+  const int r = blockIdx.x;
+  const int n_rows = n_rows_dev ? min(*n_rows_dev, rows) : rows;
+  if (r >= n_rows) return;
+  const int src = src_rows[r];
+  uint4* dst = (uint4*)(out + (size_t)r * K);
+  if (src < 0) { for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0); return; }
+  const uint4* sp = (const uint4*)(x + (size_t)src * K);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = sp[i];
+}
+
+extern "C" int cuteafd_gather_rows(const void* x, const int* src_rows, const int* n_rows_dev, void* out, int rows, int K, cudaStream_t s) {
+  CA_REQUIRE(K % 8 == 0, "gather_rows: K must be a multiple of 8");
+  if (rows <= 0) return CA_OK;
+  gather_rows_kernel<<<rows, 128, 0, s>>>((const bf16*)x, src_rows, n_rows_dev, (bf16*)out, rows, K);
+  CA_CHECK_LAUNCH("gather_rows");
+  return CA_OK;
+}
+
+// ---------------------------------------------------------------- FP8 wire rows (E4M3 + UE8M0 / 32)
+// Activation hand-off format between attention ranks and expert ranks: BF16-rounded input, amax floor 1e-4,
+// scale = 2^ceil(log2(amax / 448)).  One warp-lane group of 4 threads per 32 elements (8 each).
+__global__ void act_quant_fp8_ue8m0_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int rows, int H) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = H / 8;
+  if (gid >= (long long)rows * per_row) return;
+  const int r = (int)(gid / per_row), c = (int)(gid % per_row);
+  uint4 a = *(const uint4*)(x + (size_t)r * H + c * 8);
+  const bf16* e = (const bf16*)&a;
+  float v[8], amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { v[j] = __bfloat162float(e[j]); amax = fmaxf(amax, fabsf(v[j])); }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, 1e-4f);
+  const uint8_t sb = ue8m0_ceil(amax / 448.f);
+  const float inv = 1.f / ue8m0_to_float(sb);
+  uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { w0 |= (uint32_t)float_to_e4m3(v[j] * inv) << (8 * j); w1 |= (uint32_t)float_to_e4m3(v[4 + j] * inv) << (8 * j); }
+  *(uint2*)(q + (size_t)r * H + c * 8) = make_uint2(w0, w1);
+  if ((c & 3) == 0) sf[(size_t)r * (H / 32) + (c >> 2)] = sb;
+}
+
+extern "C" int cuteafd_act_quant_fp8_ue8m0(const void* x, void* q, void* sf, int rows, int H, cudaStream_t s) {
+  CA_REQUIRE(H % 32 == 0, "act_quant_fp8_ue8m0: H must be a multiple of 32");
+  if (rows <= 0) return CA_OK;
+  const long long n = (long long)rows * (H / 8);
+  act_quant_fp8_ue8m0_kernel<<<(int)((n + 255) / 256), 256, 0, s>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)sf, rows, H);
+  CA_CHECK_LAUNCH("act_quant_fp8_ue8m0");
+  return CA_OK;
+}
+
+// ---------------------------------------------------------------- silu(gate) * up  (unfused FC1 outputs)
+__global__ void silu_mul_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u, bf16* __restrict__ o, long long n, float limit) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (i >= n) return;
+  float2 a = __bfloat1622float2(*(const bf162*)(g + i)), b = __bfloat1622float2(*(const bf162*)(u + i));
+  if (limit > 0.f) { a.x = fminf(a.x, limit); a.y = fminf(a.y, limit); b.x = fminf(fmaxf(b.x, -limit), limit); b.y = fminf(fmaxf(b.y, -limit), limit); }
+  float2 r = make_float2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+  *(bf162*)(o + i) = __float22bfloat162_rn(r);
+}
+
+extern "C" int cuteafd_silu_mul(const void* g, const void* u, void* o, long long n, float limit, cudaStream_t s) {
+  CA_REQUIRE(n % 2 == 0, "silu_mul: element count must be even");
+  if (n <= 0) return CA_OK;
+  silu_mul_kernel<<<(int)((n / 2 + 255) / 256), 256, 0, s>>>((const bf16*)g, (const bf16*)u, (bf16*)o, n, limit);
+  CA_CHECK_LAUNCH("silu_mul");
+  return CA_OK;
+}

@@ -1,0 +1,365 @@
+// tcgen05 linear layer family for sm_100a:  Y[rows, N] = X[rows, K] * W[N, K]^T  (dense or grouped per expert).
+//
+// One persistent, warp-specialised kernel covers every GEMM-shaped op of the engine:
+//   * operand kinds: BF16 (kind::f16), NVFP4 (kind::mxf4nvf4, E4M3 scale / 16, scale_vec::4X) and
+//     MXFP4 (kind::mxf4, UE8M0 scale / 32, scale_vec::2X), fp32 accumulation in tensor memory;
+//   * "swap-AB": the 128 weight rows of a tile are the MMA M dimension and the tokens are the MMA N
+//     dimension (TN = 16..256), so decode batches of 1..64 rows still fill the tensor core and the kernel
+//     streams each weight byte from HBM exactly once;
+//   * grouped mode walks a device-side tile table {expert, first row, row count} built by the route
+//     packer, so one fixed-size launch (CUDA-graph friendly) serves any routing;
+//   * SWIGLU mode multiplies two weight tiles (gate, up) against the same activation tile into two
+//     accumulators and writes silu(g) * u, which is FC1 of an expert without materialising g and u.
+//   * split-K for skinny dense layers: partial tiles go to fp32 scratch, the last CTA to arrive (a
+//     per-tile counter) sums them in split order, so results are deterministic.
+//
+// Pipeline per CTA (192 threads): warp 0 = TMA producer (+ activation scale staging), warp 1 = MMA issuer and
+// tensor-memory owner, warps 2-5 = epilogue (tcgen05.ld -> registers -> global).  Shared-memory stages
+// are handed over with mbarriers (full/empty); accumulators are double-buffered in tensor memory when they
+// fit so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Replaces, in the reference, the AOT-exported expert/FP8/FFN programs whose sources are absent
+// (native/shared/include/cuteafd_experts.h:13-44, cuteafd_fp8_moe.h:1-51) and the cuBLAS linears
+// (native/shared/cuda/linear.cu:865-1350).
+#include "common.cuh"
+
+enum { KIND_BF16 = 0, KIND_NVFP4 = 1, KIND_MXFP4 = 2 };
+enum { EPI_BF16 = 0, EPI_BF16_RESIDUAL = 1, EPI_F32 = 3 };
+
+struct TcArgs {
+  const CUtensorMap* tmA;     // [G] weight descriptors (gate weights in SWIGLU mode)
+  const CUtensorMap* tmA2;    // [G] up-weight descriptors (SWIGLU)
+  const CUtensorMap* tmB;     // activation descriptor
+  const uint8_t* const* sfa;  // [G] weight scales in the 128x4 atom layout
+  const uint8_t* const* sfa2;
+  const uint8_t* sfb;         // activation scales, row-major [rows, K / vec]
+  const float* alpha;         // [G] output scale (weight global scale x activation global scale) or null
+  const float* alpha2;
+  const int4* tiles;          // grouped: {group, first row, rows, 0}; null = dense
+  const int* n_tiles;         // grouped: number of entries in `tiles` (device)
+  void* Y;
+  const bf16* R;              // residual (EPI_BF16_RESIDUAL)
+  float* splitk_ws;           // [splits, rows_pad, N] partials (dense split-K)
+  int* splitk_cnt;            // [items * n_tiles * 4] arrival counters, zero on entry, left zero on exit
+  int* status;
+  int ldsfb, ldy, rows_total, N, K, epi, splits;
+};
+
+template <int KIND, int TN, bool SWIGLU>
+struct TcCfg {
+  static constexpr int NA = SWIGLU ? 2 : 1;
+  static constexpr int A_BYTES = 128 * 128;
+  static constexpr int B_BYTES = TN * 128;
+  static constexpr int NBLK = TN > 128 ? 2 : 1;                      // 128-token scale blocks
+  static constexpr int SF_CHUNKS = KIND == KIND_NVFP4 ? 4 : (KIND == KIND_MXFP4 ? 2 : 0);  // 512 B chunks / stage
+  static constexpr int SFA_BYTES = SF_CHUNKS * 512;
+  static constexpr int SFB_BYTES = SF_CHUNKS * 512 * NBLK;
+  static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + NA * SFA_BYTES + SFB_BYTES;
+  static constexpr int NSTAGE_RAW = (200 * 1024) / STAGE_BYTES;
+  static constexpr int NSTAGE = NSTAGE_RAW > 8 ? 8 : NSTAGE_RAW;
+  static constexpr int ACC_COLS = NA * TN;
+  static constexpr int NACC = (2 * ACC_COLS <= 384) ? 2 : 1;
+  static constexpr int SFA_COL = 448, SFA2_COL = 464, SFB_COL = 480;   // tensor-memory columns of the scales
+  static constexpr int K_ELEMS = KIND == KIND_BF16 ? 64 : 256;         // K elements per stage (128 bytes per row)
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024;
+  static_assert(NSTAGE >= 2, "tile too large for shared memory");
+  static_assert(ACC_COLS * NACC <= 448, "accumulators overlap the scale columns");
+};
+
+__device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) {
+  uint32_t d = 0;
+  if (kind == KIND_BF16) {
+    d |= 1u << 4;            // fp32 accumulator
+    d |= 1u << 7;            // A = bf16
+    d |= 1u << 10;           // B = bf16
+  } else {
+    d |= sf_id << 4;         // B scale-factor id
+    d |= 1u << 7;            // A = E2M1
+    d |= 1u << 10;           // B = E2M1
+    if (kind == KIND_MXFP4) d |= 1u << 23;   // UE8M0 scales (0 = UE4M3)
+    d |= sf_id << 29;        // A scale-factor id
+  }
+  d |= (uint32_t)(n >> 3) << 17;
+  d |= (uint32_t)(128 >> 4) << 24;
+  return d;
+}
+
+template <int KIND, int TN, bool SWIGLU>
+__global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant__ TcArgs a) {
+  using C = TcCfg<KIND, TN, SWIGLU>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[C::NSTAGE], empty_bar[C::NSTAGE], accf_bar[2], acce_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::NSTAGE; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&accf_bar[i], 1); mbar_init(&acce_bar[i], 128); }
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  const int n_items = a.tiles ? *a.n_tiles : (a.rows_total + TN - 1) / TN;
+  const int n_nt = (a.N + 127) / 128;
+  const int nkb_all = (a.K + C::K_ELEMS - 1) / C::K_ELEMS;
+  const int splits = a.splits > 1 ? a.splits : 1;
+  const int total = n_items * n_nt * splits;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    uint32_t it = 0;
+    for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x) {
+      const int sp = w % splits, tile = w / splits, item = tile / n_nt, nt = tile % n_nt;
+      int g = 0, row0 = item * TN, nrows = min(TN, a.rows_total - row0);
+      if (a.tiles) { int4 t = a.tiles[item]; g = t.x; row0 = t.y; nrows = t.z; }
+      const int kb0 = (int)(((long long)nkb_all * sp) / splits), kb1 = (int)(((long long)nkb_all * (sp + 1)) / splits);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % C::NSTAGE;
+        if (!mbar_wait_bounded(&empty_bar[s], ((it / C::NSTAGE) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, w); break; }
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        uint8_t* sA = st, *sB = st + C::NA * C::A_BYTES, *sSFA = sB + C::B_BYTES, *sSFB = sSFA + C::NA * C::SFA_BYTES;
+        if (lane == 0) {
+          mbar_expect_tx(&full_bar[s], C::NA * C::A_BYTES + C::B_BYTES + C::NA * C::SFA_BYTES);
+          const int kx = kb * (KIND == KIND_BF16 ? 64 : 128);      // elements of the descriptor's type
+          tma_load_3d(sA, a.tmA + g, &full_bar[s], kx, nt * 128, 0);
+          if (SWIGLU) tma_load_3d(sA + C::A_BYTES, a.tmA2 + g, &full_bar[s], kx, nt * 128, 0);
+          tma_load_3d(sB, a.tmB, &full_bar[s], kx, row0, 0);
+          if (KIND != KIND_BF16) {
+            const size_t off = ((size_t)nt * nkb_all + (size_t)kb) * C::SF_CHUNKS * 512;   // scales are padded to whole stages
+            bulk_load_1d(sSFA, a.sfa[g] + off, C::SFA_BYTES, &full_bar[s]);
+            if (SWIGLU) bulk_load_1d(sSFA + C::SFA_BYTES, a.sfa2[g] + off, C::SFA_BYTES, &full_bar[s]);
+          }
+        }
+        if (KIND != KIND_BF16) {
+          // Activation scales: each token owns SF_CHUNKS*4 consecutive bytes per stage in the row-major array;
+          // re-tile them into the 32x16-byte chunk layout tcgen05.cp expects.
+          constexpr int SFB_PER_STAGE = C::SF_CHUNKS * 4;
+          for (int c = lane; c < TN; c += 32) {
+            uint32_t v[4] = {0, 0, 0, 0};
+            const int row = row0 + c;
+            if (c < nrows && row < a.rows_total) {
+              const uint8_t* src = a.sfb + (size_t)row * a.ldsfb + (size_t)kb * SFB_PER_STAGE;
+              if (C::SF_CHUNKS == 4) { uint4 q = *(const uint4*)src; v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+              else { uint2 q = *(const uint2*)src; v[0] = q.x; v[1] = q.y; }
+            }
+            uint8_t* dst = sSFB + (c >> 7) * (C::SF_CHUNKS * 512) + (c & 31) * 16 + ((c & 127) >> 5) * 4;
+#pragma unroll
+            for (int q = 0; q < C::SF_CHUNKS; ++q) *(uint32_t*)(dst + q * 512) = v[q];
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t it = 0, tc = 0;
+    for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x, ++tc) {
+      const int sp = w % splits;
+      const int kb0 = (int)(((long long)nkb_all * sp) / splits), kb1 = (int)(((long long)nkb_all * (sp + 1)) / splits);
+      const int acc = tc % C::NACC;
+      if (!mbar_wait_bounded(&acce_bar[acc], ((tc / C::NACC) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, w); break; }
+      tc_fence_after();
+      const uint32_t d0 = tmem + acc * C::ACC_COLS;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % C::NSTAGE;
+        if (!mbar_wait_bounded(&full_bar[s], (it / C::NSTAGE) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, w); ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t st = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t sA = st, sB = st + C::NA * C::A_BYTES, sSFA = sB + C::B_BYTES, sSFB = sSFA + C::NA * C::SFA_BYTES;
+          if (KIND != KIND_BF16) {
+#pragma unroll
+            for (int q = 0; q < C::SF_CHUNKS; ++q) {
+              tc_cp_sf(tmem + C::SFA_COL + 4 * q, umma_desc_sf(sSFA + q * 512));
+              if (SWIGLU) tc_cp_sf(tmem + C::SFA2_COL + 4 * q, umma_desc_sf(sSFA + C::SFA_BYTES + q * 512));
+#pragma unroll
+              for (int b = 0; b < C::NBLK; ++b)
+                tc_cp_sf(tmem + C::SFB_COL + (4 * C::NBLK) * q + 4 * b, umma_desc_sf(sSFB + b * (C::SF_CHUNKS * 512) + q * 512));
+            }
+          }
+          const uint64_t adesc = umma_desc_sw128(sA), a2desc = umma_desc_sw128(sA + C::A_BYTES), bdesc = umma_desc_sw128(sB);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            if (KIND == KIND_BF16) {
+              const uint32_t id = make_idesc(KIND_BF16, TN, 0);
+              tc_mma_f16(d0, adesc + 2 * k, bdesc + 2 * k, id, accum);
+              if (SWIGLU) tc_mma_f16(d0 + TN, a2desc + 2 * k, bdesc + 2 * k, id, accum);
+            } else if (KIND == KIND_NVFP4) {
+              const uint32_t id = make_idesc(KIND_NVFP4, TN, 0);
+              tc_mma_nvf4(d0, adesc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA_COL + 4 * k, tmem + C::SFB_COL + 4 * C::NBLK * k);
+              if (SWIGLU) tc_mma_nvf4(d0 + TN, a2desc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA2_COL + 4 * k, tmem + C::SFB_COL + 4 * C::NBLK * k);
+            } else {
+              const uint32_t id = make_idesc(KIND_MXFP4, TN, (k & 1) * 2);
+              const int q = k >> 1;
+              tc_mma_mxf4(d0, adesc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA_COL + 4 * q, tmem + C::SFB_COL + 4 * C::NBLK * q);
+              if (SWIGLU) tc_mma_mxf4(d0 + TN, a2desc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA2_COL + 4 * q, tmem + C::SFB_COL + 4 * C::NBLK * q);
+            }
+          }
+          tc_commit(&empty_bar[s]);
+        }
+        __syncwarp();
+      }
+      if (!ok) break;
+      if (lane == 0) tc_commit(&accf_bar[acc]);
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q4 = warp & 3;                 // tensor-memory lane quarter this warp may read
+    const int et = q4 * 32 + lane;           // 0..127: weight row inside the tile
+    uint32_t tc = 0;
+    for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x, ++tc) {
+      const int sp = w % splits, tile = w / splits, item = tile / n_nt, nt = tile % n_nt;
+      int g = 0, row0 = item * TN, nrows = min(TN, a.rows_total - row0);
+      if (a.tiles) { int4 t = a.tiles[item]; g = t.x; row0 = t.y; nrows = t.z; }
+      nrows = min(nrows, a.rows_total - row0);
+      const int acc = tc % C::NACC;
+      if (!mbar_wait_bounded(&accf_bar[acc], (tc / C::NACC) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, w); break; }
+      tc_fence_after();
+      const int n = nt * 128 + et;
+      const bool n_ok = n < a.N;
+      const float al = a.alpha ? a.alpha[g] : 1.f;
+      const float al2 = (SWIGLU && a.alpha2) ? a.alpha2[g] : al;
+      const uint32_t tbase = tmem + ((uint32_t)(q4 * 32) << 16) + acc * C::ACC_COLS;
+      float* ws = (splits > 1) ? a.splitk_ws + ((size_t)sp * a.rows_total) * a.N : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        uint32_t r[16], r2[16];
+        tmem_ld_x16(tbase + c0, r);
+        if (SWIGLU) tmem_ld_x16(tbase + TN + c0, r2);
+        tc_wait_ld();
+        if (c0 < nrows && n_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int c = c0 + j;
+            if (c < nrows) {
+              float v = __uint_as_float(r[j]) * al;
+              if (SWIGLU) {
+                const float u = __uint_as_float(r2[j]) * al2;
+                v = v / (1.f + __expf(-v)) * u;
+              }
+              const size_t o = (size_t)(row0 + c) * a.ldy + n;
+              if (splits > 1) ws[(size_t)(row0 + c) * a.N + n] = v;
+              else if (a.epi == EPI_F32) ((float*)a.Y)[o] = v;
+              else {
+                if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
+                ((bf16*)a.Y)[o] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acce_bar[acc]);
+      if (splits > 1) {
+        // Deterministic split-K fix-up, warp by warp (no cross-warp barrier, so an aborting warp can never
+        // strand another): each warp owns 32 weight rows of the tile and a counter; the last split to
+        // arrive sums all partials in split order.
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(&a.splitk_cnt[tile * 4 + q4], 1) == splits - 1);
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          if (n_ok) {
+            for (int c = 0; c < nrows; ++c) {
+              float v = 0.f;
+              for (int p = 0; p < splits; ++p) v += __ldcg(a.splitk_ws + ((size_t)p * a.rows_total + row0 + c) * a.N + n);
+              const size_t o = (size_t)(row0 + c) * a.ldy + n;
+              if (a.epi == EPI_F32) ((float*)a.Y)[o] = v;
+              else {
+                if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
+                ((bf16*)a.Y)[o] = __float2bfloat16(v);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) a.splitk_cnt[tile * 4 + q4] = 0;
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abortp && warp == 0) {
+    // give copies already in flight time to land before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+template <int KIND, int TN, bool SWIGLU>
+static int launch(const TcArgs& a, int grid, cudaStream_t stream) {
+  using C = TcCfg<KIND, TN, SWIGLU>;
+  auto kern = tc_linear_kernel<KIND, TN, SWIGLU>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(tc_linear)");
+    attr_set[dev & 63] = true;
+  }
+  kern<<<grid, 192, C::SMEM_BYTES, stream>>>(a);
+  CA_CHECK_LAUNCH("tc_linear launch");
+  return CA_OK;
+}
+
+template <int KIND, bool SWIGLU>
+static int launch_tn(int tn, const TcArgs& a, int grid, cudaStream_t stream) {
+  switch (tn) {
+    case 16: return launch<KIND, 16, SWIGLU>(a, grid, stream);
+    case 32: return launch<KIND, 32, SWIGLU>(a, grid, stream);
+    case 64: return launch<KIND, 64, SWIGLU>(a, grid, stream);
+    case 128: return launch<KIND, 128, SWIGLU>(a, grid, stream);
+    case 256: if constexpr (!SWIGLU) return launch<KIND, 256, false>(a, grid, stream);
+    default: return ca_fail(CA_ERR_ARG, "tc_linear: unsupported token tile %d (swiglu=%d)", tn, (int)SWIGLU);
+  }
+}
+
+extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, const void* tmA2, const void* tmB,
+                                 const void* sfa, const void* sfa2, const void* sfb, int ldsfb, const float* alpha,
+                                 const float* alpha2, const void* tiles, const int* n_tiles, int max_tiles, void* Y,
+                                 const void* R, int ldy, int rows_total, int N, int K, int epi, int splits,
+                                 float* splitk_ws, int* splitk_cnt, int* status, int max_ctas, cudaStream_t stream) {
+  CA_REQUIRE(kind >= 0 && kind <= 2, "tc_linear: bad kind %d", kind);
+  CA_REQUIRE(tmA && tmB && Y, "tc_linear: null operand");
+  CA_REQUIRE(!swiglu || tmA2, "tc_linear: swiglu needs the up-projection descriptor");
+  CA_REQUIRE(kind == KIND_BF16 || (sfa && sfb && K % 32 == 0), "tc_linear: fp4 kinds need scales and K %% 32 == 0 (K=%d)", K);
+  CA_REQUIRE(kind == KIND_BF16 ? (K % 8 == 0) : true, "tc_linear: K must be a multiple of 8");
+  CA_REQUIRE(splits <= 1 || (!tiles && !swiglu && splitk_ws && splitk_cnt), "tc_linear: split-K is dense, non-swiglu only and needs scratch");
+  CA_REQUIRE(epi == EPI_BF16 || epi == EPI_BF16_RESIDUAL || epi == EPI_F32, "tc_linear: bad epilogue %d", epi);
+  CA_REQUIRE(epi != EPI_BF16_RESIDUAL || R, "tc_linear: residual epilogue needs R");
+  if (rows_total <= 0 || N <= 0) return CA_OK;
+  TcArgs a;
+  a.tmA = (const CUtensorMap*)tmA; a.tmA2 = (const CUtensorMap*)tmA2; a.tmB = (const CUtensorMap*)tmB;
+  a.sfa = (const uint8_t* const*)sfa; a.sfa2 = (const uint8_t* const*)sfa2; a.sfb = (const uint8_t*)sfb;
+  a.alpha = alpha; a.alpha2 = alpha2; a.tiles = (const int4*)tiles; a.n_tiles = n_tiles;
+  a.Y = Y; a.R = (const bf16*)R; a.splitk_ws = splitk_ws; a.splitk_cnt = splitk_cnt; a.status = status;
+  a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;
+  const int n_nt = (N + 127) / 128;
+  long long work = tiles ? (long long)max_tiles * n_nt : (long long)((rows_total + tn - 1) / tn) * n_nt * a.splits;
+  int cap = max_ctas > 0 ? max_ctas : ca_sm_count();
+  int grid = (int)(work < cap ? work : cap);
+  if (grid < 1) grid = 1;
+  if (kind == KIND_BF16) return swiglu ? launch_tn<KIND_BF16, true>(tn, a, grid, stream) : launch_tn<KIND_BF16, false>(tn, a, grid, stream);
+  if (kind == KIND_NVFP4) return swiglu ? launch_tn<KIND_NVFP4, true>(tn, a, grid, stream) : launch_tn<KIND_NVFP4, false>(tn, a, grid, stream);
+  return swiglu ? launch_tn<KIND_MXFP4, true>(tn, a, grid, stream) : launch_tn<KIND_MXFP4, false>(tn, a, grid, stream);
+}

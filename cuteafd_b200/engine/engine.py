@@ -1,0 +1,307 @@
+"""Model engine: runs prefill / decode / speculative-verify steps of a MoE decoder on one GPU (or one rank's
+share of it) by launching the native kernels on the current stream, with decode steps replayed from
+CUDA graphs keyed by their exact shape.
+
+Shape of one step (reference: Engine::step_inner, families/deepseek_v4/engine.rs:909-1241):
+  inputs  -> one packed int32 block copied H2D (tokens, positions, KV slots, per-sequence lengths, page table)
+  per layer: RMSNorm -> [act quant] -> QKV GEMM -> head-norm + RoPE + paged KV write -> paged attention ->
+             [act quant] -> O GEMM (+residual) -> RMSNorm -> router GEMM + top-k -> route pack ->
+             gather + quant into expert order -> grouped FC1 (SwiGLU fused) -> [quant] -> grouped FC2 ->
+             shared expert -> ordered weighted combine + shared + residual
+  tail    -> gather rows that need logits -> RMSNorm -> LM head GEMM -> token selection on device.
+Only token ids / status words return to the host.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..config import ModelSpec
+from ..models.weights import DeviceWeights, LayerWeights
+from ..ops import ActBuffer, KIND_BF16, pick_tn
+
+PAGE = 64
+
+
+@dataclass
+class StepShape:
+    """Static shape of a captured step."""
+    T: int            # token rows
+    n_seq: int
+    max_q_len: int
+    n_logits: int
+    attn_splits: int
+
+    def key(self):
+        return (self.T, self.n_seq, self.max_q_len, self.n_logits, self.attn_splits)
+
+
+class Lane:
+    """Activation buffers for steps of up to `cap` token rows (one lane per row bucket)."""
+
+    def __init__(self, eng: "Engine", cap: int):
+        spec, dev, w = eng.spec, eng.device, eng.weights
+        a, m, H = spec.attn, spec.moe, spec.hidden
+        self.cap = cap
+        self.tn = pick_tn(cap)
+        bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        dk, ek = eng.dense_kind, eng.expert_kind
+        self.x = bf(cap, H)
+        self.xn = bf(cap, H)
+        self.xn_act = ActBuffer.wrap_bf16(self.xn, self.tn)
+        self.xq = ActBuffer.alloc(dk, cap, H, self.tn, dev) if dk != KIND_BF16 else self.xn_act
+        qkv_n = (a.n_heads + 2 * a.n_kv_heads) * a.head_dim
+        self.qkv = bf(cap, qkv_n)
+        self.attn = bf(cap, a.n_heads * a.head_dim)
+        self.attn_q = (ActBuffer.alloc(dk, cap, a.n_heads * a.head_dim, self.tn, dev) if dk != KIND_BF16
+                       else ActBuffer.wrap_bf16(self.attn, self.tn))
+        # logits
+        self.xl = bf(cap, H)
+        self.xln = bf(cap, H)
+        self.xln_act = ActBuffer.wrap_bf16(self.xln, self.tn)
+        self.logits = torch.zeros(cap, spec.vocab, dtype=torch.float32, device=dev)
+        self.next_tok = i32(cap)
+        self.tok_status = i32(cap)
+        # shared expert / dense FFN intermediates, created on first use per width (always during the
+        # un-captured warm-up run of a shape)
+        self.ffn_bufs: dict = {}
+        self.shared = bf(cap, H)
+        # routed experts
+        if m.n_experts and eng.n_local_experts:
+            rows = cap * m.top_k
+            exp_rows = max(1, math.ceil(rows / max(1, m.n_experts)) * 2)
+            self.tn_g = pick_tn(min(exp_rows, 128), swiglu=True)
+            self.max_tiles = eng.n_local_experts + rows // self.tn_g + 1
+            self.router_logits = torch.zeros(cap, m.n_experts, dtype=torch.float32, device=dev)
+            self.idx, self.wts = i32(cap, m.top_k), torch.zeros(cap, m.top_k, dtype=torch.float32, device=dev)
+            self.src_token, self.slot_row = i32(rows), i32(cap, m.top_k)
+            self.counts, self.offsets = i32(eng.n_local_experts), i32(eng.n_local_experts)
+            self.tiles, self.n_tiles, self.n_rows = i32(self.max_tiles, 4), i32(1), i32(1)
+            self.xs = ActBuffer.alloc(ek, rows, H, self.tn_g, dev)
+            self.h1 = bf(rows, m.intermediate)
+            self.h1_q = (ActBuffer.alloc(ek, rows, m.intermediate, self.tn_g, dev) if ek != KIND_BF16
+                         else ActBuffer.wrap_bf16(self.h1, self.tn_g))
+            self.y2 = bf(rows, H)
+
+    def ffn_buf(self, eng, inter: int):
+        if inter not in self.ffn_bufs:
+            s1 = torch.zeros(self.cap, inter, dtype=torch.bfloat16, device=eng.device)
+            act = (ActBuffer.alloc(eng.dense_kind, self.cap, inter, self.tn, eng.device) if eng.dense_kind != KIND_BF16
+                   else ActBuffer.wrap_bf16(s1, self.tn))
+            self.ffn_bufs[inter] = (s1, act)
+        return self.ffn_bufs[inter]
+
+
+class Engine:
+    def __init__(self, weights: DeviceWeights, *, n_pages: int, max_seqs: int = 64, max_pages_per_seq: int = 0,
+                 expert_range: tuple | None = None, device=None, sm_count: int = 148):
+        self.weights, self.spec = weights, weights.spec
+        spec = self.spec
+        if spec.attn.kind != "gqa":
+            raise NotImplementedError("Engine: GQA models; MLA models run through engine.mla")
+        self.device = device or weights.embed.device
+        self.dense_kind = weights.layers[0].wqkv.kind
+        first_moe = next((l for l in weights.layers if l.w_gate is not None), None)
+        self.expert_kind = first_moe.w_gate.kind if first_moe is not None else KIND_BF16
+        self.expert_range = expert_range or (0, spec.moe.n_experts)
+        self.n_local_experts = first_moe.w_gate.G if first_moe is not None else 0
+        self.n_pages, self.max_seqs = n_pages, max_seqs
+        self.max_pages = max_pages_per_seq or n_pages
+        self.sm_count = sm_count
+        a = spec.attn
+        # one allocation for every layer's paged KV: [layers, slots, 2, Hkv, D]; zero-filled so masked
+        # (never-written) slots hold finite values
+        self.kv = torch.zeros(spec.n_layers, n_pages * PAGE, 2, a.n_kv_heads, a.head_dim, dtype=torch.bfloat16, device=self.device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.lanes: dict[int, Lane] = {}
+        self.graphs: dict = {}
+        self.graph_captures = 0
+        self._meta_cap = 0
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ buffers
+    def lane(self, T: int) -> Lane:
+        cap = next(c for c in (16, 64, 256, 1024, 4096, 16384) if T <= c)
+        if cap not in self.lanes:
+            self.lanes[cap] = Lane(self, cap)
+        return self.lanes[cap]
+
+    def _ensure_meta(self, T: int):
+        """Packed int32 step inputs: host (pinned) + device copies and named views."""
+        cap = max(T, 16)
+        if cap <= self._meta_cap:
+            return
+        cap = 1 << (cap - 1).bit_length()
+        S, MP = self.max_seqs, self.max_pages
+        n = 4 * cap + 3 * S + S * MP
+        self.meta_host = torch.zeros(n, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else torch.zeros(n, dtype=torch.int32)
+        self.meta_dev = torch.zeros(n, dtype=torch.int32, device=self.device)
+
+        def views(buf):
+            o = 0
+            out = {}
+            for name, cnt in (("tokens", cap), ("positions", cap), ("slot_map", cap), ("logit_rows", cap),
+                              ("kv_len", S), ("q_start", S), ("q_len", S)):
+                out[name] = buf[o:o + cnt]
+                o += cnt
+            out["page_table"] = buf[o:o + S * MP].view(S, MP)
+            return out
+        self.mh, self.md = views(self.meta_host), views(self.meta_dev)
+        self._meta_cap = cap
+        self.graphs.clear()     # views moved: captured graphs are stale
+
+    def set_inputs(self, tokens, positions, slot_map, logit_rows, kv_len, q_start, q_len, page_table_rows):
+        """Fill the pinned host block and enqueue ONE host-to-device copy."""
+        T, S = len(tokens), len(kv_len)
+        self._ensure_meta(T)
+        mh = self.mh
+        mh["tokens"][:T] = torch.as_tensor(tokens, dtype=torch.int32)
+        mh["positions"][:T] = torch.as_tensor(positions, dtype=torch.int32)
+        mh["slot_map"][:T] = torch.as_tensor(slot_map, dtype=torch.int32)
+        nl = len(logit_rows)
+        mh["logit_rows"][:nl] = torch.as_tensor(logit_rows, dtype=torch.int32)
+        mh["kv_len"][:S] = torch.as_tensor(kv_len, dtype=torch.int32)
+        mh["q_start"][:S] = torch.as_tensor(q_start, dtype=torch.int32)
+        mh["q_len"][:S] = torch.as_tensor(q_len, dtype=torch.int32)
+        for s, row in enumerate(page_table_rows):
+            mh["page_table"][s, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
+        self.meta_dev.copy_(self.meta_host, non_blocking=True)
+        return self.meta_host.numel() * 4
+
+    # ------------------------------------------------------------------ kernels
+    def _splits(self, N: int, K: int, T: int, tn: int, kind: int) -> int:
+        tiles = -(-N // 128) * -(-T // tn)
+        nkb = K // (64 if kind == KIND_BF16 else 256)
+        if tiles >= self.sm_count or nkb < 4:
+            return 1
+        return max(1, min(nkb // 2, 32, -(-2 * self.sm_count // tiles)))
+
+    def _dense(self, w, x_act, y, T, residual=None, w_up=None):
+        splits = 1 if w_up is not None else self._splits(w.N, w.K, T, x_act.tn, w.kind)
+        ops.tc_linear(w, x_act, y, rows=T, w_up=w_up, residual=residual, splits=splits, status=self.status)
+        self.launches_per_step += 1
+
+    def _quant(self, x_bf16, act: ActBuffer, T, inv_gs):
+        if act.kind == KIND_BF16:
+            return act
+        ops.quant_fp4_rows(x_bf16, act, rows=T, inv_gs=inv_gs)
+        self.launches_per_step += 1
+        return act
+
+    def _attention_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
+        spec, a, T = self.spec, self.spec.attn, sh.T
+        md = self.md
+        ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, spec.rms_eps, rows=T)
+        xq = self._quant(L.xn, L.xq, T, lw.wqkv.inv_act_gs)
+        self._dense(lw.wqkv, xq, L.qkv, T)
+        ops.qk_norm_rope_kvwrite(L.qkv, md["positions"], md["slot_map"], lw.q_norm, lw.k_norm, self.kv[li], T,
+                                 a.n_heads, a.n_kv_heads, a.head_dim, a.rope_theta, a.rope_interleaved, spec.rms_eps, self.status)
+        ops.paged_attention(L.qkv, self.kv[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
+                            T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
+                            Hkv=a.n_kv_heads, D=a.head_dim, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
+                            window=a.window, sink=lw.sink)
+        oq = self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
+        self._dense(lw.wo, oq, L.x, T, residual=L.x)
+        self.launches_per_step += 3 + (2 if sh.attn_splits > 1 else 0)
+
+    def _ffn(self, lw: LayerWeights, L: Lane, T: int, out, residual):
+        """Shared expert / dense FFN: out = residual + down(silu(gate x) * up x)."""
+        s1, s_act = L.ffn_buf(self, lw.ws_gate.N)
+        xq = self._quant(L.xn, L.xq, T, lw.ws_gate.inv_act_gs)
+        self._dense(lw.ws_gate, xq, s1, T, w_up=lw.ws_up)
+        self._quant(s1, s_act, T, lw.ws_down.inv_act_gs)
+        self._dense(lw.ws_down, s_act, out, T, residual=residual)
+
+    def _moe_layer(self, lw: LayerWeights, L: Lane, T: int):
+        spec, m = self.spec, self.spec.moe
+        ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, spec.rms_eps, rows=T)
+        self.launches_per_step += 1
+        if lw.router is None:
+            self._ffn(lw, L, T, L.x, L.x)
+            return
+        self._dense(lw.router, L.xn_act, L.router_logits, T)
+        ops.router_select(L.router_logits, lw.router_bias, L.idx, L.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                          m.n_group, m.topk_group)
+        e_lo, e_hi = self.expert_range
+        ops.route_pack(L.idx, L.src_token, L.slot_row, L.counts, L.offsets, L.tiles, L.n_tiles, L.n_rows, T, m.top_k,
+                       e_lo, e_hi, L.tn_g, L.max_tiles)
+        rows = T * m.top_k
+        if L.xs.kind == KIND_BF16:
+            ops.gather_rows(L.xn, L.src_token, L.n_rows, L.xs.data, rows)
+        else:
+            ops.quant_fp4_rows(L.xn, L.xs, src_rows=L.src_token, n_rows_dev=L.n_rows, rows=rows, inv_gs=lw.w_gate.inv_act_gs)
+        ops.tc_linear(lw.w_gate, L.xs, L.h1, rows=rows, w_up=lw.w_up, tiles=L.tiles, n_tiles=L.n_tiles, max_tiles=L.max_tiles,
+                      status=self.status)
+        if L.h1_q.kind != KIND_BF16:
+            ops.quant_fp4_rows(L.h1, L.h1_q, n_rows_dev=L.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
+            self.launches_per_step += 1
+        ops.tc_linear(lw.w_down, L.h1_q, L.y2, rows=rows, tiles=L.tiles, n_tiles=L.n_tiles, max_tiles=L.max_tiles, status=self.status)
+        shared = None
+        if lw.ws_gate is not None:
+            self._ffn(lw, L, T, L.shared, None)
+            shared = L.shared
+        ops.moe_combine(L.y2, L.slot_row, L.wts, shared, L.x, L.x, T, m.top_k)
+        self.launches_per_step += 6
+
+    def forward(self, sh: StepShape):
+        """Launch one step on the current stream.  Inputs come from the device meta block."""
+        spec, T = self.spec, sh.T
+        L = self.lane(T)
+        a = spec.attn
+        if sh.attn_splits > 1:
+            need = sh.attn_splits * T * a.n_heads
+            if getattr(self, "part_o", None) is None or self.part_o.numel() < need * a.head_dim:
+                self.part_o = torch.empty(need * a.head_dim, dtype=torch.float32, device=self.device)
+                self.part_ml = torch.empty(need * 2, dtype=torch.float32, device=self.device)
+        elif getattr(self, "part_o", None) is None:
+            self.part_o = self.part_ml = None
+        self.launches_per_step = 0
+        ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
+        self.launches_per_step += 1
+        for li in range(spec.n_layers):
+            lw = self.weights.layer(li)
+            self._attention_layer(li, lw, L, sh)
+            self._moe_layer(lw, L, T)
+        if sh.n_logits:
+            ops.gather_rows(L.x, self.md["logit_rows"], None, L.xl, sh.n_logits)
+            ops.add_rmsnorm(L.xl, None, self.weights.final_norm, L.xln, spec.rms_eps, rows=sh.n_logits)
+            ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=sh.n_logits, status=self.status)
+            ops.argmax_rows(L.logits, L.next_tok, rows=sh.n_logits, status=L.tok_status)
+            self.launches_per_step += 4
+        return L
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def attn_splits_for(self, n_seq: int, max_q_len: int, max_kv: int) -> int:
+        a = self.spec.attn
+        tpt = max(1, 16 // (a.n_heads // a.n_kv_heads))
+        ctas = a.n_kv_heads * n_seq * (-(-max_q_len // tpt))
+        pages = max(1, -(-max_kv // PAGE))
+        return max(1, min(pages, 32, -(-2 * self.sm_count // ctas))) if max_q_len <= 16 else 1
+
+    def run(self, sh: StepShape, use_graph: bool = True) -> Lane:
+        """Run a step, replaying a captured graph when one exists for this exact shape."""
+        if not use_graph:
+            return self.forward(sh)
+        key = sh.key()
+        g = self.graphs.get(key)
+        if g is None:
+            self.forward(sh)                    # warm-up launch outside capture (loads modules, sizes scratch)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                lane = self.forward(sh)
+            self.graphs[key] = g = (graph, lane, self.launches_per_step)
+            self.graph_captures += 1
+        g[0].replay()
+        self.launches_per_step = g[2]
+        return g[1]
+
+    def check_status(self):
+        word = int(self.status[0])
+        if word:
+            from ..ops.native import decode_status
+            raise RuntimeError(f"device status: {decode_status(word)}")

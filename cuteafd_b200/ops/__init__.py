@@ -1,0 +1,305 @@
+"""Tensor-level wrappers over the native sm_100a kernels.
+
+Each function validates shapes/dtypes, then launches on the current CUDA stream (so callers can capture
+whole steps into CUDA graphs).  Nothing here falls back to PyTorch math on a GPU: if the native library is
+missing the call raises.  The fp32 oracles live in `cuteafd_b200.ref`.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import native
+from .native import call, ptr, stream
+
+KIND_BF16, KIND_NVFP4, KIND_MXFP4 = 0, 1, 2
+KIND_BY_NAME = {"bf16": KIND_BF16, "nvfp4": KIND_NVFP4, "mxfp4": KIND_MXFP4}
+EPI_BF16, EPI_BF16_RESIDUAL, EPI_F32 = 0, 1, 3
+SCORING = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}
+
+
+def _chk(t: torch.Tensor, dtype, name: str):
+    if t.dtype != dtype or not t.is_cuda or not t.is_contiguous():
+        raise ValueError(f"{name}: expected contiguous CUDA {dtype}, got {t.dtype} cuda={t.is_cuda} contiguous={t.is_contiguous()}")
+
+
+# ------------------------------------------------------------------ TMA descriptors
+def encode_tmap(t: torch.Tensor, box_rows: int) -> torch.Tensor:
+    """Descriptor array (uint8 [G, 128], on t's device) for a K-major operand [G, rows, K] or [rows, K].
+    bf16 tensors describe K elements; uint8 tensors describe K bytes (packed fp4 / fp8)."""
+    if t.dim() == 2:
+        t = t.unsqueeze(0)
+    G, rows, kdim = t.shape
+    eb = {torch.bfloat16: 2, torch.uint8: 1}[t.dtype]
+    if t.stride(2) != 1:
+        raise ValueError("operand must be K-contiguous")
+    host = torch.zeros(G, 128, dtype=torch.uint8)
+    for g in range(G):
+        call("cuteafd_tmap_encode_kmajor", host[g].data_ptr(), t[g].data_ptr(), eb, kdim, rows, 1,
+             t.stride(1) * eb, 0, box_rows)
+    return host.to(t.device)
+
+
+def swizzle_sf(sf: torch.Tensor, per_stage: int = 4) -> torch.Tensor:
+    """[rows, n_sf] uint8 block scales -> flat 128x4-atom layout (any device); see ref.quant.swizzle_sf_128x4.
+    The scale count per row is zero-padded to whole pipeline stages (`per_stage` scales: 16 NVFP4, 8 MXFP4)."""
+    rows, n = sf.shape
+    R, Cc = -(-rows // 128) * 128, -(-n // per_stage) * per_stage
+    pad = sf.new_zeros(R, Cc)
+    pad[:rows, :n] = sf
+    return pad.reshape(R // 128, 4, 32, Cc // 4, 4).permute(0, 3, 2, 1, 4).contiguous().reshape(-1)
+
+
+@dataclass
+class TcWeight:
+    """Weight set for `tc_linear`: G matrices [N, K] (G > 1 = experts), K-major as checkpoints ship them."""
+    kind: int
+    G: int
+    N: int
+    K: int
+    data: torch.Tensor              # bf16 [G, N, K] | uint8 [G, N, K/2]
+    tmap: torch.Tensor              # uint8 [G, 128]
+    sf: torch.Tensor | None = None  # uint8 [G, swizzled bytes]
+    sf_ptrs: torch.Tensor | None = None
+    alpha: torch.Tensor | None = None   # fp32 [G]: weight global scale x activation global scale
+    inv_act_gs: torch.Tensor | None = None  # fp32 [1]: 1 / activation global scale (NVFP4)
+
+    @property
+    def nbytes(self) -> int:
+        return self.data.numel() * self.data.element_size() + (self.sf.numel() if self.sf is not None else 0)
+
+    @staticmethod
+    def from_master(w: torch.Tensor, kind: str | int, device, act_gs: float = 1.0 / 64) -> "TcWeight":
+        """Quantise fp32 masters [G, N, K] (or [N, K]) with the CPU oracle and upload (tests, small models)."""
+        from ..ref import quant
+        kind = KIND_BY_NAME[kind] if isinstance(kind, str) else kind
+        if w.dim() == 2:
+            w = w.unsqueeze(0)
+        G, N, K = w.shape
+        if kind == KIND_BF16:
+            data = w.to(torch.bfloat16).to(device).contiguous()
+            return TcWeight(kind, G, N, K, data, encode_tmap(data, 128))
+        packs, sfs, alphas = [], [], []
+        for g in range(G):
+            if kind == KIND_NVFP4:
+                p, s, gs = quant.nvfp4_quantize(w[g])
+                alphas.append(float(gs) * act_gs)
+            else:
+                p, s = quant.mxfp4_quantize(w[g])
+                alphas.append(1.0)
+            packs.append(p)
+            sfs.append(swizzle_sf(s, 16 if kind == KIND_NVFP4 else 8))
+        data = torch.stack(packs).to(device).contiguous()
+        sf = torch.stack(sfs).to(device).contiguous()
+        return TcWeight._finish(kind, G, N, K, data, sf, torch.tensor(alphas, dtype=torch.float32, device=device), act_gs)
+
+    @staticmethod
+    def random(G: int, N: int, K: int, kind: str | int, device, std: float = 0.02, act_gs: float = 1.0 / 64,
+               seed: int = 0) -> "TcWeight":
+        """Random-init weights generated directly in the storage format on the device (large synthetic models)."""
+        kind = KIND_BY_NAME[kind] if isinstance(kind, str) else kind
+        gen = torch.Generator(device=device).manual_seed(seed)
+        if kind == KIND_BF16:
+            data = torch.empty(G, N, K, dtype=torch.bfloat16, device=device).normal_(0, std, generator=gen)
+            return TcWeight(kind, G, N, K, data, encode_tmap(data, 128))
+        data = torch.randint(0, 256, (G, N, K // 2), dtype=torch.uint8, device=device, generator=gen)
+        vec = 16 if kind == KIND_NVFP4 else 32
+        nsf = (-(-N // 128) * 128) * (-(-K // 256) * (256 // vec))
+        if kind == KIND_NVFP4:   # E4M3 scales in [0.5, 1.875]
+            sf = torch.randint(0x30, 0x40, (G, nsf), dtype=torch.uint8, device=device, generator=gen)
+            alpha = torch.full((G,), std / 3.4 * act_gs, dtype=torch.float32, device=device)
+        else:                    # UE8M0 scales 2^-7 .. 2^-6 -> |w| ~ std
+            sf = torch.randint(120, 122, (G, nsf), dtype=torch.uint8, device=device, generator=gen)
+            alpha = torch.full((G,), std / 0.034, dtype=torch.float32, device=device)
+        return TcWeight._finish(kind, G, N, K, data, sf, alpha, act_gs)
+
+    @staticmethod
+    def _finish(kind, G, N, K, data, sf, alpha, act_gs):
+        sf_ptrs = torch.tensor([sf[g].data_ptr() for g in range(G)], dtype=torch.int64, device=data.device)
+        inv = torch.tensor([1.0 / act_gs], dtype=torch.float32, device=data.device)
+        return TcWeight(kind, G, N, K, data, encode_tmap(data, 128), sf, sf_ptrs, alpha, inv)
+
+    def dequantize(self) -> torch.Tensor:
+        """fp32 [G, N, K] on CPU, without the activation scale folded into alpha (test helper)."""
+        from ..ref import quant
+        if self.kind == KIND_BF16:
+            return self.data.float().cpu()
+        vec = 16 if self.kind == KIND_NVFP4 else 32
+        out = []
+        for g in range(self.G):
+            s = quant.unswizzle_sf_128x4(self.sf[g].cpu(), self.N, -(-self.K // 256) * (256 // vec))[:, :self.K // vec]
+            if self.kind == KIND_NVFP4:
+                gs = float(self.alpha[g]) * float(self.inv_act_gs[0])
+                out.append(quant.nvfp4_dequantize(self.data[g].cpu(), s, gs))
+            else:
+                out.append(quant.mxfp4_dequantize(self.data[g].cpu(), s) * float(self.alpha[g]))
+        return torch.stack(out)
+
+
+@dataclass
+class ActBuffer:
+    """Activation operand for `tc_linear`: bf16 rows, or fp4 rows + row-major block scales, with its TMA
+    descriptor for a token tile of `tn` rows."""
+    kind: int
+    rows: int
+    K: int
+    tn: int
+    data: torch.Tensor
+    tmap: torch.Tensor
+    sf: torch.Tensor | None = None
+
+    @staticmethod
+    def alloc(kind: int, rows: int, K: int, tn: int, device) -> "ActBuffer":
+        if kind == KIND_BF16:
+            data = torch.zeros(rows, K, dtype=torch.bfloat16, device=device)
+            return ActBuffer(kind, rows, K, tn, data, encode_tmap(data, tn))
+        vec = 16 if kind == KIND_NVFP4 else 32
+        data = torch.zeros(rows, K // 2, dtype=torch.uint8, device=device)
+        sf = torch.zeros(rows, -(-K // 256) * (256 // vec), dtype=torch.uint8, device=device)   # padded to whole stages
+        return ActBuffer(kind, rows, K, tn, data, encode_tmap(data, tn), sf)
+
+    @staticmethod
+    def wrap_bf16(x: torch.Tensor, tn: int) -> "ActBuffer":
+        _chk(x, torch.bfloat16, "x")
+        return ActBuffer(KIND_BF16, x.shape[0], x.shape[1], tn, x, encode_tmap(x, tn))
+
+
+def pick_tn(rows: int, swiglu: bool = False) -> int:
+    for tn in (16, 32, 64, 128):
+        if rows <= tn:
+            return tn
+    return 128 if swiglu else 256
+
+
+_SPLITK_WS: dict = {}
+
+
+def _splitk_scratch(device, n_float: int, n_cnt: int):
+    key = str(device)
+    ws, cnt = _SPLITK_WS.get(key, (None, None))
+    if ws is None or ws.numel() < n_float:
+        ws = torch.empty(max(n_float, 1 << 22), dtype=torch.float32, device=device)
+    if cnt is None or cnt.numel() < n_cnt:
+        cnt = torch.zeros(max(n_cnt, 1 << 16), dtype=torch.int32, device=device)
+    _SPLITK_WS[key] = (ws, cnt)
+    return ws, cnt
+
+
+def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor, *, rows: int | None = None, w_up: TcWeight | None = None,
+              residual: torch.Tensor | None = None, tiles: torch.Tensor | None = None, n_tiles: torch.Tensor | None = None,
+              max_tiles: int = 0, splits: int = 1, status: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """y[rows, N] = x[rows, K] @ w[g]^T (per tile's expert g when `tiles` is given).  `w_up` switches on the fused
+    SwiGLU epilogue (y = silu(x w^T) * (x w_up^T)).  y is bf16 (optionally + residual) or fp32."""
+    rows = x.rows if rows is None else rows
+    if w.kind != x.kind or w.K != x.K:
+        raise ValueError("tc_linear: operand kinds / K differ")
+    epi = EPI_F32 if y.dtype == torch.float32 else (EPI_BF16_RESIDUAL if residual is not None else EPI_BF16)
+    ws = cnt = None
+    if splits > 1:
+        n_items = -(-rows // x.tn)
+        ws, cnt = _splitk_scratch(y.device, splits * rows * w.N, n_items * (-(-w.N // 128)) * 4)
+    call("cuteafd_tc_linear", w.kind, 1 if w_up is not None else 0, x.tn, ptr(w.tmap), ptr(w_up.tmap) if w_up else None,
+         ptr(x.tmap), ptr(w.sf_ptrs), ptr(w_up.sf_ptrs) if w_up else None, ptr(x.sf), x.sf.shape[1] if x.sf is not None else 0,
+         ptr(w.alpha), ptr(w_up.alpha) if w_up else None, ptr(tiles), ptr(n_tiles), max_tiles, ptr(y), ptr(residual),
+         y.stride(0), rows, w.N, w.K, epi, splits, ptr(ws), ptr(cnt), ptr(status), max_ctas, stream())
+    return y
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor | None = None):
+    _chk(tokens, torch.int32, "tokens"); _chk(table, torch.bfloat16, "table")
+    call("cuteafd_embed_gather", ptr(tokens), ptr(table), ptr(out), tokens.numel(), table.shape[1], table.shape[0], ptr(status), stream())
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, y: torch.Tensor, eps: float, rows: int | None = None):
+    """x += delta (if given, in place); y = rmsnorm(x) * w."""
+    _chk(x, torch.bfloat16, "x"); _chk(w, torch.float32, "w")
+    call("cuteafd_add_rmsnorm", ptr(x), ptr(delta), ptr(w), ptr(y), x.shape[0] if rows is None else rows, x.shape[1], eps, stream())
+    return y
+
+
+def qk_norm_rope_kvwrite(qkv, positions, slot_map, q_norm, k_norm, kv_cache, T, Hq, Hkv, D, theta, interleaved, eps, status=None):
+    n_slots = kv_cache.shape[0]
+    call("cuteafd_qk_norm_rope_kvwrite", ptr(qkv), ptr(positions), ptr(slot_map), ptr(q_norm), ptr(k_norm), ptr(kv_cache),
+         T, Hq, Hkv, D, theta, 1 if interleaved else 0, eps, n_slots, ptr(status), stream())
+
+
+def quant_fp4_rows(x: torch.Tensor, out: ActBuffer, *, src_rows: torch.Tensor | None = None, n_rows_dev: torch.Tensor | None = None,
+                   rows: int | None = None, inv_gs: torch.Tensor | None = None):
+    _chk(x, torch.bfloat16, "x")
+    call("cuteafd_quant_fp4_rows", 1 if out.kind == KIND_MXFP4 else 0, ptr(x), ptr(src_rows), ptr(n_rows_dev), ptr(out.data),
+         ptr(out.sf), out.rows if rows is None else rows, out.K, x.stride(0), out.sf.shape[1], ptr(inv_gs), stream())
+    return out
+
+
+def gather_rows(x, src_rows, n_rows_dev, out, rows):
+    call("cuteafd_gather_rows", ptr(x), ptr(src_rows), ptr(n_rows_dev), ptr(out), rows, x.shape[1], stream())
+    return out
+
+
+def act_quant_fp8_ue8m0(x, q, sf):
+    call("cuteafd_act_quant_fp8_ue8m0", ptr(x), ptr(q), ptr(sf), x.shape[0], x.shape[1], stream())
+
+
+def silu_mul(g, u, out, limit: float = 0.0):
+    call("cuteafd_silu_mul", ptr(g), ptr(u), ptr(out), g.numel(), limit, stream())
+    return out
+
+
+# ------------------------------------------------------------------ MoE control
+def router_select(logits, bias, idx, wts, T, k, scoring, normalize, route_scale, n_group=1, topk_group=1):
+    _chk(logits, torch.float32, "logits")
+    call("cuteafd_router_select", ptr(logits), ptr(bias), ptr(idx), ptr(wts), T, logits.shape[1], k, SCORING[scoring],
+         1 if normalize else 0, route_scale, n_group, topk_group, stream())
+
+
+def route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles):
+    call("cuteafd_route_pack", ptr(idx), ptr(src_token), ptr(slot_row), ptr(counts), ptr(offsets), ptr(tiles), ptr(n_tiles),
+         ptr(n_rows), T, k, e_lo, e_hi, tn, max_tiles, stream())
+
+
+def moe_combine(y, slot_row, wts, shared, residual, out, T, k):
+    call("cuteafd_moe_combine", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, stream())
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def paged_attention(q, kv, page_table, kv_len, q_start, q_len, out, *, T, n_seq, max_q_len, q_stride, Hq, Hkv, D, n_splits=1,
+                    part_o=None, part_ml=None, window=0, sink=None, scale=None):
+    call("cuteafd_paged_attention", ptr(q), ptr(kv), ptr(page_table), ptr(kv_len), ptr(q_start), ptr(q_len), ptr(sink), ptr(out),
+         ptr(part_o), ptr(part_ml), T, n_seq, max_q_len, q_stride, Hq, Hkv, D, page_table.shape[1], n_splits, window,
+         float(scale if scale is not None else D ** -0.5), stream())
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def argmax_rows(logits, tok, *, rows=None, V=None, masks=None, logprob=None, status=None):
+    _chk(logits, torch.float32, "logits")
+    call("cuteafd_argmax_rows", ptr(logits), logits.stride(0), logits.shape[0] if rows is None else rows,
+         logits.shape[1] if V is None else V, ptr(masks), masks.shape[1] if masks is not None else 0, ptr(tok), ptr(logprob),
+         ptr(status), stream())
+    return tok
+
+
+def pack_sample_params(params_list, positions) -> torch.Tensor:
+    """[(temperature, top_p, top_k, min_p, seed)], positions -> uint8 [T, 32] host tensor for `sample_rows`."""
+    import struct
+    buf = bytearray()
+    for p, pos in zip(params_list, positions):
+        buf += struct.pack("<fffiQQ", p.temperature, p.top_p, p.min_p, p.top_k, p.seed & (2 ** 64 - 1), int(pos))
+    return torch.frombuffer(buf, dtype=torch.uint8).reshape(-1, 32).clone()
+
+
+def sample_rows(logits, params_dev, tok, status, *, masks=None):
+    _chk(logits, torch.float32, "logits")
+    call("cuteafd_sample_rows", ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], ptr(masks),
+         masks.shape[1] if masks is not None else 0, ptr(params_dev), ptr(tok), ptr(status), stream())
+    return tok
+
+
+def verify_accept(inputs, target, n_drafts, accepted, n_emit, eos: int = -1):
+    n_seq, width = inputs.shape
+    call("cuteafd_verify_accept", ptr(inputs), ptr(target), ptr(n_drafts), ptr(accepted), ptr(n_emit), n_seq, width, eos, stream())

@@ -1,0 +1,93 @@
+"""ctypes binding to the in-tree native library (`_native/libcuteafd_b200.so`).
+
+The library exposes a plain C ABI (`extern "C" int cuteafd_*(..., cudaStream_t)`), like the reference's
+`libcuteafd_native.so` loaded through `libloading` (rust/crates/cuteafd-ffi/src/lib.rs).  On a machine
+with a GPU a missing library is an error, never a silent fallback: `lib()` raises with the build hint.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+_LIB = None
+LIB_PATH = Path(__file__).resolve().parent.parent / "_native" / "libcuteafd_b200.so"
+
+P, I, F, L, U64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_uint64
+
+_PROTOS = {
+    "cuteafd_abi_version": [],
+    "cuteafd_device_info": [P, P, P, P, P],
+    "cuteafd_tmap_encode_kmajor": [P, P, I, U64, U64, U64, U64, U64, C.c_uint32],
+    "cuteafd_embed_gather": [P, P, P, I, I, I, P, P],
+    "cuteafd_add_rmsnorm": [P, P, P, P, I, I, F, P],
+    "cuteafd_qk_norm_rope_kvwrite": [P, P, P, P, P, P, I, I, I, I, F, I, F, I, P, P],
+    "cuteafd_quant_fp4_rows": [I, P, P, P, P, P, I, I, I, I, P, P],
+    "cuteafd_gather_rows": [P, P, P, P, I, I, P],
+    "cuteafd_act_quant_fp8_ue8m0": [P, P, P, I, I, P],
+    "cuteafd_silu_mul": [P, P, P, L, F, P],
+    "cuteafd_router_select": [P, P, P, P, I, I, I, I, I, F, I, I, P],
+    "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "cuteafd_moe_combine": [P, P, P, P, P, P, I, I, I, P],
+    "cuteafd_paged_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
+    "cuteafd_argmax_rows": [P, I, I, I, P, I, P, P, P, P],
+    "cuteafd_sample_rows": [P, I, I, I, P, I, P, P, P, P],
+    "cuteafd_verify_accept": [P, P, P, P, P, I, I, I, P],
+    "cuteafd_tc_linear": [I, I, I, P, P, P, P, P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, I, P],
+}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        if not LIB_PATH.exists():
+            raise NativeError(f"native library missing at {LIB_PATH}; run `python -m cuteafd_b200.build`")
+        _LIB = C.CDLL(str(LIB_PATH))
+        _LIB.cuteafd_last_error.restype = C.c_char_p
+        for name, args in _PROTOS.items():
+            if hasattr(_LIB, name):
+                fn = getattr(_LIB, name)
+                fn.argtypes = args
+                fn.restype = I
+    return _LIB
+
+
+def call(name: str, *args) -> None:
+    l = lib()
+    rc = getattr(l, name)(*args)
+    if rc != 0:
+        raise NativeError(f"{name} failed ({rc}): {l.cuteafd_last_error().decode()}")
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_gpu_lib():
+    """Ops call this first: with a CUDA device present the native library must be loadable."""
+    if torch.cuda.is_available():
+        lib()
+
+
+STATUS_CODES = {1: "producer wait timed out", 2: "mma wait timed out", 3: "epilogue wait timed out",
+                4: "flag wait timed out", 5: "index out of range"}
+
+
+def decode_status(word: int) -> str:
+    if word == 0:
+        return "ok"
+    return f"{STATUS_CODES.get(word >> 24, 'unknown')} (detail {word & 0xFFFFFF})"
