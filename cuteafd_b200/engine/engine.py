@@ -46,7 +46,7 @@ class Lane:
         spec, dev, w = eng.spec, eng.device, eng.weights
         a, m, H = spec.attn, spec.moe, spec.hidden
         self.cap = cap
-        self.tn = pick_tn(cap)
+        self.tn = pick_tn(cap, swiglu=True)      # <= 128 so the same descriptors serve the fused SwiGLU GEMMs
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
         i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
         dk, ek = eng.dense_kind, eng.expert_kind
