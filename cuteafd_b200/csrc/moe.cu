@@ -131,11 +131,18 @@ __global__ void route_pack_kernel(const int* __restrict__ idx, int* __restrict__
   // walks the routes in order when T*k is small; larger batches use atomics (row order inside an expert does
   // not change any result: rows are independent in the GEMM and the combine reads them by index).
   if (n <= 4096) {
-    for (int e = threadIdx.x; e < El; e += blockDim.x) {
-      int c = cur[e];
-      for (int i = 0; i < n; ++i) if (idx[i] - e_lo == e) { src_token[c] = i / k; slot_row[i] = c; ++c; }
+    // rank of route i inside its expert = number of earlier routes to the same expert (ids staged in shared memory)
+    int* sid = cur + El;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = idx[i] - e_lo;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int e = sid[i];
+      if (e < 0 || e >= El) { slot_row[i] = -1; continue; }
+      int rank = 0;
+      for (int j = 0; j < i; ++j) rank += (sid[j] == e);
+      const int c = cur[e] + rank;
+      src_token[c] = i / k; slot_row[i] = c;
     }
-    for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = idx[i] - e_lo; if (e < 0 || e >= El) slot_row[i] = -1; }
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int e = idx[i] - e_lo;
@@ -148,7 +155,7 @@ extern "C" int cuteafd_route_pack(const int* idx, int* src_token, int* slot_row,
                                   int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, cudaStream_t s) {
   CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 4096, "route_pack: bad expert range");
   CA_REQUIRE(tn >= 1, "route_pack: bad tile rows");
-  route_pack_kernel<<<1, 1024, 2 * (e_hi - e_lo) * sizeof(int), s>>>(idx, src_token, slot_row, counts, offsets, (int4*)tiles,
+  route_pack_kernel<<<1, 1024, (2 * (e_hi - e_lo) + (T * k <= 4096 ? T * k : 0)) * sizeof(int), s>>>(idx, src_token, slot_row, counts, offsets, (int4*)tiles,
                                                                     n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles);
   CA_CHECK_LAUNCH("route_pack");
   return CA_OK;

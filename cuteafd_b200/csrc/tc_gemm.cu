@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::NSTAGE; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < C::NSTAGE; ++s) { mbar_init(&full_bar[s], 33); mbar_init(&empty_bar[s], 1); }   // 1 expect_tx + 32 lanes
     for (int i = 0; i < 2; ++i) { mbar_init(&accf_bar[i], 1); mbar_init(&acce_bar[i], 128); }
     abort_flag = 0;
     fence_barrier_init();
@@ -141,24 +141,24 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
         }
         if (KIND != KIND_BF16) {
           // Activation scales: each token owns SF_CHUNKS*4 consecutive bytes per stage in the row-major array;
-          // re-tile them into the 32x16-byte chunk layout tcgen05.cp expects.
+          // cp.async moves them 4 bytes at a time straight into the 32x16-byte chunk layout tcgen05.cp expects
+          // (zero-filling rows past the tile), so the producer never waits on a global load.
           constexpr int SFB_PER_STAGE = C::SF_CHUNKS * 4;
           for (int c = lane; c < TN; c += 32) {
-            uint32_t v[4] = {0, 0, 0, 0};
             const int row = row0 + c;
-            if (c < nrows && row < a.rows_total) {
-              const uint8_t* src = a.sfb + (size_t)row * a.ldsfb + (size_t)kb * SFB_PER_STAGE;
-              if (C::SF_CHUNKS == 4) { uint4 q = *(const uint4*)src; v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
-              else { uint2 q = *(const uint2*)src; v[0] = q.x; v[1] = q.y; }
-            }
-            uint8_t* dst = sSFB + (c >> 7) * (C::SF_CHUNKS * 512) + (c & 31) * 16 + ((c & 127) >> 5) * 4;
+            const bool live = c < nrows && row < a.rows_total;
+            const uint8_t* src = live ? a.sfb + (size_t)row * a.ldsfb + (size_t)kb * SFB_PER_STAGE : a.sfb;
+            const uint32_t dst = smem_u32(sSFB + (c >> 7) * (C::SF_CHUNKS * 512) + (c & 31) * 16 + ((c & 127) >> 5) * 4);
+            const uint32_t nbytes = live ? 4u : 0u;
 #pragma unroll
-            for (int q = 0; q < C::SF_CHUNKS; ++q) *(uint32_t*)(dst + q * 512) = v[q];
+            for (int q = 0; q < C::SF_CHUNKS; ++q)
+              asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + q * 512), "l"(src + q * 4), "r"(nbytes) : "memory");
           }
-          fence_proxy_async_smem();
+          // counts as this lane's arrival once its copies have landed
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
+        } else {
+          mbar_arrive(&full_bar[s]);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_bar[s]);
       }
     }
   } else if (warp == 1) {
@@ -176,6 +176,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
         const int s = it % C::NSTAGE;
         if (!mbar_wait_bounded(&full_bar[s], (it / C::NSTAGE) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, w); ok = false; break; }
         tc_fence_after();
+        if (KIND != KIND_BF16) fence_proxy_async_smem();   // scale bytes arrived through the generic proxy (cp.async)
         if (lane == 0) {
           const uint32_t st = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t sA = st, sB = st + C::NA * C::A_BYTES, sSFA = sB + C::B_BYTES, sSFB = sSFA + C::NA * C::SFA_BYTES;
@@ -276,14 +277,32 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
         if (last) {
           __threadfence();
           if (n_ok) {
-            for (int c = 0; c < nrows; ++c) {
-              float v = 0.f;
-              for (int p = 0; p < splits; ++p) v += __ldcg(a.splitk_ws + ((size_t)p * a.rows_total + row0 + c) * a.N + n);
-              const size_t o = (size_t)(row0 + c) * a.ldy + n;
-              if (a.epi == EPI_F32) ((float*)a.Y)[o] = v;
-              else {
-                if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
-                ((bf16*)a.Y)[o] = __float2bfloat16(v);
+            // loads are issued in batches (4 rows x up to 8 splits in flight) and summed in split order
+            for (int c = 0; c < nrows; c += 4) {
+              float v[4] = {0.f, 0.f, 0.f, 0.f};
+              for (int p0 = 0; p0 < splits; p0 += 8) {
+                float t[4][8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                  for (int p = 0; p < 8; ++p)
+                    t[j][p] = (c + j < nrows && p0 + p < splits)
+                                  ? __ldcg(a.splitk_ws + ((size_t)(p0 + p) * a.rows_total + row0 + c + j) * a.N + n) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                  for (int p = 0; p < 8; ++p) v[j] += t[j][p];
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (c + j >= nrows) break;
+                const size_t o = (size_t)(row0 + c + j) * a.ldy + n;
+                float r = v[j];
+                if (a.epi == EPI_F32) ((float*)a.Y)[o] = r;
+                else {
+                  if (a.epi == EPI_BF16_RESIDUAL) r += __bfloat162float(a.R[o]);
+                  ((bf16*)a.Y)[o] = __float2bfloat16(r);
+                }
               }
             }
           }

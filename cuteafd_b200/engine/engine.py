@@ -117,6 +117,8 @@ class Engine:
         # (never-written) slots hold finite values
         self.kv = torch.zeros(spec.n_layers, n_pages * PAGE, 2, a.n_kv_heads, a.head_dim, dtype=torch.bfloat16, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # head_dim 128 runs on the tcgen05 attention kernel (one TMA descriptor per layer's K/V store)
+        self.kv_tmaps = ops.encode_kv_tmaps(self.kv) if a.head_dim == 128 and 128 % (a.n_heads // a.n_kv_heads) == 0 else None
         self.lanes: dict[int, Lane] = {}
         self.graphs: dict = {}
         self.graph_captures = 0
@@ -200,10 +202,16 @@ class Engine:
         self._dense(lw.wqkv, xq, L.qkv, T)
         ops.qk_norm_rope_kvwrite(L.qkv, md["positions"], md["slot_map"], lw.q_norm, lw.k_norm, self.kv[li], T,
                                  a.n_heads, a.n_kv_heads, a.head_dim, a.rope_theta, a.rope_interleaved, spec.rms_eps, self.status)
-        ops.paged_attention(L.qkv, self.kv[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
-                            T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
-                            Hkv=a.n_kv_heads, D=a.head_dim, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
-                            window=a.window, sink=lw.sink)
+        if self.kv_tmaps is not None:
+            ops.paged_attention_tc(L.qkv, self.kv_tmaps[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
+                                   T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
+                                   Hkv=a.n_kv_heads, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
+                                   window=a.window, sink=lw.sink, status=self.status)
+        else:
+            ops.paged_attention(L.qkv, self.kv[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
+                                T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
+                                Hkv=a.n_kv_heads, D=a.head_dim, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
+                                window=a.window, sink=lw.sink)
         oq = self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
         self._dense(lw.wo, oq, L.x, T, residual=L.x)
         self.launches_per_step += 3 + (2 if sh.attn_splits > 1 else 0)
@@ -277,7 +285,7 @@ class Engine:
     # ------------------------------------------------------------------ CUDA graphs
     def attn_splits_for(self, n_seq: int, max_q_len: int, max_kv: int) -> int:
         a = self.spec.attn
-        tpt = max(1, 16 // (a.n_heads // a.n_kv_heads))
+        tpt = max(1, (128 if self.kv_tmaps is not None else 16) // (a.n_heads // a.n_kv_heads))
         ctas = a.n_kv_heads * n_seq * (-(-max_q_len // tpt))
         pages = max(1, -(-max_kv // PAGE))
         return max(1, min(pages, 32, -(-2 * self.sm_count // ctas))) if max_q_len <= 16 else 1

@@ -275,6 +275,27 @@ def paged_attention(q, kv, page_table, kv_len, q_start, q_len, out, *, T, n_seq,
     return out
 
 
+def encode_kv_tmaps(kv: torch.Tensor) -> torch.Tensor:
+    """TMA descriptors (uint8 [layers, 128]) for a paged K/V store [layers, slots, 2, Hkv, 128] bf16."""
+    _chk(kv, torch.bfloat16, "kv")
+    L, slots, two, Hkv, D = kv.shape
+    if D != 128 or two != 2:
+        raise ValueError("tensor-core attention needs head_dim 128")
+    host = torch.zeros(L, 128, dtype=torch.uint8)
+    for l in range(L):
+        call("cuteafd_tmap_encode_kv", host[l].data_ptr(), kv[l].data_ptr(), Hkv, slots)
+    return host.to(kv.device)
+
+
+def paged_attention_tc(q, kv_map, page_table, kv_len, q_start, q_len, out, *, T, n_seq, max_q_len, q_stride, Hq, Hkv,
+                       n_splits=1, part_o=None, part_ml=None, window=0, sink=None, scale=None, status=None):
+    """Tensor-core (tcgen05) paged attention for head_dim 128; `kv_map` is one row of `encode_kv_tmaps`."""
+    call("cuteafd_paged_attention_tc", ptr(q), ptr(kv_map), ptr(page_table), ptr(kv_len), ptr(q_start), ptr(q_len), ptr(sink),
+         ptr(out), ptr(part_o), ptr(part_ml), T, n_seq, max_q_len, q_stride, Hq, Hkv, page_table.shape[1], n_splits, window,
+         float(scale if scale is not None else 128 ** -0.5), ptr(status), stream())
+    return out
+
+
 # ------------------------------------------------------------------ sampling
 def argmax_rows(logits, tok, *, rows=None, V=None, masks=None, logprob=None, status=None):
     _chk(logits, torch.float32, "logits")

@@ -32,6 +32,8 @@ _PROTOS = {
     "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "cuteafd_moe_combine": [P, P, P, P, P, P, I, I, I, P],
     "cuteafd_paged_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
+    "cuteafd_paged_attention_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "cuteafd_tmap_encode_kv": [P, P, I, U64],
     "cuteafd_argmax_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_sample_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_verify_accept": [P, P, P, P, P, I, I, I, P],

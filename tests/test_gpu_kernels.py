@@ -302,3 +302,51 @@ def test_exact_sampler_matches_oracle():
             assert int(tok[r]) in cands.tolist()
             agree += int(tok[r]) == want
     assert agree >= 6 * 24 - 2      # a draw within float rounding of a CDF boundary may differ
+
+
+# ------------------------------------------------------------------ tcgen05 attention (head_dim 128)
+@pytest.mark.parametrize("Hq,Hkv,window,use_sink", [(16, 1, 0, False), (64, 4, 0, False), (8, 8, 0, True), (32, 2, 100, False)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_paged_attention_tc(Hq, Hkv, window, use_sink, splits):
+    D = 128
+    g = torch.Generator().manual_seed(Hq * 7 + splits)
+    lens, qlens = [300, 129, 20, 64], [1, 4, 20, 9]     # decode, verify, short prefill, chunk tail
+    n_pages = 24
+    cache = torch.zeros(1, n_pages * 64, 2, Hkv, D)
+    perm = torch.randperm(n_pages - 1, generator=g) + 1
+    tables, p, ks, vs = [], 0, [], []
+    for L in lens:
+        npg = -(-L // 64)
+        pages = perm[p:p + npg].tolist()
+        p += npg
+        tables.append(pages)
+        k, v = torch.randn(L, Hkv, D, generator=g), torch.randn(L, Hkv, D, generator=g)
+        ks.append(k), vs.append(v)
+        slots = torch.tensor([pages[t // 64] * 64 + t % 64 for t in range(L)])
+        cache[0, slots, 0], cache[0, slots, 1] = k, v
+    T = sum(qlens)
+    q = torch.randn(T, Hq, D, generator=g)
+    sink = torch.randn(Hq, generator=g) if use_sink else None
+    pt = torch.zeros(len(lens), 8, dtype=torch.int32)
+    for i, row in enumerate(tables):
+        pt[i, :len(row)] = torch.tensor(row)
+    q_start = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)[:-1]), dtype=torch.int32)
+    kv_dev = cache.to(torch.bfloat16).to(DEV).contiguous()
+    maps = ops.encode_kv_tmaps(kv_dev)
+    out = torch.zeros(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+    part_o = torch.zeros(splits * T * Hq * D, dtype=torch.float32, device=DEV)
+    part_ml = torch.zeros(splits * T * Hq * 2, dtype=torch.float32, device=DEV)
+    st = status_word()
+    ops.paged_attention_tc(q.to(torch.bfloat16).to(DEV).view(T, -1).contiguous(), maps[0], pt.to(DEV),
+                           torch.tensor(lens, dtype=torch.int32, device=DEV), q_start.to(DEV),
+                           torch.tensor(qlens, dtype=torch.int32, device=DEV), out, T=T, n_seq=len(lens), max_q_len=max(qlens),
+                           q_stride=Hq * D, Hq=Hq, Hkv=Hkv, n_splits=splits, part_o=part_o, part_ml=part_ml, window=window,
+                           sink=sink.to(DEV) if use_sink else None, status=st)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    got = out.float().cpu().view(T, Hq, D)
+    for i, (L, ql) in enumerate(zip(lens, qlens)):
+        qs = int(q_start[i])
+        ref = rops.attention(bf16r(q[qs:qs + ql]), bf16r(ks[i]), bf16r(vs[i]), torch.arange(L - ql, L), torch.arange(L),
+                             window=window, sink=sink)
+        assert torch.allclose(got[qs:qs + ql], ref, atol=3e-2, rtol=3e-2), f"seq {i}: max err {(got[qs:qs + ql] - ref).abs().max()}"
