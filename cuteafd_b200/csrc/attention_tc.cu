@@ -67,14 +67,16 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   // CTAs fit on one SM.
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = (uint64_t*)(smem + 49152 + NS * 32768);
-  uint64_t* kv_full = bars; uint64_t* kv_empty = bars + NS;
-  uint64_t& s_full = bars[2 * NS]; uint64_t& p_full = bars[2 * NS + 1]; uint64_t& o_done = bars[2 * NS + 2];
-  uint32_t& tmem_slot = *(uint32_t*)(bars + 2 * NS + 3);
-  int& abort_flag = *(int*)(bars + 2 * NS + 4);
+  uint64_t* k_full = bars; uint64_t* k_empty = bars + 2; uint64_t* v_full = bars + 4; uint64_t* v_empty = bars + 6;
+  uint64_t* s_full = bars + 8;              // two score buffers
+  uint64_t& p_full = bars[10]; uint64_t& o_done = bars[11];
+  uint32_t& tmem_slot = *(uint32_t*)(bars + 12);
+  int& abort_flag = *(int*)(bars + 13);
   if (smem_u32(smem) & 1023) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, 0xA11); return; }
   uint8_t* sQ = smem;                       // 2 x [128 rows x 128 B]
   uint8_t* sP = smem + 32768;               // [128 rows x 128 B]
-  uint8_t* sKV = smem + 49152;              // NS x {K lo, K hi, V lo, V hi} x 8 KB
+  uint8_t* sK = smem + 49152;               // 2 stages x {lo, hi} x 8 KB
+  uint8_t* sV = smem + 49152 + 32768;       // 2 stages x {lo, hi} x 8 KB
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
   const int G = a.Hq / a.Hkv;
@@ -95,9 +97,13 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   const int p0 = first_page + split * per, p1 = min(last_page, p0 + per);
   const int n_tiles = max(0, p1 - p0);
 
+  const int n_live_warps = (R + 31) / 32;               // softmax warps with at least one real row
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(&s_full, 1); mbar_init(&p_full, 128); mbar_init(&o_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+    }
+    mbar_init(&p_full, 32 * n_live_warps); mbar_init(&o_done, 1);
     abort_flag = 0;
     fence_barrier_init();
   }
@@ -115,71 +121,69 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
-  const uint32_t S_COL = 0, O_COL = 64;
+  const uint32_t S0_COL = 0, O_COL = 64, S1_COL = 192;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ K/V producer
+    // ------------------------------------------------------------------ K/V producer (separate K and V rings:
+    // a K stage is free as soon as its score MMA retires, long before the matching V stage)
     for (int i = 0; i < n_tiles && !*abortp; ++i) {
-      const int s = i % NS;
-      if (!mbar_wait_bounded(&kv_empty[s], ((i / NS) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
+      const int s = i & 1, ph = ((i >> 1) & 1) ^ 1;
+      const int page = a.page_table[(size_t)seq * a.max_pages + p0 + i];
+      if (!mbar_wait_bounded(&k_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
       if (lane == 0) {
-        const int page = a.page_table[(size_t)seq * a.max_pages + p0 + i];
-        uint8_t* st = sKV + s * 32768;
-        mbar_expect_tx(&kv_full[s], 32768);
-        tma_load_3d(st, a.kv_map, &kv_full[s], 0, kvh, page * APAGE);
-        tma_load_3d(st + 8192, a.kv_map, &kv_full[s], 64, kvh, page * APAGE);
-        tma_load_3d(st + 16384, a.kv_map, &kv_full[s], 0, a.Hkv + kvh, page * APAGE);
-        tma_load_3d(st + 24576, a.kv_map, &kv_full[s], 64, a.Hkv + kvh, page * APAGE);
+        mbar_expect_tx(&k_full[s], 16384);
+        tma_load_3d(sK + s * 16384, a.kv_map, &k_full[s], 0, kvh, page * APAGE);
+        tma_load_3d(sK + s * 16384 + 8192, a.kv_map, &k_full[s], 64, kvh, page * APAGE);
+      }
+      if (!mbar_wait_bounded(&v_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
+      if (lane == 0) {
+        mbar_expect_tx(&v_full[s], 16384);
+        tma_load_3d(sV + s * 16384, a.kv_map, &v_full[s], 0, a.Hkv + kvh, page * APAGE);
+        tma_load_3d(sV + s * 16384 + 8192, a.kv_map, &v_full[s], 64, a.Hkv + kvh, page * APAGE);
       }
       __syncwarp();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // Scores are double-buffered in tensor memory: S(i+1) is computed while the softmax of tile i runs.
     const uint32_t id_s = idesc_bf16(64, 0), id_o = idesc_bf16(128, 1);
-    bool ok = n_tiles > 0;
-    if (ok) {
-      if (!mbar_wait_bounded(&kv_full[0], 0, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0); ok = false; }
+    auto issue_scores = [&](int j) -> bool {     // S[j & 1] = Q K(j)^T
+      const int s = j & 1;
+      if (!mbar_wait_bounded(&k_full[s], (j >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, j); return false; }
       tc_fence_after();
-      if (ok && lane == 0) {
-        const uint32_t k0 = smem_u32(sKV);
+      if (lane == 0) {
+        const uint32_t k0 = smem_u32(sK + s * 16384), d = tmem + (s ? S1_COL : S0_COL);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem + S_COL, desc_kmajor_sw128(smem_u32(sQ) + kb * 16384) + 2 * k, desc_kmajor_sw128(k0 + kb * 8192) + 2 * k, id_s, (kb | k) ? 1u : 0u);
-        tc_commit(&s_full);
+            tc_mma_f16(d, desc_kmajor_sw128(smem_u32(sQ) + kb * 16384) + 2 * k, desc_kmajor_sw128(k0 + kb * 8192) + 2 * k, id_s, (kb | k) ? 1u : 0u);
+        tc_commit(&s_full[s]);
+        tc_commit(&k_empty[s]);
       }
       __syncwarp();
-    }
+      return true;
+    };
+    bool ok = true;
+    for (int j = 0; ok && j < min(2, n_tiles); ++j) ok = issue_scores(j);
     for (int i = 0; ok && i < n_tiles; ++i) {
-      const int s = i % NS;
+      const int s = i & 1;
       if (!mbar_wait_bounded(&p_full, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, i); break; }
+      if (!mbar_wait_bounded(&v_full[s], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, i); break; }
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t v0 = smem_u32(sKV + s * 32768 + 16384);
+        const uint32_t v0 = smem_u32(sV + s * 16384);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           tc_mma_f16(tmem + O_COL, desc_kmajor_sw128(smem_u32(sP)) + 2 * k, desc_mnmajor_sw128(v0 + k * 2048, 8192, 1024), id_o, (i | k) ? 1u : 0u);
-        tc_commit(&kv_empty[s]);
+        tc_commit(&v_empty[s]);
         tc_commit(&o_done);
       }
       __syncwarp();
-      if (i + 1 < n_tiles) {
-        const int s1 = (i + 1) % NS;
-        if (!mbar_wait_bounded(&kv_full[s1], ((i + 1) / NS) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, i); break; }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t k0 = smem_u32(sKV + s1 * 32768);
-#pragma unroll
-          for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              tc_mma_f16(tmem + S_COL, desc_kmajor_sw128(smem_u32(sQ) + kb * 16384) + 2 * k, desc_kmajor_sw128(k0 + kb * 8192) + 2 * k, id_s, (kb | k) ? 1u : 0u);
-          tc_commit(&s_full);
-        }
-        __syncwarp();
-      }
+      if (i + 2 < n_tiles) ok = issue_scores(i + 2);   // S[i & 1] was consumed before p_full(i) completed
     }
+  } else if ((warp & 3) >= n_live_warps) {
+    // softmax warps whose 32 rows are all padding: nothing to do (their P rows only feed their own unused O rows)
   } else {
     // ------------------------------------------------------------------ softmax + epilogue: thread = row
     const int q4 = warp & 3, r = q4 * 32 + lane;
@@ -190,11 +194,11 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
-      if (!mbar_wait_bounded(&s_full, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+      if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
       tc_fence_after();
       uint32_t sr[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_x16(tmem + lane_addr + S_COL + c * 16, sr + c * 16);
+      for (int c = 0; c < 4; ++c) tmem_ld_x16(tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL) + c * 16, sr + c * 16);
       tc_wait_ld();
       const int key0 = (p0 + i) * APAGE;
       float mx = -INFINITY;

@@ -180,7 +180,9 @@ class Engine:
         nkb = K // (64 if kind == KIND_BF16 else 256)
         if tiles >= self.sm_count or nkb < 4:
             return 1
-        return max(1, min(nkb // 2, 32, -(-2 * self.sm_count // tiles)))
+        # measured on B200 (16-row decode tiles): the fix-up cost grows with the split count, the sweet spot is
+        # about one work unit per SM and never more than 8 splits
+        return max(1, min(nkb // 2, 8, self.sm_count // tiles))
 
     def _dense(self, w, x_act, y, T, residual=None, w_up=None):
         splits = 1 if w_up is not None else self._splits(w.N, w.K, T, x_act.tn, w.kind)
@@ -288,7 +290,10 @@ class Engine:
         tpt = max(1, (128 if self.kv_tmaps is not None else 16) // (a.n_heads // a.n_kv_heads))
         ctas = a.n_kv_heads * n_seq * (-(-max_q_len // tpt))
         pages = max(1, -(-max_kv // PAGE))
-        return max(1, min(pages, 32, -(-2 * self.sm_count // ctas))) if max_q_len <= 16 else 1
+        if max_q_len > 16:
+            return 1
+        # fill the machine in ONE wave (two CTAs per SM); a ragged second wave doubles the kernel's time
+        return max(1, min(pages, 32, (2 * self.sm_count) // ctas))
 
     def run(self, sh: StepShape, use_graph: bool = True) -> Lane:
         """Run a step, replaying a captured graph when one exists for this exact shape."""
