@@ -136,15 +136,16 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // of the CTA already raised `*abort_flag`; the caller then unwinds instead of spinning.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   uint64_t timeout_ns = 2000000000ull) {
-  for (int i = 0; i < 128; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  // The SM cycle counter bounds the wait (cheap to read; ~2 cycles per ns is an upper bound on the clock,
+  // so the wall-time limit is at least `timeout_ns`).
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64(), limit = (long long)timeout_ns * 2;
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > timeout_ns) { *abort_flag = 1; return false; }
+    if (clock64() - t0 > limit) { *abort_flag = 1; return false; }
   }
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }

@@ -112,12 +112,16 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
   const int nkb_all = (a.K + C::K_ELEMS - 1) / C::K_ELEMS;
   const int splits = a.splits > 1 ? a.splits : 1;
   const int total = n_items * n_nt * splits;
+  // Each CTA takes one contiguous run of work units: consecutive units share the expert (TMA descriptor,
+  // activation rows, scale rows) and walk the weight matrix in address order.
+  const int chunk = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int w_begin = min(total, (int)blockIdx.x * chunk), w_end = min(total, w_begin + chunk);
   volatile int* abortp = &abort_flag;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     uint32_t it = 0;
-    for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x) {
+    for (int w = w_begin; w < w_end && !*abortp; ++w) {
       const int sp = w % splits, tile = w / splits, item = tile / n_nt, nt = tile % n_nt;
       int g = 0, row0 = item * TN, nrows = min(TN, a.rows_total - row0);
       if (a.tiles) { int4 t = a.tiles[item]; g = t.x; row0 = t.y; nrows = t.z; }
@@ -164,7 +168,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     uint32_t it = 0, tc = 0;
-    for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x, ++tc) {
+    for (int w = w_begin; w < w_end && !*abortp; ++w, ++tc) {
       const int sp = w % splits;
       const int kb0 = (int)(((long long)nkb_all * sp) / splits), kb1 = (int)(((long long)nkb_all * (sp + 1)) / splits);
       const int acc = tc % C::NACC;
@@ -222,7 +226,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
     const int q4 = warp & 3;                 // tensor-memory lane quarter this warp may read
     const int et = q4 * 32 + lane;           // 0..127: weight row inside the tile
     uint32_t tc = 0;
-    for (int w = blockIdx.x; w < total && !*abortp; w += gridDim.x, ++tc) {
+    for (int w = w_begin; w < w_end && !*abortp; ++w, ++tc) {
       const int sp = w % splits, tile = w / splits, item = tile / n_nt, nt = tile % n_nt;
       int g = 0, row0 = item * TN, nrows = min(TN, a.rows_total - row0);
       if (a.tiles) { int4 t = a.tiles[item]; g = t.x; row0 = t.y; nrows = t.z; }
