@@ -203,3 +203,38 @@ extern "C" int cuteafd_paged_attention(const void* q, const void* kv, const int*
   }
   return CA_OK;
 }
+
+// ---------------------------------------------------------------- allocation-free variant (see no_alloc.h)
+#include "no_alloc.h"
+
+// Split-KV scratch owned by the library.  In host code this name is only a stand-in for the symbol, never a
+// device address: the address is looked up once per device below and that pointer is what kernels receive.
+static __device__ __align__(256) float g_noalloc_scratch[CUTEAFD_NOALLOC_SCRATCH_FLOATS];
+static float* g_noalloc_ptr[64] = {nullptr};
+
+extern "C" int cuteafd_paged_attention_noalloc(const void* q, const void* kv, const int* page_table, const int* kv_len,
+                                               const int* q_start, const int* q_len, const float* sink, void* out, int T, int n_seq,
+                                               int max_q_len, int q_stride, int Hq, int Hkv, int D, int max_pages, int n_splits,
+                                               int window, float scale, cudaStream_t stream) {
+  CA_REQUIRE(n_splits >= 1 && T >= 0 && Hq > 0 && D > 0, "paged_attention_noalloc: bad shape");
+  const unsigned long long n_o = (unsigned long long)n_splits * T * Hq * D, n_ml = (unsigned long long)n_splits * T * Hq * 2;
+  if (n_o + n_ml > CUTEAFD_NOALLOC_SCRATCH_FLOATS)
+    return ca_fail(CA_ERR_ARG, "paged_attention_noalloc: %llu scratch floats needed (splits %d x rows %d x heads %d x (%d + 2)) but the "
+                   "built-in scratch holds %u; use fewer splits or the entry point that takes caller scratch",
+                   n_o + n_ml, n_splits, T, Hq, D, (unsigned)CUTEAFD_NOALLOC_SCRATCH_FLOATS);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return ca_cuda(e, "cudaGetDevice");
+  CA_REQUIRE(dev >= 0 && dev < 64, "paged_attention_noalloc: device index %d out of range", dev);
+  if (!g_noalloc_ptr[dev]) {
+    // first call on this device (it is the current device): resolve the symbol to its device address
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return ca_cuda(e, "cudaGetSymbolAddress(scratch)");
+    g_noalloc_ptr[dev] = p;
+  }
+  float* part_o = g_noalloc_ptr[dev];
+  float* part_ml = part_o + n_o;
+  return cuteafd_paged_attention(q, kv, page_table, kv_len, q_start, q_len, sink, out, part_o, part_ml, T, n_seq, max_q_len,
+                                 q_stride, Hq, Hkv, D, max_pages, n_splits, window, scale, stream);
+}
