@@ -108,7 +108,7 @@ extern "C" int cuteafd_router_select(const float* logits, const float* bias, int
 __global__ void route_pack_kernel(const int* __restrict__ idx, int* __restrict__ src_token, int* __restrict__ slot_row,
                                   int* __restrict__ counts, int* __restrict__ offsets, int4* __restrict__ tiles,
                                   int* __restrict__ n_tiles, int* __restrict__ n_rows, int T, int k, int e_lo, int e_hi, int tn,
-                                  int max_tiles) {
+                                  int max_tiles, int* __restrict__ src_route) {
   extern __shared__ int sh[];   // [E_local] counts, [E_local] offsets/cursors
   const int El = e_hi - e_lo;
   int* cnt = sh; int* cur = sh + El;
@@ -142,21 +142,22 @@ __global__ void route_pack_kernel(const int* __restrict__ idx, int* __restrict__
       for (int j = 0; j < i; ++j) rank += (sid[j] == e);
       const int c = cur[e] + rank;
       src_token[c] = i / k; slot_row[i] = c;
+      if (src_route) src_route[c] = i;
     }
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int e = idx[i] - e_lo;
-      if (e >= 0 && e < El) { const int c = atomicAdd(&cur[e], 1); src_token[c] = i / k; slot_row[i] = c; } else slot_row[i] = -1;
+      if (e >= 0 && e < El) { const int c = atomicAdd(&cur[e], 1); src_token[c] = i / k; slot_row[i] = c; if (src_route) src_route[c] = i; } else slot_row[i] = -1;
     }
   }
 }
 
 extern "C" int cuteafd_route_pack(const int* idx, int* src_token, int* slot_row, int* counts, int* offsets, void* tiles,
-                                  int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, cudaStream_t s) {
+                                  int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, int* src_route, cudaStream_t s) {
   CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 4096, "route_pack: bad expert range");
   CA_REQUIRE(tn >= 1, "route_pack: bad tile rows");
   route_pack_kernel<<<1, 1024, (2 * (e_hi - e_lo) + (T * k <= 4096 ? T * k : 0)) * sizeof(int), s>>>(idx, src_token, slot_row, counts, offsets, (int4*)tiles,
-                                                                    n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles);
+                                                                    n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route);
   CA_CHECK_LAUNCH("route_pack");
   return CA_OK;
 }

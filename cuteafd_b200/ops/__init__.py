@@ -256,9 +256,9 @@ def router_select(logits, bias, idx, wts, T, k, scoring, normalize, route_scale,
          1 if normalize else 0, route_scale, n_group, topk_group, stream())
 
 
-def route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles):
+def route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route=None):
     call("cuteafd_route_pack", ptr(idx), ptr(src_token), ptr(slot_row), ptr(counts), ptr(offsets), ptr(tiles), ptr(n_tiles),
-         ptr(n_rows), T, k, e_lo, e_hi, tn, max_tiles, stream())
+         ptr(n_rows), T, k, e_lo, e_hi, tn, max_tiles, ptr(src_route), stream())
 
 
 def moe_combine(y, slot_row, wts, shared, residual, out, T, k):

@@ -29,7 +29,7 @@ _PROTOS = {
     "cuteafd_act_quant_fp8_ue8m0": [P, P, P, I, I, P],
     "cuteafd_silu_mul": [P, P, P, L, F, P],
     "cuteafd_router_select": [P, P, P, P, I, I, I, I, I, F, I, I, P],
-    "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "cuteafd_moe_combine": [P, P, P, P, P, P, I, I, I, P],
     "cuteafd_paged_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
     "cuteafd_paged_attention_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
@@ -37,6 +37,15 @@ _PROTOS = {
     "cuteafd_argmax_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_sample_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_verify_accept": [P, P, P, P, P, I, I, I, P],
+    "cuteafd_ipc_export": [P, P, P],
+    "cuteafd_ipc_open": [P, C.c_ulonglong, P],
+    "cuteafd_ipc_close": [P, C.c_ulonglong],
+    "cuteafd_step_begin": [P, P],
+    "cuteafd_wait_flags": [P, I, I, P, C.c_uint, C.c_ulonglong, P, P],
+    "cuteafd_push_bytes": [P, P, C.c_size_t, P, P, C.c_uint, P, P],
+    "cuteafd_wait_add": [P, P, P, P, C.c_size_t, I, P, P, C.c_uint, C.c_ulonglong, P, P],
+    "cuteafd_dispatch_push": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
+    "cuteafd_combine_push": [P, P, P, P, P, P, P, I, I, I, C.c_uint, P],
     "cuteafd_tc_linear": [I, I, I, P, P, P, P, P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, I, P],
 }
 
