@@ -40,7 +40,7 @@ def run_decode_bench(args, rank: int, world: int, local: int, clocks) -> dict:
     spec = qwen3_235b_spec(args.layers or 94)
     batch = args.batch_per_gpu * world
     if world > 1:
-        from ..parallel.afd import run_decode_bench_distributed
+        from ..parallel.runner import run_decode_bench_distributed
         return run_decode_bench_distributed(args, spec, rank, world, local, clocks)
 
     t0 = time.time()

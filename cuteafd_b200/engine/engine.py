@@ -297,11 +297,16 @@ class Engine:
 
     def run(self, sh: StepShape, use_graph: bool = True) -> Lane:
         """Run a step, replaying a captured graph when one exists for this exact shape."""
+        hook = getattr(self, "on_real_step", None)      # multi-rank runs announce every executed step to their peers
         if not use_graph:
+            if hook:
+                hook(sh)
             return self.forward(sh)
         key = sh.key()
         g = self.graphs.get(key)
         if g is None:
+            if hook:
+                hook(sh)
             self.forward(sh)                    # warm-up launch outside capture (loads modules, sizes scratch)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -309,6 +314,8 @@ class Engine:
                 lane = self.forward(sh)
             self.graphs[key] = g = (graph, lane, self.launches_per_step)
             self.graph_captures += 1
+        if hook:
+            hook(sh)
         g[0].replay()
         self.launches_per_step = g[2]
         return g[1]

@@ -75,7 +75,7 @@ class DeviceWeights:
         return self.layers[self.layer_map[i]]
 
     def nbytes(self) -> int:
-        return sum(l.nbytes() for l in self.layers) + self.embed.numel() * 2 + self.lm_head.nbytes
+        return sum(l.nbytes() for l in self.layers) + self.embed.numel() * 2 + (self.lm_head.nbytes if self.lm_head else 0)
 
     # ------------------------------------------------------------------ from fp32 masters
     @staticmethod
@@ -168,8 +168,14 @@ class DeviceWeights:
             s = seed * 1000 + i * 16
             R = lambda G, N, K, kind, j: TcWeight.random(G, N, K, kind, device, spec.init_std, act_gs, s + j)
             out = LayerWeights(attn_norm=ones(h), ffn_norm=ones(h),
-                               wqkv=R(1, (a.n_heads + 2 * a.n_kv_heads) * a.head_dim, h, dk, 0),
-                               wo=R(1, h, a.n_heads * a.head_dim, dk, 1))
+                               wqkv=R(1, (a.n_heads + 2 * a.n_kv_heads) * a.head_dim, h, dk, 0) if with_attention else None,
+                               wo=R(1, h, a.n_heads * a.head_dim, dk, 1) if with_attention else None)
+            if not with_attention:      # expert rank: routed experts only
+                if spec.is_moe_layer(i) and e_hi > e_lo:
+                    out.w_gate = R(e_hi - e_lo, m.intermediate, h, ek, 3)
+                    out.w_up = R(e_hi - e_lo, m.intermediate, h, ek, 4)
+                    out.w_down = R(e_hi - e_lo, h, m.intermediate, ek, 5)
+                return out
             if a.qk_norm:
                 out.q_norm, out.k_norm = ones(a.head_dim), ones(a.head_dim)
             if spec.is_moe_layer(i):
@@ -189,10 +195,12 @@ class DeviceWeights:
             return out
 
         gen = torch.Generator(device=device).manual_seed(seed)
-        embed = torch.empty(spec.vocab, h, dtype=torch.bfloat16, device=device).normal_(0, spec.init_std, generator=gen)
-        dw = DeviceWeights(spec=spec, embed=embed, final_norm=ones(h),
-                           lm_head=TcWeight.random(1, spec.vocab, h, "bf16", device, spec.init_std, act_gs, seed + 7),
-                           act_gs=act_gs)
+        if with_attention:
+            embed = torch.empty(spec.vocab, h, dtype=torch.bfloat16, device=device).normal_(0, spec.init_std, generator=gen)
+            head = TcWeight.random(1, spec.vocab, h, "bf16", device, spec.init_std, act_gs, seed + 7)
+        else:
+            embed, head = torch.zeros(8, h, dtype=torch.bfloat16, device=device), None
+        dw = DeviceWeights(spec=spec, embed=embed, final_norm=ones(h), lm_head=head, act_gs=act_gs)
         dw.layers = [make_layer(i) for i in range(n_sets)]
         dw.layer_map = [i % n_sets for i in range(spec.n_layers)]
         return dw

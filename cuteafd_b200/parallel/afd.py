@@ -1,0 +1,307 @@
+"""Attention/FFN disaggregation inside one NVSwitch node.
+
+Ranks split into an attention group (TP over heads; holds embeddings, attention, router, shared expert, LM head and
+the KV cache) and an expert group (expert-parallel routed experts).  Per MoE layer:
+
+  attention rank:  ... -> router top-k -> route pack (replicated, deterministic) -> DISPATCH: quantise my half of the
+                   tokens and store the rows straight into the owning expert ranks' slabs over NVLink (+ flag)
+                   -> shared expert meanwhile -> wait COMBINE flags -> ordered weighted top-k sum + shared + residual
+  expert rank:     wait DISPATCH flags -> route pack of its own expert range on the received routing table ->
+                   grouped FC1 (SwiGLU) -> quant -> grouped FC2 (tcgen05, TMA from the LOCAL slab) ->
+                   COMBINE: store every output row into [token][slot] of both attention ranks (+ flag)
+  attention TP2:   wo partial -> push to the peer + flag -> wait -> add in rank order (bit-identical on both ranks)
+
+`comm="p2p"` uses the peer-memory kernels of `csrc/peer.cu`; `comm="nccl"` is the baseline that only calls NCCL
+(broadcast activations + routes, all-reduce expert partial sums, all-reduce attention partials).
+
+Reference: the coordinator/Spark split (families/deepseek_v4/engine.rs:1036-1191, 2047-2133), TP2 head split
+(engine.rs:1524-1552), ordered combine (native/shared/include/cuteafd_experts.h:136-183).
+"""
+from __future__ import annotations
+
+import dataclasses
+import time
+
+import torch
+
+from .. import ops
+from ..config import Deployment, ModelSpec, default_deployment
+from ..engine.engine import Engine, Lane, StepShape, PAGE
+from ..models.weights import DeviceWeights, LayerWeights
+from ..ops import ActBuffer, KIND_BF16, KIND_NVFP4, pick_tn
+from . import peer_ops
+from .symm import SymmetricBlock
+
+PH_DISPATCH, PH_COMBINE, PH_TP = 0, 1, 2
+
+
+def local_attention_spec(spec: ModelSpec, tp: int) -> ModelSpec:
+    a = spec.attn
+    if a.n_heads % tp or a.n_kv_heads % tp:
+        raise ValueError(f"heads ({a.n_heads}/{a.n_kv_heads}) do not split over tp={tp}")
+    return spec.replace(attn=dataclasses.replace(a, n_heads=a.n_heads // tp, n_kv_heads=a.n_kv_heads // tp))
+
+
+def make_block(spec: ModelSpec, dep: Deployment, t_max: int, expert_kind: int, rank: int, device, group) -> SymmetricBlock:
+    """Symmetric regions (same layout on every rank; each role uses its part)."""
+    H, k = spec.hidden, spec.moe.top_k
+    rows = t_max * k
+    row_bytes = H * 2 if expert_kind == KIND_BF16 else H // 2
+    vec = 16 if expert_kind == KIND_NVFP4 else 32
+    sf_ld = -(-H // 256) * (256 // vec)
+    regions = {
+        "slab_q": rows * row_bytes, "slab_sf": rows * sf_ld, "idx": rows * 4,
+        "y_recv": rows * H * 2, "tp_recv": 2 * t_max * H * 2,
+        "flags": 3 * spec.n_layers * 8 * 4,
+    }
+    return SymmetricBlock(regions, device, group, rank, dep.world)
+
+
+def flag_offset(spec: ModelSpec, phase: int, layer: int, src: int) -> int:
+    return ((phase * spec.n_layers + layer) * 8 + src) * 4
+
+
+class AttnRankEngine(Engine):
+    """Engine of one attention rank: local heads, replicated residual stream, routed experts remote."""
+
+    def __init__(self, spec: ModelSpec, dep: Deployment, rank: int, device, *, t_max: int, n_pages: int, max_seqs: int,
+                 max_pages_per_seq: int, comm: str, block: SymmetricBlock | None, expert_kind: int, act_gs: float = 1.0 / 64, seed: int = 1):
+        self.full_spec, self.dep, self.rank, self.comm, self.block = spec, dep, rank, comm, block
+        self.tp, self.tp_rank = dep.tp, dep.attn_ranks.index(rank)
+        lw = DeviceWeights.random(local_attention_spec(spec, self.tp), device, seed=seed, experts_range=(0, 0), act_gs=act_gs)
+        super().__init__(lw, n_pages=n_pages, max_seqs=max_seqs, max_pages_per_seq=max_pages_per_seq, device=device)
+        self.remote_kind = expert_kind
+        self.t_max = t_max
+        m, H = spec.moe, spec.hidden
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=device)
+        self.ctl = torch.zeros(4, dtype=torch.int32, device=device)
+        self.done = torch.zeros(8, dtype=torch.int32, device=device)
+        self.inv_gs = torch.tensor([1.0 / act_gs], dtype=torch.float32, device=device)
+        rows = t_max * m.top_k
+        self.router_logits = torch.zeros(t_max, m.n_experts, dtype=torch.float32, device=device)
+        self.idx, self.wts = i32(t_max, m.top_k), torch.zeros(t_max, m.top_k, dtype=torch.float32, device=device)
+        self.src_token, self.slot_row = i32(rows), i32(t_max, m.top_k)
+        self.counts, self.offsets = i32(m.n_experts), i32(m.n_experts)
+        self.tiles, self.n_tiles, self.n_rows = i32(m.n_experts + rows + 1, 4), i32(1), i32(1)
+        self.identity_rows = torch.arange(rows, dtype=torch.int32, device=device).view(t_max, m.top_k).contiguous()
+        self.part = torch.zeros(t_max, H, dtype=torch.bfloat16, device=device)
+        self.e_local = m.n_experts // dep.ep
+        if block is not None:
+            vec = 16 if expert_kind == KIND_NVFP4 else 32
+            self.sf_ld = -(-H // 256) * (256 // vec)
+            self.slab_q_tbl = block.ptr_table(dep.expert_ranks, "slab_q")
+            self.slab_sf_tbl = block.ptr_table(dep.expert_ranks, "slab_sf")
+            self.idx_tbl = block.ptr_table(dep.expert_ranks, "idx")
+            self.y_recv = block.local("y_recv", torch.bfloat16, (rows, H))
+            self.tp_recv = block.local("tp_recv", torch.bfloat16, (2, t_max, H))
+
+    # -- attention with the TP all-reduce of the output projection
+    def _attention_layer(self, li, lw, L, sh):
+        if self.tp == 1:
+            return super()._attention_layer(li, lw, L, sh)
+        spec, a, T = self.spec, self.spec.attn, sh.T
+        md = self.md
+        ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, spec.rms_eps, rows=T)
+        xq = self._quant(L.xn, L.xq, T, lw.wqkv.inv_act_gs)
+        self._dense(lw.wqkv, xq, L.qkv, T)
+        ops.qk_norm_rope_kvwrite(L.qkv, md["positions"], md["slot_map"], lw.q_norm, lw.k_norm, self.kv[li], T,
+                                 a.n_heads, a.n_kv_heads, a.head_dim, a.rope_theta, a.rope_interleaved, spec.rms_eps, self.status)
+        ops.paged_attention_tc(L.qkv, self.kv_tmaps[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
+                               T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
+                               Hkv=a.n_kv_heads, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
+                               window=a.window, sink=lw.sink, status=self.status)
+        oq = self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
+        self._dense(lw.wo, oq, self.part, T)                      # partial sum over my heads
+        self.launches_per_step += 4
+        self._tp_allreduce(li, self.part, L.x, T)
+
+    def _tp_allreduce(self, li, part, x, T):
+        """x += part(rank 0) + part(rank 1), identical bits on both ranks."""
+        H = self.full_spec.hidden
+        if self.comm == "nccl":
+            import torch.distributed as dist
+            dist.all_reduce(part[:T], group=self.tp_group)
+            x[:T] += part[:T]
+            return
+        peer = self.dep.attn_ranks[1 - self.tp_rank]
+        buf = li & 1
+        nbytes = T * H * 2
+        peer_ops.push_bytes(part, self.block.peer_ptr(peer, "tp_recv", buf * self.t_max * H * 2), nbytes,
+                            self.block.peer_ptr(peer, "flags", flag_offset(self.full_spec, PH_TP, li, self.tp_rank)),
+                            self.ctl, 0, self.done[0:1])
+        peer_ops.wait_add(part, self.tp_recv[buf], x, x, T * H, self.tp_rank,
+                          self.block.peer_ptr(self.rank, "flags", flag_offset(self.full_spec, PH_TP, li, 1 - self.tp_rank)),
+                          self.ctl, 0, self.status)
+        self.launches_per_step += 2
+
+    # -- FFN: router local, routed experts remote
+    def _moe_layer_at(self, li, lw, L, T):
+        spec, m, dep = self.full_spec, self.full_spec.moe, self.dep
+        ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, spec.rms_eps, rows=T)
+        self._dense(lw.router, L.xn_act, self.router_logits, T)
+        ops.router_select(self.router_logits, lw.router_bias, self.idx, self.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                          m.n_group, m.topk_group)
+        self.launches_per_step += 2
+        shared = None
+        if self.comm == "nccl":
+            return self._moe_nccl(li, lw, L, T)
+        ops.route_pack(self.idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
+                       T, m.top_k, 0, m.n_experts, 1 << 20, self.tiles.shape[0])
+        # my share of the tokens (the other attention rank sends the rest; both hold identical activations)
+        per = -(-T // self.tp)
+        t0, t1 = min(T, self.tp_rank * per), min(T, (self.tp_rank + 1) * per)
+        flag_tbl = self.block.ptr_table(dep.expert_ranks, "flags", flag_offset(spec, PH_DISPATCH, li, self.tp_rank))
+        peer_ops.dispatch_push(L.xn, self.idx, self.slot_row, self.offsets, self.slab_q_tbl, self.slab_sf_tbl, self.idx_tbl, flag_tbl,
+                               self.inv_gs, self.ctl, self.done[1:2], t0, t1, spec.hidden, m.top_k, self.e_local, dep.ep,
+                               self.remote_kind, self.sf_ld, self.t_max * m.top_k, 0, self.status)
+        self._keep.append(flag_tbl)
+        if lw.ws_gate is not None:
+            self._ffn(lw, L, T, L.shared, None)
+            shared = L.shared
+        peer_ops.wait_flags(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_COMBINE, li, 0)), dep.ep, 1, self.ctl, 0, self.status)
+        ops.moe_combine(self.y_recv, self.identity_rows, self.wts, shared, L.x, L.x, T, m.top_k)
+        self.launches_per_step += 4
+
+    def _moe_nccl(self, li, lw, L, T):
+        import torch.distributed as dist
+        m, H = self.full_spec.moe, self.full_spec.hidden
+        src = self.dep.attn_ranks[0]
+        dist.broadcast(L.xn[:T], src)
+        dist.broadcast(self.idx[:T], src)
+        dist.broadcast(self.wts[:T], src)
+        acc = torch.zeros(T, H, dtype=torch.bfloat16, device=self.device)
+        dist.all_reduce(acc)                      # expert ranks contribute their weighted partial sums
+        if lw.ws_gate is not None:
+            self._ffn(lw, L, T, L.shared, None)
+            acc += L.shared[:T]
+        L.x[:T] += acc
+
+    def forward(self, sh: StepShape):
+        self._keep = []          # ctypes tables referenced by launches of this step
+        self._layer_cursor = 0
+        if self.block is not None and self.comm == "p2p":
+            peer_ops.step_begin(self.ctl)
+        return super().forward(sh)
+
+    def _moe_layer(self, lw, L, T):
+        li = self._layer_cursor
+        self._layer_cursor += 1
+        if lw.router is None:
+            return super()._moe_layer(lw, L, T)
+        return self._moe_layer_at(li, lw, L, T)
+
+
+class ExpertRankWorker:
+    """One expert-parallel rank: receives dispatched rows, runs its experts, returns rows to the attention ranks."""
+
+    def __init__(self, spec: ModelSpec, dep: Deployment, rank: int, device, *, t_max: int, comm: str, block: SymmetricBlock | None,
+                 act_gs: float = 1.0 / 64, seed: int = 1):
+        self.spec, self.dep, self.rank, self.comm, self.block, self.device = spec, dep, rank, comm, block, device
+        self.ep_rank = dep.expert_ranks.index(rank)
+        m = spec.moe
+        self.e_local = m.n_experts // dep.ep
+        self.e_lo, self.e_hi = self.ep_rank * self.e_local, (self.ep_rank + 1) * self.e_local
+        self.weights = DeviceWeights.random(spec, device, seed=seed, experts_range=(self.e_lo, self.e_hi), with_attention=False, act_gs=act_gs)
+        self.kind = next(l.w_gate.kind for l in self.weights.layers if l.w_gate is not None)
+        self.t_max, H, k = t_max, spec.hidden, m.top_k
+        rows = t_max * k
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.ctl, self.done = i32(4), i32(8)
+        self.tn = pick_tn(min(max(1, -(-rows // m.n_experts) * 2), 128), swiglu=True)
+        self.max_tiles = self.e_local + rows // self.tn + 1
+        self.src_token, self.src_route, self.slot_row = i32(rows), i32(rows), i32(t_max, k)
+        self.counts, self.offsets = i32(self.e_local), i32(self.e_local)
+        self.tiles, self.n_tiles, self.n_rows = i32(self.max_tiles, 4), i32(1), i32(1)
+        self.h1 = torch.zeros(rows, m.intermediate, dtype=torch.bfloat16, device=device)
+        self.h1_q = (ActBuffer.alloc(self.kind, rows, m.intermediate, self.tn, device) if self.kind != KIND_BF16
+                     else ActBuffer.wrap_bf16(self.h1, self.tn))
+        self.y2 = torch.zeros(rows, H, dtype=torch.bfloat16, device=device)
+        self.launches_per_step = 0
+        if block is not None:
+            if self.kind == KIND_BF16:
+                data = block.local("slab_q", torch.bfloat16, (rows, H))
+                self.xs = ActBuffer(self.kind, rows, H, self.tn, data, ops.encode_tmap(data, self.tn))
+            else:
+                vec = 16 if self.kind == KIND_NVFP4 else 32
+                data = block.local("slab_q", torch.uint8, (rows, H // 2))
+                sf = block.local("slab_sf", torch.uint8, (rows, -(-H // 256) * (256 // vec)))
+                self.xs = ActBuffer(self.kind, rows, H, self.tn, data, ops.encode_tmap(data, self.tn), sf)
+            self.idx = block.local("idx", torch.int32, (t_max, k))
+            self.recv_tbl = block.ptr_table(dep.attn_ranks, "y_recv")
+        else:
+            self.xs = ActBuffer.alloc(self.kind, rows, H, self.tn, device)
+            self.idx = i32(t_max, k)
+        self._keep = []
+
+    def layer(self, li: int, T: int):
+        spec, m, dep = self.spec, self.spec.moe, self.dep
+        lw = self.weights.layer(li)
+        if lw.w_gate is None:
+            return
+        rows = T * m.top_k
+        if self.comm == "nccl":
+            return self._layer_nccl(li, lw, T)
+        peer_ops.wait_flags(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_DISPATCH, li, 0)), dep.tp, 1, self.ctl, 0, self.status)
+        ops.route_pack(self.idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
+                       T, m.top_k, self.e_lo, self.e_hi, self.tn, self.max_tiles, src_route=self.src_route)
+        ops.tc_linear(lw.w_gate, self.xs, self.h1, rows=rows, w_up=lw.w_up, tiles=self.tiles, n_tiles=self.n_tiles,
+                      max_tiles=self.max_tiles, status=self.status)
+        if self.kind != KIND_BF16:
+            ops.quant_fp4_rows(self.h1, self.h1_q, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
+        ops.tc_linear(lw.w_down, self.h1_q, self.y2, rows=rows, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
+                      status=self.status)
+        flag_tbl = self.block.ptr_table(dep.attn_ranks, "flags", flag_offset(spec, PH_COMBINE, li, self.ep_rank))
+        self._keep.append(flag_tbl)
+        peer_ops.combine_push(self.y2, self.src_route, self.n_rows, self.recv_tbl, flag_tbl, self.ctl, self.done[0:1], spec.hidden,
+                              dep.tp, rows, 0)
+        self.launches_per_step += 6
+
+    def _layer_nccl(self, li, lw, T):
+        import torch.distributed as dist
+        m, H = self.spec.moe, self.spec.hidden
+        src = self.dep.attn_ranks[0]
+        xn = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
+        idx = torch.empty(T, m.top_k, dtype=torch.int32, device=self.device)
+        wts = torch.empty(T, m.top_k, dtype=torch.float32, device=self.device)
+        dist.broadcast(xn, src); dist.broadcast(idx, src); dist.broadcast(wts, src)
+        rows = T * m.top_k
+        ops.route_pack(idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
+                       T, m.top_k, self.e_lo, self.e_hi, self.tn, self.max_tiles)
+        if self.kind == KIND_BF16:
+            ops.gather_rows(xn, self.src_token, self.n_rows, self.xs.data, rows)
+        else:
+            ops.quant_fp4_rows(xn, self.xs, src_rows=self.src_token, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_gate.inv_act_gs)
+        ops.tc_linear(lw.w_gate, self.xs, self.h1, rows=rows, w_up=lw.w_up, tiles=self.tiles, n_tiles=self.n_tiles,
+                      max_tiles=self.max_tiles, status=self.status)
+        if self.kind != KIND_BF16:
+            ops.quant_fp4_rows(self.h1, self.h1_q, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
+        ops.tc_linear(lw.w_down, self.h1_q, self.y2, rows=rows, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
+                      status=self.status)
+        acc = torch.zeros(T, H, dtype=torch.bfloat16, device=self.device)
+        ops.moe_combine(self.y2, self.slot_row, wts, None, None, acc, T, m.top_k)
+        dist.all_reduce(acc)
+
+    def step(self, T: int):
+        self._keep = []
+        self.launches_per_step = 0
+        if self.comm == "p2p":
+            peer_ops.step_begin(self.ctl)
+        for li in range(self.spec.n_layers):
+            self.layer(li, T)
+
+    def run(self, T: int, graphs: dict, use_graph: bool = True):
+        if not use_graph or self.comm != "p2p":
+            return self.step(T)
+        if T not in graphs:
+            raise RuntimeError("expert graph for this step size was not captured")
+        graphs[T].replay()
+
+
+def capture_expert_graph(worker: ExpertRankWorker, T: int) -> torch.cuda.CUDAGraph:
+    """Capture one expert-rank step.  Waiting kernels are part of the graph, so the capture itself must not run
+    them: capture records launches without executing."""
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        worker.step(T)
+    return g

@@ -350,3 +350,27 @@ def test_paged_attention_tc(Hq, Hkv, window, use_sink, splits):
         ref = rops.attention(bf16r(q[qs:qs + ql]), bf16r(ks[i]), bf16r(vs[i]), torch.arange(L - ql, L), torch.arange(L),
                              window=window, sink=sink)
         assert torch.allclose(got[qs:qs + ql], ref, atol=3e-2, rtol=3e-2), f"seq {i}: max err {(got[qs:qs + ql] - ref).abs().max()}"
+
+
+# ------------------------------------------------------------------ bounded flag waits (failure detection without a fault)
+def test_flag_wait_runs_out_and_reports_status():
+    from cuteafd_b200.parallel import peer_ops
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)        # nothing ever sets these
+    ctl = torch.zeros(4, dtype=torch.int32, device=DEV)
+    st = status_word()
+    peer_ops.step_begin(ctl)
+    peer_ops.wait_flags(flags.data_ptr(), 2, 1, ctl, 0, st, timeout_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert int(st[0]) >> 24 == 4 and int(ctl[0]) == 1            # CA_DEV_TIMEOUT_FLAG recorded, abort word published
+    # later kernels of the same step fall through instead of waiting again
+    out = torch.zeros(64, dtype=torch.bfloat16, device=DEV)
+    a = torch.ones(64, dtype=torch.bfloat16, device=DEV)
+    peer_ops.wait_add(a, a, None, out, 64, 0, flags.data_ptr(), ctl, 0, st, timeout_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert float(out.float().sum()) == 0.0
+    # a flag that is set lets the wait through and the sum is formed in rank order
+    peer_ops.step_begin(ctl)
+    flags[0] = int(ctl[1])
+    peer_ops.wait_add(a, a * 2, a, out, 64, 0, flags.data_ptr(), ctl, 0, st, timeout_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert torch.equal(out.float(), torch.full((64,), 4.0, device=DEV)) and int(ctl[0]) == 0
