@@ -1,0 +1,142 @@
+"""`ModelRunner` implementations: the GPU engine adapter and a deterministic fake for CPU tests.
+
+`EngineRunner.run(rows)` packs the rows of a scheduler round into one engine step (one host-to-device copy of the
+step inputs, CUDA-graph replay for decode-shaped steps), selects tokens on the device (greedy argmax, or the exact
+sampler / masked argmax for rows that ask for it) and reads only token ids back.
+`FakeRunner` computes "the model's" next token as a pure function of the token prefix, so scheduler, prefix-cache
+and speculation tests are exact without a GPU (reference: cuteafd-bench/examples/fake_server.rs:1-10,
+cuteafd-transport/src/synthetic.rs:128-131).
+"""
+from __future__ import annotations
+
+import hashlib
+
+import torch
+
+from .scheduler import Row
+
+
+class FakeRunner:
+    def __init__(self, vocab: int = 1000, max_rows: int = 4096, eos_every: int = 0):
+        self.vocab, self._max_rows, self.calls, self.rows_seen, self.fail_next = vocab, max_rows, 0, 0, None
+        self.kv: dict = {}           # (id(seq), position) -> token: lets tests check that cached KV is really reused
+
+    @property
+    def max_rows(self) -> int:
+        return self._max_rows
+
+    def next_token(self, prefix: list[int]) -> int:
+        h = hashlib.blake2b(repr(prefix[-8:]).encode() + len(prefix).to_bytes(4, "little"), digest_size=4).digest()
+        return int.from_bytes(h, "little") % self.vocab
+
+    def run(self, rows: list[Row]) -> list[list[int]]:
+        self.calls += 1
+        if self.fail_next:
+            msg, self.fail_next = self.fail_next, None
+            raise RuntimeError(msg)
+        out = []
+        for r in rows:
+            self.rows_seen += len(r.tokens)
+            history = r.state.tokens[:r.start_pos]       # tokens whose KV must already be cached
+            assert len(history) == r.start_pos, "scheduler asked to run a row at a position beyond its history"
+            toks = []
+            for i in r.want_logits:
+                toks.append(self.next_token(history + r.tokens[:i + 1]))
+            out.append(toks)
+        return out
+
+
+class EngineRunner:
+    def __init__(self, engine, max_rows: int = 4096):
+        self.eng, self._max_rows = engine, max_rows
+        self.h2d_bytes = self.d2h_bytes = 0
+        self._tok_host = torch.zeros(max(64, max_rows), dtype=torch.int32)
+        if torch.cuda.is_available():
+            self._tok_host = self._tok_host.pin_memory()
+
+    @property
+    def max_rows(self) -> int:
+        return self._max_rows
+
+    def run(self, rows: list[Row]) -> list[list[int]]:
+        from ..engine.engine import StepShape
+        from .. import ops
+        eng = self.eng
+        tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages = [], [], [], [], [], [], [], []
+        for r in rows:
+            seq = r.state.seq
+            q_start.append(len(tokens))
+            n = len(r.tokens)
+            seq.ensure(eng_pool(self), r.start_pos + n)
+            for i, t in enumerate(r.tokens):
+                tokens.append(t)
+                positions.append(r.start_pos + i)
+                slots.append(seq.slot(r.start_pos + i))
+            logit_rows += [q_start[-1] + i for i in r.want_logits]
+            kv_len.append(r.start_pos + n)
+            q_len.append(n)
+            pages.append(seq.pages)
+        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages)
+        max_q = max(q_len)
+        decode_like = max_q <= 8
+        sh = StepShape(T=len(tokens), n_seq=len(rows), max_q_len=max_q, n_logits=len(logit_rows),
+                       attn_splits=eng.attn_splits_for(len(rows), max_q, max(kv_len)) if decode_like else 1)
+        lane = eng.run(sh, use_graph=decode_like)
+        n = len(logit_rows)
+        # rows that sample or carry a grammar mask are re-selected from their logits row on the device
+        special = []
+        base = 0
+        for r in rows:
+            st = r.state
+            if r.want_logits and (not st.req.sampling.greedy or st.req.constraint is not None):
+                special.append((base, r))
+            base += len(r.want_logits)
+        for off, r in special:
+            self._select_special(lane, off, r)
+        if n:
+            self._tok_host[:n].copy_(lane.next_tok[:n], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            self.d2h_bytes += 4 * n
+        eng.check_status()
+        flat = self._tok_host[:n].tolist()
+        out, base = [], 0
+        for r in rows:
+            out.append(flat[base:base + len(r.want_logits)])
+            base += len(r.want_logits)
+        return out
+
+    def _select_special(self, lane, off: int, r: Row):
+        from .. import ops
+        from ..ref import sampler as ref_sampler
+        st = r.state
+        k = len(r.want_logits)
+        logits = lane.logits[off:off + k]
+        mask = None
+        if st.req.constraint is not None:
+            m = st.req.constraint.mask(st.tokens)
+            if m is not None:
+                mask = m.to(logits.device).view(1, -1).expand(k, -1).contiguous()
+        p = st.req.sampling
+        if p.greedy:
+            ops.argmax_rows(logits, lane.next_tok[off:off + k], masks=mask, status=lane.tok_status[off:off + k])
+        elif 1 <= p.top_k <= 1024:
+            pos = [len(st.tokens) + i for i in range(k)]
+            par = ops.pack_sample_params([p] * k, pos).to(logits.device)
+            ops.sample_rows(logits, par, lane.next_tok[off:off + k], lane.tok_status[off:off + k], masks=mask)
+        else:   # unbounded candidate sets go through the exact host sampler on the logits row
+            host = logits.float().cpu()
+            for i in range(k):
+                mk = None
+                if mask is not None:
+                    bits = mask[i].cpu()
+                    mk = torch.tensor([(int(bits[j >> 5]) >> (j & 31)) & 1 for j in range(host.shape[1])], dtype=torch.bool)
+                lane.next_tok[off + i] = ref_sampler.sample(host[i], p, len(st.tokens) + i, mk)
+
+
+def eng_pool(runner: EngineRunner):
+    return runner.pool
+
+
+def attach_pool(runner: EngineRunner, pool):
+    runner.pool = pool
+    return runner

@@ -1,0 +1,323 @@
+"""Continuous-batching scheduler: admission with prefix reuse, chunked prefill with a decode time share,
+speculative decode with lossless verification, per-request isolation, stats.
+
+One `step()` = admit -> (one prefill round | one decode/verify round).  The scheduler talks to the model through a
+small `ModelRunner` interface (`run(rows) -> tokens`), implemented by `EngineRunner` over the GPU engine and by
+`FakeRunner` for CPU tests - the same split the reference uses between its serve loop and `Engine`
+(families/deepseek_v4/serve.rs:610-983: admission :641-767, prefill round :768-898, speculative step :389-537,
+verify budget of 64 rows, failure isolation :932-940).
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Protocol
+
+from ..engine.kv import PAGE, OutOfPages, PagePool, SeqKV
+from ..ref.ops import greedy_verify
+from ..ref.sampler import SamplingParams
+from .draft_policy import DraftPolicy, SimpleDraftPolicy
+from .prefix import PrefixCache
+
+VERIFY_ROWS = 64
+
+
+@dataclass
+class Request:
+    rid: str
+    prompt: list[int]
+    max_tokens: int = 128
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_ids: tuple = ()
+    eos_id: int | None = None
+    on_token: Callable[[list[int], bool, str | None], None] | None = None   # (new tokens, finished, reason)
+    constraint: object | None = None        # object with .mask(prefix_tokens) -> allowed-token bitmask or None
+    use_cache: bool = True
+    allow_drafts: bool = True
+    arrived: float = field(default_factory=time.time)
+
+
+@dataclass
+class SeqState:
+    req: Request
+    seq: SeqKV
+    prefilled: int = 0              # prompt tokens whose KV is in the cache
+    out: list = field(default_factory=list)
+    pending: int | None = None      # last emitted token whose KV is not written yet (the next anchor)
+    cache_hit: int = 0
+    ttft: float | None = None
+    finished: bool = False
+    reason: str | None = None
+    cancelled: bool = False
+
+    @property
+    def tokens(self) -> list[int]:
+        return self.req.prompt + self.out
+
+
+@dataclass
+class Row:
+    """One sequence's contribution to a model step."""
+    state: SeqState
+    tokens: list[int]
+    start_pos: int
+    want_logits: list[int]          # indices into `tokens` whose next-token choice is needed
+
+
+class ModelRunner(Protocol):
+    def run(self, rows: list[Row]) -> list[list[int]]: ...
+    @property
+    def max_rows(self) -> int: ...
+
+
+class Drafter(Protocol):
+    def propose(self, state: SeqState, n: int) -> list[int]: ...
+
+
+class NgramDrafter:
+    """Copy-continuation drafts: if the last `k` tokens occurred before, propose what followed them
+    (the reference mixes such copy drafts with neural ones; serve.rs:446-465)."""
+
+    def __init__(self, k: int = 3):
+        self.k = k
+
+    def propose(self, state: SeqState, n: int) -> list[int]:
+        toks = state.tokens
+        for k in range(min(self.k, len(toks) - 1), 0, -1):
+            tail = toks[-k:]
+            for s in range(len(toks) - k - 1, -1, -1):
+                if toks[s:s + k] == tail:
+                    cont = toks[s + k:s + k + n]
+                    if cont:
+                        return cont
+        return []
+
+
+class Scheduler:
+    def __init__(self, runner: ModelRunner, pool: PagePool, *, max_seqs: int = 16, prefill_chunk: int = 4096, decode_share: float = 0.2,
+                 prefix: PrefixCache | None = None, drafter: Drafter | None = None, policy: DraftPolicy | None = None,
+                 max_draft: int = 3, queue_limit: int = 64):
+        self.runner, self.pool = runner, pool
+        self.max_seqs, self.prefill_chunk, self.decode_share = max_seqs, prefill_chunk, decode_share
+        self.prefix = prefix
+        self.drafter, self.policy, self.max_draft = drafter, policy or SimpleDraftPolicy(max_draft), max_draft
+        self.queue: deque[Request] = deque()
+        self.queue_limit = queue_limit
+        self.active: list[SeqState] = []
+        self.fatal: str | None = None
+        self._prefill_debt = 0.0
+        self.stats = {"requests": 0, "finished": 0, "generated": 0, "prefill_tokens": 0, "steps": 0, "verify_rows": 0,
+                      "drafted": 0, "accepted": 0, "failed": 0, "deferred": 0, "rejected": 0}
+
+    # ------------------------------------------------------------------ intake
+    def submit(self, req: Request) -> bool:
+        if self.fatal:
+            self._finish_unadmitted(req, "unavailable: " + self.fatal)
+            return False
+        if len(self.queue) >= self.queue_limit:
+            self.stats["rejected"] += 1
+            self._finish_unadmitted(req, "queue full")
+            return False
+        self.queue.append(req)
+        self.stats["requests"] += 1
+        return True
+
+    def cancel(self, rid: str):
+        for s in self.active:
+            if s.req.rid == rid:
+                s.cancelled = True
+        self.queue = deque(r for r in self.queue if r.rid != rid)
+
+    def _finish_unadmitted(self, req: Request, reason: str):
+        if req.on_token:
+            req.on_token([], True, reason)
+
+    def fail_all(self, cause: str):
+        """A terminal engine/transport failure: every admitted and queued client hears about it
+        (reference: mimo_v2/serve_failures.rs:14-40)."""
+        self.fatal = cause
+        for s in self.active:
+            self._finish(s, "error: " + cause, capture=False)
+        self.active = []
+        while self.queue:
+            self._finish_unadmitted(self.queue.popleft(), "error: " + cause)
+
+    # ------------------------------------------------------------------ admission
+    def _admit(self):
+        while self.queue and len(self.active) < self.max_seqs:
+            req = self.queue[0]
+            if not req.prompt:
+                self.queue.popleft()
+                self._finish_unadmitted(req, "error: empty prompt")
+                continue
+            try:
+                if self.prefix is not None and req.use_cache:
+                    adm = self.prefix.admit(req.prompt, reserve_new=req.max_tokens + self.max_draft + 1)
+                    st = SeqState(req, adm.seq, prefilled=adm.hit_tokens, cache_hit=adm.hit_tokens)
+                else:
+                    seq = SeqKV()
+                    need = seq.pages_needed(len(req.prompt) + req.max_tokens + self.max_draft + 1)
+                    if not self.pool.can_alloc(need):
+                        raise OutOfPages("pool")
+                    seq.ensure(self.pool, len(req.prompt) + req.max_tokens + self.max_draft + 1)
+                    st = SeqState(req, seq)
+            except OutOfPages:
+                self.stats["deferred"] += 1      # KV pressure defers, it does not reject
+                if not self.active:
+                    self.queue.popleft()
+                    self._finish_unadmitted(req, "error: prompt does not fit the KV pool")
+                    continue
+                break
+            self.queue.popleft()
+            self.active.append(st)
+
+    # ------------------------------------------------------------------ rounds
+    def _prefill_round(self, states: list[SeqState]):
+        rows, budget = [], min(self.prefill_chunk, self.runner.max_rows)
+        for st in states:
+            if budget <= 0:
+                break
+            take = min(len(st.req.prompt) - st.prefilled, budget)
+            last = st.prefilled + take == len(st.req.prompt)
+            rows.append(Row(st, st.req.prompt[st.prefilled:st.prefilled + take], st.prefilled, [take - 1] if last else []))
+            budget -= take
+        outs = self._run(rows)
+        if outs is None:
+            return
+        for row, toks in zip(rows, outs):
+            st = row.state
+            st.prefilled += len(row.tokens)
+            st.seq.length = st.prefilled
+            self.stats["prefill_tokens"] += len(row.tokens)
+            if st.cancelled:
+                if self.prefix is not None:
+                    self.prefix.park(st.req.prompt, st.seq)
+                self._finish(st, "cancelled", capture=False)
+                continue
+            if row.want_logits:
+                st.ttft = time.time() - st.req.arrived
+                if self.prefix is not None and st.req.use_cache:
+                    self.prefix.capture(st.req.prompt, st.seq, kind="prompt")
+                self._emit(st, [toks[0]])
+
+    def _decode_round(self, states: list[SeqState]):
+        rows, budget = [], min(VERIFY_ROWS, self.runner.max_rows)
+        plan = []
+        for st in states:
+            drafts = []
+            if self.drafter is not None and st.req.allow_drafts and st.req.sampling.greedy and st.req.constraint is None:
+                width = self.policy.width(st.req.rid, budget - (len(states) - len(plan)))
+                room = st.req.max_tokens - len(st.out) - 1
+                if width > 0 and room > 0:
+                    drafts = self.drafter.propose(st, min(width, room))
+            if budget - (1 + len(drafts)) < len(states) - len(plan) - 1:
+                drafts = []
+            inputs = [st.pending] + drafts
+            budget -= len(inputs)
+            plan.append((st, inputs))
+            rows.append(Row(st, inputs, st.seq.length, list(range(len(inputs)))))
+        outs = self._run(rows)
+        if outs is None:
+            return
+        for (st, inputs), target in zip(plan, outs):
+            remaining = st.req.max_tokens - len(st.out)
+            accepted, emitted, _, _ = greedy_verify(inputs, target, st.req.eos_id, max(1, remaining))
+            st.seq.length += accepted
+            self.stats["verify_rows"] += len(inputs)
+            self.stats["drafted"] += len(inputs) - 1
+            self.stats["accepted"] += accepted - 1
+            self.policy.observe(st.req.rid, len(inputs) - 1, accepted - 1)
+            self._emit(st, emitted)
+
+    def _run(self, rows: list[Row]):
+        if not rows:
+            return []
+        try:
+            self.stats["steps"] += 1
+            return self.runner.run(rows)
+        except Exception as e:  # a failed step fails the sequences in it, the server keeps going
+            for r in rows:
+                self.stats["failed"] += 1
+                self._finish(r.state, f"error: {e}", capture=False)
+            return None
+
+    # ------------------------------------------------------------------ bookkeeping
+    def _emit(self, st: SeqState, toks: list[int]):
+        new = []
+        for t in toks:
+            if st.finished:
+                break
+            st.out.append(t)
+            new.append(t)
+            st.pending = t
+            self.stats["generated"] += 1
+            if st.req.eos_id is not None and t == st.req.eos_id:
+                self._finish(st, "stop", new)
+            elif t in st.req.stop_ids:
+                self._finish(st, "stop", new)
+            elif len(st.out) >= st.req.max_tokens:
+                self._finish(st, "length", new)
+        if not st.finished and st.cancelled:
+            self._finish(st, "cancelled", new)
+        elif not st.finished and new and st.req.on_token:
+            try:
+                st.req.on_token(new, False, None)
+            except Exception as e:          # a broken client stream fails one request, never the batch
+                self._finish(st, f"error: stream: {e}", capture=False)
+
+    def _finish(self, st: SeqState, reason: str, new: list | None = None, capture: bool = True):
+        if st.finished:
+            return
+        st.finished, st.reason = True, reason
+        if capture and self.prefix is not None and st.req.use_cache and not reason.startswith("error"):
+            toks = st.tokens[:st.seq.length]
+            self.prefix.capture(toks, st.seq, kind="turn")
+        if self.prefix is not None:
+            self.prefix.release(st.seq)
+        else:
+            st.seq.release(self.pool)
+        self.stats["finished"] += 1
+        if st.req.on_token:
+            try:
+                st.req.on_token(new or [], True, reason)
+            except Exception:
+                pass
+
+    def step(self) -> bool:
+        """Returns False when there was nothing to do."""
+        if self.fatal:
+            return False
+        self._admit()
+        self.active = [s for s in self.active if not s.finished]
+        for s in self.active:
+            if s.cancelled and s.prefilled == len(s.req.prompt):
+                self._finish(s, "cancelled")
+        self.active = [s for s in self.active if not s.finished]
+        prefilling = [s for s in self.active if s.prefilled < len(s.req.prompt)]
+        decoding = [s for s in self.active if s.prefilled == len(s.req.prompt) and s.pending is not None]
+        if not prefilling and not decoding:
+            return False
+        # decode keeps a time share while prompts are being ingested (reference: prefill_share.rs:1-19)
+        if prefilling and (not decoding or self._prefill_debt <= 0):
+            self._prefill_round(prefilling)
+            self._prefill_debt += self.decode_share / max(1e-6, 1.0 - self.decode_share)
+        else:
+            self._decode_round(decoding)
+            self._prefill_debt -= 1.0
+        self.active = [s for s in self.active if not s.finished]
+        if self.prefix is not None:
+            self.prefix.tick()
+        return True
+
+    def run_until_idle(self, max_steps: int = 100000):
+        n = 0
+        while n < max_steps and (self.step() or self.queue):
+            n += 1
+        return n
+
+    def snapshot(self) -> dict:
+        return dict(self.stats, active=len(self.active), queued=len(self.queue),
+                    prefilling=sum(1 for s in self.active if s.prefilled < len(s.req.prompt)),
+                    prefix=self.prefix.snapshot() if self.prefix else None, draft_policy=self.policy.snapshot(),
+                    free_pages=self.pool.n_free, fatal=self.fatal)
