@@ -192,7 +192,7 @@ struct DispatchArgs {
   FlagPtrs flags;           // per expert rank: flag this attention rank releases
   const float* inv_gs;
   uint32_t* ctl; uint32_t* done_counter;
-  int T0, T1, H, k, E_local, n_ep, kind, sf_ld, rows_cap;
+  int T0, T1, H, k, E_local /* total routed experts */, n_ep, kind, sf_ld, rows_cap;
   uint32_t step_offset;
   int* status;
 };
@@ -243,9 +243,11 @@ __global__ void dispatch_push_kernel(const DispatchArgs a) {
       for (int d = 0; d < a.n_ep; ++d) ((int*)a.idx_dst.p[d])[(size_t)t * a.k + threadIdx.x] = a.idx[(size_t)t * a.k + threadIdx.x];
     for (int sl = 0; sl < a.k; ++sl) {
       const int e = a.idx[(size_t)t * a.k + sl];
-      const int owner = e / a.E_local;
+      // expert ranks own contiguous, nearly equal ranges: rank o holds experts [o*E/n_ep, (o+1)*E/n_ep)
+      int owner = -1;
+      for (int o = 0; o < a.n_ep; ++o) if (e >= (o * a.E_local) / a.n_ep && e < ((o + 1) * a.E_local) / a.n_ep) owner = o;
       if (owner < 0 || owner >= a.n_ep) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, t); continue; }
-      const int row = a.slot_row[(size_t)t * a.k + sl] - a.offsets[owner * a.E_local];
+      const int row = a.slot_row[(size_t)t * a.k + sl] - a.offsets[(owner * a.E_local) / a.n_ep];
       if (row < 0 || row >= a.rows_cap) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, t); continue; }
       uint4* dq = (uint4*)((uint8_t*)a.slab_q.p[owner] + (size_t)row * row_bytes);
       for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dq[i] = ((const uint4*)pay)[i];

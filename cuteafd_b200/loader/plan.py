@@ -1,0 +1,100 @@
+"""`cuteafd plan MODEL`: read a snapshot's config + safetensors headers, detect the family and every weight's
+storage format, check them against what the kernels can execute, and (optionally) print the per-rank layout.
+Unsupported combinations are reported as results with hints, never raised.
+Reference: cuteafd-daemon/src/commands/plan.rs:118-298, cuteafd-loader/src/plan/mod.rs, AGENTS.md:274-275.
+"""
+from __future__ import annotations
+
+import json
+from collections import Counter
+from dataclasses import dataclass, field
+from pathlib import Path
+
+from ..config import ModelSpec, from_hf_config, spec_by_name, NAMED_SPECS
+from . import formats, placement
+from .safetensors_io import catalog
+
+# what each kernel family can run today: (operand format) -> kernel
+EXECUTABLE = {
+    "bf16": "tc_linear kind::f16", "nvfp4": "tc_linear kind::mxf4nvf4 (W4A4)", "mxfp4": "tc_linear kind::mxf4 (W4A4)",
+    "fp8_block128": "tc_linear kind::f8f6f4 + block promotion", "fp8_block32": "tc_linear kind::mxf8f6f4",
+    "f32": "cast to bf16 at load", "f16": "cast to bf16 at load",
+}
+HINTS = {
+    "exl3": "EXL3 trellis weights are decoded by the dequant-GEMM path (K2-K5); check `cuteafd doctor` for the kernel",
+}
+
+
+@dataclass
+class PlanReport:
+    model: str
+    family: str | None
+    spec: ModelSpec | None
+    supported: bool
+    format_counts: dict = field(default_factory=dict)
+    problems: list = field(default_factory=list)
+    hints: list = field(default_factory=list)
+    layout: placement.Layout | None = None
+    files: list = field(default_factory=list)
+
+    def to_json(self) -> dict:
+        return {"model": self.model, "family": self.family, "supported": self.supported, "formats": self.format_counts,
+                "problems": self.problems, "hints": self.hints,
+                "layout": None if self.layout is None else {
+                    "fits": self.layout.fits, "pool_tokens": self.layout.pool_tokens, "notes": self.layout.notes,
+                    "ranks": [{"rank": r.rank, "role": r.role, "weights_gib": round(r.weight_bytes / placement.GIB, 2),
+                               "kv_gib": round(r.kv_pool / placement.GIB, 2)} for r in self.layout.ranks]},
+                "files": self.files}
+
+    def text(self) -> str:
+        out = [f"model    : {self.model}", f"family   : {self.family}", f"supported: {self.supported}"]
+        out += [f"format   : {k} x{v}" for k, v in sorted(self.format_counts.items())]
+        out += [f"problem  : {p}" for p in self.problems] + [f"hint     : {h}" for h in self.hints]
+        if self.layout is not None:
+            out.append(self.layout.table())
+        return "\n".join(out)
+
+
+def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = False, pool_tokens: int = 0, gpu_gib: int = 180) -> PlanReport:
+    """`model` is a snapshot directory (config.json + *.safetensors) or one of the named synthetic shapes."""
+    problems, hints, counts, flist = [], [], Counter(), []
+    p = Path(model)
+    spec = family = None
+    if p.is_dir():
+        try:
+            spec = from_hf_config(p)
+            family = spec.family
+        except Exception as e:
+            problems.append(f"config.json: {e}")
+        try:
+            cat = catalog(p)
+            ops, bad = formats.detect_all(cat)
+            for b in bad:
+                problems.append(f"{b.stem}: {b.reason}")
+            for op in ops.values():
+                if len(op.logical) >= 2:
+                    counts[op.format] += 1
+            if files:
+                flist = sorted({Path(t.file).name for t in cat.values()})
+        except Exception as e:
+            problems.append(f"safetensors: {e}")
+    elif model in NAMED_SPECS:
+        spec = spec_by_name(model)
+        family = spec.family
+        counts[spec.quant.experts] += 1
+        counts[spec.quant.dense] += 1
+    else:
+        problems.append(f"{model!r} is neither a snapshot directory nor a known shape ({', '.join(sorted(NAMED_SPECS))})")
+    for fmt in counts:
+        base = fmt.split("_k")[0] if fmt.startswith("exl3") else fmt
+        if base not in EXECUTABLE:
+            (hints if base in HINTS else problems).append(HINTS.get(base, f"no kernel executes weights stored as {fmt}"))
+    if spec is not None and spec.attn.kind == "gqa" and spec.attn.head_dim not in (32, 64, 128):
+        problems.append(f"attention head_dim {spec.attn.head_dim} has no kernel (32, 64 or 128)")
+    rep = PlanReport(model, family, spec, supported=spec is not None and not problems, format_counts=dict(counts), problems=problems,
+                     hints=hints, files=flist)
+    if layout and spec is not None:
+        rep.layout = placement.solve(spec, world=world, gpu_bytes=gpu_gib * placement.GIB, pool_tokens=pool_tokens)
+        if not rep.layout.fits:
+            rep.supported = False
+    return rep

@@ -85,7 +85,7 @@ class AttnRankEngine(Engine):
         self.tiles, self.n_tiles, self.n_rows = i32(m.n_experts + rows + 1, 4), i32(1), i32(1)
         self.identity_rows = torch.arange(rows, dtype=torch.int32, device=device).view(t_max, m.top_k).contiguous()
         self.part = torch.zeros(t_max, H, dtype=torch.bfloat16, device=device)
-        self.e_local = m.n_experts // dep.ep
+        self.e_local = m.n_experts          # the dispatch kernel derives each rank's expert range from the total
         if block is not None:
             vec = 16 if expert_kind == KIND_NVFP4 else 32
             self.sf_ld = -(-H // 256) * (256 // vec)
@@ -199,8 +199,8 @@ class ExpertRankWorker:
         self.spec, self.dep, self.rank, self.comm, self.block, self.device = spec, dep, rank, comm, block, device
         self.ep_rank = dep.expert_ranks.index(rank)
         m = spec.moe
-        self.e_local = m.n_experts // dep.ep
-        self.e_lo, self.e_hi = self.ep_rank * self.e_local, (self.ep_rank + 1) * self.e_local
+        self.e_lo, self.e_hi = (self.ep_rank * m.n_experts) // dep.ep, ((self.ep_rank + 1) * m.n_experts) // dep.ep
+        self.e_local = self.e_hi - self.e_lo
         self.weights = DeviceWeights.random(spec, device, seed=seed, experts_range=(self.e_lo, self.e_hi), with_attention=False, act_gs=act_gs)
         self.kind = next(l.w_gate.kind for l in self.weights.layers if l.w_gate is not None)
         self.t_max, H, k = t_max, spec.hidden, m.top_k
