@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   uint64_t& p_full = bars[10]; uint64_t& o_done = bars[11];
   uint32_t& tmem_slot = *(uint32_t*)(bars + 12);
   int& abort_flag = *(int*)(bars + 13);
+  uint64_t& x_bar = bars[14];               // column-split softmax: cross-warp exchange barrier
   if (smem_u32(smem) & 1023) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, 0xA11); return; }
   uint8_t* sQ = smem;                       // 2 x [128 rows x 128 B]
   uint8_t* sP = smem + 32768;               // [128 rows x 128 B]
@@ -97,13 +98,16 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   const int p0 = first_page + split * per, p1 = min(last_page, p0 + per);
   const int n_tiles = max(0, p1 - p0);
 
-  const int n_live_warps = (R + 31) / 32;               // softmax warps with at least one real row
+  // Decode-shaped tiles (<= 32 real rows) replicate the rows into every 32-lane quarter of the MMA tile so that
+  // the four softmax warps each take 16 of the 64 score columns of the SAME rows (4x shorter per-tile chain).
+  const bool rep4 = R <= 32;
+  const int n_live_warps = rep4 ? 4 : (R + 31) / 32;    // softmax warps with work
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
     }
-    mbar_init(&p_full, 32 * n_live_warps); mbar_init(&o_done, 1);
+    mbar_init(&p_full, 32 * n_live_warps); mbar_init(&o_done, 1); mbar_init(&x_bar, 128);
     abort_flag = 0;
     fence_barrier_init();
   }
@@ -112,7 +116,8 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   for (int i = tid; i < 128 * 16; i += 192) {
     const int r = i >> 4, c = i & 15;                  // 16-byte chunk c of row r
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < R) v = *(const uint4*)(a.q + (size_t)(row_base + r / G) * a.q_stride + (size_t)(kvh * G + r % G) * AD + c * 8);
+    const int qr = rep4 ? (r & 31) : r;                // decode tiles replicate their <= 32 rows into all four lane quarters
+    if (qr < R) v = *(const uint4*)(a.q + (size_t)(row_base + qr / G) * a.q_stride + (size_t)(kvh * G + qr % G) * AD + c * 8);
     *(uint4*)(sQ + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
   }
   fence_proxy_async_smem();
@@ -188,11 +193,81 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
     // ------------------------------------------------------------------ softmax + epilogue: thread = row
     const int q4 = warp & 3, r = q4 * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
-    const bool live = r < R;
+    const bool live = r < R;                  // in the replicated layout quarter 0 (r = lane) holds the real rows
     const int qpos = live ? first_pos + r / G : -1;
     const float sc2 = a.scale * 1.4426950408889634f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    if (rep4) {
+      // ---- column-split path: thread (q4, lane) owns row `lane`, score columns [16*q4, 16*q4 + 16)
+      const bool rlive = lane < R;
+      const int rq = rlive ? first_pos + lane / G : -1;
+      float* xchg = (float*)(sP + 8192);                 // [2][4][32] row maxima (P rows >= 64 are never read back)
+      float* lsum = xchg + 256;                          // [4][32]
+      const int col0 = 16 * q4;
+      for (int i = 0; i < n_tiles; ++i) {
+        if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+        tc_fence_after();
+        uint32_t sr[16];
+        tmem_ld_x16(tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL) + col0, sr);
+        tc_wait_ld();
+        const int key0 = (p0 + i) * APAGE + col0;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int kp = key0 + j;
+          const bool vis = rlive && kp <= rq && kp < kvlen && (a.window <= 0 || kp > rq - a.window);
+          const float v = vis ? __uint_as_float(sr[j]) * sc2 : -INFINITY;
+          sr[j] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+        float* xb = xchg + (i & 1) * 128;
+        xb[q4 * 32 + lane] = mx;
+        mbar_arrive(&x_bar);
+        if (!mbar_wait_bounded(&x_bar, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+        mx = fmaxf(fmaxf(xb[lane], xb[32 + lane]), fmaxf(xb[64 + lane], xb[96 + lane]));
+        if (i > 0 && !mbar_wait_bounded(&o_done, (i - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+        tc_fence_after();
+        float alpha = 1.f;
+        if (mx > m_ref + 8.f) {
+          if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
+          m_ref = mx;
+        }
+        if (q4 == 0 && i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // the real O rows live in lane quarter 0
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[16];
+            tmem_ld_x16(tmem + O_COL + c * 16, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st_x16(tmem + O_COL + c * 16, o);
+          }
+          tc_wait_st();
+        }
+        uint32_t pk[8];
+        float psum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float a0 = __uint_as_float(sr[2 * j]), a1 = __uint_as_float(sr[2 * j + 1]);
+          const float e0 = (m_ref == -INFINITY) ? 0.f : exp2f(a0 - m_ref), e1 = (m_ref == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
+          psum += e0 + e1;
+          bf162 h = __floats2bfloat162_rn(e0, e1);
+          pk[j] = *(uint32_t*)&h;
+        }
+        l += psum;
+        *(uint4*)(sP + lane * 128 + (((2 * q4) ^ (lane & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *(uint4*)(sP + lane * 128 + (((2 * q4 + 1) ^ (lane & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&p_full);
+      }
+      // total row sums: every warp contributes the sum over its 16 columns
+      lsum[q4 * 32 + lane] = l;
+      mbar_arrive(&x_bar);
+      if (ok && !mbar_wait_bounded(&x_bar, n_tiles & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, 998); ok = false; }
+      l = lsum[lane] + lsum[32 + lane] + lsum[64 + lane] + lsum[96 + lane];
+    } else
     for (int i = 0; i < n_tiles; ++i) {
       if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
       tc_fence_after();
@@ -255,7 +330,7 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
     tc_fence_after();
     // Epilogue.  The tensor-memory reads are warp-collective: every lane of a warp executes them (rows past
     // R read zeros or stale columns and simply do not store).
-    if (__all_sync(0xffffffffu, ok)) {
+    if (__all_sync(0xffffffffu, ok) && (!rep4 || q4 == 0)) {
       const int rr = live ? r : 0;
       const int t = row_base + rr / G, h = kvh * G + rr % G;
       const float m_nat = (m_ref == -INFINITY) ? -INFINITY : m_ref * 0.6931471805599453f;
