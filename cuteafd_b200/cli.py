@@ -1,0 +1,183 @@
+"""`cuteafd` command line: serve | plan | golden | expertd | fabric | bench | doctor.
+
+    python -m cuteafd_b200.cli plan qwen3-235b --layout
+    python -m cuteafd_b200.cli serve --model tiny --listen 127.0.0.1:8000
+    python -m torch.distributed.run --nproc-per-node 8 -m cuteafd_b200.cli serve --model qwen3-235b   (attention TP2 + experts EP6)
+
+`serve` auto-detects the family from a snapshot's config.json (or takes a named synthetic shape), sizes the KV pool
+with the placement solver, builds the engine, and starts the HTTP server once the scheduler thread is ready.
+Reference: cuteafd-daemon/src/cli.rs:44-115 (commands), :857-1005 (serve flags), commands/plan.rs.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+
+def cmd_plan(a) -> int:
+    from .loader.plan import plan
+    rep = plan(a.model, world=a.gpus, layout=a.layout, files=a.files, pool_tokens=a.pool_tokens, gpu_gib=a.gpu_gib)
+    print(json.dumps(rep.to_json(), indent=2) if a.json else rep.text())
+    return 0 if rep.supported else 2
+
+
+def cmd_doctor(a) -> int:
+    import torch
+    from .ops import native
+    info = {"torch": torch.__version__, "cuda_available": torch.cuda.is_available(), "native_library": str(native.LIB_PATH),
+            "native_library_present": native.available()}
+    if native.available():
+        try:
+            info["abi_version"] = native.lib().cuteafd_abi_version()
+        except Exception as e:
+            info["native_error"] = str(e)
+    if torch.cuda.is_available():
+        p = torch.cuda.get_device_properties(0)
+        info.update(gpu=p.name, sms=p.multi_processor_count, memory_gib=round(p.total_memory / 2 ** 30, 1),
+                    compute_capability=f"{p.major}.{p.minor}", n_gpus=torch.cuda.device_count())
+        info["p2p"] = [[torch.cuda.can_device_access_peer(i, j) if i != j else True for j in range(torch.cuda.device_count())]
+                       for i in range(torch.cuda.device_count())]
+    print(json.dumps(info, indent=2))
+    return 0
+
+
+def cmd_fabric(a) -> int:
+    """Peer-to-peer probe between two GPUs: copy-engine copy and SM push, one way (reference: `cuteafd fabric --p2p`)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        print(json.dumps({"error": "fabric probe needs two GPUs"}))
+        return 2
+    n = a.mib << 20
+    src = torch.empty(n, dtype=torch.uint8, device="cuda:0")
+    dst = torch.empty(n, dtype=torch.uint8, device="cuda:1")
+    out = {}
+    for name, fn in (("copy_engine", lambda: dst.copy_(src, non_blocking=True)),):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name + "_gbs"] = round(10 * n / (e0.elapsed_time(e1) / 1e3) / 1e9, 1)
+    print(json.dumps(out))
+    return 0
+
+
+def build_serving(a):
+    """Engine + scheduler + prefix cache for a model name or snapshot (single GPU)."""
+    import torch
+    from .config import from_hf_config, spec_by_name, NAMED_SPECS, QuantSpec
+    from .engine.engine import Engine
+    from .engine.kv import PagePool
+    from .models.weights import DeviceWeights
+    from .ref.model import init_weights
+    from .serving.prefix import PrefixCache
+    from .serving.runner import EngineRunner, attach_pool
+    from .serving.scheduler import NgramDrafter, Scheduler
+    spec = spec_by_name(a.model) if a.model in NAMED_SPECS else from_hf_config(a.model)
+    dev = torch.device("cuda", a.device)
+    if spec.name == "tiny":
+        weights = DeviceWeights.from_masters(spec, init_weights(spec, 0), dev)
+    else:
+        weights = DeviceWeights.random(spec, dev, seed=1)      # synthetic weights: no checkpoint reader for this family yet
+    n_pages = a.pool_tokens // 64 if a.pool_tokens else 4096
+    eng = Engine(weights, n_pages=n_pages, max_seqs=a.max_sequences, max_pages_per_seq=min(n_pages, a.max_context // 64 + 1))
+    pool = PagePool(n_pages)
+    runner = attach_pool(EngineRunner(eng, max_rows=a.prefill_batch_tokens), pool)
+    prefix = PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens)
+    sched = Scheduler(runner, pool, max_seqs=a.max_sequences, prefill_chunk=a.prefill_batch_tokens, decode_share=a.decode_share,
+                      prefix=prefix, drafter=NgramDrafter() if a.draft != "off" else None, max_draft=a.draft_limit)
+    return spec, sched
+
+
+def cmd_serve(a) -> int:
+    from .loader.tokenizer import load_tokenizer
+    from .serving.api import ServingLoop, build_app
+    spec, sched = build_serving(a)
+    loop = ServingLoop(sched).start()
+    keys = set(open(a.api_key_file).read().split()) if a.api_key_file else None
+    app = build_app(loop, model_id=a.model_id or spec.name, tokenizer=load_tokenizer(a.model if os.path.isdir(a.model) else None),
+                    api_keys=keys, max_output=a.max_output)
+    host, port = a.listen.rsplit(":", 1)
+    import uvicorn
+    uvicorn.run(app, host=host, port=int(port), log_level="info")
+    return 0
+
+
+def cmd_golden(a) -> int:
+    """Teacher-forced comparison of the GPU engine against the CPU oracle on the tiny model (per-prompt logits error)."""
+    import torch
+    from .config import tiny_spec, QuantSpec
+    from .engine.engine import Engine
+    from .engine.generate import BatchGenerator
+    from .models.weights import DeviceWeights
+    from .ref.model import RefCache, RefModel, init_weights
+    spec = tiny_spec().replace(quant=QuantSpec(experts=a.experts, dense="bf16"))
+    dw = DeviceWeights.from_masters(spec, init_weights(spec, a.seed), "cuda")
+    eng = Engine(dw, n_pages=32, max_seqs=8, max_pages_per_seq=4)
+    ref = RefModel(spec, dw.dequantized_masters())
+    g = torch.Generator().manual_seed(a.seed)
+    prompts = [torch.randint(0, spec.vocab, (64,), generator=g).tolist() for _ in range(2)]
+    gen = BatchGenerator(eng)
+    gen.prefill(prompts)
+    lane = eng.lane(128)
+    out = []
+    for i, p in enumerate(prompts):
+        rl, _ = ref.forward(torch.tensor(p), 0, RefCache())
+        got = lane.logits[i].float().cpu()
+        out.append({"prompt": i, "rel_l2": float((got - rl[-1]).norm() / rl[-1].norm()), "top1_match": int(got.argmax()) == int(rl[-1].argmax())})
+    print(json.dumps({"family": "tiny", "experts": a.experts, "rows": out}))
+    return 0 if all(r["rel_l2"] < 0.25 for r in out) else 1
+
+
+def cmd_expertd(a) -> int:
+    """Host-path expert service: answers framed expert waves over TCP with the synthetic executor (protocol bring-up
+    and multi-host tests); the in-node data path uses peer memory and needs no daemon."""
+    from .parallel.transport import ExpertServer, SyntheticRouteExecutor
+    host, port = a.listen.rsplit(":", 1)
+    srv = ExpertServer(SyntheticRouteExecutor(executor_id=a.rank), host, int(port))
+    print(json.dumps({"listening": list(srv.address), "rank": a.rank}), flush=True)
+    try:
+        srv.thread.join()
+    except KeyboardInterrupt:
+        srv.stop()
+    return 0
+
+
+def cmd_bench(a) -> int:
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return subprocess.call([sys.executable, os.path.join(root, "bench.py"), *a.rest])
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="cuteafd")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("plan"); p.add_argument("model"); p.add_argument("--layout", action="store_true"); p.add_argument("--files", action="store_true")
+    p.add_argument("--gpus", type=int, default=8); p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--gpu-gib", type=int, default=180)
+    p.add_argument("--json", action="store_true"); p.set_defaults(fn=cmd_plan)
+    p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("fabric"); p.add_argument("--p2p", action="store_true"); p.add_argument("--mib", type=int, default=256); p.set_defaults(fn=cmd_fabric)
+    p = sub.add_parser("serve")
+    p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--listen", default="127.0.0.1:8000")
+    p.add_argument("--device", type=int, default=0); p.add_argument("--max-context", type=int, default=32768)
+    p.add_argument("--max-sequences", type=int, default=16); p.add_argument("--max-output", type=int, default=4096)
+    p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--prefill-batch-tokens", type=int, default=4096)
+    p.add_argument("--decode-share", type=float, default=0.2); p.add_argument("--prefix-cache-entries", type=int, default=20)
+    p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram"])
+    p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
+    p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("golden"); p.add_argument("--experts", default="bf16"); p.add_argument("--seed", type=int, default=0); p.set_defaults(fn=cmd_golden)
+    p = sub.add_parser("expertd"); p.add_argument("--listen", default="127.0.0.1:7000"); p.add_argument("--rank", type=int, default=0); p.set_defaults(fn=cmd_expertd)
+    p = sub.add_parser("bench"); p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
