@@ -1,0 +1,421 @@
+// Multi-head latent attention (DeepSeek-V3 style), absorbed form, on the 5th-generation tensor cores.
+//
+// Every head of a token attends to the same per-token latent: cache row = [c_kv (512, RMS-normed) | k_rope (64)] in
+// bf16.  With W_UK folded into the query (q_lat = W_UK^T q_nope) the score of head h is q_full[h] . row, q_full =
+// [q_lat (512) | q_rope (64)], and the value is the latent itself (W_UV is applied afterwards), so the kernel is an
+// MQA with a 576-wide QK and a 512-wide V that share one cache row.
+//
+// CTA = (KV split, V half, sequence x query tile); rows of the MMA tile = local heads x tokens (128 rows).
+//   S[128 x 32]   = Q K^T over nine 64-wide chunks (tcgen05.mma kind::f16, Q 144 KB resident in shared memory,
+//                   K tiles of 32 keys x 576 through a two-stage TMA ring)
+//   softmax       thread per row, lazy rescale (as in the GQA kernel), P in bf16 to shared memory
+//   O[128 x 256] += P V_half, V_half read in place from the K tile as an MN-major operand (chunks 4*vh .. 4*vh+3)
+// The 512-wide fp32 output of 128 rows would fill all of tensor memory, so the V dimension is split over two CTAs
+// that both compute the (cheap) scores; adjacent CTAs run together, so the second reads the latent from L2.
+// Outputs are head-major [heads, T, 512] for the grouped W_UV GEMM that follows; with several KV splits the
+// unnormalised partials go to scratch and `mla_merge_kernel` combines them.
+//
+// Reference counterparts: native/shared/cuda/attention.cu:385 (mla_compressed_attention_bf16), :986 (merge),
+// families/glm5/cuda/glm_mla_prefill.cu:123-960 (mma.sync MLA prefill), kv_cache.cu:142 (mla_kv_prepare).
+#include <string.h>
+
+#include "common.cuh"
+
+#define MKEYS 32
+#define MPAGE 64
+#define DQK 576
+#define DV 512
+#define NCH 9            // 64-wide chunks of the QK dimension
+
+struct MlaArgs {
+  const bf16* q_lat;        // [Hl * T, 512] head-major
+  const bf16* q_rope;       // [T, Hl, 64]
+  const CUtensorMap* kv_map;    // 2-D (as 3-D): {576, slots, 1}, box {64, 32, 1}, 128-byte swizzle
+  const int* page_table; const int* kv_len; const int* q_start; const int* q_len;
+  bf16* out;                // [Hl, T, 512] head-major
+  float* part_o;            // [splits, T, Hl, 512]
+  float* part_ml;           // [splits, T, Hl, 2]
+  int* status;
+  int Hl, max_pages, n_splits, max_q_tiles, T;
+  float scale;
+};
+
+__device__ __forceinline__ uint64_t mla_desc_k_sw128(uint32_t saddr) { return umma_desc_sw128(saddr); }
+__device__ __forceinline__ uint64_t mla_desc_mn_sw128(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// K-major operand without swizzle: 8-row x 16-byte core matrices, `lbo` bytes between core matrices along K,
+// `sbo` bytes between 8-row groups.
+__device__ __forceinline__ uint64_t mla_desc_k_plain(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ uint32_t mla_idesc(int n, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void mla_tmem_st_x16(uint32_t addr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                 "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+#define SQ_BYTES (NCH * 16384)              // 9 chunks x [128 rows x 128 B]
+#define SK_STAGE (NCH * 4096)               // 9 chunks x [32 keys x 128 B]
+#define SP_BYTES 8192                       // [128 rows x 32 keys] bf16, core-matrix layout
+#define MLA_SMEM (SQ_BYTES + 2 * SK_STAGE + SP_BYTES + 128)
+
+__global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant__ MlaArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + SQ_BYTES;
+  uint8_t* sP = sK + 2 * SK_STAGE;
+  uint64_t* bars = (uint64_t*)(sP + SP_BYTES);
+  uint64_t* k_full = bars; uint64_t* k_empty = bars + 2; uint64_t* s_full = bars + 4;
+  uint64_t& p_full = bars[6]; uint64_t& o_done = bars[7];
+  uint32_t& tmem_slot = *(uint32_t*)(bars + 8);
+  int& abort_flag = *(int*)(bars + 9);
+  if (smem_u32(smem) & 1023) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, 0xA12); return; }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+
+  const int tok_per_tile = 128 / a.Hl;
+  const int split = blockIdx.x, vh = blockIdx.y;
+  const int seq = blockIdx.z / a.max_q_tiles, qt = blockIdx.z % a.max_q_tiles;
+  const int qlen = a.q_len[seq], kvlen = a.kv_len[seq];
+  const int tok0 = qt * tok_per_tile;
+  if (tok0 >= qlen) return;
+  const int ntok = min(tok_per_tile, qlen - tok0);
+  const int R = ntok * a.Hl;
+  const int row_base = a.q_start[seq] + tok0;
+  const int first_pos = kvlen - qlen + tok0;
+  const int hi = first_pos + ntok;
+  const int last_tile = (hi + MKEYS - 1) / MKEYS;                     // key tiles [0, last_tile)
+  const int per = (last_tile + a.n_splits - 1) / a.n_splits;
+  const int t0 = split * per, t1 = min(last_tile, t0 + per);
+  const int n_tiles = max(0, t1 - t0);
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&s_full[s], 1); }
+    mbar_init(&p_full, 128); mbar_init(&o_done, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  // Q rows -> nine swizzled K-major chunk tiles: chunks 0..7 from q_lat, chunk 8 from q_rope
+  for (int i = tid; i < 128 * 72; i += 192) {
+    const int r = i / 72, c = i % 72;                    // 16-byte chunk c (8 elements) of row r
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < R) {
+      const int t = row_base + r / a.Hl, h = r % a.Hl;
+      v = (c < 64) ? *(const uint4*)(a.q_lat + ((size_t)h * a.T + t) * DV + c * 8)
+                   : *(const uint4*)(a.q_rope + ((size_t)t * a.Hl + h) * 64 + (c - 64) * 8);
+    }
+    *(uint4*)(sQ + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  const uint32_t S0_COL = 0, S1_COL = 32, O_COL = 64;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ latent tile producer
+    for (int i = 0; i < n_tiles && !*abortp; ++i) {
+      const int s = i & 1;
+      if (!mbar_wait_bounded(&k_empty[s], ((i >> 1) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
+      if (lane == 0) {
+        const int key0 = (t0 + i) * MKEYS;
+        const int page = a.page_table[(size_t)seq * a.max_pages + key0 / MPAGE];
+        const int slot0 = page * MPAGE + key0 % MPAGE;
+        mbar_expect_tx(&k_full[s], SK_STAGE);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * SK_STAGE + c * 4096, a.kv_map, &k_full[s], c * 64, slot0, 0);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t id_s = mla_idesc(MKEYS, 0), id_o = mla_idesc(256, 1);
+    auto issue_scores = [&](int j) -> bool {
+      const int s = j & 1;
+      if (!mbar_wait_bounded(&k_full[s], (j >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, j); return false; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t k0 = smem_u32(sK + s * SK_STAGE), d = tmem + (s ? S1_COL : S0_COL);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + c * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, (c | k) ? 1u : 0u);
+        tc_commit(&s_full[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = true;
+    if (n_tiles > 0) ok = issue_scores(0);
+    for (int i = 0; ok && i < n_tiles; ++i) {
+      const int s = i & 1;
+      // the next tile's scores are issued first so they overlap this tile's softmax (its K stage is the other one)
+      if (i + 1 < n_tiles) { ok = issue_scores(i + 1); if (!ok) break; }
+      if (!mbar_wait_bounded(&p_full, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, i); break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * 4096;
+#pragma unroll
+        for (int k = 0; k < 2; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
+          tc_mma_f16(tmem + O_COL, mla_desc_k_plain(smem_u32(sP) + k * 256, 128, 512), mla_desc_mn_sw128(v0 + k * 2048, 4096, 1024), id_o, (i | k) ? 1u : 0u);
+        tc_commit(&k_empty[s]);
+        tc_commit(&o_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue: thread = row
+    const int q4 = warp & 3, r = q4 * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+    const bool live = r < R;
+    const int qpos = live ? first_pos + r / a.Hl : -1;
+    const float sc2 = a.scale * 1.4426950408889634f;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+      tc_fence_after();
+      uint32_t sr[32];
+      tmem_ld_x16(tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL), sr);
+      tmem_ld_x16(tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL) + 16, sr + 16);
+      tc_wait_ld();
+      const int key0 = (t0 + i) * MKEYS;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int kp = key0 + j;
+        const float v = (live && kp <= qpos && kp < kvlen) ? __uint_as_float(sr[j]) * sc2 : -INFINITY;
+        sr[j] = __float_as_uint(v);
+        mx = fmaxf(mx, v);
+      }
+      if (i > 0 && !mbar_wait_bounded(&o_done, (i - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+      tc_fence_after();
+      float alpha = 1.f;
+      if (mx > m_ref + 8.f) {
+        if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
+        m_ref = mx;
+      }
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {       // warp-uniform: tcgen05.ld/st are warp collectives
+#pragma unroll 1
+        for (int c = 0; c < 16; ++c) {
+          uint32_t o[16];
+          tmem_ld_x16(tmem + lane_addr + O_COL + c * 16, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          mla_tmem_st_x16(tmem + lane_addr + O_COL + c * 16, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+      uint32_t pk[16];
+      float psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float a0 = __uint_as_float(sr[2 * j]), a1 = __uint_as_float(sr[2 * j + 1]);
+        const float e0 = (m_ref == -INFINITY) ? 0.f : exp2f(a0 - m_ref), e1 = (m_ref == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
+        psum += e0 + e1;
+        bf162 h = __floats2bfloat162_rn(e0, e1);
+        pk[j] = *(uint32_t*)&h;
+      }
+      l += psum;
+      // core-matrix layout: 8-row groups 512 B apart, the four 8-key columns 128 B apart, 16 B per row inside
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *(uint4*)(sP + (r >> 3) * 512 + c * 128 + (r & 7) * 16) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&p_full);
+    }
+    if (ok && n_tiles > 0 && !mbar_wait_bounded(&o_done, (n_tiles - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, 999); ok = false; }
+    tc_fence_after();
+    if (__all_sync(0xffffffffu, ok)) {
+      const int rr = live ? r : 0;
+      const int t = row_base + rr / a.Hl, h = rr % a.Hl;
+      const float m_nat = (m_ref == -INFINITY) ? -INFINITY : m_ref * 0.6931471805599453f;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = a.out + ((size_t)h * a.T + t) * DV + vh * 256;
+      float* po = a.n_splits > 1 ? a.part_o + (((size_t)split * a.T + t) * a.Hl + h) * DV + vh * 256 : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < 16; ++c) {
+        uint32_t o[16];
+        if (n_tiles > 0) { tmem_ld_x16(tmem + lane_addr + O_COL + c * 16, o); tc_wait_ld(); }
+        else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = 0;
+        }
+        if (!live) continue;
+        if (a.n_splits == 1) {
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { bf162 hh = __floats2bfloat162_rn(__uint_as_float(o[2 * j]) * inv, __uint_as_float(o[2 * j + 1]) * inv); w[j] = *(uint32_t*)&hh; }
+          *(uint4*)(dst + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+          *(uint4*)(dst + c * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *(uint4*)(po + c * 16 + j * 4) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        }
+      }
+      if (live && a.n_splits > 1 && vh == 0) {
+        float* ml = a.part_ml + (((size_t)split * a.T + t) * a.Hl + h) * 2;
+        ml[0] = m_nat; ml[1] = l;
+      }
+    }
+  }
+  if (*abortp && warp == 0) { const long long c0 = clock64(); while (clock64() - c0 < 400000) __nanosleep(1000); }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// out[h, t, :] = sum_s o_s * exp(m_s - M) / sum_s l_s * exp(m_s - M); partials are token-major, the output head-major.
+__global__ void mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int T, int Hl, int n_splits) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(((size_t)s * T + t) * Hl + h) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float* ml = part_ml + (((size_t)s * T + t) * Hl + h) * 2;
+    if (ml[0] != -INFINITY) L += ml[1] * __expf(ml[0] - M);
+  }
+  for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = part_ml[(((size_t)s * T + t) * Hl + h) * 2];
+      if (m != -INFINITY) o += part_o[(((size_t)s * T + t) * Hl + h) * DV + d] * __expf(m - M);
+    }
+    out[((size_t)h * T + t) * DV + d] = __float2bfloat16(L > 0.f ? o / L : 0.f);
+  }
+}
+
+__global__ void mla_fill_ml_kernel(float* ml, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) ml[i] = (i & 1) ? 0.f : -INFINITY;
+}
+
+extern "C" int cuteafd_mla_attention(const void* q_lat, const void* q_rope, const void* kv_map, const int* page_table, const int* kv_len,
+                                     const int* q_start, const int* q_len, void* out, float* part_o, float* part_ml, int T, int n_seq,
+                                     int max_q_len, int Hl, int max_pages, int n_splits, float scale, int* status, cudaStream_t s) {
+  CA_REQUIRE(Hl >= 1 && Hl <= 128 && 128 % Hl == 0, "mla_attention: local head count %d must divide 128", Hl);
+  CA_REQUIRE(n_splits >= 1 && (n_splits == 1 || (part_o && part_ml)), "mla_attention: split-KV needs scratch");
+  if (T <= 0 || n_seq <= 0) return CA_OK;
+  MlaArgs a;
+  a.q_lat = (const bf16*)q_lat; a.q_rope = (const bf16*)q_rope; a.kv_map = (const CUtensorMap*)kv_map; a.page_table = page_table;
+  a.kv_len = kv_len; a.q_start = q_start; a.q_len = q_len; a.out = (bf16*)out; a.part_o = part_o; a.part_ml = part_ml; a.status = status;
+  a.Hl = Hl; a.max_pages = max_pages; a.n_splits = n_splits; a.T = T; a.scale = scale;
+  const int tpt = 128 / Hl;
+  a.max_q_tiles = (max_q_len + tpt - 1) / tpt;
+  static bool attr_set[64] = {false};
+  int dev = 0; cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MLA_SMEM);
+    if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(mla_attn)");
+    attr_set[dev & 63] = true;
+  }
+  if (n_splits > 1) {
+    const long long n = (long long)n_splits * T * Hl * 2;
+    mla_fill_ml_kernel<<<(int)((n + 255) / 256), 256, 0, s>>>(part_ml, n);
+  }
+  dim3 grid(n_splits, 2, n_seq * a.max_q_tiles);
+  mla_attn_kernel<<<grid, 192, MLA_SMEM, s>>>(a);
+  CA_CHECK_LAUNCH("mla_attention");
+  if (n_splits > 1) {
+    mla_merge_kernel<<<dim3(T, Hl), 128, 0, s>>>(part_o, part_ml, (bf16*)out, T, Hl, n_splits);
+    CA_CHECK_LAUNCH("mla_merge");
+  }
+  return CA_OK;
+}
+
+// Descriptor of one layer's latent cache [slots, 576] bf16: box {64 elements, 32 slots}.
+extern "C" int cuteafd_tmap_encode_latent(void* out128, const void* base, uint64_t n_slots) {
+  CUtensorMap m;
+  int rc = ca_encode_tmap_3d(&m, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, DQK, n_slots, 1, DQK * 2, (uint64_t)DQK * 2 * n_slots, 64, MKEYS, 1,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  memcpy(out128, &m, sizeof(m));
+  return CA_OK;
+}
+
+// ---------------------------------------------------------------- MLA glue
+// kv_a [T, 576] -> cache row: RMSNorm(c_kv) * w over the first 512, interleaved RoPE over the last 64.
+__global__ void mla_kv_prepare_kernel(const bf16* __restrict__ kv_a, const float* __restrict__ w, const int* __restrict__ positions,
+                                      const int* __restrict__ slot_map, bf16* __restrict__ cache, int n_slots, float theta, float eps,
+                                      int interleaved, int* status) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, tid = threadIdx.x;       // 128 threads
+  const int slot = slot_map[t];
+  if (slot < 0 || slot >= n_slots) { if (tid == 0) ca_dev_fail(status, CA_DEV_BAD_INDEX, t); return; }
+  const bf16* src = kv_a + (size_t)t * DQK;
+  bf16* dst = cache + (size_t)slot * DQK;
+  float v[4], ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[j] = __bfloat162float(src[tid * 4 + j]); ss += v[j] * v[j]; }
+  const float inv = rsqrtf(block_sum(ss, red) / 512.f + eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) dst[tid * 4 + j] = __float2bfloat16(v[j] * inv * w[tid * 4 + j]);
+  if (tid < 32) {
+    const int i0 = interleaved ? 2 * tid : tid, i1 = interleaved ? 2 * tid + 1 : tid + 32;
+    const float x0 = __bfloat162float(src[512 + i0]), x1 = __bfloat162float(src[512 + i1]);
+    const float ang = (float)positions[t] * powf(theta, -2.f * (float)tid / 64.f);
+    const float sn = sinf(ang), cs = cosf(ang);
+    dst[512 + i0] = __float2bfloat16(x0 * cs - x1 * sn);
+    dst[512 + i1] = __float2bfloat16(x0 * sn + x1 * cs);
+  }
+}
+
+extern "C" int cuteafd_mla_kv_prepare(const void* kv_a, const float* w, const int* positions, const int* slot_map, void* cache, int T,
+                                      int n_slots, float theta, float eps, int interleaved, int* status, cudaStream_t s) {
+  if (T <= 0) return CA_OK;
+  mla_kv_prepare_kernel<<<T, 128, 0, s>>>((const bf16*)kv_a, w, positions, slot_map, (bf16*)cache, n_slots, theta, eps, interleaved, status);
+  CA_CHECK_LAUNCH("mla_kv_prepare");
+  return CA_OK;
+}
+
+// q [T, Hl * 192] -> q_nope head-major [Hl, T, 128] and q_rope [T, Hl, 64] (RoPE applied).  One warp per (t, h).
+__global__ void mla_q_split_kernel(const bf16* __restrict__ q, const int* __restrict__ positions, bf16* __restrict__ q_nope,
+                                   bf16* __restrict__ q_rope, int T, int Hl, float theta, int interleaved) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= T * Hl) return;
+  const int t = w / Hl, h = w % Hl;
+  const bf16* src = q + ((size_t)t * Hl + h) * 192;
+  bf16* dn = q_nope + ((size_t)h * T + t) * 128;
+  *(uint2*)(dn + lane * 4) = *(const uint2*)(src + lane * 4);
+  const int i0 = interleaved ? 2 * lane : lane, i1 = interleaved ? 2 * lane + 1 : lane + 32;
+  const float x0 = __bfloat162float(src[128 + i0]), x1 = __bfloat162float(src[128 + i1]);
+  const float ang = (float)positions[t] * powf(theta, -2.f * (float)lane / 64.f);
+  const float sn = sinf(ang), cs = cosf(ang);
+  bf16* dr = q_rope + ((size_t)t * Hl + h) * 64;
+  dr[i0] = __float2bfloat16(x0 * cs - x1 * sn);
+  dr[i1] = __float2bfloat16(x0 * sn + x1 * cs);
+}
+
+extern "C" int cuteafd_mla_q_split(const void* q, const int* positions, void* q_nope, void* q_rope, int T, int Hl, float theta,
+                                   int interleaved, cudaStream_t s) {
+  if (T <= 0) return CA_OK;
+  const long long warps = (long long)T * Hl;
+  mla_q_split_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, s>>>((const bf16*)q, positions, (bf16*)q_nope, (bf16*)q_rope, T, Hl, theta, interleaved);
+  CA_CHECK_LAUNCH("mla_q_split");
+  return CA_OK;
+}
+
+// head-major [Hl, T, D] -> token-major [T, Hl * D]
+__global__ void head_to_token_major_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int T, int Hl, int D) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const uint4* src = (const uint4*)(in + ((size_t)h * T + t) * D);
+  uint4* dst = (uint4*)(out + ((size_t)t * Hl + h) * D);
+  for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int cuteafd_head_to_token_major(const void* in, void* out, int T, int Hl, int D, cudaStream_t s) {
+  CA_REQUIRE(D % 8 == 0, "head_to_token_major: D must be a multiple of 8");
+  if (T <= 0) return CA_OK;
+  head_to_token_major_kernel<<<dim3(T, Hl), 32, 0, s>>>((const bf16*)in, (bf16*)out, T, Hl, D);
+  CA_CHECK_LAUNCH("head_to_token_major");
+  return CA_OK;
+}

@@ -54,11 +54,12 @@ class Lane:
         self.xn = bf(cap, H)
         self.xn_act = ActBuffer.wrap_bf16(self.xn, self.tn)
         self.xq = ActBuffer.alloc(dk, cap, H, self.tn, dev) if dk != KIND_BF16 else self.xn_act
-        qkv_n = (a.n_heads + 2 * a.n_kv_heads) * a.head_dim
-        self.qkv = bf(cap, qkv_n)
-        self.attn = bf(cap, a.n_heads * a.head_dim)
-        self.attn_q = (ActBuffer.alloc(dk, cap, a.n_heads * a.head_dim, self.tn, dev) if dk != KIND_BF16
-                       else ActBuffer.wrap_bf16(self.attn, self.tn))
+        if a.kind == "gqa":
+            qkv_n = (a.n_heads + 2 * a.n_kv_heads) * a.head_dim
+            self.qkv = bf(cap, qkv_n)
+            self.attn = bf(cap, a.n_heads * a.head_dim)
+            self.attn_q = (ActBuffer.alloc(dk, cap, a.n_heads * a.head_dim, self.tn, dev) if dk != KIND_BF16
+                           else ActBuffer.wrap_bf16(self.attn, self.tn))
         # logits
         self.xl = bf(cap, H)
         self.xln = bf(cap, H)
@@ -101,10 +102,13 @@ class Engine:
                  expert_range: tuple | None = None, device=None, sm_count: int = 148):
         self.weights, self.spec = weights, weights.spec
         spec = self.spec
-        if spec.attn.kind != "gqa":
-            raise NotImplementedError("Engine: GQA models; MLA models run through engine.mla")
         self.device = device or weights.embed.device
-        self.dense_kind = weights.layers[0].wqkv.kind
+        if spec.attn.kind != "gqa":
+            if not hasattr(self, "_alloc_attention_state"):
+                raise NotImplementedError("Engine runs GQA models; MLA models use engine.mla.MlaEngine")
+            self.dense_kind = weights.layers[0].wo.kind
+        else:
+            self.dense_kind = weights.layers[0].wqkv.kind
         first_moe = next((l for l in weights.layers if l.w_gate is not None), None)
         self.expert_kind = first_moe.w_gate.kind if first_moe is not None else KIND_BF16
         self.expert_range = expert_range or (0, spec.moe.n_experts)
@@ -115,10 +119,13 @@ class Engine:
         a = spec.attn
         # one allocation for every layer's paged KV: [layers, slots, 2, Hkv, D]; zero-filled so masked
         # (never-written) slots hold finite values
-        self.kv = torch.zeros(spec.n_layers, n_pages * PAGE, 2, a.n_kv_heads, a.head_dim, dtype=torch.bfloat16, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        # head_dim 128 runs on the tcgen05 attention kernel (one TMA descriptor per layer's K/V store)
-        self.kv_tmaps = ops.encode_kv_tmaps(self.kv) if a.head_dim == 128 and 128 % (a.n_heads // a.n_kv_heads) == 0 else None
+        if spec.attn.kind == "gqa":
+            self.kv = torch.zeros(spec.n_layers, n_pages * PAGE, 2, a.n_kv_heads, a.head_dim, dtype=torch.bfloat16, device=self.device)
+            # head_dim 128 runs on the tcgen05 attention kernel (one TMA descriptor per layer's K/V store)
+            self.kv_tmaps = ops.encode_kv_tmaps(self.kv) if a.head_dim == 128 and 128 % (a.n_heads // a.n_kv_heads) == 0 else None
+        else:
+            self._alloc_attention_state()
         self.lanes: dict[int, Lane] = {}
         self.graphs: dict = {}
         self.graph_captures = 0

@@ -1,0 +1,215 @@
+"""DeepSeek-V3-shape engine: multi-head latent attention in absorbed form on top of the generic engine.
+
+Per layer: RMSNorm -> q_a (H -> q_lora) -> RMSNorm -> q_b -> split {q_nope head-major, q_rope + RoPE}
+           -> grouped GEMM per head  q_lat = q_nope W_UK   (W_UK folded into the query, so keys stay latent)
+           kv_a (H -> 512 + 64) -> RMSNorm(c_kv) | RoPE(k_rope) -> paged latent cache row (576 bf16 per token)
+           -> `mla_attention` (tcgen05; scores over 576, values = the 512-wide latent, two V halves per tile)
+           -> grouped GEMM per head  o = o_lat W_UV^T  -> token-major -> wo (+ residual)
+The FFN half (dense first layers, then router + routed + shared experts) is the generic engine's.
+The latent cache is replicated on the attention ranks of a TP group (heads are split, the latent is shared), as in
+the reference's head-split mode (families/deepseek_v4/engine.rs:97-119).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..config import ModelSpec
+from ..models.weights import DeviceWeights, LayerWeights, _dense_kind, _expert_kind
+from ..ops import ActBuffer, KIND_BF16, TcWeight
+from ..ops.native import call, ptr, stream
+from .engine import Engine, Lane, PAGE, StepShape
+
+DQK, DV = 576, 512
+
+
+@dataclass
+class MlaWeights:
+    """Attention weights of one MLA layer (dense kind of the model; the two absorb matrices stay bf16)."""
+    wq_a: TcWeight | None
+    q_a_norm: torch.Tensor | None
+    wq_b: TcWeight              # [Hl * 192, q_lora]  (or [Hl * 192, H] without q compression)
+    wkv_a: TcWeight             # [576, H]
+    kv_a_norm: torch.Tensor
+    w_uk_t: TcWeight            # G = Hl, [512, 128]: q_lat = q_nope @ W_UK
+    w_uv: TcWeight              # G = Hl, [128, 512]: o = o_lat @ W_UV^T
+
+
+def _mla_from_masters(spec: ModelSpec, lw: dict, device, dk: str, act_gs: float) -> MlaWeights:
+    a = spec.attn
+    nope, rope, dv, H = a.qk_nope_head_dim, a.qk_rope_head_dim, a.v_head_dim, a.n_heads
+    kvb = lw["wkv_b"].reshape(H, nope + dv, a.kv_lora_rank)
+    w_uk_t = kvb[:, :nope].transpose(1, 2).contiguous()          # [H, 512, 128]
+    w_uv = kvb[:, nope:].contiguous()                            # [H, 128, 512]
+    f32 = lambda t: t.float().to(device).contiguous()
+    return MlaWeights(
+        wq_a=TcWeight.from_master(lw["wq_a"], dk, device, act_gs) if "wq_a" in lw else None,
+        q_a_norm=f32(lw["q_a_norm"]) if "q_a_norm" in lw else None,
+        wq_b=TcWeight.from_master(lw["wq_b"] if "wq_b" in lw else lw["wq"], dk, device, act_gs),
+        wkv_a=TcWeight.from_master(lw["wkv_a"], dk, device, act_gs), kv_a_norm=f32(lw["kv_a_norm"]),
+        w_uk_t=TcWeight.from_master(w_uk_t, "bf16", device), w_uv=TcWeight.from_master(w_uv, "bf16", device))
+
+
+def mla_weights_from_masters(spec: ModelSpec, masters: dict, device, act_gs: float = 1.0 / 64) -> DeviceWeights:
+    """DeviceWeights whose layers carry `.mla` (MlaWeights) instead of a fused QKV projection."""
+    dk, ek = _dense_kind(spec), _expert_kind(spec)
+    f32 = lambda t: t.float().to(device).contiguous()
+    dw = DeviceWeights(spec=spec, embed=masters["embed"].to(torch.bfloat16).to(device).contiguous(), final_norm=f32(masters["final_norm"]),
+                       lm_head=TcWeight.from_master(masters["lm_head"], "bf16", device), act_gs=act_gs)
+    for lw in masters["layers"]:
+        out = LayerWeights(attn_norm=f32(lw["attn_norm"]), ffn_norm=f32(lw["ffn_norm"]), wqkv=None,
+                           wo=TcWeight.from_master(lw["wo"], dk, device, act_gs))
+        out.mla = _mla_from_masters(spec, lw, device, dk, act_gs)
+        if "router" in lw:
+            out.router = TcWeight.from_master(lw["router"], "bf16", device)
+            if "router_bias" in lw:
+                out.router_bias = f32(lw["router_bias"])
+            out.w_gate, out.w_up, out.w_down = (TcWeight.from_master(lw[k], ek, device, act_gs) for k in ("w_gate", "w_up", "w_down"))
+            if "ws_gate" in lw:
+                out.ws_gate, out.ws_up, out.ws_down = (TcWeight.from_master(lw[k], dk, device, act_gs) for k in ("ws_gate", "ws_up", "ws_down"))
+        else:
+            out.ws_gate, out.ws_up, out.ws_down = (TcWeight.from_master(lw[k], dk, device, act_gs) for k in ("wd_gate", "wd_up", "wd_down"))
+        dw.layers.append(out)
+    dw.layer_map = list(range(spec.n_layers))
+    return dw
+
+
+def mla_weights_random(spec: ModelSpec, device, *, heads_local: int | None = None, experts_range: tuple | None = None,
+                       distinct_moe_layers: int = 0, act_gs: float = 1.0 / 64, seed: int = 1) -> DeviceWeights:
+    """Random weights directly in storage format.  `heads_local` < n_heads builds one TP shard of the attention;
+    `distinct_moe_layers` > 0 cycles that many distinct MoE layer sets (every layer still runs at full size)."""
+    a, m, h = spec.attn, spec.moe, spec.hidden
+    dk, ek = _dense_kind(spec), _expert_kind(spec)
+    Hl = heads_local or a.n_heads
+    ones = lambda n: torch.ones(n, dtype=torch.float32, device=device)
+    e_lo, e_hi = experts_range if experts_range is not None else (0, m.n_experts)
+    gen = torch.Generator(device=device).manual_seed(seed)
+    dw = DeviceWeights(spec=spec, embed=torch.empty(spec.vocab, h, dtype=torch.bfloat16, device=device).normal_(0, spec.init_std, generator=gen),
+                       final_norm=ones(h), lm_head=TcWeight.random(1, spec.vocab, h, "bf16", device, spec.init_std, act_gs, seed + 7), act_gs=act_gs)
+
+    def make(i: int) -> LayerWeights:
+        s = seed * 1000 + i * 32
+        R = lambda G, N, K, kind, j: TcWeight.random(G, N, K, kind, device, spec.init_std, act_gs, s + j)
+        out = LayerWeights(attn_norm=ones(h), ffn_norm=ones(h), wqkv=None, wo=R(1, h, Hl * a.v_head_dim, dk, 1))
+        qk = a.qk_nope_head_dim + a.qk_rope_head_dim
+        out.mla = MlaWeights(wq_a=R(1, a.q_lora_rank, h, dk, 2) if a.q_lora_rank else None, q_a_norm=ones(a.q_lora_rank) if a.q_lora_rank else None,
+                             wq_b=R(1, Hl * qk, a.q_lora_rank or h, dk, 3), wkv_a=R(1, a.kv_lora_rank + a.qk_rope_head_dim, h, dk, 4),
+                             kv_a_norm=ones(a.kv_lora_rank), w_uk_t=R(Hl, a.kv_lora_rank, a.qk_nope_head_dim, "bf16", 5),
+                             w_uv=R(Hl, a.v_head_dim, a.kv_lora_rank, "bf16", 6))
+        if spec.is_moe_layer(i):
+            out.router = R(1, m.n_experts, h, "bf16", 7)
+            if m.use_bias:
+                out.router_bias = torch.zeros(m.n_experts, dtype=torch.float32, device=device)
+            if e_hi > e_lo:
+                out.w_gate, out.w_up, out.w_down = R(e_hi - e_lo, m.intermediate, h, ek, 8), R(e_hi - e_lo, m.intermediate, h, ek, 9), R(e_hi - e_lo, h, m.intermediate, ek, 10)
+            if m.shared_inter:
+                out.ws_gate, out.ws_up, out.ws_down = R(1, m.shared_inter, h, dk, 11), R(1, m.shared_inter, h, dk, 12), R(1, h, m.shared_inter, dk, 13)
+        else:
+            inter = m.dense_intermediate or m.intermediate
+            out.ws_gate, out.ws_up, out.ws_down = R(1, inter, h, dk, 11), R(1, inter, h, dk, 12), R(1, h, inter, dk, 13)
+        return out
+
+    n_dense = min(m.first_dense, spec.n_layers)
+    n_moe = spec.n_layers - n_dense
+    n_sets = n_moe if distinct_moe_layers <= 0 else min(distinct_moe_layers, n_moe)
+    dw.layers = [make(i) for i in range(n_dense)] + [make(n_dense + j) for j in range(n_sets)]
+    dw.layer_map = list(range(n_dense)) + [n_dense + (j % n_sets) for j in range(n_moe)]
+    return dw
+
+
+class MlaEngine(Engine):
+    def _alloc_attention_state(self):
+        spec = self.spec
+        self.heads_local = self.weights.layers[0].mla.w_uv.G
+        # latent cache: one row of 576 bf16 per token and layer (zero-filled: masked slots must hold finite values)
+        self.kv = torch.zeros(spec.n_layers, self.n_pages * PAGE, DQK, dtype=torch.bfloat16, device=self.device)
+        host = torch.zeros(spec.n_layers, 128, dtype=torch.uint8)
+        for l in range(spec.n_layers):
+            call("cuteafd_tmap_encode_latent", host[l].data_ptr(), self.kv[l].data_ptr(), self.n_pages * PAGE)
+        self.kv_tmaps = host.to(self.device)
+        self.mla_bufs: dict = {}
+
+    def _mla_buf(self, L: Lane):
+        if L.cap not in self.mla_bufs:
+            a, dev, Hl, cap = self.spec.attn, self.device, self.heads_local, L.cap
+            bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+            i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+            b = {"q_a": bf(cap, max(a.q_lora_rank, 8)), "q_an": bf(cap, max(a.q_lora_rank, 8)), "q": bf(cap, Hl * 192), "kv_a": bf(cap, DQK),
+                 "q_nope": bf(Hl * cap, 128), "q_rope": bf(cap, Hl, 64), "q_lat": bf(Hl * cap, DV), "o_lat": bf(Hl * cap, DV),
+                 "o_head": bf(Hl * cap, a.v_head_dim), "o_tok": bf(cap, Hl * a.v_head_dim)}
+            b["q_an_act"] = (ActBuffer.alloc(self.dense_kind, cap, a.q_lora_rank, L.tn, dev) if self.dense_kind != KIND_BF16 and a.q_lora_rank
+                             else ActBuffer.wrap_bf16(b["q_an"], L.tn))
+            b["o_tok_act"] = (ActBuffer.alloc(self.dense_kind, cap, Hl * a.v_head_dim, L.tn, dev) if self.dense_kind != KIND_BF16
+                              else ActBuffer.wrap_bf16(b["o_tok"], L.tn))
+            self.mla_bufs[L.cap] = b
+        return self.mla_bufs[L.cap]
+
+    def _head_tiles(self, b, T: int, tn: int):
+        """Tile table for the per-head grouped GEMMs over head-major buffers laid out [Hl, T, .]."""
+        key = ("tiles", T, tn)
+        if key not in b:
+            rows = []
+            for h in range(self.heads_local):
+                for r0 in range(0, T, tn):
+                    rows.append([h, h * T + r0, min(tn, T - r0), 0])
+            b[key] = (torch.tensor(rows, dtype=torch.int32, device=self.device), torch.tensor([len(rows)], dtype=torch.int32, device=self.device), len(rows))
+        return b[key]
+
+    def attn_splits_for(self, n_seq: int, max_q_len: int, max_kv: int) -> int:
+        tpt = max(1, 128 // self.heads_local)
+        ctas = 2 * n_seq * (-(-max_q_len // tpt))
+        tiles = max(1, -(-max_kv // 32))
+        return max(1, min(tiles, 32, self.sm_count // ctas)) if max_q_len <= 16 else 1
+
+    def _attention_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
+        spec, a, T, md, w = self.spec, self.spec.attn, sh.T, self.md, lw.mla
+        Hl = self.heads_local
+        b = self._mla_buf(L)
+        ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, spec.rms_eps, rows=T)
+        xq = self._quant(L.xn, L.xq, T, w.wkv_a.inv_act_gs)
+        if w.wq_a is not None:
+            self._dense(w.wq_a, xq, b["q_a"], T)
+            ops.add_rmsnorm(b["q_a"], None, w.q_a_norm, b["q_an"], spec.rms_eps, rows=T)
+            qa = self._quant(b["q_an"], b["q_an_act"], T, w.wq_b.inv_act_gs)
+            self._dense(w.wq_b, qa, b["q"], T)
+        else:
+            self._dense(w.wq_b, xq, b["q"], T)
+        self._dense(w.wkv_a, xq, b["kv_a"], T)
+        call("cuteafd_mla_kv_prepare", ptr(b["kv_a"]), ptr(w.kv_a_norm), ptr(md["positions"]), ptr(md["slot_map"]), ptr(self.kv[li]), T,
+             self.kv.shape[1], a.rope_theta, spec.rms_eps, 1 if a.rope_interleaved else 0, ptr(self.status), stream())
+        q_nope, q_lat = b["q_nope"][:Hl * T], b["q_lat"][:Hl * T]
+        call("cuteafd_mla_q_split", ptr(b["q"]), ptr(md["positions"]), ptr(q_nope), ptr(b["q_rope"]), T, Hl, a.rope_theta,
+             1 if a.rope_interleaved else 0, stream())
+        tn = ops.pick_tn(T, swiglu=True)
+        tiles, n_tiles, max_tiles = self._head_tiles(b, T, tn)
+        qn_act = self._act(b, ("qn", T, tn), q_nope, tn)
+        ops.tc_linear(w.w_uk_t, qn_act, q_lat, rows=Hl * T, tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=self.status)
+        o_lat = b["o_lat"][:Hl * T]
+        if sh.attn_splits > 1:
+            need = sh.attn_splits * T * Hl
+            if getattr(self, "mla_part_o", None) is None or self.mla_part_o.numel() < need * DV:
+                self.mla_part_o = torch.empty(need * DV, dtype=torch.float32, device=self.device)
+                self.mla_part_ml = torch.empty(need * 2, dtype=torch.float32, device=self.device)
+        po, pml = (self.mla_part_o, self.mla_part_ml) if sh.attn_splits > 1 else (None, None)
+        scale = (a.qk_nope_head_dim + a.qk_rope_head_dim) ** -0.5
+        call("cuteafd_mla_attention", ptr(q_lat), ptr(b["q_rope"]), ptr(self.kv_tmaps[li]), ptr(md["page_table"]), ptr(md["kv_len"]),
+             ptr(md["q_start"]), ptr(md["q_len"]), ptr(o_lat), ptr(po), ptr(pml), T, sh.n_seq, sh.max_q_len, Hl, md["page_table"].shape[1],
+             sh.attn_splits, scale, ptr(self.status), stream())
+        o_head = b["o_head"][:Hl * T]
+        ol_act = self._act(b, ("ol", T, tn), o_lat, tn)
+        ops.tc_linear(w.w_uv, ol_act, o_head, rows=Hl * T, tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=self.status)
+        call("cuteafd_head_to_token_major", ptr(o_head), ptr(b["o_tok"]), T, Hl, a.v_head_dim, stream())
+        oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
+        self._attn_out(li, lw, oq, L, T)
+        self.launches_per_step += 8
+
+    def _attn_out(self, li, lw, oq, L, T):
+        self._dense(lw.wo, oq, L.x, T, residual=L.x)
+
+    def _act(self, b, key, tensor, tn):
+        """bf16 activation operand over a view of a head-major buffer (descriptor cached per shape)."""
+        if key not in b:
+            b[key] = ActBuffer.wrap_bf16(tensor, tn)
+        return b[key]

@@ -34,6 +34,11 @@ _PROTOS = {
     "cuteafd_paged_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
     "cuteafd_paged_attention_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
     "cuteafd_tmap_encode_kv": [P, P, I, U64],
+    "cuteafd_mla_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P],
+    "cuteafd_tmap_encode_latent": [P, P, U64],
+    "cuteafd_mla_kv_prepare": [P, P, P, P, P, I, I, F, F, I, P, P],
+    "cuteafd_mla_q_split": [P, P, P, P, I, I, F, I, P],
+    "cuteafd_head_to_token_major": [P, P, I, I, I, P],
     "cuteafd_argmax_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_sample_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_verify_accept": [P, P, P, P, P, I, I, I, P],
