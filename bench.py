@@ -83,8 +83,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="qwen3-235b-decode")
+    ap.add_argument("--config", default="qwen3-235b-decode", choices=["qwen3-235b-decode", "deepseek-v3-decode"])
     ap.add_argument("--batch-per-gpu", type=int, default=16)
+    ap.add_argument("--batch-total", type=int, default=0, help="fixed global batch instead of a per-GPU batch (DeepSeek-V3 decode: 1 or 64)")
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"], help="multi-GPU transport: fused peer-memory kernels, or the NCCL-only baseline")

@@ -13,7 +13,7 @@ import time
 
 import torch
 
-from ..config import qwen3_235b_spec, default_deployment
+from ..config import deepseek_v3_spec, qwen3_235b_spec, default_deployment
 from ..engine.engine import Engine, StepShape, PAGE
 from ..engine.generate import BatchGenerator
 from ..engine.kv import PagePool, SeqKV
@@ -37,8 +37,13 @@ def _fill_context(gen: BatchGenerator, eng: Engine, batch: int, context: int, vo
 
 def run_decode_bench(args, rank: int, world: int, local: int, clocks) -> dict:
     dev = torch.device("cuda", local)
-    spec = qwen3_235b_spec(args.layers or 94)
-    batch = args.batch_per_gpu * world
+    if args.config.startswith("deepseek-v3"):
+        spec = deepseek_v3_spec(args.layers or 61)
+        if world == 1:
+            raise SystemExit("the DeepSeek-V3 shape needs the attention/expert split (run with --gpus 4 or 8)")
+    else:
+        spec = qwen3_235b_spec(args.layers or 94)
+    batch = getattr(args, "batch_total", 0) or args.batch_per_gpu * world
     if world > 1:
         from ..parallel.runner import run_decode_bench_distributed
         return run_decode_bench_distributed(args, spec, rank, world, local, clocks)

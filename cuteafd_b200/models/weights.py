@@ -156,8 +156,8 @@ class DeviceWeights:
     @staticmethod
     def random(spec: ModelSpec, device, distinct_layers: int = 0, act_gs: float = 1.0 / 64, seed: int = 0,
                experts_range: tuple | None = None, with_attention: bool = True) -> "DeviceWeights":
-        if spec.attn.kind != "gqa":
-            raise NotImplementedError("random: MLA layers are built by models.mla")
+        if spec.attn.kind != "gqa" and with_attention:
+            raise NotImplementedError("random: MLA attention layers are built by engine.mla.mla_weights_random")
         a, m, h = spec.attn, spec.moe, spec.hidden
         dk, ek = _dense_kind(spec), _expert_kind(spec)
         n_sets = spec.n_layers if distinct_layers <= 0 else min(distinct_layers, spec.n_layers)

@@ -68,7 +68,7 @@ class AttnRankEngine(Engine):
                  max_pages_per_seq: int, comm: str, block: SymmetricBlock | None, expert_kind: int, act_gs: float = 1.0 / 64, seed: int = 1):
         self.full_spec, self.dep, self.rank, self.comm, self.block = spec, dep, rank, comm, block
         self.tp, self.tp_rank = dep.tp, dep.attn_ranks.index(rank)
-        lw = DeviceWeights.random(local_attention_spec(spec, self.tp), device, seed=seed, experts_range=(0, 0), act_gs=act_gs)
+        lw = self._make_weights(spec, device, seed, act_gs)
         super().__init__(lw, n_pages=n_pages, max_seqs=max_seqs, max_pages_per_seq=max_pages_per_seq, device=device)
         self.remote_kind = expert_kind
         self.t_max = t_max
@@ -94,6 +94,10 @@ class AttnRankEngine(Engine):
             self.idx_tbl = block.ptr_table(dep.expert_ranks, "idx")
             self.y_recv = block.local("y_recv", torch.bfloat16, (rows, H))
             self.tp_recv = block.local("tp_recv", torch.bfloat16, (2, t_max, H))
+
+    def _make_weights(self, spec, device, seed, act_gs):
+        """This rank's share: attention heads split over the TP group, router/shared/dense replicated, no routed experts."""
+        return DeviceWeights.random(local_attention_spec(spec, self.tp), device, seed=seed, experts_range=(0, 0), act_gs=act_gs)
 
     # -- attention with the TP all-reduce of the output projection
     def _attention_layer(self, li, lw, L, sh):
@@ -189,6 +193,32 @@ class AttnRankEngine(Engine):
         if lw.router is None:
             return super()._moe_layer(lw, L, T)
         return self._moe_layer_at(li, lw, L, T)
+
+
+class MlaAttnRankEngine(AttnRankEngine):
+    """Attention rank of an MLA model (DeepSeek-V3 shape): local heads, replicated latent cache."""
+
+    def _make_weights(self, spec, device, seed, act_gs):
+        from ..engine.mla import mla_weights_random
+        return mla_weights_random(spec, device, heads_local=spec.attn.n_heads // self.tp, experts_range=(0, 0), act_gs=act_gs, seed=seed)
+
+    def _attn_out(self, li, lw, oq, L, T):
+        if self.tp == 1:
+            self._dense(lw.wo, oq, L.x, T, residual=L.x)
+            return
+        self._dense(lw.wo, oq, self.part, T)              # partial sum over my heads, then the TP exchange
+        self._tp_allreduce(li, self.part, L.x, T)
+
+
+def _bind_mla(cls):
+    """MLA attention methods come from MlaEngine; everything else (TP exchange, remote experts) from AttnRankEngine."""
+    from ..engine.mla import MlaEngine
+    for name in ("_alloc_attention_state", "_mla_buf", "_head_tiles", "attn_splits_for", "_attention_layer", "_act"):
+        setattr(cls, name, getattr(MlaEngine, name))
+    return cls
+
+
+_bind_mla(MlaAttnRankEngine)
 
 
 class ExpertRankWorker:

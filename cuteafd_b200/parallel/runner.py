@@ -19,7 +19,7 @@ from ..engine.engine import PAGE, StepShape
 from ..engine.generate import BatchGenerator
 from ..engine.kv import PagePool, SeqKV
 from ..ops import KIND_BY_NAME
-from .afd import AttnRankEngine, ExpertRankWorker, capture_expert_graph, make_block
+from .afd import AttnRankEngine, ExpertRankWorker, MlaAttnRankEngine, capture_expert_graph, make_block
 
 OP_STOP, OP_STEP, OP_TIMER_START, OP_TIMER_STOP = 0, 1, 2, 3
 
@@ -39,7 +39,8 @@ class AfdRunner:
         self.block = make_block(spec, self.dep, t_max, kind, rank, self.dev, None) if comm == "p2p" else None
         self.engine = self.worker = None
         if self.is_attn:
-            self.engine = AttnRankEngine(spec, self.dep, rank, self.dev, t_max=t_max, n_pages=n_pages, max_seqs=max_seqs,
+            cls = MlaAttnRankEngine if spec.attn.kind == "mla" else AttnRankEngine
+            self.engine = cls(spec, self.dep, rank, self.dev, t_max=t_max, n_pages=n_pages, max_seqs=max_seqs,
                                          max_pages_per_seq=max_pages_per_seq, comm=comm, block=self.block, expert_kind=kind, seed=seed)
             self.engine.tp_group = self.tp_group
             self.engine.on_real_step = self._announce
@@ -107,7 +108,7 @@ class AfdRunner:
 
 def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, local: int, clocks) -> dict:
     comm = getattr(args, "comm", "p2p")
-    batch = args.batch_per_gpu * world
+    batch = getattr(args, "batch_total", 0) or args.batch_per_gpu * world
     ctx_pages = -(-(args.context + 4 * (args.steps + args.warmup) + 64) // PAGE)
     pages = batch * (ctx_pages + 1) + 2
     t0 = time.time()
@@ -174,7 +175,8 @@ def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, l
         res = {
             "metric": "decode_tokens_per_s", "value": round(batch * args.steps / (ms / 1e3), 2), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, NVFP4 (W4A4) GEMMs",
+            "higher_is_better": True, "scaling": "weak" if not getattr(args, "batch_total", 0) else "strong", "vs_baseline": None,
+            "dtype": f"bf16 activations, {spec.quant.experts} experts / {spec.quant.dense} dense (dense runs as bf16 when the format has no kernel yet)",
             "data": "synthetic token ids, random-init weights, context KV random-filled",
             "config": {"model": spec.name + (f" (DEBUG {args.layers} layers: INVALID)" if args.layers else ""), "global_batch": batch,
                        "seq_len": args.context, "parallelism": f"afd attn-tp{dep.tp} + experts-ep{dep.ep} ({comm})", "layers": spec.n_layers,
