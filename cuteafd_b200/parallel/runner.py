@@ -144,11 +144,11 @@ def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, l
         for _ in range(args.warmup):
             eng.run(sh, use_graph)
         torch.cuda.synchronize()
-        run.control(OP_TIMER_START)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         clocks.start()
         time.sleep(0.2)
         torch.cuda.synchronize()
+        run.control(OP_TIMER_START)          # expert ranks start their own device timers right before the first timed step
         ev0.record()
         for _ in range(args.steps):
             eng.run(sh, use_graph)
