@@ -64,6 +64,7 @@ __device__ __forceinline__ void mla_tmem_st_x16(uint32_t addr, const uint32_t* r
 #define MLA_SMEM (SQ_BYTES + 2 * SK_STAGE + SP_BYTES + 128)
 
 __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant__ MlaArgs a) {
+  pdl_launch(); pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sK = smem + SQ_BYTES;
@@ -276,6 +277,7 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
 
 // out[h, t, :] = sum_s o_s * exp(m_s - M) / sum_s l_s * exp(m_s - M); partials are token-major, the output head-major.
 __global__ void mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int T, int Hl, int n_splits) {
+  pdl_launch(); pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(((size_t)s * T + t) * Hl + h) * 2]);
@@ -295,6 +297,7 @@ __global__ void mla_merge_kernel(const float* __restrict__ part_o, const float* 
 }
 
 __global__ void mla_fill_ml_kernel(float* ml, long long n) {
+  pdl_launch(); pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) ml[i] = (i & 1) ? 0.f : -INFINITY;
 }
@@ -320,13 +323,13 @@ extern "C" int cuteafd_mla_attention(const void* q_lat, const void* q_rope, cons
   }
   if (n_splits > 1) {
     const long long n = (long long)n_splits * T * Hl * 2;
-    mla_fill_ml_kernel<<<(int)((n + 255) / 256), 256, 0, s>>>(part_ml, n);
+    CA_LAUNCH_PDL(mla_fill_ml_kernel, (int)((n + 255) / 256), 256, 0, s, part_ml, n);
   }
   dim3 grid(n_splits, 2, n_seq * a.max_q_tiles);
-  mla_attn_kernel<<<grid, 192, MLA_SMEM, s>>>(a);
+  CA_LAUNCH_PDL(mla_attn_kernel, grid, 192, MLA_SMEM, s, a);
   CA_CHECK_LAUNCH("mla_attention");
   if (n_splits > 1) {
-    mla_merge_kernel<<<dim3(T, Hl), 128, 0, s>>>(part_o, part_ml, (bf16*)out, T, Hl, n_splits);
+    CA_LAUNCH_PDL(mla_merge_kernel, dim3(T, Hl), 128, 0, s, part_o, part_ml, (bf16*)out, T, Hl, n_splits);
     CA_CHECK_LAUNCH("mla_merge");
   }
   return CA_OK;
@@ -347,6 +350,7 @@ extern "C" int cuteafd_tmap_encode_latent(void* out128, const void* base, uint64
 __global__ void mla_kv_prepare_kernel(const bf16* __restrict__ kv_a, const float* __restrict__ w, const int* __restrict__ positions,
                                       const int* __restrict__ slot_map, bf16* __restrict__ cache, int n_slots, float theta, float eps,
                                       int interleaved, int* status) {
+  pdl_launch(); pdl_wait();
   __shared__ float red[32];
   const int t = blockIdx.x, tid = threadIdx.x;       // 128 threads
   const int slot = slot_map[t];
@@ -372,7 +376,7 @@ __global__ void mla_kv_prepare_kernel(const bf16* __restrict__ kv_a, const float
 extern "C" int cuteafd_mla_kv_prepare(const void* kv_a, const float* w, const int* positions, const int* slot_map, void* cache, int T,
                                       int n_slots, float theta, float eps, int interleaved, int* status, cudaStream_t s) {
   if (T <= 0) return CA_OK;
-  mla_kv_prepare_kernel<<<T, 128, 0, s>>>((const bf16*)kv_a, w, positions, slot_map, (bf16*)cache, n_slots, theta, eps, interleaved, status);
+  CA_LAUNCH_PDL(mla_kv_prepare_kernel, T, 128, 0, s, (const bf16*)kv_a, w, positions, slot_map, (bf16*)cache, n_slots, theta, eps, interleaved, status);
   CA_CHECK_LAUNCH("mla_kv_prepare");
   return CA_OK;
 }
@@ -380,6 +384,7 @@ extern "C" int cuteafd_mla_kv_prepare(const void* kv_a, const float* w, const in
 // q [T, Hl * 192] -> q_nope head-major [Hl, T, 128] and q_rope [T, Hl, 64] (RoPE applied).  One warp per (t, h).
 __global__ void mla_q_split_kernel(const bf16* __restrict__ q, const int* __restrict__ positions, bf16* __restrict__ q_nope,
                                    bf16* __restrict__ q_rope, int T, int Hl, float theta, int interleaved) {
+  pdl_launch(); pdl_wait();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= T * Hl) return;
   const int t = w / Hl, h = w % Hl;
@@ -399,13 +404,14 @@ extern "C" int cuteafd_mla_q_split(const void* q, const int* positions, void* q_
                                    int interleaved, cudaStream_t s) {
   if (T <= 0) return CA_OK;
   const long long warps = (long long)T * Hl;
-  mla_q_split_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, s>>>((const bf16*)q, positions, (bf16*)q_nope, (bf16*)q_rope, T, Hl, theta, interleaved);
+  CA_LAUNCH_PDL(mla_q_split_kernel, (int)((warps * 32 + 255) / 256), 256, 0, s, (const bf16*)q, positions, (bf16*)q_nope, (bf16*)q_rope, T, Hl, theta, interleaved);
   CA_CHECK_LAUNCH("mla_q_split");
   return CA_OK;
 }
 
 // head-major [Hl, T, D] -> token-major [T, Hl * D]
 __global__ void head_to_token_major_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int T, int Hl, int D) {
+  pdl_launch(); pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const uint4* src = (const uint4*)(in + ((size_t)h * T + t) * D);
   uint4* dst = (uint4*)(out + ((size_t)t * Hl + h) * D);
@@ -415,7 +421,7 @@ __global__ void head_to_token_major_kernel(const bf16* __restrict__ in, bf16* __
 extern "C" int cuteafd_head_to_token_major(const void* in, void* out, int T, int Hl, int D, cudaStream_t s) {
   CA_REQUIRE(D % 8 == 0, "head_to_token_major: D must be a multiple of 8");
   if (T <= 0) return CA_OK;
-  head_to_token_major_kernel<<<dim3(T, Hl), 32, 0, s>>>((const bf16*)in, (bf16*)out, T, Hl, D);
+  CA_LAUNCH_PDL(head_to_token_major_kernel, dim3(T, Hl), 32, 0, s, (const bf16*)in, (bf16*)out, T, Hl, D);
   CA_CHECK_LAUNCH("head_to_token_major");
   return CA_OK;
 }

@@ -63,6 +63,7 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t addr, const uint32_t* r) {
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_constant__ AttnTcArgs a) {
+  pdl_launch(); pdl_wait();
   // All shared memory is dynamic and 1024-byte aligned (operand tiles first, barriers at the tail) so that two
   // CTAs fit on one SM.
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -399,13 +400,13 @@ extern "C" int cuteafd_paged_attention_tc(const void* q, const void* kv_map, con
   }
   if (n_splits > 1) {
     const long long n = (long long)n_splits * T * Hq * 2;
-    attn_fill_ml_kernel<<<(int)((n + 255) / 256), 256, 0, s>>>(part_ml, n);
+    CA_LAUNCH_PDL(attn_fill_ml_kernel, (int)((n + 255) / 256), 256, 0, s, part_ml, n);
   }
   dim3 grid(n_splits, Hkv, n_seq * a.max_q_tiles);
-  paged_attn_tc_kernel<<<grid, 192, smem, s>>>(a);
+  CA_LAUNCH_PDL(paged_attn_tc_kernel, grid, 192, smem, s, a);
   CA_CHECK_LAUNCH("paged_attention_tc");
   if (n_splits > 1) {
-    attn_merge_kernel<<<dim3(T, Hq), 128, 0, s>>>(part_o, part_ml, sink, (bf16*)out, T, Hq, AD, n_splits);
+    CA_LAUNCH_PDL(attn_merge_kernel, dim3(T, Hq), 128, 0, s, part_o, part_ml, sink, (bf16*)out, T, Hq, (int)AD, n_splits);
     CA_CHECK_LAUNCH("attn_merge");
   }
   return CA_OK;

@@ -7,6 +7,7 @@
 // ignored through the `valid` test on m.
 static __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
                                   bf16* __restrict__ out, int T, int Hq, int D, int n_splits) {
+  pdl_launch(); pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   float M = sink ? sink[h] : -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(((size_t)s * T + t) * Hq + h) * 2]);
@@ -26,6 +27,7 @@ static __global__ void attn_merge_kernel(const float* __restrict__ part_o, const
 }
 
 static __global__ void attn_fill_ml_kernel(float* ml, long long n) {
+  pdl_launch(); pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) ml[i] = (i & 1) ? 0.f : -INFINITY;
 }

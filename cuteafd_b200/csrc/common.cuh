@@ -31,6 +31,27 @@ int ca_cuda(cudaError_t e, const char* what);
 typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// Kernels launched with CA_LAUNCH_PDL may become resident before the previous kernel in the stream has
+// finished; they run their prologue (barrier init, tensor-memory alloc, loads of STATIC data such as weights)
+// and must execute pdl_wait() before touching anything an earlier kernel produced and before their first
+// global write.  pdl_launch() lets the NEXT kernel in the stream start its own prologue.  Both are no-ops
+// for a kernel launched the ordinary way, so a kernel may be launched either way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+int ca_pdl_enabled();
+#define CA_LAUNCH_PDL(kern_, grid_, block_, smem_, stream_, ...)                                              \
+  do {                                                                                                   \
+    cudaLaunchConfig_t _cfg = {};                                                                        \
+    _cfg.gridDim = dim3(grid_); _cfg.blockDim = dim3(block_); _cfg.dynamicSmemBytes = (smem_); _cfg.stream = (stream_); \
+    cudaLaunchAttribute _at[1];                                                                          \
+    _at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                      \
+    _at[0].val.programmaticStreamSerializationAllowed = 1;                                               \
+    _cfg.attrs = _at; _cfg.numAttrs = ca_pdl_enabled() ? 1 : 0;                                          \
+    cudaError_t _le = cudaLaunchKernelEx(&_cfg, kern_, __VA_ARGS__);                                      \
+    if (_le != cudaSuccess) return ca_cuda(_le, #kern_ " launch");                                        \
+  } while (0)
+
 // Device status word layout (one int per kernel family, owned by the caller):
 // 0 = ok; otherwise (code << 24) | detail.  Written with atomicCAS so the first failure wins.
 #define CA_DEV_TIMEOUT_PRODUCER 1

@@ -9,6 +9,7 @@
 // ---------------------------------------------------------------- embedding
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const bf16* __restrict__ table, bf16* __restrict__ out,
                                     int H, int vocab, int* status) {
+  pdl_launch(); pdl_wait();
   const int t = blockIdx.x;
   int tok = tokens[t];
   if (tok < 0 || tok >= vocab) { ca_dev_fail(status, CA_DEV_BAD_INDEX, t); tok = 0; }
@@ -21,7 +22,7 @@ extern "C" int cuteafd_embed_gather(const int* tokens, const void* table, void* 
                                     cudaStream_t s) {
   CA_REQUIRE(H % 8 == 0, "embed_gather: hidden must be a multiple of 8");
   if (T <= 0) return CA_OK;
-  embed_gather_kernel<<<T, 128, 0, s>>>(tokens, (const bf16*)table, (bf16*)out, H, vocab, status);
+  CA_LAUNCH_PDL(embed_gather_kernel, T, 128, 0, s, tokens, (const bf16*)table, (bf16*)out, H, vocab, status);
   CA_CHECK_LAUNCH("embed_gather");
   return CA_OK;
 }
@@ -32,6 +33,7 @@ extern "C" int cuteafd_embed_gather(const int* tokens, const void* table, void* 
 template <int VEC>
 __global__ void add_rmsnorm_kernel(bf16* __restrict__ x, const bf16* __restrict__ delta, const float* __restrict__ w,
                                    bf16* __restrict__ y, int H, float eps) {
+  pdl_launch(); pdl_wait();
   __shared__ float red[32];
   const size_t base = (size_t)blockIdx.x * H;
   float v[VEC * 8];
@@ -77,9 +79,9 @@ extern "C" int cuteafd_add_rmsnorm(void* x, const void* delta, const float* w, v
   int threads = vecs >= 1024 ? 1024 : ((vecs + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   const int per = (vecs + threads - 1) / threads;
-  if (per == 1) add_rmsnorm_kernel<1><<<T, threads, 0, s>>>((bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
-  else if (per == 2) add_rmsnorm_kernel<2><<<T, threads, 0, s>>>((bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
-  else add_rmsnorm_kernel<4><<<T, threads, 0, s>>>((bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
+  if (per == 1) CA_LAUNCH_PDL(add_rmsnorm_kernel<1>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
+  else if (per == 2) CA_LAUNCH_PDL(add_rmsnorm_kernel<2>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
+  else CA_LAUNCH_PDL(add_rmsnorm_kernel<4>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
   CA_CHECK_LAUNCH("add_rmsnorm");
   return CA_OK;
 }
@@ -91,6 +93,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(bf16* __restrict__ qkv, const int* _
                                             const int* __restrict__ slot_map, const float* __restrict__ q_norm,
                                             const float* __restrict__ k_norm, bf16* __restrict__ kv_cache, int T, int Hq,
                                             int Hkv, int D, float theta, int interleaved, float eps, int n_slots, int* status) {
+  pdl_launch(); pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int heads = Hq + 2 * Hkv;
   if (warp >= T * heads) return;
@@ -148,7 +151,7 @@ extern "C" int cuteafd_qk_norm_rope_kvwrite(void* qkv, const int* positions, con
   if (T <= 0) return CA_OK;
   const long long warps = (long long)T * (Hq + 2 * Hkv);
   const int blocks = (int)((warps * 32 + 255) / 256);
-  qk_norm_rope_kvwrite_kernel<<<blocks, 256, 0, s>>>((bf16*)qkv, positions, slot_map, q_norm, k_norm, (bf16*)kv_cache, T, Hq,
+  CA_LAUNCH_PDL(qk_norm_rope_kvwrite_kernel, blocks, 256, 0, s, (bf16*)qkv, positions, slot_map, q_norm, k_norm, (bf16*)kv_cache, T, Hq,
                                                      Hkv, D, theta, interleaved, eps, n_slots, status);
   CA_CHECK_LAUNCH("qk_norm_rope_kvwrite");
   return CA_OK;
@@ -162,6 +165,7 @@ template <bool MX>
 __global__ void quant_fp4_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ src_rows, const int* __restrict__ n_rows_dev,
                                       uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int rows, int K, int ldx, int ldsf,
                                       const float* __restrict__ inv_gs_ptr) {
+  pdl_launch(); pdl_wait();
   const int per_row = K / 16;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int n_rows = n_rows_dev ? min(*n_rows_dev, rows) : rows;
@@ -213,8 +217,8 @@ extern "C" int cuteafd_quant_fp4_rows(int mx, const void* x, const int* src_rows
   if (rows <= 0) return CA_OK;
   const long long n = (long long)rows * (K / 16);
   const int blocks = (int)((n + 255) / 256);
-  if (mx) quant_fp4_rows_kernel<true><<<blocks, 256, 0, s>>>((const bf16*)x, src_rows, n_rows_dev, (uint8_t*)q, (uint8_t*)sf, rows, K, ldx, ldsf, inv_gs);
-  else quant_fp4_rows_kernel<false><<<blocks, 256, 0, s>>>((const bf16*)x, src_rows, n_rows_dev, (uint8_t*)q, (uint8_t*)sf, rows, K, ldx, ldsf, inv_gs);
+  if (mx) CA_LAUNCH_PDL(quant_fp4_rows_kernel<true>, blocks, 256, 0, s, (const bf16*)x, src_rows, n_rows_dev, (uint8_t*)q, (uint8_t*)sf, rows, K, ldx, ldsf, inv_gs);
+  else CA_LAUNCH_PDL(quant_fp4_rows_kernel<false>, blocks, 256, 0, s, (const bf16*)x, src_rows, n_rows_dev, (uint8_t*)q, (uint8_t*)sf, rows, K, ldx, ldsf, inv_gs);
   CA_CHECK_LAUNCH("quant_fp4_rows");
   return CA_OK;
 }
@@ -222,6 +226,7 @@ extern "C" int cuteafd_quant_fp4_rows(int mx, const void* x, const int* src_rows
 // Gather bf16 rows into expert order (BF16 expert path).
 __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ src_rows, const int* __restrict__ n_rows_dev,
                                    bf16* __restrict__ out, int rows, int K) {
+  pdl_launch(); pdl_wait();
   const int r = blockIdx.x;
   const int n_rows = n_rows_dev ? min(*n_rows_dev, rows) : rows;
   if (r >= n_rows) return;
@@ -235,7 +240,7 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __rest
 extern "C" int cuteafd_gather_rows(const void* x, const int* src_rows, const int* n_rows_dev, void* out, int rows, int K, cudaStream_t s) {
   CA_REQUIRE(K % 8 == 0, "gather_rows: K must be a multiple of 8");
   if (rows <= 0) return CA_OK;
-  gather_rows_kernel<<<rows, 128, 0, s>>>((const bf16*)x, src_rows, n_rows_dev, (bf16*)out, rows, K);
+  CA_LAUNCH_PDL(gather_rows_kernel, rows, 128, 0, s, (const bf16*)x, src_rows, n_rows_dev, (bf16*)out, rows, K);
   CA_CHECK_LAUNCH("gather_rows");
   return CA_OK;
 }

@@ -14,6 +14,7 @@ enum { SCORE_SIGMOID = 0, SCORE_SOFTMAX = 1, SCORE_SQRTSOFTPLUS = 2 };
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx,
                                      float* __restrict__ wts, int E, int k, int scoring, int normalize, float route_scale,
                                      int n_group, int topk_group) {
+  pdl_launch(); pdl_wait();
   __shared__ float score[512], choice[512], red[32];
   __shared__ float gscore[32];
   __shared__ int sel[16];
@@ -95,7 +96,7 @@ extern "C" int cuteafd_router_select(const float* logits, const float* bias, int
   CA_REQUIRE(n_group >= 1 && n_group <= 32 && E % n_group == 0, "router_select: bad group count");
   if (T <= 0) return CA_OK;
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
-  router_select_kernel<<<T, threads, 0, s>>>(logits, bias, idx, wts, E, k, scoring, normalize, route_scale, n_group, topk_group);
+  CA_LAUNCH_PDL(router_select_kernel, T, threads, 0, s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale, n_group, topk_group);
   CA_CHECK_LAUNCH("router_select");
   return CA_OK;
 }
@@ -109,6 +110,7 @@ __global__ void route_pack_kernel(const int* __restrict__ idx, int* __restrict__
                                   int* __restrict__ counts, int* __restrict__ offsets, int4* __restrict__ tiles,
                                   int* __restrict__ n_tiles, int* __restrict__ n_rows, int T, int k, int e_lo, int e_hi, int tn,
                                   int max_tiles, int* __restrict__ src_route) {
+  pdl_launch(); pdl_wait();
   extern __shared__ int sh[];   // [E_local] counts, [E_local] offsets/cursors
   const int El = e_hi - e_lo;
   int* cnt = sh; int* cur = sh + El;
@@ -156,7 +158,7 @@ extern "C" int cuteafd_route_pack(const int* idx, int* src_token, int* slot_row,
                                   int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, int* src_route, cudaStream_t s) {
   CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 4096, "route_pack: bad expert range");
   CA_REQUIRE(tn >= 1, "route_pack: bad tile rows");
-  route_pack_kernel<<<1, 1024, (2 * (e_hi - e_lo) + (T * k <= 4096 ? T * k : 0)) * sizeof(int), s>>>(idx, src_token, slot_row, counts, offsets, (int4*)tiles,
+  CA_LAUNCH_PDL(route_pack_kernel, 1, 1024, (2 * (e_hi - e_lo) + (T * k <= 4096 ? T * k : 0)) * sizeof(int), s, idx, src_token, slot_row, counts, offsets, (int4*)tiles,
                                                                     n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route);
   CA_CHECK_LAUNCH("route_pack");
   return CA_OK;
@@ -168,6 +170,7 @@ extern "C" int cuteafd_route_pack(const int* idx, int* src_token, int* slot_row,
 __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __restrict__ slot_row, const float* __restrict__ wts,
                                    const bf16* __restrict__ shared, const bf16* __restrict__ residual, bf16* __restrict__ out,
                                    int H, int k) {
+  pdl_launch(); pdl_wait();
   const int t = blockIdx.x;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float acc[8];
@@ -200,7 +203,7 @@ extern "C" int cuteafd_moe_combine(const void* y, const int* slot_row, const flo
   CA_REQUIRE(H % 8 == 0, "moe_combine: hidden must be a multiple of 8");
   if (T <= 0) return CA_OK;
   const int threads = H / 8 >= 256 ? 256 : (H / 8 >= 128 ? 128 : 64);
-  moe_combine_kernel<<<T, threads, 0, s>>>((const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, (bf16*)out, H, k);
+  CA_LAUNCH_PDL(moe_combine_kernel, T, threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, (bf16*)out, H, k);
   CA_CHECK_LAUNCH("moe_combine");
   return CA_OK;
 }

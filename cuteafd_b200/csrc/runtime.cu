@@ -73,7 +73,25 @@ int ca_sm_count() {
   return sms[dev] > 0 ? sms[dev] : 148;
 }
 
+// Programmatic dependent launch switch: -1 = not decided yet (environment CUTEAFD_PDL=1 turns it on; default off:
+// measured on B200 it did not pay for the decode step, see the note in the kernel profile).
+static int g_pdl = -1;
+int ca_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("CUTEAFD_PDL");
+    g_pdl = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_pdl;
+}
+
 extern "C" {
+
+// Turns programmatic dependent launch on or off for later launches of this process; returns the old value.
+int cuteafd_set_pdl(int on) {
+  int old = ca_pdl_enabled();
+  g_pdl = on ? 1 : 0;
+  return old;
+}
 
 // Fills a 128-byte host buffer with a tiled TMA descriptor for a K-major operand whose box is
 // {128 bytes of K, box_rows rows} with the 128-byte swizzle.  elem_bytes: 1 (fp8 / packed fp4 bytes) or 2 (bf16).

@@ -21,6 +21,7 @@ __device__ __forceinline__ bool allowed(const uint32_t* mask, int i) { return !m
 // status[t]: 0 ok, 1 = non-finite logit seen, 2 = mask allows nothing.
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int V, const uint32_t* __restrict__ masks, int mask_words,
                                    int* __restrict__ tok, float* __restrict__ logprob, int* __restrict__ status) {
+  pdl_launch(); pdl_wait();
   __shared__ float sv[32]; __shared__ int si[32]; __shared__ float red[32];
   const int t = blockIdx.x;
   const float* x = logits + (size_t)t * ld;
@@ -63,7 +64,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int
 extern "C" int cuteafd_argmax_rows(const float* logits, int ld, int T, int V, const uint32_t* masks, int mask_words, int* tok,
                                    float* logprob, int* status, cudaStream_t s) {
   if (T <= 0) return CA_OK;
-  argmax_rows_kernel<<<T, 1024, 0, s>>>(logits, ld, V, masks, mask_words, tok, logprob, status);
+  CA_LAUNCH_PDL(argmax_rows_kernel, T, 1024, 0, s, logits, ld, V, masks, mask_words, tok, logprob, status);
   CA_CHECK_LAUNCH("argmax_rows");
   return CA_OK;
 }

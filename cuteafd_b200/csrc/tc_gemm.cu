@@ -42,8 +42,18 @@ struct TcArgs {
   float* splitk_ws;           // [splits, rows_pad, N] partials (dense split-K)
   int* splitk_cnt;            // [items * n_tiles * 4] arrival counters, zero on entry, left zero on exit
   int* status;
-  int ldsfb, ldy, rows_total, N, K, epi, splits;
+  long long* trace;           // optional per-unit time stamps [grid, trace_units, 8] (see cuteafd_tc_trace)
+  int ldsfb, ldy, rows_total, N, K, epi, splits, trace_units;
 };
+
+// Per-unit device trace: slot 0/1 producer first/last load issued, 2 MMA thread owns the accumulator, 4 last MMA
+// issued, 5/6 epilogue (first epilogue warp) begin/end - SM cycle counter - and 7 the global nanosecond timer at
+// the producer's unit start (slot 3 is unused).
+#define TC_TRACE(slot, val)                                                                        \
+  do {                                                                                              \
+    if (a.trace && lane == 0 && (w - w_begin) < a.trace_units)                                      \
+      a.trace[((size_t)blockIdx.x * a.trace_units + (w - w_begin)) * 8 + (slot)] = (long long)(val); \
+  } while (0)
 
 template <int KIND, int TN, bool SWIGLU>
 struct TcCfg {
@@ -55,15 +65,20 @@ struct TcCfg {
   static constexpr int SFA_BYTES = SF_CHUNKS * 512;
   static constexpr int SFB_BYTES = SF_CHUNKS * 512 * NBLK;
   static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + NA * SFA_BYTES + SFB_BYTES;
-  static constexpr int NSTAGE_RAW = (200 * 1024) / STAGE_BYTES;
+  // Decode-sized token tiles run two CTAs per SM (half the shared memory and half the tensor memory each): the
+  // per-stage chain of one CTA (barrier wait -> scale copies -> MMAs -> commit) is latency-bound, two
+  // independent chains per SM keep the memory system busy.
+  static constexpr int OCC = TN <= 32 ? 2 : 1;
+  static constexpr int NSTAGE_RAW = ((OCC == 2 ? 104 : 200) * 1024) / STAGE_BYTES;
   static constexpr int NSTAGE = NSTAGE_RAW > 8 ? 8 : NSTAGE_RAW;
   static constexpr int ACC_COLS = NA * TN;
   static constexpr int NACC = (2 * ACC_COLS <= 384) ? 2 : 1;
-  static constexpr int SFA_COL = 448, SFA2_COL = 464, SFB_COL = 480;   // tensor-memory columns of the scales
+  static constexpr int TMEM_COLS = OCC == 2 ? 256 : 512;
+  static constexpr int SFA_COL = TMEM_COLS - 64, SFA2_COL = TMEM_COLS - 48, SFB_COL = TMEM_COLS - 32;   // tensor-memory columns of the scales
   static constexpr int K_ELEMS = KIND == KIND_BF16 ? 64 : 256;         // K elements per stage (128 bytes per row)
   static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024;
   static_assert(NSTAGE >= 2, "tile too large for shared memory");
-  static_assert(ACC_COLS * NACC <= 448, "accumulators overlap the scale columns");
+  static_assert(ACC_COLS * NACC <= SFA_COL, "accumulators overlap the scale columns");
 };
 
 __device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) {
@@ -85,7 +100,7 @@ __device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) 
 }
 
 template <int KIND, int TN, bool SWIGLU>
-__global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant__ TcArgs a) {
+__global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_kernel(const __grid_constant__ TcArgs a) {
   using C = TcCfg<KIND, TN, SWIGLU>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[C::NSTAGE], empty_bar[C::NSTAGE], accf_bar[2], acce_bar[2];
@@ -101,13 +116,19 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
     abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  const int n_items = a.tiles ? *a.n_tiles : (a.rows_total + TN - 1) / TN;
+  // The next kernel of the stream may start its prologue now.  Grouped launches read the tile table an earlier
+  // kernel wrote, so every thread waits for the previous kernel here; a dense launch lets its producer warp
+  // stream the first weight stages (static data) before it waits.
+  pdl_launch();
+  const bool dense = a.tiles == nullptr;
+  if (!(dense && warp == 0)) pdl_wait();
+  const int n_items = dense ? (a.rows_total + TN - 1) / TN : *a.n_tiles;
   const int n_nt = (a.N + 127) / 128;
   const int nkb_all = (a.K + C::K_ELEMS - 1) / C::K_ELEMS;
   const int splits = a.splits > 1 ? a.splits : 1;
@@ -120,28 +141,45 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    uint32_t it = 0;
+    uint32_t it = 0, npre = 0;
+    // weight-side loads of one stage (static data: legal before the previous kernel has finished)
+    auto load_weights = [&](int s, int g, int nt, int kb) {
+      uint8_t* st = smem + s * C::STAGE_BYTES;
+      uint8_t* sA = st, *sSFA = st + C::NA * C::A_BYTES + C::B_BYTES;
+      mbar_expect_tx(&full_bar[s], C::NA * C::A_BYTES + C::B_BYTES + C::NA * C::SFA_BYTES);
+      const int kx = kb * (KIND == KIND_BF16 ? 64 : 128);      // elements of the descriptor's type
+      tma_load_3d(sA, a.tmA + g, &full_bar[s], kx, nt * 128, 0);
+      if (SWIGLU) tma_load_3d(sA + C::A_BYTES, a.tmA2 + g, &full_bar[s], kx, nt * 128, 0);
+      if (KIND != KIND_BF16) {
+        const size_t off = ((size_t)nt * nkb_all + (size_t)kb) * C::SF_CHUNKS * 512;   // scales are padded to whole stages
+        bulk_load_1d(sSFA, a.sfa[g] + off, C::SFA_BYTES, &full_bar[s]);
+        if (SWIGLU) bulk_load_1d(sSFA + C::SFA_BYTES, a.sfa2[g] + off, C::SFA_BYTES, &full_bar[s]);
+      }
+    };
+    if (dense) {
+      if (w_begin < w_end) {
+        const int sp = w_begin % splits, nt = (w_begin / splits) % n_nt;
+        const int kb0 = (int)(((long long)nkb_all * sp) / splits), kb1 = (int)(((long long)nkb_all * (sp + 1)) / splits);
+        npre = (uint32_t)min(C::NSTAGE, kb1 - kb0);
+        if (lane == 0)
+          for (uint32_t i = 0; i < npre; ++i) load_weights((int)i, 0, nt, kb0 + (int)i);
+      }
+      pdl_wait();
+    }
     for (int w = w_begin; w < w_end && !*abortp; ++w) {
       const int sp = w % splits, tile = w / splits, item = tile / n_nt, nt = tile % n_nt;
       int g = 0, row0 = item * TN, nrows = min(TN, a.rows_total - row0);
       if (a.tiles) { int4 t = a.tiles[item]; g = t.x; row0 = t.y; nrows = t.z; }
       const int kb0 = (int)(((long long)nkb_all * sp) / splits), kb1 = (int)(((long long)nkb_all * (sp + 1)) / splits);
+      TC_TRACE(0, clock64()); TC_TRACE(7, globaltimer_ns());
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % C::NSTAGE;
         if (!mbar_wait_bounded(&empty_bar[s], ((it / C::NSTAGE) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, w); break; }
         uint8_t* st = smem + s * C::STAGE_BYTES;
-        uint8_t* sA = st, *sB = st + C::NA * C::A_BYTES, *sSFA = sB + C::B_BYTES, *sSFB = sSFA + C::NA * C::SFA_BYTES;
+        uint8_t* sB = st + C::NA * C::A_BYTES, *sSFB = sB + C::B_BYTES + C::NA * C::SFA_BYTES;
         if (lane == 0) {
-          mbar_expect_tx(&full_bar[s], C::NA * C::A_BYTES + C::B_BYTES + C::NA * C::SFA_BYTES);
-          const int kx = kb * (KIND == KIND_BF16 ? 64 : 128);      // elements of the descriptor's type
-          tma_load_3d(sA, a.tmA + g, &full_bar[s], kx, nt * 128, 0);
-          if (SWIGLU) tma_load_3d(sA + C::A_BYTES, a.tmA2 + g, &full_bar[s], kx, nt * 128, 0);
-          tma_load_3d(sB, a.tmB, &full_bar[s], kx, row0, 0);
-          if (KIND != KIND_BF16) {
-            const size_t off = ((size_t)nt * nkb_all + (size_t)kb) * C::SF_CHUNKS * 512;   // scales are padded to whole stages
-            bulk_load_1d(sSFA, a.sfa[g] + off, C::SFA_BYTES, &full_bar[s]);
-            if (SWIGLU) bulk_load_1d(sSFA + C::SFA_BYTES, a.sfa2[g] + off, C::SFA_BYTES, &full_bar[s]);
-          }
+          if (it >= npre) load_weights(s, g, nt, kb);          // the first `npre` stages already hold their weights
+          tma_load_3d(sB, a.tmB, &full_bar[s], kb * (KIND == KIND_BF16 ? 64 : 128), row0, 0);
         }
         if (KIND != KIND_BF16) {
           // Activation scales: each token owns SF_CHUNKS*4 consecutive bytes per stage in the row-major array;
@@ -164,25 +202,30 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
           mbar_arrive(&full_bar[s]);
         }
       }
+      TC_TRACE(1, clock64());
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    uint32_t it = 0, tc = 0;
-    for (int w = w_begin; w < w_end && !*abortp; ++w, ++tc) {
-      const int sp = w % splits;
-      const int kb0 = (int)(((long long)nkb_all * sp) / splits), kb1 = (int)(((long long)nkb_all * (sp + 1)) / splits);
-      const int acc = tc % C::NACC;
-      if (!mbar_wait_bounded(&acce_bar[acc], ((tc / C::NACC) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, w); break; }
-      tc_fence_after();
-      const uint32_t d0 = tmem + acc * C::ACC_COLS;
-      bool ok = true;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const int s = it % C::NSTAGE;
-        if (!mbar_wait_bounded(&full_bar[s], (it / C::NSTAGE) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, w); ok = false; break; }
+    // One elected thread waits and issues (the other lanes park at the warp barrier below): no per-stage
+    // divergence or reconvergence on the chain that bounds a decode-sized tile.
+    if (lane == 0) {
+      uint32_t it = 0, tc = 0;
+      const uint32_t smem_base = smem_u32(smem);
+      for (int w = w_begin; w < w_end && !*abortp; ++w, ++tc) {
+        const int sp = w % splits;
+        const int kb0 = (int)(((long long)nkb_all * sp) / splits), kb1 = (int)(((long long)nkb_all * (sp + 1)) / splits);
+        const int acc = tc % C::NACC;
+        if (!mbar_wait_bounded(&acce_bar[acc], ((tc / C::NACC) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, w); break; }
         tc_fence_after();
-        if (KIND != KIND_BF16) fence_proxy_async_smem();   // scale bytes arrived through the generic proxy (cp.async)
-        if (lane == 0) {
-          const uint32_t st = smem_u32(smem + s * C::STAGE_BYTES);
+        TC_TRACE(2, clock64());
+        const uint32_t d0 = tmem + acc * C::ACC_COLS;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % C::NSTAGE;
+          if (!mbar_wait_bounded(&full_bar[s], (it / C::NSTAGE) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, w); ok = false; break; }
+          tc_fence_after();
+          if (KIND != KIND_BF16) fence_proxy_async_smem();   // scale bytes arrived through the generic proxy (cp.async)
+          const uint32_t st = smem_base + s * C::STAGE_BYTES;
           const uint32_t sA = st, sB = st + C::NA * C::A_BYTES, sSFA = sB + C::B_BYTES, sSFB = sSFA + C::NA * C::SFA_BYTES;
           if (KIND != KIND_BF16) {
 #pragma unroll
@@ -215,12 +258,12 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
           }
           tc_commit(&empty_bar[s]);
         }
-        __syncwarp();
+        if (!ok) break;
+        tc_commit(&accf_bar[acc]);
+        TC_TRACE(4, clock64());
       }
-      if (!ok) break;
-      if (lane == 0) tc_commit(&accf_bar[acc]);
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q4 = warp & 3;                 // tensor-memory lane quarter this warp may read
@@ -234,6 +277,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
       const int acc = tc % C::NACC;
       if (!mbar_wait_bounded(&accf_bar[acc], (tc / C::NACC) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, w); break; }
       tc_fence_after();
+      if (warp == 2) TC_TRACE(5, clock64());
       const int n = nt * 128 + et;
       const bool n_ok = n < a.N;
       const float al = a.alpha ? a.alpha[g] : 1.f;
@@ -269,6 +313,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
       }
       tc_fence_before();
       mbar_arrive(&acce_bar[acc]);
+      if (warp == 2) TC_TRACE(6, clock64());
       if (splits > 1) {
         // Deterministic split-K fix-up, warp by warp (no cross-warp barrier, so an aborting warp can never
         // strand another): each warp owns 32 weight rows of the tile and a counter; the last split to
@@ -325,7 +370,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_kernel(const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
+  if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
 template <int KIND, int TN, bool SWIGLU>
@@ -340,8 +385,7 @@ static int launch(const TcArgs& a, int grid, cudaStream_t stream) {
     if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(tc_linear)");
     attr_set[dev & 63] = true;
   }
-  kern<<<grid, 192, C::SMEM_BYTES, stream>>>(a);
-  CA_CHECK_LAUNCH("tc_linear launch");
+  CA_LAUNCH_PDL(kern, grid, 192, C::SMEM_BYTES, stream, a);
   return CA_OK;
 }
 
@@ -355,6 +399,16 @@ static int launch_tn(int tn, const TcArgs& a, int grid, cudaStream_t stream) {
     case 256: if constexpr (!SWIGLU) return launch<KIND, 256, false>(a, grid, stream);
     default: return ca_fail(CA_ERR_ARG, "tc_linear: unsupported token tile %d (swiglu=%d)", tn, (int)SWIGLU);
   }
+}
+
+// Device trace buffer for later launches on the calling thread's device: [grid, units, 8] 64-bit stamps, or
+// null to switch tracing off.  (No counterpart in the reference, whose GEMM programs are opaque AOT exports.)
+static long long* g_trace = nullptr;
+static int g_trace_units = 0;
+extern "C" int cuteafd_tc_trace(void* buf, int units) {
+  g_trace = (long long*)buf;
+  g_trace_units = buf ? units : 0;
+  return CA_OK;
 }
 
 extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, const void* tmA2, const void* tmB,
@@ -376,10 +430,11 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.sfa = (const uint8_t* const*)sfa; a.sfa2 = (const uint8_t* const*)sfa2; a.sfb = (const uint8_t*)sfb;
   a.alpha = alpha; a.alpha2 = alpha2; a.tiles = (const int4*)tiles; a.n_tiles = n_tiles;
   a.Y = Y; a.R = (const bf16*)R; a.splitk_ws = splitk_ws; a.splitk_cnt = splitk_cnt; a.status = status;
+  a.trace = g_trace; a.trace_units = g_trace_units;
   a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;
   const int n_nt = (N + 127) / 128;
   long long work = tiles ? (long long)max_tiles * n_nt : (long long)((rows_total + tn - 1) / tn) * n_nt * a.splits;
-  int cap = max_ctas > 0 ? max_ctas : ca_sm_count();
+  int cap = max_ctas > 0 ? max_ctas : ca_sm_count() * (tn <= 32 ? 2 : 1);
   int grid = (int)(work < cap ? work : cap);
   if (grid < 1) grid = 1;
   if (kind == KIND_BF16) return swiglu ? launch_tn<KIND_BF16, true>(tn, a, grid, stream) : launch_tn<KIND_BF16, false>(tn, a, grid, stream);

@@ -25,6 +25,18 @@ def _chk(t: torch.Tensor, dtype, name: str):
         raise ValueError(f"{name}: expected contiguous CUDA {dtype}, got {t.dtype} cuda={t.is_cuda} contiguous={t.is_contiguous()}")
 
 
+# ------------------------------------------------------------------ launch mode / tracing
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the kernels that support it (off by default; CUTEAFD_PDL=1 turns it on).
+    Graphs captured earlier keep the mode they were captured with."""
+    native.lib().cuteafd_set_pdl(1 if on else 0)
+
+
+def tc_trace(buf: torch.Tensor | None, units: int = 0) -> None:
+    """Per-unit device time stamps of later `tc_linear` launches: int64 [grid, units, 8] (None = off)."""
+    call("cuteafd_tc_trace", ptr(buf), units)
+
+
 # ------------------------------------------------------------------ TMA descriptors
 def encode_tmap(t: torch.Tensor, box_rows: int) -> torch.Tensor:
     """Descriptor array (uint8 [G, 128], on t's device) for a K-major operand [G, rows, K] or [rows, K].

@@ -19,6 +19,8 @@ P, I, F, L, U64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_uint64
 
 _PROTOS = {
     "cuteafd_abi_version": [],
+    "cuteafd_set_pdl": [I],
+    "cuteafd_tc_trace": [P, I],
     "cuteafd_device_info": [P, P, P, P, P],
     "cuteafd_tmap_encode_kmajor": [P, P, I, U64, U64, U64, U64, U64, C.c_uint32],
     "cuteafd_embed_gather": [P, P, P, I, I, I, P, P],
