@@ -89,6 +89,7 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"], help="multi-GPU transport: fused peer-memory kernels, or the NCCL-only baseline")
+    ap.add_argument("--attn-groups", type=int, default=0, help="data-parallel attention groups in the attention/expert split (0 = the config's default)")
     ap.add_argument("--real-prefill", action="store_true", help="build the context by running prefill instead of filling KV")
     args = ap.parse_args()
     if args.impl == "reference":

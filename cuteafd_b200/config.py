@@ -286,25 +286,42 @@ class Deployment:
     attn_ranks: tuple = (0,)
     expert_ranks: tuple = (0,)
     colocated: bool = True
+    attn_groups: int = 1        # data-parallel attention groups; each group is `tp` consecutive entries of attn_ranks
 
     @property
     def tp(self) -> int:
-        return len(self.attn_ranks)
+        return len(self.attn_ranks) // max(1, self.attn_groups)
 
     @property
     def ep(self) -> int:
         return len(self.expert_ranks)
 
+    def group_of(self, rank: int) -> int:
+        return self.attn_ranks.index(rank) // self.tp
+
+    def group_ranks(self, g: int) -> tuple:
+        return tuple(self.attn_ranks[g * self.tp:(g + 1) * self.tp])
+
     def describe(self) -> str:
         if self.world == 1:
             return "single"
-        return f"attn-tp{self.tp}+ep{self.ep}" if not self.colocated else f"tp{self.tp}-ep{self.ep}-colocated"
+        dp = f"dp{self.attn_groups}x" if self.attn_groups > 1 else ""
+        return f"attn-{dp}tp{self.tp}+ep{self.ep}" if not self.colocated else f"tp{self.tp}-ep{self.ep}-colocated"
 
 
-def default_deployment(world: int) -> Deployment:
-    """North-star split: attention TP2 on ranks 0-1, experts EP on the rest (8 GPUs -> TP2 + EP6)."""
+def default_deployment(world: int, attn_groups: int = 1) -> Deployment:
+    """North-star split: attention TP2 on ranks 0-1, experts EP on the rest (8 GPUs -> TP2 + EP6).  With
+    `attn_groups` > 1 the attention side is that many data-parallel groups (each serving its own sequences, all
+    sending to the same expert ranks, which work on one group's tokens while the other groups run attention):
+    4 GPUs -> 2 x TP1 + EP2, 8 GPUs -> 2 x TP2 + EP4."""
     if world == 1:
         return Deployment()
     if world == 2:
         return Deployment(world=2, attn_ranks=(0,), expert_ranks=(1,), colocated=False)
-    return Deployment(world=world, attn_ranks=(0, 1), expert_ranks=tuple(range(2, world)), colocated=False)
+    if attn_groups <= 1:
+        return Deployment(world=world, attn_ranks=(0, 1), expert_ranks=tuple(range(2, world)), colocated=False)
+    n_attn = max(attn_groups, (world // 2 // attn_groups) * attn_groups)
+    if n_attn >= world:
+        raise ValueError(f"{attn_groups} attention groups leave no expert rank in a world of {world}")
+    return Deployment(world=world, attn_ranks=tuple(range(n_attn)), expert_ranks=tuple(range(n_attn, world)), colocated=False,
+                      attn_groups=attn_groups)

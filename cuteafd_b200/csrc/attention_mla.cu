@@ -19,6 +19,7 @@
 // families/glm5/cuda/glm_mla_prefill.cu:123-960 (mma.sync MLA prefill), kv_cache.cu:142 (mla_kv_prepare).
 #include <string.h>
 
+#define CA_PDL_CLASS 2
 #include "common.cuh"
 
 #define MKEYS 32

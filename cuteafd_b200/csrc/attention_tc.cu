@@ -18,6 +18,7 @@
 // kernels (native/shared/cuda/draft_attention.cu:41-340, families/glm5/cuda/glm_mla_prefill.cu:123-960).
 #include <string.h>
 
+#define CA_PDL_CLASS 2
 #include "common.cuh"
 #include "attn_common.cuh"
 

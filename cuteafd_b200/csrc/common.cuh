@@ -39,7 +39,12 @@ typedef __nv_bfloat162 bf162;
 // for a kernel launched the ordinary way, so a kernel may be launched either way.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-int ca_pdl_enabled();
+// Classes: bit 0 glue kernels (norm, quant, routing, sampling), bit 1 GEMM, bit 2 attention; a file names its class
+// with CA_PDL_CLASS before including this header.
+int ca_pdl_enabled(int cls);
+#ifndef CA_PDL_CLASS
+#define CA_PDL_CLASS 0
+#endif
 #define CA_LAUNCH_PDL(kern_, grid_, block_, smem_, stream_, ...)                                              \
   do {                                                                                                   \
     cudaLaunchConfig_t _cfg = {};                                                                        \
@@ -47,7 +52,7 @@ int ca_pdl_enabled();
     cudaLaunchAttribute _at[1];                                                                          \
     _at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                      \
     _at[0].val.programmaticStreamSerializationAllowed = 1;                                               \
-    _cfg.attrs = _at; _cfg.numAttrs = ca_pdl_enabled() ? 1 : 0;                                          \
+    _cfg.attrs = _at; _cfg.numAttrs = ca_pdl_enabled(CA_PDL_CLASS) ? 1 : 0;                                          \
     cudaError_t _le = cudaLaunchKernelEx(&_cfg, kern_, __VA_ARGS__);                                      \
     if (_le != cudaSuccess) return ca_cuda(_le, #kern_ " launch");                                        \
   } while (0)

@@ -4,6 +4,7 @@
 // (native/shared/src/cuteafd_native.cc: status/last-error, device info, copies).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -73,23 +74,25 @@ int ca_sm_count() {
   return sms[dev] > 0 ? sms[dev] : 148;
 }
 
-// Programmatic dependent launch switch: -1 = not decided yet (environment CUTEAFD_PDL=1 turns it on; default off:
-// measured on B200 it did not pay for the decode step, see the note in the kernel profile).
+// Programmatic dependent launch switch: a bit mask over kernel classes (bit 0 glue, bit 1 GEMM, bit 2 attention);
+// -1 = not decided yet (environment CUTEAFD_PDL=<mask>; default 2: measured on B200, GEMM-only is the one setting that pays - chains of
+// early-resident kernels take shared memory from the attention kernel and cost more than they save).
 static int g_pdl = -1;
-int ca_pdl_enabled() {
+int ca_pdl_enabled(int cls) {
   if (g_pdl < 0) {
     const char* e = getenv("CUTEAFD_PDL");
-    g_pdl = (e && e[0] == '1') ? 1 : 0;
+    g_pdl = e ? atoi(e) & 7 : 2;
   }
-  return g_pdl;
+  return (g_pdl >> cls) & 1;
 }
 
 extern "C" {
 
-// Turns programmatic dependent launch on or off for later launches of this process; returns the old value.
-int cuteafd_set_pdl(int on) {
-  int old = ca_pdl_enabled();
-  g_pdl = on ? 1 : 0;
+// Sets the programmatic-dependent-launch class mask for later launches of this process; returns the old mask.
+int cuteafd_set_pdl(int mask) {
+  ca_pdl_enabled(0);
+  int old = g_pdl;
+  g_pdl = mask & 7;
   return old;
 }
 

@@ -21,6 +21,7 @@
 // Replaces, in the reference, the AOT-exported expert/FP8/FFN programs whose sources are absent
 // (native/shared/include/cuteafd_experts.h:13-44, cuteafd_fp8_moe.h:1-51) and the cuBLAS linears
 // (native/shared/cuda/linear.cu:865-1350).
+#define CA_PDL_CLASS 1
 #include "common.cuh"
 
 enum { KIND_BF16 = 0, KIND_NVFP4 = 1, KIND_MXFP4 = 2 };

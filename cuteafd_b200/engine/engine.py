@@ -222,8 +222,12 @@ class Engine:
                                 Hkv=a.n_kv_heads, D=a.head_dim, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
                                 window=a.window, sink=lw.sink)
         oq = self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
-        self._dense(lw.wo, oq, L.x, T, residual=L.x)
+        self._attn_out(li, lw, oq, L, T)
         self.launches_per_step += 3 + (2 if sh.attn_splits > 1 else 0)
+
+    def _attn_out(self, li: int, lw: LayerWeights, oq: ActBuffer, L: Lane, T: int):
+        """Output projection + residual (a tensor-parallel rank overrides this with partial sum + exchange)."""
+        self._dense(lw.wo, oq, L.x, T, residual=L.x)
 
     def _ffn(self, lw: LayerWeights, L: Lane, T: int, out, residual):
         """Shared expert / dense FFN: out = residual + down(silu(gate x) * up x)."""

@@ -103,7 +103,8 @@ def mla_weights_random(spec: ModelSpec, device, *, heads_local: int | None = Non
             if m.use_bias:
                 out.router_bias = torch.zeros(m.n_experts, dtype=torch.float32, device=device)
             if e_hi > e_lo:
-                out.w_gate, out.w_up, out.w_down = R(e_hi - e_lo, m.intermediate, h, ek, 8), R(e_hi - e_lo, m.intermediate, h, ek, 9), R(e_hi - e_lo, h, m.intermediate, ek, 10)
+                RE = lambda N, K, j: TcWeight.random(m.n_experts, N, K, ek, device, spec.init_std, act_gs, s + j, groups=(e_lo, e_hi))
+                out.w_gate, out.w_up, out.w_down = RE(m.intermediate, h, 8), RE(m.intermediate, h, 9), RE(h, m.intermediate, 10)
             if m.shared_inter:
                 out.ws_gate, out.ws_up, out.ws_down = R(1, m.shared_inter, h, dk, 11), R(1, m.shared_inter, h, dk, 12), R(1, h, m.shared_inter, dk, 13)
         else:

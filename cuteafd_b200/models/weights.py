@@ -167,14 +167,13 @@ class DeviceWeights:
         def make_layer(i: int) -> LayerWeights:
             s = seed * 1000 + i * 16
             R = lambda G, N, K, kind, j: TcWeight.random(G, N, K, kind, device, spec.init_std, act_gs, s + j)
+            RE = lambda N, K, j: TcWeight.random(m.n_experts, N, K, ek, device, spec.init_std, act_gs, s + j, groups=(e_lo, e_hi))
             out = LayerWeights(attn_norm=ones(h), ffn_norm=ones(h),
                                wqkv=R(1, (a.n_heads + 2 * a.n_kv_heads) * a.head_dim, h, dk, 0) if with_attention else None,
                                wo=R(1, h, a.n_heads * a.head_dim, dk, 1) if with_attention else None)
             if not with_attention:      # expert rank: routed experts only
                 if spec.is_moe_layer(i) and e_hi > e_lo:
-                    out.w_gate = R(e_hi - e_lo, m.intermediate, h, ek, 3)
-                    out.w_up = R(e_hi - e_lo, m.intermediate, h, ek, 4)
-                    out.w_down = R(e_hi - e_lo, h, m.intermediate, ek, 5)
+                    out.w_gate, out.w_up, out.w_down = RE(m.intermediate, h, 3), RE(m.intermediate, h, 4), RE(h, m.intermediate, 5)
                 return out
             if a.qk_norm:
                 out.q_norm, out.k_norm = ones(a.head_dim), ones(a.head_dim)
@@ -183,9 +182,7 @@ class DeviceWeights:
                 if m.use_bias:
                     out.router_bias = torch.zeros(m.n_experts, dtype=torch.float32, device=device)
                 if e_hi > e_lo:
-                    out.w_gate = R(e_hi - e_lo, m.intermediate, h, ek, 3)
-                    out.w_up = R(e_hi - e_lo, m.intermediate, h, ek, 4)
-                    out.w_down = R(e_hi - e_lo, h, m.intermediate, ek, 5)
+                    out.w_gate, out.w_up, out.w_down = RE(m.intermediate, h, 3), RE(m.intermediate, h, 4), RE(h, m.intermediate, 5)
                 if m.shared_inter:
                     out.ws_gate, out.ws_up = R(1, m.shared_inter, h, dk, 6), R(1, m.shared_inter, h, dk, 7)
                     out.ws_down = R(1, h, m.shared_inter, dk, 8)

@@ -26,10 +26,10 @@ def _chk(t: torch.Tensor, dtype, name: str):
 
 
 # ------------------------------------------------------------------ launch mode / tracing
-def set_pdl(on: bool) -> None:
-    """Programmatic dependent launch for the kernels that support it (off by default; CUTEAFD_PDL=1 turns it on).
-    Graphs captured earlier keep the mode they were captured with."""
-    native.lib().cuteafd_set_pdl(1 if on else 0)
+def set_pdl(mask: int) -> None:
+    """Programmatic dependent launch per kernel class (bit 0 glue kernels, bit 1 GEMMs, bit 2 attention; 0 = off, the
+    default; CUTEAFD_PDL=<mask> sets it from the environment).  Graphs captured earlier keep their mode."""
+    native.lib().cuteafd_set_pdl(int(mask))
 
 
 def tc_trace(buf: torch.Tensor | None, units: int = 0) -> None:
@@ -109,23 +109,27 @@ class TcWeight:
 
     @staticmethod
     def random(G: int, N: int, K: int, kind: str | int, device, std: float = 0.02, act_gs: float = 1.0 / 64,
-               seed: int = 0) -> "TcWeight":
-        """Random-init weights generated directly in the storage format on the device (large synthetic models)."""
+               seed: int = 0, groups: tuple | None = None) -> "TcWeight":
+        """Random-init weights generated directly in the storage format on the device (large synthetic models).
+        `groups=(lo, hi)` keeps only groups [lo, hi) of the G generated ones, so an expert-parallel rank holds exactly
+        the experts a single-GPU model of the same seed has at those indices."""
         kind = KIND_BY_NAME[kind] if isinstance(kind, str) else kind
         gen = torch.Generator(device=device).manual_seed(seed)
+        lo, hi = groups if groups is not None else (0, G)
+        cut = (lambda t: t[lo:hi].clone()) if (lo, hi) != (0, G) else (lambda t: t)
         if kind == KIND_BF16:
-            data = torch.empty(G, N, K, dtype=torch.bfloat16, device=device).normal_(0, std, generator=gen)
-            return TcWeight(kind, G, N, K, data, encode_tmap(data, 128))
-        data = torch.randint(0, 256, (G, N, K // 2), dtype=torch.uint8, device=device, generator=gen)
+            data = cut(torch.empty(G, N, K, dtype=torch.bfloat16, device=device).normal_(0, std, generator=gen))
+            return TcWeight(kind, hi - lo, N, K, data, encode_tmap(data, 128))
+        data = cut(torch.randint(0, 256, (G, N, K // 2), dtype=torch.uint8, device=device, generator=gen))
         vec = 16 if kind == KIND_NVFP4 else 32
         nsf = (-(-N // 128) * 128) * (-(-K // 256) * (256 // vec))
         if kind == KIND_NVFP4:   # E4M3 scales in [0.5, 1.875]
-            sf = torch.randint(0x30, 0x40, (G, nsf), dtype=torch.uint8, device=device, generator=gen)
-            alpha = torch.full((G,), std / 3.4 * act_gs, dtype=torch.float32, device=device)
+            sf = cut(torch.randint(0x30, 0x40, (G, nsf), dtype=torch.uint8, device=device, generator=gen))
+            alpha = torch.full((hi - lo,), std / 3.4 * act_gs, dtype=torch.float32, device=device)
         else:                    # UE8M0 scales 2^-7 .. 2^-6 -> |w| ~ std
-            sf = torch.randint(120, 122, (G, nsf), dtype=torch.uint8, device=device, generator=gen)
-            alpha = torch.full((G,), std / 0.034, dtype=torch.float32, device=device)
-        return TcWeight._finish(kind, G, N, K, data, sf, alpha, act_gs)
+            sf = cut(torch.randint(120, 122, (G, nsf), dtype=torch.uint8, device=device, generator=gen))
+            alpha = torch.full((hi - lo,), std / 0.034, dtype=torch.float32, device=device)
+        return TcWeight._finish(kind, hi - lo, N, K, data, sf, alpha, act_gs)
 
     @staticmethod
     def _finish(kind, G, N, K, data, sf, alpha, act_gs):

@@ -11,6 +11,10 @@ the KV cache) and an expert group (expert-parallel routed experts).  Per MoE lay
                    COMBINE: store every output row into [token][slot] of both attention ranks (+ flag)
   attention TP2:   wo partial -> push to the peer + flag -> wait -> add in rank order (bit-identical on both ranks)
 
+With several data-parallel attention groups (`Deployment.attn_groups`) every group serves its own sequences and owns a
+slab / routing-table / flag lane on each expert rank; an expert rank runs the lanes one after the other per layer, so
+it computes group A's experts while group B is in attention (the groups fall out of phase after the first layer).
+
 `comm="p2p"` uses the peer-memory kernels of `csrc/peer.cu`; `comm="nccl"` is the baseline that only calls NCCL
 (broadcast activations + routes, all-reduce expert partial sums, all-reduce attention partials).
 
@@ -44,13 +48,13 @@ def local_attention_spec(spec: ModelSpec, tp: int) -> ModelSpec:
 
 def make_block(spec: ModelSpec, dep: Deployment, t_max: int, expert_kind: int, rank: int, device, group) -> SymmetricBlock:
     """Symmetric regions (same layout on every rank; each role uses its part)."""
-    H, k = spec.hidden, spec.moe.top_k
+    H, k, G = spec.hidden, spec.moe.top_k, dep.attn_groups
     rows = t_max * k
     row_bytes = H * 2 if expert_kind == KIND_BF16 else H // 2
     vec = 16 if expert_kind == KIND_NVFP4 else 32
     sf_ld = -(-H // 256) * (256 // vec)
-    regions = {
-        "slab_q": rows * row_bytes, "slab_sf": rows * sf_ld, "idx": rows * 4,
+    regions = {     # the expert-side regions hold one lane per attention group
+        "slab_q": G * rows * row_bytes, "slab_sf": G * rows * sf_ld, "idx": G * rows * 4,
         "y_recv": rows * H * 2, "tp_recv": 2 * t_max * H * 2,
         "flags": 3 * spec.n_layers * 8 * 4,
     }
@@ -67,7 +71,10 @@ class AttnRankEngine(Engine):
     def __init__(self, spec: ModelSpec, dep: Deployment, rank: int, device, *, t_max: int, n_pages: int, max_seqs: int,
                  max_pages_per_seq: int, comm: str, block: SymmetricBlock | None, expert_kind: int, act_gs: float = 1.0 / 64, seed: int = 1):
         self.full_spec, self.dep, self.rank, self.comm, self.block = spec, dep, rank, comm, block
-        self.tp, self.tp_rank = dep.tp, dep.attn_ranks.index(rank)
+        self.tp, self.tp_rank = dep.tp, dep.attn_ranks.index(rank) % dep.tp
+        self.group = dep.group_of(rank)
+        self.group_ranks = dep.group_ranks(self.group)
+        self.flag_src = self.group * dep.tp + self.tp_rank       # this rank's slot among the dispatch flags
         lw = self._make_weights(spec, device, seed, act_gs)
         super().__init__(lw, n_pages=n_pages, max_seqs=max_seqs, max_pages_per_seq=max_pages_per_seq, device=device)
         self.remote_kind = expert_kind
@@ -89,34 +96,40 @@ class AttnRankEngine(Engine):
         if block is not None:
             vec = 16 if expert_kind == KIND_NVFP4 else 32
             self.sf_ld = -(-H // 256) * (256 // vec)
-            self.slab_q_tbl = block.ptr_table(dep.expert_ranks, "slab_q")
-            self.slab_sf_tbl = block.ptr_table(dep.expert_ranks, "slab_sf")
-            self.idx_tbl = block.ptr_table(dep.expert_ranks, "idx")
+            row_bytes = H * 2 if expert_kind == KIND_BF16 else H // 2
+            g = self.group                                       # my group's lane on every expert rank
+            self.slab_q_tbl = block.ptr_table(dep.expert_ranks, "slab_q", g * rows * row_bytes)
+            self.slab_sf_tbl = block.ptr_table(dep.expert_ranks, "slab_sf", g * rows * self.sf_ld)
+            self.idx_tbl = block.ptr_table(dep.expert_ranks, "idx", g * rows * 4)
             self.y_recv = block.local("y_recv", torch.bfloat16, (rows, H))
             self.tp_recv = block.local("tp_recv", torch.bfloat16, (2, t_max, H))
 
     def _make_weights(self, spec, device, seed, act_gs):
-        """This rank's share: attention heads split over the TP group, router/shared/dense replicated, no routed experts."""
-        return DeviceWeights.random(local_attention_spec(spec, self.tp), device, seed=seed, experts_range=(0, 0), act_gs=act_gs)
+        """This rank's share: attention heads split over the TP group, router/shared/dense replicated, no routed experts.
+        With bf16 projections the shard is cut out of the full-model weights of the same seed (so the split reproduces
+        the single-GPU model exactly); block-scaled projections are generated per shard (synthetic benchmarks)."""
+        if self.tp == 1 or spec.quant.dense != "bf16":
+            return DeviceWeights.random(local_attention_spec(spec, self.tp), device, seed=seed, experts_range=(0, 0), act_gs=act_gs)
+        from ..ops import TcWeight, encode_tmap
+        dw = DeviceWeights.random(spec, device, seed=seed, experts_range=(0, 0), act_gs=act_gs)
+        a, r, tp = spec.attn, self.tp_rank, self.tp
+        hq, hkv, D = a.n_heads // tp, a.n_kv_heads // tp, a.head_dim
+        nq, nk = a.n_heads * D, a.n_kv_heads * D
+        for lw in dw.layers:
+            w = lw.wqkv.data[0]
+            rows = torch.cat([w[r * hq * D:(r + 1) * hq * D], w[nq + r * hkv * D:nq + (r + 1) * hkv * D],
+                              w[nq + nk + r * hkv * D:nq + nk + (r + 1) * hkv * D]]).unsqueeze(0).contiguous()
+            lw.wqkv = TcWeight(KIND_BF16, 1, rows.shape[1], rows.shape[2], rows, encode_tmap(rows, 128))
+            cols = lw.wo.data[:, :, r * hq * D:(r + 1) * hq * D].contiguous()
+            lw.wo = TcWeight(KIND_BF16, 1, cols.shape[1], cols.shape[2], cols, encode_tmap(cols, 128))
+        dw.spec = local_attention_spec(spec, tp)
+        return dw
 
-    # -- attention with the TP all-reduce of the output projection
-    def _attention_layer(self, li, lw, L, sh):
+    # -- output projection with the TP all-reduce
+    def _attn_out(self, li, lw, oq, L, T):
         if self.tp == 1:
-            return super()._attention_layer(li, lw, L, sh)
-        spec, a, T = self.spec, self.spec.attn, sh.T
-        md = self.md
-        ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, spec.rms_eps, rows=T)
-        xq = self._quant(L.xn, L.xq, T, lw.wqkv.inv_act_gs)
-        self._dense(lw.wqkv, xq, L.qkv, T)
-        ops.qk_norm_rope_kvwrite(L.qkv, md["positions"], md["slot_map"], lw.q_norm, lw.k_norm, self.kv[li], T,
-                                 a.n_heads, a.n_kv_heads, a.head_dim, a.rope_theta, a.rope_interleaved, spec.rms_eps, self.status)
-        ops.paged_attention_tc(L.qkv, self.kv_tmaps[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
-                               T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
-                               Hkv=a.n_kv_heads, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
-                               window=a.window, sink=lw.sink, status=self.status)
-        oq = self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
-        self._dense(lw.wo, oq, self.part, T)                      # partial sum over my heads
-        self.launches_per_step += 4
+            return super()._attn_out(li, lw, oq, L, T)
+        self._dense(lw.wo, oq, self.part, T)              # partial sum over my heads, then the TP exchange
         self._tp_allreduce(li, self.part, L.x, T)
 
     def _tp_allreduce(self, li, part, x, T):
@@ -127,7 +140,7 @@ class AttnRankEngine(Engine):
             dist.all_reduce(part[:T], group=self.tp_group)
             x[:T] += part[:T]
             return
-        peer = self.dep.attn_ranks[1 - self.tp_rank]
+        peer = self.group_ranks[1 - self.tp_rank]
         buf = li & 1
         nbytes = T * H * 2
         peer_ops.push_bytes(part, self.block.peer_ptr(peer, "tp_recv", buf * self.t_max * H * 2), nbytes,
@@ -154,7 +167,7 @@ class AttnRankEngine(Engine):
         # my share of the tokens (the other attention rank sends the rest; both hold identical activations)
         per = -(-T // self.tp)
         t0, t1 = min(T, self.tp_rank * per), min(T, (self.tp_rank + 1) * per)
-        flag_tbl = self.block.ptr_table(dep.expert_ranks, "flags", flag_offset(spec, PH_DISPATCH, li, self.tp_rank))
+        flag_tbl = self.block.ptr_table(dep.expert_ranks, "flags", flag_offset(spec, PH_DISPATCH, li, self.flag_src))
         peer_ops.dispatch_push(L.xn, self.idx, self.slot_row, self.offsets, self.slab_q_tbl, self.slab_sf_tbl, self.idx_tbl, flag_tbl,
                                self.inv_gs, self.ctl, self.done[1:2], t0, t1, spec.hidden, m.top_k, self.e_local, dep.ep,
                                self.remote_kind, self.sf_ld, self.t_max * m.top_k, 0, self.status)
@@ -168,6 +181,8 @@ class AttnRankEngine(Engine):
 
     def _moe_nccl(self, li, lw, L, T):
         import torch.distributed as dist
+        if self.dep.attn_groups > 1:
+            raise NotImplementedError("the NCCL-only baseline runs one attention group")
         m, H = self.full_spec.moe, self.full_spec.hidden
         src = self.dep.attn_ranks[0]
         dist.broadcast(L.xn[:T], src)
@@ -201,13 +216,6 @@ class MlaAttnRankEngine(AttnRankEngine):
     def _make_weights(self, spec, device, seed, act_gs):
         from ..engine.mla import mla_weights_random
         return mla_weights_random(spec, device, heads_local=spec.attn.n_heads // self.tp, experts_range=(0, 0), act_gs=act_gs, seed=seed)
-
-    def _attn_out(self, li, lw, oq, L, T):
-        if self.tp == 1:
-            self._dense(lw.wo, oq, L.x, T, residual=L.x)
-            return
-        self._dense(lw.wo, oq, self.part, T)              # partial sum over my heads, then the TP exchange
-        self._tp_allreduce(li, self.part, L.x, T)
 
 
 def _bind_mla(cls):
@@ -248,17 +256,24 @@ class ExpertRankWorker:
                      else ActBuffer.wrap_bf16(self.h1, self.tn))
         self.y2 = torch.zeros(rows, H, dtype=torch.bfloat16, device=device)
         self.launches_per_step = 0
+        G = dep.attn_groups
         if block is not None:
+            # one lane (slab, scales, routing table, destination ranks) per attention group
+            self.xs_g, self.idx_g, self.recv_tbl_g = [], [], []
             if self.kind == KIND_BF16:
-                data = block.local("slab_q", torch.bfloat16, (rows, H))
-                self.xs = ActBuffer(self.kind, rows, H, self.tn, data, ops.encode_tmap(data, self.tn))
+                data_all = block.local("slab_q", torch.bfloat16, (G, rows, H))
+                sf_all = None
             else:
                 vec = 16 if self.kind == KIND_NVFP4 else 32
-                data = block.local("slab_q", torch.uint8, (rows, H // 2))
-                sf = block.local("slab_sf", torch.uint8, (rows, -(-H // 256) * (256 // vec)))
-                self.xs = ActBuffer(self.kind, rows, H, self.tn, data, ops.encode_tmap(data, self.tn), sf)
-            self.idx = block.local("idx", torch.int32, (t_max, k))
-            self.recv_tbl = block.ptr_table(dep.attn_ranks, "y_recv")
+                data_all = block.local("slab_q", torch.uint8, (G, rows, H // 2))
+                sf_all = block.local("slab_sf", torch.uint8, (G, rows, -(-H // 256) * (256 // vec)))
+            idx_all = block.local("idx", torch.int32, (G, t_max, k))
+            for g in range(G):
+                self.xs_g.append(ActBuffer(self.kind, rows, H, self.tn, data_all[g], ops.encode_tmap(data_all[g], self.tn),
+                                           sf_all[g] if sf_all is not None else None))
+                self.idx_g.append(idx_all[g])
+                self.recv_tbl_g.append(block.ptr_table(dep.group_ranks(g), "y_recv"))
+            self.xs, self.idx = self.xs_g[0], self.idx_g[0]
         else:
             self.xs = ActBuffer.alloc(self.kind, rows, H, self.tn, device)
             self.idx = i32(t_max, k)
@@ -272,20 +287,23 @@ class ExpertRankWorker:
         rows = T * m.top_k
         if self.comm == "nccl":
             return self._layer_nccl(li, lw, T)
-        peer_ops.wait_flags(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_DISPATCH, li, 0)), dep.tp, 1, self.ctl, 0, self.status)
-        ops.route_pack(self.idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
-                       T, m.top_k, self.e_lo, self.e_hi, self.tn, self.max_tiles, src_route=self.src_route)
-        ops.tc_linear(lw.w_gate, self.xs, self.h1, rows=rows, w_up=lw.w_up, tiles=self.tiles, n_tiles=self.n_tiles,
-                      max_tiles=self.max_tiles, status=self.status)
-        if self.kind != KIND_BF16:
-            ops.quant_fp4_rows(self.h1, self.h1_q, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
-        ops.tc_linear(lw.w_down, self.h1_q, self.y2, rows=rows, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
-                      status=self.status)
-        flag_tbl = self.block.ptr_table(dep.attn_ranks, "flags", flag_offset(spec, PH_COMBINE, li, self.ep_rank))
-        self._keep.append(flag_tbl)
-        peer_ops.combine_push(self.y2, self.src_route, self.n_rows, self.recv_tbl, flag_tbl, self.ctl, self.done[0:1], spec.hidden,
-                              dep.tp, rows, 0)
-        self.launches_per_step += 6
+        for g in range(dep.attn_groups):
+            xs, idx = self.xs_g[g], self.idx_g[g]
+            peer_ops.wait_flags(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_DISPATCH, li, g * dep.tp)), dep.tp, 1,
+                                self.ctl, 0, self.status)
+            ops.route_pack(idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
+                           T, m.top_k, self.e_lo, self.e_hi, self.tn, self.max_tiles, src_route=self.src_route)
+            ops.tc_linear(lw.w_gate, xs, self.h1, rows=rows, w_up=lw.w_up, tiles=self.tiles, n_tiles=self.n_tiles,
+                          max_tiles=self.max_tiles, status=self.status)
+            if self.kind != KIND_BF16:
+                ops.quant_fp4_rows(self.h1, self.h1_q, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
+            ops.tc_linear(lw.w_down, self.h1_q, self.y2, rows=rows, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
+                          status=self.status)
+            flag_tbl = self.block.ptr_table(dep.group_ranks(g), "flags", flag_offset(spec, PH_COMBINE, li, self.ep_rank))
+            self._keep.append(flag_tbl)
+            peer_ops.combine_push(self.y2, self.src_route, self.n_rows, self.recv_tbl_g[g], flag_tbl, self.ctl, self.done[0:1], spec.hidden,
+                                  dep.tp, rows, 0)
+            self.launches_per_step += 6
 
     def _layer_nccl(self, li, lw, T):
         import torch.distributed as dist

@@ -26,10 +26,10 @@ OP_STOP, OP_STEP, OP_TIMER_START, OP_TIMER_STOP = 0, 1, 2, 3
 
 class AfdRunner:
     def __init__(self, spec: ModelSpec, rank: int, world: int, local: int, *, t_max: int, n_pages: int, max_seqs: int,
-                 max_pages_per_seq: int, comm: str = "p2p", seed: int = 1):
+                 max_pages_per_seq: int, comm: str = "p2p", seed: int = 1, attn_groups: int = 1):
         self.spec, self.rank, self.world = spec, rank, world
         self.dev = torch.device("cuda", local)
-        self.dep = default_deployment(world)
+        self.dep = default_deployment(world, attn_groups)
         self.comm = comm
         self.ctrl = dist.new_group(backend="gloo")
         self.tp_group = dist.new_group(list(self.dep.attn_ranks))
@@ -108,11 +108,18 @@ class AfdRunner:
 
 def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, local: int, clocks) -> dict:
     comm = getattr(args, "comm", "p2p")
-    batch = getattr(args, "batch_total", 0) or args.batch_per_gpu * world
+    batch_total = getattr(args, "batch_total", 0) or args.batch_per_gpu * world
+    # Data-parallel attention groups: by default two once there are four GPUs (GQA models over the peer-memory path);
+    # MLA configs keep the single TP2 group their published layout names.
+    groups = getattr(args, "attn_groups", 0) or (2 if (world >= 4 and comm == "p2p" and spec.attn.kind == "gqa" and batch_total % 2 == 0) else 1)
+    if batch_total % groups:
+        raise SystemExit(f"batch {batch_total} does not split over {groups} attention groups")
+    batch = batch_total // groups                     # sequences served by each attention group
     ctx_pages = -(-(args.context + 4 * (args.steps + args.warmup) + 64) // PAGE)
     pages = batch * (ctx_pages + 1) + 2
     t0 = time.time()
-    run = AfdRunner(spec, rank, world, local, t_max=max(16, batch), n_pages=pages, max_seqs=batch, max_pages_per_seq=ctx_pages + 1, comm=comm)
+    run = AfdRunner(spec, rank, world, local, t_max=max(16, batch), n_pages=pages, max_seqs=batch, max_pages_per_seq=ctx_pages + 1, comm=comm,
+                    attn_groups=groups)
     use_graph = comm == "p2p"
     res = None
     if run.is_attn:
@@ -173,16 +180,16 @@ def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, l
         ms = float(tmax[0])
         dep = run.dep
         res = {
-            "metric": "decode_tokens_per_s", "value": round(batch * args.steps / (ms / 1e3), 2), "unit": "tokens/s",
+            "metric": "decode_tokens_per_s", "value": round(batch_total * args.steps / (ms / 1e3), 2), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
             "higher_is_better": True, "scaling": "weak" if not getattr(args, "batch_total", 0) else "strong", "vs_baseline": None,
             "dtype": f"bf16 activations, {spec.quant.experts} experts / {spec.quant.dense} dense (dense runs as bf16 when the format has no kernel yet)",
             "data": "synthetic token ids, random-init weights, context KV random-filled",
-            "config": {"model": spec.name + (f" (DEBUG {args.layers} layers: INVALID)" if args.layers else ""), "global_batch": batch,
-                       "seq_len": args.context, "parallelism": f"afd attn-tp{dep.tp} + experts-ep{dep.ep} ({comm})", "layers": spec.n_layers,
+            "config": {"model": spec.name + (f" (DEBUG {args.layers} layers: INVALID)" if args.layers else ""), "global_batch": batch_total,
+                       "seq_len": args.context, "parallelism": f"afd {dep.describe()} ({comm})", "layers": spec.n_layers,
                        "l2": "inputs (weights + KV) far larger than L2; no flush needed", "setup_s": round(setup_s, 1)},
             "clocks": clk,
-            "e2e": {"value": round(batch * args.steps / e2e_s, 2), "unit": "tokens/s", "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
+            "e2e": {"value": round(batch_total * args.steps / e2e_s, 2), "unit": "tokens/s", "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(float(tsum[1])) * args.steps,
         }

@@ -25,28 +25,37 @@ def main() -> int:
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     experts = os.environ.get("CUTEAFD_SELFTEST_EXPERTS", "nvfp4")
     spec = tiny_spec().replace(quant=QuantSpec(experts=experts, dense="bf16"))
-    g = torch.Generator().manual_seed(3)
-    prompts = [torch.randint(0, spec.vocab, (24,), generator=g).tolist() for _ in range(2)]
+    groups = int(os.environ.get("CUTEAFD_SELFTEST_GROUPS", "1"))
     n_new = 6
     ok = True
-    want = None
-    if rank == 0:
+    from ..config import default_deployment
+    dep = default_deployment(world, groups)
+    leaders = [dep.group_ranks(g)[0] for g in range(dep.attn_groups)]
+    want = prompts = None
+    if rank in leaders:
+        # every attention group serves its own prompts; its leader checks them against the single-GPU engine
+        g = torch.Generator().manual_seed(3 + dep.group_of(rank))
+        prompts = [torch.randint(0, spec.vocab, (24,), generator=g).tolist() for _ in range(2)]
         ref_eng = Engine(DeviceWeights.random(spec, "cuda", seed=1), n_pages=16, max_seqs=4, max_pages_per_seq=4)
         want = generate(ref_eng, prompts, n_new, use_graph=False)
         del ref_eng
-    for comm in ("p2p", "nccl"):
-        run = AfdRunner(spec, rank, world, local, t_max=64, n_pages=16, max_seqs=4, max_pages_per_seq=4, comm=comm, seed=1)
+    elif rank in dep.attn_ranks:
+        g = torch.Generator().manual_seed(3 + dep.group_of(rank))
+        prompts = [torch.randint(0, spec.vocab, (24,), generator=g).tolist() for _ in range(2)]
+    for comm in (("p2p", "nccl") if groups == 1 else ("p2p",)):
+        run = AfdRunner(spec, rank, world, local, t_max=64, n_pages=16, max_seqs=4, max_pages_per_seq=4, comm=comm, seed=1, attn_groups=groups)
         if run.is_attn:
             gen = BatchGenerator(run.engine, PagePool(16))
             out = [[t] for t in gen.prefill(prompts)]
             for _ in range(n_new - 1):
-                for o, t in zip(out, gen.decode_step(use_graph=(comm == "p2p"))):
+                for o, t in zip(out, gen.decode_step(use_graph=(comm == "p2p" and not os.environ.get("CUTEAFD_SELFTEST_EAGER")))):
                     o.append(t)
             run.control(OP_STOP)
             run.check()
-            if rank == 0:
+            if rank in leaders:
                 same = out == want
-                print(f"[selftest] comm={comm} experts={experts} world={world}: {'OK' if same else 'MISMATCH'} {out} vs {want}", flush=True)
+                print(f"[selftest] comm={comm} experts={experts} world={world} layout={dep.describe()} rank={rank}: "
+                      f"{'OK' if same else 'MISMATCH'} {out} vs {want}", flush=True)
                 ok = ok and same
         else:
             run.serve_loop()
