@@ -183,12 +183,20 @@ class Engine:
 
     # ------------------------------------------------------------------ kernels
     def _splits(self, N: int, K: int, T: int, tn: int, kind: int) -> int:
+        """Split-K factor of a dense layer.  Decode-sized token tiles (<= 32 rows) split over a thread-block cluster
+        (2, 4 or 8 CTAs reduce through distributed shared memory): the largest power of two that still fits one wave
+        and leaves every CTA at least two pipeline stages of K."""
         tiles = -(-N // 128) * -(-T // tn)
         nkb = K // (64 if kind == KIND_BF16 else 256)
         if tiles >= self.sm_count or nkb < 4:
             return 1
-        # measured on B200 (16-row decode tiles): the fix-up cost grows with the split count, the sweet spot is
-        # about one work unit per SM and never more than 8 splits
+        if tn <= 32:
+            for s in ((8, 4, 2) if tn == 16 else (4, 2)):
+                if tiles * s <= self.sm_count and nkb // s >= 2:
+                    return s
+            return 1
+        # larger token tiles: global-memory fix-up (measured on B200: its cost grows with the split count, the sweet
+        # spot is about one work unit per SM and never more than 8 splits)
         return max(1, min(nkb // 2, 8, self.sm_count // tiles))
 
     def _dense(self, w, x_act, y, T, residual=None, w_up=None):

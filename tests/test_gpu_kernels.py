@@ -105,6 +105,35 @@ def test_tc_linear_fp4_dense(kind, T, N, K):
 
 
 @pytest.mark.parametrize("kind", ["bf16", "nvfp4", "mxfp4"])
+@pytest.mark.parametrize("T,splits", [(5, 2), (16, 4), (16, 8), (30, 4), (9, 3)])
+def test_tc_linear_split_k_variants_match_unsplit(kind, T, splits):
+    """Cluster split-K (2/4/8-way, reduced through distributed shared memory; K slices longer than the stage ring
+    recycle stages) and the global-memory fix-up (3-way) against the unsplit kernel: same values up to the
+    summation order, bit-identical from run to run."""
+    N, K = 384, 4096
+    g = torch.Generator().manual_seed(T * 10 + splits)
+    w = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(T, K, generator=g)
+    W = TcWeight.from_master(w, kind, DEV)
+    tn = ops.pick_tn(T)
+    xb = x.to(torch.bfloat16).to(DEV).contiguous()
+    if W.kind == KIND_BF16:
+        xa = ActBuffer.wrap_bf16(xb, tn)
+    else:
+        xa = ActBuffer.alloc(W.kind, T, K, tn, DEV)
+        ops.quant_fp4_rows(xb, xa, inv_gs=W.inv_act_gs)
+    st = status_word()
+    y1, y2, y3 = (torch.zeros(T, N, dtype=torch.float32, device=DEV) for _ in range(3))
+    ops.tc_linear(W, xa, y1, status=st)
+    ops.tc_linear(W, xa, y2, splits=splits, status=st)
+    ops.tc_linear(W, xa, y3, splits=splits, status=st)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    assert rel_err(y2.cpu(), y1.cpu()) < 1e-5
+    assert torch.equal(y2, y3)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "nvfp4", "mxfp4"])
 def test_tc_linear_grouped_swiglu_and_down(kind):
     E, H, I, T, k = 8, 256, 256, 37, 2
     g = torch.Generator().manual_seed(3)
