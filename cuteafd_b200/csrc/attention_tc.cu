@@ -380,7 +380,11 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
 extern "C" int cuteafd_paged_attention_tc(const void* q, const void* kv_map, const int* page_table, const int* kv_len,
                                           const int* q_start, const int* q_len, const float* sink, void* out, float* part_o,
                                           float* part_ml, int T, int n_seq, int max_q_len, int q_stride, int Hq, int Hkv,
-                                          int max_pages, int n_splits, int window, float scale, int* status, cudaStream_t s) {
+                                          int max_pages, int n_splits, int window, float scale, int* status, void* q_out, void* sf_out,
+                                          int ldsf, const float* inv_gs, int qkind, cudaStream_t s) {
+  // q_out/sf_out (qkind 1 NVFP4 / 2 MXFP4): with split-KV the merge also writes the output rows quantised for the
+  // projection that follows; ignored (the caller quantises) when n_splits == 1.
+  CA_REQUIRE(qkind == 0 || (q_out && sf_out && (Hq * AD) % 256 == 0), "paged_attention_tc: FP4 output needs buffers and Hq*128 %% 256 == 0");
   CA_REQUIRE(Hq % Hkv == 0 && 128 % (Hq / Hkv) == 0, "paged_attention_tc: group size %d unsupported", Hq / Hkv);
   CA_REQUIRE(n_splits >= 1 && (n_splits == 1 || (part_o && part_ml)), "paged_attention_tc: split-KV needs scratch");
   CA_REQUIRE(q_stride % 8 == 0, "paged_attention_tc: q rows must be 16-byte aligned");
@@ -399,15 +403,14 @@ extern "C" int cuteafd_paged_attention_tc(const void* q, const void* kv_map, con
     if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(paged_attn_tc)");
     attr_set[dev & 63] = true;
   }
-  if (n_splits > 1) {
-    const long long n = (long long)n_splits * T * Hq * 2;
-    CA_LAUNCH_PDL(attn_fill_ml_kernel, (int)((n + 255) / 256), 256, 0, s, part_ml, n);
-  }
+  // No pre-fill of the (m, l) partials: every CTA writes them for all of its live rows, also when its split
+  // holds no key (m = -inf, l = 0), and a CTA that gives up reports through the status word.
   dim3 grid(n_splits, Hkv, n_seq * a.max_q_tiles);
   CA_LAUNCH_PDL(paged_attn_tc_kernel, grid, 192, smem, s, a);
   CA_CHECK_LAUNCH("paged_attention_tc");
   if (n_splits > 1) {
-    CA_LAUNCH_PDL(attn_merge_kernel, dim3(T, Hq), 128, 0, s, part_o, part_ml, sink, (bf16*)out, T, Hq, (int)AD, n_splits);
+    CA_LAUNCH_PDL(attn_merge8_kernel, dim3(T, (Hq * AD / 8 + 127) / 128), 128, 0, s, part_o, part_ml, sink, (bf16*)out, T, Hq, (int)AD, n_splits,
+                  (uint8_t*)q_out, (uint8_t*)sf_out, ldsf, inv_gs, qkind);
     CA_CHECK_LAUNCH("attn_merge");
   }
   return CA_OK;

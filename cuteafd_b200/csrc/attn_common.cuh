@@ -26,6 +26,43 @@ static __global__ void attn_merge_kernel(const float* __restrict__ part_o, const
   }
 }
 
+// Same merge, eight output elements per thread, optionally also writing the merged row quantised to FP4 for the
+// output projection that follows (qkind 1 NVFP4 / 2 MXFP4; needs Hq * D % 256 == 0).  grid (T, ceil(Hq * D / 8 / 128)).
+static __global__ void attn_merge8_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
+                                          bf16* __restrict__ out, int T, int Hq, int D, int n_splits, uint8_t* __restrict__ q,
+                                          uint8_t* __restrict__ sf, int ldsf, const float* __restrict__ inv_gs_ptr, int qkind) {
+  pdl_launch(); pdl_wait();
+  const int t = blockIdx.x, vi = blockIdx.y * blockDim.x + threadIdx.x, vpr = D / 8;
+  if (vi >= Hq * vpr) return;                     // whole warps leave together (Hq * D / 8 is a multiple of 32 with FP4 output)
+  const int h = vi / vpr, d0 = (vi % vpr) * 8;
+  float M = sink ? sink[h] : -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(((size_t)s * T + t) * Hq + h) * 2]);
+  float L = sink ? __expf(sink[h] - M) : 0.f;
+  float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < n_splits; ++s) {
+    const float* ml = part_ml + (((size_t)s * T + t) * Hq + h) * 2;
+    const float m = ml[0];
+    if (m == -INFINITY) continue;
+    const float e = __expf(m - M);
+    L += ml[1] * e;
+    const float4* po = (const float4*)(part_o + (((size_t)s * T + t) * Hq + h) * D + d0);
+    const float4 a = po[0], b = po[1];
+    o[0] += a.x * e; o[1] += a.y * e; o[2] += a.z * e; o[3] += a.w * e;
+    o[4] += b.x * e; o[5] += b.y * e; o[6] += b.z * e; o[7] += b.w * e;
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  bf16 ob[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ob[j] = __float2bfloat16(o[j] * inv);
+  *(uint4*)(out + ((size_t)t * Hq + h) * D + d0) = *(uint4*)ob;
+  if (qkind) {
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(ob[j]);
+    quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)t * (Hq * D / 2), sf + (size_t)t * ldsf, h * D + d0);
+  }
+}
+
 static __global__ void attn_fill_ml_kernel(float* ml, long long n) {
   pdl_launch(); pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;

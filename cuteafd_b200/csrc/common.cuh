@@ -132,6 +132,48 @@ __device__ __forceinline__ uint8_t ue8m0_ceil(float s) {
   return (uint8_t)min(e, 254u);
 }
 
+// FP4 block quantisation of 8 consecutive values held by this thread.  The block (16 values NVFP4, 32 values MXFP4)
+// spans 2 or 4 adjacent lanes, which must call this together (full warp converged).  Returns the 8 packed E2M1
+// codes; `sb` is the block's scale byte (E4M3 with the static global scale 1/inv_gs, or UE8M0).  Same arithmetic as
+// the stand-alone quantiser kernel, so fused and unfused paths produce identical bytes.
+template <bool MX>
+__device__ __forceinline__ uint32_t quant8_fp4(const float* v, float inv_gs, uint8_t& sb) {
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  float eff;
+  if (MX) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    int e = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xFF) - 2 : 0;   // OCP MX: floor(log2(amax)) - 2
+    e = max(e, 0); e = min(e, 254);
+    sb = (uint8_t)e;
+    eff = ue8m0_to_float(sb);
+  } else {
+    sb = float_to_e4m3(fminf(amax * inv_gs / 6.f, 448.f));
+    eff = e4m3_to_float(sb) / inv_gs;
+  }
+  const float inv = eff > 0.f ? 1.f / eff : 0.f;
+  uint32_t w = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) w |= float_to_e2m1(v[j] * inv) << (4 * j);
+  return w;
+}
+// Writes one thread's share of a quantised row: codes of elements [i, i+8) and, from the first lane of the block,
+// the scale byte.  qkind 1 = NVFP4, 2 = MXFP4.
+__device__ __forceinline__ void quant8_store(const float* v, int qkind, float inv_gs, uint8_t* q_row, uint8_t* sf_row, int i) {
+  uint8_t sb;
+  if (qkind == 2) {
+    const uint32_t w = quant8_fp4<true>(v, 1.f, sb);
+    *(uint32_t*)(q_row + i / 2) = w;
+    if (((i >> 3) & 3) == 0) sf_row[i >> 5] = sb;
+  } else {
+    const uint32_t w = quant8_fp4<false>(v, inv_gs, sb);
+    *(uint32_t*)(q_row + i / 2) = w;
+    if (((i >> 3) & 1) == 0) sf_row[i >> 4] = sb;
+  }
+}
+
 // ------------------------------------------------------------------ PTX: smem / mbarrier
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -30,9 +30,12 @@ extern "C" int cuteafd_embed_gather(const int* tokens, const void* table, void* 
 // ---------------------------------------------------------------- (add +) rmsnorm
 // x_out = x (+ delta)  [written back when delta != null];  y = rmsnorm(x_out) * w.
 // One block per row; the row is kept in registers between the two passes (H <= 8 * 1024 elements at 1024 threads).
+// Optional FP4 output (qkind 1 NVFP4 / 2 MXFP4): the normalised row is also written quantised (codes + block scales)
+// for the GEMM that follows, saving the separate quantiser launch; y may then be null.
 template <int VEC>
 __global__ void add_rmsnorm_kernel(bf16* __restrict__ x, const bf16* __restrict__ delta, const float* __restrict__ w,
-                                   bf16* __restrict__ y, int H, float eps) {
+                                   bf16* __restrict__ y, int H, float eps, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                   int ldsf, const float* __restrict__ inv_gs_ptr, int qkind) {
   pdl_launch(); pdl_wait();
   __shared__ float red[32];
   const size_t base = (size_t)blockIdx.x * H;
@@ -67,21 +70,42 @@ __global__ void add_rmsnorm_kernel(bf16* __restrict__ x, const bf16* __restrict_
       bf16 o[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16(v[k * 8 + j] * inv * w[i + j]);
-      *(uint4*)(y + base + i) = *(uint4*)o;
+      if (y) *(uint4*)(y + base + i) = *(uint4*)o;
+      if (qkind) {      // H is a multiple of 256 here, so whole warps take this branch together
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(o[j]);
+        quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)blockIdx.x * (H / 2), sf + (size_t)blockIdx.x * ldsf, i);
+      }
     }
   }
 }
 
+static int add_rmsnorm_launch(void* x, const void* delta, const float* w, void* y, int T, int H, float eps, void* q, void* sf, int ldsf,
+                              const float* inv_gs, int qkind, cudaStream_t s);
+
 extern "C" int cuteafd_add_rmsnorm(void* x, const void* delta, const float* w, void* y, int T, int H, float eps, cudaStream_t s) {
+  return add_rmsnorm_launch(x, delta, w, y, T, H, eps, nullptr, nullptr, 0, nullptr, 0, s);
+}
+
+// add_rmsnorm that also (or only, y == null) writes the row quantised to FP4: qkind 1 = NVFP4, 2 = MXFP4.
+extern "C" int cuteafd_add_rmsnorm_quant(void* x, const void* delta, const float* w, void* y, int T, int H, float eps, void* q, void* sf,
+                                         int ldsf, const float* inv_gs, int qkind, cudaStream_t s) {
+  CA_REQUIRE((qkind == 1 || qkind == 2) && q && sf && H % 256 == 0, "add_rmsnorm_quant: needs FP4 outputs and hidden %% 256 == 0");
+  return add_rmsnorm_launch(x, delta, w, y, T, H, eps, q, sf, ldsf, inv_gs, qkind, s);
+}
+
+static int add_rmsnorm_launch(void* x, const void* delta, const float* w, void* y, int T, int H, float eps, void* q, void* sf, int ldsf,
+                              const float* inv_gs, int qkind, cudaStream_t s) {
   CA_REQUIRE(H % 8 == 0 && H <= 32768, "add_rmsnorm: hidden %d unsupported", H);
   if (T <= 0) return CA_OK;
   const int vecs = H / 8;
   int threads = vecs >= 1024 ? 1024 : ((vecs + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   const int per = (vecs + threads - 1) / threads;
-  if (per == 1) CA_LAUNCH_PDL(add_rmsnorm_kernel<1>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
-  else if (per == 2) CA_LAUNCH_PDL(add_rmsnorm_kernel<2>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
-  else CA_LAUNCH_PDL(add_rmsnorm_kernel<4>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps);
+  if (per == 1) CA_LAUNCH_PDL(add_rmsnorm_kernel<1>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps, (uint8_t*)q, (uint8_t*)sf, ldsf, inv_gs, qkind);
+  else if (per == 2) CA_LAUNCH_PDL(add_rmsnorm_kernel<2>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps, (uint8_t*)q, (uint8_t*)sf, ldsf, inv_gs, qkind);
+  else CA_LAUNCH_PDL(add_rmsnorm_kernel<4>, T, threads, 0, s, (bf16*)x, (const bf16*)delta, w, (bf16*)y, H, eps, (uint8_t*)q, (uint8_t*)sf, ldsf, inv_gs, qkind);
   CA_CHECK_LAUNCH("add_rmsnorm");
   return CA_OK;
 }

@@ -7,14 +7,79 @@
 
 enum { SCORE_SIGMOID = 0, SCORE_SOFTMAX = 1, SCORE_SQRTSOFTPLUS = 2 };
 
+// ---------------------------------------------------------------- route packing
+// Inputs: idx [T, k] (expert ids; ids outside [e_lo, e_hi) are skipped - they belong to another expert rank).
+// Outputs: src_token [cap]  (token of each packed row, expert-major), slot_row [T, k] (packed row of each
+// route, -1 when skipped), counts/offsets per local expert, a tile table {local expert, first row, rows, 0}
+// with at most `tn` rows per entry, n_tiles and n_rows.  Runs in ONE block (any size); T*k up to ~64K routes.
+struct RoutePack {
+  const int* idx; int* src_token; int* slot_row; int* counts; int* offsets; int4* tiles; int* n_tiles; int* n_rows; int* src_route;
+  int T, k, e_lo, e_hi, tn, max_tiles;
+  int* ticket;      // fused with the router: arrival counter of the select blocks (zero on entry, left zero)
+};
+
+__device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
+  // sh: [E_local] counts, [E_local] offsets/cursors, [T*k] staged ids (small batches)
+  const int El = p.e_hi - p.e_lo;
+  int* cnt = sh; int* cur = sh + El;
+  for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  const int n = p.T * p.k;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = __ldcg(p.idx + i) - p.e_lo; if (e >= 0 && e < El) atomicAdd(&cnt[e], 1); }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, nt = 0;
+    for (int e = 0; e < El; ++e) {
+      cur[e] = off; p.offsets[e] = off; p.counts[e] = cnt[e];
+      for (int r = 0; r < cnt[e]; r += p.tn) { if (nt < p.max_tiles) p.tiles[nt] = make_int4(e, off + r, min(p.tn, cnt[e] - r), 0); ++nt; }
+      off += cnt[e];
+    }
+    *p.n_tiles = min(nt, p.max_tiles); *p.n_rows = off;
+  }
+  __syncthreads();
+  // Stable placement (token order inside each expert) so packed layouts are reproducible: each route counts the
+  // earlier routes to its expert when T*k is small; larger batches use atomics (row order inside an expert does
+  // not change any result: rows are independent in the GEMM and the combine reads them by index).
+  if (n <= 4096) {
+    int* sid = cur + El;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = __ldcg(p.idx + i) - p.e_lo;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int e = sid[i];
+      if (e < 0 || e >= El) { p.slot_row[i] = -1; continue; }
+      int rank = 0;
+      for (int j = 0; j < i; ++j) rank += (sid[j] == e);
+      const int c = cur[e] + rank;
+      p.src_token[c] = i / p.k; p.slot_row[i] = c;
+      if (p.src_route) p.src_route[c] = i;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const int e = __ldcg(p.idx + i) - p.e_lo;
+      if (e >= 0 && e < El) { const int c = atomicAdd(&cur[e], 1); p.src_token[c] = i / p.k; p.slot_row[i] = c; if (p.src_route) p.src_route[c] = i; } else p.slot_row[i] = -1;
+    }
+  }
+}
+
+__global__ void route_pack_kernel(const RoutePack p) {
+  pdl_launch(); pdl_wait();
+  extern __shared__ int sh[];
+  route_pack_body(p, sh);
+}
+
+static size_t route_pack_smem(int T, int k, int e_lo, int e_hi) { return (size_t)(2 * (e_hi - e_lo) + (T * k <= 4096 ? T * k : 0)) * sizeof(int); }
+
+
 // One block per token.  logits fp32 [T, E] (E <= 512).  Selection uses score + bias (bias may be null),
 // optional group-limited routing (top `topk_group` of `n_group` groups ranked by the sum of their two
 // best biased scores); gate weights come from the unbiased scores, normalised over the chosen k and
 // multiplied by route_scale.  Ties resolve to the lowest expert id.
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx,
                                      float* __restrict__ wts, int E, int k, int scoring, int normalize, float route_scale,
-                                     int n_group, int topk_group) {
+                                     int n_group, int topk_group, const RoutePack pack) {
   pdl_launch(); pdl_wait();
+  extern __shared__ int pack_sh[];
+  __shared__ int is_last;
   __shared__ float score[512], choice[512], red[32];
   __shared__ float gscore[32];
   __shared__ int sel[16];
@@ -88,6 +153,19 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     const float inv = normalize ? 1.f / fmaxf(s, 1e-12f) : 1.f;
     for (int r = 0; r < k; ++r) { idx[(size_t)t * k + r] = sel[r]; wts[(size_t)t * k + r] = selw[r] * inv * route_scale; }
   }
+  if (pack.ticket) {
+    // the block that finishes last sees every token's routes and packs them (one launch instead of two)
+    if (tid == 0) {
+      __threadfence();
+      is_last = (atomicAdd(pack.ticket, 1) == (int)gridDim.x - 1);
+      __threadfence();
+    }
+    __syncthreads();
+    if (is_last) {
+      route_pack_body(pack, pack_sh);
+      if (tid == 0) *pack.ticket = 0;
+    }
+  }
 }
 
 extern "C" int cuteafd_router_select(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k,
@@ -96,71 +174,34 @@ extern "C" int cuteafd_router_select(const float* logits, const float* bias, int
   CA_REQUIRE(n_group >= 1 && n_group <= 32 && E % n_group == 0, "router_select: bad group count");
   if (T <= 0) return CA_OK;
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
-  CA_LAUNCH_PDL(router_select_kernel, T, threads, 0, s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale, n_group, topk_group);
-  CA_CHECK_LAUNCH("router_select");
+  RoutePack none{};
+  CA_LAUNCH_PDL(router_select_kernel, T, threads, 0, s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale, n_group, topk_group, none);
   return CA_OK;
-}
-
-// ---------------------------------------------------------------- route packing
-// Inputs: idx [T, k] (expert ids; ids outside [e_lo, e_hi) are skipped - they belong to another expert rank).
-// Outputs: src_token [cap]  (token of each packed row, expert-major), slot_row [T, k] (packed row of each
-// route, -1 when skipped), counts/offsets per local expert, a tile table {local expert, first row, rows, 0}
-// with at most `tn` rows per entry, n_tiles and n_rows.  Single block; T*k up to ~64K routes.
-__global__ void route_pack_kernel(const int* __restrict__ idx, int* __restrict__ src_token, int* __restrict__ slot_row,
-                                  int* __restrict__ counts, int* __restrict__ offsets, int4* __restrict__ tiles,
-                                  int* __restrict__ n_tiles, int* __restrict__ n_rows, int T, int k, int e_lo, int e_hi, int tn,
-                                  int max_tiles, int* __restrict__ src_route) {
-  pdl_launch(); pdl_wait();
-  extern __shared__ int sh[];   // [E_local] counts, [E_local] offsets/cursors
-  const int El = e_hi - e_lo;
-  int* cnt = sh; int* cur = sh + El;
-  for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
-  __syncthreads();
-  const int n = T * k;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = idx[i] - e_lo; if (e >= 0 && e < El) atomicAdd(&cnt[e], 1); }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int off = 0, nt = 0;
-    for (int e = 0; e < El; ++e) {
-      cur[e] = off; offsets[e] = off; counts[e] = cnt[e];
-      for (int r = 0; r < cnt[e]; r += tn) { if (nt < max_tiles) tiles[nt] = make_int4(e, off + r, min(tn, cnt[e] - r), 0); ++nt; }
-      off += cnt[e];
-    }
-    *n_tiles = min(nt, max_tiles); *n_rows = off;
-  }
-  __syncthreads();
-  // Stable placement (token order inside each expert) so packed layouts are reproducible: one thread per expert
-  // walks the routes in order when T*k is small; larger batches use atomics (row order inside an expert does
-  // not change any result: rows are independent in the GEMM and the combine reads them by index).
-  if (n <= 4096) {
-    // rank of route i inside its expert = number of earlier routes to the same expert (ids staged in shared memory)
-    int* sid = cur + El;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = idx[i] - e_lo;
-    __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const int e = sid[i];
-      if (e < 0 || e >= El) { slot_row[i] = -1; continue; }
-      int rank = 0;
-      for (int j = 0; j < i; ++j) rank += (sid[j] == e);
-      const int c = cur[e] + rank;
-      src_token[c] = i / k; slot_row[i] = c;
-      if (src_route) src_route[c] = i;
-    }
-  } else {
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const int e = idx[i] - e_lo;
-      if (e >= 0 && e < El) { const int c = atomicAdd(&cur[e], 1); src_token[c] = i / k; slot_row[i] = c; if (src_route) src_route[c] = i; } else slot_row[i] = -1;
-    }
-  }
 }
 
 extern "C" int cuteafd_route_pack(const int* idx, int* src_token, int* slot_row, int* counts, int* offsets, void* tiles,
                                   int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, int* src_route, cudaStream_t s) {
   CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 4096, "route_pack: bad expert range");
   CA_REQUIRE(tn >= 1, "route_pack: bad tile rows");
-  CA_LAUNCH_PDL(route_pack_kernel, 1, 1024, (2 * (e_hi - e_lo) + (T * k <= 4096 ? T * k : 0)) * sizeof(int), s, idx, src_token, slot_row, counts, offsets, (int4*)tiles,
-                                                                    n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route);
-  CA_CHECK_LAUNCH("route_pack");
+  RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, nullptr};
+  CA_LAUNCH_PDL(route_pack_kernel, 1, 1024, route_pack_smem(T, k, e_lo, e_hi), s, p);
+  return CA_OK;
+}
+
+// Router selection and route packing in one launch: the select block that finishes last packs the routes.
+extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k,
+                                          int scoring, int normalize, float route_scale, int n_group, int topk_group,
+                                          int* src_token, int* slot_row, int* counts, int* offsets, void* tiles, int* n_tiles,
+                                          int* n_rows, int e_lo, int e_hi, int tn, int max_tiles, int* src_route, int* ticket,
+                                          cudaStream_t s) {
+  CA_REQUIRE(E >= k && E <= 512 && k >= 1 && k <= 16, "router_select: need k <= 16 and E <= 512 (E=%d k=%d)", E, k);
+  CA_REQUIRE(n_group >= 1 && n_group <= 32 && E % n_group == 0, "router_select: bad group count");
+  CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 512 && tn >= 1 && ticket, "router_select_pack: bad pack arguments");
+  if (T <= 0) return CA_OK;
+  const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
+  RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, ticket};
+  CA_LAUNCH_PDL(router_select_kernel, T, threads, route_pack_smem(T, k, e_lo, e_hi), s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale,
+                n_group, topk_group, p);
   return CA_OK;
 }
 
@@ -172,7 +213,7 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __rest
                                    int H, int k) {
   pdl_launch(); pdl_wait();
   const int t = blockIdx.x;
-  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8; i < H; i += gridDim.y * blockDim.x * 8) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -198,12 +239,92 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __rest
   }
 }
 
+// Combine fused with the NEXT layer's input norm: one block per token holds the whole row in registers, writes
+// the new residual stream `out`, then rmsnorm(out) * norm_w as bf16 (`xn`, optional) and/or quantised to FP4
+// (`q`/`sf`, optional) - three launches (combine, norm, quantise) in one for decode-sized steps.
+template <int VEC>
+__global__ void moe_combine_norm_kernel(const bf16* __restrict__ y, const int* __restrict__ slot_row, const float* __restrict__ wts,
+                                        const bf16* __restrict__ shared, const bf16* __restrict__ residual, bf16* __restrict__ out,
+                                        int H, int k, const float* __restrict__ norm_w, float eps, bf16* __restrict__ xn,
+                                        uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int ldsf,
+                                        const float* __restrict__ inv_gs_ptr, int qkind) {
+  pdl_launch(); pdl_wait();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  float v[VEC * 8];
+  float ss = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < VEC; ++kk) {
+    const int i = (threadIdx.x + kk * blockDim.x) * 8;
+    if (i < H) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int sl = 0; sl < k; ++sl) {
+        const int r = slot_row[(size_t)t * k + sl];
+        if (r < 0) continue;
+        const float w = wts[(size_t)t * k + sl];
+        uint4 qv = *(const uint4*)(y + (size_t)r * H + i);
+        const bf16* e = (const bf16*)&qv;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += w * __bfloat162float(e[j]);
+      }
+      if (shared) { uint4 qv = *(const uint4*)(shared + (size_t)t * H + i); const bf16* e = (const bf16*)&qv;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(e[j]); }
+      if (residual) { uint4 qv = *(const uint4*)(residual + (size_t)t * H + i); const bf16* e = (const bf16*)&qv;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(e[j]); }
+      bf16 o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { o[j] = __float2bfloat16(acc[j]); v[kk * 8 + j] = __bfloat162float(o[j]); ss += v[kk * 8 + j] * v[kk * 8 + j]; }
+      *(uint4*)(out + (size_t)t * H + i) = *(uint4*)o;
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / H + eps);
+#pragma unroll
+  for (int kk = 0; kk < VEC; ++kk) {
+    const int i = (threadIdx.x + kk * blockDim.x) * 8;
+    if (i < H) {
+      bf16 o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16(v[kk * 8 + j] * inv * norm_w[i + j]);
+      if (xn) *(uint4*)(xn + (size_t)t * H + i) = *(uint4*)o;
+      if (qkind) {
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(o[j]);
+        quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)t * (H / 2), sf + (size_t)t * ldsf, i);
+      }
+    }
+  }
+}
+
+extern "C" int cuteafd_moe_combine_norm(const void* y, const int* slot_row, const float* wts, const void* shared, const void* residual,
+                                        void* out, int T, int H, int k, const float* norm_w, float eps, void* xn, void* q, void* sf,
+                                        int ldsf, const float* inv_gs, int qkind, cudaStream_t s) {
+  CA_REQUIRE(H % 8 == 0 && H <= 32768 && norm_w, "moe_combine_norm: bad arguments");
+  CA_REQUIRE(qkind == 0 || ((qkind == 1 || qkind == 2) && q && sf && H % 256 == 0), "moe_combine_norm: FP4 output needs buffers and hidden %% 256 == 0");
+  if (T <= 0) return CA_OK;
+  const int vecs = H / 8;
+  int threads = vecs >= 1024 ? 1024 : ((vecs + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  const int per = (vecs + threads - 1) / threads;
+#define CA_CN(V) CA_LAUNCH_PDL(moe_combine_norm_kernel<V>, T, threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, \
+                               (bf16*)out, H, k, norm_w, eps, (bf16*)xn, (uint8_t*)q, (uint8_t*)sf, ldsf, inv_gs, qkind)
+  if (per == 1) CA_CN(1); else if (per == 2) CA_CN(2); else CA_CN(4);
+#undef CA_CN
+  return CA_OK;
+}
+
 extern "C" int cuteafd_moe_combine(const void* y, const int* slot_row, const float* wts, const void* shared, const void* residual,
                                    void* out, int T, int H, int k, cudaStream_t s) {
   CA_REQUIRE(H % 8 == 0, "moe_combine: hidden must be a multiple of 8");
   if (T <= 0) return CA_OK;
   const int threads = H / 8 >= 256 ? 256 : (H / 8 >= 128 ? 128 : 64);
-  CA_LAUNCH_PDL(moe_combine_kernel, T, threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, (bf16*)out, H, k);
+  // few tokens: split the row over several blocks so more SMs pull the k routed rows
+  const int ysplit = T >= 64 ? 1 : (H / 8 + threads - 1) / threads;
+  CA_LAUNCH_PDL(moe_combine_kernel, dim3(T, ysplit), threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, (bf16*)out, H, k);
   CA_CHECK_LAUNCH("moe_combine");
   return CA_OK;
 }

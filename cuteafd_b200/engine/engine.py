@@ -211,27 +211,56 @@ class Engine:
         self.launches_per_step += 1
         return act
 
+    def _attn_in_gs(self, lw: LayerWeights):
+        """Activation global scale of the first projection of the attention block (NVFP4)."""
+        return lw.wqkv.inv_act_gs
+
+    def _norm_in(self, lw: LayerWeights, L: Lane, T: int) -> ActBuffer:
+        """Input of the attention block: RMSNorm of the residual stream as the GEMM operand (bf16 or FP4, quantised in
+        the same launch) - unless the previous layer's combine already produced it."""
+        if self._pre_normed:
+            self._pre_normed = False
+            return L.xq
+        if L.xq.kind == KIND_BF16:
+            ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, self.spec.rms_eps, rows=T)
+        else:
+            ops.add_rmsnorm(L.x, None, lw.attn_norm, None, self.spec.rms_eps, rows=T, quant=L.xq, inv_gs=self._attn_in_gs(lw))
+        self.launches_per_step += 1
+        return L.xq
+
+    def _combine(self, y, rows, wts, shared, L: Lane, T: int, k: int):
+        """Weighted top-k sum + shared expert + residual; when another layer follows, its input norm (and FP4
+        quantisation) rides in the same launch."""
+        nxt = self._next_lw
+        if nxt is None:
+            ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k)
+            return
+        fp4 = L.xq.kind != KIND_BF16
+        ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, norm_w=nxt.attn_norm, eps=self.spec.rms_eps, xn=None if fp4 else L.xn,
+                        quant=L.xq if fp4 else None, inv_gs=self._attn_in_gs(nxt) if fp4 else None)
+        self._pre_normed = True
+
     def _attention_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
         spec, a, T = self.spec, self.spec.attn, sh.T
         md = self.md
-        ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, spec.rms_eps, rows=T)
-        xq = self._quant(L.xn, L.xq, T, lw.wqkv.inv_act_gs)
+        xq = self._norm_in(lw, L, T)
         self._dense(lw.wqkv, xq, L.qkv, T)
         ops.qk_norm_rope_kvwrite(L.qkv, md["positions"], md["slot_map"], lw.q_norm, lw.k_norm, self.kv[li], T,
                                  a.n_heads, a.n_kv_heads, a.head_dim, a.rope_theta, a.rope_interleaved, spec.rms_eps, self.status)
+        fused_q = False
         if self.kv_tmaps is not None:
-            ops.paged_attention_tc(L.qkv, self.kv_tmaps[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
-                                   T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
-                                   Hkv=a.n_kv_heads, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
-                                   window=a.window, sink=lw.sink, status=self.status)
+            fused_q = ops.paged_attention_tc(L.qkv, self.kv_tmaps[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
+                                             T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
+                                             Hkv=a.n_kv_heads, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
+                                             window=a.window, sink=lw.sink, status=self.status, quant=L.attn_q, inv_gs=lw.wo.inv_act_gs)
         else:
             ops.paged_attention(L.qkv, self.kv[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
                                 T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
                                 Hkv=a.n_kv_heads, D=a.head_dim, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
                                 window=a.window, sink=lw.sink)
-        oq = self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
+        oq = L.attn_q if fused_q else self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
         self._attn_out(li, lw, oq, L, T)
-        self.launches_per_step += 3 + (2 if sh.attn_splits > 1 else 0)
+        self.launches_per_step += 2 + (1 if sh.attn_splits > 1 else 0)
 
     def _attn_out(self, li: int, lw: LayerWeights, oq: ActBuffer, L: Lane, T: int):
         """Output projection + residual (a tensor-parallel rank overrides this with partial sum + exchange)."""
@@ -253,11 +282,17 @@ class Engine:
             self._ffn(lw, L, T, L.x, L.x)
             return
         self._dense(lw.router, L.xn_act, L.router_logits, T)
-        ops.router_select(L.router_logits, lw.router_bias, L.idx, L.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
-                          m.n_group, m.topk_group)
         e_lo, e_hi = self.expert_range
-        ops.route_pack(L.idx, L.src_token, L.slot_row, L.counts, L.offsets, L.tiles, L.n_tiles, L.n_rows, T, m.top_k,
-                       e_lo, e_hi, L.tn_g, L.max_tiles)
+        if T * m.top_k <= 1024 and e_hi - e_lo <= 512:     # decode / verify steps: select and pack in one launch
+            ops.router_select_pack(L.router_logits, lw.router_bias, L.idx, L.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                                   m.n_group, m.topk_group, L.src_token, L.slot_row, L.counts, L.offsets, L.tiles, L.n_tiles, L.n_rows,
+                                   e_lo, e_hi, L.tn_g, L.max_tiles)
+            self.launches_per_step -= 1
+        else:
+            ops.router_select(L.router_logits, lw.router_bias, L.idx, L.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                              m.n_group, m.topk_group)
+            ops.route_pack(L.idx, L.src_token, L.slot_row, L.counts, L.offsets, L.tiles, L.n_tiles, L.n_rows, T, m.top_k,
+                           e_lo, e_hi, L.tn_g, L.max_tiles)
         rows = T * m.top_k
         if L.xs.kind == KIND_BF16:
             ops.gather_rows(L.xn, L.src_token, L.n_rows, L.xs.data, rows)
@@ -273,7 +308,7 @@ class Engine:
         if lw.ws_gate is not None:
             self._ffn(lw, L, T, L.shared, None)
             shared = L.shared
-        ops.moe_combine(L.y2, L.slot_row, L.wts, shared, L.x, L.x, T, m.top_k)
+        self._combine(L.y2, L.slot_row, L.wts, shared, L, T, m.top_k)
         self.launches_per_step += 6
 
     def forward(self, sh: StepShape):
@@ -289,10 +324,12 @@ class Engine:
         elif getattr(self, "part_o", None) is None:
             self.part_o = self.part_ml = None
         self.launches_per_step = 0
+        self._pre_normed = False
         ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
         self.launches_per_step += 1
         for li in range(spec.n_layers):
             lw = self.weights.layer(li)
+            self._next_lw = self.weights.layer(li + 1) if li + 1 < spec.n_layers else None
             self._attention_layer(li, lw, L, sh)
             self._moe_layer(lw, L, T)
         if sh.n_logits:

@@ -168,8 +168,7 @@ class MlaEngine(Engine):
         spec, a, T, md, w = self.spec, self.spec.attn, sh.T, self.md, lw.mla
         Hl = self.heads_local
         b = self._mla_buf(L)
-        ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, spec.rms_eps, rows=T)
-        xq = self._quant(L.xn, L.xq, T, w.wkv_a.inv_act_gs)
+        xq = self._norm_in(lw, L, T)
         if w.wq_a is not None:
             self._dense(w.wq_a, xq, b["q_a"], T)
             ops.add_rmsnorm(b["q_a"], None, w.q_a_norm, b["q_an"], spec.rms_eps, rows=T)
@@ -204,10 +203,10 @@ class MlaEngine(Engine):
         call("cuteafd_head_to_token_major", ptr(o_head), ptr(b["o_tok"]), T, Hl, a.v_head_dim, stream())
         oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
         self._attn_out(li, lw, oq, L, T)
-        self.launches_per_step += 8
+        self.launches_per_step += 7
 
-    def _attn_out(self, li, lw, oq, L, T):
-        self._dense(lw.wo, oq, L.x, T, residual=L.x)
+    def _attn_in_gs(self, lw):
+        return lw.mla.wkv_a.inv_act_gs
 
     def _act(self, b, key, tensor, tn):
         """bf16 activation operand over a view of a head-major buffer (descriptor cached per shape)."""

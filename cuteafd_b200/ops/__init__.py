@@ -230,10 +230,17 @@ def embed_gather(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, s
     return out
 
 
-def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, y: torch.Tensor, eps: float, rows: int | None = None):
-    """x += delta (if given, in place); y = rmsnorm(x) * w."""
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, y: torch.Tensor | None, eps: float, rows: int | None = None,
+                quant: "ActBuffer | None" = None, inv_gs: torch.Tensor | None = None):
+    """x += delta (if given, in place); y = rmsnorm(x) * w.  With `quant` (an FP4 activation buffer) the normalised
+    rows are also written quantised in the same launch (y may then be None)."""
     _chk(x, torch.bfloat16, "x"); _chk(w, torch.float32, "w")
-    call("cuteafd_add_rmsnorm", ptr(x), ptr(delta), ptr(w), ptr(y), x.shape[0] if rows is None else rows, x.shape[1], eps, stream())
+    n = x.shape[0] if rows is None else rows
+    if quant is not None and quant.kind != KIND_BF16:
+        call("cuteafd_add_rmsnorm_quant", ptr(x), ptr(delta), ptr(w), ptr(y), n, x.shape[1], eps, ptr(quant.data), ptr(quant.sf),
+             quant.sf.shape[1], ptr(inv_gs), 2 if quant.kind == KIND_MXFP4 else 1, stream())
+    else:
+        call("cuteafd_add_rmsnorm", ptr(x), ptr(delta), ptr(w), ptr(y), n, x.shape[1], eps, stream())
     return y
 
 
@@ -272,13 +279,36 @@ def router_select(logits, bias, idx, wts, T, k, scoring, normalize, route_scale,
          1 if normalize else 0, route_scale, n_group, topk_group, stream())
 
 
+_TICKETS: dict = {}
+
+
+def router_select_pack(logits, bias, idx, wts, T, k, scoring, normalize, route_scale, n_group, topk_group,
+                       src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, e_lo, e_hi, tn, max_tiles, src_route=None):
+    """`router_select` followed by `route_pack` in one launch (the select block that finishes last packs)."""
+    _chk(logits, torch.float32, "logits")
+    dev = logits.device
+    if dev not in _TICKETS:
+        _TICKETS[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    call("cuteafd_router_select_pack", ptr(logits), ptr(bias), ptr(idx), ptr(wts), T, logits.shape[1], k, SCORING[scoring],
+         1 if normalize else 0, route_scale, n_group, topk_group, ptr(src_token), ptr(slot_row), ptr(counts), ptr(offsets),
+         ptr(tiles), ptr(n_tiles), ptr(n_rows), e_lo, e_hi, tn, max_tiles, ptr(src_route), ptr(_TICKETS[dev]), stream())
+
+
 def route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route=None):
     call("cuteafd_route_pack", ptr(idx), ptr(src_token), ptr(slot_row), ptr(counts), ptr(offsets), ptr(tiles), ptr(n_tiles),
          ptr(n_rows), T, k, e_lo, e_hi, tn, max_tiles, ptr(src_route), stream())
 
 
-def moe_combine(y, slot_row, wts, shared, residual, out, T, k):
-    call("cuteafd_moe_combine", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, stream())
+def moe_combine(y, slot_row, wts, shared, residual, out, T, k, *, norm_w=None, eps: float = 0.0, xn=None, quant=None, inv_gs=None):
+    """out = residual + shared + sum_slot w * y[slot_row].  With `norm_w` the same launch also applies the next
+    layer's RMSNorm to `out`, written as bf16 (`xn`) and/or FP4 (`quant`, an activation buffer)."""
+    if norm_w is None:
+        call("cuteafd_moe_combine", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, stream())
+        return out
+    fp4 = quant is not None and quant.kind != KIND_BF16
+    call("cuteafd_moe_combine_norm", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, ptr(norm_w),
+         eps, ptr(xn), ptr(quant.data) if fp4 else None, ptr(quant.sf) if fp4 else None, quant.sf.shape[1] if fp4 else 0,
+         ptr(inv_gs) if fp4 else None, (2 if quant.kind == KIND_MXFP4 else 1) if fp4 else 0, stream())
     return out
 
 
@@ -304,12 +334,17 @@ def encode_kv_tmaps(kv: torch.Tensor) -> torch.Tensor:
 
 
 def paged_attention_tc(q, kv_map, page_table, kv_len, q_start, q_len, out, *, T, n_seq, max_q_len, q_stride, Hq, Hkv,
-                       n_splits=1, part_o=None, part_ml=None, window=0, sink=None, scale=None, status=None):
-    """Tensor-core (tcgen05) paged attention for head_dim 128; `kv_map` is one row of `encode_kv_tmaps`."""
+                       n_splits=1, part_o=None, part_ml=None, window=0, sink=None, scale=None, status=None, quant=None, inv_gs=None) -> bool:
+    """Tensor-core (tcgen05) paged attention for head_dim 128; `kv_map` is one row of `encode_kv_tmaps`.
+    `quant` (an FP4 activation buffer): with split-KV the merge also writes the output rows quantised for the output
+    projection.  Returns True when that happened (False: the caller quantises `out` itself)."""
+    fused = quant is not None and quant.kind != KIND_BF16 and n_splits > 1 and (Hq * 128) % 256 == 0
     call("cuteafd_paged_attention_tc", ptr(q), ptr(kv_map), ptr(page_table), ptr(kv_len), ptr(q_start), ptr(q_len), ptr(sink),
          ptr(out), ptr(part_o), ptr(part_ml), T, n_seq, max_q_len, q_stride, Hq, Hkv, page_table.shape[1], n_splits, window,
-         float(scale if scale is not None else 128 ** -0.5), ptr(status), stream())
-    return out
+         float(scale if scale is not None else 128 ** -0.5), ptr(status), ptr(quant.data) if fused else None,
+         ptr(quant.sf) if fused else None, quant.sf.shape[1] if fused else 0, ptr(inv_gs) if fused else None,
+         (2 if quant.kind == KIND_MXFP4 else 1) if fused else 0, stream())
+    return fused
 
 
 # ------------------------------------------------------------------ sampling

@@ -31,10 +31,13 @@ _PROTOS = {
     "cuteafd_act_quant_fp8_ue8m0": [P, P, P, I, I, P],
     "cuteafd_silu_mul": [P, P, P, L, F, P],
     "cuteafd_router_select": [P, P, P, P, I, I, I, I, I, F, I, I, P],
+    "cuteafd_add_rmsnorm_quant": [P, P, P, P, I, I, F, P, P, I, P, I, P],
+    "cuteafd_moe_combine_norm": [P, P, P, P, P, P, I, I, I, P, F, P, P, P, I, P, I, P],
+    "cuteafd_router_select_pack": [P, P, P, P, I, I, I, I, I, F, I, I, P, P, P, P, P, P, P, I, I, I, I, P, P, P],
     "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "cuteafd_moe_combine": [P, P, P, P, P, P, I, I, I, P],
     "cuteafd_paged_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
-    "cuteafd_paged_attention_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P],
+    "cuteafd_paged_attention_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P, P, I, P, I, P],
     "cuteafd_tmap_encode_kv": [P, P, I, U64],
     "cuteafd_mla_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P],
     "cuteafd_tmap_encode_latent": [P, P, U64],

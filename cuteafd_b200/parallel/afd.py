@@ -156,14 +156,21 @@ class AttnRankEngine(Engine):
         spec, m, dep = self.full_spec, self.full_spec.moe, self.dep
         ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, spec.rms_eps, rows=T)
         self._dense(lw.router, L.xn_act, self.router_logits, T)
-        ops.router_select(self.router_logits, lw.router_bias, self.idx, self.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
-                          m.n_group, m.topk_group)
         self.launches_per_step += 2
         shared = None
         if self.comm == "nccl":
+            ops.router_select(self.router_logits, lw.router_bias, self.idx, self.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                              m.n_group, m.topk_group)
             return self._moe_nccl(li, lw, L, T)
-        ops.route_pack(self.idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
-                       T, m.top_k, 0, m.n_experts, 1 << 20, self.tiles.shape[0])
+        if T * m.top_k <= 1024 and m.n_experts <= 512:
+            ops.router_select_pack(self.router_logits, lw.router_bias, self.idx, self.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                                   m.n_group, m.topk_group, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles,
+                                   self.n_tiles, self.n_rows, 0, m.n_experts, 1 << 20, self.tiles.shape[0])
+        else:
+            ops.router_select(self.router_logits, lw.router_bias, self.idx, self.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                              m.n_group, m.topk_group)
+            ops.route_pack(self.idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
+                           T, m.top_k, 0, m.n_experts, 1 << 20, self.tiles.shape[0])
         # my share of the tokens (the other attention rank sends the rest; both hold identical activations)
         per = -(-T // self.tp)
         t0, t1 = min(T, self.tp_rank * per), min(T, (self.tp_rank + 1) * per)
@@ -176,7 +183,7 @@ class AttnRankEngine(Engine):
             self._ffn(lw, L, T, L.shared, None)
             shared = L.shared
         peer_ops.wait_flags(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_COMBINE, li, 0)), dep.ep, 1, self.ctl, 0, self.status)
-        ops.moe_combine(self.y_recv, self.identity_rows, self.wts, shared, L.x, L.x, T, m.top_k)
+        self._combine(self.y_recv, self.identity_rows, self.wts, shared, L, T, m.top_k)
         self.launches_per_step += 4
 
     def _moe_nccl(self, li, lw, L, T):
@@ -221,7 +228,7 @@ class MlaAttnRankEngine(AttnRankEngine):
 def _bind_mla(cls):
     """MLA attention methods come from MlaEngine; everything else (TP exchange, remote experts) from AttnRankEngine."""
     from ..engine.mla import MlaEngine
-    for name in ("_alloc_attention_state", "_mla_buf", "_head_tiles", "attn_splits_for", "_attention_layer", "_act"):
+    for name in ("_alloc_attention_state", "_mla_buf", "_head_tiles", "attn_splits_for", "_attention_layer", "_act", "_attn_in_gs"):
         setattr(cls, name, getattr(MlaEngine, name))
     return cls
 

@@ -379,6 +379,22 @@ def test_paged_attention_tc(Hq, Hkv, window, use_sink, splits):
         ref = rops.attention(bf16r(q[qs:qs + ql]), bf16r(ks[i]), bf16r(vs[i]), torch.arange(L - ql, L), torch.arange(L),
                              window=window, sink=sink)
         assert torch.allclose(got[qs:qs + ql], ref, atol=3e-2, rtol=3e-2), f"seq {i}: max err {(got[qs:qs + ql] - ref).abs().max()}"
+    if splits > 1:
+        # the merge can also emit the rows quantised for the output projection: same bytes as the stand-alone quantiser
+        inv_gs = torch.tensor([64.0], device=DEV)
+        for kind in (KIND_NVFP4, KIND_MXFP4):
+            fused, sep = ActBuffer.alloc(kind, T, Hq * D, 16, DEV), ActBuffer.alloc(kind, T, Hq * D, 16, DEV)
+            out2 = torch.zeros_like(out)
+            did = ops.paged_attention_tc(q.to(torch.bfloat16).to(DEV).view(T, -1).contiguous(), maps[0], pt.to(DEV),
+                                         torch.tensor(lens, dtype=torch.int32, device=DEV), q_start.to(DEV),
+                                         torch.tensor(qlens, dtype=torch.int32, device=DEV), out2, T=T, n_seq=len(lens), max_q_len=max(qlens),
+                                         q_stride=Hq * D, Hq=Hq, Hkv=Hkv, n_splits=splits, part_o=part_o, part_ml=part_ml, window=window,
+                                         sink=sink.to(DEV) if use_sink else None, status=st, quant=fused, inv_gs=inv_gs)
+            ops.quant_fp4_rows(out2, sep, inv_gs=inv_gs)
+            torch.cuda.synchronize()
+            assert did and torch.equal(out2, out)
+            nsf = Hq * D // (16 if kind == KIND_NVFP4 else 32)
+            assert torch.equal(fused.data, sep.data) and torch.equal(fused.sf[:, :nsf], sep.sf[:, :nsf])
 
 
 # ------------------------------------------------------------------ bounded flag waits (failure detection without a fault)
@@ -403,3 +419,84 @@ def test_flag_wait_runs_out_and_reports_status():
     peer_ops.wait_add(a, a * 2, a, out, 64, 0, flags.data_ptr(), ctl, 0, st, timeout_ns=20_000_000)
     torch.cuda.synchronize()
     assert torch.equal(out.float(), torch.full((64,), 4.0, device=DEV)) and int(ctl[0]) == 0
+
+
+# ------------------------------------------------------------------ fused glue kernels == their unfused sequences
+@pytest.mark.parametrize("kind", [KIND_NVFP4, KIND_MXFP4])
+@pytest.mark.parametrize("H", [256, 4096, 7168])
+def test_add_rmsnorm_with_fp4_output_matches_separate_quantiser(kind, H):
+    T = 5
+    g = torch.Generator().manual_seed(H)
+    x = (torch.randn(T, H, generator=g) * 2).to(torch.bfloat16).to(DEV)
+    w = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    inv_gs = torch.tensor([64.0], device=DEV)
+    y1, y2 = torch.zeros_like(x), torch.zeros_like(x)
+    a, b = ActBuffer.alloc(kind, T, H, 16, DEV), ActBuffer.alloc(kind, T, H, 16, DEV)
+    ops.add_rmsnorm(x.clone(), None, w, y1, 1e-6)
+    ops.quant_fp4_rows(y1, a, inv_gs=inv_gs)
+    ops.add_rmsnorm(x.clone(), None, w, y2, 1e-6, quant=b, inv_gs=inv_gs)
+    c = ActBuffer.alloc(kind, T, H, 16, DEV)
+    ops.add_rmsnorm(x.clone(), None, w, None, 1e-6, quant=c, inv_gs=inv_gs)      # FP4 output only
+    torch.cuda.synchronize()
+    nsf = H // (16 if kind == KIND_NVFP4 else 32)
+    assert torch.equal(y1, y2)
+    for o in (b, c):
+        assert torch.equal(a.data, o.data) and torch.equal(a.sf[:, :nsf], o.sf[:, :nsf])
+
+
+@pytest.mark.parametrize("kind", [KIND_BF16, KIND_NVFP4, KIND_MXFP4])
+@pytest.mark.parametrize("T,H", [(3, 256), (16, 4096), (70, 7168)])
+def test_combine_with_next_norm_matches_separate_kernels(kind, T, H):
+    k, rows = 4, T * 4
+    g = torch.Generator().manual_seed(T + H)
+    y = torch.randn(rows, H, generator=g).to(torch.bfloat16).to(DEV)
+    slot = torch.randperm(rows, generator=g).view(T, k).to(torch.int32)
+    slot[0, 1] = -1
+    slot = slot.to(DEV)
+    wts = torch.rand(T, k, generator=g).to(DEV)
+    shared = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    inv_gs = torch.tensor([64.0], device=DEV)
+    x1, x2 = x.clone(), x.clone()
+    xn1, xn2 = torch.zeros_like(x), torch.zeros_like(x)
+    ops.moe_combine(y, slot, wts, shared, x1, x1, T, k)
+    ops.add_rmsnorm(x1, None, w, xn1, 1e-6)
+    if kind == KIND_BF16:
+        ops.moe_combine(y, slot, wts, shared, x2, x2, T, k, norm_w=w, eps=1e-6, xn=xn2)
+        torch.cuda.synchronize()
+        assert torch.equal(x1, x2) and torch.equal(xn1, xn2)
+        return
+    a, b = ActBuffer.alloc(kind, T, H, 16, DEV), ActBuffer.alloc(kind, T, H, 16, DEV)
+    ops.quant_fp4_rows(xn1, a, inv_gs=inv_gs)
+    ops.moe_combine(y, slot, wts, shared, x2, x2, T, k, norm_w=w, eps=1e-6, quant=b, inv_gs=inv_gs)
+    torch.cuda.synchronize()
+    nsf = H // (16 if kind == KIND_NVFP4 else 32)
+    assert torch.equal(x1, x2)
+    assert torch.equal(a.data, b.data) and torch.equal(a.sf[:, :nsf], b.sf[:, :nsf])
+
+
+@pytest.mark.parametrize("T,E,k,e_lo,e_hi", [(1, 128, 8, 0, 128), (16, 128, 8, 0, 128), (37, 256, 8, 64, 128), (100, 64, 6, 0, 64)])
+def test_router_select_pack_matches_two_kernels(T, E, k, e_lo, e_hi):
+    g = torch.Generator().manual_seed(T * E)
+    logits = torch.randn(T, E, generator=g).to(DEV)
+    tn, rows = 16, T * k
+    max_tiles = (e_hi - e_lo) + rows // tn + 1
+    i32 = lambda *s: torch.full(s, -7, dtype=torch.int32, device=DEV)
+
+    def bufs():
+        return dict(idx=i32(T, k), wts=torch.zeros(T, k, device=DEV), src=i32(rows), slot=i32(T, k), cnt=i32(e_hi - e_lo), off=i32(e_hi - e_lo),
+                    tiles=i32(max_tiles, 4), nt=i32(1), nr=i32(1), route=i32(rows))
+    a, b = bufs(), bufs()
+    ops.router_select(logits, None, a["idx"], a["wts"], T, k, "softmax", True, 1.0)
+    ops.route_pack(a["idx"], a["src"], a["slot"], a["cnt"], a["off"], a["tiles"], a["nt"], a["nr"], T, k, e_lo, e_hi, tn, max_tiles, src_route=a["route"])
+    for _ in range(2):      # twice: the arrival counter must be left at zero
+        ops.router_select_pack(logits, None, b["idx"], b["wts"], T, k, "softmax", True, 1.0, 1, 1, b["src"], b["slot"], b["cnt"], b["off"],
+                               b["tiles"], b["nt"], b["nr"], e_lo, e_hi, tn, max_tiles, src_route=b["route"])
+    torch.cuda.synchronize()
+    n_rows, n_tiles = int(a["nr"][0]), int(a["nt"][0])
+    assert int(b["nr"][0]) == n_rows and int(b["nt"][0]) == n_tiles
+    for key in ("idx", "wts", "slot", "cnt", "off"):
+        assert torch.equal(a[key], b[key]), key
+    assert torch.equal(a["src"][:n_rows], b["src"][:n_rows]) and torch.equal(a["route"][:n_rows], b["route"][:n_rows])
+    assert torch.equal(a["tiles"][:n_tiles], b["tiles"][:n_tiles])
