@@ -1,0 +1,129 @@
+"""Micro-benchmarks of the tcgen05 linear kernels (decode-sized token tiles), timed as CUDA-graph replays of several
+launches over DISTINCT weights (so nothing is served from L2) with CUDA events.
+
+    python -m cuteafd_b200.bench.gemm --mode stream     # weight streaming: GB/s of large skinny GEMMs per format and K
+    python -m cuteafd_b200.bench.gemm --mode small      # decode projections (QKV / O / router shapes) per split-K factor
+    python -m cuteafd_b200.bench.gemm --mode trace      # device time stamps of the persistent kernel on small layers
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from .. import ops
+from ..ops import ActBuffer, TcWeight
+
+
+def graph_time_us(fns, reps: int = 5) -> float:
+    """Median device time per launch (microseconds) of one graph holding every callable of `fns`."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / len(fns))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def stream(dev, T: int = 16):
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    cases = [("bf16 K4096", "bf16", 75776, 4096, False), ("nvfp4 K8192", "nvfp4", 151552, 8192, False),
+             ("nvfp4 K4096", "nvfp4", 303104, 4096, False), ("nvfp4 K2048", "nvfp4", 606208, 2048, False),
+             ("nvfp4 K1536", "nvfp4", 606208, 1536, False), ("nvfp4 K1024", "nvfp4", 606208, 1024, False),
+             ("mxfp4 K4096", "mxfp4", 303104, 4096, False), ("mxfp4 K1536", "mxfp4", 606208, 1536, False),
+             ("nvfp4 swiglu K4096", "nvfp4", 151552, 4096, True)]
+    for name, kind, N, K, sw in cases:
+        copies = 3
+        Ws = [TcWeight.random(1, N, K, kind, dev, seed=i) for i in range(copies * (2 if sw else 1))]
+        x = ActBuffer.alloc(Ws[0].kind, T, K, ops.pick_tn(T, swiglu=True), dev)
+        y = torch.zeros(T, N, dtype=torch.bfloat16, device=dev)
+        if sw:
+            fns = [(lambda i=i: ops.tc_linear(Ws[2 * i], x, y, w_up=Ws[2 * i + 1], status=st)) for i in range(copies)]
+            nbytes = Ws[0].nbytes * 2
+        else:
+            fns = [(lambda W=W: ops.tc_linear(W, x, y, status=st)) for W in Ws]
+            nbytes = Ws[0].nbytes
+        us = graph_time_us(fns)
+        print(f"{name:20s} N={N} K={K} T={T} {us:8.1f} us  {nbytes / us / 1e3:7.1f} GB/s  ({nbytes / 1e6:.0f} MB)", flush=True)
+        del Ws
+    print("status", st.tolist())
+
+
+SMALL = [("wqkv", "nvfp4", 9216, 4096, 12), ("wo", "nvfp4", 4096, 8192, 12), ("router", "bf16", 128, 4096, 64),
+         ("shared-ish", "nvfp4", 1536, 4096, 40), ("q_b (mla)", "bf16", 12288, 1536, 8), ("o (mla)", "bf16", 7168, 8192, 4)]
+
+
+def small(dev, T: int = 16):
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    for name, kind, N, K, copies in SMALL:
+        Ws = [TcWeight.random(1, N, K, kind, dev, seed=i) for i in range(copies)]
+        x = ActBuffer.alloc(Ws[0].kind, T, K, 16, dev)
+        y = torch.zeros(T, N, dtype=torch.bfloat16, device=dev)
+        for splits in (1, 2, 3, 4, 8):
+            us = graph_time_us([(lambda W=W: ops.tc_linear(W, x, y, splits=splits, status=st)) for W in Ws])
+            how = "cluster" if splits in (2, 4, 8) else ("global fix-up" if splits > 1 else "-")
+            print(f"{name:10s} T={T} splits={splits} ({how:13s}) {us:8.2f} us/launch  {Ws[0].nbytes / us / 1e3:7.1f} GB/s", flush=True)
+    print("status", st.tolist())
+
+
+def trace(dev, T: int = 16):
+    """Period between launches, first load -> end of the last epilogue, and the gap to the next launch's first load
+    (tear-down + launch + prologue, and for the global fix-up the fix-up itself), from the kernel's own stamps."""
+    import numpy as np
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    for name, kind, N, K, splits in [("wqkv", "nvfp4", 9216, 4096, 1), ("wqkv", "nvfp4", 9216, 4096, 3), ("wo", "nvfp4", 4096, 8192, 1),
+                                     ("wo", "nvfp4", 4096, 8192, 3), ("router", "bf16", 128, 4096, 3)]:
+        copies = 10
+        Ws = [TcWeight.random(1, N, K, kind, dev, seed=i) for i in range(copies)]
+        x = ActBuffer.alloc(Ws[0].kind, T, K, 16, dev)
+        y = torch.zeros(T, N, dtype=torch.bfloat16, device=dev)
+        bufs = [torch.zeros(296, 4, 8, dtype=torch.int64, device=dev) for _ in range(copies)]
+
+        def run():
+            for W, b in zip(Ws, bufs):
+                ops.tc_trace(b, 4)
+                ops.tc_linear(W, x, y, splits=splits, status=st)
+            ops.tc_trace(None)
+        run()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        starts, ends = [], []
+        for b in bufs:
+            t = b.cpu().numpy()
+            starts.append(t[:, :, 7][t[:, :, 7] != 0].min())
+            ends.append(t[:, :, 3][t[:, :, 3] != 0].max())
+        starts, ends = np.array(starts), np.array(ends)
+        print(f"{name} splits={splits}: period {np.diff(starts)[2:].mean() / 1e3:.2f} us, first load -> last epilogue "
+              f"{(ends - starts)[2:].mean() / 1e3:.2f} us, gap to the next first load {(starts[1:] - ends[:-1])[2:].mean() / 1e3:.2f} us", flush=True)
+    print("status", st.tolist())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="stream", choices=["stream", "small", "trace"])
+    ap.add_argument("--tokens", type=int, default=16)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    {"stream": stream, "small": small, "trace": trace}[a.mode](dev, a.tokens)
+
+
+if __name__ == "__main__":
+    main()

@@ -346,6 +346,31 @@ __device__ __forceinline__ bool wait_flag_bounded(const uint32_t* flag, uint32_t
   }
 }
 
+// A flag wait folded into the kernel that consumes what the peer sent (instead of a wait-only launch in front of
+// it): threads 0..n-1 of every block poll flags[i * stride] >= ctl[1] (the current step) with the usual time limit;
+// on failure the status word and the abort word ctl[0] are set and the block learns it must not touch the data.
+struct FlagWait {
+  const uint32_t* flags; uint32_t* ctl; int* status; unsigned long long timeout_ns; int n, stride;
+};
+__device__ __forceinline__ bool flag_wait_block(const FlagWait& w) {
+  if (!w.flags) return true;
+  __shared__ int fw_ok;
+  if (threadIdx.x == 0) fw_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < w.n) {
+    if (w.ctl[0]) fw_ok = 0;
+    else if (!wait_flag_bounded(w.flags + (size_t)threadIdx.x * w.stride, w.ctl[1], w.timeout_ns)) {
+      ca_dev_fail(w.status, CA_DEV_TIMEOUT_FLAG, (int)threadIdx.x);
+      atomicExch(&w.ctl[0], 1u);
+      fw_ok = 0;
+    }
+  }
+  __syncthreads();
+  return fw_ok != 0;
+}
+// One-shot hand-over from cuteafd_arm_flag_wait() to the next launch of this host thread that supports it.
+FlagWait ca_take_flag_wait();
+
 // ------------------------------------------------------------------ host: TMA descriptor encode
 // Resolved at run time from the driver so the library links without libcuda.
 int ca_encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint64_t inner, uint64_t outer,

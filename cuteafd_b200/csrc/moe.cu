@@ -16,6 +16,7 @@ struct RoutePack {
   const int* idx; int* src_token; int* slot_row; int* counts; int* offsets; int4* tiles; int* n_tiles; int* n_rows; int* src_route;
   int T, k, e_lo, e_hi, tn, max_tiles;
   int* ticket;      // fused with the router: arrival counter of the select blocks (zero on entry, left zero)
+  FlagWait wait;    // expert ranks: the routing table and the rows arrive from peers; wait for their flags first
 };
 
 __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
@@ -64,6 +65,10 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
 __global__ void route_pack_kernel(const RoutePack p) {
   pdl_launch(); pdl_wait();
   extern __shared__ int sh[];
+  if (!flag_wait_block(p.wait)) {      // the peer never delivered: publish an empty work list
+    if (threadIdx.x == 0) { *p.n_tiles = 0; *p.n_rows = 0; }
+    return;
+  }
   route_pack_body(p, sh);
 }
 
@@ -175,6 +180,7 @@ extern "C" int cuteafd_router_select(const float* logits, const float* bias, int
   if (T <= 0) return CA_OK;
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
   RoutePack none{};
+  none.wait = FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0};
   CA_LAUNCH_PDL(router_select_kernel, T, threads, 0, s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale, n_group, topk_group, none);
   return CA_OK;
 }
@@ -183,7 +189,8 @@ extern "C" int cuteafd_route_pack(const int* idx, int* src_token, int* slot_row,
                                   int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, int* src_route, cudaStream_t s) {
   CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 4096, "route_pack: bad expert range");
   CA_REQUIRE(tn >= 1, "route_pack: bad tile rows");
-  RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, nullptr};
+  RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, nullptr,
+              ca_take_flag_wait()};
   CA_LAUNCH_PDL(route_pack_kernel, 1, 1024, route_pack_smem(T, k, e_lo, e_hi), s, p);
   return CA_OK;
 }
@@ -199,7 +206,8 @@ extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias
   CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 512 && tn >= 1 && ticket, "router_select_pack: bad pack arguments");
   if (T <= 0) return CA_OK;
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
-  RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, ticket};
+  RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, ticket,
+              FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0}};
   CA_LAUNCH_PDL(router_select_kernel, T, threads, route_pack_smem(T, k, e_lo, e_hi), s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale,
                 n_group, topk_group, p);
   return CA_OK;
@@ -210,8 +218,9 @@ extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias
 // residual / shared may be null; routes with slot_row < 0 are skipped.
 __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __restrict__ slot_row, const float* __restrict__ wts,
                                    const bf16* __restrict__ shared, const bf16* __restrict__ residual, bf16* __restrict__ out,
-                                   int H, int k) {
+                                   int H, int k, const FlagWait fw) {
   pdl_launch(); pdl_wait();
+  if (!flag_wait_block(fw)) return;
   const int t = blockIdx.x;
   for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8; i < H; i += gridDim.y * blockDim.x * 8) {
     float acc[8];
@@ -247,9 +256,10 @@ __global__ void moe_combine_norm_kernel(const bf16* __restrict__ y, const int* _
                                         const bf16* __restrict__ shared, const bf16* __restrict__ residual, bf16* __restrict__ out,
                                         int H, int k, const float* __restrict__ norm_w, float eps, bf16* __restrict__ xn,
                                         uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int ldsf,
-                                        const float* __restrict__ inv_gs_ptr, int qkind) {
+                                        const float* __restrict__ inv_gs_ptr, int qkind, const FlagWait fw) {
   pdl_launch(); pdl_wait();
   __shared__ float red[32];
+  if (!flag_wait_block(fw)) return;
   const int t = blockIdx.x;
   float v[VEC * 8];
   float ss = 0.f;
@@ -311,7 +321,8 @@ extern "C" int cuteafd_moe_combine_norm(const void* y, const int* slot_row, cons
   if (threads < 32) threads = 32;
   const int per = (vecs + threads - 1) / threads;
 #define CA_CN(V) CA_LAUNCH_PDL(moe_combine_norm_kernel<V>, T, threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, \
-                               (bf16*)out, H, k, norm_w, eps, (bf16*)xn, (uint8_t*)q, (uint8_t*)sf, ldsf, inv_gs, qkind)
+                               (bf16*)out, H, k, norm_w, eps, (bf16*)xn, (uint8_t*)q, (uint8_t*)sf, ldsf, inv_gs, qkind, fw)
+  const FlagWait fw = ca_take_flag_wait();
   if (per == 1) CA_CN(1); else if (per == 2) CA_CN(2); else CA_CN(4);
 #undef CA_CN
   return CA_OK;
@@ -324,7 +335,8 @@ extern "C" int cuteafd_moe_combine(const void* y, const int* slot_row, const flo
   const int threads = H / 8 >= 256 ? 256 : (H / 8 >= 128 ? 128 : 64);
   // few tokens: split the row over several blocks so more SMs pull the k routed rows
   const int ysplit = T >= 64 ? 1 : (H / 8 + threads - 1) / threads;
-  CA_LAUNCH_PDL(moe_combine_kernel, dim3(T, ysplit), threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, (bf16*)out, H, k);
+  const FlagWait fw = ca_take_flag_wait();
+  CA_LAUNCH_PDL(moe_combine_kernel, dim3(T, ysplit), threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, (bf16*)out, H, k, fw);
   CA_CHECK_LAUNCH("moe_combine");
   return CA_OK;
 }

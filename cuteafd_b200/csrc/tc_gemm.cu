@@ -43,6 +43,10 @@ struct TcArgs {
   float* splitk_ws;           // [splits, rows_pad, N] partials (dense split-K)
   int* splitk_cnt;            // [items * n_tiles * 4] arrival counters, zero on entry, left zero on exit
   int* status;
+  uint8_t* q_out;             // optional FP4 copy of the output (same kind as the operands): codes [rows, N / 2] ...
+  uint8_t* sf_out;            // ... and block scales [rows, ldsf_out], for the GEMM that consumes this one's output
+  const float* inv_gs_out;    // NVFP4: 1 / activation global scale of that consumer
+  int ldsf_out;
   long long* trace;           // optional per-unit time stamps [grid, trace_units, 8] (see cuteafd_tc_trace)
   int ldsfb, ldy, rows_total, N, K, epi, splits, trace_units;
 };
@@ -291,7 +295,44 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
         tmem_ld_x16(tbase + c0, r);
         if (SWIGLU) tmem_ld_x16(tbase + TN + c0, r2);
         tc_wait_ld();
-        if (c0 < nrows && n_ok) {
+        if (KIND != KIND_BF16 && a.q_out) {
+          // FP4 output for the next GEMM: this lane holds output feature n of 16 tokens; a quantisation block is 16
+          // (NVFP4) or 32 (MXFP4) consecutive features = adjacent lanes, so amax and the nibble packing are shuffles.
+          // Same arithmetic as the stand-alone quantiser on the bf16-rounded value.
+          if (c0 < nrows) {
+            const float inv_gs = (KIND == KIND_NVFP4 && a.inv_gs_out) ? *a.inv_gs_out : 1.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int c = c0 + j;
+              if (c < nrows) {                       // warp-uniform
+                float v = __uint_as_float(r[j]) * al;
+                if (SWIGLU) {
+                  const float u = __uint_as_float(r2[j]) * al2;
+                  v = v / (1.f + __expf(-v)) * u;
+                }
+                const bf16 vb = __float2bfloat16(n_ok ? v : 0.f);
+                v = __bfloat162float(vb);
+                float am = fabsf(v);
+                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1)); am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4)); am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 8));
+                float eff; uint8_t sb;
+                if (KIND == KIND_MXFP4) {
+                  am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 16));
+                  int e = am > 0.f ? (int)((__float_as_uint(am) >> 23) & 0xFF) - 2 : 0;
+                  e = max(e, 0); e = min(e, 254); sb = (uint8_t)e; eff = ue8m0_to_float(sb);
+                } else {
+                  sb = float_to_e4m3(fminf(am * inv_gs / 6.f, 448.f)); eff = e4m3_to_float(sb) / inv_gs;
+                }
+                uint32_t wv = float_to_e2m1(v * (eff > 0.f ? 1.f / eff : 0.f)) << (4 * (lane & 7));
+                wv |= __shfl_xor_sync(0xffffffffu, wv, 1); wv |= __shfl_xor_sync(0xffffffffu, wv, 2); wv |= __shfl_xor_sync(0xffffffffu, wv, 4);
+                const size_t row = (size_t)(row0 + c);
+                if (n_ok && (lane & 7) == 0) *(uint32_t*)(a.q_out + row * (a.N / 2) + n / 2) = wv;
+                if (n_ok && (lane & (KIND == KIND_MXFP4 ? 31 : 15)) == 0) a.sf_out[row * a.ldsf_out + n / (KIND == KIND_MXFP4 ? 32 : 16)] = sb;
+                if (a.Y && n_ok) ((bf16*)a.Y)[row * a.ldy + n] = vb;
+              }
+            }
+          }
+        } else if (c0 < nrows && n_ok) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int c = c0 + j;
@@ -651,13 +692,26 @@ extern "C" int cuteafd_tc_trace(void* buf, int units) {
   return CA_OK;
 }
 
+static thread_local struct { void* q; void* sf; const float* inv_gs; int ldsf; } g_q_out = {nullptr, nullptr, nullptr, 0};
+
+// Arms the NEXT cuteafd_tc_linear call of this thread to also write its output quantised to FP4 (the operands'
+// format; grouped or dense, not with split-K): codes [rows, N / 2], scales [rows, ldsf].  Y may then be null.
+extern "C" int cuteafd_tc_linear_fp4_out(void* q, void* sf, int ldsf, const float* inv_gs) {
+  g_q_out.q = q; g_q_out.sf = sf; g_q_out.ldsf = ldsf; g_q_out.inv_gs = inv_gs;
+  return CA_OK;
+}
+
 extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, const void* tmA2, const void* tmB,
                                  const void* sfa, const void* sfa2, const void* sfb, int ldsfb, const float* alpha,
                                  const float* alpha2, const void* tiles, const int* n_tiles, int max_tiles, void* Y,
                                  const void* R, int ldy, int rows_total, int N, int K, int epi, int splits,
                                  float* splitk_ws, int* splitk_cnt, int* status, int max_ctas, cudaStream_t stream) {
   CA_REQUIRE(kind >= 0 && kind <= 2, "tc_linear: bad kind %d", kind);
-  CA_REQUIRE(tmA && tmB && Y, "tc_linear: null operand");
+  void* q_out = g_q_out.q; void* sf_out = g_q_out.sf; const float* inv_gs_out = g_q_out.inv_gs; const int ldsf_out = g_q_out.ldsf;
+  g_q_out.q = g_q_out.sf = nullptr;       // one-shot
+  CA_REQUIRE(tmA && tmB && (Y || q_out), "tc_linear: null operand");
+  CA_REQUIRE(!q_out || (kind != KIND_BF16 && sf_out && splits <= 1 && N % 32 == 0 && epi == EPI_BF16),
+             "tc_linear: FP4 output needs an FP4 kind, no split-K, N %% 32 == 0 and the plain bf16 epilogue");
   CA_REQUIRE(!swiglu || tmA2, "tc_linear: swiglu needs the up-projection descriptor");
   CA_REQUIRE(kind == KIND_BF16 || (sfa && sfb && K % 32 == 0), "tc_linear: fp4 kinds need scales and K %% 32 == 0 (K=%d)", K);
   CA_REQUIRE(kind == KIND_BF16 ? (K % 8 == 0) : true, "tc_linear: K must be a multiple of 8");
@@ -671,6 +725,7 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.alpha = alpha; a.alpha2 = alpha2; a.tiles = (const int4*)tiles; a.n_tiles = n_tiles;
   a.Y = Y; a.R = (const bf16*)R; a.splitk_ws = splitk_ws; a.splitk_cnt = splitk_cnt; a.status = status;
   a.trace = g_trace; a.trace_units = g_trace_units;
+  a.q_out = (uint8_t*)q_out; a.sf_out = (uint8_t*)sf_out; a.inv_gs_out = inv_gs_out; a.ldsf_out = ldsf_out;
   a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;
   const int n_nt = (N + 127) / 128;
   if (!tiles && !swiglu && (tn == 16 || tn == 32) && (a.splits == 2 || a.splits == 4 || (a.splits == 8 && tn == 16))) {

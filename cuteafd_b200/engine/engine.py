@@ -298,11 +298,16 @@ class Engine:
             ops.gather_rows(L.xn, L.src_token, L.n_rows, L.xs.data, rows)
         else:
             ops.quant_fp4_rows(L.xn, L.xs, src_rows=L.src_token, n_rows_dev=L.n_rows, rows=rows, inv_gs=lw.w_gate.inv_act_gs)
-        ops.tc_linear(lw.w_gate, L.xs, L.h1, rows=rows, w_up=lw.w_up, tiles=L.tiles, n_tiles=L.n_tiles, max_tiles=L.max_tiles,
-                      status=self.status)
-        if L.h1_q.kind != KIND_BF16:
-            ops.quant_fp4_rows(L.h1, L.h1_q, n_rows_dev=L.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
-            self.launches_per_step += 1
+        if L.h1_q.kind != KIND_BF16 and m.intermediate % 32 == 0:
+            # FC1's epilogue writes silu(g) * u already quantised for FC2 (no bf16 round trip, no quantiser launch)
+            ops.tc_linear(lw.w_gate, L.xs, None, rows=rows, w_up=lw.w_up, tiles=L.tiles, n_tiles=L.n_tiles, max_tiles=L.max_tiles,
+                          status=self.status, quant_out=L.h1_q, inv_gs_out=lw.w_down.inv_act_gs)
+        else:
+            ops.tc_linear(lw.w_gate, L.xs, L.h1, rows=rows, w_up=lw.w_up, tiles=L.tiles, n_tiles=L.n_tiles, max_tiles=L.max_tiles,
+                          status=self.status)
+            if L.h1_q.kind != KIND_BF16:
+                ops.quant_fp4_rows(L.h1, L.h1_q, n_rows_dev=L.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
+                self.launches_per_step += 1
         ops.tc_linear(lw.w_down, L.h1_q, L.y2, rows=rows, tiles=L.tiles, n_tiles=L.n_tiles, max_tiles=L.max_tiles, status=self.status)
         shared = None
         if lw.ws_gate is not None:

@@ -203,23 +203,33 @@ def _splitk_scratch(device, n_float: int, n_cnt: int):
     return ws, cnt
 
 
-def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor, *, rows: int | None = None, w_up: TcWeight | None = None,
+def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor | None, *, rows: int | None = None, w_up: TcWeight | None = None,
               residual: torch.Tensor | None = None, tiles: torch.Tensor | None = None, n_tiles: torch.Tensor | None = None,
-              max_tiles: int = 0, splits: int = 1, status: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+              max_tiles: int = 0, splits: int = 1, status: torch.Tensor | None = None, max_ctas: int = 0,
+              quant_out: ActBuffer | None = None, inv_gs_out: torch.Tensor | None = None) -> torch.Tensor | None:
     """y[rows, N] = x[rows, K] @ w[g]^T (per tile's expert g when `tiles` is given).  `w_up` switches on the fused
-    SwiGLU epilogue (y = silu(x w^T) * (x w_up^T)).  y is bf16 (optionally + residual) or fp32."""
+    SwiGLU epilogue (y = silu(x w^T) * (x w_up^T)).  y is bf16 (optionally + residual) or fp32.  `quant_out` (an FP4
+    activation buffer of the operands' kind, K = N) also receives the output quantised for the GEMM that follows
+    (`inv_gs_out`: that GEMM's activation scale, NVFP4); y may then be None."""
     rows = x.rows if rows is None else rows
     if w.kind != x.kind or w.K != x.K:
         raise ValueError("tc_linear: operand kinds / K differ")
-    epi = EPI_F32 if y.dtype == torch.float32 else (EPI_BF16_RESIDUAL if residual is not None else EPI_BF16)
+    if y is None:
+        epi = EPI_BF16
+    else:
+        epi = EPI_F32 if y.dtype == torch.float32 else (EPI_BF16_RESIDUAL if residual is not None else EPI_BF16)
     ws = cnt = None
     if splits > 1:
         n_items = -(-rows // x.tn)
-        ws, cnt = _splitk_scratch(y.device, splits * rows * w.N, n_items * (-(-w.N // 128)) * 4)
+        ws, cnt = _splitk_scratch(x.data.device, splits * rows * w.N, n_items * (-(-w.N // 128)) * 4)
+    if quant_out is not None:
+        if quant_out.kind != w.kind or quant_out.K != w.N:
+            raise ValueError("tc_linear: quant_out must be an FP4 buffer of the operands' kind with K = N")
+        call("cuteafd_tc_linear_fp4_out", ptr(quant_out.data), ptr(quant_out.sf), quant_out.sf.shape[1], ptr(inv_gs_out))
     call("cuteafd_tc_linear", w.kind, 1 if w_up is not None else 0, x.tn, ptr(w.tmap), ptr(w_up.tmap) if w_up else None,
          ptr(x.tmap), ptr(w.sf_ptrs), ptr(w_up.sf_ptrs) if w_up else None, ptr(x.sf), x.sf.shape[1] if x.sf is not None else 0,
          ptr(w.alpha), ptr(w_up.alpha) if w_up else None, ptr(tiles), ptr(n_tiles), max_tiles, ptr(y), ptr(residual),
-         y.stride(0), rows, w.N, w.K, epi, splits, ptr(ws), ptr(cnt), ptr(status), max_ctas, stream())
+         y.stride(0) if y is not None else 0, rows, w.N, w.K, epi, splits, ptr(ws), ptr(cnt), ptr(status), max_ctas, stream())
     return y
 
 

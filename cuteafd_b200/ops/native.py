@@ -21,6 +21,8 @@ _PROTOS = {
     "cuteafd_abi_version": [],
     "cuteafd_set_pdl": [I],
     "cuteafd_tc_trace": [P, I],
+    "cuteafd_arm_flag_wait": [P, I, I, P, C.c_ulonglong, P],
+    "cuteafd_tc_linear_fp4_out": [P, P, I, P],
     "cuteafd_device_info": [P, P, P, P, P],
     "cuteafd_tmap_encode_kmajor": [P, P, I, U64, U64, U64, U64, U64, C.c_uint32],
     "cuteafd_embed_gather": [P, P, P, I, I, I, P, P],

@@ -182,9 +182,9 @@ class AttnRankEngine(Engine):
         if lw.ws_gate is not None:
             self._ffn(lw, L, T, L.shared, None)
             shared = L.shared
-        peer_ops.wait_flags(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_COMBINE, li, 0)), dep.ep, 1, self.ctl, 0, self.status)
+        peer_ops.arm_flag_wait(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_COMBINE, li, 0)), dep.ep, 1, self.ctl, self.status)
         self._combine(self.y_recv, self.identity_rows, self.wts, shared, L, T, m.top_k)
-        self.launches_per_step += 4
+        self.launches_per_step += 3
 
     def _moe_nccl(self, li, lw, L, T):
         import torch.distributed as dist
@@ -296,21 +296,25 @@ class ExpertRankWorker:
             return self._layer_nccl(li, lw, T)
         for g in range(dep.attn_groups):
             xs, idx = self.xs_g[g], self.idx_g[g]
-            peer_ops.wait_flags(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_DISPATCH, li, g * dep.tp)), dep.tp, 1,
-                                self.ctl, 0, self.status)
+            peer_ops.arm_flag_wait(self.block.peer_ptr(self.rank, "flags", flag_offset(spec, PH_DISPATCH, li, g * dep.tp)), dep.tp, 1,
+                                   self.ctl, self.status)       # the pack kernel waits for this group's dispatch itself
             ops.route_pack(idx, self.src_token, self.slot_row, self.counts, self.offsets, self.tiles, self.n_tiles, self.n_rows,
                            T, m.top_k, self.e_lo, self.e_hi, self.tn, self.max_tiles, src_route=self.src_route)
-            ops.tc_linear(lw.w_gate, xs, self.h1, rows=rows, w_up=lw.w_up, tiles=self.tiles, n_tiles=self.n_tiles,
-                          max_tiles=self.max_tiles, status=self.status)
-            if self.kind != KIND_BF16:
-                ops.quant_fp4_rows(self.h1, self.h1_q, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
+            if self.kind != KIND_BF16 and m.intermediate % 32 == 0:      # FC1 writes its output quantised for FC2
+                ops.tc_linear(lw.w_gate, xs, None, rows=rows, w_up=lw.w_up, tiles=self.tiles, n_tiles=self.n_tiles,
+                              max_tiles=self.max_tiles, status=self.status, quant_out=self.h1_q, inv_gs_out=lw.w_down.inv_act_gs)
+            else:
+                ops.tc_linear(lw.w_gate, xs, self.h1, rows=rows, w_up=lw.w_up, tiles=self.tiles, n_tiles=self.n_tiles,
+                              max_tiles=self.max_tiles, status=self.status)
+                if self.kind != KIND_BF16:
+                    ops.quant_fp4_rows(self.h1, self.h1_q, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
             ops.tc_linear(lw.w_down, self.h1_q, self.y2, rows=rows, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
                           status=self.status)
             flag_tbl = self.block.ptr_table(dep.group_ranks(g), "flags", flag_offset(spec, PH_COMBINE, li, self.ep_rank))
             self._keep.append(flag_tbl)
             peer_ops.combine_push(self.y2, self.src_route, self.n_rows, self.recv_tbl_g[g], flag_tbl, self.ctl, self.done[0:1], spec.hidden,
                                   dep.tp, rows, 0)
-            self.launches_per_step += 6
+            self.launches_per_step += 4
 
     def _layer_nccl(self, li, lw, T):
         import torch.distributed as dist

@@ -18,6 +18,11 @@ def wait_flags(flags_ptr: int, n: int, stride: int, ctl, step_offset: int, statu
     call("cuteafd_wait_flags", flags_ptr, n, stride, ptr(ctl), step_offset, timeout_ns, ptr(status), stream())
 
 
+def arm_flag_wait(flags_ptr: int, n: int, stride: int, ctl, status, timeout_ns: int = WAIT_NS):
+    """The next route_pack / moe_combine launch waits for these flags inside the kernel (no wait-only launch)."""
+    call("cuteafd_arm_flag_wait", flags_ptr, n, stride, ptr(ctl), timeout_ns, ptr(status))
+
+
 def push_bytes(src: torch.Tensor, peer_dst: int, nbytes: int, peer_flag: int, ctl, step_offset: int, done_counter):
     call("cuteafd_push_bytes", ptr(src), peer_dst, nbytes, peer_flag, ptr(ctl), step_offset, ptr(done_counter), stream())
 

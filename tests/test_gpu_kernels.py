@@ -177,6 +177,17 @@ def test_tc_linear_grouped_swiglu_and_down(kind):
     ref = rops.moe_forward(bf16r(x), dq(Wg), dq(Wu), dq(Wd), idx.long(), wts)
     tol = 3e-2 if kind == "bf16" else 0.25      # fp4 activations are re-quantised twice on the GPU path
     assert rel_err(out.float().cpu() - resid.float().cpu(), ref) < tol
+    if Wg.kind != KIND_BF16:
+        # FC1 can write its output already quantised for FC2: same bytes as bf16 output + stand-alone quantiser
+        h1f, h1qf = torch.zeros_like(h1), ActBuffer.alloc(Wg.kind, rows, I, tn, DEV)
+        ops.tc_linear(Wg, xs, h1f, w_up=Wu, tiles=tiles, n_tiles=nt, max_tiles=max_tiles, status=st, quant_out=h1qf, inv_gs_out=Wd.inv_act_gs)
+        h1qn = ActBuffer.alloc(Wg.kind, rows, I, tn, DEV)
+        ops.tc_linear(Wg, xs, None, w_up=Wu, tiles=tiles, n_tiles=nt, max_tiles=max_tiles, status=st, quant_out=h1qn, inv_gs_out=Wd.inv_act_gs)
+        torch.cuda.synchronize()
+        nsf = I // (16 if Wg.kind == KIND_NVFP4 else 32)
+        assert int(st[0]) == 0 and torch.equal(h1f, h1)
+        for o in (h1qf, h1qn):
+            assert torch.equal(o.data, h1q.data) and torch.equal(o.sf[:, :nsf], h1q.sf[:, :nsf])
 
 
 # ------------------------------------------------------------------ elementwise
