@@ -47,6 +47,15 @@ struct TcArgs {
   uint8_t* sf_out;            // ... and block scales [rows, ldsf_out], for the GEMM that consumes this one's output
   const float* inv_gs_out;    // NVFP4: 1 / activation global scale of that consumer
   int ldsf_out;
+  // Fused hand-off to peer GPUs: the bf16 output tile is also stored straight into peers' memory over NVLink from
+  // the epilogue (row r of this GEMM lands in row peer_row_map[r], or r), and once every CTA has finished, the last
+  // one releases the peers' flags with the current step number - GEMM and transfer are one kernel, tile by tile.
+  void* peer_y[2];
+  uint32_t* peer_flags[2];
+  const int* peer_row_map;
+  uint32_t* peer_ctl;         // [0] abort word, [1] step number
+  uint32_t* peer_done;        // arrival counter: zero on entry, left zero
+  int peer_ld, n_peer;
   long long* trace;           // optional per-unit time stamps [grid, trace_units, 8] (see cuteafd_tc_trace)
   int ldsfb, ldy, rows_total, N, K, epi, splits, trace_units;
 };
@@ -102,6 +111,26 @@ __device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) 
   d |= (uint32_t)(n >> 3) << 17;
   d |= (uint32_t)(128 >> 4) << 24;
   return d;
+}
+
+// Tail of a kernel whose epilogue stored to peers: the 128 epilogue threads fence their stores, one of them counts the
+// CTA in, and the CTA that arrives last publishes the flags (system-scope release) and re-arms the counter.
+__device__ __forceinline__ void peer_publish(const TcArgs& a, int warp, int lane) {
+  __threadfence_system();
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (warp == 2 && lane == 0) {
+    const uint32_t prev = atomicAdd(a.peer_done, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      const uint32_t step = a.peer_ctl[1];
+      for (int d = 0; d < a.n_peer; ++d) st_release_sys(a.peer_flags[d], step);
+      *a.peer_done = 0;
+    }
+  }
+}
+__device__ __forceinline__ void peer_store(const TcArgs& a, int row, int n, bf16 v) {
+  const size_t prow = a.peer_row_map ? (size_t)a.peer_row_map[row] : (size_t)row;
+  for (int d = 0; d < a.n_peer; ++d) ((bf16*)a.peer_y[d])[prow * a.peer_ld + n] = v;
 }
 
 template <int KIND, int TN, bool SWIGLU>
@@ -347,7 +376,9 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
               else if (a.epi == EPI_F32) ((float*)a.Y)[o] = v;
               else {
                 if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
-                ((bf16*)a.Y)[o] = __float2bfloat16(v);
+                const bf16 vb = __float2bfloat16(v);
+                if (a.Y) ((bf16*)a.Y)[o] = vb;
+                if (a.n_peer) peer_store(a, row0 + c, n, vb);
               }
             }
           }
@@ -392,7 +423,9 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
                 if (a.epi == EPI_F32) ((float*)a.Y)[o] = r;
                 else {
                   if (a.epi == EPI_BF16_RESIDUAL) r += __bfloat162float(a.R[o]);
-                  ((bf16*)a.Y)[o] = __float2bfloat16(r);
+                  const bf16 rb = __float2bfloat16(r);
+                  if (a.Y) ((bf16*)a.Y)[o] = rb;
+                  if (a.n_peer) peer_store(a, row0 + c + j, n, rb);
                 }
               }
             }
@@ -402,6 +435,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
         }
       }
     }
+    if (a.n_peer) peer_publish(a, warp, lane);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -641,13 +675,16 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
             if (a.epi == EPI_F32) ((float*)a.Y)[o] = v;
             else {
               if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
-              ((bf16*)a.Y)[o] = __float2bfloat16(v);
+              const bf16 vb = __float2bfloat16(v);
+              if (a.Y) ((bf16*)a.Y)[o] = vb;
+              if (a.n_peer) peer_store(a, row0 + c, n, vb);
             }
           }
         }
       }
     }
   }
+  if (warp >= 2 && a.n_peer) peer_publish(a, warp, lane);      // every CTA counts in; only rank 0 of a cluster stored
   if (*abortp && warp == 0) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000) __nanosleep(1000);
@@ -701,6 +738,18 @@ extern "C" int cuteafd_tc_linear_fp4_out(void* q, void* sf, int ldsf, const floa
   return CA_OK;
 }
 
+static thread_local struct { void* y[2]; void* flags[2]; const int* row_map; void* ctl; void* done; int ld, n; } g_peer_out = {};
+
+// Arms the NEXT cuteafd_tc_linear call of this thread (bf16 output, dense or grouped, any split mode) to store its
+// output tiles into `n` peers' buffers as well (row r -> row row_map[r] when a map is given) and to release
+// `flags[d]` with the step number ctl[1] when the whole GEMM has been written.  `done` is a zeroed device counter.
+extern "C" int cuteafd_tc_linear_peer_out(void* y0, void* y1, int n, int ld, const int* row_map, void* flag0, void* flag1, void* ctl, void* done) {
+  CA_REQUIRE(n >= 1 && n <= 2 && y0 && flag0 && ctl && done && (n == 1 || (y1 && flag1)), "tc_linear_peer_out: 1 or 2 peers with buffers and flags");
+  g_peer_out.y[0] = y0; g_peer_out.y[1] = y1; g_peer_out.flags[0] = flag0; g_peer_out.flags[1] = flag1;
+  g_peer_out.row_map = row_map; g_peer_out.ctl = ctl; g_peer_out.done = done; g_peer_out.ld = ld; g_peer_out.n = n;
+  return CA_OK;
+}
+
 extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, const void* tmA2, const void* tmB,
                                  const void* sfa, const void* sfa2, const void* sfb, int ldsfb, const float* alpha,
                                  const float* alpha2, const void* tiles, const int* n_tiles, int max_tiles, void* Y,
@@ -709,7 +758,10 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   CA_REQUIRE(kind >= 0 && kind <= 2, "tc_linear: bad kind %d", kind);
   void* q_out = g_q_out.q; void* sf_out = g_q_out.sf; const float* inv_gs_out = g_q_out.inv_gs; const int ldsf_out = g_q_out.ldsf;
   g_q_out.q = g_q_out.sf = nullptr;       // one-shot
-  CA_REQUIRE(tmA && tmB && (Y || q_out), "tc_linear: null operand");
+  const auto peer = g_peer_out;
+  g_peer_out.n = 0;                       // one-shot
+  CA_REQUIRE(tmA && tmB && (Y || q_out || peer.n), "tc_linear: null operand");
+  CA_REQUIRE(!peer.n || (epi != EPI_F32 && !q_out), "tc_linear: peer output is a bf16 epilogue");
   CA_REQUIRE(!q_out || (kind != KIND_BF16 && sf_out && splits <= 1 && N % 32 == 0 && epi == EPI_BF16),
              "tc_linear: FP4 output needs an FP4 kind, no split-K, N %% 32 == 0 and the plain bf16 epilogue");
   CA_REQUIRE(!swiglu || tmA2, "tc_linear: swiglu needs the up-projection descriptor");
@@ -725,6 +777,8 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.alpha = alpha; a.alpha2 = alpha2; a.tiles = (const int4*)tiles; a.n_tiles = n_tiles;
   a.Y = Y; a.R = (const bf16*)R; a.splitk_ws = splitk_ws; a.splitk_cnt = splitk_cnt; a.status = status;
   a.trace = g_trace; a.trace_units = g_trace_units;
+  a.peer_y[0] = peer.y[0]; a.peer_y[1] = peer.y[1]; a.peer_flags[0] = (uint32_t*)peer.flags[0]; a.peer_flags[1] = (uint32_t*)peer.flags[1];
+  a.peer_row_map = peer.row_map; a.peer_ctl = (uint32_t*)peer.ctl; a.peer_done = (uint32_t*)peer.done; a.peer_ld = peer.ld; a.n_peer = peer.n;
   a.q_out = (uint8_t*)q_out; a.sf_out = (uint8_t*)sf_out; a.inv_gs_out = inv_gs_out; a.ldsf_out = ldsf_out;
   a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;
   const int n_nt = (N + 127) / 128;

@@ -1,0 +1,287 @@
+// FP8 (E4M3) linear layer with DeepSeek-style block scales for sm_100a:
+//   Y[rows, N] = sum_kb  sa[row, kb] * sw[n / 128, kb] * ( Xq[rows, kb-th 128 of K] * Wq[N, same 128]^T )
+// weights carry one fp32 scale per 128 x 128 block (the checkpoint's `weight_scale_inv`), activations one fp32 scale
+// per token and 128 channels (quantised on the fly by `act_quant_fp8_block128`).
+//
+// tcgen05 has no 128-wide fp32 block scaling, so the scaling happens between the tensor core and the registers:
+// one pipeline stage is exactly one scale block (128 bytes of K per row, four kind::f8f6f4 MMAs of K = 32), each
+// stage accumulates into a FRESH tensor-memory buffer (ring of four), and the epilogue warps pull every finished
+// buffer with tcgen05.ld and add it, scaled, to fp32 registers while the next stages run.  swap-AB as in the other
+// GEMMs (weight rows = MMA M, tokens = MMA N = 16..128), one work unit (128 x TN tile, one K slice) per CTA, optional
+// split-K over a thread-block cluster with the partial tiles reduced through distributed shared memory.
+//
+// Reference counterparts: the W8A8 FP8 GEMV/GEMM (native/shared/cuda/fp8_gemv.cu, fp8_block.cu) and the block-scale
+// handling of the FP8 backbone (families/deepseek_v4/engine.rs:1320-1390).
+#define CA_PDL_CLASS 1
+#include "common.cuh"
+
+enum { F8_EPI_BF16 = 0, F8_EPI_BF16_RESIDUAL = 1, F8_EPI_F32 = 3 };
+
+struct Fp8Args {
+  const CUtensorMap* tmA;   // weights [N, K] bytes, box {128, 128}
+  const CUtensorMap* tmB;   // activations [rows, K] bytes, box {128, TN}
+  const float* sw;          // [ceil(N / 128), ceil(K / 128)]
+  const float* sa;          // [rows, ceil(K / 128)]
+  void* Y;
+  const bf16* R;
+  int* status;
+  int ldy, rows_total, N, K, epi, splits;
+};
+
+template <int TN>
+struct Fp8Cfg {
+  static constexpr int A_BYTES = 128 * 128, B_BYTES = TN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int NACC = 4;
+  static constexpr int TMEM_COLS = NACC * TN < 32 ? 32 : NACC * TN;       // 64 / 128 / 256 / 512
+  static constexpr int BUDGET = 200 * 1024, MAX_RING = 8;
+  static constexpr int SMEM_BYTES = BUDGET + 1024;
+  __host__ __device__ static constexpr int ring(int S) {
+    return (BUDGET - (S - 1) * 128 * TN * 4) / STAGE_BYTES > MAX_RING ? MAX_RING : (BUDGET - (S - 1) * 128 * TN * 4) / STAGE_BYTES;
+  }
+};
+
+__device__ __forceinline__ uint32_t f8_cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void f8_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int TN>
+__global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constant__ Fp8Args a) {
+  using C = Fp8Cfg<TN>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[C::MAX_RING], empty_bar[C::MAX_RING], accf_bar[C::NACC], acce_bar[C::NACC];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int S = a.splits > 1 ? a.splits : 1;
+  const int ring = C::ring(S);
+  float* staging = (float*)(smem + ring * C::STAGE_BYTES);                 // [S-1][TN][128] fp32 on cluster rank 0
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::MAX_RING; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < C::NACC; ++b) { mbar_init(&accf_bar[b], 1); mbar_init(&acce_bar[b], 128); }
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(&tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  pdl_launch();
+
+  const int sp = (int)f8_cluster_ctarank();
+  const int tile = (int)blockIdx.x / S;
+  const int n_nt = (a.N + 127) / 128;
+  const int item = tile / n_nt, nt = tile % n_nt;
+  const int row0 = item * TN, nrows = min(TN, a.rows_total - row0);
+  const int nkb_all = (a.K + 127) / 128;
+  const int kb0 = (int)(((long long)nkb_all * sp) / S), kb1 = (int)(((long long)nkb_all * (sp + 1)) / S);
+  volatile int* abortp = &abort_flag;
+
+  float acc[TN];
+#pragma unroll
+  for (int j = 0; j < TN; ++j) acc[j] = 0.f;
+  const int q4 = warp & 3, et = q4 * 32 + lane;
+
+  if (warp == 0) {
+    // ---- producer: weight tiles first (static data), then wait for the previous kernel, then activation tiles
+    const int npre = min(ring, kb1 - kb0);
+    if (lane == 0)
+      for (int i = 0; i < npre; ++i) {
+        mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+        tma_load_3d(smem + i * C::STAGE_BYTES, a.tmA, &full_bar[i], (kb0 + i) * 128, nt * 128, 0);
+      }
+    pdl_wait();
+    for (int kb = kb0, it = 0; kb < kb1 && !*abortp; ++kb, ++it) {
+      const int s = it % ring;
+      if (it >= ring) {
+        if (!mbar_wait_bounded(&empty_bar[s], ((it / ring) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, (int)blockIdx.x); break; }
+        if (lane == 0) {
+          mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+          tma_load_3d(smem + s * C::STAGE_BYTES, a.tmA, &full_bar[s], kb * 128, nt * 128, 0);
+        }
+      }
+      if (lane == 0) tma_load_3d(smem + s * C::STAGE_BYTES + C::A_BYTES, a.tmB, &full_bar[s], kb * 128, row0, 0);
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: one fresh accumulator buffer per stage (= per scale block)
+    pdl_wait();
+    if (lane == 0) {
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // E4M3 x E4M3 -> fp32
+      for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+        const int s = it % ring, b = it % C::NACC;
+        if (!mbar_wait_bounded(&acce_bar[b], ((it / C::NACC) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, (int)blockIdx.x); break; }
+        if (!mbar_wait_bounded(&full_bar[s], (it / ring) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, (int)blockIdx.x); break; }
+        tc_fence_after();
+        const uint32_t st = smem_base + s * C::STAGE_BYTES;
+        const uint64_t adesc = umma_desc_sw128(st), bdesc = umma_desc_sw128(st + C::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc_mma_f8(tmem + b * TN, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+        tc_commit(&empty_bar[s]);
+        tc_commit(&accf_bar[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---- epilogue warps: scaled accumulation of every finished stage into registers
+    pdl_wait();
+    const uint32_t tbase = tmem + ((uint32_t)(q4 * 32) << 16);
+    bool ok = true;
+    for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+      const int b = it % C::NACC;
+      const float swv = a.sw[(size_t)nt * nkb_all + kb];
+      float sav[(TN + 15) / 16];                 // lane j (< 16) of chunk c holds the scale of token c * 16 + j
+#pragma unroll
+      for (int c = 0; c < (TN + 15) / 16; ++c) {
+        const int tcol = c * 16 + (lane & 15);
+        sav[c] = (tcol < nrows) ? a.sa[(size_t)(row0 + tcol) * nkb_all + kb] * swv : 0.f;
+      }
+      ok = mbar_wait_bounded(&accf_bar[b], (it / C::NACC) & 1, abortp);
+      ok = __all_sync(0xffffffffu, ok);          // tensor-memory loads must stay warp-uniform
+      if (!ok) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, (int)blockIdx.x); break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < (TN + 15) / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld_x16(tbase + b * TN + c * 16, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[c * 16 + j] += __uint_as_float(r[j]) * __shfl_sync(0xffffffffu, sav[c], j);
+      }
+      tc_fence_before();
+      mbar_arrive(&acce_bar[b]);
+    }
+    if (S > 1 && sp != 0) {
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(staging)), "r"(0));
+      remote += (uint32_t)(sp - 1) * (128 * TN * 4);
+#pragma unroll
+      for (int j = 0; j < TN; ++j)
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(j * 128 + et) * 4), "f"(acc[j]) : "memory");
+    }
+  }
+  __syncwarp();
+  if (S > 1) f8_cluster_sync();              // every thread of every CTA of the cluster, exactly once
+  if (warp >= 2 && sp == 0) {
+    const int n = nt * 128 + et;
+    if (n < a.N) {
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        if (j < nrows) {
+          float v = acc[j];
+          for (int p = 1; p < S; ++p) v += staging[(size_t)(p - 1) * (128 * TN) + j * 128 + et];
+          const size_t o = (size_t)(row0 + j) * a.ldy + n;
+          if (a.epi == F8_EPI_F32) ((float*)a.Y)[o] = v;
+          else {
+            if (a.epi == F8_EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
+            ((bf16*)a.Y)[o] = __float2bfloat16(v);
+          }
+        }
+      }
+    }
+  }
+  if (*abortp && warp == 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+template <int TN>
+static int fp8_launch(const Fp8Args& a, int grid, cudaStream_t stream) {
+  using C = Fp8Cfg<TN>;
+  auto kern = fp8_linear_kernel<TN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(fp8_linear)");
+    attr_set[dev & 63] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = C::SMEM_BYTES; cfg.stream = stream;
+  cudaLaunchAttribute at[2];
+  int n_at = 0;
+  if (a.splits > 1) {
+    at[n_at].id = cudaLaunchAttributeClusterDimension;
+    at[n_at].val.clusterDim.x = a.splits; at[n_at].val.clusterDim.y = 1; at[n_at].val.clusterDim.z = 1;
+    ++n_at;
+  }
+  if (ca_pdl_enabled(CA_PDL_CLASS)) {
+    at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n_at].val.programmaticStreamSerializationAllowed = 1;
+    ++n_at;
+  }
+  cfg.attrs = at; cfg.numAttrs = n_at;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) return ca_cuda(e, "fp8_linear launch");
+  return CA_OK;
+}
+
+extern "C" int cuteafd_fp8_linear(int tn, const void* tmA, const void* tmB, const float* sw, const float* sa, void* Y, const void* R,
+                                  int ldy, int rows_total, int N, int K, int epi, int splits, int* status, cudaStream_t stream) {
+  CA_REQUIRE(tmA && tmB && sw && sa && Y, "fp8_linear: null operand");
+  CA_REQUIRE(K % 16 == 0, "fp8_linear: K must be a multiple of 16 (K=%d)", K);
+  CA_REQUIRE(epi == F8_EPI_BF16 || epi == F8_EPI_BF16_RESIDUAL || epi == F8_EPI_F32, "fp8_linear: bad epilogue %d", epi);
+  CA_REQUIRE(epi != F8_EPI_BF16_RESIDUAL || R, "fp8_linear: residual epilogue needs R");
+  if (splits < 1) splits = 1;
+  CA_REQUIRE(splits == 1 || ((splits == 2 || splits == 4 || (splits == 8 && tn == 16)) && tn <= 32),
+             "fp8_linear: split-K is 2/4(/8)-way for token tiles of 16 or 32 rows");
+  if (rows_total <= 0 || N <= 0) return CA_OK;
+  Fp8Args a;
+  a.tmA = (const CUtensorMap*)tmA; a.tmB = (const CUtensorMap*)tmB; a.sw = sw; a.sa = sa; a.Y = Y; a.R = (const bf16*)R; a.status = status;
+  a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits;
+  const int grid = ((rows_total + tn - 1) / tn) * ((N + 127) / 128) * splits;
+  switch (tn) {
+    case 16: return fp8_launch<16>(a, grid, stream);
+    case 32: return fp8_launch<32>(a, grid, stream);
+    case 64: return fp8_launch<64>(a, grid, stream);
+    case 128: return fp8_launch<128>(a, grid, stream);
+    default: return ca_fail(CA_ERR_ARG, "fp8_linear: unsupported token tile %d", tn);
+  }
+}
+
+// ---------------------------------------------------------------- activation quantisation: E4M3 + fp32 scale / 128
+// One warp per (row, 128-channel group): scale = max(amax, 1e-4) / 448, q = e4m3(x / scale).
+__global__ void act_quant_fp8_block128_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ sa, int rows, int K,
+                                              int ldx, int nkb) {
+  pdl_launch(); pdl_wait();
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long long)rows * nkb) return;
+  const int r = (int)(w / nkb), g = (int)(w % nkb);
+  const int k0 = g * 128 + lane * 4;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (k0 < K) {
+    const uint2 raw = *(const uint2*)(x + (size_t)r * ldx + k0);
+    const bf16* e = (const bf16*)&raw;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(e[j]);
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-4f) / 448.f;
+  if (k0 < K) {
+    uint32_t pk = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pk |= (uint32_t)float_to_e4m3(v[j] / scale) << (8 * j);
+    *(uint32_t*)(q + (size_t)r * K + k0) = pk;
+  }
+  if (lane == 0) sa[(size_t)r * nkb + g] = scale;
+}
+
+extern "C" int cuteafd_act_quant_fp8_block128(const void* x, void* q, float* sa, int rows, int K, int ldx, cudaStream_t s) {
+  CA_REQUIRE(K % 4 == 0 && ldx % 4 == 0, "act_quant_fp8_block128: K must be a multiple of 4");
+  if (rows <= 0) return CA_OK;
+  const int nkb = (K + 127) / 128;
+  const long long warps = (long long)rows * nkb;
+  CA_LAUNCH_PDL(act_quant_fp8_block128_kernel, (int)((warps * 32 + 255) / 256), 256, 0, s, (const bf16*)x, (uint8_t*)q, sa, rows, K, ldx, nkb);
+  return CA_OK;
+}

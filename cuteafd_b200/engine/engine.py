@@ -21,7 +21,7 @@ import torch
 from .. import ops
 from ..config import ModelSpec
 from ..models.weights import DeviceWeights, LayerWeights
-from ..ops import ActBuffer, KIND_BF16, pick_tn
+from ..ops import ActBuffer, FP4_KINDS, KIND_BF16, KIND_FP8B, pick_tn
 
 PAGE = 64
 
@@ -121,12 +121,15 @@ class Engine:
         # (never-written) slots hold finite values
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         if spec.attn.kind == "gqa":
-            self.kv = torch.zeros(spec.n_layers, n_pages * PAGE, 2, a.n_kv_heads, a.head_dim, dtype=torch.bfloat16, device=self.device)
+            # MTP draft layers keep their KV rows in extra layers of the same store (same pages, same slots)
+            self.kv = torch.zeros(spec.n_layers + len(weights.mtp), n_pages * PAGE, 2, a.n_kv_heads, a.head_dim, dtype=torch.bfloat16,
+                                  device=self.device)
             # head_dim 128 runs on the tcgen05 attention kernel (one TMA descriptor per layer's K/V store)
             self.kv_tmaps = ops.encode_kv_tmaps(self.kv) if a.head_dim == 128 and 128 % (a.n_heads // a.n_kv_heads) == 0 else None
         else:
             self._alloc_attention_state()
         self.lanes: dict[int, Lane] = {}
+        self.mtp_lanes: dict[int, Lane] = {}
         self.graphs: dict = {}
         self.graph_captures = 0
         self._meta_cap = 0
@@ -187,7 +190,7 @@ class Engine:
         (2, 4 or 8 CTAs reduce through distributed shared memory): the largest power of two that still fits one wave
         and leaves every CTA at least two pipeline stages of K."""
         tiles = -(-N // 128) * -(-T // tn)
-        nkb = K // (64 if kind == KIND_BF16 else 256)
+        nkb = K // (64 if kind == KIND_BF16 else (128 if kind == KIND_FP8B else 256))
         if tiles >= self.sm_count or nkb < 4:
             return 1
         if tn <= 32:
@@ -221,10 +224,11 @@ class Engine:
         if self._pre_normed:
             self._pre_normed = False
             return L.xq
-        if L.xq.kind == KIND_BF16:
-            ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, self.spec.rms_eps, rows=T)
-        else:
+        if L.xq.kind in FP4_KINDS:
             ops.add_rmsnorm(L.x, None, lw.attn_norm, None, self.spec.rms_eps, rows=T, quant=L.xq, inv_gs=self._attn_in_gs(lw))
+        else:
+            ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, self.spec.rms_eps, rows=T)
+            self._quant(L.xn, L.xq, T, None)              # FP8 operands: separate quantiser (no-op for bf16)
         self.launches_per_step += 1
         return L.xq
 
@@ -235,9 +239,11 @@ class Engine:
         if nxt is None:
             ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k)
             return
-        fp4 = L.xq.kind != KIND_BF16
+        fp4 = L.xq.kind in FP4_KINDS
         ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, norm_w=nxt.attn_norm, eps=self.spec.rms_eps, xn=None if fp4 else L.xn,
                         quant=L.xq if fp4 else None, inv_gs=self._attn_in_gs(nxt) if fp4 else None)
+        if not fp4:
+            self._quant(L.xn, L.xq, T, None)              # FP8 operands: separate quantiser (no-op for bf16)
         self._pre_normed = True
 
     def _attention_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
@@ -270,7 +276,17 @@ class Engine:
         """Shared expert / dense FFN: out = residual + down(silu(gate x) * up x)."""
         s1, s_act = L.ffn_buf(self, lw.ws_gate.N)
         xq = self._quant(L.xn, L.xq, T, lw.ws_gate.inv_act_gs)
-        self._dense(lw.ws_gate, xq, s1, T, w_up=lw.ws_up)
+        if lw.ws_gate.kind == KIND_FP8B:      # no fused SwiGLU epilogue in the FP8 kernel: two GEMMs + silu(g) * u
+            key = ("up", lw.ws_gate.N)
+            if key not in L.ffn_bufs:
+                L.ffn_bufs[key] = torch.zeros_like(s1)
+            s_up = L.ffn_bufs[key]
+            self._dense(lw.ws_gate, xq, s1, T)
+            self._dense(lw.ws_up, xq, s_up, T)
+            ops.silu_mul(s1[:T], s_up[:T], s1[:T])
+            self.launches_per_step += 1
+        else:
+            self._dense(lw.ws_gate, xq, s1, T, w_up=lw.ws_up)
         self._quant(s1, s_act, T, lw.ws_down.inv_act_gs)
         self._dense(lw.ws_down, s_act, out, T, residual=residual)
 
@@ -320,14 +336,7 @@ class Engine:
         """Launch one step on the current stream.  Inputs come from the device meta block."""
         spec, T = self.spec, sh.T
         L = self.lane(T)
-        a = spec.attn
-        if sh.attn_splits > 1:
-            need = sh.attn_splits * T * a.n_heads
-            if getattr(self, "part_o", None) is None or self.part_o.numel() < need * a.head_dim:
-                self.part_o = torch.empty(need * a.head_dim, dtype=torch.float32, device=self.device)
-                self.part_ml = torch.empty(need * 2, dtype=torch.float32, device=self.device)
-        elif getattr(self, "part_o", None) is None:
-            self.part_o = self.part_ml = None
+        self._ensure_attn_scratch(sh)
         self.launches_per_step = 0
         self._pre_normed = False
         ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
@@ -343,6 +352,50 @@ class Engine:
             ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=sh.n_logits, status=self.status)
             ops.argmax_rows(L.logits, L.next_tok, rows=sh.n_logits, status=L.tok_status)
             self.launches_per_step += 4
+        return L
+
+    def _ensure_attn_scratch(self, sh: StepShape):
+        a, T = self.spec.attn, sh.T
+        if sh.attn_splits > 1:
+            need = sh.attn_splits * T * a.n_heads
+            if getattr(self, "part_o", None) is None or self.part_o.numel() < need * a.head_dim:
+                self.part_o = torch.empty(need * a.head_dim, dtype=torch.float32, device=self.device)
+                self.part_ml = torch.empty(need * 2, dtype=torch.float32, device=self.device)
+        elif getattr(self, "part_o", None) is None:
+            self.part_o = self.part_ml = None
+
+    # ------------------------------------------------------------------ MTP draft module
+    def mtp_forward(self, depth: int, sh: StepShape, prev_hidden: torch.Tensor) -> Lane:
+        """One step of MTP module `depth` over the rows described by the device meta block (tokens, positions, KV
+        slots, lengths - as for `forward`, with the draft layer's own row numbering).  prev_hidden [T, H] bf16 is the
+        hidden state paired with each row.  Returns the draft lane: `.x` holds the module's output hidden of every
+        row, `.next_tok` the arg-max token of the rows listed in md["logit_rows"].
+        (Reference: the MTP head of the DeepSeek families, families/deepseek_v4/engine.rs:2047-2133; oracle
+        `RefModel.mtp_forward`.)"""
+        spec, T, H = self.spec, sh.T, self.spec.hidden
+        enorm, hnorm, eh_proj, lw, norm = self.weights.mtp[depth]
+        cap = next(c for c in (16, 64, 256, 1024, 4096, 16384) if T <= c)
+        if cap not in self.mtp_lanes:
+            L = Lane(self, cap)
+            L.cat = torch.zeros(cap, 2 * H, dtype=torch.bfloat16, device=self.device)
+            L.cat_act = ActBuffer.wrap_bf16(L.cat, L.tn)
+            self.mtp_lanes[cap] = L
+        L = self.mtp_lanes[cap]
+        self._ensure_attn_scratch(sh)
+        ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.xl, self.status)
+        ops.add_rmsnorm(L.xl, None, enorm, L.xln, spec.rms_eps, rows=T)
+        L.cat[:T, :H].copy_(L.xln[:T])
+        ops.add_rmsnorm(prev_hidden.contiguous(), None, hnorm, L.xln, spec.rms_eps, rows=T)
+        L.cat[:T, H:].copy_(L.xln[:T])
+        ops.tc_linear(eh_proj, L.cat_act, L.x, rows=T, status=self.status)
+        self._pre_normed, self._next_lw = False, None
+        self._attention_layer(spec.n_layers + depth, lw, L, sh)
+        self._moe_layer(lw, L, T)
+        if sh.n_logits:
+            ops.gather_rows(L.x, self.md["logit_rows"], None, L.xl, sh.n_logits)
+            ops.add_rmsnorm(L.xl, None, norm, L.xln, spec.rms_eps, rows=sh.n_logits)
+            ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=sh.n_logits, status=self.status)
+            ops.argmax_rows(L.logits, L.next_tok, rows=sh.n_logits, status=L.tok_status)
         return L
 
     # ------------------------------------------------------------------ CUDA graphs

@@ -125,9 +125,10 @@ class MlaEngine(Engine):
         spec = self.spec
         self.heads_local = self.weights.layers[0].mla.w_uv.G
         # latent cache: one row of 576 bf16 per token and layer (zero-filled: masked slots must hold finite values)
-        self.kv = torch.zeros(spec.n_layers, self.n_pages * PAGE, DQK, dtype=torch.bfloat16, device=self.device)
-        host = torch.zeros(spec.n_layers, 128, dtype=torch.uint8)
-        for l in range(spec.n_layers):
+        n_kv = spec.n_layers + len(self.weights.mtp)          # MTP draft layers keep their rows in extra layers
+        self.kv = torch.zeros(n_kv, self.n_pages * PAGE, DQK, dtype=torch.bfloat16, device=self.device)
+        host = torch.zeros(n_kv, 128, dtype=torch.uint8)
+        for l in range(n_kv):
             call("cuteafd_tmap_encode_latent", host[l].data_ptr(), self.kv[l].data_ptr(), self.n_pages * PAGE)
         self.kv_tmaps = host.to(self.device)
         self.mla_bufs: dict = {}

@@ -25,7 +25,7 @@ from ..ops import TcWeight, KIND_BF16, KIND_BY_NAME
 
 
 def _dense_kind(spec: ModelSpec) -> str:
-    return {"bf16": "bf16", "nvfp4": "nvfp4", "mxfp4": "mxfp4"}.get(spec.quant.dense, "bf16")
+    return {"bf16": "bf16", "nvfp4": "nvfp4", "mxfp4": "mxfp4", "fp8_block128": "fp8_block128"}.get(spec.quant.dense, "bf16")
 
 
 def _expert_kind(spec: ModelSpec) -> str:

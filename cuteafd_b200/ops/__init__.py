@@ -14,8 +14,9 @@ import torch
 from . import native
 from .native import call, ptr, stream
 
-KIND_BF16, KIND_NVFP4, KIND_MXFP4 = 0, 1, 2
-KIND_BY_NAME = {"bf16": KIND_BF16, "nvfp4": KIND_NVFP4, "mxfp4": KIND_MXFP4}
+KIND_BF16, KIND_NVFP4, KIND_MXFP4, KIND_FP8B = 0, 1, 2, 3      # FP8B: E4M3 with fp32 scales per 128 x 128 (weights) / 1 x 128 (activations)
+KIND_BY_NAME = {"bf16": KIND_BF16, "nvfp4": KIND_NVFP4, "mxfp4": KIND_MXFP4, "fp8_block128": KIND_FP8B}
+FP4_KINDS = (KIND_NVFP4, KIND_MXFP4)
 EPI_BF16, EPI_BF16_RESIDUAL, EPI_F32 = 0, 1, 3
 SCORING = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}
 
@@ -93,6 +94,10 @@ class TcWeight:
         if kind == KIND_BF16:
             data = w.to(torch.bfloat16).to(device).contiguous()
             return TcWeight(kind, G, N, K, data, encode_tmap(data, 128))
+        if kind == KIND_FP8B:
+            qs = [quant.fp8_block_quantize(w[g]) for g in range(G)]
+            data = torch.stack([q for q, _ in qs]).to(device).contiguous()
+            return TcWeight(kind, G, N, K, data, encode_tmap(data, 128), torch.stack([s for _, s in qs]).to(device).contiguous())
         packs, sfs, alphas = [], [], []
         for g in range(G):
             if kind == KIND_NVFP4:
@@ -120,6 +125,12 @@ class TcWeight:
         if kind == KIND_BF16:
             data = cut(torch.empty(G, N, K, dtype=torch.bfloat16, device=device).normal_(0, std, generator=gen))
             return TcWeight(kind, hi - lo, N, K, data, encode_tmap(data, 128))
+        if kind == KIND_FP8B:    # random sign and magnitude codes below the NaN pattern; |w| ~ std with one common block scale
+            mag = torch.randint(0, 0x78, (G, N, K), dtype=torch.uint8, device=device, generator=gen)
+            sign = torch.randint(0, 2, (G, N, K), dtype=torch.uint8, device=device, generator=gen) << 7
+            data = cut(mag | sign)
+            sw = torch.full((hi - lo, -(-N // 128), -(-K // 128)), std / 60.0, dtype=torch.float32, device=device)
+            return TcWeight(kind, hi - lo, N, K, data, encode_tmap(data, 128), sw)
         data = cut(torch.randint(0, 256, (G, N, K // 2), dtype=torch.uint8, device=device, generator=gen))
         vec = 16 if kind == KIND_NVFP4 else 32
         nsf = (-(-N // 128) * 128) * (-(-K // 256) * (256 // vec))
@@ -142,6 +153,8 @@ class TcWeight:
         from ..ref import quant
         if self.kind == KIND_BF16:
             return self.data.float().cpu()
+        if self.kind == KIND_FP8B:
+            return torch.stack([quant.fp8_block_dequantize(self.data[g].cpu(), self.sf[g].cpu()) for g in range(self.G)])
         vec = 16 if self.kind == KIND_NVFP4 else 32
         out = []
         for g in range(self.G):
@@ -171,6 +184,9 @@ class ActBuffer:
         if kind == KIND_BF16:
             data = torch.zeros(rows, K, dtype=torch.bfloat16, device=device)
             return ActBuffer(kind, rows, K, tn, data, encode_tmap(data, tn))
+        if kind == KIND_FP8B:    # E4M3 bytes + one fp32 scale per row and 128 channels
+            data = torch.zeros(rows, K, dtype=torch.uint8, device=device)
+            return ActBuffer(kind, rows, K, tn, data, encode_tmap(data, tn), torch.zeros(rows, -(-K // 128), dtype=torch.float32, device=device))
         vec = 16 if kind == KIND_NVFP4 else 32
         data = torch.zeros(rows, K // 2, dtype=torch.uint8, device=device)
         sf = torch.zeros(rows, -(-K // 256) * (256 // vec), dtype=torch.uint8, device=device)   # padded to whole stages
@@ -206,11 +222,15 @@ def _splitk_scratch(device, n_float: int, n_cnt: int):
 def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor | None, *, rows: int | None = None, w_up: TcWeight | None = None,
               residual: torch.Tensor | None = None, tiles: torch.Tensor | None = None, n_tiles: torch.Tensor | None = None,
               max_tiles: int = 0, splits: int = 1, status: torch.Tensor | None = None, max_ctas: int = 0,
-              quant_out: ActBuffer | None = None, inv_gs_out: torch.Tensor | None = None) -> torch.Tensor | None:
+              quant_out: ActBuffer | None = None, inv_gs_out: torch.Tensor | None = None, peer: dict | None = None) -> torch.Tensor | None:
     """y[rows, N] = x[rows, K] @ w[g]^T (per tile's expert g when `tiles` is given).  `w_up` switches on the fused
     SwiGLU epilogue (y = silu(x w^T) * (x w_up^T)).  y is bf16 (optionally + residual) or fp32.  `quant_out` (an FP4
     activation buffer of the operands' kind, K = N) also receives the output quantised for the GEMM that follows
-    (`inv_gs_out`: that GEMM's activation scale, NVFP4); y may then be None."""
+    (`inv_gs_out`: that GEMM's activation scale, NVFP4); y may then be None.
+    `peer` fuses the hand-off to other GPUs into the epilogue: {"y": [device addresses of 1-2 peers' bf16 buffers], "ld": row
+    pitch in elements, "row_map": int32 tensor or None (row r lands in row_map[r]), "flags": [peer flag addresses],
+    "ctl": control block tensor, "done": zeroed uint32 counter tensor}; the flags are released with the step number
+    once the whole output has been stored (y may be None when only the peers need the result)."""
     rows = x.rows if rows is None else rows
     if w.kind != x.kind or w.K != x.K:
         raise ValueError("tc_linear: operand kinds / K differ")
@@ -218,6 +238,14 @@ def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor | None, *, rows: int | 
         epi = EPI_BF16
     else:
         epi = EPI_F32 if y.dtype == torch.float32 else (EPI_BF16_RESIDUAL if residual is not None else EPI_BF16)
+    if w.kind == KIND_FP8B:
+        if w_up is not None or tiles is not None or quant_out is not None or w.G != 1:
+            raise ValueError("tc_linear: the FP8 block-scaled kernel is dense only (no SwiGLU / grouped / FP4 output)")
+        if splits not in (1, 2, 4, 8) or (splits > 1 and x.tn > 32) or (splits == 8 and x.tn != 16):
+            splits = 1
+        call("cuteafd_fp8_linear", x.tn, ptr(w.tmap), ptr(x.tmap), ptr(w.sf), ptr(x.sf), ptr(y), ptr(residual), y.stride(0), rows, w.N, w.K,
+             epi, splits, ptr(status), stream())
+        return y
     ws = cnt = None
     if splits > 1:
         n_items = -(-rows // x.tn)
@@ -226,10 +254,59 @@ def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor | None, *, rows: int | 
         if quant_out.kind != w.kind or quant_out.K != w.N:
             raise ValueError("tc_linear: quant_out must be an FP4 buffer of the operands' kind with K = N")
         call("cuteafd_tc_linear_fp4_out", ptr(quant_out.data), ptr(quant_out.sf), quant_out.sf.shape[1], ptr(inv_gs_out))
+    if peer is not None:
+        ys, fl = list(peer["y"]), list(peer["flags"])
+        call("cuteafd_tc_linear_peer_out", ys[0], ys[1] if len(ys) > 1 else None, len(ys), peer["ld"], ptr(peer.get("row_map")),
+             fl[0], fl[1] if len(fl) > 1 else None, ptr(peer["ctl"]), ptr(peer["done"]))
     call("cuteafd_tc_linear", w.kind, 1 if w_up is not None else 0, x.tn, ptr(w.tmap), ptr(w_up.tmap) if w_up else None,
          ptr(x.tmap), ptr(w.sf_ptrs), ptr(w_up.sf_ptrs) if w_up else None, ptr(x.sf), x.sf.shape[1] if x.sf is not None else 0,
          ptr(w.alpha), ptr(w_up.alpha) if w_up else None, ptr(tiles), ptr(n_tiles), max_tiles, ptr(y), ptr(residual),
          y.stride(0) if y is not None else 0, rows, w.N, w.K, epi, splits, ptr(ws), ptr(cnt), ptr(status), max_ctas, stream())
+    return y
+
+
+# ------------------------------------------------------------------ EXL3 (trellis) weights
+@dataclass
+class Exl3Weight:
+    """One EXL3 linear as shipped: trellis uint16 [K/16, N/16, 16*bits], suh fp16 [K], svh fp16 [N] (y = x @ W)."""
+    trellis: torch.Tensor
+    suh: torch.Tensor
+    svh: torch.Tensor
+
+    @property
+    def K(self) -> int:
+        return self.trellis.shape[0] * 16
+
+    @property
+    def N(self) -> int:
+        return self.trellis.shape[1] * 16
+
+    @property
+    def bits(self) -> int:
+        return self.trellis.shape[2] // 16
+
+
+_EXL3_WS: dict = {}
+
+
+def exl3_linear(w: Exl3Weight, x: torch.Tensor, y: torch.Tensor, *, rows: int | None = None, residual: torch.Tensor | None = None,
+                k_splits: int = 0) -> torch.Tensor:
+    """y[rows, N] = x[rows, K] @ W(+ residual) with W decoded from the trellis inside the GEMM (decode-sized batches)."""
+    _chk(x, torch.bfloat16, "x")
+    rows = x.shape[0] if rows is None else rows
+    K, N = w.K, w.N
+    if not k_splits:      # enough warps to fill the machine: N/16 strips x splits ~ 4 per SM sub-partition
+        k_splits = max(1, min(K // 256, -(-148 * 16 // (N // 16))))
+    pad = -(-rows // 16) * 16
+    key = str(x.device)
+    xr, part = _EXL3_WS.get(key, (None, None))
+    if xr is None or xr.numel() < pad * K:
+        xr = torch.empty(max(pad * K, 1 << 20), dtype=torch.float16, device=x.device)
+    if part is None or part.numel() < k_splits * pad * N:
+        part = torch.empty(max(k_splits * pad * N, 1 << 22), dtype=torch.float32, device=x.device)
+    _EXL3_WS[key] = (xr, part)
+    call("cuteafd_exl3_linear", ptr(x), ptr(w.trellis), ptr(w.suh), ptr(w.svh), ptr(residual), ptr(y), ptr(xr), ptr(part), rows, K, N, w.bits,
+         k_splits, y.stride(0), stream())
     return y
 
 
@@ -246,7 +323,7 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, y:
     rows are also written quantised in the same launch (y may then be None)."""
     _chk(x, torch.bfloat16, "x"); _chk(w, torch.float32, "w")
     n = x.shape[0] if rows is None else rows
-    if quant is not None and quant.kind != KIND_BF16:
+    if quant is not None and quant.kind in FP4_KINDS:
         call("cuteafd_add_rmsnorm_quant", ptr(x), ptr(delta), ptr(w), ptr(y), n, x.shape[1], eps, ptr(quant.data), ptr(quant.sf),
              quant.sf.shape[1], ptr(inv_gs), 2 if quant.kind == KIND_MXFP4 else 1, stream())
     else:
@@ -263,6 +340,11 @@ def qk_norm_rope_kvwrite(qkv, positions, slot_map, q_norm, k_norm, kv_cache, T, 
 def quant_fp4_rows(x: torch.Tensor, out: ActBuffer, *, src_rows: torch.Tensor | None = None, n_rows_dev: torch.Tensor | None = None,
                    rows: int | None = None, inv_gs: torch.Tensor | None = None):
     _chk(x, torch.bfloat16, "x")
+    if out.kind == KIND_FP8B:
+        if src_rows is not None or n_rows_dev is not None:
+            raise ValueError("FP8 activation quantisation has no gather form")
+        call("cuteafd_act_quant_fp8_block128", ptr(x), ptr(out.data), ptr(out.sf), out.rows if rows is None else rows, out.K, x.stride(0), stream())
+        return out
     call("cuteafd_quant_fp4_rows", 1 if out.kind == KIND_MXFP4 else 0, ptr(x), ptr(src_rows), ptr(n_rows_dev), ptr(out.data),
          ptr(out.sf), out.rows if rows is None else rows, out.K, x.stride(0), out.sf.shape[1], ptr(inv_gs), stream())
     return out
@@ -315,7 +397,7 @@ def moe_combine(y, slot_row, wts, shared, residual, out, T, k, *, norm_w=None, e
     if norm_w is None:
         call("cuteafd_moe_combine", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, stream())
         return out
-    fp4 = quant is not None and quant.kind != KIND_BF16
+    fp4 = quant is not None and quant.kind in FP4_KINDS
     call("cuteafd_moe_combine_norm", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, ptr(norm_w),
          eps, ptr(xn), ptr(quant.data) if fp4 else None, ptr(quant.sf) if fp4 else None, quant.sf.shape[1] if fp4 else 0,
          ptr(inv_gs) if fp4 else None, (2 if quant.kind == KIND_MXFP4 else 1) if fp4 else 0, stream())
@@ -348,7 +430,7 @@ def paged_attention_tc(q, kv_map, page_table, kv_len, q_start, q_len, out, *, T,
     """Tensor-core (tcgen05) paged attention for head_dim 128; `kv_map` is one row of `encode_kv_tmaps`.
     `quant` (an FP4 activation buffer): with split-KV the merge also writes the output rows quantised for the output
     projection.  Returns True when that happened (False: the caller quantises `out` itself)."""
-    fused = quant is not None and quant.kind != KIND_BF16 and n_splits > 1 and (Hq * 128) % 256 == 0
+    fused = quant is not None and quant.kind in FP4_KINDS and n_splits > 1 and (Hq * 128) % 256 == 0
     call("cuteafd_paged_attention_tc", ptr(q), ptr(kv_map), ptr(page_table), ptr(kv_len), ptr(q_start), ptr(q_len), ptr(sink),
          ptr(out), ptr(part_o), ptr(part_ml), T, n_seq, max_q_len, q_stride, Hq, Hkv, page_table.shape[1], n_splits, window,
          float(scale if scale is not None else 128 ** -0.5), ptr(status), ptr(quant.data) if fused else None,

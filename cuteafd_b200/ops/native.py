@@ -21,6 +21,10 @@ _PROTOS = {
     "cuteafd_abi_version": [],
     "cuteafd_set_pdl": [I],
     "cuteafd_tc_trace": [P, I],
+    "cuteafd_exl3_linear": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "cuteafd_fp8_linear": [I, P, P, P, P, P, P, I, I, I, I, I, I, P, P],
+    "cuteafd_act_quant_fp8_block128": [P, P, P, I, I, I, P],
+    "cuteafd_tc_linear_peer_out": [P, P, I, I, P, P, P, P, P],
     "cuteafd_arm_flag_wait": [P, I, I, P, C.c_ulonglong, P],
     "cuteafd_tc_linear_fp4_out": [P, P, I, P],
     "cuteafd_device_info": [P, P, P, P, P],

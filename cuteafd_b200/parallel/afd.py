@@ -24,6 +24,7 @@ Reference: the coordinator/Spark split (families/deepseek_v4/engine.rs:1036-1191
 from __future__ import annotations
 
 import dataclasses
+import os
 import time
 
 import torch
@@ -37,6 +38,9 @@ from . import peer_ops
 from .symm import SymmetricBlock
 
 PH_DISPATCH, PH_COMBINE, PH_TP = 0, 1, 2
+# GEMM epilogues store straight into peer memory (output projection -> TP partner, expert FC2 -> attention ranks) and
+# publish the flags themselves; CUTEAFD_FUSED_PEER=0 falls back to separate push kernels (for A/B measurements).
+FUSED_PEER = os.environ.get("CUTEAFD_FUSED_PEER", "1") != "0"
 
 
 def local_attention_spec(spec: ModelSpec, tp: int) -> ModelSpec:
@@ -129,6 +133,20 @@ class AttnRankEngine(Engine):
     def _attn_out(self, li, lw, oq, L, T):
         if self.tp == 1:
             return super()._attn_out(li, lw, oq, L, T)
+        if self.comm == "p2p" and FUSED_PEER and lw.wo.kind != ops.KIND_FP8B:
+            # the projection's epilogue writes my partial sum locally AND into the partner's landing buffer, then raises
+            # its flag: GEMM -> exchange in one kernel; the wait + ordered add follows
+            H, peer, buf = self.full_spec.hidden, self.group_ranks[1 - self.tp_rank], li & 1
+            splits = self._splits(lw.wo.N, lw.wo.K, T, oq.tn, lw.wo.kind)
+            ops.tc_linear(lw.wo, oq, self.part, rows=T, splits=splits, status=self.status,
+                          peer={"y": [self.block.peer_ptr(peer, "tp_recv", buf * self.t_max * H * 2)], "ld": H, "row_map": None,
+                                "flags": [self.block.peer_ptr(peer, "flags", flag_offset(self.full_spec, PH_TP, li, self.tp_rank))],
+                                "ctl": self.ctl, "done": self.done[2:3]})
+            peer_ops.wait_add(self.part, self.tp_recv[buf], L.x, L.x, T * H, self.tp_rank,
+                              self.block.peer_ptr(self.rank, "flags", flag_offset(self.full_spec, PH_TP, li, 1 - self.tp_rank)),
+                              self.ctl, 0, self.status)
+            self.launches_per_step += 2
+            return
         self._dense(lw.wo, oq, self.part, T)              # partial sum over my heads, then the TP exchange
         self._tp_allreduce(li, self.part, L.x, T)
 
@@ -308,6 +326,17 @@ class ExpertRankWorker:
                               max_tiles=self.max_tiles, status=self.status)
                 if self.kind != KIND_BF16:
                     ops.quant_fp4_rows(self.h1, self.h1_q, n_rows_dev=self.n_rows, rows=rows, inv_gs=lw.w_down.inv_act_gs)
+            if FUSED_PEER:
+                # FC2's epilogue stores every output row straight into [token][slot] of the group's attention ranks and
+                # the last CTA raises their flags: grouped GEMM -> combine transfer in one kernel
+                ranks = dep.group_ranks(g)
+                ops.tc_linear(lw.w_down, self.h1_q, None, rows=rows, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
+                              status=self.status,
+                              peer={"y": [self.block.peer_ptr(r, "y_recv") for r in ranks], "ld": spec.hidden, "row_map": self.src_route,
+                                    "flags": [self.block.peer_ptr(r, "flags", flag_offset(spec, PH_COMBINE, li, self.ep_rank)) for r in ranks],
+                                    "ctl": self.ctl, "done": self.done[0:1]})
+                self.launches_per_step += 3
+                continue
             ops.tc_linear(lw.w_down, self.h1_q, self.y2, rows=rows, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
                           status=self.status)
             flag_tbl = self.block.ptr_table(dep.group_ranks(g), "flags", flag_offset(spec, PH_COMBINE, li, self.ep_rank))

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from cuteafd_b200 import ops
-from cuteafd_b200.ops import ActBuffer, TcWeight, KIND_BF16, KIND_NVFP4, KIND_MXFP4
+from cuteafd_b200.ops import ActBuffer, TcWeight, KIND_BF16, KIND_NVFP4, KIND_MXFP4, KIND_FP8B
 from cuteafd_b200.ref import ops as rops, quant, sampler
 
 pytestmark = pytest.mark.gpu
@@ -511,3 +511,58 @@ def test_router_select_pack_matches_two_kernels(T, E, k, e_lo, e_hi):
         assert torch.equal(a[key], b[key]), key
     assert torch.equal(a["src"][:n_rows], b["src"][:n_rows]) and torch.equal(a["route"][:n_rows], b["route"][:n_rows])
     assert torch.equal(a["tiles"][:n_tiles], b["tiles"][:n_tiles])
+
+
+# ------------------------------------------------------------------ FP8 with 128 x 128 / 1 x 128 fp32 block scales
+@pytest.mark.parametrize("T,N,K,splits", [(3, 128, 256, 1), (16, 384, 512, 2), (16, 256, 7168, 8), (70, 256, 1024, 1), (128, 130, 768, 1),
+                                          (30, 256, 2048, 4), (9, 1536, 7168, 8)])
+def test_fp8_block_linear(T, N, K, splits):
+    g = torch.Generator().manual_seed(T + N + K)
+    w = torch.randn(N, K, generator=g) * 0.05
+    x = torch.randn(T, K, generator=g) * 3
+    W = TcWeight.from_master(w, "fp8_block128", DEV)
+    tn = ops.pick_tn(T)
+    xb = x.to(torch.bfloat16).to(DEV).contiguous()
+    xq = ActBuffer.alloc(KIND_FP8B, T, K, tn, DEV)
+    ops.quant_fp4_rows(xb, xq)
+    y = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+    st = status_word()
+    ops.tc_linear(W, xq, y, splits=splits, status=st)
+    r = torch.randn(T, N, generator=g).to(torch.bfloat16).to(DEV)
+    y2 = r.clone()
+    ops.tc_linear(W, xq, y2, residual=y2, splits=splits, status=st)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    # exact reference: what the GPU quantiser wrote times the dequantised weights
+    xd = quant.e4m3_decode(xq.data.cpu()) * xq.sf.cpu().repeat_interleave(128, 1)[:, :K]
+    ref = xd @ W.dequantize()[0].T
+    assert rel_err(y.cpu(), ref) < 2e-3
+    assert rel_err(y2.float().cpu(), ref + r.float().cpu()) < 1e-2
+    # the GPU activation quantiser agrees with the oracle's recipe
+    qo, so = quant.act_quant_fp8_block(xb.float().cpu())
+    xo = quant.e4m3_decode(qo) * so.repeat_interleave(128, 1)[:, :K]
+    assert rel_err(xd, xo) < 1e-3
+
+
+# ------------------------------------------------------------------ EXL3 trellis dequant-GEMM
+@pytest.mark.parametrize("bits,T,K,N", [(4, 5, 256, 256), (3, 16, 512, 384), (2, 20, 384, 128), (5, 1, 256, 512)])
+def test_exl3_linear_matches_oracle(bits, T, K, N):
+    import numpy as np
+    from cuteafd_b200.ref import exl3
+    rng = np.random.default_rng(bits * 100 + T)
+    inner = rng.standard_normal((K, N)).astype(np.float32)
+    trellis = exl3.encode_tiles_greedy(inner, bits, seed=1)
+    suh = (rng.choice([-1.0, 1.0], K) * rng.uniform(0.5, 1.5, K)).astype(np.float16)
+    svh = (rng.choice([-1.0, 1.0], N) * rng.uniform(0.5, 1.5, N)).astype(np.float16)
+    W = exl3.dequantize(trellis, suh.astype(np.float64), svh.astype(np.float64))
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, K, generator=g)
+    r = torch.randn(T, N, generator=g).to(torch.bfloat16)
+    w = ops.Exl3Weight(torch.from_numpy(trellis.astype(np.int16)).view(torch.uint16).to(DEV).contiguous(),
+                       torch.from_numpy(suh).to(DEV), torch.from_numpy(svh).to(DEV))
+    assert (w.K, w.N, w.bits) == (K, N, bits)
+    y = torch.zeros(T, N, dtype=torch.bfloat16, device=DEV)
+    ops.exl3_linear(w, x.to(torch.bfloat16).to(DEV), y, residual=r.to(DEV))
+    torch.cuda.synchronize()
+    ref = bf16r(x).double() @ torch.from_numpy(W) + r.double()
+    assert rel_err(y.float().cpu(), ref.float()) < 1.5e-2
