@@ -50,8 +50,8 @@ struct TcArgs {
   // Fused hand-off to peer GPUs: the bf16 output tile is also stored straight into peers' memory over NVLink from
   // the epilogue (row r of this GEMM lands in row peer_row_map[r], or r), and once every CTA has finished, the last
   // one releases the peers' flags with the current step number - GEMM and transfer are one kernel, tile by tile.
-  void* peer_y[2];
-  uint32_t* peer_flags[2];
+  void* peer_y0; void* peer_y1;
+  uint32_t* peer_flag0; uint32_t* peer_flag1;
   const int* peer_row_map;
   uint32_t* peer_ctl;         // [0] abort word, [1] step number
   uint32_t* peer_done;        // arrival counter: zero on entry, left zero
@@ -123,17 +123,21 @@ __device__ __forceinline__ void peer_publish(const TcArgs& a, int warp, int lane
     if (prev == gridDim.x - 1) {
       __threadfence_system();
       const uint32_t step = a.peer_ctl[1];
-      for (int d = 0; d < a.n_peer; ++d) st_release_sys(a.peer_flags[d], step);
+      st_release_sys(a.peer_flag0, step);
+      if (a.n_peer > 1) st_release_sys(a.peer_flag1, step);
       *a.peer_done = 0;
     }
   }
 }
 __device__ __forceinline__ void peer_store(const TcArgs& a, int row, int n, bf16 v) {
   const size_t prow = a.peer_row_map ? (size_t)a.peer_row_map[row] : (size_t)row;
-  for (int d = 0; d < a.n_peer; ++d) ((bf16*)a.peer_y[d])[prow * a.peer_ld + n] = v;
+  ((bf16*)a.peer_y0)[prow * a.peer_ld + n] = v;
+  if (a.n_peer > 1) ((bf16*)a.peer_y1)[prow * a.peer_ld + n] = v;
 }
 
-template <int KIND, int TN, bool SWIGLU>
+// PEER instantiations carry the peer-store epilogue; the others are the plain local kernels (the extra code costs
+// ~1.5 us per launch even when switched off at run time, so it is compiled in only where it is used).
+template <int KIND, int TN, bool SWIGLU, bool PEER, bool QOUT>
 __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_kernel(const __grid_constant__ TcArgs a) {
   using C = TcCfg<KIND, TN, SWIGLU>;
   extern __shared__ uint8_t smem_raw[];
@@ -324,7 +328,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
         tmem_ld_x16(tbase + c0, r);
         if (SWIGLU) tmem_ld_x16(tbase + TN + c0, r2);
         tc_wait_ld();
-        if (KIND != KIND_BF16 && a.q_out) {
+        if (QOUT && KIND != KIND_BF16 && a.q_out) {
           // FP4 output for the next GEMM: this lane holds output feature n of 16 tokens; a quantisation block is 16
           // (NVFP4) or 32 (MXFP4) consecutive features = adjacent lanes, so amax and the nibble packing are shuffles.
           // Same arithmetic as the stand-alone quantiser on the bf16-rounded value.
@@ -378,7 +382,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
                 if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
                 const bf16 vb = __float2bfloat16(v);
                 if (a.Y) ((bf16*)a.Y)[o] = vb;
-                if (a.n_peer) peer_store(a, row0 + c, n, vb);
+                if (PEER && a.n_peer) peer_store(a, row0 + c, n, vb);
               }
             }
           }
@@ -425,7 +429,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
                   if (a.epi == EPI_BF16_RESIDUAL) r += __bfloat162float(a.R[o]);
                   const bf16 rb = __float2bfloat16(r);
                   if (a.Y) ((bf16*)a.Y)[o] = rb;
-                  if (a.n_peer) peer_store(a, row0 + c + j, n, rb);
+                  if (PEER && a.n_peer) peer_store(a, row0 + c + j, n, rb);
                 }
               }
             }
@@ -435,7 +439,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
         }
       }
     }
-    if (a.n_peer) peer_publish(a, warp, lane);
+    if (PEER && a.n_peer) peer_publish(a, warp, lane);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -449,10 +453,10 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
   if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-template <int KIND, int TN, bool SWIGLU>
-static int launch(const TcArgs& a, int grid, cudaStream_t stream) {
+template <int KIND, int TN, bool SWIGLU, bool PEER, bool QOUT>
+static int launch_p(const TcArgs& a, int grid, cudaStream_t stream) {
   using C = TcCfg<KIND, TN, SWIGLU>;
-  auto kern = tc_linear_kernel<KIND, TN, SWIGLU>;
+  auto kern = tc_linear_kernel<KIND, TN, SWIGLU, PEER, QOUT>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -463,6 +467,13 @@ static int launch(const TcArgs& a, int grid, cudaStream_t stream) {
   }
   CA_LAUNCH_PDL(kern, grid, 192, C::SMEM_BYTES, stream, a);
   return CA_OK;
+}
+
+template <int KIND, int TN, bool SWIGLU>
+static int launch(const TcArgs& a, int grid, cudaStream_t stream) {
+  if constexpr (!SWIGLU) { if (a.n_peer) return launch_p<KIND, TN, false, true, false>(a, grid, stream); }
+  if constexpr (SWIGLU && KIND != KIND_BF16) { if (a.q_out) return launch_p<KIND, TN, true, false, true>(a, grid, stream); }
+  return launch_p<KIND, TN, SWIGLU, false, false>(a, grid, stream);
 }
 
 template <int KIND, bool SWIGLU>
@@ -514,7 +525,7 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-template <int KIND, int TN>
+template <int KIND, int TN, bool PEER>
 __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_constant__ TcArgs a) {
   using C = TcCfg<KIND, TN, false>;
   using L = ClCfg<KIND, TN>;
@@ -677,14 +688,14 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
               if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
               const bf16 vb = __float2bfloat16(v);
               if (a.Y) ((bf16*)a.Y)[o] = vb;
-              if (a.n_peer) peer_store(a, row0 + c, n, vb);
+              if (PEER && a.n_peer) peer_store(a, row0 + c, n, vb);
             }
           }
         }
       }
     }
   }
-  if (warp >= 2 && a.n_peer) peer_publish(a, warp, lane);      // every CTA counts in; only rank 0 of a cluster stored
+  if (PEER && warp >= 2 && a.n_peer) peer_publish(a, warp, lane);      // every CTA counts in; only rank 0 of a cluster stored
   if (*abortp && warp == 0) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000) __nanosleep(1000);
@@ -694,10 +705,10 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
   if (warp == 1) tmem_dealloc(tmem, L::TMEM_COLS);
 }
 
-template <int KIND, int TN>
-static int launch_cluster(const TcArgs& a, int grid, cudaStream_t stream) {
+template <int KIND, int TN, bool PEER>
+static int launch_cluster_p(const TcArgs& a, int grid, cudaStream_t stream) {
   using L = ClCfg<KIND, TN>;
-  auto kern = tc_linear_cluster_kernel<KIND, TN>;
+  auto kern = tc_linear_cluster_kernel<KIND, TN, PEER>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -717,6 +728,11 @@ static int launch_cluster(const TcArgs& a, int grid, cudaStream_t stream) {
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
   if (e != cudaSuccess) return ca_cuda(e, "tc_linear_cluster launch");
   return CA_OK;
+}
+
+template <int KIND, int TN>
+static int launch_cluster(const TcArgs& a, int grid, cudaStream_t stream) {
+  return a.n_peer ? launch_cluster_p<KIND, TN, true>(a, grid, stream) : launch_cluster_p<KIND, TN, false>(a, grid, stream);
 }
 
 // Device trace buffer for later launches on the calling thread's device: [grid, units, 8] 64-bit stamps, or
@@ -761,9 +777,9 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   const auto peer = g_peer_out;
   g_peer_out.n = 0;                       // one-shot
   CA_REQUIRE(tmA && tmB && (Y || q_out || peer.n), "tc_linear: null operand");
-  CA_REQUIRE(!peer.n || (epi != EPI_F32 && !q_out), "tc_linear: peer output is a bf16 epilogue");
-  CA_REQUIRE(!q_out || (kind != KIND_BF16 && sf_out && splits <= 1 && N % 32 == 0 && epi == EPI_BF16),
-             "tc_linear: FP4 output needs an FP4 kind, no split-K, N %% 32 == 0 and the plain bf16 epilogue");
+  CA_REQUIRE(!peer.n || (epi != EPI_F32 && !q_out && !swiglu), "tc_linear: peer output is a plain bf16 epilogue (no SwiGLU, no FP4 output)");
+  CA_REQUIRE(!q_out || (kind != KIND_BF16 && swiglu && sf_out && splits <= 1 && N % 32 == 0 && epi == EPI_BF16),
+             "tc_linear: FP4 output is an option of the fused SwiGLU GEMM of an FP4 kind (no split-K, N %% 32 == 0, bf16 epilogue)");
   CA_REQUIRE(!swiglu || tmA2, "tc_linear: swiglu needs the up-projection descriptor");
   CA_REQUIRE(kind == KIND_BF16 || (sfa && sfb && K % 32 == 0), "tc_linear: fp4 kinds need scales and K %% 32 == 0 (K=%d)", K);
   CA_REQUIRE(kind == KIND_BF16 ? (K % 8 == 0) : true, "tc_linear: K must be a multiple of 8");
@@ -777,7 +793,7 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.alpha = alpha; a.alpha2 = alpha2; a.tiles = (const int4*)tiles; a.n_tiles = n_tiles;
   a.Y = Y; a.R = (const bf16*)R; a.splitk_ws = splitk_ws; a.splitk_cnt = splitk_cnt; a.status = status;
   a.trace = g_trace; a.trace_units = g_trace_units;
-  a.peer_y[0] = peer.y[0]; a.peer_y[1] = peer.y[1]; a.peer_flags[0] = (uint32_t*)peer.flags[0]; a.peer_flags[1] = (uint32_t*)peer.flags[1];
+  a.peer_y0 = peer.y[0]; a.peer_y1 = peer.y[1]; a.peer_flag0 = (uint32_t*)peer.flags[0]; a.peer_flag1 = (uint32_t*)peer.flags[1];
   a.peer_row_map = peer.row_map; a.peer_ctl = (uint32_t*)peer.ctl; a.peer_done = (uint32_t*)peer.done; a.peer_ld = peer.ld; a.n_peer = peer.n;
   a.q_out = (uint8_t*)q_out; a.sf_out = (uint8_t*)sf_out; a.inv_gs_out = inv_gs_out; a.ldsf_out = ldsf_out;
   a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;

@@ -13,7 +13,8 @@ from pathlib import Path
 import torch
 
 _LIB = None
-LIB_PATH = Path(__file__).resolve().parent.parent / "_native" / "libcuteafd_b200.so"
+# CUTEAFD_LIB points at an alternative build of the native library (A/B measurements of kernel variants)
+LIB_PATH = Path(os.environ.get("CUTEAFD_LIB") or Path(__file__).resolve().parent.parent / "_native" / "libcuteafd_b200.so")
 
 P, I, F, L, U64 = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_uint64
 
