@@ -38,9 +38,9 @@ from . import peer_ops
 from .symm import SymmetricBlock
 
 PH_DISPATCH, PH_COMBINE, PH_TP = 0, 1, 2
-# GEMM epilogues store straight into peer memory (output projection -> TP partner, expert FC2 -> attention ranks) and
-# publish the flags themselves; CUTEAFD_FUSED_PEER=0 falls back to separate push kernels (for A/B measurements).
-FUSED_PEER = os.environ.get("CUTEAFD_FUSED_PEER", "1") != "0"
+# GEMM epilogues can store straight into peer memory (output projection -> TP partner, expert FC2 -> attention ranks)
+# and publish the flags themselves: CUTEAFD_FUSED_PEER=1; the default keeps the separate push kernels.
+FUSED_PEER = os.environ.get("CUTEAFD_FUSED_PEER", "0") == "1"
 
 
 def local_attention_spec(spec: ModelSpec, tp: int) -> ModelSpec:
