@@ -86,6 +86,26 @@ def main():
           f"FC1 + FC2 + combine_push {t_u:.1f} us; identical output: {same}; status {st.tolist()} flags {flags[:2].tolist()}")
     print(f"FC2 part: fused {t_f - t_1:.1f} us ({wbytes / (t_f - t_1) / 1e3:.0f} GB/s of expert weights), unfused {t_u - t_1:.1f} us")
 
+    # attention-rank side of the same hand-off: quantise T token rows once and scatter every (token, expert) row, its block
+    # scales and the routing table into the owning expert rank's slab (two "ranks" here, both local), then raise their flags
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    row_bytes = H * 2 if kind == ops.KIND_BF16 else H // 2
+    sf_ld = -(-H // 256) * (256 // (16 if kind == ops.KIND_NVFP4 else 32))
+    slab_q = [torch.zeros(rows, row_bytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    slab_sf = [torch.zeros(rows, sf_ld, dtype=torch.uint8, device=dev) for _ in range(2)]
+    idx_dst = [i32(T, k) for _ in range(2)]
+    tbl = lambda ts: (C.c_void_p * 2)(ts[0].data_ptr(), ts[1].data_ptr())
+    q_tbl, sf_tbl, i_tbl = tbl(slab_q), tbl(slab_sf), tbl(idx_dst)
+    f_tbl = (C.c_void_p * 2)(flags.data_ptr() + 8, flags.data_ptr() + 12)
+    inv_gs = torch.tensor([64.0], device=dev)
+
+    def dispatch():
+        peer_ops.dispatch_push(x, idx, slot, off, q_tbl, sf_tbl, i_tbl, f_tbl, inv_gs, ctl, done[2:3], 0, T, H, k, E, 2, kind, sf_ld, rows, 0, st)
+
+    t_d = graph_time_us([dispatch for _ in range(8)])
+    moved = rows * (row_bytes + (H // (16 if kind == ops.KIND_NVFP4 else 32) if kind != ops.KIND_BF16 else 0))
+    print(f"dispatch_push: {t_d:.1f} us for {rows} rows ({moved / 1e6:.2f} MB stored, {moved / t_d / 1e3:.0f} GB/s); status {st.tolist()}")
+
 
 if __name__ == "__main__":
     main()

@@ -50,6 +50,10 @@ class EngineRunner:
     def __init__(self, engine, max_rows: int = 4096):
         self.eng, self._max_rows = engine, max_rows
         self.h2d_bytes = self.d2h_bytes = 0
+        # with `keep_hidden` every step leaves, per sequence, (start position, input tokens, target hidden rows): what an
+        # MTP drafter pairs with the next tokens (serving.mtp_drafter)
+        self.keep_hidden = False
+        self.records: dict = {}
         self._tok_host = torch.zeros(max(64, max_rows), dtype=torch.int32)
         if torch.cuda.is_available():
             self._tok_host = self._tok_host.pin_memory()
@@ -82,6 +86,12 @@ class EngineRunner:
         sh = StepShape(T=len(tokens), n_seq=len(rows), max_q_len=max_q, n_logits=len(logit_rows),
                        attn_splits=eng.attn_splits_for(len(rows), max_q, max(kv_len)) if decode_like else 1)
         lane = eng.run(sh, use_graph=decode_like)
+        if self.keep_hidden:
+            for r, qs, ql in zip(rows, q_start, q_len):
+                recs = self.records.setdefault(id(r.state), [])
+                recs.append((r.start_pos, list(r.tokens), lane.x[qs:qs + ql].clone()))
+                if len(recs) > 256:          # nobody is consuming them (a request that never drafts): keep the tail only
+                    del recs[:-64]
         n = len(logit_rows)
         # rows that sample or carry a grammar mask are re-selected from their logits row on the device
         special = []

@@ -1,0 +1,46 @@
+"""Rank layouts of the attention/expert split (CPU)."""
+import pytest
+
+from cuteafd_b200.config import default_deployment
+
+
+def test_named_layouts():
+    d = default_deployment(8)
+    assert (d.attn_ranks, d.expert_ranks, d.tp, d.ep, d.attn_groups) == ((0, 1), (2, 3, 4, 5, 6, 7), 2, 6, 1)
+    assert d.describe() == "attn-tp2+ep6"
+    assert default_deployment(1).describe() == "single"
+    d2 = default_deployment(2)
+    assert (d2.attn_ranks, d2.expert_ranks, d2.tp) == ((0,), (1,), 1)
+
+
+@pytest.mark.parametrize("world,groups,attn,experts,tp", [(4, 2, (0, 1), (2, 3), 1), (8, 2, (0, 1, 2, 3), (4, 5, 6, 7), 2),
+                                                          (8, 4, (0, 1, 2, 3), (4, 5, 6, 7), 1)])
+def test_data_parallel_attention_groups(world, groups, attn, experts, tp):
+    d = default_deployment(world, groups)
+    assert (d.attn_ranks, d.expert_ranks, d.tp, d.attn_groups) == (attn, experts, tp, groups)
+    seen = []
+    for g in range(groups):
+        ranks = d.group_ranks(g)
+        assert len(ranks) == tp and all(d.group_of(r) == g for r in ranks)
+        seen += list(ranks)
+    assert tuple(seen) == attn
+    assert f"dp{groups}x" in d.describe()
+
+
+def test_groups_need_an_expert_rank():
+    with pytest.raises(ValueError):
+        default_deployment(4, 4)
+
+
+def test_dispatch_flag_slots_are_distinct_per_group_and_tp_rank():
+    from cuteafd_b200.config import tiny_spec
+    from cuteafd_b200.parallel.afd import PH_COMBINE, PH_DISPATCH, PH_TP, flag_offset
+    spec = tiny_spec()
+    d = default_deployment(8, 2)
+    offs = set()
+    for ph in (PH_DISPATCH, PH_COMBINE, PH_TP):
+        for layer in range(spec.n_layers):
+            for src in range(8):
+                offs.add(flag_offset(spec, ph, layer, src))
+    assert len(offs) == 3 * spec.n_layers * 8 and max(offs) < 3 * spec.n_layers * 8 * 4
+    assert {g * d.tp + t for g in range(d.attn_groups) for t in range(d.tp)} == {0, 1, 2, 3}

@@ -62,3 +62,24 @@ def test_sampling_depends_only_on_seed_and_position():
     assert a[0] == b[0] and len(set(a[0])) > 1
     c = run_requests(sched, [p], 10, sampling=SamplingParams(temperature=0.9, top_p=0.95, top_k=40, seed=8))
     assert c[0] != a[0]
+
+
+def test_scheduler_with_mtp_drafter_is_lossless():
+    """The model's own MTP module drafts inside the serving loop (chunked prefill, several sequences): the output must
+    equal plain greedy generation, and drafts must have been proposed and verified."""
+    from cuteafd_b200.serving.mtp_drafter import MtpDrafter
+    spec = tiny_spec().replace(mtp_layers=1)
+    masters = init_weights(spec, 4)
+    n_pages = 64
+    eng = Engine(DeviceWeights.from_masters(spec, masters, DEV), n_pages=n_pages, max_seqs=8, max_pages_per_seq=8)
+    pool = PagePool(n_pages)
+    runner = attach_pool(EngineRunner(eng, max_rows=256), pool)
+    drafter = MtpDrafter(runner)
+    sched = Scheduler(runner, pool, max_seqs=4, prefill_chunk=48, drafter=drafter)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, spec.vocab, (n,), generator=g).tolist() for n in (7, 70, 23)]
+    ref_eng = Engine(DeviceWeights.from_masters(spec, masters, DEV), n_pages=n_pages, max_seqs=8, max_pages_per_seq=8)
+    want = generate(ref_eng, prompts, 14, use_graph=False)
+    got = run_requests(sched, prompts, 14)
+    assert got == want
+    assert drafter.proposed > 0 and sched.stats["drafted"] > 0
