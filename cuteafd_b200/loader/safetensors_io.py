@@ -90,7 +90,7 @@ def write_file(path: str | Path, tensors: dict[str, torch.Tensor], dtypes: dict[
         hdr["__metadata__"] = {k: str(v) for k, v in metadata.items()}
     for name, t in tensors.items():
         t = t.contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""      # reshape: 0-dim tensors too
         hdr[name] = {"dtype": (dtypes or {}).get(name, TO_ST[t.dtype]), "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)

@@ -1,0 +1,72 @@
+"""Checkpoint reader: HF-layout snapshots (bf16, FP8 128x128, NVFP4, MXFP4; sharded) decode to the oracle's masters."""
+import dataclasses
+
+import pytest
+import torch
+
+from cuteafd_b200.config import tiny_spec
+from cuteafd_b200.loader import checkpoint as ck
+from cuteafd_b200.loader.formats import detect_all
+from cuteafd_b200.loader.safetensors_io import catalog
+from cuteafd_b200.ref import quant
+from cuteafd_b200.ref.model import RefModel, init_weights
+
+
+def bf16r(t):
+    return t.to(torch.bfloat16).float()
+
+
+def test_bf16_snapshot_round_trip_and_same_tokens(tmp_path):
+    spec = tiny_spec().replace(mtp_layers=1)
+    masters = init_weights(spec, 3)
+    snap = ck.export_snapshot(spec, masters, tmp_path / "snap", shard_layers=1)
+    assert len(list(snap.glob("*.safetensors"))) == spec.n_layers
+    got = ck.read_masters(snap, spec)
+    assert torch.equal(got["embed"], bf16r(masters["embed"])) and torch.equal(got["lm_head"], bf16r(masters["lm_head"]))
+    for a, b in zip(got["layers"] + [got["mtp"][0]["layer"]], masters["layers"] + [masters["mtp"][0]["layer"]]):
+        assert set(a) == set(b)
+        for k in b:
+            want = b[k].float() if k in ("router_bias", "sink") else bf16r(b[k])
+            assert torch.equal(a[k], want), k
+    assert torch.equal(got["mtp"][0]["eh_proj"], bf16r(masters["mtp"][0]["eh_proj"]))
+    prompt = torch.randint(0, spec.vocab, (9,), generator=torch.Generator().manual_seed(0))
+    rounded = RefModel(spec, got).generate_greedy(prompt, 5)[0]
+    spec_toks, _ = RefModel(spec, got).generate_speculative(prompt, 5, 2)
+    assert rounded == spec_toks
+
+
+@pytest.mark.parametrize("experts", ["nvfp4", "mxfp4"])
+def test_fp4_expert_snapshot_decodes_to_the_oracle_quantisation(tmp_path, experts):
+    spec = tiny_spec()
+    masters = init_weights(spec, 4)
+    snap = ck.export_snapshot(spec, masters, tmp_path / "snap", experts=experts)
+    ops, bad = detect_all(catalog(snap))
+    assert not bad
+    assert ops["model.layers.0.mlp.experts.3.up_proj"].format == experts
+    got = ck.read_masters(snap, spec)
+    for li, lw in enumerate(masters["layers"]):
+        if "w_up" not in lw:
+            continue
+        for e in (0, spec.moe.n_experts - 1):
+            w = lw["w_down"][e]
+            if experts == "nvfp4":
+                p, s, g = quant.nvfp4_quantize(w)
+                want = quant.nvfp4_dequantize(p, s, g)
+            else:
+                p, s = quant.mxfp4_quantize(w)
+                want = quant.mxfp4_dequantize(p, s)
+            assert torch.equal(got["layers"][li]["w_down"][e], want)
+    assert torch.equal(got["layers"][0]["wq"], bf16r(masters["layers"][0]["wq"]))      # dense stays bf16
+
+
+def test_fp8_block_dense_snapshot(tmp_path):
+    base = tiny_spec()
+    spec = base.replace(attn=dataclasses.replace(base.attn, n_kv_heads=4))           # k/v projections of 128 rows: whole scale blocks
+    masters = init_weights(spec, 5)
+    snap = ck.export_snapshot(spec, masters, tmp_path / "snap", dense="fp8_block128")
+    ops, bad = detect_all(catalog(snap))
+    assert not bad and ops["model.layers.1.self_attn.o_proj"].format == "fp8_block128"
+    got = ck.read_masters(snap, spec)
+    q, s = quant.fp8_block_quantize(masters["layers"][1]["wo"])
+    assert torch.equal(got["layers"][1]["wo"], quant.fp8_block_dequantize(q, s))
+    assert torch.equal(got["layers"][0]["router"], bf16r(masters["layers"][0]["router"]))
