@@ -14,6 +14,7 @@ Only token ids / status words return to the host.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -75,7 +76,7 @@ class Lane:
         if m.n_experts and eng.n_local_experts:
             rows = cap * m.top_k
             exp_rows = max(1, math.ceil(rows / max(1, m.n_experts)) * 2)
-            self.tn_g = pick_tn(min(exp_rows, 128), swiglu=True)
+            self.tn_g = pick_tn(min(exp_rows, int(os.environ.get("CUTEAFD_TNG", "128"))), swiglu=True)
             self.max_tiles = eng.n_local_experts + rows // self.tn_g + 1
             self.router_logits = torch.zeros(cap, m.n_experts, dtype=torch.float32, device=dev)
             self.idx, self.wts = i32(cap, m.top_k), torch.zeros(cap, m.top_k, dtype=torch.float32, device=dev)
