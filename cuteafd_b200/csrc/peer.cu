@@ -100,9 +100,11 @@ extern "C" int cuteafd_wait_flags(const void* flags, int n, int stride, void* ct
 // flags (flag pointers are peer addresses) with the current step number, then resets the counter.
 __device__ __forceinline__ void publish_when_last(uint32_t* done_counter, uint32_t* const* flag_ptrs, int n_dst,
                                                   uint32_t value) {
-  __threadfence_system();
+  // CTA-level release: the barrier orders every thread's stores before thread 0, whose system-scope fence is
+  // cumulative over them (the pattern of a grid-wide barrier) - one fence per block instead of one per thread
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const uint32_t prev = atomicAdd(done_counter, 1u);
     if (prev == gridDim.x * gridDim.y - 1) {
       __threadfence_system();

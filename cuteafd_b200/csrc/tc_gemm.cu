@@ -116,9 +116,9 @@ __device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) 
 // Tail of a kernel whose epilogue stored to peers: the 128 epilogue threads fence their stores, one of them counts the
 // CTA in, and the CTA that arrives last publishes the flags (system-scope release) and re-arms the counter.
 __device__ __forceinline__ void peer_publish(const TcArgs& a, int warp, int lane) {
-  __threadfence_system();
   asm volatile("bar.sync 1, 128;" ::: "memory");
   if (warp == 2 && lane == 0) {
+    __threadfence_system();                     // cumulative over the stores the barrier ordered before this thread
     const uint32_t prev = atomicAdd(a.peer_done, 1u);
     if (prev == gridDim.x - 1) {
       __threadfence_system();

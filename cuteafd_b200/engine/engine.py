@@ -47,7 +47,7 @@ class Lane:
         spec, dev, w = eng.spec, eng.device, eng.weights
         a, m, H = spec.attn, spec.moe, spec.hidden
         self.cap = cap
-        self.tn = pick_tn(cap, swiglu=True)      # <= 128 so the same descriptors serve the fused SwiGLU GEMMs
+        self.tn = pick_tn(min(cap, int(os.environ.get("CUTEAFD_TN", "128"))), swiglu=True)      # <= 128 so the same descriptors serve the fused SwiGLU GEMMs
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
         i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
         dk, ek = eng.dense_kind, eng.expert_kind
@@ -76,7 +76,10 @@ class Lane:
         if m.n_experts and eng.n_local_experts:
             rows = cap * m.top_k
             exp_rows = max(1, math.ceil(rows / max(1, m.n_experts)) * 2)
-            self.tn_g = pick_tn(min(exp_rows, int(os.environ.get("CUTEAFD_TNG", "128"))), swiglu=True)
+            # token tiles of the grouped expert GEMMs stay <= 32 rows even in prefill: those tiles run two CTAs per SM with
+            # double-buffered accumulators, which measured 2x faster end to end than 128-row tiles (one CTA per SM, the
+            # SwiGLU epilogue not overlapped); CUTEAFD_TNG overrides for experiments
+            self.tn_g = pick_tn(min(exp_rows, int(os.environ.get("CUTEAFD_TNG", "32"))), swiglu=True)
             self.max_tiles = eng.n_local_experts + rows // self.tn_g + 1
             self.router_logits = torch.zeros(cap, m.n_experts, dtype=torch.float32, device=dev)
             self.idx, self.wts = i32(cap, m.top_k), torch.zeros(cap, m.top_k, dtype=torch.float32, device=dev)

@@ -271,7 +271,7 @@ class ExpertRankWorker:
         i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.ctl, self.done = i32(4), i32(8)
-        self.tn = pick_tn(min(max(1, -(-rows // m.n_experts) * 2), 128), swiglu=True)
+        self.tn = pick_tn(min(max(1, -(-rows // m.n_experts) * 2), 32), swiglu=True)      # <= 32: see Lane.tn_g
         self.max_tiles = self.e_local + rows // self.tn + 1
         self.src_token, self.src_route, self.slot_row = i32(rows), i32(rows), i32(t_max, k)
         self.counts, self.offsets = i32(self.e_local), i32(self.e_local)
