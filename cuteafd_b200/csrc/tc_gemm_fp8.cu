@@ -232,8 +232,8 @@ extern "C" int cuteafd_fp8_linear(int tn, const void* tmA, const void* tmB, cons
   CA_REQUIRE(epi == F8_EPI_BF16 || epi == F8_EPI_BF16_RESIDUAL || epi == F8_EPI_F32, "fp8_linear: bad epilogue %d", epi);
   CA_REQUIRE(epi != F8_EPI_BF16_RESIDUAL || R, "fp8_linear: residual epilogue needs R");
   if (splits < 1) splits = 1;
-  CA_REQUIRE(splits == 1 || ((splits == 2 || splits == 4 || (splits == 8 && tn == 16)) && tn <= 32),
-             "fp8_linear: split-K is 2/4(/8)-way for token tiles of 16 or 32 rows");
+  CA_REQUIRE(splits == 1 || ((splits == 2 || splits == 4 || (splits == 8 && tn == 16)) && tn <= 64),
+             "fp8_linear: split-K is 2- or 4-way for token tiles of up to 64 rows (8-way for 16 rows)");
   if (rows_total <= 0 || N <= 0) return CA_OK;
   Fp8Args a;
   a.tmA = (const CUtensorMap*)tmA; a.tmB = (const CUtensorMap*)tmB; a.sw = sw; a.sa = sa; a.Y = Y; a.R = (const bf16*)R; a.status = status;

@@ -197,7 +197,7 @@ class Engine:
         nkb = K // (64 if kind == KIND_BF16 else (128 if kind == KIND_FP8B else 256))
         if tiles >= self.sm_count or nkb < 4:
             return 1
-        if tn <= 32:
+        if tn <= 32 or (kind == KIND_FP8B and tn <= 64):      # the FP8 kernel's cluster reduction also takes 64-row tiles
             for s in ((8, 4, 2) if tn == 16 else (4, 2)):
                 if tiles * s <= self.sm_count and nkb // s >= 2:
                     return s

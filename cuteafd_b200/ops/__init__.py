@@ -241,7 +241,7 @@ def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor | None, *, rows: int | 
     if w.kind == KIND_FP8B:
         if w_up is not None or tiles is not None or quant_out is not None or w.G != 1:
             raise ValueError("tc_linear: the FP8 block-scaled kernel is dense only (no SwiGLU / grouped / FP4 output)")
-        if splits not in (1, 2, 4, 8) or (splits > 1 and x.tn > 32) or (splits == 8 and x.tn != 16):
+        if splits not in (1, 2, 4, 8) or (splits > 1 and x.tn > 64) or (splits == 8 and x.tn != 16):
             splits = 1
         call("cuteafd_fp8_linear", x.tn, ptr(w.tmap), ptr(x.tmap), ptr(w.sf), ptr(x.sf), ptr(y), ptr(residual), y.stride(0), rows, w.N, w.K,
              epi, splits, ptr(status), stream())

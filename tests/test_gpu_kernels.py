@@ -515,7 +515,7 @@ def test_router_select_pack_matches_two_kernels(T, E, k, e_lo, e_hi):
 
 # ------------------------------------------------------------------ FP8 with 128 x 128 / 1 x 128 fp32 block scales
 @pytest.mark.parametrize("T,N,K,splits", [(3, 128, 256, 1), (16, 384, 512, 2), (16, 256, 7168, 8), (70, 256, 1024, 1), (128, 130, 768, 1),
-                                          (30, 256, 2048, 4), (9, 1536, 7168, 8)])
+                                          (30, 256, 2048, 4), (9, 1536, 7168, 8), (64, 256, 7168, 4), (50, 1536, 1536, 2)])
 def test_fp8_block_linear(T, N, K, splits):
     g = torch.Generator().manual_seed(T + N + K)
     w = torch.randn(N, K, generator=g) * 0.05
