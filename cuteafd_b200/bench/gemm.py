@@ -63,14 +63,15 @@ def stream(dev, T: int = 16):
 
 
 SMALL = [("wqkv", "nvfp4", 9216, 4096, 12), ("wo", "nvfp4", 4096, 8192, 12), ("router", "bf16", 128, 4096, 64),
-         ("shared-ish", "nvfp4", 1536, 4096, 40), ("q_b (mla)", "bf16", 12288, 1536, 8), ("o (mla)", "bf16", 7168, 8192, 4)]
+         ("shared-ish", "nvfp4", 1536, 4096, 40), ("q_b (mla)", "bf16", 12288, 1536, 8), ("o (mla)", "bf16", 7168, 8192, 4),
+         ("q_a fp8", "fp8_block128", 1536, 7168, 12), ("q_b fp8", "fp8_block128", 24576, 1536, 6), ("o fp8", "fp8_block128", 7168, 16384, 4)]
 
 
 def small(dev, T: int = 16):
     st = torch.zeros(4, dtype=torch.int32, device=dev)
     for name, kind, N, K, copies in SMALL:
         Ws = [TcWeight.random(1, N, K, kind, dev, seed=i) for i in range(copies)]
-        x = ActBuffer.alloc(Ws[0].kind, T, K, 16, dev)
+        x = ActBuffer.alloc(Ws[0].kind, T, K, ops.pick_tn(T, swiglu=True), dev)
         y = torch.zeros(T, N, dtype=torch.bfloat16, device=dev)
         for splits in (1, 2, 3, 4, 8):
             us = graph_time_us([(lambda W=W: ops.tc_linear(W, x, y, splits=splits, status=st)) for W in Ws])

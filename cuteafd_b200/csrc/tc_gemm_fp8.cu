@@ -35,8 +35,13 @@ struct Fp8Cfg {
   static constexpr int TMEM_COLS = NACC * TN < 32 ? 32 : NACC * TN;       // 64 / 128 / 256 / 512
   static constexpr int BUDGET = 200 * 1024, MAX_RING = 8;
   static constexpr int SMEM_BYTES = BUDGET + 1024;
-  __host__ __device__ static constexpr int ring(int S) {
-    return (BUDGET - (S - 1) * 128 * TN * 4) / STAGE_BYTES > MAX_RING ? MAX_RING : (BUDGET - (S - 1) * 128 * TN * 4) / STAGE_BYTES;
+  // Shared memory = stage ring + staging area of the cluster reduction + the table of combined scales
+  // sa[token, kb] * sw[n / 128, kb] of this CTA's K slice (one fp32 per token and stage; without the table every stage
+  // exposed two dependent global loads, ~0.5 us, in the epilogue warps).
+  __host__ __device__ static constexpr int table_bytes(int nk) { return nk * TN * 4 <= 64 * 1024 ? nk * TN * 4 : 0; }
+  __host__ __device__ static constexpr int ring(int S, int nk) {
+    return (BUDGET - (S - 1) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES > MAX_RING
+               ? MAX_RING : (BUDGET - (S - 1) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES;
   }
 };
 
@@ -55,8 +60,11 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
   __shared__ int abort_flag;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int S = a.splits > 1 ? a.splits : 1;
-  const int ring = C::ring(S);
+  const int nk_max = ((a.K + 127) / 128 + S - 1) / S;                      // stages of the longest K slice
+  const int ring = C::ring(S, nk_max);
   float* staging = (float*)(smem + ring * C::STAGE_BYTES);                 // [S-1][TN][128] fp32 on cluster rank 0
+  float* sc_tab = staging + (size_t)(S - 1) * 128 * TN;                    // [stages of my slice][TN] combined scales
+  const bool use_tab = C::table_bytes(nk_max) > 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -131,14 +139,27 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
     pdl_wait();
     const uint32_t tbase = tmem + ((uint32_t)(q4 * 32) << 16);
     bool ok = true;
+    if (use_tab) {
+      const int et128 = (warp - 2) * 32 + lane;          // 0..127 over the four epilogue warps
+      for (int i = et128; i < (kb1 - kb0) * TN; i += 128) {
+        const int kk = i / TN, tcol = i % TN;
+        sc_tab[i] = (tcol < nrows) ? a.sa[(size_t)(row0 + tcol) * nkb_all + kb0 + kk] * a.sw[(size_t)nt * nkb_all + kb0 + kk] : 0.f;
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+    }
     for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
       const int b = it % C::NACC;
-      const float swv = a.sw[(size_t)nt * nkb_all + kb];
       float sav[(TN + 15) / 16];                 // lane j (< 16) of chunk c holds the scale of token c * 16 + j
+      if (use_tab) {
 #pragma unroll
-      for (int c = 0; c < (TN + 15) / 16; ++c) {
-        const int tcol = c * 16 + (lane & 15);
-        sav[c] = (tcol < nrows) ? a.sa[(size_t)(row0 + tcol) * nkb_all + kb] * swv : 0.f;
+        for (int c = 0; c < (TN + 15) / 16; ++c) sav[c] = sc_tab[it * TN + c * 16 + (lane & 15)];
+      } else {
+        const float swv = a.sw[(size_t)nt * nkb_all + kb];
+#pragma unroll
+        for (int c = 0; c < (TN + 15) / 16; ++c) {
+          const int tcol = c * 16 + (lane & 15);
+          sav[c] = (tcol < nrows) ? a.sa[(size_t)(row0 + tcol) * nkb_all + kb] * swv : 0.f;
+        }
       }
       ok = mbar_wait_bounded(&accf_bar[b], (it / C::NACC) & 1, abortp);
       ok = __all_sync(0xffffffffu, ok);          // tensor-memory loads must stay warp-uniform
