@@ -81,17 +81,29 @@ def build_serving(a):
     from .serving.scheduler import NgramDrafter, Scheduler
     spec = spec_by_name(a.model) if a.model in NAMED_SPECS else from_hf_config(a.model)
     dev = torch.device("cuda", a.device)
-    if spec.name == "tiny":
+    layers = getattr(a, "layers", 0)
+    if layers:
+        spec = spec.replace(n_layers=layers)
+    if os.path.isdir(a.model) and spec.attn.kind == "gqa":
+        from .loader.checkpoint import load_device_weights
+        weights = load_device_weights(a.model, spec, dev)      # tensors in their stored formats, no repacking
+    elif spec.name == "tiny":
         weights = DeviceWeights.from_masters(spec, init_weights(spec, 0), dev)
     else:
-        weights = DeviceWeights.random(spec, dev, seed=1)      # synthetic weights: no checkpoint reader for this family yet
+        weights = DeviceWeights.random(spec, dev, seed=1)      # named shapes without a snapshot: synthetic weights
     n_pages = a.pool_tokens // 64 if a.pool_tokens else 4096
     eng = Engine(weights, n_pages=n_pages, max_seqs=a.max_sequences, max_pages_per_seq=min(n_pages, a.max_context // 64 + 1))
     pool = PagePool(n_pages)
     runner = attach_pool(EngineRunner(eng, max_rows=a.prefill_batch_tokens), pool)
     prefix = PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens)
+    drafter = None
+    if a.draft == "ngram":
+        drafter = NgramDrafter()
+    elif a.draft == "mtp":
+        from .serving.mtp_drafter import MtpDrafter
+        drafter = MtpDrafter(runner)                           # the model's own MTP module (needs MTP weights)
     sched = Scheduler(runner, pool, max_seqs=a.max_sequences, prefill_chunk=a.prefill_batch_tokens, decode_share=a.decode_share,
-                      prefix=prefix, drafter=NgramDrafter() if a.draft != "off" else None, max_draft=a.draft_limit)
+                      prefix=prefix, drafter=drafter, max_draft=a.draft_limit)
     return spec, sched
 
 
@@ -149,6 +161,40 @@ def cmd_expertd(a) -> int:
     return 0
 
 
+def cmd_card(a) -> int:
+    """Baseline card (C1 decode, C4/C8/C16 aggregate, 8k prefill + TTFT, quick quality gates) through the scheduler."""
+    import json
+    import torch
+    from .bench.card import run_card
+    state = {}
+
+    def make():
+        # one engine for the whole card (weights stay resident); every section gets a fresh scheduler, pool and prefix cache
+        if "eng" not in state:
+            state["spec"], sched = build_serving(a)
+            state["eng"] = sched.runner.eng
+            return sched
+        from .engine.kv import PagePool
+        from .serving.prefix import PrefixCache
+        from .serving.runner import EngineRunner, attach_pool
+        from .serving.scheduler import NgramDrafter, Scheduler
+        eng = state["eng"]
+        pool = PagePool(eng.n_pages)
+        runner = attach_pool(EngineRunner(eng, max_rows=a.prefill_batch_tokens), pool)
+        return Scheduler(runner, pool, max_seqs=a.max_sequences, prefill_chunk=a.prefill_batch_tokens, decode_share=a.decode_share,
+                         prefix=PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens),
+                         drafter=NgramDrafter() if a.draft == "ngram" else None, max_draft=a.draft_limit)
+    first = make()                                             # builds the engine; its spec gives the vocabulary
+    pending = [first]
+    card = run_card(lambda: pending.pop() if pending else make(), vocab=state["spec"].vocab, c1_tokens=a.c1_tokens,
+                    prefill_tokens=a.prefill_tokens)
+    card["model"] = state["spec"].name
+    card["layers"] = state["spec"].n_layers
+    torch.cuda.synchronize()
+    print(json.dumps(card))
+    return 0
+
+
 def cmd_bench(a) -> int:
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -169,9 +215,19 @@ def main(argv=None) -> int:
     p.add_argument("--max-sequences", type=int, default=16); p.add_argument("--max-output", type=int, default=4096)
     p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--prefill-batch-tokens", type=int, default=4096)
     p.add_argument("--decode-share", type=float, default=0.2); p.add_argument("--prefix-cache-entries", type=int, default=20)
-    p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram"])
+    p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram", "mtp"])
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
+    p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("card")
+    p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--device", type=int, default=0)
+    p.add_argument("--max-context", type=int, default=16384); p.add_argument("--max-sequences", type=int, default=16)
+    p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--prefill-batch-tokens", type=int, default=4096)
+    p.add_argument("--decode-share", type=float, default=0.2); p.add_argument("--prefix-cache-entries", type=int, default=20)
+    p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram"])
+    p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--layers", type=int, default=0)
+    p.add_argument("--c1-tokens", type=int, default=320); p.add_argument("--prefill-tokens", type=int, default=8192)
+    p.set_defaults(fn=cmd_card)
     p = sub.add_parser("golden"); p.add_argument("--experts", default="bf16"); p.add_argument("--seed", type=int, default=0); p.set_defaults(fn=cmd_golden)
     p = sub.add_parser("expertd"); p.add_argument("--listen", default="127.0.0.1:7000"); p.add_argument("--rank", type=int, default=0); p.set_defaults(fn=cmd_expertd)
     p = sub.add_parser("bench"); p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
