@@ -24,6 +24,9 @@ def main() -> int:
     ap.add_argument("--sessions", type=int, default=4)
     ap.add_argument("--decode", type=int, default=32)
     ap.add_argument("--chunk", type=int, default=4096)
+    ap.add_argument("--host-tier-gib", type=float, default=0.0,
+                    help="attach a pinned host tier of this size and empty the device prefix cache between sessions, so every warm "
+                         "session restores its shared pages from host memory")
     a = ap.parse_args()
     from ..config import qwen3_235b_spec, tiny_spec
     from ..engine.engine import Engine
@@ -40,7 +43,11 @@ def main() -> int:
     eng = Engine(dw, n_pages=n_pages, max_seqs=4, max_pages_per_seq=pages_per)
     pool = PagePool(n_pages)
     runner = attach_pool(EngineRunner(eng, max_rows=a.chunk), pool)
-    cache = PrefixCache(pool, max_entries=64, min_tokens=64, max_cached_pages=n_pages)
+    host = None
+    if a.host_tier_gib > 0:
+        from ..serving.hostcache import attach_host_tier
+        host = attach_host_tier(eng, a.host_tier_gib)
+    cache = PrefixCache(pool, max_entries=64, min_tokens=64, max_cached_pages=n_pages, host=host)
     sched = Scheduler(runner, pool, max_seqs=1, prefill_chunk=a.chunk, prefix=cache)
     g = torch.Generator().manual_seed(0)
     shared = torch.randint(0, spec.vocab, (a.shared,), generator=g).tolist()
@@ -59,13 +66,16 @@ def main() -> int:
         sched.run_until_idle()
         ttfts.append(t_first[0])
         outs.append(len(toks))
+        if host is not None:
+            cache.evict(n_pages)            # the device tier forgets everything: the next session restores from the host tier
     eng.check_status()
     warm = sorted(ttfts[1:])
     print(json.dumps({"bench": "ttft_prefix_restore", "model": spec.name, "layers": spec.n_layers, "prompt_tokens": a.prompt,
                       "shared_prefix_tokens": a.shared, "sessions": a.sessions, "cold_ttft_s": round(ttfts[0], 4),
                       "cold_prefill_tok_s": round(a.prompt / ttfts[0], 1),
                       "restore_ttft_s_p50": round(warm[len(warm) // 2], 4) if warm else None, "restore_ttfts_s": [round(t, 4) for t in ttfts[1:]],
-                      "decoded_per_session": outs, "prefix_cache": cache.snapshot(), "data": "synthetic tokens, random-init weights"}))
+                      "decoded_per_session": outs, "prefix_cache": cache.snapshot(),
+                      "host_tier": (dict(host.snapshot(), copy_launches=host.copy.launches) if host is not None else None), "data": "synthetic tokens, random-init weights"}))
     return 0
 
 

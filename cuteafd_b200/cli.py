@@ -95,7 +95,11 @@ def build_serving(a):
     eng = Engine(weights, n_pages=n_pages, max_seqs=a.max_sequences, max_pages_per_seq=min(n_pages, a.max_context // 64 + 1))
     pool = PagePool(n_pages)
     runner = attach_pool(EngineRunner(eng, max_rows=a.prefill_batch_tokens), pool)
-    prefix = PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens)
+    host = None
+    if getattr(a, "host_cache_gib", 0) > 0:
+        from .serving.hostcache import attach_host_tier
+        host = attach_host_tier(eng, a.host_cache_gib)
+    prefix = PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens, host=host)
     drafter = None
     if a.draft == "ngram":
         drafter = NgramDrafter()
@@ -216,6 +220,7 @@ def main(argv=None) -> int:
     p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--prefill-batch-tokens", type=int, default=4096)
     p.add_argument("--decode-share", type=float, default=0.2); p.add_argument("--prefix-cache-entries", type=int, default=20)
     p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram", "mtp"])
+    p.add_argument("--host-cache-gib", type=float, default=0.0, help="pinned host memory behind the prefix cache (0 = off)")
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.set_defaults(fn=cmd_serve)

@@ -138,39 +138,51 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t id_s = mla_idesc(MKEYS, 0), id_o = mla_idesc(256, 1);
-    auto issue_scores = [&](int j) -> bool {
-      const int s = j & 1;
-      if (!mbar_wait_bounded(&k_full[s], (j >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, j); return false; }
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t k0 = smem_u32(sK + s * SK_STAGE), d = tmem + (s ? S1_COL : S0_COL);
+    // The issuer polls two conditions and serves whichever is ready: "the latent tile qk has landed" (issue its
+    // scores) and "the probabilities of tile pv are in shared memory" (issue its PV product, which also releases the
+    // tile's stage to the producer).  Waiting for them in a fixed order would put the load latency of tile i+1 in
+    // front of the PV product of tile i, i.e. one full load latency per tile on the critical path.
+    // Scores of tile qk go to S buffer qk & 1, which the softmax of tile qk - 2 has read once PV(qk - 2) could be
+    // issued: qk <= pv + 1.
+    int qk = 0, pv = 0, idle = 0;
+    long long idle_t0 = 0;
+    while (pv < n_tiles) {
+      bool did = false;
+      if (pv < qk && __shfl_sync(0xffffffffu, (int)mbar_test(&p_full, pv & 1), 0)) {
+        tc_fence_after();
+        if (lane == 0) {
+          const int s = pv & 1;
+          const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * 4096;
 #pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + c * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, (c | k) ? 1u : 0u);
-        tc_commit(&s_full[s]);
+          for (int k = 0; k < 2; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
+            tc_mma_f16(tmem + O_COL, mla_desc_k_plain(smem_u32(sP) + k * 256, 128, 512), mla_desc_mn_sw128(v0 + k * 2048, 4096, 1024), id_o, (pv | k) ? 1u : 0u);
+          tc_commit(&k_empty[s]);
+          tc_commit(&o_done);
+        }
+        __syncwarp();
+        ++pv; did = true;
       }
-      __syncwarp();
-      return true;
-    };
-    bool ok = true;
-    if (n_tiles > 0) ok = issue_scores(0);
-    for (int i = 0; ok && i < n_tiles; ++i) {
-      const int s = i & 1;
-      // the next tile's scores are issued first so they overlap this tile's softmax (its K stage is the other one)
-      if (i + 1 < n_tiles) { ok = issue_scores(i + 1); if (!ok) break; }
-      if (!mbar_wait_bounded(&p_full, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, i); break; }
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * 4096;
+      if (qk < n_tiles && qk <= pv + 1 && __shfl_sync(0xffffffffu, (int)mbar_test(&k_full[qk & 1], (qk >> 1) & 1), 0)) {
+        tc_fence_after();
+        if (lane == 0) {
+          const int s = qk & 1;
+          const uint32_t k0 = smem_u32(sK + s * SK_STAGE), d = tmem + (s ? S1_COL : S0_COL);
 #pragma unroll
-        for (int k = 0; k < 2; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
-          tc_mma_f16(tmem + O_COL, mla_desc_k_plain(smem_u32(sP) + k * 256, 128, 512), mla_desc_mn_sw128(v0 + k * 2048, 4096, 1024), id_o, (i | k) ? 1u : 0u);
-        tc_commit(&k_empty[s]);
-        tc_commit(&o_done);
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + c * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, (c | k) ? 1u : 0u);
+          tc_commit(&s_full[s]);
+        }
+        __syncwarp();
+        ++qk; did = true;
       }
-      __syncwarp();
+      if (did) { idle = 0; continue; }
+      if (idle++ == 0) idle_t0 = clock64();
+      if ((idle & 255) == 0) {
+        if (*abortp) break;
+        if (clock64() - idle_t0 > 4000000000LL) { *abortp = 1; ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, pv); break; }
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue: thread = row

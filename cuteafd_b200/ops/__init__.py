@@ -355,6 +355,21 @@ def gather_rows(x, src_rows, n_rows_dev, out, rows):
     return out
 
 
+def kv_pages_copy(kv, pairs, pool, to_pool: bool):
+    """Moves KV pages between the device store `kv` [layers, slots, ...] and a slab pool [slabs, layers, page...] (device
+    memory or pinned host memory) in one launch.  `pairs` is an int32 device tensor [n, 2] of (device page, slab)."""
+    L = kv.shape[0]
+    page_bytes = pool[0, 0].numel() * pool.element_size()
+    assert pool.shape[1] == L and kv.is_contiguous() and pool.is_contiguous() and pairs.dtype == torch.int32 and pairs.is_cuda
+    call("cuteafd_kv_pages_copy", ptr(kv), kv.stride(0) * kv.element_size(), L, page_bytes, ptr(pairs), pairs.shape[0], pool.data_ptr(),
+         pool.stride(0) * pool.element_size(), 0 if to_pool else 1, stream())
+
+
+def l2_prefetch(t):
+    """Hints the memory system to pull a tensor (e.g. the next layer's weights) into L2; returns immediately."""
+    call("cuteafd_l2_prefetch", ptr(t), t.numel() * t.element_size(), stream())
+
+
 def act_quant_fp8_ue8m0(x, q, sf):
     call("cuteafd_act_quant_fp8_ue8m0", ptr(x), ptr(q), ptr(sf), x.shape[0], x.shape[1], stream())
 

@@ -36,6 +36,8 @@ _PROTOS = {
     "cuteafd_quant_fp4_rows": [I, P, P, P, P, P, I, I, I, I, P, P],
     "cuteafd_gather_rows": [P, P, P, P, I, I, P],
     "cuteafd_act_quant_fp8_ue8m0": [P, P, P, I, I, P],
+    "cuteafd_kv_pages_copy": [P, L, I, I, P, I, P, L, I, P],
+    "cuteafd_l2_prefetch": [P, L, P],
     "cuteafd_silu_mul": [P, P, P, L, F, P],
     "cuteafd_router_select": [P, P, P, P, I, I, I, I, I, F, I, I, P],
     "cuteafd_add_rmsnorm_quant": [P, P, P, P, I, I, F, P, P, I, P, I, P],

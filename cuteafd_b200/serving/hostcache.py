@@ -17,10 +17,19 @@ from dataclasses import dataclass, field
 
 
 class CopyEngine:
-    """Moves one KV page between the device pool and a host slab."""
+    """Moves KV pages between the device pool and host slabs."""
     def d2h(self, device_page: int, slab: int): ...
     def h2d(self, slab: int, device_page: int): ...
     def synchronize(self): ...
+
+    def d2h_many(self, pairs: list):
+        """`pairs` = [(device page, slab), ...]; engines that can batch override this."""
+        for page, slab in pairs:
+            self.d2h(page, slab)
+
+    def h2d_many(self, pairs: list):
+        for page, slab in pairs:
+            self.h2d(slab, page)
 
 
 class StubCopyEngine(CopyEngine):
@@ -51,7 +60,13 @@ class StubCopyEngine(CopyEngine):
 
 
 class CudaCopyEngine(CopyEngine):
-    """Copies pages of the engine's KV tensor [layers, slots, ...] to/from one pinned host tensor on a side stream."""
+    """Copies pages of the engine's KV tensor [layers, slots, ...] to/from one pinned host tensor on a side stream.
+
+    A batch of pages moves in ONE kernel launch that reads or writes the pinned slabs through their device mapping
+    (`ops.kv_pages_copy`).  Ordering against the compute stream is by stream dependencies only, never a host wait: the
+    side stream first waits for the work already queued on the caller's stream (the pages' content is final; a page about
+    to be overwritten is no longer read), and the caller's stream then waits for the copy (a page released after a
+    write-behind is not reused before it has left; a restored page is complete before attention reads it)."""
 
     def __init__(self, kv, n_slabs: int, page_tokens: int = 64):
         import torch
@@ -59,18 +74,34 @@ class CudaCopyEngine(CopyEngine):
         L = kv.shape[0]
         self.host = torch.empty((n_slabs, L, page_tokens) + tuple(kv.shape[2:]), dtype=kv.dtype).pin_memory()
         self.stream = torch.cuda.Stream(device=kv.device)
+        self.page_bytes = self.host[0].numel() * self.host.element_size()
+        self.launches = 0
+
+    def _move(self, pairs, to_pool: bool):
+        import torch
+        from .. import ops
+        if not pairs:
+            return
+        cur = torch.cuda.current_stream(self.kv.device)
+        t = torch.tensor(pairs, dtype=torch.int32).pin_memory().to(self.kv.device, non_blocking=True)
+        self.stream.wait_stream(cur)
+        with torch.cuda.stream(self.stream):
+            ops.kv_pages_copy(self.kv, t, self.host, to_pool)
+        t.record_stream(self.stream)
+        cur.wait_stream(self.stream)
+        self.launches += 1
+
+    def d2h_many(self, pairs):
+        self._move(pairs, True)
+
+    def h2d_many(self, pairs):
+        self._move(pairs, False)
 
     def d2h(self, device_page, slab):
-        import torch
-        s0 = device_page * self.page_tokens
-        with torch.cuda.stream(self.stream):
-            self.host[slab].copy_(self.kv[:, s0:s0 + self.page_tokens], non_blocking=True)
+        self._move([(device_page, slab)], True)
 
     def h2d(self, slab, device_page):
-        import torch
-        s0 = device_page * self.page_tokens
-        with torch.cuda.stream(self.stream):
-            self.kv[:, s0:s0 + self.page_tokens].copy_(self.host[slab], non_blocking=True)
+        self._move([(device_page, slab)], False)
 
     def synchronize(self):
         self.stream.synchronize()
@@ -102,15 +133,16 @@ class HostCache:
         self.stats = {"stored_pages": 0, "shared_hits": 0, "restored_pages": 0, "evicted_pages": 0, "rejected": 0, "lookups": 0, "hits": 0}
 
     # ---- write-behind on device eviction
-    def store(self, tokens: list[int], device_pages: list[int]) -> int:
-        """Persist the pages of a prefix (tokens cover len(device_pages) full pages).  Returns pages newly written."""
+    def store(self, tokens: list[int], device_pages: list[int], keys: list | None = None) -> int:
+        """Persist the pages of a prefix (tokens cover len(device_pages) full pages).  Returns pages newly written.
+        `keys` may carry the chain keys of the pages when the caller keeps them (saves re-hashing the tokens)."""
         n = len(device_pages)
         if n * self.page_tokens < self.min_tokens:
             self.stats["rejected"] += 1
             return 0
-        key, written = b"", 0
+        key, written, batch = b"", 0, []
         for d in range(n):
-            key = chain_key(key, tuple(tokens[d * self.page_tokens:(d + 1) * self.page_tokens]))
+            key = keys[d] if keys is not None else chain_key(key, tuple(tokens[d * self.page_tokens:(d + 1) * self.page_tokens]))
             hp = self.pages.get(key)
             if hp is None:
                 if not self.free and not self._evict_one(protect=key):
@@ -118,13 +150,14 @@ class HostCache:
                 if not self.free:
                     break
                 hp = HostPage(self.free.pop())
-                self.copy.d2h(device_pages[d], hp.slab)
+                batch.append((device_pages[d], hp.slab))
                 self.pages[key] = hp
                 self.stats["stored_pages"] += 1
                 written += 1
             else:
                 self.stats["shared_hits"] += 1
             hp.last_used = next(self.clock)
+        self.copy.d2h_many(batch)
         return written
 
     # ---- restore
@@ -141,14 +174,15 @@ class HostCache:
 
     def restore(self, tokens: list[int], first_page: int, device_pages: list[int]) -> int:
         """Copy host pages [first_page, first_page + len(device_pages)) of the prefix into the given device pages."""
-        key = b""
+        key, batch = b"", []
         for d in range(first_page + len(device_pages)):
             key = chain_key(key, tuple(tokens[d * self.page_tokens:(d + 1) * self.page_tokens]))
             if d >= first_page:
                 hp = self.pages[key]
                 hp.last_used = next(self.clock)
-                self.copy.h2d(hp.slab, device_pages[d - first_page])
+                batch.append((device_pages[d - first_page], hp.slab))
                 self.stats["restored_pages"] += 1
+        self.copy.h2d_many(batch)
         self.copy.synchronize()
         if device_pages:
             self.stats["hits"] += 1
@@ -165,6 +199,16 @@ class HostCache:
 
     def snapshot(self) -> dict:
         return dict(self.stats, resident_pages=len(self.pages), free_slabs=len(self.free), bytes=len(self.pages) * self.page_bytes)
+
+
+def attach_host_tier(engine, gib: float, min_tokens: int = 512, page_tokens: int = 64) -> "HostCache":
+    """Host tier of `gib` GiB of pinned memory behind an engine's paged KV store (any engine exposing `kv` as
+    [layers, slots, ...]); pass the result to `PrefixCache(..., host=...)`."""
+    copy_probe = engine.kv[0, :page_tokens]
+    page_bytes = engine.kv.shape[0] * copy_probe.numel() * copy_probe.element_size()
+    n_slabs = max(1, int(gib * (1 << 30)) // page_bytes)
+    copy = CudaCopyEngine(engine.kv, n_slabs, page_tokens)
+    return HostCache(copy, n_slabs, page_bytes, min_tokens=min_tokens, page_tokens=page_tokens)
 
 
 def simulate(n_requests: int = 200, n_prefixes: int = 12, prefix_pages: int = 40, device_pages: int = 128, host_slabs: int = 512,

@@ -27,6 +27,7 @@ class Node:
     last_used: int = 0
     kind: str = "prompt"                # prompt | turn | parked
     logits_row: object = None           # retained last-row logits for whole-prompt hits
+    hkey: bytes | None = None           # content identity of the chain up to this page (host tier key), computed on demand
 
 
 @dataclass
@@ -37,13 +38,17 @@ class Admission:
 
 
 class PrefixCache:
-    def __init__(self, pool: PagePool, max_entries: int = 20, min_tokens: int = 64, max_cached_pages: int | None = None):
+    def __init__(self, pool: PagePool, max_entries: int = 20, min_tokens: int = 64, max_cached_pages: int | None = None, host=None):
+        """`host` is an optional `HostCache`: evicted chains are written behind into it and a prompt whose prefix lives only
+        there gets its pages copied back into fresh device pages on admission (cuteafd-hostcache/src/lib.rs:1-24)."""
         self.pool, self.max_entries, self.min_tokens = pool, max_entries, min_tokens
+        self.host = host
         self.max_cached_pages = max_cached_pages if max_cached_pages is not None else pool.n_pages // 2
         self.root = Node()
         self.clock = itertools.count(1)
         self.n_nodes = 0
-        self.stats = {"lookups": 0, "hits": 0, "hit_tokens": 0, "captures": 0, "evictions": 0, "parked": 0, "deferred": 0}
+        self.stats = {"lookups": 0, "hits": 0, "hit_tokens": 0, "captures": 0, "evictions": 0, "parked": 0, "deferred": 0,
+                      "host_hits": 0, "host_hit_tokens": 0, "host_stored_pages": 0}
 
     # ------------------------------------------------------------------ lookup / admit
     def _walk(self, tokens: list[int]):
@@ -66,6 +71,8 @@ class PrefixCache:
         the cached node kept them.  Raises OutOfPages (after trying eviction) when the pool cannot hold it."""
         self.stats["lookups"] += 1
         node, depth = self._walk(tokens)
+        if self.host is not None:
+            node, depth = self._extend_from_host(tokens, node, depth)
         logits_row = None
         if depth * PAGE == len(tokens):
             if node.logits_row is not None:
@@ -94,6 +101,51 @@ class PrefixCache:
             self.stats["hits"] += 1
             self.stats["hit_tokens"] += depth * PAGE
         return Admission(seq, depth * PAGE, logits_row)
+
+    # ------------------------------------------------------------------ host tier
+    def _chain(self, n: Node):
+        """Nodes from the first page to `n`."""
+        out = []
+        while n is not self.root:
+            out.append(n)
+            n = n.parent
+        out.reverse()
+        return out
+
+    def _hkeys(self, chain) -> list:
+        from .hostcache import chain_key
+        prev = b""
+        for n in chain:
+            if n.hkey is None:
+                n.hkey = chain_key(prev, n.key)
+            prev = n.hkey
+        return [n.hkey for n in chain]
+
+    def _extend_from_host(self, tokens: list[int], node: Node, depth: int):
+        """Pages [depth, n_host) of the prompt exist only on the host: copy them into fresh device pages and hang them
+        into the tree, so the admission below (and later requests) see an ordinary device hit."""
+        n_host = self.host.lookup(tokens)
+        if n_host <= depth or n_host * PAGE < self.min_tokens:
+            return node, depth
+        chain_pages = {n.page for n in self._chain(node)}
+        want = n_host - depth
+        if not self.pool.can_alloc(want):
+            self.evict(want - self.pool.n_free, protect=chain_pages)
+        want = min(want, self.pool.n_free)
+        if want <= 0:
+            return node, depth
+        pages = [self.pool.alloc() for _ in range(want)]            # the tree owns these references
+        self.host.restore(tokens, depth, pages)
+        for i, page in enumerate(pages):
+            key = tuple(tokens[(depth + i) * PAGE:(depth + i + 1) * PAGE])
+            nxt = Node(page=page, parent=node, key=key, kind="host")
+            nxt.last_used = next(self.clock)
+            node.children[key] = nxt
+            self.n_nodes += 1
+            node = nxt
+        self.stats["host_hits"] += 1
+        self.stats["host_hit_tokens"] += want * PAGE
+        return node, depth + want
 
     # ------------------------------------------------------------------ capture / park
     def capture(self, tokens: list[int], seq: SeqKV, kind: str = "prompt", logits_row=None) -> int:
@@ -135,6 +187,9 @@ class PrefixCache:
         return out
 
     def _drop(self, n: Node):
+        if self.host is not None:
+            chain = self._chain(n)
+            self.stats["host_stored_pages"] += self.host.store([], [c.page for c in chain], keys=self._hkeys(chain))
         del n.parent.children[n.key]
         self.pool.release(n.page)
         self.n_nodes -= 1

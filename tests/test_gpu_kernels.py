@@ -566,3 +566,28 @@ def test_exl3_linear_matches_oracle(bits, T, K, N):
     torch.cuda.synchronize()
     ref = bf16r(x).double() @ torch.from_numpy(W) + r.double()
     assert rel_err(y.float().cpu(), ref.float()) < 1.5e-2
+
+
+def test_kv_pages_copy_roundtrip_through_pinned_host_and_l2_prefetch():
+    L, pages, row = 3, 10, (2, 2, 32)
+    kv = torch.randn(L, pages * 64, *row, device=DEV).to(torch.bfloat16)
+    host = torch.zeros(6, L, 64, *row, dtype=torch.bfloat16).pin_memory()
+    pairs = torch.tensor([[7, 0], [2, 5], [9, 3]], dtype=torch.int32, device=DEV)
+    ops.kv_pages_copy(kv, pairs, host, True)
+    torch.cuda.synchronize()
+    for page, slab in pairs.tolist():
+        assert torch.equal(host[slab], kv[:, page * 64:(page + 1) * 64].cpu())
+    assert host[1].abs().sum() == 0 and host[2].abs().sum() == 0 and host[4].abs().sum() == 0
+    kv2 = torch.zeros_like(kv)
+    back = torch.tensor([[1, 0], [4, 5], [8, 3]], dtype=torch.int32, device=DEV)
+    ops.kv_pages_copy(kv2, back, host, False)
+    dev_pool = host.to(DEV)
+    kv3 = torch.zeros_like(kv)
+    ops.kv_pages_copy(kv3, back, dev_pool, False)                      # the pool may also be device memory (staging buffer)
+    ops.l2_prefetch(kv)
+    ops.l2_prefetch(kv.view(-1)[:1000 * 8])
+    torch.cuda.synchronize()
+    for (dst, slab), (src, _) in zip(back.tolist(), pairs.tolist()):
+        want = kv[:, src * 64:(src + 1) * 64]
+        assert torch.equal(kv2[:, dst * 64:(dst + 1) * 64], want) and torch.equal(kv3[:, dst * 64:(dst + 1) * 64], want)
+    assert kv2[:, :64].abs().sum() == 0

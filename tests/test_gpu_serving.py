@@ -83,3 +83,25 @@ def test_scheduler_with_mtp_drafter_is_lossless():
     got = run_requests(sched, prompts, 14)
     assert got == want
     assert drafter.proposed > 0 and sched.stats["drafted"] > 0
+
+
+def test_host_tier_restores_an_evicted_prefix_exactly():
+    """Pages written behind into pinned host memory and copied back give the same tokens as the device-resident prefix."""
+    from cuteafd_b200.serving.hostcache import attach_host_tier
+    spec, eng, sched, _ = build(prefix=False)
+    pool = sched.pool
+    host = attach_host_tier(eng, 0.05, min_tokens=128)
+    cache = PrefixCache(pool, min_tokens=64, host=host)
+    sched.prefix = cache
+    g = torch.Generator().manual_seed(5)
+    shared = torch.randint(0, spec.vocab, (200,), generator=g).tolist()
+    p1, p2 = shared + [3, 4, 5], shared + [9, 8, 7, 6]
+    ref = run_requests(build(prefix=False)[2], [p1, p2], 12)
+    out1 = run_requests(sched, [p1], 12)[0]
+    cache.evict(10 ** 6)                                               # the device tier forgets the chain
+    assert cache.lookup(p2) == 0 and host.lookup(p2) == 3
+    eng.kv.zero_()                                                     # whatever was on the device is gone for good
+    out2 = run_requests(sched, [p2], 12)[0]
+    eng.check_status()
+    assert out1 == ref[0] and out2 == ref[1]
+    assert cache.stats["host_hits"] == 1 and cache.stats["host_hit_tokens"] == 192 and host.copy.launches >= 2

@@ -37,3 +37,35 @@ def test_budget_and_lru_eviction():
 def test_simulator_shows_the_host_tier_paying_off():
     r = simulate(n_requests=300)
     assert r["host_hits"] > 0 and r["saved_ms"] > r["copy_ms"] and r["device_hits"] + r["host_hits"] + r["cold"] == 300
+
+
+def test_prefix_cache_writes_evicted_chains_behind_and_restores_them():
+    from cuteafd_b200.engine.kv import PagePool
+    from cuteafd_b200.serving.prefix import PrefixCache
+    eng = StubCopyEngine(page_bytes=4096)
+    hc = HostCache(eng, n_slabs=64, page_bytes=4096, min_tokens=128)
+    pool = PagePool(12)
+    pc = PrefixCache(pool, max_entries=4, min_tokens=64, max_cached_pages=8, host=hc)
+    a = _toks(1, 4) + [7, 8, 9]
+    adm = pc.admit(a, reserve_new=1)
+    assert adm.hit_tokens == 0
+    for i, p in enumerate(adm.seq.pages[:4]):
+        eng.device[p] = ("a", i)                                   # what a prefill would have written
+    adm.seq.length = len(a)
+    pc.capture(a, adm.seq)
+    pc.release(adm.seq)
+    assert pc.lookup(a) == 256
+    pc.evict(100)                                                  # device tier loses the chain; the host tier keeps it
+    assert pc.lookup(a) == 0 and hc.lookup(a) == 4 and pc.stats["host_stored_pages"] == 4
+    for p in list(eng.device):
+        eng.device[p] = None                                       # device pages get reused by someone else
+    adm2 = pc.admit(a, reserve_new=1)
+    assert adm2.hit_tokens == 256 and pc.stats["host_hits"] == 1
+    assert [eng.device[p] for p in adm2.seq.pages[:4]] == [("a", i) for i in range(4)]
+    assert pc.lookup(a) == 256                                     # restored pages are ordinary device entries again
+    pc.release(adm2.seq)
+    # a prompt sharing two pages restores only those
+    pc.evict(100)
+    b = a[:128] + _toks(2, 2)
+    adm3 = pc.admit(b, reserve_new=1)
+    assert adm3.hit_tokens == 128
