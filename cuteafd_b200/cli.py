@@ -114,11 +114,12 @@ def build_serving(a):
 def cmd_serve(a) -> int:
     from .loader.tokenizer import load_tokenizer
     from .serving.api import ServingLoop, build_app
+    from .serving.chat_templates import template_for
     spec, sched = build_serving(a)
     loop = ServingLoop(sched).start()
     keys = set(open(a.api_key_file).read().split()) if a.api_key_file else None
     app = build_app(loop, model_id=a.model_id or spec.name, tokenizer=load_tokenizer(a.model if os.path.isdir(a.model) else None),
-                    api_keys=keys, max_output=a.max_output)
+                    api_keys=keys, max_output=a.max_output, template=template_for(a.chat_template or spec.name))
     host, port = a.listen.rsplit(":", 1)
     import uvicorn
     uvicorn.run(app, host=host, port=int(port), log_level="info")
@@ -221,6 +222,7 @@ def main(argv=None) -> int:
     p.add_argument("--decode-share", type=float, default=0.2); p.add_argument("--prefix-cache-entries", type=int, default=20)
     p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram", "mtp"])
     p.add_argument("--host-cache-gib", type=float, default=0.0, help="pinned host memory behind the prefix cache (0 = off)")
+    p.add_argument("--chat-template", default="", help="chat template family (chatml / qwen3-coder / deepseek / glm / plain); default: by model name")
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.set_defaults(fn=cmd_serve)

@@ -15,23 +15,52 @@ import uuid
 
 from ..loader.tokenizer import StreamDecoder, load_tokenizer
 from ..ref.sampler import SamplingParams
+from .chat_templates import ChatTemplate, parse_completion, template_for
+from .constraints import ChoiceConstraint, constraint_from_request
 from .scheduler import Request, Scheduler
 
 KEEPALIVE_S = 15.0
 
 
 def render_chat(messages, system=None) -> str:
-    """Minimal role-tagged prompt rendering (model-specific chat templates plug in here)."""
-    parts = []
-    if system:
-        parts.append(f"<|system|>\n{system}\n")
-    for m in messages:
+    """Role-tagged prompt of the plain template (models without a chat template, byte tokenizer)."""
+    return ChatTemplate().render(messages, system=system)
+
+
+def _anthropic_to_openai(body: dict) -> tuple[list, list]:
+    """Anthropic Messages content blocks -> OpenAI-style messages and tool specs (gateway/anthropic.rs mapping)."""
+    msgs = []
+    for m in body.get("messages", []):
         content = m.get("content")
-        if isinstance(content, list):
-            content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
-        parts.append(f"<|{m.get('role', 'user')}|>\n{content}\n")
-    parts.append("<|assistant|>\n")
-    return "".join(parts)
+        if not isinstance(content, list):
+            msgs.append({"role": m.get("role", "user"), "content": content})
+            continue
+        text, calls = [], []
+        for b in content:
+            kind = b.get("type")
+            if kind == "text":
+                text.append(b.get("text", ""))
+            elif kind == "tool_use":
+                calls.append({"id": b.get("id"), "function": {"name": b.get("name"), "arguments": b.get("input", {})}})
+            elif kind == "tool_result":
+                inner = b.get("content")
+                if isinstance(inner, list):
+                    inner = "".join(x.get("text", "") for x in inner if isinstance(x, dict))
+                msgs.append({"role": "tool", "tool_call_id": b.get("tool_use_id"), "content": inner or ""})
+        if text or calls:
+            msg = {"role": m.get("role", "user"), "content": "".join(text)}
+            if calls:
+                msg["tool_calls"] = calls
+            msgs.append(msg)
+    tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
+                                               "parameters": t.get("input_schema") or {"type": "object", "properties": {}}}}
+             for t in body.get("tools") or [] if t.get("name")]
+    return msgs, tools
+
+
+def _cut_at_stop(text: str, stops) -> tuple[str, bool]:
+    cut = min((i for i in (text.find(s) for s in stops if s) if i >= 0), default=-1)
+    return (text[:cut], True) if cut >= 0 else (text, False)
 
 
 class ServingLoop:
@@ -100,12 +129,31 @@ except ImportError:      # pragma: no cover - the HTTP layer is optional
     FastAPI = None
 
 
-def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=None, api_keys=None, max_output: int = 4096):
+def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=None, api_keys=None, max_output: int = 4096, template=None):
     if FastAPI is None:
         raise RuntimeError("fastapi is not installed")
 
     tok = tokenizer or load_tokenizer(None)
+    tmpl = template or template_for(model_id)
+    vocab_size = getattr(tok, "vocab_size", None)
     app = FastAPI(title="cuteafd-b200")
+
+    def chat_options(body: dict):
+        """(thinking, stop strings) of a request."""
+        kw = body.get("chat_template_kwargs") or {}
+        thinking = bool(kw.get("enable_thinking", kw.get("thinking", False)) or (body.get("thinking") or {}).get("type") == "enabled")
+        stop = body.get("stop") or body.get("stop_sequences") or []
+        stop = [stop] if isinstance(stop, str) else [x for x in stop if isinstance(x, str)]
+        return thinking, list(tmpl.stop_strings) + stop
+
+    def constraint_for(body: dict, prompt_len: int):
+        if vocab_size is None:
+            return None
+        eos = getattr(tok, "eos_id", None)
+        c = constraint_from_request(body, tok, vocab_size, prompt_len, eos)
+        if c is None and isinstance(body.get("guided_choice"), list):
+            c = ChoiceConstraint(tok, vocab_size, prompt_len, [str(x) for x in body["guided_choice"]], eos)
+        return c
 
     def auth(authorization, x_api_key=None):
         if not api_keys:
@@ -122,7 +170,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         except ValueError as e:
             raise HTTPException(400, str(e))
 
-    def start_generation(prompt_ids, body, max_tokens):
+    def start_generation(prompt_ids, body, max_tokens, constraint=None):
         if not loop.healthy():
             raise HTTPException(503, loop.died or loop.sched.fatal or "unavailable")
         events: asyncio.Queue = asyncio.Queue()
@@ -132,7 +180,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         def on_token(toks, done, reason):
             aloop.call_soon_threadsafe(events.put_nowait, (toks, done, reason))
         req = Request(rid, prompt_ids, max_tokens=max(1, min(max_tokens, max_output)), sampling=sampling_from(body),
-                      eos_id=getattr(tok, "eos_id", None), on_token=on_token)
+                      eos_id=getattr(tok, "eos_id", None), on_token=on_token, constraint=constraint)
         if not loop.submit(req):
             raise HTTPException(429, "admission queue is full")
         return rid, events
@@ -157,6 +205,18 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         return {"lanes": [{"rid": a.req.rid, "prompt": len(a.req.prompt), "prefilled": a.prefilled, "generated": len(a.out),
                            "cache_hit": a.cache_hit} for a in s.active], "queue": len(s.queue), "stats": s.snapshot()}
 
+    def openai_calls(calls):
+        return [{"id": c["id"], "type": "function", "function": {"name": c["name"], "arguments": json.dumps(c["arguments"], ensure_ascii=False)}}
+                for c in calls]
+
+    async def collect(events):
+        ids, reason = [], None
+        while True:
+            toks, done, reason = await events.get()
+            ids += toks
+            if done:
+                return ids, reason
+
     @app.post("/v1/chat/completions")
     async def chat(http: HttpRequest, authorization: str = Header(None)):
         auth(authorization)
@@ -164,31 +224,53 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         msgs = body.get("messages")
         if not isinstance(msgs, list) or not msgs:
             raise HTTPException(400, "messages must be a non-empty list")
-        prompt_ids = tok.encode(render_chat(msgs))
+        thinking, stops = chat_options(body)
+        tools = body.get("tools") if body.get("tool_choice") != "none" else None
+        prompt_ids = tok.encode(tmpl.render(msgs, tools=tools, thinking=thinking))
         max_tokens = int(body.get("max_completion_tokens") or body.get("max_tokens") or 256)
-        rid, events = start_generation(prompt_ids, body, max_tokens)
+        rid, events = start_generation(prompt_ids, body, max_tokens, constraint_for(body, len(prompt_ids)))
         created, cid = int(time.time()), "chatcmpl-" + rid
 
-        async def gather():
-            ids, reason = [], None
-            while True:
-                toks, done, reason = await events.get()
-                ids += toks
-                if done:
-                    return ids, reason
         if not body.get("stream"):
-            ids, reason = await gather()
+            ids, reason = await collect(events)
             if reason and reason.startswith(("error", "unavailable")):
                 raise HTTPException(503 if "unavailable" in reason or "transport" in reason else 500, reason)
+            text, stopped = _cut_at_stop(tok.decode(ids), stops)
+            parsed = parse_completion(tmpl, text, thinking)
+            message = {"role": "assistant", "content": parsed["content"]}
+            if parsed["reasoning"]:
+                message["reasoning_content"] = parsed["reasoning"]
+            if parsed["tool_calls"]:
+                message["tool_calls"] = openai_calls(parsed["tool_calls"])
+            finish = "tool_calls" if parsed["tool_calls"] else ("stop" if stopped else reason)
             return {"id": cid, "object": "chat.completion", "created": created, "model": model_id,
-                    "choices": [{"index": 0, "message": {"role": "assistant", "content": tok.decode(ids)}, "finish_reason": reason}],
+                    "choices": [{"index": 0, "message": message, "finish_reason": finish}],
                     "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": len(ids), "total_tokens": len(prompt_ids) + len(ids)}}
 
         async def sse():
-            dec = StreamDecoder(tok)
-            def chunk(delta, finish=None):
-                return "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_id,
-                                              "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}) + "\n\n"
+            dec, parser = StreamDecoder(tok), tmpl.parser(thinking)
+            held, n_calls, n_out = "", 0, 0
+            hold = max((len(x) for x in stops), default=1) - 1         # text that may still become a stop string stays back
+
+            def chunk(delta, finish=None, usage=None):
+                d = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_id,
+                     "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+                if usage:
+                    d["usage"] = usage
+                return "data: " + json.dumps(d) + "\n\n"
+
+            def deltas(evs):
+                nonlocal n_calls
+                out = []
+                for kind, x in evs:
+                    if kind == "content" and x:
+                        out.append(chunk({"content": x}))
+                    elif kind == "reasoning" and x:
+                        out.append(chunk({"reasoning_content": x}))
+                    elif kind == "tool_call":
+                        out.append(chunk({"tool_calls": [dict(openai_calls([x])[0], index=n_calls)]}))
+                        n_calls += 1
+                return out
             yield chunk({"role": "assistant"})
             try:
                 while True:
@@ -197,22 +279,38 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                     except asyncio.TimeoutError:
                         yield ": keepalive\n\n"
                         continue
-                    text = dec.push(toks) if toks else ""
-                    if text:
-                        yield chunk({"content": text})
-                    if done:
-                        yield chunk({}, reason)
+                    n_out += len(toks)
+                    held += dec.push(toks) if toks else ""
+                    cut, stopped = _cut_at_stop(held, stops)
+                    if stopped or done:
+                        for c in deltas(parser.push(cut) + parser.finish()):
+                            yield c
+                        finish = "tool_calls" if n_calls else ("stop" if stopped else reason)
+                        usage = {"prompt_tokens": len(prompt_ids), "completion_tokens": n_out, "total_tokens": len(prompt_ids) + n_out}
+                        yield chunk({}, finish, usage if (body.get("stream_options") or {}).get("include_usage") else None)
                         yield "data: [DONE]\n\n"
                         return
+                    safe = len(held) - hold
+                    if safe > 0:
+                        for c in deltas(parser.push(held[:safe])):
+                            yield c
+                        held = held[safe:]
             finally:
                 loop.cancel(rid)
         return StreamingResponse(sse(), media_type="text/event-stream")
 
+    def anthropic_prompt(body):
+        msgs, tools = _anthropic_to_openai(body)
+        system = body.get("system")
+        if isinstance(system, list):
+            system = "".join(b.get("text", "") for b in system if isinstance(b, dict))
+        thinking, stops = chat_options(body)
+        return tok.encode(tmpl.render(msgs, tools=tools or None, system=system or None, thinking=thinking)), thinking, stops
+
     @app.post("/v1/messages/count_tokens")
     async def count_tokens(http: HttpRequest, authorization: str = Header(None), x_api_key: str = Header(None)):
         auth(authorization, x_api_key)
-        body = await http.json()
-        return {"input_tokens": len(tok.encode(render_chat(body.get("messages", []), body.get("system"))))}
+        return {"input_tokens": len(anthropic_prompt(await http.json())[0])}
 
     @app.post("/v1/messages")
     async def messages(http: HttpRequest, authorization: str = Header(None), x_api_key: str = Header(None)):
@@ -220,18 +318,93 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         body = await http.json()
         if "max_tokens" not in body:
             raise HTTPException(400, "max_tokens is required")
-        prompt_ids = tok.encode(render_chat(body.get("messages", []), body.get("system") if isinstance(body.get("system"), str) else None))
+        prompt_ids, thinking, stops = anthropic_prompt(body)
         rid, events = start_generation(prompt_ids, body, int(body["max_tokens"]))
-        ids, reason = [], None
-        while True:
-            toks, done, reason = await events.get()
-            ids += toks
-            if done:
-                break
-        if reason and reason.startswith(("error", "unavailable")):
-            raise HTTPException(503, reason)
-        return {"id": "msg_" + rid, "type": "message", "role": "assistant", "model": model_id,
-                "content": [{"type": "text", "text": tok.decode(ids)}], "stop_reason": "end_turn" if reason == "stop" else "max_tokens",
-                "usage": {"input_tokens": len(prompt_ids), "output_tokens": len(ids)}}
+        mid = "msg_" + rid
+
+        def blocks_of(parsed):
+            out = []
+            if parsed["reasoning"]:
+                out.append({"type": "thinking", "thinking": parsed["reasoning"]})
+            if parsed["content"] or not parsed["tool_calls"]:
+                out.append({"type": "text", "text": parsed["content"]})
+            out += [{"type": "tool_use", "id": "toolu_" + c["id"][5:], "name": c["name"], "input": c["arguments"]} for c in parsed["tool_calls"]]
+            return out
+
+        def stop_reason(parsed, stopped, reason):
+            return "tool_use" if parsed["tool_calls"] else ("stop_sequence" if stopped and body.get("stop_sequences") else
+                                                            ("end_turn" if stopped or reason == "stop" else "max_tokens"))
+        if not body.get("stream"):
+            ids, reason = await collect(events)
+            if reason and reason.startswith(("error", "unavailable")):
+                raise HTTPException(503, reason)
+            text, stopped = _cut_at_stop(tok.decode(ids), stops)
+            parsed = parse_completion(tmpl, text, thinking)
+            return {"id": mid, "type": "message", "role": "assistant", "model": model_id, "content": blocks_of(parsed),
+                    "stop_reason": stop_reason(parsed, stopped, reason), "stop_sequence": None,
+                    "usage": {"input_tokens": len(prompt_ids), "output_tokens": len(ids)}}
+
+        async def sse():
+            """Anthropic event stream; blocks are emitted whole-block-at-a-time per parser event."""
+            def ev(name, data):
+                return f"event: {name}\ndata: " + json.dumps(dict(data, type=name)) + "\n\n"
+            yield ev("message_start", {"message": {"id": mid, "type": "message", "role": "assistant", "model": model_id, "content": [],
+                                                   "stop_reason": None, "usage": {"input_tokens": len(prompt_ids), "output_tokens": 0}}})
+            dec, parser = StreamDecoder(tok), tmpl.parser(thinking)
+            held, n_out, index, open_kind, any_call = "", 0, -1, None, False
+            hold = max((len(x) for x in stops), default=1) - 1
+
+            def emit(evs):
+                nonlocal index, open_kind, any_call
+                out = []
+                for kind, x in evs:
+                    want = {"content": "text", "reasoning": "thinking", "tool_call": "tool_use"}[kind]
+                    if kind != "tool_call" and not x:
+                        continue
+                    if open_kind is not None and (open_kind != want or want == "tool_use"):
+                        out.append(ev("content_block_stop", {"index": index}))
+                        open_kind = None
+                    if open_kind is None:
+                        index += 1
+                        start = ({"type": "text", "text": ""} if want == "text" else {"type": "thinking", "thinking": ""} if want == "thinking"
+                                 else {"type": "tool_use", "id": "toolu_" + x["id"][5:], "name": x["name"], "input": {}})
+                        out.append(ev("content_block_start", {"index": index, "content_block": start}))
+                        open_kind = want
+                    if want == "text":
+                        out.append(ev("content_block_delta", {"index": index, "delta": {"type": "text_delta", "text": x}}))
+                    elif want == "thinking":
+                        out.append(ev("content_block_delta", {"index": index, "delta": {"type": "thinking_delta", "thinking": x}}))
+                    else:
+                        any_call = True
+                        out.append(ev("content_block_delta", {"index": index, "delta": {"type": "input_json_delta",
+                                                                                       "partial_json": json.dumps(x["arguments"], ensure_ascii=False)}}))
+                return out
+            try:
+                while True:
+                    try:
+                        toks, done, reason = await asyncio.wait_for(events.get(), KEEPALIVE_S)
+                    except asyncio.TimeoutError:
+                        yield ev("ping", {})
+                        continue
+                    n_out += len(toks)
+                    held += dec.push(toks) if toks else ""
+                    cut, stopped = _cut_at_stop(held, stops)
+                    if stopped or done:
+                        for c in emit(parser.push(cut) + parser.finish()):
+                            yield c
+                        if open_kind is not None:
+                            yield ev("content_block_stop", {"index": index})
+                        sr = "tool_use" if any_call else ("end_turn" if stopped or reason == "stop" else "max_tokens")
+                        yield ev("message_delta", {"delta": {"stop_reason": sr, "stop_sequence": None}, "usage": {"output_tokens": n_out}})
+                        yield ev("message_stop", {})
+                        return
+                    safe = len(held) - hold
+                    if safe > 0:
+                        for c in emit(parser.push(held[:safe])):
+                            yield c
+                        held = held[safe:]
+            finally:
+                loop.cancel(rid)
+        return StreamingResponse(sse(), media_type="text/event-stream")
 
     return app

@@ -1,0 +1,299 @@
+"""Structured output: token masks that keep a completion inside a grammar.
+
+A constraint object has `mask(tokens) -> int32 bit words [ceil(vocab / 32)] | None` (bit set = token allowed), which is
+what the runner hands to the masked argmax / sampler kernels for rows that carry one.  Two grammars are built in:
+
+  * `JsonConstraint`: the completion must be one JSON value (optionally an object / array at the top, for
+    `response_format = json_object` and the top-level type of a `json_schema`), then end of sequence;
+  * `ChoiceConstraint`: the completion must be exactly one of a list of strings (tool_choice by name, enums).
+
+Both work on the decoded text of single tokens, so they run with any tokenizer that can decode one id at a time.  The
+JSON automaton is a character-level pushdown recogniser of JSON *prefixes*; masks are cached per automaton state, so a
+long string or number costs one vocabulary scan, not one per token.
+
+Reference: cuteafd-api/src/openai/constraints.rs (grammar specs handed to the sampler as per-row token masks),
+shared/constraints.rs (`SelectBatch` masks).
+"""
+from __future__ import annotations
+
+import torch
+
+WS = " \t\n\r"
+
+
+class JsonPrefix:
+    """Recogniser of prefixes of one JSON value.  `feed(ch)` returns False when `ch` cannot follow."""
+    __slots__ = ("stack", "mode", "lit", "lit_pos", "hex_left", "num", "done", "top")
+
+    def __init__(self, top: str | None = None):
+        self.stack: list[str] = []      # "{" / "[" frames; the mode says where in the frame we are
+        self.mode = "value"             # value | string | key | escape | kescape | hex | khex | number | literal | after | key_start | key_or_end | colon | value_or_end
+        self.lit, self.lit_pos, self.hex_left, self.num = "", 0, 0, ""
+        self.done = False
+        self.top = top                  # None | "object" | "array"
+
+    def copy(self) -> "JsonPrefix":
+        c = JsonPrefix(self.top)
+        c.stack, c.mode, c.lit, c.lit_pos, c.hex_left, c.num, c.done = list(self.stack), self.mode, self.lit, self.lit_pos, self.hex_left, self.num, self.done
+        return c
+
+    def signature(self):
+        return (tuple(self.stack), self.mode, self.lit, self.lit_pos, self.hex_left, self._num_class(), self.done)
+
+    # -------------------------------------------------------------- numbers: -?(0|[1-9]\d*)(\.\d+)?([eE][+-]?\d+)?
+    def _num_class(self) -> str:
+        n = self.num
+        if not n:
+            return ""
+        if n == "-":
+            return "sign"
+        if "e" in n or "E" in n:
+            tail = n.replace("E", "e").split("e", 1)[1]
+            return "exp0" if tail == "" else ("expsign" if tail in "+-" else "exp")
+        if "." in n:
+            return "frac0" if n.endswith(".") else "frac"
+        return "zero" if n.lstrip("-") == "0" else "int"
+
+    def _num_can_end(self) -> bool:
+        return self._num_class() in ("zero", "int", "frac", "exp")
+
+    def _num_feed(self, ch: str) -> bool:
+        c = self._num_class()
+        if ch.isdigit() and ch.isascii():
+            if c == "zero":
+                return False
+            self.num += ch
+            return True
+        if ch == "." and c in ("zero", "int"):
+            self.num += ch
+            return True
+        if ch in "eE" and c in ("zero", "int", "frac"):
+            self.num += ch
+            return True
+        if ch in "+-" and c == "exp0":
+            self.num += ch
+            return True
+        return False
+
+    # -------------------------------------------------------------- transitions
+    def _value_done(self):
+        if not self.stack:
+            self.done, self.mode = True, "after"
+        else:
+            self.mode = "after"
+
+    def _start_value(self, ch: str) -> bool:
+        if not self.stack and self.top and not self.done:
+            if (self.top == "object" and ch != "{") or (self.top == "array" and ch != "["):
+                return False
+        if ch == "{":
+            self.stack.append("{"); self.mode = "key_or_end"; return True
+        if ch == "[":
+            self.stack.append("["); self.mode = "value_or_end"; return True
+        if ch == '"':
+            self.mode = "string"; return True
+        if ch == "-" or (ch.isdigit() and ch.isascii()):
+            self.num, self.mode = ch, "number"; return True
+        for lit in ("true", "false", "null"):
+            if ch == lit[0]:
+                self.lit, self.lit_pos, self.mode = lit, 1, "literal"; return True
+        return False
+
+    def feed(self, ch: str) -> bool:
+        m = self.mode
+        if m in ("string", "key"):
+            if ch == '"':
+                if m == "key":
+                    self.mode = "colon"
+                else:
+                    self._value_done()
+                return True
+            if ch == "\\":
+                self.mode = "escape" if m == "string" else "kescape"
+                return True
+            return ch >= " "
+        if m in ("escape", "kescape"):
+            back = "string" if m == "escape" else "key"
+            if ch in '"\\/bfnrt':
+                self.mode = back; return True
+            if ch == "u":
+                self.hex_left, self.mode = 4, "hex" if m == "escape" else "khex"; return True
+            return False
+        if m in ("hex", "khex"):
+            if ch not in "0123456789abcdefABCDEF":
+                return False
+            self.hex_left -= 1
+            if self.hex_left == 0:
+                self.mode = "string" if m == "hex" else "key"
+            return True
+        if m == "literal":
+            if ch != self.lit[self.lit_pos]:
+                return False
+            self.lit_pos += 1
+            if self.lit_pos == len(self.lit):
+                self._value_done()
+            return True
+        if m == "number":
+            if self._num_feed(ch):
+                return True
+            if not self._num_can_end():
+                return False
+            self.num = ""
+            self._value_done()
+            return self.feed(ch)
+        if ch in WS:
+            return True
+        if m == "value":
+            return (not self.done) and self._start_value(ch)
+        if m == "value_or_end":
+            if ch == "]":
+                self.stack.pop(); self._value_done(); return True
+            return self._start_value(ch)
+        if m == "key_or_end":
+            if ch == "}":
+                self.stack.pop(); self._value_done(); return True
+            if ch == '"':
+                self.mode = "key"; return True
+            return False
+        if m == "key_start":
+            if ch == '"':
+                self.mode = "key"; return True
+            return False
+        if m == "colon":
+            if ch == ":":
+                self.mode = "value"; return True
+            return False
+        if m == "after":
+            if not self.stack:
+                return False
+            if ch == ",":
+                self.mode = "key_start" if self.stack[-1] == "{" else "value"; return True
+            if ch == "}" and self.stack[-1] == "{" or ch == "]" and self.stack[-1] == "[":
+                self.stack.pop(); self._value_done(); return True
+            return False
+        return False
+
+    @property
+    def complete(self) -> bool:
+        """The text so far is a whole value (a top-level number also counts once it can end)."""
+        return (self.done and self.mode == "after" and not self.stack) or (not self.stack and self.mode == "number" and self._num_can_end())
+
+    def feed_text(self, text: str) -> bool:
+        for ch in text:
+            if not self.feed(ch):
+                return False
+        return True
+
+
+def _pack_bits(allowed: list[bool]) -> torch.Tensor:
+    n = len(allowed)
+    words = torch.zeros((n + 31) // 32, dtype=torch.int64)
+    idx = torch.tensor([i for i, a in enumerate(allowed) if a], dtype=torch.int64)
+    if idx.numel():
+        words.index_put_((idx >> 5,), torch.ones_like(idx) << (idx & 31), accumulate=True)   # distinct bits: add == or
+    words = torch.where(words >= (1 << 31), words - (1 << 32), words)
+    return words.to(torch.int32)
+
+
+class _TextConstraint:
+    """Shared part: the decoded text of every token id and the prompt length (only generated tokens are constrained)."""
+
+    def __init__(self, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None):
+        self.vocab_size, self.prompt_len, self.eos_id = vocab_size, prompt_len, eos_id
+        self.pieces = token_pieces(tokenizer, vocab_size)
+
+    def _text_of(self, ids) -> str:
+        return "".join(self.pieces[i] or "" for i in ids if 0 <= i < self.vocab_size)
+
+
+_PIECE_CACHE: dict = {}
+
+
+def token_pieces(tokenizer, vocab_size: int) -> list:
+    """Decoded text per token id (None for ids that decode to nothing: specials, padding)."""
+    key = (id(tokenizer), vocab_size)
+    if key not in _PIECE_CACHE:
+        out = []
+        for i in range(vocab_size):
+            try:
+                s = tokenizer.decode([i])
+            except Exception:
+                s = ""
+            out.append(s if s and "�" not in s else None)
+        _PIECE_CACHE[key] = out
+    return _PIECE_CACHE[key]
+
+
+class JsonConstraint(_TextConstraint):
+    def __init__(self, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None = None, top: str | None = "object"):
+        super().__init__(tokenizer, vocab_size, prompt_len, eos_id)
+        self.top = top
+        self.state, self.seen = JsonPrefix(top), 0
+        self.cache: dict = {}
+
+    def _advance(self, tokens):
+        gen = tokens[self.prompt_len:]
+        if len(gen) < self.seen:                       # a speculative tail was rolled back: replay
+            self.state, self.seen = JsonPrefix(self.top), 0
+        for t in gen[self.seen:]:
+            if t != self.eos_id:
+                self.state.feed_text(self.pieces[t] or "")
+        self.seen = len(gen)
+
+    def mask(self, tokens):
+        self._advance(tokens)
+        sig = self.state.signature()
+        m = self.cache.get(sig)
+        if m is None:
+            done = self.state.complete and not self.state.stack and self.state.mode == "after"
+            allowed = [False] * self.vocab_size
+            if not done:
+                for i, piece in enumerate(self.pieces):
+                    if piece and self.state.copy().feed_text(piece):
+                        allowed[i] = True
+            if self.eos_id is not None and 0 <= self.eos_id < self.vocab_size:
+                allowed[self.eos_id] = self.state.complete
+            if not any(allowed) and self.eos_id is not None:
+                allowed[self.eos_id] = True            # never hand the sampler an empty set
+            m = self.cache[sig] = _pack_bits(allowed)
+        return m
+
+
+class ChoiceConstraint(_TextConstraint):
+    """The completion must spell exactly one of `choices`."""
+
+    def __init__(self, tokenizer, vocab_size: int, prompt_len: int, choices: list[str], eos_id: int | None = None):
+        super().__init__(tokenizer, vocab_size, prompt_len, eos_id)
+        self.choices = list(choices)
+
+    def mask(self, tokens):
+        text = self._text_of(t for t in tokens[self.prompt_len:] if t != self.eos_id)
+        live = [c for c in self.choices if c.startswith(text)]
+        allowed = [False] * self.vocab_size
+        for i, piece in enumerate(self.pieces):
+            if piece and any(c.startswith(text + piece) for c in live):
+                allowed[i] = True
+        if self.eos_id is not None and (text in self.choices or not any(allowed)):
+            allowed[self.eos_id] = True
+        return _pack_bits(allowed)
+
+
+def constraint_from_request(body: dict, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None):
+    """OpenAI `response_format` -> constraint (None when the request asks for plain text)."""
+    rf = body.get("response_format") or {}
+    kind = rf.get("type") if isinstance(rf, dict) else None
+    if kind == "json_object":
+        return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, top="object")
+    if kind == "json_schema":
+        schema = (rf.get("json_schema") or {}).get("schema") or {}
+        if isinstance(schema.get("enum"), list) and all(isinstance(e, str) for e in schema["enum"]):
+            import json
+            return ChoiceConstraint(tokenizer, vocab_size, prompt_len, [json.dumps(e) for e in schema["enum"]], eos_id)
+        top = {"object": "object", "array": "array"}.get(schema.get("type"))
+        return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, top=top)
+    return None
+
+
+def unpack_bits(words: torch.Tensor, vocab_size: int) -> list[bool]:
+    w = words.to(torch.int64) & 0xFFFFFFFF
+    return [bool((int(w[i >> 5]) >> (i & 31)) & 1) for i in range(vocab_size)]

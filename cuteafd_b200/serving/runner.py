@@ -41,7 +41,15 @@ class FakeRunner:
             assert len(history) == r.start_pos, "scheduler asked to run a row at a position beyond its history"
             toks = []
             for i in r.want_logits:
-                toks.append(self.next_token(history + r.tokens[:i + 1]))
+                prefix = history + r.tokens[:i + 1]
+                t = self.next_token(prefix)
+                c = getattr(r.state.req, "constraint", None)
+                m = c.mask(prefix) if c is not None else None
+                if m is not None:                        # grammar mask: the fake model's pick moves to an allowed token
+                    w = m.to("cpu").tolist()
+                    allowed = [j for j in range(self.vocab) if (w[j >> 5] >> (j & 31)) & 1]
+                    t = allowed[t % len(allowed)] if allowed else t
+                toks.append(t)
             out.append(toks)
         return out
 

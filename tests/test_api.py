@@ -75,3 +75,97 @@ def test_wire_failure_turns_the_server_unavailable(client):
     assert client.get("/health").status_code == 503
     r = client.post("/v1/chat/completions", headers=H, json={"messages": [{"role": "user", "content": "x"}]})
     assert r.status_code == 503
+
+
+def _scripted_client(script: str, model: str):
+    """Server whose fake model recites `script` (then end of sequence) after any prompt."""
+    from cuteafd_b200.serving.chat_templates import template_for
+    pool = PagePool(512)
+    runner = FakeRunner(vocab=258)
+    data = script.encode()
+    state = {}
+
+    def next_token(prefix):
+        n0 = state.setdefault("prompt", len(prefix))             # the first call sees exactly the prompt
+        i = len(prefix) - n0
+        return data[i] if i < len(data) else 257
+    runner.next_token = next_token
+    loop = ServingLoop(Scheduler(runner, pool), Health()).start()
+    return TestClient(build_app(loop, model_id=model, template=template_for(model))), loop
+
+
+def test_tool_calls_reasoning_and_stop_strings_in_chat_completions():
+    script = "<think>\nuse the tool\n</think>\n\nOn it.\n<tool_call>\n{\"name\": \"get_weather\", \"arguments\": {\"city\": \"Oslo\"}}\n</tool_call><|im_end|>"
+    c, loop = _scripted_client(script, "qwen3-235b")
+    try:
+        body = {"messages": [{"role": "user", "content": "weather?"}], "max_tokens": 200,
+                "tools": [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object"}}}]}
+        m = c.post("/v1/chat/completions", json=body).json()["choices"][0]
+        assert m["finish_reason"] == "tool_calls" and m["message"]["content"] == "On it." and m["message"]["reasoning_content"].strip() == "use the tool"
+        call = m["message"]["tool_calls"][0]
+        assert call["function"]["name"] == "get_weather" and json.loads(call["function"]["arguments"]) == {"city": "Oslo"}
+    finally:
+        loop.stop()
+    c, loop = _scripted_client(script, "qwen3-235b")
+    try:
+        text, reasoning, calls, finish = "", "", [], None
+        with c.stream("POST", "/v1/chat/completions", json=dict(body, stream=True)) as r:
+            for line in r.iter_lines():
+                if line.startswith("data: ") and line != "data: [DONE]":
+                    ch = json.loads(line[6:])["choices"][0]
+                    text += ch["delta"].get("content", "")
+                    reasoning += ch["delta"].get("reasoning_content", "")
+                    calls += ch["delta"].get("tool_calls", [])
+                    finish = ch["finish_reason"] or finish
+        assert finish == "tool_calls" and text.strip() == "On it." and reasoning.strip() == "use the tool" and "<" not in text
+        assert calls[0]["function"]["name"] == "get_weather" and calls[0]["index"] == 0
+    finally:
+        loop.stop()
+    c, loop = _scripted_client("alpha beta STOP gamma", "plain")
+    try:
+        m = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "max_tokens": 50, "stop": ["STOP"]}).json()["choices"][0]
+        assert m["message"]["content"] == "alpha beta " and m["finish_reason"] == "stop"
+    finally:
+        loop.stop()
+
+
+def test_json_mode_masks_the_fake_model_into_json(client):
+    from cuteafd_b200.serving.constraints import JsonPrefix
+    client.loop.sched.runner.vocab = 258
+    r = client.post("/v1/chat/completions", headers=H, json={"messages": [{"role": "user", "content": "json please"}], "max_tokens": 40,
+                                                             "response_format": {"type": "json_object"}}).json()["choices"][0]
+    text = r["message"]["content"]
+    assert text.lstrip().startswith("{") and JsonPrefix("object").feed_text(text)
+    if r["finish_reason"] == "stop":
+        assert isinstance(json.loads(text), dict)
+
+
+def test_anthropic_tools_and_event_stream():
+    script = "Checking.<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Oslo</arg_value>\n</tool_call>"
+    body = {"max_tokens": 200, "messages": [{"role": "user", "content": [{"type": "text", "text": "weather?"}]}],
+            "tools": [{"name": "get_weather", "description": "w", "input_schema": {"type": "object"}}]}
+    c, loop = _scripted_client(script, "glm-5")
+    try:
+        j = c.post("/v1/messages", json=body).json()
+        assert j["stop_reason"] == "tool_use" and [b["type"] for b in j["content"]] == ["text", "tool_use"]
+        assert j["content"][1]["name"] == "get_weather" and j["content"][1]["input"] == {"city": "Oslo"}
+    finally:
+        loop.stop()
+    c, loop = _scripted_client(script, "glm-5")
+    try:
+        names, text, partial = [], "", ""
+        with c.stream("POST", "/v1/messages", json=dict(body, stream=True)) as r:
+            for line in r.iter_lines():
+                if line.startswith("event: "):
+                    names.append(line[7:])
+                elif line.startswith("data: "):
+                    d = json.loads(line[6:])
+                    if d["type"] == "content_block_delta":
+                        text += d["delta"].get("text", "")
+                        partial += d["delta"].get("partial_json", "")
+                    if d["type"] == "message_delta":
+                        assert d["delta"]["stop_reason"] == "tool_use"
+        assert names[0] == "message_start" and names[-1] == "message_stop" and names.count("content_block_start") == 2
+        assert text == "Checking." and json.loads(partial) == {"city": "Oslo"}
+    finally:
+        loop.stop()

@@ -1,0 +1,112 @@
+"""Chat templates, tool-call parsers, the streaming output parser and grammar constraints (CPU only)."""
+import json
+import random
+
+from cuteafd_b200.loader.tokenizer import ByteTokenizer
+from cuteafd_b200.serving.chat_templates import parse_completion, template_for
+from cuteafd_b200.serving.constraints import ChoiceConstraint, JsonConstraint, JsonPrefix, constraint_from_request, unpack_bits
+
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "description": "weather", "parameters": {"type": "object", "properties": {"city": {"type": "string"}}}}}]
+HISTORY = [{"role": "system", "content": "be terse"}, {"role": "user", "content": "weather in Oslo?"},
+           {"role": "assistant", "content": "<think>need the tool</think>\n\nLet me check.",
+            "tool_calls": [{"id": "c1", "type": "function", "function": {"name": "get_weather", "arguments": "{\"city\": \"Oslo\"}"}}]},
+           {"role": "tool", "tool_call_id": "c1", "content": "-3C"}, {"role": "user", "content": "and Bergen?"}]
+
+
+def test_templates_render_roles_tools_and_drop_old_reasoning():
+    q = template_for("qwen3-235b").render(HISTORY, tools=TOOLS, thinking=True)
+    assert q.startswith("<|im_start|>system\nbe terse") and "<tools>" in q and '"name": "get_weather"' in q
+    assert "need the tool" not in q and "Let me check." in q and "<tool_response>\n-3C\n</tool_response>" in q
+    assert q.endswith("<|im_start|>assistant\n<think>\n") and q.count("<|im_start|>user") == 3
+    d = template_for("deepseek-v3").render(HISTORY, tools=TOOLS)
+    assert d.startswith("<｜begin▁of▁sentence｜>be terse") and "<｜tool▁call▁begin｜>function<｜tool▁sep｜>get_weather" in d
+    assert "<｜tool▁output▁begin｜>-3C<｜tool▁output▁end｜>" in d and d.endswith("<｜Assistant｜>") and "need the tool" not in d
+    g = template_for("glm-5").render(HISTORY, tools=TOOLS)
+    assert g.startswith("[gMASK]<sop>") and "<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Oslo</arg_value>" in g and "<|observation|>" in g
+    c = template_for("qwen3-coder").render(HISTORY, tools=TOOLS)
+    assert "<function=get_weather>\n<parameter=city>\nOslo\n</parameter>" in c
+    assert template_for("something-else").render([{"role": "user", "content": "x"}]) == "<|user|>\nx\n<|assistant|>\n"
+
+
+CASES = [
+    ("qwen3-235b", "<think>\nplan\n</think>\n\nSure.\n<tool_call>\n{\"name\": \"get_weather\", \"arguments\": {\"city\": \"Oslo\"}}\n</tool_call><|im_end|>junk", True),
+    ("qwen3-coder", "<tool_call>\n<function=get_weather>\n<parameter=city>\nOslo\n</parameter>\n</function>\n</tool_call>", False),
+    ("glm-5", "Checking.<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Oslo</arg_value>\n</tool_call>", False),
+    ("deepseek-v3", "ok<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>function<｜tool▁sep｜>get_weather\n```json\n{\"city\": \"Oslo\"}\n```<｜tool▁call▁end｜><｜tool▁calls▁end｜>", False),
+]
+
+
+def test_tool_calls_parse_in_every_family_and_streaming_agrees_with_whole_text():
+    for model, text, has_reasoning in CASES:
+        t = template_for(model)
+        whole = parse_completion(t, text)
+        assert [(c["name"], c["arguments"]) for c in whole["tool_calls"]] == [("get_weather", {"city": "Oslo"})], model
+        assert bool(whole["reasoning"]) == has_reasoning and "junk" not in whole["content"]
+        # the same text pushed in random pieces gives the same events, and never leaks a partial tag
+        cut = text.split("<|im_end|>")[0]
+        for seed in range(5):
+            rng, p, ev, i = random.Random(seed), t.parser(), [], 0
+            while i < len(cut):
+                n = rng.randrange(1, 7)
+                ev += p.push(cut[i:i + n])
+                i += n
+            ev += p.finish()
+            content = "".join(x for k, x in ev if k == "content")
+            assert "<tool_call" not in content and "<think" not in content and "tool▁call▁begin" not in content
+            assert [c[1]["name"] for c in ev if c[0] == "tool_call"] == ["get_weather"]
+            assert "".join(x for k, x in ev if k == "reasoning") == whole["reasoning"]
+    broken = parse_completion(template_for("qwen3"), "text <tool_call>\nnot json\n</tool_call> more")
+    assert broken["tool_calls"] == [] and "not json" in broken["content"]          # an unparsable call stays visible as text
+
+
+def test_json_prefix_automaton():
+    for s in ['{"a": [1, 2.5e-3, true, null, "x\\n\\u00e9"], "b": {}}', "[]", "-0.5", '"hi"', " { } ", "[[],{}]", "1E+9"]:
+        p = JsonPrefix()
+        assert p.feed_text(s) and p.complete, s
+        json.loads(s)
+    for s in ["{a", "[1,]", "01", '{"a" 1', "1.e", "tru e", '{"a":1}}', "[1 2]", '{"a":}', '"\\x"', "-", "[1,", '{"a"']:
+        p = JsonPrefix()
+        assert not (p.feed_text(s) and p.complete), s
+    assert not JsonPrefix("object").feed_text("[") and JsonPrefix("array").feed_text("[1")
+
+
+def test_json_constraint_keeps_a_random_walk_inside_json():
+    tok, rng = ByteTokenizer(), random.Random(0)
+    finished = 0
+    for trial in range(12):
+        c, toks = JsonConstraint(tok, 258, 3, eos_id=257, top="object"), [1, 2, 3]
+        for _ in range(300):
+            allowed = [i for i, a in enumerate(unpack_bits(c.mask(toks), 258)) if a]
+            assert allowed
+            closers = [a for a in allowed if a in (257, ord("}"), ord("]"), ord('"'))]
+            toks.append(rng.choice(closers) if closers and rng.random() < 0.4 else rng.choice(allowed))
+            if toks[-1] == 257:
+                break
+        text = tok.decode([t for t in toks[3:] if t != 257])
+        assert JsonPrefix("object").feed_text(text)
+        if toks[-1] == 257:
+            assert isinstance(json.loads(text), dict)
+            finished += 1
+    assert finished >= 6
+    # a rolled-back speculative tail is replayed from the start
+    c = JsonConstraint(tok, 258, 0, eos_id=257)
+    c.mask(list(b'{"a"'))
+    assert ord(":") in [i for i, a in enumerate(unpack_bits(c.mask(list(b'{"a"')), 258)) if a]
+    assert ord('"') in [i for i, a in enumerate(unpack_bits(c.mask(list(b"{")), 258)) if a]
+
+
+def test_choice_constraint_and_response_format_mapping():
+    tok = ByteTokenizer()
+    ch, t = ChoiceConstraint(tok, 258, 0, ["get_weather", "get_time"], eos_id=257), []
+    for _ in range(20):
+        al = [i for i, a in enumerate(unpack_bits(ch.mask(t), 258)) if a]
+        t.append(al[0])
+        if t[-1] == 257:
+            break
+    assert tok.decode(t[:-1]) in ("get_weather", "get_time") and t[-1] == 257
+    assert constraint_from_request({}, tok, 258, 0, 257) is None
+    assert isinstance(constraint_from_request({"response_format": {"type": "json_object"}}, tok, 258, 0, 257), JsonConstraint)
+    c = constraint_from_request({"response_format": {"type": "json_schema", "json_schema": {"schema": {"type": "array"}}}}, tok, 258, 0, 257)
+    assert c.top == "array"
+    e = constraint_from_request({"response_format": {"type": "json_schema", "json_schema": {"schema": {"enum": ["a", "b"]}}}}, tok, 258, 0, 257)
+    assert isinstance(e, ChoiceConstraint) and e.choices == ['"a"', '"b"']
