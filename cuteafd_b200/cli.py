@@ -118,11 +118,56 @@ def cmd_serve(a) -> int:
     spec, sched = build_serving(a)
     loop = ServingLoop(sched).start()
     keys = set(open(a.api_key_file).read().split()) if a.api_key_file else None
+    usage = thermal = None
+    if a.usage == "on":
+        from .serving.usage import UsageStore
+        os.makedirs(a.usage_dir, exist_ok=True)
+        usage = UsageStore(os.path.join(a.usage_dir, "usage.sqlite"))
+    try:
+        from .utils.thermal import ThermalMonitor
+        thermal = ThermalMonitor()
+    except Exception:
+        thermal = None
     app = build_app(loop, model_id=a.model_id or spec.name, tokenizer=load_tokenizer(a.model if os.path.isdir(a.model) else None),
-                    api_keys=keys, max_output=a.max_output, template=template_for(a.chat_template or spec.name))
+                    api_keys=keys, max_output=a.max_output, template=template_for(a.chat_template or spec.name),
+                    usage=usage, enable_bench=a.enable_bench, thermal=thermal)
     host, port = a.listen.rsplit(":", 1)
     import uvicorn
     uvicorn.run(app, host=host, port=int(port), log_level="info")
+    return 0
+
+
+def cmd_usage(a) -> int:
+    """`usage clear | clear-log | export-csv | demo`: manage the request history without a browser; `demo` serves
+    `/usage` over a synthetic history (no GPU, no model).  Reference: cuteafd-daemon/src/commands/usage.rs."""
+    import sys
+    from .serving.usage import UsageStore, synthetic_history
+    path = os.path.join(a.dir, "usage.sqlite") if a.dir != ":memory:" else ":memory:"
+    if a.action == "demo":
+        from .engine.kv import PagePool
+        from .serving.api import ServingLoop, build_app
+        from .serving.runner import FakeRunner
+        from .serving.scheduler import Scheduler
+        store = UsageStore(":memory:")
+        synthetic_history(store)
+        loop = ServingLoop(Scheduler(FakeRunner(vocab=258), PagePool(256))).start()
+        app = build_app(loop, model_id="demo-model", usage=store)
+        host, port = a.listen.rsplit(":", 1)
+        import uvicorn
+        uvicorn.run(app, host=host, port=int(port), log_level="info")
+        return 0
+    os.makedirs(a.dir, exist_ok=True)
+    store = UsageStore(path)
+    if a.action == "clear":
+        store.clear()
+    elif a.action == "clear-log":
+        store.clear_log()
+    elif a.action == "export-csv":
+        out = open(a.out, "w", newline="") if a.out else sys.stdout
+        n = store.export_csv(out, a.range)
+        if a.out:
+            out.close()
+            print(f"{n} rows -> {a.out}")
     return 0
 
 
@@ -222,6 +267,8 @@ def main(argv=None) -> int:
     p.add_argument("--decode-share", type=float, default=0.2); p.add_argument("--prefix-cache-entries", type=int, default=20)
     p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram", "mtp"])
     p.add_argument("--host-cache-gib", type=float, default=0.0, help="pinned host memory behind the prefix cache (0 = off)")
+    p.add_argument("--usage", default="off", choices=["on", "off"]); p.add_argument("--enable-bench", action="store_true")
+    p.add_argument("--usage-dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage"))
     p.add_argument("--chat-template", default="", help="chat template family (chatml / qwen3-coder / deepseek / glm / plain); default: by model name")
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
@@ -235,6 +282,9 @@ def main(argv=None) -> int:
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--layers", type=int, default=0)
     p.add_argument("--c1-tokens", type=int, default=320); p.add_argument("--prefill-tokens", type=int, default=8192)
     p.set_defaults(fn=cmd_card)
+    p = sub.add_parser("usage"); p.add_argument("action", choices=["clear", "clear-log", "export-csv", "demo"])
+    p.add_argument("--dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage")); p.add_argument("--range", default="7d", choices=["1h", "6h", "24h", "7d"])
+    p.add_argument("--out", default=""); p.add_argument("--listen", default="127.0.0.1:8010"); p.set_defaults(fn=cmd_usage)
     p = sub.add_parser("golden"); p.add_argument("--experts", default="bf16"); p.add_argument("--seed", type=int, default=0); p.set_defaults(fn=cmd_golden)
     p = sub.add_parser("expertd"); p.add_argument("--listen", default="127.0.0.1:7000"); p.add_argument("--rank", type=int, default=0); p.set_defaults(fn=cmd_expertd)
     p = sub.add_parser("bench"); p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)

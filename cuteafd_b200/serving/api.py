@@ -129,7 +129,11 @@ except ImportError:      # pragma: no cover - the HTTP layer is optional
     FastAPI = None
 
 
-def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=None, api_keys=None, max_output: int = 4096, template=None):
+def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=None, api_keys=None, max_output: int = 4096, template=None,
+              usage=None, enable_bench: bool = False, thermal=None):
+    """`usage`: a `UsageStore` that gets one row per finished request and backs `/usage`.  `enable_bench` turns on the
+    probe header `x-cuteafd-probe` (JSON: `skip_cache`, `no_drafts`, `token_ids`) that benchmarks use to pin what a
+    request exercises (cuteafd-api/src/openai/probe.rs).  `thermal`: object with `.sample()` for `/v1/thermal`."""
     if FastAPI is None:
         raise RuntimeError("fastapi is not installed")
 
@@ -170,17 +174,44 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         except ValueError as e:
             raise HTTPException(400, str(e))
 
-    def start_generation(prompt_ids, body, max_tokens, constraint=None):
+    gen_meta: dict = {}
+
+    def key_of(authorization, x_api_key=None):
+        k = (authorization or "").removeprefix("Bearer ").strip() or (x_api_key or "")
+        return (k[:6] + "...") if k else "-"
+
+    def account(rid, key, t0, t_first, n_prompt, n_out, finish):
+        if usage is None:
+            return
+        now = time.time()
+        hit = gen_meta.pop(rid, {}).get("hit", 0)
+        usage.record(rid, model_id, key, n_prompt, n_out, hit, ((t_first or now) - t0) * 1e3, (now - t0) * 1e3, finish or "")
+
+    def probe_of(http) -> dict:
+        if not enable_bench:
+            return {}
+        try:
+            d = json.loads(http.headers.get("x-cuteafd-probe") or "{}")
+            return d if isinstance(d, dict) else {}
+        except json.JSONDecodeError:
+            raise HTTPException(400, "x-cuteafd-probe is not JSON")
+
+    def start_generation(prompt_ids, body, max_tokens, constraint=None, probe=None):
         if not loop.healthy():
             raise HTTPException(503, loop.died or loop.sched.fatal or "unavailable")
         events: asyncio.Queue = asyncio.Queue()
         aloop = asyncio.get_running_loop()
         rid = uuid.uuid4().hex[:16]
 
+        meta = gen_meta[rid] = {}
+
         def on_token(toks, done, reason):
+            if "hit" not in meta:        # runs on the scheduler thread while the request is still active
+                meta["hit"] = next((a.cache_hit for a in loop.sched.active if a.req.rid == rid), 0)
             aloop.call_soon_threadsafe(events.put_nowait, (toks, done, reason))
         req = Request(rid, prompt_ids, max_tokens=max(1, min(max_tokens, max_output)), sampling=sampling_from(body),
-                      eos_id=getattr(tok, "eos_id", None), on_token=on_token, constraint=constraint)
+                      eos_id=getattr(tok, "eos_id", None), on_token=on_token, constraint=constraint,
+                      use_cache=not (probe or {}).get("skip_cache", False), allow_drafts=not (probe or {}).get("no_drafts", False))
         if not loop.submit(req):
             raise HTTPException(429, "admission queue is full")
         return rid, events
@@ -198,6 +229,17 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
     @app.get("/v1/stats")
     async def stats():
         return dict(loop.sched.snapshot(), uptime_s=round(time.time() - loop.started, 1), healthy=loop.healthy())
+
+    @app.get("/v1/thermal")
+    async def thermal_ep():
+        return thermal.sample() if thermal is not None else {"available": False}
+
+    @app.get("/usage")
+    async def usage_ep(authorization: str = Header(None)):
+        auth(authorization)
+        if usage is None:
+            raise HTTPException(404, "usage accounting is off")
+        return {"totals": usage.totals(), "daily": usage.daily(), "by_key": usage.by_key()}
 
     @app.get("/v1/console/snapshot")
     async def console():
@@ -226,9 +268,12 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
             raise HTTPException(400, "messages must be a non-empty list")
         thinking, stops = chat_options(body)
         tools = body.get("tools") if body.get("tool_choice") != "none" else None
-        prompt_ids = tok.encode(tmpl.render(msgs, tools=tools, thinking=thinking))
+        probe = probe_of(http)
+        ids_given = probe.get("token_ids")
+        prompt_ids = [int(x) for x in ids_given] if isinstance(ids_given, list) and ids_given else tok.encode(tmpl.render(msgs, tools=tools, thinking=thinking))
         max_tokens = int(body.get("max_completion_tokens") or body.get("max_tokens") or 256)
-        rid, events = start_generation(prompt_ids, body, max_tokens, constraint_for(body, len(prompt_ids)))
+        t0, key = time.time(), key_of(authorization)
+        rid, events = start_generation(prompt_ids, body, max_tokens, constraint_for(body, len(prompt_ids)), probe)
         created, cid = int(time.time()), "chatcmpl-" + rid
 
         if not body.get("stream"):
@@ -237,6 +282,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                 raise HTTPException(503 if "unavailable" in reason or "transport" in reason else 500, reason)
             text, stopped = _cut_at_stop(tok.decode(ids), stops)
             parsed = parse_completion(tmpl, text, thinking)
+            account(rid, key, t0, None, len(prompt_ids), len(ids), reason)
             message = {"role": "assistant", "content": parsed["content"]}
             if parsed["reasoning"]:
                 message["reasoning_content"] = parsed["reasoning"]
@@ -249,7 +295,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
 
         async def sse():
             dec, parser = StreamDecoder(tok), tmpl.parser(thinking)
-            held, n_calls, n_out = "", 0, 0
+            held, n_calls, n_out, t_first = "", 0, 0, None
             hold = max((len(x) for x in stops), default=1) - 1         # text that may still become a stop string stays back
 
             def chunk(delta, finish=None, usage=None):
@@ -280,12 +326,15 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                         yield ": keepalive\n\n"
                         continue
                     n_out += len(toks)
+                    if toks and t_first is None:
+                        t_first = time.time()
                     held += dec.push(toks) if toks else ""
                     cut, stopped = _cut_at_stop(held, stops)
                     if stopped or done:
                         for c in deltas(parser.push(cut) + parser.finish()):
                             yield c
                         finish = "tool_calls" if n_calls else ("stop" if stopped else reason)
+                        account(rid, key, t0, t_first, len(prompt_ids), n_out, finish)
                         usage = {"prompt_tokens": len(prompt_ids), "completion_tokens": n_out, "total_tokens": len(prompt_ids) + n_out}
                         yield chunk({}, finish, usage if (body.get("stream_options") or {}).get("include_usage") else None)
                         yield "data: [DONE]\n\n"
@@ -319,6 +368,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         if "max_tokens" not in body:
             raise HTTPException(400, "max_tokens is required")
         prompt_ids, thinking, stops = anthropic_prompt(body)
+        t0, key = time.time(), key_of(authorization, x_api_key)
         rid, events = start_generation(prompt_ids, body, int(body["max_tokens"]))
         mid = "msg_" + rid
 
@@ -340,6 +390,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                 raise HTTPException(503, reason)
             text, stopped = _cut_at_stop(tok.decode(ids), stops)
             parsed = parse_completion(tmpl, text, thinking)
+            account(rid, key, t0, None, len(prompt_ids), len(ids), reason)
             return {"id": mid, "type": "message", "role": "assistant", "model": model_id, "content": blocks_of(parsed),
                     "stop_reason": stop_reason(parsed, stopped, reason), "stop_sequence": None,
                     "usage": {"input_tokens": len(prompt_ids), "output_tokens": len(ids)}}
@@ -395,6 +446,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                         if open_kind is not None:
                             yield ev("content_block_stop", {"index": index})
                         sr = "tool_use" if any_call else ("end_turn" if stopped or reason == "stop" else "max_tokens")
+                        account(rid, key, t0, None, len(prompt_ids), n_out, sr)
                         yield ev("message_delta", {"delta": {"stop_reason": sr, "stop_sequence": None}, "usage": {"output_tokens": n_out}})
                         yield ev("message_stop", {})
                         return

@@ -42,3 +42,48 @@ class UsageStore:
         with self.lock:
             cur = self.db.execute("select api_key, count(*), sum(prompt_tokens + completion_tokens) from requests group by 1")
             return [{"api_key": k, "requests": n, "tokens": t} for k, n, t in cur.fetchall()]
+
+    # ------------------------------------------------------------------ maintenance (the `usage` command)
+    RANGES = {"1h": 3600.0, "6h": 6 * 3600.0, "24h": 86400.0, "7d": 7 * 86400.0}
+
+    def clear(self):
+        """Both tiers: request metadata and the prompt log."""
+        with self.lock:
+            self.db.executescript("delete from requests; delete from prompt_log;")
+            self.db.commit()
+
+    def clear_log(self):
+        """Only the prompt log (payloads); metadata stays."""
+        with self.lock:
+            self.db.execute("delete from prompt_log")
+            self.db.commit()
+
+    def export_csv(self, out, range_: str = "7d", now=None) -> int:
+        """Request metadata of the range ending now as CSV (never payloads).  Returns rows written."""
+        import csv
+        now = now or time.time()
+        with self.lock:
+            rows = self.db.execute("select id, t, model, api_key, prompt_tokens, completion_tokens, cache_hit_tokens, ttft_ms, total_ms, finish "
+                                   "from requests where t >= ? order by t", (now - self.RANGES[range_],)).fetchall()
+        w = csv.writer(out)
+        w.writerow(["id", "time", "model", "api_key", "prompt_tokens", "completion_tokens", "cache_hit_tokens", "ttft_ms", "total_ms", "finish"])
+        w.writerows(rows)
+        return len(rows)
+
+    def totals(self) -> dict:
+        with self.lock:
+            n, p, c, h = self.db.execute("select count(*), coalesce(sum(prompt_tokens),0), coalesce(sum(completion_tokens),0), "
+                                         "coalesce(sum(cache_hit_tokens),0) from requests").fetchone()
+        return {"requests": n, "prompt_tokens": p, "completion_tokens": c, "cache_hit_tokens": h}
+
+
+def synthetic_history(store: UsageStore, days: int = 7, per_day: int = 40, seed: int = 0, now=None):
+    """Fills a store with a plausible request history (the usage page can be developed without a GPU or a model)."""
+    import random
+    rng, now = random.Random(seed), now or time.time()
+    for d in range(days):
+        for i in range(per_day):
+            t = now - d * 86400 - rng.random() * 86000
+            p, c = rng.randrange(50, 30000), rng.randrange(1, 2000)
+            store.record(f"demo-{d}-{i}", "demo-model", rng.choice(["key-a", "key-b", "key-c"]), p, c, rng.choice([0, 0, (p // 64) * 64 // 2]),
+                         rng.uniform(20, 3000), rng.uniform(100, 60000), rng.choice(["stop", "length", "tool_calls"]), now=t)

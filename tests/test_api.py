@@ -169,3 +169,41 @@ def test_anthropic_tools_and_event_stream():
         assert text == "Checking." and json.loads(partial) == {"city": "Oslo"}
     finally:
         loop.stop()
+
+
+def test_usage_accounting_probe_header_and_usage_command(tmp_path):
+    import io
+    from cuteafd_b200 import cli
+    from cuteafd_b200.serving.usage import UsageStore, synthetic_history
+    pool = PagePool(256)
+    runner = FakeRunner(vocab=96)
+    cache = PrefixCache(pool)
+    loop = ServingLoop(Scheduler(runner, pool, prefix=cache), Health()).start()
+    store = UsageStore(str(tmp_path / "usage.sqlite"))
+    c = TestClient(build_app(loop, usage=store, enable_bench=True, api_keys={"sekret-key-1"}))
+    try:
+        long_prompt = "p" * 300
+        body = {"messages": [{"role": "user", "content": long_prompt}], "max_tokens": 4}
+        for _ in range(2):
+            assert c.post("/v1/chat/completions", headers={"Authorization": "Bearer sekret-key-1"}, json=body).status_code == 200
+        u = c.get("/usage", headers={"Authorization": "Bearer sekret-key-1"}).json()
+        assert u["totals"]["requests"] == 2 and u["totals"]["completion_tokens"] == 8 and u["totals"]["cache_hit_tokens"] >= 256
+        assert u["by_key"][0]["api_key"] == "sekret..."                                   # keys are stored truncated
+        hits = cache.stats["hits"]
+        probe = {"x-cuteafd-probe": json.dumps({"skip_cache": True, "no_drafts": True}), "Authorization": "Bearer sekret-key-1"}
+        assert c.post("/v1/chat/completions", headers=probe, json=body).status_code == 200
+        assert cache.stats["hits"] == hits                                                # the probe bypassed the prefix cache
+        ids = {"x-cuteafd-probe": json.dumps({"token_ids": [40, 41, 42]}), "Authorization": "Bearer sekret-key-1"}
+        assert c.post("/v1/chat/completions", headers=ids, json=body).json()["usage"]["prompt_tokens"] == 3
+        assert c.get("/v1/thermal").status_code == 200
+    finally:
+        loop.stop()
+    buf = io.StringIO()
+    assert store.export_csv(buf, "1h") == 4 and buf.getvalue().splitlines()[0].startswith("id,time,model")
+    assert cli.main(["usage", "export-csv", "--dir", str(tmp_path), "--out", str(tmp_path / "u.csv")]) == 0
+    assert len((tmp_path / "u.csv").read_text().splitlines()) == 5
+    assert cli.main(["usage", "clear", "--dir", str(tmp_path)]) == 0
+    assert UsageStore(str(tmp_path / "usage.sqlite")).totals()["requests"] == 0
+    demo = UsageStore()
+    synthetic_history(demo, days=3, per_day=5)
+    assert demo.totals()["requests"] == 15 and len(demo.daily()) >= 3
