@@ -23,6 +23,7 @@ from .. import ops
 from ..config import ModelSpec
 from ..models.weights import DeviceWeights, LayerWeights
 from ..ops import ActBuffer, FP4_KINDS, KIND_BF16, KIND_FP8B, pick_tn
+from ..utils.graph_census import GraphCensus
 
 PAGE = 64
 
@@ -136,6 +137,7 @@ class Engine:
         self.mtp_lanes: dict[int, Lane] = {}
         self.graphs: dict = {}
         self.graph_captures = 0
+        self.census = GraphCensus()
         self._meta_cap = 0
         self.launches_per_step = 0
 
@@ -169,6 +171,7 @@ class Engine:
         self.mh, self.md = views(self.meta_host), views(self.meta_dev)
         self._meta_cap = cap
         self.graphs.clear()     # views moved: captured graphs are stale
+        self.census.invalidate()
 
     def set_inputs(self, tokens, positions, slot_map, logit_rows, kv_len, q_start, q_len, page_table_rows):
         """Fill the pinned host block and enqueue ONE host-to-device copy."""
@@ -419,6 +422,7 @@ class Engine:
         if not use_graph:
             if hook:
                 hook(sh)
+            self.census.ran_eager(sh.key())
             return self.forward(sh)
         key = sh.key()
         g = self.graphs.get(key)
@@ -432,9 +436,11 @@ class Engine:
                 lane = self.forward(sh)
             self.graphs[key] = g = (graph, lane, self.launches_per_step)
             self.graph_captures += 1
+            self.census.captured(key, self.launches_per_step)
         if hook:
             hook(sh)
         g[0].replay()
+        self.census.replayed(key)
         self.launches_per_step = g[2]
         return g[1]
 

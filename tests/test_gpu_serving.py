@@ -105,3 +105,18 @@ def test_host_tier_restores_an_evicted_prefix_exactly():
     eng.check_status()
     assert out1 == ref[0] and out2 == ref[1]
     assert cache.stats["host_hits"] == 1 and cache.stats["host_hit_tokens"] == 192 and host.copy.launches >= 2
+
+
+def test_graph_census_follows_the_engine_and_times_both_arms():
+    from cuteafd_b200.utils.graph_census import measure_arms
+    spec, eng, sched, _ = build(prefix=False)
+    g = torch.Generator().manual_seed(1)
+    run_requests(sched, [torch.randint(0, spec.vocab, (40,), generator=g).tolist()], 6)
+    snap = eng.census.snapshot()
+    assert snap["captures"] == eng.graph_captures and snap["replays"] >= snap["captures"] > 0
+    eng.census.seal()
+    key = next(iter(eng.graphs))
+    before = eng.graph_captures
+    run_requests(sched, [torch.randint(0, spec.vocab, (40,), generator=g).tolist()], 6)       # same shapes: no new capture
+    assert eng.graph_captures == before and eng.census.snapshot()["steady_state_captures"] == 0
+    assert key in eng.census.shapes
