@@ -111,6 +111,34 @@ def build_serving(a):
     return spec, sched
 
 
+def _aliases(a) -> dict:
+    """`--official-model-names a,b,c` and/or `--official-model-names-file FILE` (one name per line)."""
+    names = [n for n in (a.official_model_names or "").split(",") if n]
+    if a.official_model_names_file:
+        names += [l.strip() for l in open(a.official_model_names_file) if l.strip() and not l.startswith("#")]
+    return {n: "served" for n in names}
+
+
+def cmd_gateway(a) -> int:
+    """The gateway surfaces (Anthropic Messages, OpenAI Responses, aliases, CORS) over a CPU stand-in model: lets
+    client integrations be developed without a GPU.  With a GPU the same surfaces are part of `serve --gateway on`.
+    Reference: cuteafd-daemon/src/commands/gateway.rs."""
+    from .engine.kv import PagePool
+    from .serving.api import ServingLoop, build_app
+    from .serving.chat_templates import template_for
+    from .serving.runner import FakeRunner
+    from .serving.scheduler import Scheduler
+    runner = FakeRunner(vocab=258)
+    runner.next_token = lambda prefix: 257 if len(prefix) % 97 == 0 else 32 + (sum(prefix[-3:]) % 90)
+    loop = ServingLoop(Scheduler(runner, PagePool(1024))).start()
+    app = build_app(loop, model_id=a.model_id, template=template_for(a.chat_template or "plain"), model_aliases=_aliases(a),
+                    allow_origin=a.gateway_allow_origin or None, enable_bench=True)
+    host, port = a.listen.rsplit(":", 1)
+    import uvicorn
+    uvicorn.run(app, host=host, port=int(port), log_level="info")
+    return 0
+
+
 def cmd_serve(a) -> int:
     from .loader.tokenizer import load_tokenizer
     from .serving.api import ServingLoop, build_app
@@ -130,7 +158,8 @@ def cmd_serve(a) -> int:
         thermal = None
     app = build_app(loop, model_id=a.model_id or spec.name, tokenizer=load_tokenizer(a.model if os.path.isdir(a.model) else None),
                     api_keys=keys, max_output=a.max_output, template=template_for(a.chat_template or spec.name),
-                    usage=usage, enable_bench=a.enable_bench, thermal=thermal)
+                    usage=usage, enable_bench=a.enable_bench, thermal=thermal, gateway=a.gateway == "on",
+                    model_aliases=_aliases(a), allow_origin=a.gateway_allow_origin or None)
     host, port = a.listen.rsplit(":", 1)
     import uvicorn
     uvicorn.run(app, host=host, port=int(port), log_level="info")
@@ -269,6 +298,8 @@ def main(argv=None) -> int:
     p.add_argument("--host-cache-gib", type=float, default=0.0, help="pinned host memory behind the prefix cache (0 = off)")
     p.add_argument("--usage", default="off", choices=["on", "off"]); p.add_argument("--enable-bench", action="store_true")
     p.add_argument("--usage-dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage"))
+    p.add_argument("--gateway", default="on", choices=["on", "off"]); p.add_argument("--official-model-names", default="")
+    p.add_argument("--official-model-names-file", default=""); p.add_argument("--gateway-allow-origin", default="")
     p.add_argument("--chat-template", default="", help="chat template family (chatml / qwen3-coder / deepseek / glm / plain); default: by model name")
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
@@ -282,6 +313,9 @@ def main(argv=None) -> int:
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--layers", type=int, default=0)
     p.add_argument("--c1-tokens", type=int, default=320); p.add_argument("--prefill-tokens", type=int, default=8192)
     p.set_defaults(fn=cmd_card)
+    p = sub.add_parser("gateway"); p.add_argument("--listen", default="127.0.0.1:8020"); p.add_argument("--model-id", default="cuteafd-b200")
+    p.add_argument("--official-model-names", default=""); p.add_argument("--official-model-names-file", default="")
+    p.add_argument("--gateway-allow-origin", default=""); p.add_argument("--chat-template", default=""); p.set_defaults(fn=cmd_gateway)
     p = sub.add_parser("usage"); p.add_argument("action", choices=["clear", "clear-log", "export-csv", "demo"])
     p.add_argument("--dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage")); p.add_argument("--range", default="7d", choices=["1h", "6h", "24h", "7d"])
     p.add_argument("--out", default=""); p.add_argument("--listen", default="127.0.0.1:8010"); p.set_defaults(fn=cmd_usage)

@@ -130,10 +130,14 @@ except ImportError:      # pragma: no cover - the HTTP layer is optional
 
 
 def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=None, api_keys=None, max_output: int = 4096, template=None,
-              usage=None, enable_bench: bool = False, thermal=None):
+              usage=None, enable_bench: bool = False, thermal=None, gateway: bool = True, model_aliases: dict | None = None,
+              allow_origin: str | None = None):
     """`usage`: a `UsageStore` that gets one row per finished request and backs `/usage`.  `enable_bench` turns on the
     probe header `x-cuteafd-probe` (JSON: `skip_cache`, `no_drafts`, `token_ids`) that benchmarks use to pin what a
-    request exercises (cuteafd-api/src/openai/probe.rs).  `thermal`: object with `.sample()` for `/v1/thermal`."""
+    request exercises (cuteafd-api/src/openai/probe.rs).  `thermal`: object with `.sample()` for `/v1/thermal`.
+    `gateway` adds the surfaces other clients speak, mapped onto the same scheduler: Anthropic Messages and OpenAI
+    Responses (`/v1/responses`, stored responses with `previous_response_id` chaining); `model_aliases` lists
+    official model names that clients may ask for and that are answered by the served model (gateway/models.rs)."""
     if FastAPI is None:
         raise RuntimeError("fastapi is not installed")
 
@@ -224,7 +228,8 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
     @app.get("/v1/models")
     async def models(authorization: str = Header(None)):
         auth(authorization)
-        return {"object": "list", "data": [{"id": model_id, "object": "model", "owned_by": "cuteafd-b200"}]}
+        names = [model_id] + [n for n in (model_aliases or {}) if n != model_id]
+        return {"object": "list", "data": [{"id": n, "object": "model", "owned_by": "cuteafd-b200"} for n in names]}
 
     @app.get("/v1/stats")
     async def stats():
@@ -289,7 +294,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
             if parsed["tool_calls"]:
                 message["tool_calls"] = openai_calls(parsed["tool_calls"])
             finish = "tool_calls" if parsed["tool_calls"] else ("stop" if stopped else reason)
-            return {"id": cid, "object": "chat.completion", "created": created, "model": model_id,
+            return {"id": cid, "object": "chat.completion", "created": created, "model": served_name(body),
                     "choices": [{"index": 0, "message": message, "finish_reason": finish}],
                     "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": len(ids), "total_tokens": len(prompt_ids) + len(ids)}}
 
@@ -299,7 +304,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
             hold = max((len(x) for x in stops), default=1) - 1         # text that may still become a stop string stays back
 
             def chunk(delta, finish=None, usage=None):
-                d = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model_id,
+                d = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": served_name(body),
                      "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
                 if usage:
                     d["usage"] = usage
@@ -347,6 +352,161 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
             finally:
                 loop.cancel(rid)
         return StreamingResponse(sse(), media_type="text/event-stream")
+
+    aliases = dict(model_aliases or {})
+
+    def served_name(body):
+        """The name echoed back: a known alias is accepted as is, anything else is answered under the served id."""
+        asked = body.get("model")
+        return asked if asked in aliases or asked == model_id else model_id
+
+    if allow_origin:
+        @app.middleware("http")
+        async def cors(request, call_next):
+            if request.method == "OPTIONS":
+                resp = JSONResponse({})
+            else:
+                resp = await call_next(request)
+            resp.headers["access-control-allow-origin"] = allow_origin
+            resp.headers["access-control-allow-headers"] = "authorization, content-type, x-api-key, anthropic-version"
+            resp.headers["access-control-allow-methods"] = "GET, POST, DELETE, OPTIONS"
+            return resp
+
+    if not gateway:
+        return app
+
+    # ------------------------------------------------------------------ OpenAI Responses
+    stored: dict = {}              # response id -> {"response": ..., "messages": conversation including the answer}
+
+    def responses_messages(body):
+        msgs = []
+        prev = body.get("previous_response_id")
+        if prev:
+            if prev not in stored:
+                raise HTTPException(404, f"no stored response {prev}")
+            msgs += stored[prev]["messages"]
+        inp = body.get("input")
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        for item in inp if isinstance(inp, list) else []:
+            kind = item.get("type", "message")
+            if kind == "message":
+                content = item.get("content")
+                if isinstance(content, list):
+                    content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
+                msgs.append({"role": item.get("role", "user"), "content": content})
+            elif kind == "function_call":
+                msgs.append({"role": "assistant", "content": "", "tool_calls": [{"id": item.get("call_id"), "function": {
+                    "name": item.get("name"), "arguments": item.get("arguments", "{}")}}]})
+            elif kind == "function_call_output":
+                msgs.append({"role": "tool", "tool_call_id": item.get("call_id"), "content": str(item.get("output", ""))})
+        tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""), "parameters": t.get("parameters")}}
+                 for t in body.get("tools") or [] if t.get("type") == "function" and t.get("name")]
+        return msgs, tools
+
+    def response_object(rid, body, parsed, n_in, n_out, status="completed"):
+        out = []
+        if parsed["reasoning"]:
+            out.append({"type": "reasoning", "id": "rs_" + rid, "summary": [{"type": "summary_text", "text": parsed["reasoning"]}]})
+        if parsed["content"] or not parsed["tool_calls"]:
+            out.append({"type": "message", "id": "msg_" + rid, "role": "assistant", "status": "completed",
+                        "content": [{"type": "output_text", "text": parsed["content"], "annotations": []}]})
+        for c in parsed["tool_calls"]:
+            out.append({"type": "function_call", "id": "fc_" + c["id"][5:], "call_id": c["id"], "name": c["name"],
+                        "arguments": json.dumps(c["arguments"], ensure_ascii=False), "status": "completed"})
+        return {"id": "resp_" + rid, "object": "response", "created_at": int(time.time()), "status": status, "model": served_name(body),
+                "output": out, "output_text": parsed["content"], "previous_response_id": body.get("previous_response_id"),
+                "usage": {"input_tokens": n_in, "output_tokens": n_out, "total_tokens": n_in + n_out}}
+
+    @app.post("/v1/responses")
+    async def responses(http: HttpRequest, authorization: str = Header(None)):
+        auth(authorization)
+        body = await http.json()
+        msgs, tools = responses_messages(body)
+        if not msgs:
+            raise HTTPException(400, "input is required")
+        thinking, stops = chat_options(body)
+        if (body.get("reasoning") or {}).get("effort") not in (None, "none", "minimal"):
+            thinking = True
+        prompt_ids = tok.encode(tmpl.render(msgs, tools=tools or None, system=body.get("instructions"), thinking=thinking))
+        t0, key = time.time(), key_of(authorization)
+        rf = {"response_format": (body.get("text") or {}).get("format")} if isinstance((body.get("text") or {}).get("format"), dict) else {}
+        rid, events = start_generation(prompt_ids, body, int(body.get("max_output_tokens") or 256), constraint_for(rf, len(prompt_ids)))
+
+        def finish(ids, reason):
+            text, _ = _cut_at_stop(tok.decode(ids), stops)
+            parsed = parse_completion(tmpl, text, thinking)
+            account(rid, key, t0, None, len(prompt_ids), len(ids), reason)
+            resp = response_object(rid, body, parsed, len(prompt_ids), len(ids), "completed" if reason != "length" else "incomplete")
+            if body.get("store", True):
+                answer = {"role": "assistant", "content": parsed["content"]}
+                if parsed["tool_calls"]:
+                    answer["tool_calls"] = openai_calls(parsed["tool_calls"])
+                stored[resp["id"]] = {"response": resp, "messages": msgs + [answer]}
+                while len(stored) > 256:
+                    stored.pop(next(iter(stored)))
+            return resp, parsed
+        if not body.get("stream"):
+            ids, reason = await collect(events)
+            if reason and reason.startswith(("error", "unavailable")):
+                raise HTTPException(503, reason)
+            return finish(ids, reason)[0]
+
+        async def sse():
+            seq = 0
+
+            def ev(name, data):
+                nonlocal seq
+                seq += 1
+                return f"event: {name}\ndata: " + json.dumps(dict(data, type=name, sequence_number=seq)) + "\n\n"
+            shell = response_object(rid, body, {"reasoning": "", "content": "", "tool_calls": []}, len(prompt_ids), 0, "in_progress")
+            shell["output"] = []
+            yield ev("response.created", {"response": shell})
+            dec, parser, ids = StreamDecoder(tok), tmpl.parser(thinking), []
+            held = ""
+            hold = max((len(x) for x in stops), default=1) - 1
+            try:
+                while True:
+                    try:
+                        toks, done, reason = await asyncio.wait_for(events.get(), KEEPALIVE_S)
+                    except asyncio.TimeoutError:
+                        yield ": keepalive\n\n"
+                        continue
+                    ids += toks
+                    held += dec.push(toks) if toks else ""
+                    cut, stopped = _cut_at_stop(held, stops)
+                    final = stopped or done
+                    safe = len(cut) if final else len(held) - hold
+                    if safe > 0:
+                        for kind, x in parser.push(held[:safe]) + (parser.finish() if final else []):
+                            if kind == "content" and x:
+                                yield ev("response.output_text.delta", {"item_id": "msg_" + rid, "output_index": 0, "content_index": 0, "delta": x})
+                            elif kind == "reasoning" and x:
+                                yield ev("response.reasoning_summary_text.delta", {"item_id": "rs_" + rid, "output_index": 0, "summary_index": 0, "delta": x})
+                        held = held[safe:]
+                    if final:
+                        resp, parsed = finish(ids, "stop" if stopped else reason)
+                        for i, item in enumerate(resp["output"]):
+                            yield ev("response.output_item.done", {"output_index": i, "item": item})
+                        yield ev("response.completed", {"response": resp})
+                        return
+            finally:
+                loop.cancel(rid)
+        return StreamingResponse(sse(), media_type="text/event-stream")
+
+    @app.get("/v1/responses/{response_id}")
+    async def get_response(response_id: str, authorization: str = Header(None)):
+        auth(authorization)
+        if response_id not in stored:
+            raise HTTPException(404, "no such response")
+        return stored[response_id]["response"]
+
+    @app.delete("/v1/responses/{response_id}")
+    async def delete_response(response_id: str, authorization: str = Header(None)):
+        auth(authorization)
+        if stored.pop(response_id, None) is None:
+            raise HTTPException(404, "no such response")
+        return {"id": response_id, "object": "response", "deleted": True}
 
     def anthropic_prompt(body):
         msgs, tools = _anthropic_to_openai(body)

@@ -207,3 +207,51 @@ def test_usage_accounting_probe_header_and_usage_command(tmp_path):
     demo = UsageStore()
     synthetic_history(demo, days=3, per_day=5)
     assert demo.totals()["requests"] == 15 and len(demo.daily()) >= 3
+
+
+def test_responses_surface_stores_chains_and_streams():
+    c, loop = _scripted_client("Hello there.", "plain")
+    try:
+        r1 = c.post("/v1/responses", json={"model": "cuteafd-b200", "input": "hi", "instructions": "be brief", "max_output_tokens": 50}).json()
+        assert r1["status"] == "completed" and r1["output_text"] == "Hello there." and r1["output"][0]["content"][0]["type"] == "output_text"
+        assert c.get("/v1/responses/" + r1["id"]).json()["id"] == r1["id"]
+        # the follow-up renders the stored conversation in front of the new input
+        r2 = c.post("/v1/responses", json={"input": [{"type": "message", "role": "user", "content": [{"type": "input_text", "text": "again"}]}],
+                                           "previous_response_id": r1["id"], "max_output_tokens": 50}).json()
+        assert r2["previous_response_id"] == r1["id"] and r2["usage"]["input_tokens"] > r1["usage"]["input_tokens"]
+        assert c.post("/v1/responses", json={"input": "x", "previous_response_id": "resp_missing"}).status_code == 404
+        assert c.delete("/v1/responses/" + r1["id"]).json()["deleted"] and c.get("/v1/responses/" + r1["id"]).status_code == 404
+    finally:
+        loop.stop()
+    c, loop = _scripted_client("Hello there.", "plain")
+    try:
+        names, text, final = [], "", None
+        with c.stream("POST", "/v1/responses", json={"input": "hi", "stream": True, "max_output_tokens": 50}) as r:
+            for line in r.iter_lines():
+                if line.startswith("event: "):
+                    names.append(line[7:])
+                elif line.startswith("data: "):
+                    d = json.loads(line[6:])
+                    text += d.get("delta", "") if d["type"] == "response.output_text.delta" else ""
+                    final = d["response"] if d["type"] == "response.completed" else final
+        assert names[0] == "response.created" and names[-1] == "response.completed" and text == "Hello there." == final["output_text"]
+    finally:
+        loop.stop()
+
+
+def test_model_aliases_cors_and_gateway_off():
+    pool = PagePool(64)
+    loop = ServingLoop(Scheduler(FakeRunner(vocab=96), pool), Health()).start()
+    try:
+        c = TestClient(build_app(loop, model_aliases={"gpt-4o": "served", "claude-x": "served"}, allow_origin="https://ui.example"))
+        ids = [m["id"] for m in c.get("/v1/models").json()["data"]]
+        assert ids == ["cuteafd-b200", "gpt-4o", "claude-x"]
+        r = c.post("/v1/chat/completions", json={"model": "gpt-4o", "messages": [{"role": "user", "content": "x"}], "max_tokens": 2})
+        assert r.json()["model"] == "gpt-4o" and r.headers["access-control-allow-origin"] == "https://ui.example"
+        assert c.post("/v1/chat/completions", json={"model": "unknown", "messages": [{"role": "user", "content": "x"}], "max_tokens": 2}).json()["model"] == "cuteafd-b200"
+        off = TestClient(build_app(loop, gateway=False))
+        assert off.post("/v1/messages", json={"max_tokens": 2, "messages": [{"role": "user", "content": "x"}]}).status_code == 404
+        assert off.post("/v1/responses", json={"input": "x"}).status_code == 404
+        assert off.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "max_tokens": 2}).status_code == 200
+    finally:
+        loop.stop()
