@@ -274,6 +274,21 @@ def cmd_card(a) -> int:
     return 0
 
 
+def cmd_run(a) -> int:
+    """`run --config FILE [--set K=V ...] [--print]`: the operator's KEY=VALUE file becomes a command line."""
+    import shlex
+    from . import configfile
+    try:
+        argv = configfile.to_argv(configfile.load(a.config, a.set), a.subparsers)
+    except configfile.ConfigError as e:
+        print(f"config error: {e}", file=sys.stderr)
+        return 2
+    if a.print:
+        print("cuteafd " + " ".join(shlex.quote(x) for x in argv))
+        return 0
+    return main(argv)
+
+
 def cmd_bench(a) -> int:
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -287,6 +302,8 @@ def main(argv=None) -> int:
     p.add_argument("--gpus", type=int, default=8); p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--gpu-gib", type=int, default=180)
     p.add_argument("--json", action="store_true"); p.set_defaults(fn=cmd_plan)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("run"); p.add_argument("--config", required=True); p.add_argument("--set", action="append", default=[])
+    p.add_argument("--print", action="store_true"); p.set_defaults(fn=cmd_run, subparsers=sub.choices)
     p = sub.add_parser("fabric"); p.add_argument("--p2p", action="store_true"); p.add_argument("--mib", type=int, default=256); p.set_defaults(fn=cmd_fabric)
     p = sub.add_parser("serve")
     p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--listen", default="127.0.0.1:8000")
