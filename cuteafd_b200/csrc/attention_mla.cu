@@ -138,52 +138,56 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t id_s = mla_idesc(MKEYS, 0), id_o = mla_idesc(256, 1);
-    // The issuer polls two conditions and serves whichever is ready: "the latent tile qk has landed" (issue its
-    // scores) and "the probabilities of tile pv are in shared memory" (issue its PV product, which also releases the
-    // tile's stage to the producer).  Waiting for them in a fixed order would put the load latency of tile i+1 in
-    // front of the PV product of tile i, i.e. one full load latency per tile on the critical path.
+    // One thread issues everything.  It polls two conditions and serves whichever is ready: "the latent tile qk has
+    // landed" (issue its scores) and "the probabilities of tile pv are in shared memory" (issue its PV product, which
+    // also releases the tile's stage to the producer).  The 36 score MMAs of a tile keep the issuing thread busy for
+    // as long as they execute (the MMA queue is short), so the PV probe is repeated between the 64-wide chunks:
+    // otherwise a PV product that became ready just after the scores started would wait a whole score pass, and with
+    // it the stage release and the next load.
     // Scores of tile qk go to S buffer qk & 1, which the softmax of tile qk - 2 has read once PV(qk - 2) could be
-    // issued: qk <= pv + 1.
-    int qk = 0, pv = 0, idle = 0;
-    long long idle_t0 = 0;
-    while (pv < n_tiles) {
-      bool did = false;
-      if (pv < qk && __shfl_sync(0xffffffffu, (int)mbar_test(&p_full, pv & 1), 0)) {
+    // issued: qk <= pv + 1 when the scores start.
+    if (lane == 0) {
+      int qk = 0, pv = 0, idle = 0;
+      long long idle_t0 = 0;
+      auto try_pv = [&]() -> bool {
+        if (pv >= qk || !mbar_test(&p_full, pv & 1)) return false;
         tc_fence_after();
-        if (lane == 0) {
-          const int s = pv & 1;
-          const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * 4096;
+        const int s = pv & 1;
+        const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * 4096;
 #pragma unroll
-          for (int k = 0; k < 2; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
-            tc_mma_f16(tmem + O_COL, mla_desc_k_plain(smem_u32(sP) + k * 256, 128, 512), mla_desc_mn_sw128(v0 + k * 2048, 4096, 1024), id_o, (pv | k) ? 1u : 0u);
-          tc_commit(&k_empty[s]);
-          tc_commit(&o_done);
-        }
-        __syncwarp();
-        ++pv; did = true;
-      }
-      if (qk < n_tiles && qk <= pv + 1 && __shfl_sync(0xffffffffu, (int)mbar_test(&k_full[qk & 1], (qk >> 1) & 1), 0)) {
-        tc_fence_after();
-        if (lane == 0) {
+        for (int k = 0; k < 2; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
+          tc_mma_f16(tmem + O_COL, mla_desc_k_plain(smem_u32(sP) + k * 256, 128, 512), mla_desc_mn_sw128(v0 + k * 2048, 4096, 1024), id_o, (pv | k) ? 1u : 0u);
+        tc_commit(&k_empty[s]);
+        tc_commit(&o_done);
+        ++pv;
+        return true;
+      };
+      while (pv < n_tiles) {
+        bool did = try_pv();
+        if (qk < n_tiles && qk <= pv + 1 && mbar_test(&k_full[qk & 1], (qk >> 1) & 1)) {
+          tc_fence_after();
           const int s = qk & 1;
           const uint32_t k0 = smem_u32(sK + s * SK_STAGE), d = tmem + (s ? S1_COL : S0_COL);
-#pragma unroll
-          for (int c = 0; c < NCH; ++c)
+#pragma unroll 1
+          for (int c = 0; c < NCH; ++c) {
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + c * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, (c | k) ? 1u : 0u);
+            if (c + 1 < NCH) try_pv();
+          }
           tc_commit(&s_full[s]);
+          ++qk;
+          did = true;
         }
-        __syncwarp();
-        ++qk; did = true;
-      }
-      if (did) { idle = 0; continue; }
-      if (idle++ == 0) idle_t0 = clock64();
-      if ((idle & 255) == 0) {
-        if (*abortp) break;
-        if (clock64() - idle_t0 > 4000000000LL) { *abortp = 1; ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, pv); break; }
+        if (did) { idle = 0; continue; }
+        if (idle++ == 0) idle_t0 = clock64();
+        if ((idle & 255) == 0) {
+          if (*abortp) break;
+          if (clock64() - idle_t0 > 4000000000LL) { *abortp = 1; ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, pv); break; }
+        }
       }
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax + epilogue: thread = row
     const int q4 = warp & 3, r = q4 * 32 + lane;
@@ -209,13 +213,26 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
         sr[j] = __float_as_uint(v);
         mx = fmaxf(mx, v);
       }
-      if (i > 0 && !mbar_wait_bounded(&o_done, (i - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
-      tc_fence_after();
       float alpha = 1.f;
       if (mx > m_ref + 8.f) {
         if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
         m_ref = mx;
       }
+      // the probabilities only need the reference maximum, so they are computed while PV(i - 1) still runs; the
+      // wait below guards the accumulator rescale and the P buffer, both of which PV(i - 1) uses
+      uint32_t pk[16];
+      float psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float a0 = __uint_as_float(sr[2 * j]), a1 = __uint_as_float(sr[2 * j + 1]);
+        const float e0 = (m_ref == -INFINITY) ? 0.f : exp2f(a0 - m_ref), e1 = (m_ref == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
+        psum += e0 + e1;
+        bf162 h = __floats2bfloat162_rn(e0, e1);
+        pk[j] = *(uint32_t*)&h;
+      }
+      l += psum;
+      if (i > 0 && !mbar_wait_bounded(&o_done, (i - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+      tc_fence_after();
       if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {       // warp-uniform: tcgen05.ld/st are warp collectives
 #pragma unroll 1
         for (int c = 0; c < 16; ++c) {
@@ -228,17 +245,6 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      uint32_t pk[16];
-      float psum = 0.f;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float a0 = __uint_as_float(sr[2 * j]), a1 = __uint_as_float(sr[2 * j + 1]);
-        const float e0 = (m_ref == -INFINITY) ? 0.f : exp2f(a0 - m_ref), e1 = (m_ref == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
-        psum += e0 + e1;
-        bf162 h = __floats2bfloat162_rn(e0, e1);
-        pk[j] = *(uint32_t*)&h;
-      }
-      l += psum;
       // core-matrix layout: 8-row groups 512 B apart, the four 8-key columns 128 B apart, 16 B per row inside
 #pragma unroll
       for (int c = 0; c < 4; ++c)
