@@ -6,8 +6,10 @@
 // MQA with a 576-wide QK and a 512-wide V that share one cache row.
 //
 // CTA = (KV split, V half, sequence x query tile); rows of the MMA tile = local heads x tokens (128 rows).
-//   S[128 x 32]   = Q K^T over nine 64-wide chunks (tcgen05.mma kind::f16, Q 144 KB resident in shared memory,
-//                   K tiles of 32 keys x 576 through a two-stage TMA ring)
+//   S[128 x 32]   = Q K^T over nine 64-wide chunks (tcgen05.mma kind::f16; Q is resident: chunks 0..5 in tensor
+//                   memory as the A operand, chunks 6..8 in shared memory; K tiles of 32 keys x 576 through a
+//                   four-stage TMA ring).  With N = 32 a score MMA is bound by its A operand, and an A read from
+//                   shared memory costs ~65 cycles per instruction whatever N is.
 //   softmax       thread per row, lazy rescale (as in the GQA kernel), P in bf16 to shared memory
 //   O[128 x 256] += P V_half, V_half read in place from the K tile as an MN-major operand (chunks 4*vh .. 4*vh+3)
 // The 512-wide fp32 output of 128 rows would fill all of tensor memory, so the V dimension is split over two CTAs
@@ -59,22 +61,24 @@ __device__ __forceinline__ void mla_tmem_st_x16(uint32_t addr, const uint32_t* r
                  "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 
-#define SQ_BYTES (NCH * 16384)              // 9 chunks x [128 rows x 128 B]
+#define QT_CH 6                             // Q chunks 0..5 live in tensor memory (192 columns), chunks 6..8 in shared memory
+#define NST 4                               // latent tile stages
+#define SQ_BYTES ((NCH - QT_CH) * 16384)    // 3 chunks x [128 rows x 128 B]
 #define SK_STAGE (NCH * 4096)               // 9 chunks x [32 keys x 128 B]
 #define SP_BYTES 8192                       // [128 rows x 32 keys] bf16, core-matrix layout
-#define MLA_SMEM (SQ_BYTES + 2 * SK_STAGE + SP_BYTES + 128)
+#define MLA_SMEM (SQ_BYTES + NST * SK_STAGE + SP_BYTES + 128)
 
 __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant__ MlaArgs a) {
   pdl_launch(); pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sK = smem + SQ_BYTES;
-  uint8_t* sP = sK + 2 * SK_STAGE;
+  uint8_t* sP = sK + NST * SK_STAGE;
   uint64_t* bars = (uint64_t*)(sP + SP_BYTES);
-  uint64_t* k_full = bars; uint64_t* k_empty = bars + 2; uint64_t* s_full = bars + 4;
-  uint64_t& p_full = bars[6]; uint64_t& o_done = bars[7];
-  uint32_t& tmem_slot = *(uint32_t*)(bars + 8);
-  int& abort_flag = *(int*)(bars + 9);
+  uint64_t* k_full = bars; uint64_t* k_empty = bars + NST; uint64_t* s_full = bars + 2 * NST;
+  uint64_t& p_full = bars[2 * NST + 2]; uint64_t& o_done = bars[2 * NST + 3];
+  uint32_t& tmem_slot = *(uint32_t*)(bars + 2 * NST + 4);
+  int& abort_flag = *(int*)(bars + 2 * NST + 5);
   if (smem_u32(smem) & 1023) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, 0xA12); return; }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -95,22 +99,23 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
   const int n_tiles = max(0, t1 - t0);
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&s_full[s], 1); }
+    for (int s = 0; s < NST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) mbar_init(&s_full[s], 1);
     mbar_init(&p_full, 128); mbar_init(&o_done, 1);
     abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
-  // Q rows -> nine swizzled K-major chunk tiles: chunks 0..7 from q_lat, chunk 8 from q_rope
-  for (int i = tid; i < 128 * 72; i += 192) {
-    const int r = i / 72, c = i % 72;                    // 16-byte chunk c (8 elements) of row r
+  // Q rows: the 64-wide chunks 6, 7 (q_lat) and 8 (q_rope) become swizzled K-major tiles in shared memory ...
+  for (int i = tid; i < 128 * 24; i += 192) {
+    const int r = i / 24, c = 8 * QT_CH + i % 24;        // 16-byte chunk c (8 elements) of row r
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < R) {
       const int t = row_base + r / a.Hl, h = r % a.Hl;
       v = (c < 64) ? *(const uint4*)(a.q_lat + ((size_t)h * a.T + t) * DV + c * 8)
                    : *(const uint4*)(a.q_rope + ((size_t)t * a.Hl + h) * 64 + (c - 64) * 8);
     }
-    *(uint4*)(sQ + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+    *(uint4*)(sQ + ((c >> 3) - QT_CH) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
   }
   fence_proxy_async_smem();
   tc_fence_before();
@@ -118,13 +123,35 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
-  const uint32_t S0_COL = 0, S1_COL = 32, O_COL = 64;
+  const uint32_t S0_COL = 0, S1_COL = 32, O_COL = 64, QT_COL = 320;
+  // ... and chunks 0..5 go to tensor memory (row = lane, two elements per 32-bit column), where the score MMAs
+  // read them as the A operand without touching shared memory: with 32-key tiles the A operand is what the
+  // score MMAs wait for, and Q is the same for every tile.
+  if (warp >= 2) {
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t dst = tmem + ((uint32_t)((warp & 3) * 32) << 16) + QT_COL;
+    const bf16* src = a.q_lat + ((size_t)((r < R ? r : 0) % a.Hl) * a.T + row_base + (r < R ? r : 0) / a.Hl) * DV;
+#pragma unroll 1
+    for (int g = 0; g < QT_CH * 2; ++g) {                // 16 columns = 32 elements per store
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = r < R ? *(const uint4*)(src + g * 32 + j * 8) : make_uint4(0, 0, 0, 0);
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
+      mla_tmem_st_x16(dst + g * 16, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ latent tile producer
     for (int i = 0; i < n_tiles && !*abortp; ++i) {
-      const int s = i & 1;
-      if (!mbar_wait_bounded(&k_empty[s], ((i >> 1) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
+      const int s = i % NST;
+      if (!mbar_wait_bounded(&k_empty[s], ((i / NST) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
       if (lane == 0) {
         const int key0 = (t0 + i) * MKEYS;
         const int page = a.page_table[(size_t)seq * a.max_pages + key0 / MPAGE];
@@ -152,7 +179,7 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
       auto try_pv = [&]() -> bool {
         if (pv >= qk || !mbar_test(&p_full, pv & 1)) return false;
         tc_fence_after();
-        const int s = pv & 1;
+        const int s = pv % NST;
         const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * 4096;
 #pragma unroll
         for (int k = 0; k < 2; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
@@ -164,18 +191,23 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
       };
       while (pv < n_tiles) {
         bool did = try_pv();
-        if (qk < n_tiles && qk <= pv + 1 && mbar_test(&k_full[qk & 1], (qk >> 1) & 1)) {
+        if (qk < n_tiles && qk <= pv + 1 && mbar_test(&k_full[qk % NST], (qk / NST) & 1)) {
           tc_fence_after();
-          const int s = qk & 1;
-          const uint32_t k0 = smem_u32(sK + s * SK_STAGE), d = tmem + (s ? S1_COL : S0_COL);
+          const uint32_t k0 = smem_u32(sK + (qk % NST) * SK_STAGE), d = tmem + ((qk & 1) ? S1_COL : S0_COL);
 #pragma unroll 1
           for (int c = 0; c < NCH; ++c) {
+            if (c < QT_CH) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + c * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, (c | k) ? 1u : 0u);
+              for (int k = 0; k < 4; ++k)
+                tc_mma_f16_ta(d, tmem + QT_COL + c * 32 + k * 8, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, (c | k) ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + (c - QT_CH) * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, 1u);
+            }
             if (c + 1 < NCH) try_pv();
           }
-          tc_commit(&s_full[s]);
+          tc_commit(&s_full[qk & 1]);
           ++qk;
           did = true;
         }

@@ -271,6 +271,13 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d, uint64_t adesc, uint64_t 
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// Same with the A operand in tensor memory: lane = row, each 32-bit column holds two consecutive K elements
+// (8 columns per K = 16 instruction).  A read from tensor memory costs no shared-memory bandwidth.
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 // kind::f8f6f4 (e4m3/e5m2/e2m1-padded inputs, fp32 accumulate), K = 32 per instruction
 __device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
