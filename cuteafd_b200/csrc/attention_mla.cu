@@ -6,10 +6,10 @@
 // MQA with a 576-wide QK and a 512-wide V that share one cache row.
 //
 // CTA = (KV split, V half, sequence x query tile); rows of the MMA tile = local heads x tokens (128 rows).
-//   S[128 x 32]   = Q K^T over nine 64-wide chunks (tcgen05.mma kind::f16; Q is resident: chunks 0..5 in tensor
-//                   memory as the A operand, chunks 6..8 in shared memory; K tiles of 32 keys x 576 through a
-//                   four-stage TMA ring).  With N = 32 a score MMA is bound by its A operand, and an A read from
-//                   shared memory costs ~65 cycles per instruction whatever N is.
+//   S[128 x 64]   = Q K^T over nine 64-wide chunks (tcgen05.mma kind::f16; Q is resident: chunks 0..5 in tensor
+//                   memory as the A operand, chunks 6..8 in shared memory; K tiles of 64 keys x 576 = one page
+//                   through a two-stage TMA ring).  A score MMA costs ~130 cycles here whether it covers 32 or 64
+//                   keys and wherever its A operand lives, so wide tiles are what makes the scores cheaper.
 //   softmax       thread per row, lazy rescale (as in the GQA kernel), P in bf16 to shared memory
 //   O[128 x 256] += P V_half, V_half read in place from the K tile as an MN-major operand (chunks 4*vh .. 4*vh+3)
 // The 512-wide fp32 output of 128 rows would fill all of tensor memory, so the V dimension is split over two CTAs
@@ -24,7 +24,7 @@
 #define CA_PDL_CLASS 2
 #include "common.cuh"
 
-#define MKEYS 32
+#define MKEYS 64            // keys per tile = one page
 #define MPAGE 64
 #define DQK 576
 #define DV 512
@@ -62,10 +62,11 @@ __device__ __forceinline__ void mla_tmem_st_x16(uint32_t addr, const uint32_t* r
 }
 
 #define QT_CH 6                             // Q chunks 0..5 live in tensor memory (192 columns), chunks 6..8 in shared memory
-#define NST 4                               // latent tile stages
+#define NST 2                               // latent tile stages
 #define SQ_BYTES ((NCH - QT_CH) * 16384)    // 3 chunks x [128 rows x 128 B]
-#define SK_STAGE (NCH * 4096)               // 9 chunks x [32 keys x 128 B]
-#define SP_BYTES 8192                       // [128 rows x 32 keys] bf16, core-matrix layout
+#define SK_CHUNK (MKEYS * 128)              // one 64-wide chunk of a tile: [64 keys x 128 B]
+#define SK_STAGE (NCH * SK_CHUNK)           // 9 chunks
+#define SP_BYTES (128 * MKEYS * 2)          // [128 rows x 64 keys] bf16, core-matrix layout
 #define MLA_SMEM (SQ_BYTES + NST * SK_STAGE + SP_BYTES + 128)
 
 __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant__ MlaArgs a) {
@@ -75,7 +76,8 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
   uint8_t* sK = smem + SQ_BYTES;
   uint8_t* sP = sK + NST * SK_STAGE;
   uint64_t* bars = (uint64_t*)(sP + SP_BYTES);
-  uint64_t* k_full = bars; uint64_t* k_empty = bars + NST; uint64_t* s_full = bars + 2 * NST;
+  uint64_t* k_full = bars; uint64_t* k_empty = bars + NST;
+  uint64_t& s_full = bars[2 * NST]; uint64_t& s_free = bars[2 * NST + 1];
   uint64_t& p_full = bars[2 * NST + 2]; uint64_t& o_done = bars[2 * NST + 3];
   uint32_t& tmem_slot = *(uint32_t*)(bars + 2 * NST + 4);
   int& abort_flag = *(int*)(bars + 2 * NST + 5);
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
 
   if (tid == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) mbar_init(&s_full[s], 1);
+    mbar_init(&s_full, 1); mbar_init(&s_free, 128);
     mbar_init(&p_full, 128); mbar_init(&o_done, 1);
     abort_flag = 0;
     fence_barrier_init();
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
-  const uint32_t S0_COL = 0, S1_COL = 32, O_COL = 64, QT_COL = 320;
+  const uint32_t S_COL = 0, O_COL = 64, QT_COL = 320;
   // ... and chunks 0..5 go to tensor memory (row = lane, two elements per 32-bit column), where the score MMAs
   // read them as the A operand without touching shared memory: with 32-key tiles the A operand is what the
   // score MMAs wait for, and Q is the same for every tile.
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
         const int slot0 = page * MPAGE + key0 % MPAGE;
         mbar_expect_tx(&k_full[s], SK_STAGE);
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * SK_STAGE + c * 4096, a.kv_map, &k_full[s], c * 64, slot0, 0);
+        for (int c = 0; c < NCH; ++c) tma_load_3d(sK + s * SK_STAGE + c * SK_CHUNK, a.kv_map, &k_full[s], c * 64, slot0, 0);
       }
       __syncwarp();
     }
@@ -166,13 +168,13 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t id_s = mla_idesc(MKEYS, 0), id_o = mla_idesc(256, 1);
     // One thread issues everything.  It polls two conditions and serves whichever is ready: "the latent tile qk has
-    // landed" (issue its scores) and "the probabilities of tile pv are in shared memory" (issue its PV product, which
-    // also releases the tile's stage to the producer).  The 36 score MMAs of a tile keep the issuing thread busy for
-    // as long as they execute (the MMA queue is short), so the PV probe is repeated between the 64-wide chunks:
+    // landed and the score buffer is free" (issue its scores) and "the probabilities of tile pv are in shared memory"
+    // (issue its PV product, which also releases the tile's stage to the producer).  The 36 score MMAs of a tile
+    // keep the issuing thread busy for as long as they execute (~130 cycles each whatever their operands, so a tile
+    // is 64 keys wide to halve the count per key), and the PV probe is repeated between the 64-wide chunks:
     // otherwise a PV product that became ready just after the scores started would wait a whole score pass, and with
     // it the stage release and the next load.
-    // Scores of tile qk go to S buffer qk & 1, which the softmax of tile qk - 2 has read once PV(qk - 2) could be
-    // issued: qk <= pv + 1 when the scores start.
+    // There is one score buffer: the softmax threads copy it to registers first thing and release it (s_free).
     if (lane == 0) {
       int qk = 0, pv = 0, idle = 0;
       long long idle_t0 = 0;
@@ -180,10 +182,11 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
         if (pv >= qk || !mbar_test(&p_full, pv & 1)) return false;
         tc_fence_after();
         const int s = pv % NST;
-        const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * 4096;
+        const uint32_t v0 = smem_u32(sK + s * SK_STAGE) + (4 * vh) * SK_CHUNK;
 #pragma unroll
-        for (int k = 0; k < 2; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
-          tc_mma_f16(tmem + O_COL, mla_desc_k_plain(smem_u32(sP) + k * 256, 128, 512), mla_desc_mn_sw128(v0 + k * 2048, 4096, 1024), id_o, (pv | k) ? 1u : 0u);
+        for (int k = 0; k < MKEYS / 16; ++k)       // 16 keys per MMA: two 8-key groups = 2048 B along K
+          tc_mma_f16(tmem + O_COL, mla_desc_k_plain(smem_u32(sP) + k * 256, 128, MKEYS * 16), mla_desc_mn_sw128(v0 + k * 2048, SK_CHUNK, 1024), id_o,
+                     (pv | k) ? 1u : 0u);
         tc_commit(&k_empty[s]);
         tc_commit(&o_done);
         ++pv;
@@ -191,23 +194,23 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
       };
       while (pv < n_tiles) {
         bool did = try_pv();
-        if (qk < n_tiles && qk <= pv + 1 && mbar_test(&k_full[qk % NST], (qk / NST) & 1)) {
+        if (qk < n_tiles && (qk == 0 || mbar_test(&s_free, (qk - 1) & 1)) && mbar_test(&k_full[qk % NST], (qk / NST) & 1)) {
           tc_fence_after();
-          const uint32_t k0 = smem_u32(sK + (qk % NST) * SK_STAGE), d = tmem + ((qk & 1) ? S1_COL : S0_COL);
+          const uint32_t k0 = smem_u32(sK + (qk % NST) * SK_STAGE), d = tmem + S_COL;
 #pragma unroll 1
           for (int c = 0; c < NCH; ++c) {
             if (c < QT_CH) {
 #pragma unroll
               for (int k = 0; k < 4; ++k)
-                tc_mma_f16_ta(d, tmem + QT_COL + c * 32 + k * 8, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, (c | k) ? 1u : 0u);
+                tc_mma_f16_ta(d, tmem + QT_COL + c * 32 + k * 8, mla_desc_k_sw128(k0 + c * SK_CHUNK) + 2 * k, id_s, (c | k) ? 1u : 0u);
             } else {
 #pragma unroll
               for (int k = 0; k < 4; ++k)
-                tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + (c - QT_CH) * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * 4096) + 2 * k, id_s, 1u);
+                tc_mma_f16(d, mla_desc_k_sw128(smem_u32(sQ) + (c - QT_CH) * 16384) + 2 * k, mla_desc_k_sw128(k0 + c * SK_CHUNK) + 2 * k, id_s, 1u);
             }
             if (c + 1 < NCH) try_pv();
           }
-          tc_commit(&s_full[qk & 1]);
+          tc_commit(&s_full);
           ++qk;
           did = true;
         }
@@ -230,16 +233,18 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
-      if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+      if (!mbar_wait_bounded(&s_full, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
       tc_fence_after();
-      uint32_t sr[32];
-      tmem_ld_x16(tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL), sr);
-      tmem_ld_x16(tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL) + 16, sr + 16);
+      uint32_t sr[MKEYS];
+#pragma unroll
+      for (int j = 0; j < MKEYS / 16; ++j) tmem_ld_x16(tmem + lane_addr + S_COL + 16 * j, sr + 16 * j);
       tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s_free);                                // the scores are in registers: the next tile may overwrite them
       const int key0 = (t0 + i) * MKEYS;
       float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < MKEYS; ++j) {
         const int kp = key0 + j;
         const float v = (live && kp <= qpos && kp < kvlen) ? __uint_as_float(sr[j]) * sc2 : -INFINITY;
         sr[j] = __float_as_uint(v);
@@ -252,10 +257,10 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
       }
       // the probabilities only need the reference maximum, so they are computed while PV(i - 1) still runs; the
       // wait below guards the accumulator rescale and the P buffer, both of which PV(i - 1) uses
-      uint32_t pk[16];
+      uint32_t pk[MKEYS / 2];
       float psum = 0.f;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
+      for (int j = 0; j < MKEYS / 2; ++j) {
         const float a0 = __uint_as_float(sr[2 * j]), a1 = __uint_as_float(sr[2 * j + 1]);
         const float e0 = (m_ref == -INFINITY) ? 0.f : exp2f(a0 - m_ref), e1 = (m_ref == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
         psum += e0 + e1;
@@ -277,10 +282,10 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      // core-matrix layout: 8-row groups 512 B apart, the four 8-key columns 128 B apart, 16 B per row inside
+      // core-matrix layout: 8-row groups 1024 B apart, the eight 8-key columns 128 B apart, 16 B per row inside
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        *(uint4*)(sP + (r >> 3) * 512 + c * 128 + (r & 7) * 16) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      for (int c = 0; c < MKEYS / 8; ++c)
+        *(uint4*)(sP + (r >> 3) * (MKEYS * 16) + c * 128 + (r & 7) * 16) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full);

@@ -162,7 +162,7 @@ class MlaEngine(Engine):
     def attn_splits_for(self, n_seq: int, max_q_len: int, max_kv: int) -> int:
         tpt = max(1, 128 // self.heads_local)
         ctas = 2 * n_seq * (-(-max_q_len // tpt))
-        tiles = max(1, -(-max_kv // 32))
+        tiles = max(1, -(-max_kv // 64))         # the kernel walks the cache in 64-key tiles (one page)
         return max(1, min(tiles, 32, self.sm_count // ctas)) if max_q_len <= 16 else 1
 
     def _attention_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
