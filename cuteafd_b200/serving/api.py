@@ -63,6 +63,25 @@ def _cut_at_stop(text: str, stops) -> tuple[str, bool]:
     return (text[:cut], True) if cut >= 0 else (text, False)
 
 
+DASHBOARD_HTML = """<!doctype html><meta charset=utf-8><title>cuteafd-b200 console</title>
+<style>body{font:13px ui-monospace,monospace;margin:1.5em;background:#111;color:#ddd}h1{font-size:15px}table{border-collapse:collapse}
+td,th{padding:2px 10px;text-align:right;border-bottom:1px solid #333}th{color:#8bf}#ev{white-space:pre;color:#9c9;max-height:16em;overflow:auto}
+.bar{display:inline-block;height:9px;background:#4a8}</style>
+<h1>cuteafd-b200 console</h1><div id=top></div><h1>lanes</h1><table id=lanes></table><h1>draft acceptance by position</h1><div id=acc></div>
+<h1>recent requests</h1><table id=recent></table><h1>events</h1><div id=ev></div>
+<script>
+const row=(cells,tag='td')=>'<tr>'+cells.map(c=>`<${tag}>${c}</${tag}>`).join('')+'</tr>';
+async function tick(){try{const s=await (await fetch('/v1/console/snapshot')).json(),st=s.stats;
+top.textContent=`active ${st.active}  queued ${st.queued}  generated ${st.generated}  steps ${st.steps}  prefix hits ${st.prefix?st.prefix.hits:'-'}  free pages ${st.free_pages}  graphs ${st.graphs?st.graphs.captures:'-'}`;
+lanes.innerHTML=row(['request','prompt','prefilled','generated','cache hit'],'th')+s.lanes.map(l=>row([l.rid,l.prompt,l.prefilled,l.generated,l.cache_hit])).join('');
+acc.innerHTML=(st.draft_acceptance_by_position||[]).map((a,i)=>a==null?'':`#${i+1} <span class=bar style="width:${Math.round(a*200)}px"></span> ${(a*100).toFixed(0)}%<br>`).join('');
+recent.innerHTML=row(['request','prompt','generated','cache hit','finish'],'th')+s.recent.slice().reverse().map(r=>row([r.rid,r.prompt,r.generated,r.cache_hit,r.reason])).join('');
+}catch(e){top.textContent='unreachable: '+e}}
+setInterval(tick,1000);tick();
+const es=new EventSource('/v1/console/events');es.onmessage=m=>{ev.textContent=(m.data+'\n'+ev.textContent).slice(0,6000)};
+</script>"""
+
+
 class ServingLoop:
     """Owns the scheduler on one thread; HTTP tasks talk to it through thread-safe queues."""
 
@@ -250,7 +269,41 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
     async def console():
         s = loop.sched
         return {"lanes": [{"rid": a.req.rid, "prompt": len(a.req.prompt), "prefilled": a.prefilled, "generated": len(a.out),
-                           "cache_hit": a.cache_hit} for a in s.active], "queue": len(s.queue), "stats": s.snapshot()}
+                           "cache_hit": a.cache_hit} for a in list(s.active)], "queue": len(s.queue), "stats": s.snapshot(),
+                "recent": list(getattr(s, "recent", []))}
+
+    @app.get("/v1/console/events")
+    async def console_events(http: HttpRequest):
+        """Server-sent stream of scheduler events (decode rounds, finished requests); the scheduler only records events
+        while at least one viewer is connected."""
+        s = loop.sched
+
+        async def stream():
+            s.watchers += 1
+            last = None
+            try:
+                yield "retry: 2000\n\n"
+                while not await http.is_disconnected():
+                    evs = list(s.events)
+                    start = 0
+                    if last is not None:
+                        for i in range(len(evs) - 1, -1, -1):
+                            if evs[i] is last:
+                                start = i + 1
+                                break
+                    for e in evs[start:]:
+                        yield "data: " + json.dumps(e) + "\n\n"
+                    if evs:
+                        last = evs[-1]
+                    await asyncio.sleep(0.25)
+            finally:
+                s.watchers -= 1
+        return StreamingResponse(stream(), media_type="text/event-stream")
+
+    @app.get("/")
+    async def dashboard():
+        from fastapi.responses import HTMLResponse
+        return HTMLResponse(DASHBOARD_HTML)
 
     def openai_calls(calls):
         return [{"id": c["id"], "type": "function", "function": {"name": c["name"], "arguments": json.dumps(c["arguments"], ensure_ascii=False)}}

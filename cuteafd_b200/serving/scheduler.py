@@ -17,6 +17,7 @@ from typing import Callable, Protocol
 from ..engine.kv import PAGE, OutOfPages, PagePool, SeqKV
 from ..ref.ops import greedy_verify
 from ..ref.sampler import SamplingParams
+from ..utils.trace import PhaseProfile, SpeculationTrace
 from .draft_policy import DraftPolicy, SimpleDraftPolicy
 from .prefix import PrefixCache
 
@@ -109,6 +110,14 @@ class Scheduler:
         self._prefill_debt = 0.0
         self.stats = {"requests": 0, "finished": 0, "generated": 0, "prefill_tokens": 0, "steps": 0, "verify_rows": 0,
                       "drafted": 0, "accepted": 0, "failed": 0, "deferred": 0, "rejected": 0}
+        # observability: host phases of a step, draft acceptance by draft position, a ring of recent events for the
+        # console (only filled while somebody watches), the speculation trace file when the environment names one
+        self.profile = PhaseProfile()
+        self.accept_by_pos = [[0, 0] for _ in range(8)]          # [offered, accepted] per draft position
+        self.events: deque = deque(maxlen=512)
+        self.watchers = 0
+        self.spec_trace = SpeculationTrace()
+        self.recent: deque = deque(maxlen=32)
 
     # ------------------------------------------------------------------ intake
     def submit(self, req: Request) -> bool:
@@ -217,9 +226,11 @@ class Scheduler:
             budget -= len(inputs)
             plan.append((st, inputs))
             rows.append(Row(st, inputs, st.seq.length, list(range(len(inputs)))))
+        t0 = time.perf_counter()
         outs = self._run(rows)
         if outs is None:
             return
+        step_ms = (time.perf_counter() - t0) * 1e3
         for (st, inputs), target in zip(plan, outs):
             remaining = st.req.max_tokens - len(st.out)
             accepted, emitted, _, _ = greedy_verify(inputs, target, st.req.eos_id, max(1, remaining))
@@ -227,15 +238,22 @@ class Scheduler:
             self.stats["verify_rows"] += len(inputs)
             self.stats["drafted"] += len(inputs) - 1
             self.stats["accepted"] += accepted - 1
+            for pos in range(min(len(inputs) - 1, len(self.accept_by_pos))):
+                self.accept_by_pos[pos][0] += 1
+                self.accept_by_pos[pos][1] += 1 if pos < accepted - 1 else 0
+            if len(inputs) > 1:
+                self.spec_trace.record(st.req.rid, len(inputs) - 1, accepted - 1, step_ms)
             self.policy.observe(st.req.rid, len(inputs) - 1, accepted - 1)
             self._emit(st, emitted)
+        self._event("decode", rows=sum(len(i) for _, i in plan), seqs=len(plan), ms=round(step_ms, 3))
 
     def _run(self, rows: list[Row]):
         if not rows:
             return []
         try:
             self.stats["steps"] += 1
-            return self.runner.run(rows)
+            with self.profile.phase("run"):
+                return self.runner.run(rows)
         except Exception as e:  # a failed step fails the sequences in it, the server keeps going
             for r in rows:
                 self.stats["failed"] += 1
@@ -278,6 +296,8 @@ class Scheduler:
         else:
             st.seq.release(self.pool)
         self.stats["finished"] += 1
+        self.recent.append({"rid": st.req.rid, "prompt": len(st.req.prompt), "generated": len(st.out), "cache_hit": st.cache_hit, "reason": reason})
+        self._event("finish", rid=st.req.rid, reason=reason, generated=len(st.out))
         if st.req.on_token:
             try:
                 st.req.on_token(new or [], True, reason)
@@ -288,7 +308,8 @@ class Scheduler:
         """Returns False when there was nothing to do."""
         if self.fatal:
             return False
-        self._admit()
+        with self.profile.phase("admit"):
+            self._admit()
         self.active = [s for s in self.active if not s.finished]
         for s in self.active:
             if s.cancelled and s.prefilled == len(s.req.prompt):
@@ -316,8 +337,17 @@ class Scheduler:
             n += 1
         return n
 
+    def _event(self, kind: str, **fields):
+        """Console events cost nothing while nobody watches (docs/dashboard.md:1-24 in the reference: producers skip
+        work when there are no viewers)."""
+        if self.watchers > 0:
+            self.events.append(dict(fields, kind=kind, t=round(time.time(), 3), seq=self.stats["steps"]))
+
     def snapshot(self) -> dict:
+        census = getattr(getattr(self.runner, "eng", None), "census", None)
         return dict(self.stats, active=len(self.active), queued=len(self.queue),
                     prefilling=sum(1 for s in self.active if s.prefilled < len(s.req.prompt)),
                     prefix=self.prefix.snapshot() if self.prefix else None, draft_policy=self.policy.snapshot(),
-                    free_pages=self.pool.n_free, fatal=self.fatal)
+                    free_pages=self.pool.n_free, fatal=self.fatal, phases=self.profile.snapshot(),
+                    draft_acceptance_by_position=[round(a / o, 3) if o else None for o, a in self.accept_by_pos],
+                    graphs=census.snapshot() if census is not None else None)

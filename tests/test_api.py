@@ -255,3 +255,35 @@ def test_model_aliases_cors_and_gateway_off():
         assert off.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "max_tokens": 2}).status_code == 200
     finally:
         loop.stop()
+
+
+def test_console_dashboard_snapshot_and_scheduler_observability(client, tmp_path, monkeypatch):
+    assert "cuteafd-b200 console" in client.get("/").text
+    s = client.loop.sched
+    s.watchers += 1                                           # as if a dashboard were connected
+    client.post("/v1/chat/completions", headers=H, json={"messages": [{"role": "user", "content": "observe me"}], "max_tokens": 6})
+    snap = client.get("/v1/console/snapshot").json()
+    assert snap["recent"][-1]["generated"] == 6 and snap["stats"]["phases"]["run"]["n"] >= 1
+    kinds = {e["kind"] for e in s.events}
+    assert {"decode", "finish"} <= kinds
+    s.watchers -= 1
+    n = len(s.events)
+    client.post("/v1/chat/completions", headers=H, json={"messages": [{"role": "user", "content": "nobody watches"}], "max_tokens": 3})
+    assert len(s.events) == n                                 # no viewers: nothing recorded
+
+
+def test_speculation_trace_and_acceptance_by_position(tmp_path, monkeypatch):
+    from cuteafd_b200.serving.scheduler import NgramDrafter, Request
+    path = tmp_path / "spec.jsonl"
+    monkeypatch.setenv("CUTEAFD_SPECULATION_TRACE", str(path))
+    pool = PagePool(128)
+    runner = FakeRunner(vocab=50)
+    runner.next_token = lambda prefix: prefix[-4]             # period-4 stream: the n-gram drafter predicts it
+    sched = Scheduler(runner, pool, drafter=NgramDrafter(), max_draft=3)
+    sched.submit(Request("r", [1, 2, 3, 4] * 6, max_tokens=24))
+    sched.run_until_idle()
+    snap = sched.snapshot()
+    assert snap["drafted"] > 0 and snap["accepted"] > 0 and snap["draft_acceptance_by_position"][0] is not None
+    lines = [json.loads(l) for l in path.read_text().splitlines()]
+    assert lines and all(l["rid"] == "r" and 0 <= l["accepted"] <= l["drafted"] for l in lines)
+    assert sum(l["drafted"] for l in lines) == snap["drafted"]
