@@ -72,7 +72,7 @@ class ClockSampler:
 
 def reference_arm(args):
     out = {"impl": "reference", "unavailable": "reference cannot be built offline: its GEMM/attention/expert kernels are AOT exports "
-           "of the empty third_party/sparkinfer submodule and target sm_120/sm_121 only (no pip-installable package at /root/reference)"}
+           "of the empty third_party/sparkinfer submodule and target sm_120/sm_121 only (the reference tree holds no pip-installable package)"}
     print(json.dumps(out))
     return 0
 
