@@ -98,7 +98,7 @@ def build_serving(a):
     host = None
     if getattr(a, "host_cache_gib", 0) > 0:
         from .serving.hostcache import attach_host_tier
-        host = attach_host_tier(eng, a.host_cache_gib)
+        host = attach_host_tier(eng, max(0.0, a.host_cache_gib - a.host_cache_headroom_gib), min_tokens=a.host_cache_min_tokens)
     prefix = PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens, host=host)
     drafter = None
     if a.draft == "ngram":
@@ -313,6 +313,8 @@ def main(argv=None) -> int:
     p.add_argument("--decode-share", type=float, default=0.2); p.add_argument("--prefix-cache-entries", type=int, default=20)
     p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram", "mtp"])
     p.add_argument("--host-cache-gib", type=float, default=0.0, help="pinned host memory behind the prefix cache (0 = off)")
+    p.add_argument("--host-cache-headroom-gib", type=float, default=0.0, help="part of --host-cache-gib left unused")
+    p.add_argument("--host-cache-min-tokens", type=int, default=512, help="shorter prefixes are not written to the host tier")
     p.add_argument("--usage", default="off", choices=["on", "off"]); p.add_argument("--enable-bench", action="store_true")
     p.add_argument("--usage-dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage"))
     p.add_argument("--gateway", default="on", choices=["on", "off"]); p.add_argument("--official-model-names", default="")

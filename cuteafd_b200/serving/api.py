@@ -258,6 +258,11 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
     async def thermal_ep():
         return thermal.sample() if thermal is not None else {"available": False}
 
+    @app.get("/v1/fabric")
+    async def fabric_ep():
+        from ..utils.thermal import fabric_snapshot
+        return fabric_snapshot()
+
     @app.get("/usage")
     async def usage_ep(authorization: str = Header(None)):
         auth(authorization)

@@ -38,3 +38,37 @@ class ThermalMonitor:
                 "sm_max_mhz": int(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)),
                 "power_w": n.nvmlDeviceGetPowerUsage(h) / 1000.0, "temp_c": int(n.nvmlDeviceGetTemperature(h, n.NVML_TEMPERATURE_GPU)),
                 "reasons": active, "throttle_seconds": dict(self.throttle_s)}
+
+
+def fabric_snapshot(nvml=None) -> dict:
+    """Read-only view of the NVLink fabric for `/v1/fabric`: GPUs, which pairs can reach each other's memory, and the
+    NVLink link states NVML reports.  Nothing is changed on any GPU.  (Reference: `/v1/fabric` reports port traffic of the
+    RDMA fabric, cuteafd-api/src/openai.rs:340-347; on an NVSwitch node the fabric is NVLink.)"""
+    out: dict = {"available": False}
+    try:
+        import torch
+        n = torch.cuda.device_count()
+    except Exception:
+        return out
+    if n == 0:
+        return out
+    out = {"available": True, "gpus": n,
+           "peer_access": [[bool(i == j or torch.cuda.can_device_access_peer(i, j)) for j in range(n)] for i in range(n)]}
+    try:
+        if nvml is None:
+            import pynvml as nvml
+            nvml.nvmlInit()
+        links = []
+        for i in range(n):
+            h = nvml.nvmlDeviceGetHandleByIndex(i)
+            up = 0
+            for l in range(18):
+                try:
+                    up += 1 if nvml.nvmlDeviceGetNvLinkState(h, l) else 0
+                except Exception:
+                    break
+            links.append(up)
+        out["nvlink_links_up"] = links
+    except Exception:
+        pass
+    return out

@@ -287,3 +287,8 @@ def test_speculation_trace_and_acceptance_by_position(tmp_path, monkeypatch):
     lines = [json.loads(l) for l in path.read_text().splitlines()]
     assert lines and all(l["rid"] == "r" and 0 <= l["accepted"] <= l["drafted"] for l in lines)
     assert sum(l["drafted"] for l in lines) == snap["drafted"]
+
+
+def test_fabric_endpoint_without_gpus(client):
+    r = client.get("/v1/fabric")
+    assert r.status_code == 200 and "available" in r.json()
