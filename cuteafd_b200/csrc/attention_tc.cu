@@ -377,6 +377,26 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   if (warp == 1) tmem_dealloc(tmem, 256);
 }
 
+// Context split (a long context whose KV pages live on several GPUs): every owner runs the attention over ITS pages
+// with "partials only" armed, which leaves the unnormalised outputs and (max, sum) pairs of its splits in the scratch
+// buffers instead of merging them; the partials of all owners are then laid side by side ([owner 0 splits | owner 1
+// splits | ...], moved with the ordinary peer copy) and merged once by `cuteafd_attn_merge`.  For decode rows
+// (one query token per sequence) every cached key is visible to the query, so each owner simply passes the length of
+// its own part.  Reference: the token-split attention exchange of the two-GPU coordinator split
+// (shared/peer_split/context.rs) and its `lse_combine2` primitive.
+static thread_local bool g_partials_only = false;
+extern "C" int cuteafd_attn_partials_only() { g_partials_only = true; return CA_OK; }   // arms the next attention call of this thread
+
+extern "C" int cuteafd_attn_merge(const float* part_o, const float* part_ml, const float* sink, void* out, int T, int Hq, int n_parts,
+                                  cudaStream_t s) {
+  CA_REQUIRE(part_o && part_ml && out && n_parts >= 1, "attn_merge: needs partials");
+  if (T <= 0) return CA_OK;
+  CA_LAUNCH_PDL(attn_merge8_kernel, dim3(T, (Hq * AD / 8 + 127) / 128), 128, 0, s, part_o, part_ml, sink, (bf16*)out, T, Hq, (int)AD, n_parts,
+                (uint8_t*)nullptr, (uint8_t*)nullptr, 0, (const float*)nullptr, 0);
+  CA_CHECK_LAUNCH("attn_merge");
+  return CA_OK;
+}
+
 extern "C" int cuteafd_paged_attention_tc(const void* q, const void* kv_map, const int* page_table, const int* kv_len,
                                           const int* q_start, const int* q_len, const float* sink, void* out, float* part_o,
                                           float* part_ml, int T, int n_seq, int max_q_len, int q_stride, int Hq, int Hkv,
@@ -388,6 +408,9 @@ extern "C" int cuteafd_paged_attention_tc(const void* q, const void* kv_map, con
   CA_REQUIRE(Hq % Hkv == 0 && 128 % (Hq / Hkv) == 0, "paged_attention_tc: group size %d unsupported", Hq / Hkv);
   CA_REQUIRE(n_splits >= 1 && (n_splits == 1 || (part_o && part_ml)), "paged_attention_tc: split-KV needs scratch");
   CA_REQUIRE(q_stride % 8 == 0, "paged_attention_tc: q rows must be 16-byte aligned");
+  const bool partials_only = g_partials_only;
+  g_partials_only = false;
+  CA_REQUIRE(!partials_only || n_splits >= 2, "paged_attention_tc: partials-only needs at least two splits");
   if (T <= 0 || n_seq <= 0) return CA_OK;
   AttnTcArgs a;
   a.q = (const bf16*)q; a.kv_map = (const CUtensorMap*)kv_map; a.page_table = page_table; a.kv_len = kv_len; a.q_start = q_start;
@@ -408,7 +431,7 @@ extern "C" int cuteafd_paged_attention_tc(const void* q, const void* kv_map, con
   dim3 grid(n_splits, Hkv, n_seq * a.max_q_tiles);
   CA_LAUNCH_PDL(paged_attn_tc_kernel, grid, 192, smem, s, a);
   CA_CHECK_LAUNCH("paged_attention_tc");
-  if (n_splits > 1) {
+  if (n_splits > 1 && !partials_only) {
     CA_LAUNCH_PDL(attn_merge8_kernel, dim3(T, (Hq * AD / 8 + 127) / 128), 128, 0, s, part_o, part_ml, sink, (bf16*)out, T, Hq, (int)AD, n_splits,
                   (uint8_t*)q_out, (uint8_t*)sf_out, ldsf, inv_gs, qkind);
     CA_CHECK_LAUNCH("attn_merge");

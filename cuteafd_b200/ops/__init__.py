@@ -441,17 +441,48 @@ def encode_kv_tmaps(kv: torch.Tensor) -> torch.Tensor:
 
 
 def paged_attention_tc(q, kv_map, page_table, kv_len, q_start, q_len, out, *, T, n_seq, max_q_len, q_stride, Hq, Hkv,
-                       n_splits=1, part_o=None, part_ml=None, window=0, sink=None, scale=None, status=None, quant=None, inv_gs=None) -> bool:
+                       n_splits=1, part_o=None, part_ml=None, window=0, sink=None, scale=None, status=None, quant=None, inv_gs=None,
+                       partials_only=False) -> bool:
     """Tensor-core (tcgen05) paged attention for head_dim 128; `kv_map` is one row of `encode_kv_tmaps`.
     `quant` (an FP4 activation buffer): with split-KV the merge also writes the output rows quantised for the output
-    projection.  Returns True when that happened (False: the caller quantises `out` itself)."""
-    fused = quant is not None and quant.kind in FP4_KINDS and n_splits > 1 and (Hq * 128) % 256 == 0
+    projection.  Returns True when that happened (False: the caller quantises `out` itself).
+    `partials_only` (context split, needs n_splits >= 2): leave the unnormalised split outputs in `part_o` / `part_ml`
+    ([n_splits, T, Hq, 128] / [n_splits, T, Hq, 2]) and do not merge; `attn_merge` finishes over all owners' partials."""
+    fused = quant is not None and quant.kind in FP4_KINDS and n_splits > 1 and (Hq * 128) % 256 == 0 and not partials_only
+    if partials_only:
+        call("cuteafd_attn_partials_only")
     call("cuteafd_paged_attention_tc", ptr(q), ptr(kv_map), ptr(page_table), ptr(kv_len), ptr(q_start), ptr(q_len), ptr(sink),
          ptr(out), ptr(part_o), ptr(part_ml), T, n_seq, max_q_len, q_stride, Hq, Hkv, page_table.shape[1], n_splits, window,
          float(scale if scale is not None else 128 ** -0.5), ptr(status), ptr(quant.data) if fused else None,
          ptr(quant.sf) if fused else None, quant.sf.shape[1] if fused else 0, ptr(inv_gs) if fused else None,
          (2 if quant.kind == KIND_MXFP4 else 1) if fused else 0, stream())
     return fused
+
+
+def attn_merge(part_o, part_ml, out, *, T, Hq, n_parts, sink=None):
+    """Merges `n_parts` attention partials laid side by side (unnormalised outputs [n_parts, T, Hq, 128] fp32 and
+    (max, sum) pairs [n_parts, T, Hq, 2]) into `out` [T, Hq * 128] bf16.  With a context split the parts are the
+    splits of every GPU that owns a piece of the context."""
+    call("cuteafd_attn_merge", ptr(part_o), ptr(part_ml), ptr(sink), ptr(out), T, Hq, n_parts, stream())
+    return out
+
+
+def context_split_attention(q, kv_maps, page_tables, kv_lens, q_start, q_len, out, *, T, n_seq, Hq, Hkv, splits_per_part=2, scale=None,
+                            status=None, sink=None):
+    """Decode attention over a context whose pages are held in several paged stores (one per owner): partial attention
+    per owner, then one merge.  On one GPU the owners are just different stores, which is how the path is tested; across
+    GPUs every owner runs its own part and ships its `part_o` / `part_ml` slices to the merging rank with the peer copy.
+    Decode rows only (one query token per sequence): every cached key is visible, so each owner passes its own length."""
+    n_own = len(kv_maps)
+    s = splits_per_part
+    part_o = torch.empty(n_own * s * T * Hq * 128, dtype=torch.float32, device=q.device)
+    part_ml = torch.empty(n_own * s * T * Hq * 2, dtype=torch.float32, device=q.device)
+    for o in range(n_own):
+        po = part_o[o * s * T * Hq * 128:(o + 1) * s * T * Hq * 128]
+        pm = part_ml[o * s * T * Hq * 2:(o + 1) * s * T * Hq * 2]
+        paged_attention_tc(q, kv_maps[o], page_tables[o], kv_lens[o], q_start, q_len, out, T=T, n_seq=n_seq, max_q_len=1, q_stride=q.stride(0),
+                           Hq=Hq, Hkv=Hkv, n_splits=s, part_o=po, part_ml=pm, scale=scale, status=status, partials_only=True)
+    return attn_merge(part_o, part_ml, out, T=T, Hq=Hq, n_parts=n_own * s, sink=sink)
 
 
 # ------------------------------------------------------------------ sampling

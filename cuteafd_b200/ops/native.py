@@ -37,6 +37,8 @@ _PROTOS = {
     "cuteafd_gather_rows": [P, P, P, P, I, I, P],
     "cuteafd_act_quant_fp8_ue8m0": [P, P, P, I, I, P],
     "cuteafd_kv_pages_copy": [P, L, I, I, P, I, P, L, I, P],
+    "cuteafd_attn_merge": [P, P, P, P, I, I, I, P],
+    "cuteafd_attn_partials_only": [],
     "cuteafd_l2_prefetch": [P, L, P],
     "cuteafd_silu_mul": [P, P, P, L, F, P],
     "cuteafd_router_select": [P, P, P, P, I, I, I, I, I, F, I, I, P],

@@ -591,3 +591,42 @@ def test_kv_pages_copy_roundtrip_through_pinned_host_and_l2_prefetch():
         want = kv[:, src * 64:(src + 1) * 64]
         assert torch.equal(kv2[:, dst * 64:(dst + 1) * 64], want) and torch.equal(kv3[:, dst * 64:(dst + 1) * 64], want)
     assert kv2[:, :64].abs().sum() == 0
+
+
+def test_context_split_attention_matches_attention_over_the_whole_context():
+    """A context cut in two parts held in two separate paged stores (as on two GPUs): partial attention per part plus one
+    merge equals attention over the whole context."""
+    D, Hq, Hkv, n_seq = 128, 16, 2, 3
+    g = torch.Generator().manual_seed(3)
+    lens_a, lens_b = [192, 64, 130], [70, 200, 1]            # older part, newer part (the query is the last token of b)
+    q = torch.randn(n_seq, Hq, D, generator=g)
+    stores, tables, keys, vals = [], [], [[], [], []], [[], [], []]
+    for part, lens in enumerate((lens_a, lens_b)):
+        cache = torch.zeros(1, 16 * 64, 2, Hkv, D)
+        pt = torch.zeros(n_seq, 4, dtype=torch.int32)
+        nxt = 1
+        for i, L in enumerate(lens):
+            k, v = torch.randn(L, Hkv, D, generator=g), torch.randn(L, Hkv, D, generator=g)
+            keys[i].append(k), vals[i].append(v)
+            pages = list(range(nxt, nxt + -(-L // 64)))
+            nxt += len(pages)
+            pt[i, :len(pages)] = torch.tensor(pages)
+            slots = torch.tensor([pages[t // 64] * 64 + t % 64 for t in range(L)])
+            cache[0, slots, 0], cache[0, slots, 1] = k, v
+        stores.append(cache.to(torch.bfloat16).to(DEV).contiguous())
+        tables.append(pt.to(DEV))
+    maps = [ops.encode_kv_tmaps(s)[0] for s in stores]
+    out = torch.zeros(n_seq, Hq * D, dtype=torch.bfloat16, device=DEV)
+    st = status_word()
+    ones = torch.ones(n_seq, dtype=torch.int32, device=DEV)
+    ops.context_split_attention(q.to(torch.bfloat16).to(DEV).view(n_seq, -1).contiguous(), maps, tables,
+                                [torch.tensor(l, dtype=torch.int32, device=DEV) for l in (lens_a, lens_b)],
+                                torch.arange(n_seq, dtype=torch.int32, device=DEV), ones, out, T=n_seq, n_seq=n_seq, Hq=Hq, Hkv=Hkv, status=st)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    got = out.float().cpu().view(n_seq, Hq, D)
+    for i in range(n_seq):
+        k, v = torch.cat(keys[i]), torch.cat(vals[i])
+        L = k.shape[0]
+        ref = rops.attention(bf16r(q[i:i + 1]), bf16r(k), bf16r(v), torch.arange(L - 1, L), torch.arange(L))
+        assert torch.allclose(got[i:i + 1], ref, atol=3e-2, rtol=3e-2), f"seq {i}: max err {(got[i:i + 1] - ref).abs().max()}"
