@@ -18,7 +18,12 @@ import sys
 
 def cmd_plan(a) -> int:
     from .loader.plan import plan
-    rep = plan(a.model, world=a.gpus, layout=a.layout, files=a.files, pool_tokens=a.pool_tokens, gpu_gib=a.gpu_gib)
+    rep = plan(a.model, world=a.gpus, layout=a.layout or a.deployment, files=a.files, pool_tokens=a.pool_tokens, gpu_gib=a.gpu_gib,
+               attn_groups=a.attn_groups)
+    if a.deployment and rep.layout is not None:
+        from .loader.plan import deployment_decisions
+        print(json.dumps(deployment_decisions(rep.layout, a.model), indent=2))
+        return 0 if rep.supported else 2
     print(json.dumps(rep.to_json(), indent=2) if a.json else rep.text())
     return 0 if rep.supported else 2
 
@@ -300,6 +305,8 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="cmd", required=True)
     p = sub.add_parser("plan"); p.add_argument("model"); p.add_argument("--layout", action="store_true"); p.add_argument("--files", action="store_true")
     p.add_argument("--gpus", type=int, default=8); p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--gpu-gib", type=int, default=180)
+    p.add_argument("--attn-groups", type=int, default=1, help="data-parallel attention groups sharing the expert ranks")
+    p.add_argument("--deployment", action="store_true", help="print the typed launch decisions of the layout as JSON")
     p.add_argument("--json", action="store_true"); p.set_defaults(fn=cmd_plan)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
     p = sub.add_parser("run"); p.add_argument("--config", required=True); p.add_argument("--set", action="append", default=[])

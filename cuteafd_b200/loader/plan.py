@@ -55,7 +55,31 @@ class PlanReport:
         return "\n".join(out)
 
 
-def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = False, pool_tokens: int = 0, gpu_gib: int = 180) -> PlanReport:
+def deployment_decisions(layout: "placement.Layout", model: str, port: int = 29500) -> dict:
+    """Typed launch decisions for a solved layout: who does what, and the command that starts every rank of the node
+    (reference: `cuteafd plan --deployment`, which turns a layout into per-role / per-host daemon arguments)."""
+    dep = layout.deployment
+    groups = [{"group": g, "ranks": list(dep.group_ranks(g))} for g in range(dep.attn_groups)]
+    roles = []
+    for r in layout.ranks:
+        entry = {"rank": r.rank, "role": r.role, "device": r.rank}
+        if r.rank in dep.attn_ranks:
+            entry["attention_group"] = dep.group_of(r.rank)
+            entry["tp_rank"] = list(dep.group_ranks(dep.group_of(r.rank))).index(r.rank)
+        if r.rank in dep.expert_ranks:
+            entry["ep_rank"] = list(dep.expert_ranks).index(r.rank)
+        roles.append(entry)
+    return {"parallelism": dep.describe(), "world": dep.world, "attention_groups": groups, "expert_ranks": list(dep.expert_ranks),
+            "pool_tokens_per_group": layout.pool_tokens, "ranks": roles,
+            "launch": {"serve": f"python -m cuteafd_b200.cli serve --model {model}" if dep.world == 1 else None,
+                       "decode_bench": (f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {dep.world} --master-addr 127.0.0.1 "
+                                        f"--master-port {port} bench.py --gpus {dep.world} --attn-groups {dep.attn_groups}") if dep.world > 1
+                                       else "python bench.py --gpus 1"},
+            "env": {"NCCL_NVLS_ENABLE": "0"} if dep.world > 1 else {}}
+
+
+def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = False, pool_tokens: int = 0, gpu_gib: int = 180,
+         attn_groups: int = 1) -> PlanReport:
     """`model` is a snapshot directory (config.json + *.safetensors) or one of the named synthetic shapes."""
     problems, hints, counts, flist = [], [], Counter(), []
     p = Path(model)
@@ -94,7 +118,12 @@ def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = Fals
     rep = PlanReport(model, family, spec, supported=spec is not None and not problems, format_counts=dict(counts), problems=problems,
                      hints=hints, files=flist)
     if layout and spec is not None:
-        rep.layout = placement.solve(spec, world=world, gpu_bytes=gpu_gib * placement.GIB, pool_tokens=pool_tokens)
+        from ..config import default_deployment
+        rep.layout = placement.solve(spec, world=world, gpu_bytes=gpu_gib * placement.GIB, pool_tokens=pool_tokens,
+                                     deployment=default_deployment(world, attn_groups))
+        if attn_groups > 1:
+            rep.layout.notes.append(f"{attn_groups} data-parallel attention groups: the pool is per group "
+                                    f"({attn_groups * rep.layout.pool_tokens} tokens in total)")
         if not rep.layout.fits:
             rep.supported = False
     return rep

@@ -44,3 +44,16 @@ def test_dispatch_flag_slots_are_distinct_per_group_and_tp_rank():
                 offs.add(flag_offset(spec, ph, layer, src))
     assert len(offs) == 3 * spec.n_layers * 8 and max(offs) < 3 * spec.n_layers * 8 * 4
     assert {g * d.tp + t for g in range(d.attn_groups) for t in range(d.tp)} == {0, 1, 2, 3}
+
+
+def test_plan_deployment_decisions_for_two_attention_groups():
+    from cuteafd_b200.loader.plan import deployment_decisions, plan
+    rep = plan("qwen3-235b", world=8, layout=True, attn_groups=2)
+    d = deployment_decisions(rep.layout, "qwen3-235b")
+    assert d["parallelism"] == "attn-dp2xtp2+ep4" and d["expert_ranks"] == [4, 5, 6, 7]
+    assert [g["ranks"] for g in d["attention_groups"]] == [[0, 1], [2, 3]]
+    r3, r6 = d["ranks"][3], d["ranks"][6]
+    assert r3["attention_group"] == 1 and r3["tp_rank"] == 1 and r6["ep_rank"] == 2 and "attention_group" not in r6
+    assert "--attn-groups 2" in d["launch"]["decode_bench"] and d["env"] == {"NCCL_NVLS_ENABLE": "0"}
+    one = deployment_decisions(plan("qwen3-235b", world=1, layout=True).layout, "qwen3-235b")
+    assert one["parallelism"] == "single" and one["launch"]["serve"].endswith("--model qwen3-235b")
