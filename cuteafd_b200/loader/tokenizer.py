@@ -17,12 +17,43 @@ class ByteTokenizer:
         return bytes(i for i in ids if i < 256).decode("utf-8", errors="replace")
 
 
+def _eos_ids(snapshot: Path, tk) -> list[int]:
+    """End-of-sequence ids of a snapshot: `generation_config.json` / `config.json` (`eos_token_id`, int or list), else the
+    id of `eos_token` named in `tokenizer_config.json`."""
+    import json
+    ids: list[int] = []
+    for name in ("generation_config.json", "config.json"):
+        f = snapshot / name
+        if f.exists():
+            try:
+                v = json.loads(f.read_text()).get("eos_token_id")
+            except Exception:
+                v = None
+            for x in (v if isinstance(v, list) else [v]):
+                if isinstance(x, int) and x not in ids:
+                    ids.append(x)
+    f = snapshot / "tokenizer_config.json"
+    if f.exists():
+        try:
+            tok = json.loads(f.read_text()).get("eos_token")
+            tok = tok.get("content") if isinstance(tok, dict) else tok
+            i = tk.token_to_id(tok) if isinstance(tok, str) else None
+            if i is not None and i not in ids:
+                ids.append(i)
+        except Exception:
+            pass
+    return ids
+
+
 class HFTokenizer:
     def __init__(self, path: str):
         from tokenizers import Tokenizer
         self.tk = Tokenizer.from_file(path)
         self.vocab_size = self.tk.get_vocab_size()
-        self.eos_id = self.bos_id = None
+        eos = _eos_ids(Path(path).parent, self.tk)
+        self.eos_id = eos[0] if eos else None
+        self.stop_ids = tuple(eos[1:])                 # further ids that end a turn (e.g. <|im_end|> next to <|endoftext|>)
+        self.bos_id = None
 
     def encode(self, text: str) -> list[int]:
         return self.tk.encode(text, add_special_tokens=False).ids

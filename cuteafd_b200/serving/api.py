@@ -233,7 +233,8 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                 meta["hit"] = next((a.cache_hit for a in loop.sched.active if a.req.rid == rid), 0)
             aloop.call_soon_threadsafe(events.put_nowait, (toks, done, reason))
         req = Request(rid, prompt_ids, max_tokens=max(1, min(max_tokens, max_output)), sampling=sampling_from(body),
-                      eos_id=getattr(tok, "eos_id", None), on_token=on_token, constraint=constraint,
+                      eos_id=getattr(tok, "eos_id", None), stop_ids=tuple(getattr(tok, "stop_ids", ()) or ()), on_token=on_token,
+                      constraint=constraint,
                       use_cache=not (probe or {}).get("skip_cache", False), allow_drafts=not (probe or {}).get("no_drafts", False))
         if not loop.submit(req):
             raise HTTPException(429, "admission queue is full")

@@ -110,3 +110,18 @@ def test_choice_constraint_and_response_format_mapping():
     assert c.top == "array"
     e = constraint_from_request({"response_format": {"type": "json_schema", "json_schema": {"schema": {"enum": ["a", "b"]}}}}, tok, 258, 0, 257)
     assert isinstance(e, ChoiceConstraint) and e.choices == ['"a"', '"b"']
+
+
+def test_hf_tokenizer_reads_end_of_sequence_ids_from_the_snapshot(tmp_path):
+    import pytest
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from cuteafd_b200.loader.tokenizer import load_tokenizer
+    vocab = {"<|endoftext|>": 0, "<|im_end|>": 1, "a": 2, "b": 3, "[UNK]": 4}
+    tk = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tk.pre_tokenizer = pre_tokenizers.Whitespace()
+    tk.save(str(tmp_path / "tokenizer.json"))
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [1, 0]}))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"eos_token": {"content": "<|im_end|>"}}))
+    t = load_tokenizer(str(tmp_path))
+    assert t.eos_id == 1 and t.stop_ids == (0,) and t.encode("a b") == [2, 3]
