@@ -4,7 +4,8 @@ A constraint object has `mask(tokens) -> int32 bit words [ceil(vocab / 32)] | No
 what the runner hands to the masked argmax / sampler kernels for rows that carry one.  Two grammars are built in:
 
   * `JsonConstraint`: the completion must be one JSON value (optionally an object / array at the top, for
-    `response_format = json_object` and the top-level type of a `json_schema`), then end of sequence;
+    `response_format = json_object`), or follow a `json_schema` in the subset `SchemaPrefix` enforces (types, properties,
+    required, closed objects, items, string enums), then end of sequence;
   * `ChoiceConstraint`: the completion must be exactly one of a list of strings (tool_choice by name, enums).
 
 Both work on the decoded text of single tokens, so they run with any tokenizer that can decode one id at a time.  The
@@ -185,6 +186,129 @@ class JsonPrefix:
         return True
 
 
+_FIRST = {"object": "{", "array": "[", "string": '"', "number": "-0123456789", "integer": "-0123456789", "boolean": "tf", "null": "n"}
+
+
+class SchemaPrefix:
+    """`JsonPrefix` plus a cursor into a JSON schema, for the subset that covers tool arguments and typical
+    `response_format` schemas: `type` (also a list of types), `properties`, `required`, `additionalProperties: false`,
+    `items`, string `enum`, `integer` vs `number`.  Anything else in a schema is ignored (not enforced)."""
+
+    def __init__(self, schema: dict):
+        self.j = JsonPrefix()
+        self.frames: list = []            # [schema, kind, seen keys, key being typed or None]
+        self.cur = schema if isinstance(schema, dict) else {}
+        self.enum: list | None = None     # inside a string value restricted to choices: [choices, typed so far]
+        self.integer = False
+
+    def copy(self) -> "SchemaPrefix":
+        c = SchemaPrefix.__new__(SchemaPrefix)
+        c.j, c.cur, c.integer = self.j.copy(), self.cur, self.integer
+        c.frames = [[f[0], f[1], set(f[2]), f[3]] for f in self.frames]
+        c.enum = None if self.enum is None else [self.enum[0], self.enum[1]]
+        return c
+
+    def signature(self):
+        return (self.j.signature(), tuple((id(f[0]), f[1], frozenset(f[2]), f[3]) for f in self.frames), id(self.cur),
+                None if self.enum is None else self.enum[1], self.integer)
+
+    @property
+    def stack(self):
+        return self.j.stack
+
+    @property
+    def mode(self):
+        return self.j.mode
+
+    @property
+    def complete(self) -> bool:
+        return self.j.complete
+
+    @staticmethod
+    def _types(schema: dict):
+        t = schema.get("type")
+        if isinstance(schema.get("enum"), list) and schema["enum"] and all(isinstance(e, str) for e in schema["enum"]):
+            return ["string"]
+        return [t] if isinstance(t, str) else (list(t) if isinstance(t, list) else [])
+
+    def _start_ok(self, ch: str) -> bool:
+        types = self._types(self.cur)
+        if types and not any(ch in _FIRST.get(t, "") for t in types):
+            return False
+        if ch == "{":
+            self.frames.append([self.cur, "{", set(), None])
+        elif ch == "[":
+            self.frames.append([self.cur, "[", set(), None])
+            self.cur = self.cur.get("items") if isinstance(self.cur.get("items"), dict) else {}
+        elif ch == '"':
+            e = self.cur.get("enum")
+            self.enum = [[x for x in e if isinstance(x, str)], ""] if isinstance(e, list) and e else None
+        elif ch in "-0123456789":
+            self.integer = "integer" in types and "number" not in types
+        return True
+
+    def _close_ok(self, ch: str) -> bool:
+        if not self.frames:
+            return True
+        schema, kind, seen, _ = self.frames[-1]
+        if ch == "}" and kind == "{":
+            if any(r not in seen for r in schema.get("required", []) or []):
+                return False
+            self.frames.pop()
+        elif ch == "]" and kind == "[":
+            self.frames.pop()
+        elif ch == "," and kind == "[":
+            self.cur = schema.get("items") if isinstance(schema.get("items"), dict) else {}
+        return True
+
+    def feed(self, ch: str) -> bool:
+        m = self.j.mode
+        if m == "number" and not (ch.isdigit() or ch in ".eE+-"):
+            m = "after"                                         # the number ends here; `ch` is judged as what follows a value
+        if m == "number" and self.integer and ch in ".eE":
+            return False
+        if m == "key":
+            f = self.frames[-1]
+            props = f[0].get("properties") if isinstance(f[0].get("properties"), dict) else None
+            closed = props is not None and f[0].get("additionalProperties") is False
+            if ch == '"':
+                key = f[3] or ""
+                if key in f[2] or (closed and key not in props):
+                    return False
+                f[2].add(key)
+                self.cur = (props or {}).get(key, {}) if isinstance((props or {}).get(key, {}), dict) else {}
+                f[3] = None
+            else:
+                if closed and ch == "\\":
+                    return False
+                f[3] = (f[3] or "") + ch
+                if closed and not any(k.startswith(f[3]) and k not in f[2] for k in props):
+                    return False
+        elif m == "string" and self.enum is not None:
+            if ch == '"':
+                if self.enum[1] not in self.enum[0]:
+                    return False
+                self.enum = None
+            else:
+                self.enum[1] += ch
+                if ch == "\\" or not any(c.startswith(self.enum[1]) for c in self.enum[0]):
+                    return False
+        elif ch not in WS:
+            if m in ("value", "value_or_end") and not (m == "value_or_end" and ch == "]"):
+                if not self._start_ok(ch):
+                    return False
+            elif m == "value_or_end" or (m in ("after", "key_or_end") and ch in "}],"):
+                if not self._close_ok(ch):
+                    return False
+        return self.j.feed(ch)
+
+    def feed_text(self, text: str) -> bool:
+        for ch in text:
+            if not self.feed(ch):
+                return False
+        return True
+
+
 def _pack_bits(allowed: list[bool]) -> torch.Tensor:
     n = len(allowed)
     words = torch.zeros((n + 31) // 32, dtype=torch.int64)
@@ -225,16 +349,20 @@ def token_pieces(tokenizer, vocab_size: int) -> list:
 
 
 class JsonConstraint(_TextConstraint):
-    def __init__(self, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None = None, top: str | None = "object"):
+    def __init__(self, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None = None, top: str | None = "object",
+                 schema: dict | None = None):
         super().__init__(tokenizer, vocab_size, prompt_len, eos_id)
-        self.top = top
-        self.state, self.seen = JsonPrefix(top), 0
+        self.top, self.schema = top, schema
+        self.state, self.seen = self._fresh(), 0
         self.cache: dict = {}
+
+    def _fresh(self):
+        return SchemaPrefix(self.schema) if self.schema else JsonPrefix(self.top)
 
     def _advance(self, tokens):
         gen = tokens[self.prompt_len:]
         if len(gen) < self.seen:                       # a speculative tail was rolled back: replay
-            self.state, self.seen = JsonPrefix(self.top), 0
+            self.state, self.seen = self._fresh(), 0
         for t in gen[self.seen:]:
             if t != self.eos_id:
                 self.state.feed_text(self.pieces[t] or "")
@@ -290,7 +418,8 @@ def constraint_from_request(body: dict, tokenizer, vocab_size: int, prompt_len: 
             import json
             return ChoiceConstraint(tokenizer, vocab_size, prompt_len, [json.dumps(e) for e in schema["enum"]], eos_id)
         top = {"object": "object", "array": "array"}.get(schema.get("type"))
-        return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, top=top)
+        enforce = any(k in schema for k in ("properties", "items", "required", "type"))
+        return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, top=top, schema=schema if enforce else None)
     return None
 
 

@@ -125,3 +125,42 @@ def test_hf_tokenizer_reads_end_of_sequence_ids_from_the_snapshot(tmp_path):
     (tmp_path / "tokenizer_config.json").write_text(json.dumps({"eos_token": {"content": "<|im_end|>"}}))
     t = load_tokenizer(str(tmp_path))
     assert t.eos_id == 1 and t.stop_ids == (0,) and t.encode("a b") == [2, 3]
+
+
+SCHEMA = {"type": "object", "additionalProperties": False, "required": ["city", "days"],
+          "properties": {"city": {"type": "string"}, "days": {"type": "integer"}, "unit": {"enum": ["C", "F"]},
+                         "tags": {"type": "array", "items": {"type": "string"}},
+                         "geo": {"type": "object", "properties": {"lat": {"type": "number"}}, "required": ["lat"]}}}
+
+
+def test_schema_prefix_enforces_types_required_closed_objects_items_and_enums():
+    from cuteafd_b200.serving.constraints import SchemaPrefix
+    good = ['{"city": "Oslo", "days": 3}', '{"days":2,"city":"x","unit":"F","tags":["a","b"],"geo":{"lat":1.5}}', ' { "city" : "a" , "days" : -1 } ']
+    bad = ['{"city": "Oslo"}', '{"city": 1, "days": 2}', '{"city":"a","days":2.5}', '{"city":"a","days":2,"x":1}', '{"city":"a","days":2,"unit":"K"}',
+           '{"city":"a","days":2,"tags":[1]}', '{"city":"a","days":2,"geo":{}}', "[1]", '{"city":"a","city":"b","days":1}']
+    for t in good:
+        p = SchemaPrefix(SCHEMA)
+        assert p.feed_text(t) and p.complete, t
+    for t in bad:
+        p = SchemaPrefix(SCHEMA)
+        assert not (p.feed_text(t) and p.complete), t
+
+
+def test_schema_constrained_random_walk_yields_valid_documents():
+    tok, rng, done = ByteTokenizer(), random.Random(1), 0
+    for _ in range(10):
+        c, toks = JsonConstraint(tok, 258, 0, eos_id=257, schema=SCHEMA), []
+        for _ in range(400):
+            allowed = [i for i, a in enumerate(unpack_bits(c.mask(toks), 258)) if a]
+            assert allowed
+            closers = [a for a in allowed if a in (257, ord("}"), ord("]"), ord('"'), ord(","), ord(":"))]
+            toks.append(rng.choice(closers) if closers and rng.random() < 0.6 else rng.choice(allowed))
+            if toks[-1] == 257:
+                break
+        if toks[-1] == 257:
+            v = json.loads(tok.decode(toks[:-1]))
+            assert isinstance(v["city"], str) and isinstance(v["days"], int) and set(v) <= set(SCHEMA["properties"])
+            done += 1
+    assert done >= 1
+    c = constraint_from_request({"response_format": {"type": "json_schema", "json_schema": {"schema": SCHEMA}}}, tok, 258, 0, 257)
+    assert c.schema is SCHEMA
