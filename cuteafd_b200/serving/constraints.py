@@ -24,7 +24,8 @@ WS = " \t\n\r"
 
 class JsonPrefix:
     """Recogniser of prefixes of one JSON value.  `feed(ch)` returns False when `ch` cannot follow."""
-    __slots__ = ("stack", "mode", "lit", "lit_pos", "hex_left", "num", "done", "top")
+    __slots__ = ("stack", "mode", "lit", "lit_pos", "hex_left", "num", "done", "top", "ws_run")
+    MAX_WS = 2                          # consecutive whitespace characters between tokens (a model must not stall on blanks)
 
     def __init__(self, top: str | None = None):
         self.stack: list[str] = []      # "{" / "[" frames; the mode says where in the frame we are
@@ -32,14 +33,16 @@ class JsonPrefix:
         self.lit, self.lit_pos, self.hex_left, self.num = "", 0, 0, ""
         self.done = False
         self.top = top                  # None | "object" | "array"
+        self.ws_run = 0
 
     def copy(self) -> "JsonPrefix":
         c = JsonPrefix(self.top)
         c.stack, c.mode, c.lit, c.lit_pos, c.hex_left, c.num, c.done = list(self.stack), self.mode, self.lit, self.lit_pos, self.hex_left, self.num, self.done
+        c.ws_run = self.ws_run
         return c
 
     def signature(self):
-        return (tuple(self.stack), self.mode, self.lit, self.lit_pos, self.hex_left, self._num_class(), self.done)
+        return (tuple(self.stack), self.mode, self.lit, self.lit_pos, self.hex_left, self._num_class(), self.done, self.ws_run)
 
     # -------------------------------------------------------------- numbers: -?(0|[1-9]\d*)(\.\d+)?([eE][+-]?\d+)?
     def _num_class(self) -> str:
@@ -143,7 +146,9 @@ class JsonPrefix:
             self._value_done()
             return self.feed(ch)
         if ch in WS:
-            return True
+            self.ws_run += 1
+            return self.ws_run <= self.MAX_WS
+        self.ws_run = 0
         if m == "value":
             return (not self.done) and self._start_value(ch)
         if m == "value_or_end":

@@ -119,3 +119,25 @@ def test_graph_census_follows_the_engine():
     run_requests(sched, [torch.randint(0, spec.vocab, (40,), generator=g).tolist()], 6)       # same shapes: no new capture
     assert eng.graph_captures == before and eng.census.snapshot()["steady_state_captures"] == 0
     assert key in eng.census.shapes
+
+
+def test_json_grammar_mask_steers_the_real_sampler_and_argmax():
+    """A request with a grammar constraint goes through the masked argmax (greedy) and the masked sampler (top-k) kernels:
+    whatever the tiny model prefers, the text stays a JSON object prefix and only ends after a complete object."""
+    import json
+    from cuteafd_b200.loader.tokenizer import ByteTokenizer
+    from cuteafd_b200.serving.constraints import JsonConstraint, JsonPrefix
+    spec, eng, sched, _ = build(prefix=False)
+    tok = ByteTokenizer()
+    prompt = tok.encode("answer in json:")
+    for i, sampling in enumerate((SamplingParams(), SamplingParams(temperature=0.8, top_k=40, seed=7))):
+        outs = []
+        c = JsonConstraint(tok, spec.vocab, len(prompt), eos_id=257, top="object")
+        sched.submit(Request(f"j{i}", list(prompt), max_tokens=48, sampling=sampling, eos_id=257, constraint=c,
+                             on_token=lambda toks, done, reason, outs=outs: outs.extend(toks)))
+        sched.run_until_idle()
+        eng.check_status()
+        text = tok.decode([t for t in outs if t != 257])
+        assert all(t < 258 for t in outs) and text.lstrip().startswith("{") and JsonPrefix("object").feed_text(text), text
+        if outs and outs[-1] == 257:
+            assert isinstance(json.loads(text), dict)
