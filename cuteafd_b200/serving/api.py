@@ -16,7 +16,7 @@ import uuid
 from ..loader.tokenizer import StreamDecoder, load_tokenizer
 from ..ref.sampler import SamplingParams
 from .chat_templates import ChatTemplate, parse_completion, template_for
-from .constraints import ChoiceConstraint, constraint_from_request
+from .constraints import ChoiceConstraint, constraint_from_request, tool_choice_constraint
 from .scheduler import Request, Scheduler
 
 KEEPALIVE_S = 15.0
@@ -180,6 +180,8 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         c = constraint_from_request(body, tok, vocab_size, prompt_len, eos)
         if c is None and isinstance(body.get("guided_choice"), list):
             c = ChoiceConstraint(tok, vocab_size, prompt_len, [str(x) for x in body["guided_choice"]], eos)
+        if c is None and body.get("tools") and body.get("tool_choice") not in (None, "auto", "none"):
+            c = tool_choice_constraint(body, tmpl, tok, vocab_size, prompt_len, eos)      # "required" / a named function
         return c
 
     def auth(authorization, x_api_key=None):

@@ -411,6 +411,101 @@ class ChoiceConstraint(_TextConstraint):
         return _pack_bits(allowed)
 
 
+class ToolCallPrefix:
+    """Automaton of one forced tool call in the JSON call format:
+    `OPEN\n{"name": "` NAME `", "arguments": ` ARGUMENTS `}\nCLOSE`, where NAME is one of the offered functions and
+    ARGUMENTS follows that function's parameter schema (`SchemaPrefix`)."""
+
+    def __init__(self, tools: dict, call_open: str = "<tool_call>", call_close: str = "</tool_call>"):
+        self.tools = tools                               # name -> parameters schema
+        self.head = call_open + '\n{"name": "'
+        self.mid = '", "arguments": '
+        self.tail = "}\n" + call_close
+        self.phase, self.pos, self.name, self.args = 0, 0, "", None
+
+    def copy(self):
+        c = ToolCallPrefix.__new__(ToolCallPrefix)
+        c.tools, c.head, c.mid, c.tail = self.tools, self.head, self.mid, self.tail
+        c.phase, c.pos, c.name = self.phase, self.pos, self.name
+        c.args = self.args.copy() if self.args is not None else None
+        return c
+
+    def signature(self):
+        return (self.phase, self.pos, self.name, self.args.signature() if self.args is not None else None)
+
+    # the interface JsonConstraint.mask relies on
+    stack = ()
+
+    @property
+    def mode(self):
+        return "after" if self.phase == 5 else "call"
+
+    @property
+    def complete(self) -> bool:
+        return self.phase == 5
+
+    def _literal(self, lit: str, ch: str, nxt: int) -> bool:
+        if ch != lit[self.pos]:
+            return False
+        self.pos += 1
+        if self.pos == len(lit):
+            self.phase, self.pos = nxt, 0
+        return True
+
+    def feed(self, ch: str) -> bool:
+        if self.phase == 0:
+            return self._literal(self.head, ch, 1)
+        if self.phase == 1:                              # function name, ended by the quote
+            if ch == '"':
+                if self.name not in self.tools:
+                    return False
+                schema = self.tools[self.name] if isinstance(self.tools[self.name], dict) else {}
+                self.args = SchemaPrefix(dict(schema, type="object"))
+                self.phase, self.pos = 2, 1              # the quote is the first character of `mid`
+                return True
+            self.name += ch
+            return any(n.startswith(self.name) for n in self.tools)
+        if self.phase == 2:
+            return self._literal(self.mid, ch, 3)
+        if self.phase == 3:
+            if not self.args.feed(ch):
+                return False
+            if self.args.complete and not self.args.stack:
+                self.phase = 4
+            return True
+        if self.phase == 4:
+            return self._literal(self.tail, ch, 5)
+        return False
+
+    def feed_text(self, text: str) -> bool:
+        for ch in text:
+            if not self.feed(ch):
+                return False
+        return True
+
+
+def tool_choice_constraint(body: dict, template, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None):
+    """`tool_choice: "required"` or a named function -> a constraint that forces exactly one tool call (templates
+    whose calls are JSON inside `call_open` / `call_close`; other call formats are not forced)."""
+    choice = body.get("tool_choice")
+    tools = {}
+    for t in body.get("tools") or []:
+        f = t.get("function", t) if isinstance(t, dict) else None
+        if f and f.get("name"):
+            tools[f["name"]] = f.get("parameters") or f.get("input_schema") or {}
+    if isinstance(choice, dict):
+        name = (choice.get("function") or {}).get("name") or choice.get("name")
+        tools = {name: tools[name]} if name in tools else {}
+    elif choice not in ("required", "any"):
+        return None
+    if not tools or getattr(template, "name", "") != "chatml" or getattr(template, "xml_calls", False):
+        return None
+    c = JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, top=None)
+    c._fresh = lambda: ToolCallPrefix(tools, template.call_open, template.call_close)
+    c.state = c._fresh()
+    return c
+
+
 def constraint_from_request(body: dict, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None):
     """OpenAI `response_format` -> constraint (None when the request asks for plain text)."""
     rf = body.get("response_format") or {}

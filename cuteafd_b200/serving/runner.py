@@ -48,7 +48,8 @@ class FakeRunner:
                 if m is not None:                        # grammar mask: the fake model's pick moves to an allowed token
                     w = m.to("cpu").tolist()
                     allowed = [j for j in range(self.vocab) if (w[j >> 5] >> (j & 31)) & 1]
-                    t = allowed[t % len(allowed)] if allowed else t
+                    if allowed and t not in allowed:
+                        t = allowed[t % len(allowed)]
                 toks.append(t)
             out.append(toks)
         return out

@@ -292,3 +292,28 @@ def test_speculation_trace_and_acceptance_by_position(tmp_path, monkeypatch):
 def test_fabric_endpoint_without_gpus(client):
     r = client.get("/v1/fabric")
     assert r.status_code == 200 and "available" in r.json()
+
+
+def test_tool_choice_forces_a_call_with_schema_checked_arguments():
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}}, "required": ["city"], "additionalProperties": False}}}]
+    body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 120, "tools": tools,
+            "tool_choice": {"type": "function", "function": {"name": "get_weather"}}}
+    # a model that wants to chat is forced into the call format ...
+    c, loop = _scripted_client("Sure, happy to help!", "qwen3-235b")
+    try:
+        loop.sched.runner.vocab = 258
+        m = c.post("/v1/chat/completions", json=body).json()["choices"][0]
+        raw = (m["message"]["content"] or "") + json.dumps(m["message"].get("tool_calls", []))
+        assert "get_weather" in raw and "Sure" not in raw
+    finally:
+        loop.stop()
+    # ... and a model that already writes a valid call passes through unchanged
+    script = '<tool_call>\n{"name": "get_weather", "arguments": {"city": "Oslo"}}\n</tool_call>'
+    c, loop = _scripted_client(script, "qwen3-235b")
+    try:
+        loop.sched.runner.vocab = 258
+        m = c.post("/v1/chat/completions", json=dict(body, tool_choice="required")).json()["choices"][0]
+        assert m["finish_reason"] == "tool_calls" and json.loads(m["message"]["tool_calls"][0]["function"]["arguments"]) == {"city": "Oslo"}
+    finally:
+        loop.stop()

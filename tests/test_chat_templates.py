@@ -164,3 +164,32 @@ def test_schema_constrained_random_walk_yields_valid_documents():
     assert done >= 1
     c = constraint_from_request({"response_format": {"type": "json_schema", "json_schema": {"schema": SCHEMA}}}, tok, 258, 0, 257)
     assert c.schema is SCHEMA
+
+
+def test_forced_tool_call_grammar_names_a_tool_and_checks_its_arguments():
+    from cuteafd_b200.serving.constraints import ToolCallPrefix, tool_choice_constraint
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {"city": {"type": "string"}},
+                                                                                     "required": ["city"], "additionalProperties": False}}},
+             {"type": "function", "function": {"name": "get_time", "parameters": {"type": "object", "properties": {"tz": {"enum": ["UTC", "CET"]}},
+                                                                                  "required": ["tz"], "additionalProperties": False}}}]
+    schemas = {t["function"]["name"]: t["function"]["parameters"] for t in tools}
+    good = '<tool_call>\n{"name": "get_time", "arguments": {"tz": "CET"}}\n</tool_call>'
+    p = ToolCallPrefix(schemas)
+    assert p.feed_text(good) and p.complete
+    for bad in ('<tool_call>\n{"name": "nope"', '<tool_call>\n{"name": "get_time", "arguments": {"tz": "PST"', "Sure", good + "x",
+                '<tool_call>\n{"name": "get_weather", "arguments": {}}'):
+        assert not ToolCallPrefix(schemas).feed_text(bad), bad
+    tok, t, rng = ByteTokenizer(), template_for("qwen3"), random.Random(0)
+    for choice in ("required", {"type": "function", "function": {"name": "get_time"}}):
+        c, toks = tool_choice_constraint({"tools": tools, "tool_choice": choice}, t, tok, 258, 0, 257), []
+        for _ in range(300):
+            allowed = [i for i, a in enumerate(unpack_bits(c.mask(toks), 258)) if a]
+            closers = [a for a in allowed if a in (257, ord("}"), ord('"'))]
+            toks.append(rng.choice(closers) if closers and rng.random() < 0.7 else rng.choice(allowed))
+            if toks[-1] == 257:
+                break
+        assert toks[-1] == 257
+        calls = parse_completion(t, tok.decode(toks[:-1]))["tool_calls"]
+        assert len(calls) == 1 and calls[0]["name"] in schemas and (calls[0]["name"] != "get_time" or calls[0]["arguments"]["tz"] in ("UTC", "CET"))
+    assert tool_choice_constraint({"tools": tools, "tool_choice": "auto"}, t, tok, 258, 0, 257) is None
+    assert tool_choice_constraint({"tools": tools, "tool_choice": "required"}, template_for("glm-5"), tok, 258, 0, 257) is None
