@@ -20,6 +20,12 @@ def cmd_plan(a) -> int:
     from .loader.plan import plan
     rep = plan(a.model, world=a.gpus, layout=a.layout or a.deployment, files=a.files, pool_tokens=a.pool_tokens, gpu_gib=a.gpu_gib,
                attn_groups=a.attn_groups)
+    if a.rank >= 0 and os.path.isdir(a.model):
+        from .config import default_deployment
+        from .loader.plan import files_for_rank
+        n_exp = rep.spec.moe.n_experts if rep.spec is not None else None
+        print(json.dumps(files_for_rank(a.model, default_deployment(a.gpus, a.attn_groups), a.rank, n_exp), indent=2))
+        return 0
     if a.deployment and rep.layout is not None:
         from .loader.plan import deployment_decisions
         print(json.dumps(deployment_decisions(rep.layout, a.model), indent=2))
@@ -307,6 +313,7 @@ def main(argv=None) -> int:
     p.add_argument("--gpus", type=int, default=8); p.add_argument("--pool-tokens", type=int, default=0); p.add_argument("--gpu-gib", type=int, default=180)
     p.add_argument("--attn-groups", type=int, default=1, help="data-parallel attention groups sharing the expert ranks")
     p.add_argument("--deployment", action="store_true", help="print the typed launch decisions of the layout as JSON")
+    p.add_argument("--rank", type=int, default=-1, help="with a snapshot directory: list the files and bytes this rank of the layout reads")
     p.add_argument("--json", action="store_true"); p.set_defaults(fn=cmd_plan)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
     p = sub.add_parser("run"); p.add_argument("--config", required=True); p.add_argument("--set", action="append", default=[])

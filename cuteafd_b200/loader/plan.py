@@ -5,6 +5,8 @@ Reference: cuteafd-daemon/src/commands/plan.rs:118-298, cuteafd-loader/src/plan/
 """
 from __future__ import annotations
 
+import re
+
 import json
 from collections import Counter
 from dataclasses import dataclass, field
@@ -76,6 +78,36 @@ def deployment_decisions(layout: "placement.Layout", model: str, port: int = 295
                                         f"--master-port {port} bench.py --gpus {dep.world} --attn-groups {dep.attn_groups}") if dep.world > 1
                                        else "python bench.py --gpus 1"},
             "env": {"NCCL_NVLS_ENABLE": "0"} if dep.world > 1 else {}}
+
+
+_EXPERT_RE = re.compile(r"\.experts\.(\d+)\.")
+
+
+def files_for_rank(snapshot: str | Path, deployment, rank: int, n_experts: int | None = None) -> dict:
+    """Which safetensors files (and how many bytes of them) one rank of a deployment reads: attention ranks take every
+    tensor that is not a routed expert, expert ranks the experts of their range.  This is what a role-sliced copy of a
+    checkpoint contains (reference: `cuteafd plan --files --role`, docs/sliced-checkpoints.md)."""
+    cat = catalog(Path(snapshot))
+    if n_experts is None:                                  # no config at hand: the highest expert index named by a tensor
+        n_experts = 1 + max((int(m.group(1)) for m in map(_EXPERT_RE.search, cat) if m), default=-1)
+    lo = hi = -1
+    if rank in deployment.expert_ranks:
+        ep, i = max(1, deployment.ep), list(deployment.expert_ranks).index(rank)
+        lo, hi = (i * n_experts) // ep, ((i + 1) * n_experts) // ep      # the ranges the expert ranks use at run time
+    files: dict = {}
+    for name, t in cat.items():
+        m = _EXPERT_RE.search(name)
+        if m:
+            take = lo <= int(m.group(1)) < hi
+        else:
+            take = rank in deployment.attn_ranks
+        if take:
+            f = files.setdefault(Path(t.file).name, {"tensors": 0, "bytes": 0})
+            f["tensors"] += 1
+            f["bytes"] += t.nbytes
+    role = "both" if rank in deployment.attn_ranks and rank in deployment.expert_ranks else ("attention" if rank in deployment.attn_ranks else "experts")
+    return {"rank": rank, "role": role, "experts": [lo, hi] if lo >= 0 else None, "files": files,
+            "bytes": sum(f["bytes"] for f in files.values())}
 
 
 def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = False, pool_tokens: int = 0, gpu_gib: int = 180,

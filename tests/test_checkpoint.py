@@ -70,3 +70,25 @@ def test_fp8_block_dense_snapshot(tmp_path):
     q, s = quant.fp8_block_quantize(masters["layers"][1]["wo"])
     assert torch.equal(got["layers"][1]["wo"], quant.fp8_block_dequantize(q, s))
     assert torch.equal(got["layers"][0]["router"], bf16r(masters["layers"][0]["router"]))
+
+
+def test_plan_lists_the_files_each_rank_reads(tmp_path, capsys):
+    """Role-sliced view of a snapshot: attention ranks read everything but routed experts, expert ranks their expert range."""
+    from cuteafd_b200 import cli
+    from cuteafd_b200.config import default_deployment, tiny_spec
+    from cuteafd_b200.loader.checkpoint import export_snapshot
+    from cuteafd_b200.loader.plan import files_for_rank
+    from cuteafd_b200.ref.model import init_weights
+    spec = tiny_spec()
+    export_snapshot(spec, init_weights(spec, 0), tmp_path, shard_layers=1)
+    dep = default_deployment(4)
+    per_rank = [files_for_rank(tmp_path, dep, r, spec.moe.n_experts) for r in range(4)]
+    attn = [p for p in per_rank if p["role"] == "attention"]
+    exp = [p for p in per_rank if p["role"] == "experts"]
+    assert attn and exp and all(p["experts"] is None for p in attn)
+    ranges = sorted(tuple(p["experts"]) for p in exp)
+    assert ranges[0][0] == 0 and ranges[-1][1] == spec.moe.n_experts and all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+    total = sum(t.nbytes for t in __import__("cuteafd_b200.loader.safetensors_io", fromlist=["catalog"]).catalog(tmp_path).values())
+    assert attn[0]["bytes"] + sum(p["bytes"] for p in exp) == total            # every tensor has exactly one kind of reader
+    assert cli.main(["plan", str(tmp_path), "--gpus", "4", "--rank", "3"]) == 0
+    assert '"role": "experts"' in capsys.readouterr().out
