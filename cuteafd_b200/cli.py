@@ -300,6 +300,21 @@ def cmd_run(a) -> int:
     return main(argv)
 
 
+def cmd_quantize(a) -> int:
+    """`quantize SRC DST --dense FMT --experts FMT`: resumable re-quantisation of a snapshot (run the same command again
+    after an interruption)."""
+    from .config import from_hf_config
+    from .loader.quantize import quantize_snapshot
+    spec = from_hf_config(a.src)
+    try:
+        r = quantize_snapshot(a.src, a.dst, spec, dense=a.dense, experts=a.experts, restart=a.restart, log=lambda m: print(m, flush=True))
+    except ValueError as e:
+        print(f"quantize: {e}", file=sys.stderr)
+        return 2
+    print(json.dumps({"written": len(r["written"]), "skipped": len(r["skipped"]), "published": r["published"]}))
+    return 0
+
+
 def cmd_bench(a) -> int:
     import subprocess
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -349,6 +364,10 @@ def main(argv=None) -> int:
     p = sub.add_parser("gateway"); p.add_argument("--listen", default="127.0.0.1:8020"); p.add_argument("--model-id", default="cuteafd-b200")
     p.add_argument("--official-model-names", default=""); p.add_argument("--official-model-names-file", default="")
     p.add_argument("--gateway-allow-origin", default=""); p.add_argument("--chat-template", default=""); p.set_defaults(fn=cmd_gateway)
+    p = sub.add_parser("quantize"); p.add_argument("src"); p.add_argument("dst")
+    p.add_argument("--dense", default="nvfp4", choices=["bf16", "fp8_block128", "nvfp4", "mxfp4"])
+    p.add_argument("--experts", default="mxfp4", choices=["bf16", "fp8_block128", "nvfp4", "mxfp4"])
+    p.add_argument("--restart", action="store_true", help="discard a run store that belongs to another run"); p.set_defaults(fn=cmd_quantize)
     p = sub.add_parser("usage"); p.add_argument("action", choices=["clear", "clear-log", "export-csv", "demo"])
     p.add_argument("--dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage")); p.add_argument("--range", default="7d", choices=["1h", "6h", "24h", "7d"])
     p.add_argument("--out", default=""); p.add_argument("--listen", default="127.0.0.1:8010"); p.set_defaults(fn=cmd_usage)
