@@ -193,3 +193,17 @@ def test_forced_tool_call_grammar_names_a_tool_and_checks_its_arguments():
         assert len(calls) == 1 and calls[0]["name"] in schemas and (calls[0]["name"] != "get_time" or calls[0]["arguments"]["tz"] in ("UTC", "CET"))
     assert tool_choice_constraint({"tools": tools, "tool_choice": "auto"}, t, tok, 258, 0, 257) is None
     assert tool_choice_constraint({"tools": tools, "tool_choice": "required"}, template_for("glm-5"), tok, 258, 0, 257) is None
+
+
+def test_template_round_trip_of_assistant_tool_calls():
+    """What a template writes for an assistant turn with tool calls parses back to the same calls (every family)."""
+    call = {"id": "c1", "type": "function", "function": {"name": "get_weather", "arguments": json.dumps({"city": "Oslo", "days": 3, "units": ["C", "F"]})}}
+    msgs = [{"role": "user", "content": "q"}, {"role": "assistant", "content": "Looking it up.", "tool_calls": [call]}, {"role": "user", "content": "next"}]
+    for model, start, end in (("qwen3-235b", "<|im_start|>assistant\n", "<|im_end|>"), ("qwen3-coder", "<|im_start|>assistant\n", "<|im_end|>"),
+                              ("deepseek-v3", "<｜Assistant｜>", "<｜end▁of▁sentence｜>"), ("glm-5", "<|assistant|>\n", "<|user|>")):
+        t = template_for(model)
+        text = t.render(msgs, tools=TOOLS)
+        seg = text.split(start, 1)[1].split(end, 1)[0]
+        got = parse_completion(t, seg)
+        assert [(c["name"], c["arguments"]) for c in got["tool_calls"]] == [("get_weather", {"city": "Oslo", "days": 3, "units": ["C", "F"]})], model
+        assert got["content"].strip() == "Looking it up.", model

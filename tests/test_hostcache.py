@@ -69,3 +69,48 @@ def test_prefix_cache_writes_evicted_chains_behind_and_restores_them():
     b = a[:128] + _toks(2, 2)
     adm3 = pc.admit(b, reserve_new=1)
     assert adm3.hit_tokens == 128
+
+
+def test_prefix_and_host_tiers_keep_their_books_under_random_traffic():
+    """Random admissions, captures, releases and evictions over shared prefixes: page references never leak, restored
+    content is always the content that was stored, and both tiers stay within their budgets."""
+    import random
+    from cuteafd_b200.engine.kv import OutOfPages, PagePool
+    from cuteafd_b200.serving.prefix import PrefixCache
+    rng = random.Random(3)
+    eng = StubCopyEngine(page_bytes=1024)
+    hc = HostCache(eng, n_slabs=40, page_bytes=1024, min_tokens=64)
+    pool = PagePool(48)
+    pc = PrefixCache(pool, max_entries=6, min_tokens=64, max_cached_pages=20, host=hc)
+    prefixes = [_toks(10 + i, rng.randrange(1, 5)) for i in range(8)]
+    content: dict = {}                                          # (prefix id, page index) written by the "prefill"
+    live = []
+    for step in range(600):
+        if live and rng.random() < 0.45:
+            adm, toks = live.pop(rng.randrange(len(live)))
+            pc.release(adm.seq)
+            continue
+        pid = rng.randrange(len(prefixes))
+        toks = prefixes[pid] + [rng.randrange(5)] * rng.randrange(1, 40)
+        try:
+            adm = pc.admit(toks, reserve_new=1)
+        except OutOfPages:
+            continue
+        n_full = len(prefixes[pid]) // 64
+        for i in range(n_full):
+            page = adm.seq.pages[i]
+            if i * 64 < adm.hit_tokens:
+                assert eng.device.get(page) == (pid, i), "a restored or shared page holds someone else's content"
+            else:
+                eng.device[page] = (pid, i)                     # computed by this request
+        adm.seq.length = len(toks)
+        pc.capture(toks, adm.seq)
+        live.append((adm, toks))
+        if rng.random() < 0.1:
+            pc.evict(rng.randrange(1, 8))
+        assert pc.n_nodes <= 20 + 8 and len(hc.pages) + len(hc.free) == 40
+    for adm, _ in live:
+        pc.release(adm.seq)
+    pc.evict(10 ** 6)
+    assert pool.n_free == 47 and all(r == 0 for r in pool.refs[1:])          # nothing leaked (page 0 is reserved)
+    assert hc.stats["restored_pages"] > 0 and pc.stats["host_hits"] > 0
