@@ -118,7 +118,8 @@ def build_serving(a):
         from .serving.mtp_drafter import MtpDrafter
         drafter = MtpDrafter(runner)                           # the model's own MTP module (needs MTP weights)
     sched = Scheduler(runner, pool, max_seqs=a.max_sequences, prefill_chunk=a.prefill_batch_tokens, decode_share=a.decode_share,
-                      prefix=prefix, drafter=drafter, max_draft=a.draft_limit)
+                      prefix=prefix, drafter=drafter, max_draft=a.draft_limit, queue_limit=getattr(a, "http_queue", 64),
+                      queue_wait_s=getattr(a, "queue_wait_s", 0) or None)
     return spec, sched
 
 
@@ -346,6 +347,8 @@ def main(argv=None) -> int:
     p.add_argument("--host-cache-min-tokens", type=int, default=512, help="shorter prefixes are not written to the host tier")
     p.add_argument("--usage", default="off", choices=["on", "off"]); p.add_argument("--enable-bench", action="store_true")
     p.add_argument("--usage-dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage"))
+    p.add_argument("--http-queue", type=int, default=64, help="requests that may wait for a lane; more are answered 429")
+    p.add_argument("--queue-wait-s", type=float, default=0.0, help="admission wait budget in seconds (0 = wait as long as it takes)")
     p.add_argument("--gateway", default="on", choices=["on", "off"]); p.add_argument("--official-model-names", default="")
     p.add_argument("--official-model-names-file", default=""); p.add_argument("--gateway-allow-origin", default="")
     p.add_argument("--chat-template", default="", help="chat template family (chatml / qwen3-coder / deepseek / glm / plain); default: by model name")

@@ -344,8 +344,8 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
 
         if not body.get("stream"):
             ids, reason = await collect(events)
-            if reason and reason.startswith(("error", "unavailable")):
-                raise HTTPException(503 if "unavailable" in reason or "transport" in reason else 500, reason)
+            if reason and reason.startswith(("error", "unavailable", "busy", "queue full")):
+                raise HTTPException(429 if reason.startswith(("busy", "queue full")) else (503 if "unavailable" in reason or "transport" in reason else 500), reason)
             text, stopped = _cut_at_stop(tok.decode(ids), stops)
             parsed = parse_completion(tmpl, text, thinking)
             account(rid, key, t0, None, len(prompt_ids), len(ids), reason)
@@ -509,7 +509,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
             return resp, parsed
         if not body.get("stream"):
             ids, reason = await collect(events)
-            if reason and reason.startswith(("error", "unavailable")):
+            if reason and reason.startswith(("error", "unavailable", "busy", "queue full")):
                 raise HTTPException(503, reason)
             return finish(ids, reason)[0]
 
@@ -607,7 +607,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                                                             ("end_turn" if stopped or reason == "stop" else "max_tokens"))
         if not body.get("stream"):
             ids, reason = await collect(events)
-            if reason and reason.startswith(("error", "unavailable")):
+            if reason and reason.startswith(("error", "unavailable", "busy", "queue full")):
                 raise HTTPException(503, reason)
             text, stopped = _cut_at_stop(tok.decode(ids), stops)
             parsed = parse_completion(tmpl, text, thinking)

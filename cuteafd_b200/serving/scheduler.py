@@ -98,13 +98,14 @@ class NgramDrafter:
 class Scheduler:
     def __init__(self, runner: ModelRunner, pool: PagePool, *, max_seqs: int = 16, prefill_chunk: int = 4096, decode_share: float = 0.2,
                  prefix: PrefixCache | None = None, drafter: Drafter | None = None, policy: DraftPolicy | None = None,
-                 max_draft: int = 3, queue_limit: int = 64):
+                 max_draft: int = 3, queue_limit: int = 64, queue_wait_s: float | None = None):
         self.runner, self.pool = runner, pool
         self.max_seqs, self.prefill_chunk, self.decode_share = max_seqs, prefill_chunk, decode_share
         self.prefix = prefix
         self.drafter, self.policy, self.max_draft = drafter, policy or SimpleDraftPolicy(max_draft), max_draft
         self.queue: deque[Request] = deque()
         self.queue_limit = queue_limit
+        self.queue_wait_s = queue_wait_s                      # admission wait budget: a request queued longer than this is answered "busy"
         self.active: list[SeqState] = []
         self.fatal: str | None = None
         self._prefill_debt = 0.0
@@ -128,6 +129,7 @@ class Scheduler:
             self.stats["rejected"] += 1
             self._finish_unadmitted(req, "queue full")
             return False
+        req.queued_at = time.monotonic()
         self.queue.append(req)
         self.stats["requests"] += 1
         return True
@@ -154,6 +156,11 @@ class Scheduler:
 
     # ------------------------------------------------------------------ admission
     def _admit(self):
+        if self.queue_wait_s is not None:
+            now = time.monotonic()
+            while self.queue and now - getattr(self.queue[0], "queued_at", now) > self.queue_wait_s:
+                self.stats["rejected"] += 1
+                self._finish_unadmitted(self.queue.popleft(), "busy: admission wait budget exceeded")
         while self.queue and len(self.active) < self.max_seqs:
             req = self.queue[0]
             if not req.prompt:

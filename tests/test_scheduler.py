@@ -163,3 +163,20 @@ def test_resource_priced_policy_prefers_width_when_acceptance_is_high():
         q.observe("r", 4, 0)
     assert q.width("r", 64) == 0
     assert p.width("r", 1) == 0
+
+
+def test_admission_wait_budget_answers_busy_instead_of_queueing_forever():
+    import time as _t
+    from cuteafd_b200.engine.kv import PagePool
+    from cuteafd_b200.serving.runner import FakeRunner
+    from cuteafd_b200.serving.scheduler import Request, Scheduler
+    sched = Scheduler(FakeRunner(vocab=50), PagePool(64), max_seqs=1, queue_wait_s=0.05)
+    got = {}
+    for name, n in (("a", 400), ("b", 4)):
+        sched.submit(Request(name, [1, 2, 3], max_tokens=n, on_token=lambda t, d, r, name=name: got.setdefault(name, []).append((len(t), d, r))))
+    sched.step()                                   # "a" is admitted, "b" waits for a lane
+    _t.sleep(0.08)
+    sched.step()
+    assert got["b"][-1][1] and got["b"][-1][2].startswith("busy") and sched.stats["rejected"] == 1
+    sched.run_until_idle()
+    assert got["a"][-1][2] == "length"
