@@ -82,7 +82,7 @@ def cmd_fabric(a) -> int:
 def build_serving(a):
     """Engine + scheduler + prefix cache for a model name or snapshot (single GPU)."""
     import torch
-    from .config import from_hf_config, spec_by_name, NAMED_SPECS, QuantSpec
+    from .config import spec_from_snapshot, spec_by_name, NAMED_SPECS, QuantSpec
     from .engine.engine import Engine
     from .engine.kv import PagePool
     from .models.weights import DeviceWeights
@@ -90,7 +90,7 @@ def build_serving(a):
     from .serving.prefix import PrefixCache
     from .serving.runner import EngineRunner, attach_pool
     from .serving.scheduler import NgramDrafter, Scheduler
-    spec = spec_by_name(a.model) if a.model in NAMED_SPECS else from_hf_config(a.model)
+    spec = spec_by_name(a.model) if a.model in NAMED_SPECS else spec_from_snapshot(a.model)
     dev = torch.device("cuda", a.device)
     layers = getattr(a, "layers", 0)
     if layers:
@@ -304,9 +304,9 @@ def cmd_run(a) -> int:
 def cmd_quantize(a) -> int:
     """`quantize SRC DST --dense FMT --experts FMT`: resumable re-quantisation of a snapshot (run the same command again
     after an interruption)."""
-    from .config import from_hf_config
+    from .config import spec_from_snapshot
     from .loader.quantize import quantize_snapshot
-    spec = from_hf_config(a.src)
+    spec = spec_from_snapshot(a.src)
     try:
         r = quantize_snapshot(a.src, a.dst, spec, dense=a.dense, experts=a.experts, restart=a.restart, log=lambda m: print(m, flush=True))
     except ValueError as e:

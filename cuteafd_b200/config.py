@@ -276,6 +276,27 @@ def from_hf_config(cfg: dict | str | Path) -> ModelSpec:
                      max_context=cfg.get("max_position_embeddings", 1 << 20))
 
 
+SPEC_FILE = "cuteafd_spec.json"
+
+
+def spec_to_json(spec: ModelSpec) -> dict:
+    """Lossless dump of a model spec (written next to synthetic snapshots, whose shapes have no Hugging Face architecture)."""
+    return dataclasses.asdict(spec)
+
+
+def spec_from_json(d: dict) -> ModelSpec:
+    d = dict(d)
+    return ModelSpec(attn=AttentionSpec(**d.pop("attn")), moe=MoESpec(**d.pop("moe")), quant=QuantSpec(**d.pop("quant")), **d)
+
+
+def spec_from_snapshot(path: str | Path) -> ModelSpec:
+    """Model spec of a snapshot directory: the native spec file when the snapshot has one, else its `config.json`."""
+    p = Path(path)
+    if (p / SPEC_FILE).exists():
+        return spec_from_json(json.loads((p / SPEC_FILE).read_text()))
+    return from_hf_config(p)
+
+
 @dataclass(frozen=True)
 class Deployment:
     """How ranks of one node are used (reference: SparkWorld / placement decisions).

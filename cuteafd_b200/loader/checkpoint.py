@@ -136,6 +136,11 @@ def export_snapshot(spec: ModelSpec, masters: dict, path: str | Path, *, dense: 
     n = len(shards)
     for k, (tensors, dtypes) in sorted(shards.items()):
         write_file(path / f"model-{k + 1:05d}-of-{n:05d}.safetensors", tensors, dtypes)
+    import dataclasses
+    import json
+    from ..config import SPEC_FILE, QuantSpec, spec_to_json
+    stored = spec.replace(quant=dataclasses.replace(spec.quant, dense=dense, experts=experts) if isinstance(spec.quant, QuantSpec) else spec.quant)
+    (path / SPEC_FILE).write_text(json.dumps(spec_to_json(stored), indent=1))
     return path
 
 

@@ -12,7 +12,7 @@ from collections import Counter
 from dataclasses import dataclass, field
 from pathlib import Path
 
-from ..config import ModelSpec, from_hf_config, spec_by_name, NAMED_SPECS
+from ..config import ModelSpec, spec_from_snapshot, spec_by_name, NAMED_SPECS
 from . import formats, placement
 from .safetensors_io import catalog
 
@@ -118,7 +118,7 @@ def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = Fals
     spec = family = None
     if p.is_dir():
         try:
-            spec = from_hf_config(p)
+            spec = spec_from_snapshot(p)
             family = spec.family
         except Exception as e:
             problems.append(f"config.json: {e}")

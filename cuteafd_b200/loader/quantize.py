@@ -95,6 +95,12 @@ def _publish(dst: Path, src: Path, run: dict):
     for name in SIDE_FILES:
         if (src / name).exists():
             shutil.copyfile(src / name, dst / name)
+    from ..config import SPEC_FILE, spec_from_json, spec_to_json
+    if (src / SPEC_FILE).exists():                         # synthetic snapshots carry their spec; record the new formats in it
+        import dataclasses
+        spec = spec_from_json(json.loads((src / SPEC_FILE).read_text()))
+        spec = spec.replace(quant=dataclasses.replace(spec.quant, dense=run["dense"], experts=run["experts"]))
+        (dst / SPEC_FILE).write_text(json.dumps(spec_to_json(spec), indent=1))
 
 
 def quantize_snapshot(src: str | Path, dst: str | Path, spec: ModelSpec, *, dense: str = "nvfp4", experts: str = "mxfp4",

@@ -49,3 +49,19 @@ def test_run_store_of_another_run_is_refused_and_a_lost_shard_is_redone(tmp_path
     assert r["written"] == ["layer-0000"]
     r = quantize_snapshot(tmp_path / "src", tmp_path / "q", spec, dense="nvfp4", experts="nvfp4", restart=True)
     assert len(r["written"]) == 3 and json.loads((tmp_path / "q" / RUN_FILE).read_text())["dense"] == "nvfp4"
+
+
+def test_quantize_and_plan_commands_work_on_a_synthetic_snapshot(tmp_path, capsys):
+    """Synthetic snapshots carry their spec, so the commands that take a snapshot directory work on them."""
+    from cuteafd_b200 import cli
+    from cuteafd_b200.config import spec_from_snapshot
+    spec = tiny_spec()
+    export_snapshot(spec, init_weights(spec, 2), tmp_path / "src")
+    assert spec_from_snapshot(tmp_path / "src") == spec
+    assert cli.main(["quantize", str(tmp_path / "src"), str(tmp_path / "q"), "--dense", "bf16", "--experts", "mxfp4"]) == 0
+    assert '"published": true' in capsys.readouterr().out
+    q = spec_from_snapshot(tmp_path / "q")
+    assert q.quant.experts == "mxfp4" and q.quant.dense == "bf16" and q.replace(quant=spec.quant) == spec
+    assert cli.main(["plan", str(tmp_path / "q"), "--gpus", "1", "--layout"]) == 0
+    out = capsys.readouterr().out
+    assert "mxfp4" in out and "supported: True" in out
