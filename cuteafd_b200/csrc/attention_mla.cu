@@ -127,8 +127,8 @@ __global__ void __launch_bounds__(192, 1) mla_attn_kernel(const __grid_constant_
   volatile int* abortp = &abort_flag;
   const uint32_t S_COL = 0, O_COL = 64, QT_COL = 320;
   // ... and chunks 0..5 go to tensor memory (row = lane, two elements per 32-bit column), where the score MMAs
-  // read them as the A operand without touching shared memory: with 32-key tiles the A operand is what the
-  // score MMAs wait for, and Q is the same for every tile.
+  // read them as the A operand without touching shared memory; that leaves room there for two 64-key stages, and Q is
+  // the same for every tile.
   if (warp >= 2) {
     const int r = (warp & 3) * 32 + lane;
     const uint32_t dst = tmem + ((uint32_t)((warp & 3) * 32) << 16) + QT_COL;
@@ -391,7 +391,7 @@ extern "C" int cuteafd_mla_attention(const void* q_lat, const void* q_rope, cons
   return CA_OK;
 }
 
-// Descriptor of one layer's latent cache [slots, 576] bf16: box {64 elements, 32 slots}.
+// Descriptor of one layer's latent cache [slots, 576] bf16: box {64 elements, 64 slots} (one page).
 extern "C" int cuteafd_tmap_encode_latent(void* out128, const void* base, uint64_t n_slots) {
   CUtensorMap m;
   int rc = ca_encode_tmap_3d(&m, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, DQK, n_slots, 1, DQK * 2, (uint64_t)DQK * 2 * n_slots, 64, MKEYS, 1,
