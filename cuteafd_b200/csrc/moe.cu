@@ -28,14 +28,26 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
   const int n = p.T * p.k;
   for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = __ldcg(p.idx + i) - p.e_lo; if (e >= 0 && e < El) atomicAdd(&cnt[e], 1); }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int off = 0, nt = 0;
-    for (int e = 0; e < El; ++e) {
-      cur[e] = off; p.offsets[e] = off; p.counts[e] = cnt[e];
-      for (int r = 0; r < cnt[e]; r += p.tn) { if (nt < p.max_tiles) p.tiles[nt] = make_int4(e, off + r, min(p.tn, cnt[e] - r), 0); ++nt; }
-      off += cnt[e];
+  // Row offsets and the tile table in expert order: warp 0 scans, each lane owning a run of consecutive experts
+  // (a single thread walking all experts with its global stores was several microseconds of every MoE layer).
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x, per = (El + 31) / 32, e0 = min(El, lane * per), e1 = min(El, e0 + per);
+    int rows = 0, tiles = 0;
+    for (int e = e0; e < e1; ++e) { rows += cnt[e]; tiles += (cnt[e] + p.tn - 1) / p.tn; }
+    int rsum = rows, tsum = tiles;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, rsum, o), b = __shfl_up_sync(0xffffffffu, tsum, o);
+      if (lane >= o) { rsum += a; tsum += b; }
     }
-    *p.n_tiles = min(nt, p.max_tiles); *p.n_rows = off;
+    int off = rsum - rows, nt = tsum - tiles;                 // exclusive prefix of this lane's run
+    for (int e = e0; e < e1; ++e) {
+      const int c = cnt[e];
+      cur[e] = off; p.offsets[e] = off; p.counts[e] = c;
+      for (int r = 0; r < c; r += p.tn) { if (nt < p.max_tiles) p.tiles[nt] = make_int4(e, off + r, min(p.tn, c - r), 0); ++nt; }
+      off += c;
+    }
+    if (lane == 31) { *p.n_tiles = min(tsum, p.max_tiles); *p.n_rows = rsum; }
   }
   __syncthreads();
   // Stable placement (token order inside each expert) so packed layouts are reproducible: each route counts the
