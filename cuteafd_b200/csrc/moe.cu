@@ -144,26 +144,23 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     for (int e = tid; e < E; e += blockDim.x) if (gscore[e / per] != 0.f) choice[e] = -INFINITY;
     __syncthreads();
   }
-  // k rounds of block-wide argmax (value desc, index asc)
-  for (int r = 0; r < k; ++r) {
-    float bv = -INFINITY; int bi = 0x7fffffff;
-    for (int e = tid; e < E; e += blockDim.x) { const float v = choice[e]; if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; } }
+  // k rounds of argmax (value desc, index asc) by warp 0 alone: the scores are in shared memory, so the rounds need
+  // no block barrier (two per round cost more than the scan itself at 128 experts)
+  if (tid < 32) {
+    for (int r = 0; r < k; ++r) {
+      float bv = -INFINITY; int bi = 0x7fffffff;
+      for (int e = tid; e < E; e += 32) { const float v = choice[e]; if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; } }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    __shared__ float wv[32]; __shared__ int wi[32];
-    if ((tid & 31) == 0) { wv[tid >> 5] = bv; wi[tid >> 5] = bi; }
-    __syncthreads();
-    if (tid == 0) {
-      const int nw = (blockDim.x + 31) >> 5;
-      for (int j = 1; j < nw; ++j) if (wv[j] > bv || (wv[j] == bv && wi[j] < bi)) { bv = wv[j]; bi = wi[j]; }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
       if (bi >= E) bi = 0;
-      sel[r] = bi; selw[r] = score[bi]; choice[bi] = -INFINITY;
+      if (tid == 0) { sel[r] = bi; selw[r] = score[bi]; choice[bi] = -INFINITY; }
+      __syncwarp();
     }
-    __syncthreads();
   }
+  __syncthreads();
   if (tid == 0) {
     float s = 0.f;
     for (int r = 0; r < k; ++r) s += selw[r];
