@@ -182,6 +182,57 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   }
 }
 
+// Router logits for decode-sized batches: logits[t][e] = x[t] . w[e] in fp32, one block per expert.  The tensor-core
+// path needs an 8-CTA cluster split-K to spread this 1 MB weight and still spends most of its ~14 us in launch and
+// cluster overheads; here 128 blocks read 8 KB of weights each and the token rows from L2.
+#define RL_TOK 16
+__global__ void __launch_bounds__(128) router_logits_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits,
+                                                             int T, int E, int H) {
+  pdl_launch(); pdl_wait();
+  __shared__ float red[RL_TOK][4];
+  const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bf16* wr = w + (size_t)e * H;
+  for (int t0 = 0; t0 < T; t0 += RL_TOK) {
+    float acc[RL_TOK];
+#pragma unroll
+    for (int j = 0; j < RL_TOK; ++j) acc[j] = 0.f;
+    for (int c = tid; c < H / 8; c += 128) {
+      const uint4 wv = *(const uint4*)(wr + c * 8);
+      const bf162* wp = (const bf162*)&wv;
+      float wf[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(wp[q]); wf[2 * q] = f.x; wf[2 * q + 1] = f.y; }
+#pragma unroll
+      for (int j = 0; j < RL_TOK; ++j) {
+        if (t0 + j < T) {
+          const uint4 xv = *(const uint4*)(x + (size_t)(t0 + j) * H + c * 8);
+          const bf162* xp = (const bf162*)&xv;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(xp[q]); acc[j] = fmaf(f.x, wf[2 * q], acc[j]); acc[j] = fmaf(f.y, wf[2 * q + 1], acc[j]); }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < RL_TOK; ++j) {
+      float v = acc[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) red[j][warp] = v;
+    }
+    __syncthreads();
+    if (tid < RL_TOK && t0 + tid < T) logits[(size_t)(t0 + tid) * E + e] = red[tid][0] + red[tid][1] + red[tid][2] + red[tid][3];
+    __syncthreads();
+  }
+}
+
+extern "C" int cuteafd_router_logits(const void* x, const void* w, float* logits, int T, int E, int H, cudaStream_t s) {
+  CA_REQUIRE(H % 8 == 0 && E >= 1, "router_logits: hidden size must be a multiple of 8");
+  if (T <= 0) return CA_OK;
+  CA_LAUNCH_PDL(router_logits_kernel, E, 128, 0, s, (const bf16*)x, (const bf16*)w, logits, T, E, H);
+  CA_CHECK_LAUNCH("router_logits");
+  return CA_OK;
+}
+
 extern "C" int cuteafd_router_select(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k,
                                      int scoring, int normalize, float route_scale, int n_group, int topk_group, cudaStream_t s) {
   CA_REQUIRE(E >= k && E <= 512 && k >= 1 && k <= 16, "router_select: need k <= 16 and E <= 512 (E=%d k=%d)", E, k);

@@ -304,7 +304,11 @@ class Engine:
         if lw.router is None:
             self._ffn(lw, L, T, L.x, L.x)
             return
-        self._dense(lw.router, L.xn_act, L.router_logits, T)
+        if T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1":
+            ops.router_logits(L.xn, lw.router, L.router_logits, T)         # decode / verify: SIMT dot products, one block per expert
+            self.launches_per_step += 1
+        else:
+            self._dense(lw.router, L.xn_act, L.router_logits, T)
         e_lo, e_hi = self.expert_range
         if T * m.top_k <= 1024 and e_hi - e_lo <= 512:     # decode / verify steps: select and pack in one launch
             ops.router_select_pack(L.router_logits, lw.router_bias, L.idx, L.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,

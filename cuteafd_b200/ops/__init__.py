@@ -379,6 +379,14 @@ def silu_mul(g, u, out, limit: float = 0.0):
     return out
 
 
+def router_logits(x, w: "TcWeight", logits, T: int):
+    """fp32 router logits of `T` token rows (bf16 `x` [rows, H]) against a bf16 router weight [E, H]: the SIMT kernel for
+    decode-sized batches (the tensor-core GEMM is launch- and cluster-overhead bound at this size)."""
+    assert w.kind == KIND_BF16 and w.G == 1 and x.dtype == torch.bfloat16 and x.stride(0) == w.K and logits.stride(0) == w.N
+    call("cuteafd_router_logits", ptr(x), ptr(w.data), ptr(logits), T, w.N, w.K, stream())
+    return logits
+
+
 # ------------------------------------------------------------------ MoE control
 def router_select(logits, bias, idx, wts, T, k, scoring, normalize, route_scale, n_group=1, topk_group=1):
     _chk(logits, torch.float32, "logits")

@@ -38,6 +38,7 @@ _PROTOS = {
     "cuteafd_act_quant_fp8_ue8m0": [P, P, P, I, I, P],
     "cuteafd_kv_pages_copy": [P, L, I, I, P, I, P, L, I, P],
     "cuteafd_attn_merge": [P, P, P, P, I, I, I, P],
+    "cuteafd_router_logits": [P, P, P, I, I, I, P],
     "cuteafd_attn_partials_only": [],
     "cuteafd_l2_prefetch": [P, L, P],
     "cuteafd_silu_mul": [P, P, P, L, F, P],

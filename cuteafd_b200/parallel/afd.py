@@ -173,7 +173,12 @@ class AttnRankEngine(Engine):
     def _moe_layer_at(self, li, lw, L, T):
         spec, m, dep = self.full_spec, self.full_spec.moe, self.dep
         ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, spec.rms_eps, rows=T)
-        self._dense(lw.router, L.xn_act, self.router_logits, T)
+        if T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K \
+                and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1":
+            ops.router_logits(L.xn, lw.router, self.router_logits, T)      # same kernel as the single-GPU engine (token-exact layouts)
+            self.launches_per_step += 1
+        else:
+            self._dense(lw.router, L.xn_act, self.router_logits, T)
         self.launches_per_step += 2
         shared = None
         if self.comm == "nccl":

@@ -630,3 +630,17 @@ def test_context_split_attention_matches_attention_over_the_whole_context():
         L = k.shape[0]
         ref = rops.attention(bf16r(q[i:i + 1]), bf16r(k), bf16r(v), torch.arange(L - 1, L), torch.arange(L))
         assert torch.allclose(got[i:i + 1], ref, atol=3e-2, rtol=3e-2), f"seq {i}: max err {(got[i:i + 1] - ref).abs().max()}"
+
+
+@pytest.mark.parametrize("T,E,H", [(16, 128, 4096), (1, 16, 256), (37, 256, 7168)])
+def test_router_logits_simt_matches_fp32_matmul(T, E, H):
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T + 3, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, H, generator=g) * 0.05)
+    W = TcWeight.from_master(w, "bf16", DEV)
+    logits = torch.full((T + 3, E), 7.0, dtype=torch.float32, device=DEV)
+    ops.router_logits(x.to(DEV), W, logits, T)
+    torch.cuda.synchronize()
+    ref = x[:T].float() @ w.to(torch.bfloat16).float().t()
+    assert torch.allclose(logits[:T].cpu(), ref, atol=2e-3, rtol=2e-3)
+    assert bool((logits[T:] == 7.0).all())                     # rows beyond T are not touched
