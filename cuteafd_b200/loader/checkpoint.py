@@ -71,8 +71,9 @@ def _is_expert(key: str) -> bool:
 
 
 # ------------------------------------------------------------------ export (synthetic checkpoints)
-def _emit(out: dict, dtypes: dict, stem: str, w: torch.Tensor, fmt: str):
-    """One linear [N, K] in format `fmt` under HF-style member names."""
+def _emit(out: dict, dtypes: dict, stem: str, w: torch.Tensor, fmt: str, input_amax: float | None = None):
+    """One linear [N, K] in format `fmt` under HF-style member names.  `input_amax` (NVFP4) adds the calibrated
+    `input_scale` = amax / (448 * 6) a ModelOpt export carries."""
     if fmt == "bf16":
         out[f"{stem}.weight"] = w.to(torch.bfloat16)
     elif fmt == "fp8_block128":
@@ -84,6 +85,8 @@ def _emit(out: dict, dtypes: dict, stem: str, w: torch.Tensor, fmt: str):
         out[f"{stem}.weight"], out[f"{stem}.weight_scale"] = p, s
         out[f"{stem}.weight_scale_2"] = torch.tensor(float(gs), dtype=torch.float32).reshape(())
         dtypes[f"{stem}.weight_scale"] = "F8_E4M3"
+        if input_amax is not None:
+            out[f"{stem}.input_scale"] = torch.tensor(float(input_amax) / (448.0 * 6.0), dtype=torch.float32).reshape(())
     elif fmt == "mxfp4":
         p, s = quant.mxfp4_quantize(w)
         out[f"{stem}.blocks"], out[f"{stem}.scales"] = p, s          # packed codes [N, K / 2], UE8M0 [N, K / 32]
@@ -92,7 +95,7 @@ def _emit(out: dict, dtypes: dict, stem: str, w: torch.Tensor, fmt: str):
 
 
 def export_snapshot(spec: ModelSpec, masters: dict, path: str | Path, *, dense: str = "bf16", experts: str = "bf16",
-                    shard_layers: int = 0) -> Path:
+                    shard_layers: int = 0, input_amax: float | None = None) -> Path:
     """Writes `masters` (the oracle's weight dict) as an HF-layout snapshot: one safetensors shard per `shard_layers` layers
     (0 = one file).  `dense` / `experts` choose the storage format of the projections and of the routed experts."""
     path = Path(path)
@@ -117,11 +120,11 @@ def export_snapshot(spec: ModelSpec, masters: dict, path: str | Path, *, dense: 
                 name = stem if key == "router_bias" or key == "sink" else f"{stem}.weight"
                 out[name] = lw[key].to(torch.float32 if key in ("router_bias", "sink") else torch.bfloat16)
             elif _is_expert(key):
-                _emit(out, dt, stem, lw[base][int(key.split(".")[1])], experts)
+                _emit(out, dt, stem, lw[base][int(key.split(".")[1])], experts, input_amax)
             elif key == "router" or key == "wkv_b":
                 _emit(out, dt, stem, lw[key], "bf16")
             else:
-                _emit(out, dt, stem, lw[key], dense)
+                _emit(out, dt, stem, lw[key], dense, input_amax)
 
     for i, lw in enumerate(masters["layers"]):
         put_layer(i, lw)
@@ -238,6 +241,11 @@ def _tc_from_operands(group: list, device, act_gs: float):
         data = torch.stack([rd(o, "weight") for o in group]).to(device).contiguous()
         sf = torch.stack([swizzle_sf(rd(o, "weight_scale").to(device), 16) for o in group]).contiguous()
         gs = [float(rd(o, "weight_scale_2")) for o in group]
+        # The activation scale is the checkpoint's calibrated `input_scale` (ModelOpt: amax / (448 * 6)); operands launched as
+        # one grouped GEMM quantise their input once, so the group shares the largest of its members' scales.  `act_gs` is
+        # only the fallback for snapshots that ship no `input_scale`: a fixed scale clips blocks above 6 * 448 * act_gs.
+        if all("input_scale" in o.members for o in group):
+            act_gs = max(float(rd(o, "input_scale")) for o in group)
         alpha = torch.tensor([g * act_gs for g in gs], dtype=torch.float32, device=device)
         return TcWeight._finish(K.KIND_NVFP4, G, N, Kd, data, sf, alpha, act_gs)
     if f == "mxfp4":
@@ -245,6 +253,20 @@ def _tc_from_operands(group: list, device, act_gs: float):
         sf = torch.stack([swizzle_sf(rd(o, "scales").to(device), 8) for o in group]).contiguous()
         return TcWeight._finish(K.KIND_MXFP4, G, N, Kd, data, sf, torch.ones(G, dtype=torch.float32, device=device), act_gs)
     raise NotImplementedError(f"{group[0].stem}: format {f} has no tensor-core operand form (EXL3 linears load as ops.Exl3Weight)")
+
+
+def _share_act_scale(a, b):
+    """Two NVFP4 operands that multiply the SAME quantised activation (gate and up of a SwiGLU) must agree on its global
+    scale: both take the larger one and their output scales (weight scale x activation scale) follow."""
+    from .. import ops as K
+    if a is None or b is None or a.kind != K.KIND_NVFP4 or b.kind != K.KIND_NVFP4:
+        return
+    ga, gb = 1.0 / float(a.inv_act_gs[0]), 1.0 / float(b.inv_act_gs[0])
+    g = max(ga, gb)
+    for w, old in ((a, ga), (b, gb)):
+        if old != g:
+            w.alpha.mul_(g / old)
+            w.inv_act_gs.fill_(1.0 / g)
 
 
 def _fuse_rows(parts: list, device, act_gs: float):
@@ -294,10 +316,12 @@ def load_device_weights(snapshot: str | Path, spec: ModelSpec, device, *, expert
             if e_hi > e_lo:
                 for name in ("w_gate", "w_up", "w_down"):
                     setattr(lw, name, _tc_from_operands([ops[s[f"{name}.{e}"]] for e in range(e_lo, e_hi)], device, act_gs))
+                _share_act_scale(lw.w_gate, lw.w_up)
             if "ws_gate" in s:
                 lw.ws_gate, lw.ws_up, lw.ws_down = one(s["ws_gate"]), one(s["ws_up"]), one(s["ws_down"])
         else:
             lw.ws_gate, lw.ws_up, lw.ws_down = one(s["wd_gate"]), one(s["wd_up"]), one(s["wd_down"])
+        _share_act_scale(lw.ws_gate, lw.ws_up)
         return lw
 
     embed = read_tensor(ops["model.embed_tokens"].members["weight"]).to(torch.bfloat16).to(device).contiguous()

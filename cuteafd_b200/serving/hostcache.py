@@ -172,21 +172,36 @@ class HostCache:
             n += 1
         return n
 
+    def pin(self, tokens: list[int], n_pages: int, delta: int = 1) -> None:
+        """Hold (`delta` = 1) or let go of (`delta` = -1) the first `n_pages` host pages of a prefix: pinned pages are never
+        chosen by `_evict_one`, so a restore that must first make room on the device (whose evictions write behind into this
+        tier) cannot lose the pages it is about to copy back."""
+        key = b""
+        for d in range(n_pages):
+            key = chain_key(key, tuple(tokens[d * self.page_tokens:(d + 1) * self.page_tokens]))
+            hp = self.pages.get(key)
+            if hp is None:
+                break
+            hp.refs = max(0, hp.refs + delta)
+
     def restore(self, tokens: list[int], first_page: int, device_pages: list[int]) -> int:
-        """Copy host pages [first_page, first_page + len(device_pages)) of the prefix into the given device pages."""
+        """Copy host pages [first_page, first_page + len(device_pages)) of the prefix into the given device pages.  Stops at the
+        first page the tier no longer holds and returns how many pages were restored (the caller releases the rest)."""
         key, batch = b"", []
         for d in range(first_page + len(device_pages)):
             key = chain_key(key, tuple(tokens[d * self.page_tokens:(d + 1) * self.page_tokens]))
+            hp = self.pages.get(key)
+            if hp is None:
+                break
             if d >= first_page:
-                hp = self.pages[key]
                 hp.last_used = next(self.clock)
                 batch.append((device_pages[d - first_page], hp.slab))
                 self.stats["restored_pages"] += 1
         self.copy.h2d_many(batch)
         self.copy.synchronize()
-        if device_pages:
+        if batch:
             self.stats["hits"] += 1
-        return len(device_pages)
+        return len(batch)
 
     def _evict_one(self, protect: bytes | None = None) -> bool:
         cands = [(hp.last_used, k) for k, hp in self.pages.items() if hp.refs == 0 and k != protect]

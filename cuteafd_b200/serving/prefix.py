@@ -129,13 +129,29 @@ class PrefixCache:
             return node, depth
         chain_pages = {n.page for n in self._chain(node)}
         want = n_host - depth
-        if not self.pool.can_alloc(want):
-            self.evict(want - self.pool.n_free, protect=chain_pages)
-        want = min(want, self.pool.n_free)
-        if want <= 0:
+        # Making room on the device evicts chains, whose write-behind may in turn evict host pages: hold the pages of THIS
+        # prefix on the host until they have been copied back.
+        self.host.pin(tokens, n_host, +1)
+        pages = []
+        try:
+            if not self.pool.can_alloc(want):
+                self.evict(want - self.pool.n_free, protect=chain_pages)
+            want = min(want, self.pool.n_free)
+            if want <= 0:
+                return node, depth
+            pages = [self.pool.alloc() for _ in range(want)]        # the tree owns these references
+            got = self.host.restore(tokens, depth, pages)
+        except Exception:
+            for p in pages:
+                self.pool.release(p)
+            raise
+        finally:
+            self.host.pin(tokens, n_host, -1)
+        for p in pages[got:]:                                       # pages the host no longer held: back to the pool
+            self.pool.release(p)
+        pages, want = pages[:got], got
+        if not pages:
             return node, depth
-        pages = [self.pool.alloc() for _ in range(want)]            # the tree owns these references
-        self.host.restore(tokens, depth, pages)
         for i, page in enumerate(pages):
             key = tuple(tokens[(depth + i) * PAGE:(depth + i + 1) * PAGE])
             nxt = Node(page=page, parent=node, key=key, kind="host")

@@ -185,6 +185,11 @@ class Scheduler:
                     self._finish_unadmitted(req, "error: prompt does not fit the KV pool")
                     continue
                 break
+            except Exception as e:                # anything else is this request's failure, never the scheduler's
+                self.queue.popleft()
+                self.stats["rejected"] += 1
+                self._finish_unadmitted(req, f"error: admission failed ({type(e).__name__}: {e})")
+                continue
             self.queue.popleft()
             self.active.append(st)
 

@@ -114,3 +114,43 @@ def test_prefix_and_host_tiers_keep_their_books_under_random_traffic():
     pc.evict(10 ** 6)
     assert pool.n_free == 47 and all(r == 0 for r in pool.refs[1:])          # nothing leaked (page 0 is reserved)
     assert hc.stats["restored_pages"] > 0 and pc.stats["host_hits"] > 0
+
+
+def test_restore_survives_both_tiers_being_full():
+    """Device pool of 9 pages, 4 host slabs, three 3-page prompts A, B, C, then A again: making room for A's restore evicts
+    device chains, whose write-behind evicts host pages.  The pages being restored are pinned, nothing leaks, no KeyError."""
+    from cuteafd_b200.engine.kv import PagePool
+    from cuteafd_b200.serving.prefix import PrefixCache
+    eng = StubCopyEngine(page_bytes=4096)
+    hc = HostCache(eng, n_slabs=4, page_bytes=4096, min_tokens=64)
+    pool = PagePool(9)
+    pc = PrefixCache(pool, max_entries=8, min_tokens=64, max_cached_pages=9, host=hc)
+    prompts = {t: _toks(t, 3) + [1] for t in (1, 2, 3)}
+    for t in (1, 2, 3, 1, 2, 3, 1):
+        adm = pc.admit(prompts[t], reserve_new=1)
+        for i, p in enumerate(adm.seq.pages[:3]):
+            if i * 64 >= adm.hit_tokens:
+                eng.device[p] = (t, i)
+        for i, p in enumerate(adm.seq.pages[:3]):
+            assert eng.device[p] == (t, i)                          # restored pages carry this prompt's content
+        adm.seq.length = len(prompts[t])
+        pc.capture(prompts[t], adm.seq)
+        pc.release(adm.seq)
+        held = pc.n_nodes
+        assert pool.n_free + held == pool.n_pages - pool.reserved   # every page is either free or owned by the tree
+    assert all(hp.refs == 0 for hp in hc.pages.values())
+
+
+def test_restore_stops_at_a_missing_page_and_reports_the_count():
+    eng = StubCopyEngine(page_bytes=1000)
+    hc = HostCache(eng, n_slabs=8, page_bytes=1000, min_tokens=64)
+    a = _toks(1, 4)
+    for p in range(4):
+        eng.device[p] = ("a", p)
+    hc.store(a, [0, 1, 2, 3])
+    from cuteafd_b200.serving.hostcache import chain_key
+    key = b""
+    for d in range(3):
+        key = chain_key(key, tuple(a[d * 64:(d + 1) * 64]))
+    hc.free.append(hc.pages.pop(key).slab)                          # page 2 disappears
+    assert hc.restore(a, 0, [10, 11, 12, 13]) == 2
