@@ -89,7 +89,12 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then marked invalid)")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"], help="multi-GPU transport: fused peer-memory kernels, or the NCCL-only baseline")
-    ap.add_argument("--attn-groups", type=int, default=0, help="data-parallel attention groups in the attention/expert split (0 = the config's default)")
+    ap.add_argument("--attn-groups", type=int, default=0, help="data-parallel attention groups in the split layout (0 = the config's default)")
+    ap.add_argument("--layout", default=None, choices=["split", "colocated"],
+                    help="multi-GPU layout: disjoint attention / expert ranks, or both roles on every GPU (default: per model, see parallel.runner.default_layout)")
+    ap.add_argument("--n-micro", type=int, default=0, help="micro-batches an attention rank keeps in flight (0 = the layout's default)")
+    ap.add_argument("--no-selftest", action="store_true", help="skip the token-exactness check of the layout on the tiny model (N > 1)")
+    ap.add_argument("--no-nccl-baseline", action="store_true", help="skip the NCCL-only arm that N > 1 runs report beside the main number")
     ap.add_argument("--real-prefill", action="store_true", help="build the context by running prefill instead of filling KV")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -109,10 +114,44 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
 
     from cuteafd_b200.bench.decode import run_decode_bench
+    selftest = None
+    if world > 1 and not args.no_selftest and args.comm == "p2p":
+        # the layout about to be timed must first generate the single-GPU engine's tokens on the tiny model
+        from cuteafd_b200.config import deepseek_v3_spec, qwen3_235b_spec
+        from cuteafd_b200.parallel.runner import default_layout
+        from cuteafd_b200.parallel.selftest import run_selftest
+        big = deepseek_v3_spec(2) if args.config.startswith("deepseek-v3") else qwen3_235b_spec(2)
+        lay = default_layout(big, world, args.comm)
+        layout = args.layout or lay["layout"]
+        ok = run_selftest(rank, world, local, layout=layout, groups=(args.attn_groups or (1 if layout == "split" else world)),
+                          n_micro=args.n_micro or lay["n_micro"], comm="p2p", experts="nvfp4" if big.quant.experts == "nvfp4" else "mxfp4",
+                          model=big.attn.kind, verbose=False)
+        selftest = "ok" if ok else "FAILED"
     res = run_decode_bench(args, rank, world, local, ClockSampler(local))
+    nccl = None
+    if world > 1 and args.comm == "p2p" and not args.no_nccl_baseline:
+        # like-for-like baseline row: the same model, batch and context over the NCCL-only path (split layout, eager)
+        import copy
+        import gc
+        import torch
+        gc.collect(); torch.cuda.empty_cache()
+        a2 = copy.copy(args)
+        a2.comm, a2.layout, a2.n_micro, a2.attn_groups = "nccl", "split", 1, 1
+        a2.steps, a2.warmup = max(3, min(args.steps, 5)), 3
+        a2.batch_total = args.batch_total or args.batch_per_gpu * world
+        r2 = run_decode_bench(a2, rank, world, local, ClockSampler(local))
+        if rank == 0:
+            nccl = {"value": r2["value"], "unit": r2["unit"], "ms_per_step": r2["ms_per_step"], "steps": r2["steps"],
+                    "parallelism": r2["config"]["parallelism"], "e2e_value": r2["e2e"]["value"]}
     if rank == 0:
         res["vs_baseline"] = round(res["value"] / BASELINE_TOKS, 3)
         res["baseline_ref"] = BASELINE_SRC
+        res["vs_baseline_comparable"] = False     # a different, smaller model on other hardware: context only, see nccl_baseline
+        if selftest is not None:
+            res["selftest"] = selftest
+        if nccl is not None:
+            res["nccl_baseline"] = nccl
+            res["vs_nccl_baseline"] = round(res["value"] / nccl["value"], 3) if nccl["value"] else None
         print(json.dumps(res))
     if world > 1:
         import torch.distributed as dist

@@ -75,7 +75,7 @@ def run_decode_bench(args, rank: int, world: int, local: int, clocks) -> dict:
 
     # ---- device arm: graph replays timed with CUDA events
     kv_len = [s.length + 1 for s in gen.seqs]
-    sh = StepShape(T=batch, n_seq=batch, max_q_len=1, n_logits=batch, attn_splits=eng.attn_splits_for(batch, 1, max(kv_len)))
+    sh = StepShape(T=batch, n_seq=batch, max_q_len=1, n_logits=batch, attn_splits=eng.attn_splits_for(batch, 1, max(kv_len)), uniform=True)
     for _ in range(args.warmup):
         eng.run(sh)
     torch.cuda.synchronize()

@@ -327,7 +327,7 @@ class Deployment:
         if self.world == 1:
             return "single"
         dp = f"dp{self.attn_groups}x" if self.attn_groups > 1 else ""
-        return f"attn-{dp}tp{self.tp}+ep{self.ep}" if not self.colocated else f"tp{self.tp}-ep{self.ep}-colocated"
+        return f"attn-{dp}tp{self.tp}+ep{self.ep}" if not self.colocated else f"colocated attn-{dp}tp{self.tp} + ep{self.ep} on the same GPUs"
 
 
 def default_deployment(world: int, attn_groups: int = 1) -> Deployment:
@@ -346,3 +346,22 @@ def default_deployment(world: int, attn_groups: int = 1) -> Deployment:
         raise ValueError(f"{attn_groups} attention groups leave no expert rank in a world of {world}")
     return Deployment(world=world, attn_ranks=tuple(range(n_attn)), expert_ranks=tuple(range(n_attn, world)), colocated=False,
                       attn_groups=attn_groups)
+
+
+def colocated_deployment(world: int) -> Deployment:
+    """Every GPU is an attention rank for its own sequences (data-parallel attention, TP1) AND an expert rank for its share
+    of the routed experts (reference counterpart: routed layers resident on the coordinator GPUs, `--rtx-expert-layers`,
+    shared/experts/local.rs; on NVSwitch every GPU can afford both roles)."""
+    if world == 1:
+        return Deployment()
+    ranks = tuple(range(world))
+    return Deployment(world=world, attn_ranks=ranks, expert_ranks=ranks, colocated=True, attn_groups=world)
+
+
+def deployment_by_name(layout: str, world: int, attn_groups: int = 1) -> Deployment:
+    """`split` = disjoint attention / expert ranks (`default_deployment`), `colocated` = both roles on every GPU."""
+    if layout == "colocated":
+        return colocated_deployment(world)
+    if layout == "split":
+        return default_deployment(world, attn_groups)
+    raise ValueError(f"unknown layout {layout!r} (split | colocated)")

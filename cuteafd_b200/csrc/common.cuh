@@ -386,8 +386,23 @@ __device__ __forceinline__ bool flag_wait_block(const FlagWait& w) {
   __syncthreads();
   return fw_ok != 0;
 }
-// One-shot hand-over from cuteafd_arm_flag_wait() to the next launch of this host thread that supports it.
-FlagWait ca_take_flag_wait();
+// Optional arguments cross the C ABI as explicit host structs passed by pointer (null = absent): nothing is armed for "the
+// next call of this thread".
+struct CaFlagWaitArg {        // in-kernel wait in front of a consumer of peer data (route_pack, moe_combine[_norm])
+  const void* flags; void* ctl; int* status; unsigned long long timeout_ns; int n, stride;
+};
+struct CaTcExtra {            // tc_linear: FP4 copy of the output and/or stores of the output tile into peers' memory
+  void* q_out; void* sf_out; const float* inv_gs_out; int ldsf_out; int n_peer;
+  void* peer_y[2]; void* peer_flag[2]; const int* peer_row_map; void* peer_ctl; void* peer_done; int peer_ld; int reserved;
+};
+static inline FlagWait ca_flag_wait_from(const CaFlagWaitArg* a) {
+  FlagWait w = {nullptr, nullptr, nullptr, 0ull, 0, 0};
+  if (a && a->flags && a->n > 0) {
+    w.flags = (const uint32_t*)a->flags; w.ctl = (uint32_t*)a->ctl; w.status = a->status;
+    w.timeout_ns = a->timeout_ns; w.n = a->n > 32 ? 32 : a->n; w.stride = a->stride;
+  }
+  return w;
+}
 
 // ------------------------------------------------------------------ host: TMA descriptor encode
 // Resolved at run time from the driver so the library links without libcuda.

@@ -17,7 +17,16 @@ struct RoutePack {
   int T, k, e_lo, e_hi, tn, max_tiles;
   int* ticket;      // fused with the router: arrival counter of the select blocks (zero on entry, left zero)
   FlagWait wait;    // expert ranks: the routing table and the rows arrive from peers; wait for their flags first
+  // Several senders ("lanes") share one routing table laid out [lane][t_cap][k]; lane l delivered lane_T[l] tokens this step
+  // (written by the sender next to its rows).  Token index = l * t_cap + t; rows t >= lane_T[l] are stale and skipped.
+  const int* lane_T; int t_cap;
 };
+
+__device__ __forceinline__ bool route_live(const RoutePack& p, int i) {
+  if (!p.lane_T) return true;
+  const int tok = i / p.k;
+  return (tok % p.t_cap) < __ldcg(p.lane_T + tok / p.t_cap);
+}
 
 __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
   // sh: [E_local] counts, [E_local] offsets/cursors, [T*k] staged ids (small batches)
@@ -26,7 +35,11 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
   for (int e = threadIdx.x; e < El; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   const int n = p.T * p.k;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) { const int e = __ldcg(p.idx + i) - p.e_lo; if (e >= 0 && e < El) atomicAdd(&cnt[e], 1); }
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    if (!route_live(p, i)) continue;
+    const int e = __ldcg(p.idx + i) - p.e_lo;
+    if (e >= 0 && e < El) atomicAdd(&cnt[e], 1);
+  }
   __syncthreads();
   // Row offsets and the tile table in expert order: warp 0 scans, each lane owning a run of consecutive experts
   // (a single thread walking all experts with its global stores was several microseconds of every MoE layer).
@@ -53,9 +66,10 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
   // Stable placement (token order inside each expert) so packed layouts are reproducible: each route counts the
   // earlier routes to its expert when T*k is small; larger batches use atomics (row order inside an expert does
   // not change any result: rows are independent in the GEMM and the combine reads them by index).
-  if (n <= 4096) {
+  // (multi-lane tables need no agreement with the senders on row positions, so their larger cases take the atomic path)
+  if (n <= (p.lane_T ? 1024 : 4096)) {
     int* sid = cur + El;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = __ldcg(p.idx + i) - p.e_lo;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = route_live(p, i) ? __ldcg(p.idx + i) - p.e_lo : -1;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int e = sid[i];
@@ -68,7 +82,7 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
     }
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const int e = __ldcg(p.idx + i) - p.e_lo;
+      const int e = route_live(p, i) ? __ldcg(p.idx + i) - p.e_lo : -1;
       if (e >= 0 && e < El) { const int c = atomicAdd(&cur[e], 1); p.src_token[c] = i / p.k; p.slot_row[i] = c; if (p.src_route) p.src_route[c] = i; } else p.slot_row[i] = -1;
     }
   }
@@ -241,17 +255,84 @@ extern "C" int cuteafd_router_select(const float* logits, const float* bias, int
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
   RoutePack none{};
   none.wait = FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0};
+  none.lane_T = nullptr; none.t_cap = 0;
   CA_LAUNCH_PDL(router_select_kernel, T, threads, 0, s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale, n_group, topk_group, none);
   return CA_OK;
 }
 
 extern "C" int cuteafd_route_pack(const int* idx, int* src_token, int* slot_row, int* counts, int* offsets, void* tiles,
-                                  int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, int* src_route, cudaStream_t s) {
+                                  int* n_tiles, int* n_rows, int T, int k, int e_lo, int e_hi, int tn, int max_tiles, int* src_route,
+                                  const CaFlagWaitArg* wait, const int* lane_T, int t_cap, cudaStream_t s) {
+  const FlagWait fw = ca_flag_wait_from(wait);
   CA_REQUIRE(e_hi > e_lo && e_hi - e_lo <= 4096, "route_pack: bad expert range");
   CA_REQUIRE(tn >= 1, "route_pack: bad tile rows");
+  CA_REQUIRE(!lane_T || (t_cap >= 1 && T % t_cap == 0), "route_pack: a lane table needs T = lanes * t_cap");
   RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, nullptr,
-              ca_take_flag_wait()};
+              fw, lane_T, t_cap};
   CA_LAUNCH_PDL(route_pack_kernel, 1, 1024, route_pack_smem(T, k, e_lo, e_hi), s, p);
+  return CA_OK;
+}
+
+// Rows of a token-major slab (FP4 / bf16 payload + block scales, as the dispatch kernel delivered them) gathered into the
+// expert-major order of the route pack: dst row c = src row src_token[c] for c < *n_rows.  One block per packed row.
+__global__ void route_gather_kernel(const uint8_t* __restrict__ src_q, const uint8_t* __restrict__ src_sf, const int* __restrict__ src_token,
+                                    const int* __restrict__ n_rows, uint8_t* __restrict__ dst_q, uint8_t* __restrict__ dst_sf,
+                                    int row_bytes, int sf_bytes, int src_sf_ld, int dst_sf_ld, int src_rows, int* status) {
+  pdl_launch(); pdl_wait();
+  const int n = *n_rows;
+  for (int c = blockIdx.x; c < n; c += gridDim.x) {
+    const int t = src_token[c];
+    if (t < 0 || t >= src_rows) { if (threadIdx.x == 0) ca_dev_fail(status, CA_DEV_BAD_INDEX, c); continue; }
+    const uint4* sq = (const uint4*)(src_q + (size_t)t * row_bytes);
+    uint4* dq = (uint4*)(dst_q + (size_t)c * row_bytes);
+    for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dq[i] = __ldcg(sq + i);
+    if (sf_bytes) {
+      const uint8_t* ss = src_sf + (size_t)t * src_sf_ld; uint8_t* ds = dst_sf + (size_t)c * dst_sf_ld;
+      for (int i = threadIdx.x; i < sf_bytes / 4; i += blockDim.x) ((uint32_t*)ds)[i] = __ldcg((const uint32_t*)ss + i);
+    }
+  }
+}
+
+extern "C" int cuteafd_route_gather(const void* src_q, const void* src_sf, const int* src_token, const int* n_rows, void* dst_q, void* dst_sf,
+                                    int row_bytes, int sf_bytes, int src_sf_ld, int dst_sf_ld, int src_rows, int rows_cap, int* status,
+                                    cudaStream_t s) {
+  CA_REQUIRE(row_bytes % 16 == 0 && sf_bytes % 4 == 0 && src_sf_ld % 4 == 0 && dst_sf_ld % 4 == 0, "route_gather: rows are 16-byte, scales 4-byte multiples");
+  CA_REQUIRE(((uintptr_t)src_q & 15) == 0 && ((uintptr_t)dst_q & 15) == 0, "route_gather: 16-byte aligned payloads");
+  if (rows_cap <= 0) return CA_OK;
+  const int blocks = rows_cap < 592 ? rows_cap : 592;
+  CA_LAUNCH_PDL(route_gather_kernel, blocks, 128, 0, s, (const uint8_t*)src_q, (const uint8_t*)src_sf, src_token, n_rows, (uint8_t*)dst_q,
+                (uint8_t*)dst_sf, row_bytes, sf_bytes, src_sf_ld, dst_sf_ld, src_rows, status);
+  return CA_OK;
+}
+
+// Hash routing (layers whose experts are a fixed function of the token id): expert ids come from tid2eid[token][0..k), gate
+// weights are the sqrt-softplus scores of the logits at those experts, normalised over the k and scaled.  One warp per token.
+__global__ void router_hash_select_kernel(const float* __restrict__ logits, const int* __restrict__ tid2eid, const int* __restrict__ tokens,
+                                          int* __restrict__ idx, float* __restrict__ wts, int T, int E, int k, int vocab, float route_scale,
+                                          int* status) {
+  pdl_launch(); pdl_wait();
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  int tok = tokens[t];
+  if (tok < 0 || tok >= vocab) { if (lane == 0) ca_dev_fail(status, CA_DEV_BAD_INDEX, t); tok = 0; }
+  int e = 0; float sc = 0.f;
+  if (lane < k) {
+    e = tid2eid[(size_t)tok * k + lane];
+    if (e < 0 || e >= E) { ca_dev_fail(status, CA_DEV_BAD_INDEX, t); e = 0; }
+    const float x = logits[(size_t)t * E + e];
+    sc = sqrtf(x > 20.f ? x : log1pf(expf(x)));
+  }
+  float tot = sc;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+  if (lane < k) { idx[(size_t)t * k + lane] = e; wts[(size_t)t * k + lane] = sc / (tot + 1e-20f) * route_scale; }
+}
+
+extern "C" int cuteafd_router_hash_select(const float* logits, const int* tid2eid, const int* tokens, int* idx, float* wts, int T, int E, int k,
+                                          int vocab, float route_scale, int* status, cudaStream_t s) {
+  CA_REQUIRE(k >= 1 && k <= 32 && E >= k && vocab >= 1, "router_hash_select: 1 <= k <= 32 <= E");
+  if (T <= 0) return CA_OK;
+  CA_LAUNCH_PDL(router_hash_select_kernel, (T + 3) / 4, 128, 0, s, logits, tid2eid, tokens, idx, wts, T, E, k, vocab, route_scale, status);
   return CA_OK;
 }
 
@@ -267,7 +348,7 @@ extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias
   if (T <= 0) return CA_OK;
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
   RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, ticket,
-              FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0}};
+              FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0}, nullptr, 0};
   CA_LAUNCH_PDL(router_select_kernel, T, threads, route_pack_smem(T, k, e_lo, e_hi), s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale,
                 n_group, topk_group, p);
   return CA_OK;
@@ -372,7 +453,8 @@ __global__ void moe_combine_norm_kernel(const bf16* __restrict__ y, const int* _
 
 extern "C" int cuteafd_moe_combine_norm(const void* y, const int* slot_row, const float* wts, const void* shared, const void* residual,
                                         void* out, int T, int H, int k, const float* norm_w, float eps, void* xn, void* q, void* sf,
-                                        int ldsf, const float* inv_gs, int qkind, cudaStream_t s) {
+                                        int ldsf, const float* inv_gs, int qkind, const CaFlagWaitArg* wait, cudaStream_t s) {
+  const FlagWait fw = ca_flag_wait_from(wait);
   CA_REQUIRE(H % 8 == 0 && H <= 32768 && norm_w, "moe_combine_norm: bad arguments");
   CA_REQUIRE(qkind == 0 || ((qkind == 1 || qkind == 2) && q && sf && H % 256 == 0), "moe_combine_norm: FP4 output needs buffers and hidden %% 256 == 0");
   if (T <= 0) return CA_OK;
@@ -382,20 +464,19 @@ extern "C" int cuteafd_moe_combine_norm(const void* y, const int* slot_row, cons
   const int per = (vecs + threads - 1) / threads;
 #define CA_CN(V) CA_LAUNCH_PDL(moe_combine_norm_kernel<V>, T, threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, \
                                (bf16*)out, H, k, norm_w, eps, (bf16*)xn, (uint8_t*)q, (uint8_t*)sf, ldsf, inv_gs, qkind, fw)
-  const FlagWait fw = ca_take_flag_wait();
   if (per == 1) CA_CN(1); else if (per == 2) CA_CN(2); else CA_CN(4);
 #undef CA_CN
   return CA_OK;
 }
 
 extern "C" int cuteafd_moe_combine(const void* y, const int* slot_row, const float* wts, const void* shared, const void* residual,
-                                   void* out, int T, int H, int k, cudaStream_t s) {
+                                   void* out, int T, int H, int k, const CaFlagWaitArg* wait, cudaStream_t s) {
+  const FlagWait fw = ca_flag_wait_from(wait);
   CA_REQUIRE(H % 8 == 0, "moe_combine: hidden must be a multiple of 8");
   if (T <= 0) return CA_OK;
   const int threads = H / 8 >= 256 ? 256 : (H / 8 >= 128 ? 128 : 64);
   // few tokens: split the row over several blocks so more SMs pull the k routed rows
   const int ysplit = T >= 64 ? 1 : (H / 8 + threads - 1) / threads;
-  const FlagWait fw = ca_take_flag_wait();
   CA_LAUNCH_PDL(moe_combine_kernel, dim3(T, ysplit), threads, 0, s, (const bf16*)y, slot_row, wts, (const bf16*)shared, (const bf16*)residual, (bf16*)out, H, k, fw);
   CA_CHECK_LAUNCH("moe_combine");
   return CA_OK;

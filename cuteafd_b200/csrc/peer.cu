@@ -284,6 +284,124 @@ extern "C" int cuteafd_dispatch_push(const void* x, const int* idx, const int* s
   return CA_OK;
 }
 
+// ---------------------------------------------------------------- token-major dispatch
+// One block per token of my share: the row is quantised ONCE into shared memory and stored, with its block scales, into row
+// (lane base + t) of the slab of every expert rank that owns at least one of the token's top-k experts - a token crosses
+// NVLink once per destination rank, not once per route.  The token's k expert ids go to EVERY rank's routing table (a rank
+// must see that a stale row is not for it), and the lane's token count goes next to it, so the expert side needs no host
+// message to learn the step's shape.  The expert rank gathers rows into expert order itself (`route_gather`).
+struct DispatchTokArgs {
+  const bf16* x; const int* idx;
+  PeerPtrs slab_q, slab_sf, idx_dst, lane_t_dst;   // per expert rank, already offset to this lane
+  FlagPtrs flags;
+  const float* inv_gs;
+  uint32_t* ctl; uint32_t* done_counter;
+  int T0, T1, T, H, k, E, n_ep, kind, sf_ld;
+  uint32_t step_offset;
+  int* status;
+};
+
+__device__ __forceinline__ void quant_row_to_smem(const bf16* xr, int H, int kind, float inv_gs, uint8_t* pay, uint8_t* sfs) {
+  if (kind == 0) {
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) ((uint4*)pay)[i] = ((const uint4*)xr)[i];
+    return;
+  }
+  for (int c = threadIdx.x; c < H / 16; c += blockDim.x) {
+    uint4 q0 = ((const uint4*)xr)[2 * c], q1 = ((const uint4*)xr)[2 * c + 1];
+    const bf16* e0 = (const bf16*)&q0; const bf16* e1 = (const bf16*)&q1;
+    float v[16], amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[j] = __bfloat162float(e0[j]); v[8 + j] = __bfloat162float(e1[j]); }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    float eff; uint8_t sb;
+    if (kind == 2) {
+      amax = fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
+      int e = amax > 0.f ? (int)((__float_as_uint(amax) >> 23) & 0xFF) - 2 : 0;
+      e = max(e, 0); e = min(e, 254); sb = (uint8_t)e; eff = ue8m0_to_float(sb);
+      if (!(c & 1)) sfs[c >> 1] = sb;
+    } else {
+      sb = float_to_e4m3(fminf(amax * inv_gs / 6.f, 448.f)); eff = e4m3_to_float(sb) / inv_gs;
+      sfs[c] = sb;
+    }
+    const float inv = eff > 0.f ? 1.f / eff : 0.f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { lo |= float_to_e2m1(v[j] * inv) << (4 * j); hi |= float_to_e2m1(v[8 + j] * inv) << (4 * j); }
+    ((uint2*)pay)[c] = make_uint2(lo, hi);
+  }
+}
+
+__global__ void dispatch_tok_push_kernel(const DispatchTokArgs a) {
+  extern __shared__ uint8_t sh[];
+  __shared__ unsigned owners;
+  const int t = a.T0 + blockIdx.x;
+  const bool live = t < a.T1 && !a.ctl[0];
+  const int H = a.H;
+  const int row_bytes = a.kind == 0 ? H * 2 : H / 2;
+  const int n_sf = a.kind == 0 ? 0 : (a.kind == 1 ? H / 16 : H / 32);
+  uint8_t* pay = sh; uint8_t* sfs = sh + row_bytes;
+  if (threadIdx.x == 0) owners = 0u;
+  __syncthreads();
+  if (live) {
+    quant_row_to_smem(a.x + (size_t)t * H, H, a.kind, (a.kind == 1 && a.inv_gs) ? *a.inv_gs : 1.f, pay, sfs);
+    if ((int)threadIdx.x < a.k) {
+      const int e = a.idx[(size_t)t * a.k + threadIdx.x];
+      int owner = -1;
+      for (int o = 0; o < a.n_ep; ++o) if (e >= (o * a.E) / a.n_ep && e < ((o + 1) * a.E) / a.n_ep) owner = o;
+      if (owner < 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, t); else atomicOr(&owners, 1u << owner);
+      for (int d = 0; d < a.n_ep; ++d) ((int*)a.idx_dst.p[d])[(size_t)t * a.k + threadIdx.x] = e;
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 32 && !a.ctl[0])
+    for (int d = 0; d < a.n_ep; ++d) *(int*)a.lane_t_dst.p[d] = a.T;
+  __syncthreads();
+  if (live) {
+    const unsigned m = owners;
+    for (int d = 0; d < a.n_ep; ++d) {
+      if (!(m >> d & 1)) continue;
+      uint4* dq = (uint4*)((uint8_t*)a.slab_q.p[d] + (size_t)t * row_bytes);
+      for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dq[i] = ((const uint4*)pay)[i];
+      if (n_sf) {
+        uint32_t* ds = (uint32_t*)((uint8_t*)a.slab_sf.p[d] + (size_t)t * a.sf_ld);
+        for (int i = threadIdx.x; i < n_sf / 4; i += blockDim.x) ds[i] = ((const uint32_t*)sfs)[i];
+      }
+    }
+  }
+  publish_when_last(a.done_counter, a.flags.p, a.n_ep, a.ctl[1] + a.step_offset);
+}
+
+extern "C" int cuteafd_dispatch_tok_push(const void* x, const int* idx, const void* const* slab_q, const void* const* slab_sf,
+                                         const void* const* idx_dst, const void* const* lane_t_dst, const void* const* flags,
+                                         const float* inv_gs, void* ctl, void* done_counter, int T0, int T1, int T, int H, int k, int E,
+                                         int n_ep, int kind, int sf_ld, unsigned step_offset, int* status, cudaStream_t s) {
+  CA_REQUIRE(n_ep >= 1 && n_ep <= MAX_PEERS, "dispatch_tok_push: 1..8 expert ranks");
+  CA_REQUIRE(H % 256 == 0 && k >= 1 && k <= 32, "dispatch_tok_push: hidden must be a multiple of 256 and k <= 32");
+  CA_REQUIRE(kind >= 0 && kind <= 2 && (kind == 0 || (slab_sf && sf_ld % 4 == 0)), "dispatch_tok_push: FP4 rows need a scale slab");
+  CA_REQUIRE(T0 >= 0 && T1 >= T0 && T1 <= T, "dispatch_tok_push: my share [T0, T1) must lie inside the lane's T tokens");
+  DispatchTokArgs a;
+  a.x = (const bf16*)x; a.idx = idx; a.inv_gs = inv_gs;
+  for (int i = 0; i < n_ep; ++i) {
+    a.slab_q.p[i] = const_cast<void*>(slab_q[i]); a.slab_sf.p[i] = slab_sf ? const_cast<void*>(slab_sf[i]) : nullptr;
+    a.idx_dst.p[i] = const_cast<void*>(idx_dst[i]); a.lane_t_dst.p[i] = const_cast<void*>(lane_t_dst[i]); a.flags.p[i] = (uint32_t*)flags[i];
+  }
+  a.ctl = (uint32_t*)ctl; a.done_counter = (uint32_t*)done_counter; a.T0 = T0; a.T1 = T1; a.T = T; a.H = H; a.k = k; a.E = E;
+  a.n_ep = n_ep; a.kind = kind; a.sf_ld = sf_ld; a.step_offset = step_offset; a.status = status;
+  const int blocks = T1 > T0 ? T1 - T0 : 1;
+  const size_t smem = (kind == 0 ? (size_t)H * 2 : (size_t)H / 2 + H / 16);
+  static bool attr_set[64] = {false};
+  int dev = 0; cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && !attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(dispatch_tok_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(dispatch_tok_push)");
+    attr_set[dev & 63] = true;
+  }
+  CA_REQUIRE(smem <= 64 * 1024, "dispatch_tok_push: row does not fit shared memory");
+  dispatch_tok_push_kernel<<<blocks, 128, smem, s>>>(a);
+  CA_CHECK_LAUNCH("dispatch_tok_push");
+  return CA_OK;
+}
+
 // ---------------------------------------------------------------- combine: expert rank -> attention ranks
 // Row i of y (local packed order) belongs to route src_route[i] = token * k + slot; it is stored to
 // recv[token][slot][:] on every attention rank.  Rows >= *n_rows are skipped.
@@ -321,5 +439,52 @@ extern "C" int cuteafd_combine_push(const void* y, const int* src_route, const i
   int blocks = rows_cap < 296 ? (rows_cap > 0 ? rows_cap : 1) : 296;
   combine_push_kernel<<<blocks, 128, 0, s>>>(a);
   CA_CHECK_LAUNCH("combine_push");
+  return CA_OK;
+}
+
+// ---------------------------------------------------------------- combine for a lane table
+// As combine_push, for rows that came from several lanes: route = (lane * t_cap + t) * k + slot; the row goes to
+// recv[lane * tp + j][(t * k + slot)] for the tp attention ranks j of that lane (their buffers hold only their own lane),
+// and every destination's flag is released once all rows are out.
+struct CombineLanesArgs {
+  const bf16* y; const int* src_route; const int* n_rows;
+  PeerPtrs recv; FlagPtrs flags;
+  uint32_t* ctl; uint32_t* done_counter;
+  int H, k, t_cap, tp, n_dst, rows_cap;
+  uint32_t step_offset;
+  int* status;
+};
+
+__global__ void combine_push_lanes_kernel(const CombineLanesArgs a) {
+  const int n = min(*a.n_rows, a.rows_cap);
+  if (!a.ctl[0]) {
+    for (int r = blockIdx.x; r < n; r += gridDim.x) {
+      const int route = a.src_route[r];
+      const int tok = route / a.k, slot = route - tok * a.k;
+      const int lane = tok / a.t_cap, t = tok - lane * a.t_cap;
+      if (route < 0 || (lane + 1) * a.tp > a.n_dst) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, r); continue; }
+      const uint4* src = (const uint4*)(a.y + (size_t)r * a.H);
+      for (int j = 0; j < a.tp; ++j) {
+        uint4* dst = (uint4*)((bf16*)a.recv.p[lane * a.tp + j] + ((size_t)t * a.k + slot) * a.H);
+        for (int i = threadIdx.x; i < a.H / 8; i += blockDim.x) dst[i] = src[i];
+      }
+    }
+  }
+  publish_when_last(a.done_counter, a.flags.p, a.n_dst, a.ctl[1] + a.step_offset);
+}
+
+extern "C" int cuteafd_combine_push_lanes(const void* y, const int* src_route, const int* n_rows, const void* const* recv,
+                                          const void* const* flags, void* ctl, void* done_counter, int H, int k, int t_cap, int tp,
+                                          int n_dst, int rows_cap, unsigned step_offset, int* status, cudaStream_t s) {
+  CA_REQUIRE(n_dst >= 1 && n_dst <= MAX_PEERS && tp >= 1 && n_dst % tp == 0 && H % 8 == 0 && k >= 1 && t_cap >= 1,
+             "combine_push_lanes: bad arguments");
+  CombineLanesArgs a;
+  a.y = (const bf16*)y; a.src_route = src_route; a.n_rows = n_rows;
+  for (int i = 0; i < n_dst; ++i) { a.recv.p[i] = const_cast<void*>(recv[i]); a.flags.p[i] = (uint32_t*)flags[i]; }
+  a.ctl = (uint32_t*)ctl; a.done_counter = (uint32_t*)done_counter; a.H = H; a.k = k; a.t_cap = t_cap; a.tp = tp; a.n_dst = n_dst;
+  a.rows_cap = rows_cap; a.step_offset = step_offset; a.status = status;
+  int blocks = rows_cap < 296 ? (rows_cap > 0 ? rows_cap : 1) : 296;
+  combine_push_lanes_kernel<<<blocks, 128, 0, s>>>(a);
+  CA_CHECK_LAUNCH("combine_push_lanes");
   return CA_OK;
 }

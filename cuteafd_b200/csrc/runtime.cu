@@ -86,23 +86,7 @@ int ca_pdl_enabled(int cls) {
   return (g_pdl >> cls) & 1;
 }
 
-static thread_local FlagWait g_flag_wait = {nullptr, nullptr, nullptr, 0ull, 0, 0};
-FlagWait ca_take_flag_wait() {
-  FlagWait w = g_flag_wait;
-  g_flag_wait.flags = nullptr;
-  return w;
-}
-
 extern "C" {
-
-// Arms the next route_pack / moe_combine / moe_combine_norm launch of this thread to wait, inside the kernel, until
-// flags[i * stride] >= ctl[1] for i < n (at most 32 flags) before it reads its inputs.
-int cuteafd_arm_flag_wait(const void* flags, int n, int stride, void* ctl, unsigned long long timeout_ns, int* status) {
-  CA_REQUIRE(flags && ctl && n >= 1 && n <= 32, "arm_flag_wait: 1..32 flags and a control block");
-  g_flag_wait.flags = (const uint32_t*)flags; g_flag_wait.ctl = (uint32_t*)ctl; g_flag_wait.status = status;
-  g_flag_wait.timeout_ns = timeout_ns; g_flag_wait.n = n; g_flag_wait.stride = stride;
-  return CA_OK;
-}
 
 // Sets the programmatic-dependent-launch class mask for later launches of this process; returns the old mask.
 int cuteafd_set_pdl(int mask) {

@@ -745,37 +745,26 @@ extern "C" int cuteafd_tc_trace(void* buf, int units) {
   return CA_OK;
 }
 
-static thread_local struct { void* q; void* sf; const float* inv_gs; int ldsf; } g_q_out = {nullptr, nullptr, nullptr, 0};
-
-// Arms the NEXT cuteafd_tc_linear call of this thread to also write its output quantised to FP4 (the operands'
-// format; grouped or dense, not with split-K): codes [rows, N / 2], scales [rows, ldsf].  Y may then be null.
-extern "C" int cuteafd_tc_linear_fp4_out(void* q, void* sf, int ldsf, const float* inv_gs) {
-  g_q_out.q = q; g_q_out.sf = sf; g_q_out.ldsf = ldsf; g_q_out.inv_gs = inv_gs;
-  return CA_OK;
-}
-
-static thread_local struct { void* y[2]; void* flags[2]; const int* row_map; void* ctl; void* done; int ld, n; } g_peer_out = {};
-
-// Arms the NEXT cuteafd_tc_linear call of this thread (bf16 output, dense or grouped, any split mode) to store its
-// output tiles into `n` peers' buffers as well (row r -> row row_map[r] when a map is given) and to release
-// `flags[d]` with the step number ctl[1] when the whole GEMM has been written.  `done` is a zeroed device counter.
-extern "C" int cuteafd_tc_linear_peer_out(void* y0, void* y1, int n, int ld, const int* row_map, void* flag0, void* flag1, void* ctl, void* done) {
-  CA_REQUIRE(n >= 1 && n <= 2 && y0 && flag0 && ctl && done && (n == 1 || (y1 && flag1)), "tc_linear_peer_out: 1 or 2 peers with buffers and flags");
-  g_peer_out.y[0] = y0; g_peer_out.y[1] = y1; g_peer_out.flags[0] = flag0; g_peer_out.flags[1] = flag1;
-  g_peer_out.row_map = row_map; g_peer_out.ctl = ctl; g_peer_out.done = done; g_peer_out.ld = ld; g_peer_out.n = n;
-  return CA_OK;
-}
-
 extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, const void* tmA2, const void* tmB,
                                  const void* sfa, const void* sfa2, const void* sfb, int ldsfb, const float* alpha,
                                  const float* alpha2, const void* tiles, const int* n_tiles, int max_tiles, void* Y,
                                  const void* R, int ldy, int rows_total, int N, int K, int epi, int splits,
-                                 float* splitk_ws, int* splitk_cnt, int* status, int max_ctas, cudaStream_t stream) {
+                                 float* splitk_ws, int* splitk_cnt, int* status, int max_ctas, const CaTcExtra* extra,
+                                 cudaStream_t stream) {
+  // `extra` (optional): an FP4 copy of the output for the GEMM that consumes it (an option of the fused SwiGLU GEMM: codes
+  // [rows, N / 2], scales [rows, ldsf_out]; Y may then be null), and/or stores of the bf16 output tiles into 1-2 peers'
+  // buffers (row r -> row peer_row_map[r] when a map is given) with the peers' flags released with step number peer_ctl[1]
+  // once the whole GEMM has been written (`peer_done`: a zeroed device counter).
   CA_REQUIRE(kind >= 0 && kind <= 2, "tc_linear: bad kind %d", kind);
-  void* q_out = g_q_out.q; void* sf_out = g_q_out.sf; const float* inv_gs_out = g_q_out.inv_gs; const int ldsf_out = g_q_out.ldsf;
-  g_q_out.q = g_q_out.sf = nullptr;       // one-shot
-  const auto peer = g_peer_out;
-  g_peer_out.n = 0;                       // one-shot
+  void* q_out = extra ? extra->q_out : nullptr; void* sf_out = extra ? extra->sf_out : nullptr;
+  const float* inv_gs_out = extra ? extra->inv_gs_out : nullptr; const int ldsf_out = extra ? extra->ldsf_out : 0;
+  struct { void* y[2]; void* flags[2]; const int* row_map; void* ctl; void* done; int ld, n; } peer = {};
+  if (extra && extra->n_peer) {
+    peer.n = extra->n_peer; peer.ld = extra->peer_ld; peer.row_map = extra->peer_row_map; peer.ctl = extra->peer_ctl; peer.done = extra->peer_done;
+    for (int i = 0; i < 2; ++i) { peer.y[i] = extra->peer_y[i]; peer.flags[i] = extra->peer_flag[i]; }
+    CA_REQUIRE(peer.n >= 1 && peer.n <= 2 && peer.y[0] && peer.flags[0] && peer.ctl && peer.done && (peer.n == 1 || (peer.y[1] && peer.flags[1])),
+               "tc_linear: peer output takes 1 or 2 peers with buffers and flags");
+  }
   CA_REQUIRE(tmA && tmB && (Y || q_out || peer.n), "tc_linear: null operand");
   CA_REQUIRE(!peer.n || (epi != EPI_F32 && !q_out && !swiglu), "tc_linear: peer output is a plain bf16 epilogue (no SwiGLU, no FP4 output)");
   CA_REQUIRE(!q_out || (kind != KIND_BF16 && swiglu && sf_out && splits <= 1 && N % 32 == 0 && epi == EPI_BF16),

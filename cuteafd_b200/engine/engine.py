@@ -36,9 +36,13 @@ class StepShape:
     max_q_len: int
     n_logits: int
     attn_splits: int
+    # True when the caller guarantees the regular layout of decode / verify steps: every sequence has max_q_len query rows,
+    # sequence s owns rows [s * max_q_len, (s + 1) * max_q_len), and rows that need logits are listed in ascending order.  Such a
+    # step can be cut into micro-batches at sequence boundaries.
+    uniform: bool = False
 
     def key(self):
-        return (self.T, self.n_seq, self.max_q_len, self.n_logits, self.attn_splits)
+        return (self.T, self.n_seq, self.max_q_len, self.n_logits, self.attn_splits, self.uniform)
 
 
 class Lane:
@@ -239,16 +243,16 @@ class Engine:
         self.launches_per_step += 1
         return L.xq
 
-    def _combine(self, y, rows, wts, shared, L: Lane, T: int, k: int):
+    def _combine(self, y, rows, wts, shared, L: Lane, T: int, k: int, wait=None):
         """Weighted top-k sum + shared expert + residual; when another layer follows, its input norm (and FP4
-        quantisation) rides in the same launch."""
+        quantisation) rides in the same launch.  `wait`: the kernel first waits for the peers that deliver `y`."""
         nxt = self._next_lw
         if nxt is None:
-            ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k)
+            ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, wait=wait)
             return
         fp4 = L.xq.kind in FP4_KINDS
         ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, norm_w=nxt.attn_norm, eps=self.spec.rms_eps, xn=None if fp4 else L.xn,
-                        quant=L.xq if fp4 else None, inv_gs=self._attn_in_gs(nxt) if fp4 else None)
+                        quant=L.xq if fp4 else None, inv_gs=self._attn_in_gs(nxt) if fp4 else None, wait=wait)
         if not fp4:
             self._quant(L.xn, L.xq, T, None)              # FP8 operands: separate quantiser (no-op for bf16)
         self._pre_normed = True
@@ -345,6 +349,19 @@ class Engine:
 
     def forward(self, sh: StepShape):
         """Launch one step on the current stream.  Inputs come from the device meta block."""
+        lane = None
+        for item in self.program(sh):
+            if isinstance(item, Lane):
+                lane = item
+        return lane
+
+    def program(self, sh: StepShape):
+        """The step as a generator of launches.  A rank of a multi-GPU layout yields the peer flags it is about to wait for
+        before it launches the waiting kernel (a scheduler that runs several ranks' programs on one GPU resumes a program
+        only when those flags have been published); the last item yielded is the result lane."""
+        yield self._forward_single(sh)
+
+    def _forward_single(self, sh: StepShape):
         spec, T = self.spec, sh.T
         L = self.lane(T)
         self._ensure_attn_scratch(sh)
@@ -408,6 +425,40 @@ class Engine:
             ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=sh.n_logits, status=self.status)
             ops.argmax_rows(L.logits, L.next_tok, rows=sh.n_logits, status=L.tok_status)
         return L
+
+    def mtp_run(self, depth: int, sh: StepShape, prev_hidden: torch.Tensor, use_graph: bool = True) -> Lane:
+        """`mtp_forward`, replayed from a CUDA graph per (depth, shape) when `use_graph`: the hidden rows are first copied
+        into a buffer of fixed address that the captured step reads."""
+        if not use_graph:
+            return self.mtp_forward(depth, sh, prev_hidden)
+        cap = next(c for c in (16, 64, 256, 1024, 4096, 16384) if sh.T <= c)
+        key = ("mtp", depth, cap)
+        buf = self.graphs.get(key)
+        if buf is None:
+            buf = self.graphs[key] = torch.zeros(cap, self.spec.hidden, dtype=torch.bfloat16, device=self.device)
+        buf[:sh.T].copy_(prev_hidden[:sh.T])
+        gkey = ("mtp", depth) + sh.key()
+        g = self.graphs.get(gkey)
+        hook = getattr(self, "on_mtp_step", None)
+        if g is None:
+            lane = self.mtp_forward(depth, sh, buf)          # warm-up outside capture (announces itself on multi-rank runs)
+            torch.cuda.synchronize()
+            self.on_mtp_step = None                          # the capture launches nothing: nobody must be told
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    lane = self.mtp_forward(depth, sh, buf)
+            finally:
+                if hook is not None:
+                    self.on_mtp_step = hook
+                else:
+                    del self.on_mtp_step
+            self.graphs[gkey] = g = (graph, lane)
+            self.graph_captures += 1
+        if hook:
+            hook(depth, sh)
+        g[0].replay()
+        return g[1]
 
     # ------------------------------------------------------------------ CUDA graphs
     def attn_splits_for(self, n_seq: int, max_q_len: int, max_kv: int) -> int:

@@ -80,8 +80,8 @@ class BatchGenerator:
         self.last = first
         return first
 
-    def decode_step(self, use_graph: bool = True) -> list[int]:
-        """One greedy token for every live sequence (feeds `self.last`)."""
+    def plan_decode(self) -> StepShape:
+        """Stages the inputs of one greedy decode step (one token per live sequence) and returns its shape."""
         eng, n = self.eng, len(self.seqs)
         tokens, positions, slots, kv_len = [], [], [], []
         for s, t in zip(self.seqs, self.last):
@@ -93,10 +93,42 @@ class BatchGenerator:
         self.h2d_bytes += eng.set_inputs(tokens, positions, slots, list(range(n)), kv_len, list(range(n)), [1] * n,
                                          self._page_rows(self.seqs))
         splits = eng.attn_splits_for(n, 1, max(kv_len))
-        lane = eng.run(StepShape(T=n, n_seq=n, max_q_len=1, n_logits=n, attn_splits=splits), use_graph=use_graph)
-        toks = self._readback(lane, n)
+        return StepShape(T=n, n_seq=n, max_q_len=1, n_logits=n, attn_splits=splits, uniform=True)
+
+    def commit_decode(self, lane) -> list[int]:
+        toks = self._readback(lane, len(self.seqs))
         for s in self.seqs:
             s.length += 1
+        self.last = toks
+        return toks
+
+    def decode_step(self, use_graph: bool = True) -> list[int]:
+        """One greedy token for every live sequence (feeds `self.last`)."""
+        sh = self.plan_decode()
+        return self.commit_decode(self.eng.run(sh, use_graph=use_graph))
+
+    def plan_prefill_all(self, prompts: list[list[int]]) -> StepShape:
+        """Stages ONE step that ingests every prompt whole (short prompts; `prefill` chunks long ones)."""
+        eng = self.eng
+        self.seqs = [SeqKV() for _ in prompts]
+        tokens, positions, slots, logit_rows, kv_len, q_start, q_len = [], [], [], [], [], [], []
+        for s, p in zip(self.seqs, prompts):
+            s.ensure(self.pool, len(p) + 1)
+            q_start.append(len(tokens))
+            tokens += p
+            positions += list(range(len(p)))
+            slots += [s.slot(i) for i in range(len(p))]
+            kv_len.append(len(p))
+            q_len.append(len(p))
+            logit_rows.append(len(tokens) - 1)
+        self._prompt_lens = [len(p) for p in prompts]
+        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, self._page_rows(self.seqs))
+        return StepShape(T=len(tokens), n_seq=len(prompts), max_q_len=max(q_len), n_logits=len(logit_rows), attn_splits=1)
+
+    def commit_prefill_all(self, lane) -> list[int]:
+        toks = self._readback(lane, len(self.seqs))
+        for s, n in zip(self.seqs, self._prompt_lens):
+            s.length = n
         self.last = toks
         return toks
 

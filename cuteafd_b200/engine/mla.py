@@ -58,7 +58,7 @@ def mla_weights_from_masters(spec: ModelSpec, masters: dict, device, act_gs: flo
     f32 = lambda t: t.float().to(device).contiguous()
     dw = DeviceWeights(spec=spec, embed=masters["embed"].to(torch.bfloat16).to(device).contiguous(), final_norm=f32(masters["final_norm"]),
                        lm_head=TcWeight.from_master(masters["lm_head"], "bf16", device), act_gs=act_gs)
-    for lw in masters["layers"]:
+    def layer_from(lw: dict) -> LayerWeights:
         out = LayerWeights(attn_norm=f32(lw["attn_norm"]), ffn_norm=f32(lw["ffn_norm"]), wqkv=None,
                            wo=TcWeight.from_master(lw["wo"], dk, device, act_gs))
         out.mla = _mla_from_masters(spec, lw, device, dk, act_gs)
@@ -66,13 +66,19 @@ def mla_weights_from_masters(spec: ModelSpec, masters: dict, device, act_gs: flo
             out.router = TcWeight.from_master(lw["router"], "bf16", device)
             if "router_bias" in lw:
                 out.router_bias = f32(lw["router_bias"])
-            out.w_gate, out.w_up, out.w_down = (TcWeight.from_master(lw[k], ek, device, act_gs) for k in ("w_gate", "w_up", "w_down"))
+            if "w_gate" in lw:
+                out.w_gate, out.w_up, out.w_down = (TcWeight.from_master(lw[k], ek, device, act_gs) for k in ("w_gate", "w_up", "w_down"))
             if "ws_gate" in lw:
                 out.ws_gate, out.ws_up, out.ws_down = (TcWeight.from_master(lw[k], dk, device, act_gs) for k in ("ws_gate", "ws_up", "ws_down"))
         else:
             out.ws_gate, out.ws_up, out.ws_down = (TcWeight.from_master(lw[k], dk, device, act_gs) for k in ("wd_gate", "wd_up", "wd_down"))
-        dw.layers.append(out)
+        return out
+
+    dw.layers = [layer_from(lw) for lw in masters["layers"]]
     dw.layer_map = list(range(spec.n_layers))
+    for mw in masters.get("mtp", []):
+        dw.mtp.append((f32(mw["enorm"]), f32(mw["hnorm"]), TcWeight.from_master(mw["eh_proj"], "bf16", device), layer_from(mw["layer"]),
+                       f32(mw["norm"])))
     return dw
 
 
@@ -117,6 +123,10 @@ def mla_weights_random(spec: ModelSpec, device, *, heads_local: int | None = Non
     n_sets = n_moe if distinct_moe_layers <= 0 else min(distinct_moe_layers, n_moe)
     dw.layers = [make(i) for i in range(n_dense)] + [make(n_dense + j) for j in range(n_sets)]
     dw.layer_map = list(range(n_dense)) + [n_dense + (j % n_sets) for j in range(n_moe)]
+    for d in range(spec.mtp_layers):        # native next-token draft modules: one full MoE layer each plus the merge projection
+        i = spec.n_layers + d
+        dw.mtp.append((ones(h), ones(h), TcWeight.random(1, h, 2 * h, "bf16", device, spec.init_std, act_gs, seed * 1000 + i * 32 + 20),
+                       make(max(i, n_dense)), ones(h)))
     return dw
 
 
@@ -134,7 +144,7 @@ class MlaEngine(Engine):
         self.mla_bufs: dict = {}
 
     def _mla_buf(self, L: Lane):
-        if L.cap not in self.mla_bufs:
+        if getattr(L, "mla_buf", None) is None:
             a, dev, Hl, cap = self.spec.attn, self.device, self.heads_local, L.cap
             bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
             i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
@@ -145,8 +155,8 @@ class MlaEngine(Engine):
                              else ActBuffer.wrap_bf16(b["q_an"], L.tn))
             b["o_tok_act"] = (ActBuffer.alloc(self.dense_kind, cap, Hl * a.v_head_dim, L.tn, dev) if self.dense_kind != KIND_BF16
                               else ActBuffer.wrap_bf16(b["o_tok"], L.tn))
-            self.mla_bufs[L.cap] = b
-        return self.mla_bufs[L.cap]
+            L.mla_buf = b           # per lane object: micro-batch lanes of the same capacity keep separate buffers
+        return L.mla_buf
 
     def _head_tiles(self, b, T: int, tn: int):
         """Tile table for the per-head grouped GEMMs over head-major buffers laid out [Hl, T, .]."""

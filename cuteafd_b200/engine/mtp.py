@@ -38,13 +38,14 @@ class _Seq:
 
 
 class MtpSpeculator:
-    def __init__(self, engine: Engine, pool: PagePool | None = None, n_draft: int = 3, depth: int = 0):
+    def __init__(self, engine: Engine, pool: PagePool | None = None, n_draft: int = 3, depth: int = 0, use_graph: bool = False):
         if not engine.weights.mtp:
             raise ValueError("this model has no MTP module")
         self.eng, self.pool, self.n_draft, self.depth = engine, pool or PagePool(engine.n_pages), n_draft, depth
         self.seqs: list[_Seq] = []
         self.rounds = 0
         self._host = None
+        self.use_graph = use_graph       # replay draft and verify steps from CUDA graphs (steady-state serving / benchmarks)
 
     # ------------------------------------------------------------------ helpers
     def _read(self, dev_tokens: torch.Tensor, n: int) -> list[int]:
@@ -73,7 +74,7 @@ class MtpSpeculator:
         mq = max(q_len)
         sh = StepShape(T=T, n_seq=len(live), max_q_len=mq, n_logits=len(live) if want_logits else 0,
                        attn_splits=eng.attn_splits_for(len(live), mq, max(kv_len)))
-        lane = eng.mtp_forward(self.depth, sh, prev)
+        lane = eng.mtp_run(self.depth, sh, prev, self.use_graph)
         last = torch.tensor(logit_rows, device=lane.x.device)
         h_out = lane.x[:T].index_select(0, last).clone()
         toks = self._read(lane.next_tok, len(live)) if want_logits else [0] * len(live)
@@ -122,8 +123,9 @@ class MtpSpeculator:
             q_len.append(len(inputs))
         T = len(tokens)
         eng.set_inputs(tokens, positions, slots, list(range(T)), kv_len, q_start, q_len, [s.kv.pages for s in self.seqs])
-        sh = StepShape(T=T, n_seq=len(self.seqs), max_q_len=nd + 1, n_logits=T, attn_splits=eng.attn_splits_for(len(self.seqs), nd + 1, max(kv_len)))
-        lane = eng.run(sh, use_graph=False)
+        sh = StepShape(T=T, n_seq=len(self.seqs), max_q_len=nd + 1, n_logits=T, attn_splits=eng.attn_splits_for(len(self.seqs), nd + 1, max(kv_len)),
+                       uniform=True)
+        lane = eng.run(sh, use_graph=self.use_graph)
         target = self._read(lane.next_tok, T)
         vh = lane.x[:T].clone()
         for i, (s, dr) in enumerate(zip(self.seqs, drafts)):

@@ -98,9 +98,10 @@ class DeviceWeights:
                 out.router = TcWeight.from_master(lw["router"], "bf16", device)
                 if "router_bias" in lw:
                     out.router_bias = f32(lw["router_bias"])
-                out.w_gate = TcWeight.from_master(lw["w_gate"], ek, device, act_gs)
-                out.w_up = TcWeight.from_master(lw["w_up"], ek, device, act_gs)
-                out.w_down = TcWeight.from_master(lw["w_down"], ek, device, act_gs)
+                if "w_gate" in lw:      # an attention rank of a split layout holds no routed experts
+                    out.w_gate = TcWeight.from_master(lw["w_gate"], ek, device, act_gs)
+                    out.w_up = TcWeight.from_master(lw["w_up"], ek, device, act_gs)
+                    out.w_down = TcWeight.from_master(lw["w_down"], ek, device, act_gs)
                 if "ws_gate" in lw:
                     out.ws_gate = TcWeight.from_master(lw["ws_gate"], dk, device, act_gs)
                     out.ws_up = TcWeight.from_master(lw["ws_up"], dk, device, act_gs)

@@ -250,18 +250,24 @@ def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor | None, *, rows: int | 
     if splits > 1:
         n_items = -(-rows // x.tn)
         ws, cnt = _splitk_scratch(x.data.device, splits * rows * w.N, n_items * (-(-w.N // 128)) * 4)
+    extra = None
     if quant_out is not None:
         if quant_out.kind != w.kind or quant_out.K != w.N:
             raise ValueError("tc_linear: quant_out must be an FP4 buffer of the operands' kind with K = N")
-        call("cuteafd_tc_linear_fp4_out", ptr(quant_out.data), ptr(quant_out.sf), quant_out.sf.shape[1], ptr(inv_gs_out))
+        extra = native.TcExtra()
+        extra.q_out, extra.sf_out, extra.ldsf_out, extra.inv_gs_out = ptr(quant_out.data), ptr(quant_out.sf), quant_out.sf.shape[1], ptr(inv_gs_out)
     if peer is not None:
         ys, fl = list(peer["y"]), list(peer["flags"])
-        call("cuteafd_tc_linear_peer_out", ys[0], ys[1] if len(ys) > 1 else None, len(ys), peer["ld"], ptr(peer.get("row_map")),
-             fl[0], fl[1] if len(fl) > 1 else None, ptr(peer["ctl"]), ptr(peer["done"]))
+        extra = extra or native.TcExtra()
+        extra.n_peer, extra.peer_ld = len(ys), peer["ld"]
+        for i in range(len(ys)):
+            extra.peer_y[i], extra.peer_flag[i] = ys[i], fl[i]
+        extra.peer_row_map, extra.peer_ctl, extra.peer_done = ptr(peer.get("row_map")), ptr(peer["ctl"]), ptr(peer["done"])
     call("cuteafd_tc_linear", w.kind, 1 if w_up is not None else 0, x.tn, ptr(w.tmap), ptr(w_up.tmap) if w_up else None,
          ptr(x.tmap), ptr(w.sf_ptrs), ptr(w_up.sf_ptrs) if w_up else None, ptr(x.sf), x.sf.shape[1] if x.sf is not None else 0,
          ptr(w.alpha), ptr(w_up.alpha) if w_up else None, ptr(tiles), ptr(n_tiles), max_tiles, ptr(y), ptr(residual),
-         y.stride(0) if y is not None else 0, rows, w.N, w.K, epi, splits, ptr(ws), ptr(cnt), ptr(status), max_ctas, stream())
+         y.stride(0) if y is not None else 0, rows, w.N, w.K, epi, splits, ptr(ws), ptr(cnt), ptr(status), max_ctas,
+         ctypes.byref(extra) if extra is not None else None, stream())
     return y
 
 
@@ -409,21 +415,46 @@ def router_select_pack(logits, bias, idx, wts, T, k, scoring, normalize, route_s
          ptr(tiles), ptr(n_tiles), ptr(n_rows), e_lo, e_hi, tn, max_tiles, ptr(src_route), ptr(_TICKETS[dev]), stream())
 
 
-def route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route=None):
+def route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route=None, *,
+               wait=None, lane_T=None, t_cap: int = 0):
+    """Packs the routes of `T` tokens into expert order.  `wait` (a `native.FlagWaitArg`) makes the kernel wait for the peers
+    that deliver the routing table; `lane_T` (int32 device tensor, one count per lane) + `t_cap` describe a table of several
+    senders laid out [lane][t_cap][k] (T = lanes * t_cap) whose rows beyond each lane's count are skipped."""
     call("cuteafd_route_pack", ptr(idx), ptr(src_token), ptr(slot_row), ptr(counts), ptr(offsets), ptr(tiles), ptr(n_tiles),
-         ptr(n_rows), T, k, e_lo, e_hi, tn, max_tiles, ptr(src_route), stream())
+         ptr(n_rows), T, k, e_lo, e_hi, tn, max_tiles, ptr(src_route), ctypes.byref(wait) if wait is not None else None,
+         ptr(lane_T), t_cap, stream())
 
 
-def moe_combine(y, slot_row, wts, shared, residual, out, T, k, *, norm_w=None, eps: float = 0.0, xn=None, quant=None, inv_gs=None):
+def route_gather(src_q, src_sf, src_token, n_rows, dst: "ActBuffer", rows_cap: int, status=None):
+    """dst row c = slab row src_token[c] (payload and block scales) for c < n_rows: token-major slab -> expert order."""
+    row_bytes = src_q.shape[-1] * src_q.element_size()
+    sf_bytes = src_sf.shape[-1] if src_sf is not None else 0
+    call("cuteafd_route_gather", ptr(src_q), ptr(src_sf), ptr(src_token), ptr(n_rows), ptr(dst.data), ptr(dst.sf) if src_sf is not None else None,
+         row_bytes, sf_bytes, sf_bytes, dst.sf.shape[1] if src_sf is not None else 0, src_q.numel() * src_q.element_size() // row_bytes,
+         rows_cap, ptr(status), stream())
+    return dst
+
+
+def router_hash_select(logits, tid2eid, tokens, idx, wts, T, k, route_scale: float = 1.0, status=None):
+    """Hash routing: experts of token row t are tid2eid[tokens[t]] ([vocab, k] int32); gate weights are the normalised
+    sqrt-softplus scores of `logits` at those experts times `route_scale`."""
+    _chk(logits, torch.float32, "logits"); _chk(tid2eid, torch.int32, "tid2eid"); _chk(tokens, torch.int32, "tokens")
+    call("cuteafd_router_hash_select", ptr(logits), ptr(tid2eid), ptr(tokens), ptr(idx), ptr(wts), T, logits.shape[1], k, tid2eid.shape[0],
+         route_scale, ptr(status), stream())
+
+
+def moe_combine(y, slot_row, wts, shared, residual, out, T, k, *, norm_w=None, eps: float = 0.0, xn=None, quant=None, inv_gs=None, wait=None):
     """out = residual + shared + sum_slot w * y[slot_row].  With `norm_w` the same launch also applies the next
-    layer's RMSNorm to `out`, written as bf16 (`xn`) and/or FP4 (`quant`, an activation buffer)."""
+    layer's RMSNorm to `out`, written as bf16 (`xn`) and/or FP4 (`quant`, an activation buffer).  `wait` (a
+    `native.FlagWaitArg`): the kernel first waits for the peers that deliver `y`."""
+    w = ctypes.byref(wait) if wait is not None else None
     if norm_w is None:
-        call("cuteafd_moe_combine", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, stream())
+        call("cuteafd_moe_combine", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, w, stream())
         return out
     fp4 = quant is not None and quant.kind in FP4_KINDS
     call("cuteafd_moe_combine_norm", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, ptr(norm_w),
          eps, ptr(xn), ptr(quant.data) if fp4 else None, ptr(quant.sf) if fp4 else None, quant.sf.shape[1] if fp4 else 0,
-         ptr(inv_gs) if fp4 else None, (2 if quant.kind == KIND_MXFP4 else 1) if fp4 else 0, stream())
+         ptr(inv_gs) if fp4 else None, (2 if quant.kind == KIND_MXFP4 else 1) if fp4 else 0, w, stream())
     return out
 
 

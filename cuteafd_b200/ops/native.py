@@ -25,9 +25,6 @@ _PROTOS = {
     "cuteafd_exl3_linear": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "cuteafd_fp8_linear": [I, P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "cuteafd_act_quant_fp8_block128": [P, P, P, I, I, I, P],
-    "cuteafd_tc_linear_peer_out": [P, P, I, I, P, P, P, P, P],
-    "cuteafd_arm_flag_wait": [P, I, I, P, C.c_ulonglong, P],
-    "cuteafd_tc_linear_fp4_out": [P, P, I, P],
     "cuteafd_device_info": [P, P, P, P, P],
     "cuteafd_tmap_encode_kmajor": [P, P, I, U64, U64, U64, U64, U64, C.c_uint32],
     "cuteafd_embed_gather": [P, P, P, I, I, I, P, P],
@@ -44,10 +41,12 @@ _PROTOS = {
     "cuteafd_silu_mul": [P, P, P, L, F, P],
     "cuteafd_router_select": [P, P, P, P, I, I, I, I, I, F, I, I, P],
     "cuteafd_add_rmsnorm_quant": [P, P, P, P, I, I, F, P, P, I, P, I, P],
-    "cuteafd_moe_combine_norm": [P, P, P, P, P, P, I, I, I, P, F, P, P, P, I, P, I, P],
+    "cuteafd_moe_combine_norm": [P, P, P, P, P, P, I, I, I, P, F, P, P, P, I, P, I, P, P],
     "cuteafd_router_select_pack": [P, P, P, P, I, I, I, I, I, F, I, I, P, P, P, P, P, P, P, I, I, I, I, P, P, P],
-    "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P],
-    "cuteafd_moe_combine": [P, P, P, P, P, P, I, I, I, P],
+    "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, P],
+    "cuteafd_route_gather": [P, P, P, P, P, P, I, I, I, I, I, I, P, P],
+    "cuteafd_router_hash_select": [P, P, P, P, P, I, I, I, I, F, P, P],
+    "cuteafd_moe_combine": [P, P, P, P, P, P, I, I, I, P, P],
     "cuteafd_paged_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
     "cuteafd_paged_attention_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P, P, I, P, I, P],
     "cuteafd_tmap_encode_kv": [P, P, I, U64],
@@ -68,12 +67,30 @@ _PROTOS = {
     "cuteafd_wait_add": [P, P, P, P, C.c_size_t, I, P, P, C.c_uint, C.c_ulonglong, P, P],
     "cuteafd_dispatch_push": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
     "cuteafd_combine_push": [P, P, P, P, P, P, P, I, I, I, C.c_uint, P],
-    "cuteafd_tc_linear": [I, I, I, P, P, P, P, P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, I, P],
+    "cuteafd_dispatch_tok_push": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
+    "cuteafd_combine_push_lanes": [P, P, P, P, P, P, P, I, I, I, I, I, I, C.c_uint, P, P],
+    "cuteafd_tc_linear": [I, I, I, P, P, P, P, P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, I, P, P],
 }
 
 
 class NativeError(RuntimeError):
     pass
+
+
+class FlagWaitArg(C.Structure):
+    """In-kernel wait handed to a consumer of peer data (`CaFlagWaitArg` of the C ABI): the kernel polls `n` flags,
+    `stride` words apart, until each reaches the step number in ctl[1]; a wait that runs out sets `status` and ctl[0]."""
+    _fields_ = [("flags", P), ("ctl", P), ("status", P), ("timeout_ns", C.c_ulonglong), ("n", I), ("stride", I)]
+
+
+class TcExtra(C.Structure):
+    """Optional outputs of `cuteafd_tc_linear` (`CaTcExtra` of the C ABI)."""
+    _fields_ = [("q_out", P), ("sf_out", P), ("inv_gs_out", P), ("ldsf_out", I), ("n_peer", I), ("peer_y", P * 2), ("peer_flag", P * 2),
+                ("peer_row_map", P), ("peer_ctl", P), ("peer_done", P), ("peer_ld", I), ("reserved", I)]
+
+
+def flag_wait(flags_ptr: int, n: int, stride: int, ctl: torch.Tensor, status: torch.Tensor | None, timeout_ns: int = 2_000_000_000) -> FlagWaitArg:
+    return FlagWaitArg(flags_ptr, ctl.data_ptr(), status.data_ptr() if status is not None else None, timeout_ns, n, stride)
 
 
 def available() -> bool:

@@ -1,75 +1,97 @@
-"""Multi-rank driver for the attention/expert split: process groups, the control channel that tells expert ranks
-which step to run, and the distributed decode benchmark.
+"""Multi-rank driver for the attention/expert layouts: roles, the step mailbox that tells expert ranks what to run, and the
+distributed decode benchmark.
 
-Control protocol (CPU, gloo): before every step that really executes, attention rank 0 broadcasts (op, T).
-Expert ranks sit in `serve_loop`, run one step of T token rows per message (eagerly the first time a size is
-seen, from a captured CUDA graph afterwards) and leave on OP_STOP.  The data path itself never touches the host:
-rows, routing tables and flags move through peer memory.  (Reference: worker selection + per-wave requests,
-cuteafd-transport/src/worker_selection.rs, expert.rs:201-376; here the "request" shrinks to two integers.)
+Split layouts (disjoint attention / expert ranks): before every step that really executes, the attention leader posts
+(op, argument) into a shared-memory mailbox (`parallel.mailbox`); expert ranks sit in `serve_loop`, replay their captured
+step graph per message (the step's shape travels on the device: each lane's token count is written next to its rows, so ONE
+graph serves every step size) and leave on OP_STOP.  Colocated layout: every rank runs its own experts inside its own step,
+there is nobody to tell.  The data path never touches the host: rows, routing tables and flags move through peer memory.
+(Reference: worker selection + per-wave requests, cuteafd-transport/src/worker_selection.rs, expert.rs:201-376; here the
+"request" shrinks to two integers in shared memory.)
 """
 from __future__ import annotations
 
+import os
 import time
 
 import torch
 import torch.distributed as dist
 
-from ..config import ModelSpec, default_deployment
+from ..config import ModelSpec, deployment_by_name
 from ..engine.engine import PAGE, StepShape
 from ..engine.generate import BatchGenerator
 from ..engine.kv import PagePool, SeqKV
 from ..ops import KIND_BY_NAME
-from .afd import AttnRankEngine, ExpertRankWorker, MlaAttnRankEngine, capture_expert_graph, make_block
+from .afd import AttnRankEngine, ExpertRankWorker, LanePlan, MlaAttnRankEngine, capture_expert_graph, make_block
+from .mailbox import Mailbox
 
-OP_STOP, OP_STEP, OP_TIMER_START, OP_TIMER_STOP = 0, 1, 2, 3
+OP_STOP, OP_STEP, OP_TIMER_START, OP_TIMER_STOP, OP_MTP = 0, 1, 2, 3, 4
 
 
 class AfdRunner:
-    def __init__(self, spec: ModelSpec, rank: int, world: int, local: int, *, t_max: int, n_pages: int, max_seqs: int,
-                 max_pages_per_seq: int, comm: str = "p2p", seed: int = 1, attn_groups: int = 1):
+    def __init__(self, spec: ModelSpec, rank: int, world: int, local: int, *, t_cap: int, n_pages: int, max_seqs: int,
+                 max_pages_per_seq: int, comm: str = "p2p", seed: int = 1, layout: str = "split", attn_groups: int = 1, n_micro: int = 1,
+                 merged: bool | None = None, masters: dict | None = None):
         self.spec, self.rank, self.world = spec, rank, world
         self.dev = torch.device("cuda", local)
-        self.dep = default_deployment(world, attn_groups)
+        self.dep = dep = deployment_by_name(layout, world, attn_groups)
+        if comm == "nccl" and (dep.colocated or n_micro > 1):
+            raise ValueError("the NCCL-only baseline runs the split layout with one micro-batch")
+        self.plan = LanePlan(dep, t_cap=t_cap, n_micro=n_micro, merged=dep.colocated if merged is None else merged)
         self.comm = comm
-        self.ctrl = dist.new_group(backend="gloo")
-        self.tp_group = dist.new_group(list(self.dep.attn_ranks))
-        self.is_attn = rank in self.dep.attn_ranks
-        self.root = self.dep.attn_ranks[0]
+        self.tp_group = dist.new_group(list(dep.attn_ranks)) if comm == "nccl" else None
+        self.is_attn, self.is_expert = rank in dep.attn_ranks, rank in dep.expert_ranks
+        self.root = dep.attn_ranks[0]
         kind = KIND_BY_NAME[spec.quant.experts]
-        self.block = make_block(spec, self.dep, t_max, kind, rank, self.dev, None) if comm == "p2p" else None
+        self.block = make_block(spec, self.plan, kind, rank, self.dev, None) if comm == "p2p" else None
+        # step mailbox (split layouts only)
+        self.mail = None
+        if not dep.colocated:
+            name = [f"cuteafd_{os.getpid()}_{int(time.time() * 1e3) & 0xFFFFFF}" if rank == self.root else None]
+            dist.broadcast_object_list(name, src=self.root)
+            if rank == self.root:
+                self.mail = Mailbox(name[0], create=True)
+            dist.barrier()
+            if rank != self.root and self.is_expert:
+                self.mail = Mailbox(name[0], create=False)
         self.engine = self.worker = None
         if self.is_attn:
             cls = MlaAttnRankEngine if spec.attn.kind == "mla" else AttnRankEngine
-            self.engine = cls(spec, self.dep, rank, self.dev, t_max=t_max, n_pages=n_pages, max_seqs=max_seqs,
-                                         max_pages_per_seq=max_pages_per_seq, comm=comm, block=self.block, expert_kind=kind, seed=seed)
+            self.engine = cls(spec, self.plan, rank, self.dev, n_pages=n_pages, max_seqs=max_seqs, max_pages_per_seq=max_pages_per_seq, comm=comm,
+                              block=self.block, expert_kind=kind, seed=seed, masters=masters)
             self.engine.tp_group = self.tp_group
-            self.engine.on_real_step = self._announce
-        else:
-            self.worker = ExpertRankWorker(spec, self.dep, rank, self.dev, t_max=t_max, comm=comm, block=self.block, seed=seed)
+            if not dep.colocated:
+                self.engine.on_real_step = self._announce
+                self.engine.on_mtp_step = self._announce_mtp
+        if self.is_expert:
+            self.worker = ExpertRankWorker(spec, self.plan, rank, self.dev, comm=comm, block=self.block, seed=seed, masters=masters)
+            if dep.colocated:
+                self.engine.local_worker = self.worker
         self.graphs: dict = {}
         self.timer_ms = 0.0
         dist.barrier()
 
-    # ---- control channel
-    def _send(self, op: int, T: int = 0):
-        msg = torch.tensor([op, T], dtype=torch.int64)
-        dist.broadcast(msg, src=self.root, group=self.ctrl)
-        return msg
+    # ---- control channel (split layouts)
+    def _post(self, op: int, a: int = 0, b: int = 0):
+        if self.mail is not None and self.rank == self.root:
+            self.mail.post(op, a, b)
 
     def _announce(self, sh: StepShape):
-        self._send(OP_STEP, sh.T)
+        self._post(OP_STEP, sh.T)
+
+    def _announce_mtp(self, depth: int, sh: StepShape):
+        self._post(OP_MTP, sh.T, depth)
 
     def control(self, op: int):
-        """Attention ranks: forward a timer/stop op to the expert ranks (all attention ranks must call it)."""
-        self._send(op)
+        """Attention leader: forward a timer / stop op to the expert ranks (a no-op on other ranks and in the colocated layout)."""
+        self._post(op)
 
-    def serve_loop(self):
-        """Expert ranks: run steps until told to stop.  Returns device milliseconds between the timer marks."""
+    def serve_loop(self, timeout_s: float = 600.0):
+        """Expert ranks of a split layout: run steps until told to stop.  Returns device milliseconds between the timer marks."""
         w = self.worker
         ev0 = ev1 = None
         while True:
-            msg = self._send(0)
-            op, T = int(msg[0]), int(msg[1])
+            op, a, b, _ = self.mail.read(timeout_s)
             if op == OP_STOP:
                 break
             if op == OP_TIMER_START:
@@ -83,78 +105,128 @@ class AfdRunner:
                 torch.cuda.synchronize()
                 self.timer_ms = ev0.elapsed_time(ev1)
                 continue
+            layers = None if op == OP_STEP else [self.spec.n_layers + b]
             if self.comm != "p2p":
-                w.step(T)
-            elif T not in self.graphs:
-                w.step(T)                                   # first step of this size: eager, then capture for later
+                w.step_nccl(a, layers)
+                continue
+            key = "main" if op == OP_STEP else ("mtp", b)
+            if key not in self.graphs:
+                w.step(layers)                              # first step of this kind: eager, then captured for later
                 torch.cuda.synchronize()
-                self.graphs[T] = capture_expert_graph(w, T)
+                self.graphs[key] = capture_expert_graph(w, layers)
             else:
-                self.graphs[T].replay()
+                self.graphs[key].replay()
         torch.cuda.synchronize()
         return self.timer_ms
 
     def check(self):
-        st = self.engine.status if self.engine is not None else self.worker.status
-        word = int(st[0])
-        if word:
-            from ..ops.native import decode_status
-            raise RuntimeError(f"rank {self.rank}: device status {decode_status(word)}")
+        from ..ops.native import decode_status
+        for who in (self.engine, self.worker):
+            if who is not None and int(who.status[0]):
+                raise RuntimeError(f"rank {self.rank}: device status {decode_status(int(who.status[0]))}")
 
     def close(self):
         if self.block is not None:
             self.block.close()
+        if self.mail is not None:
+            self.mail.close()
+
+
+def default_layout(spec: ModelSpec, world: int, comm: str) -> dict:
+    """Layout a benchmark or a server uses when none is named.  GQA models whose weights fit every GPU several times over run
+    colocated (data-parallel attention + expert-parallel FFN on every GPU: nothing idles, every expert's weights stream once
+    per layer for the whole batch); MLA models keep the named split, attention TP2 + experts on the other GPUs, with two
+    micro-batches in flight so the expert round trip hides behind the other micro-batch's attention."""
+    if comm == "nccl":
+        return {"layout": "split", "attn_groups": 1, "n_micro": 1}
+    if spec.attn.kind == "mla":
+        return {"layout": "split", "attn_groups": 1, "n_micro": 2 if world >= 4 else 1}
+    return {"layout": "colocated", "attn_groups": world, "n_micro": 1}
 
 
 def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, local: int, clocks) -> dict:
     comm = getattr(args, "comm", "p2p")
+    lay = default_layout(spec, world, comm)
+    if getattr(args, "layout", None):
+        lay["layout"] = args.layout
+        if args.layout == "split":
+            lay["attn_groups"] = 1
+    if getattr(args, "attn_groups", 0) and lay["layout"] == "split":
+        lay["attn_groups"] = args.attn_groups
+    if getattr(args, "n_micro", 0):
+        lay["n_micro"] = args.n_micro
+    dep = deployment_by_name(lay["layout"], world, lay["attn_groups"])
+    groups = dep.attn_groups
     batch_total = getattr(args, "batch_total", 0) or args.batch_per_gpu * world
-    # Data-parallel attention groups: by default two once there are four GPUs (GQA models over the peer-memory path);
-    # MLA configs keep the single TP2 group their published layout names.
-    groups = getattr(args, "attn_groups", 0) or (2 if (world >= 4 and comm == "p2p" and spec.attn.kind == "gqa" and batch_total % 2 == 0) else 1)
-    if batch_total % groups:
-        raise SystemExit(f"batch {batch_total} does not split over {groups} attention groups")
-    batch = batch_total // groups                     # sequences served by each attention group
+    if batch_total < groups:
+        groups_used = batch_total            # fewer sequences than groups (batch 1): the other groups idle
+    else:
+        groups_used = groups
+    base, extra = divmod(batch_total, groups_used)
     ctx_pages = -(-(args.context + 4 * (args.steps + args.warmup) + 64) // PAGE)
-    pages = batch * (ctx_pages + 1) + 2
+    my_group = dep.group_of(rank) if rank in dep.attn_ranks else -1
+    batch = (base + (1 if my_group < extra else 0)) if 0 <= my_group < groups_used else 0
+    max_batch = base + (1 if extra else 0)
+    pages = max(batch, 1) * (ctx_pages + 1) + 2
+    t_cap = max(16, -(-max_batch // lay["n_micro"]))
     t0 = time.time()
-    run = AfdRunner(spec, rank, world, local, t_max=max(16, batch), n_pages=pages, max_seqs=batch, max_pages_per_seq=ctx_pages + 1, comm=comm,
-                    attn_groups=groups)
+    run = AfdRunner(spec, rank, world, local, t_cap=t_cap, n_pages=pages, max_seqs=max(max_batch, 1), max_pages_per_seq=ctx_pages + 1, comm=comm,
+                    layout=lay["layout"], attn_groups=lay["attn_groups"], n_micro=lay["n_micro"])
     use_graph = comm == "p2p"
     res = None
+    dev_ms, setup_s, e2e_s, clk, launches, h2d, d2h = 0.0, 0.0, 0.0, None, 0, 0, 0
     if run.is_attn:
         eng = run.engine
         gen = BatchGenerator(eng, PagePool(pages))
-        g = torch.Generator(device=eng.device).manual_seed(0)
+        g = torch.Generator(device=eng.device).manual_seed(rank)
         gen.seqs = []
         for _ in range(batch):
             s = SeqKV(); s.ensure(gen.pool, args.context + 1); s.length = args.context
             gen.seqs.append(s)
         for li in range(eng.kv.shape[0]):
             eng.kv[li].normal_(0, 1, generator=g)
-        gen.last = torch.randint(0, spec.vocab, (batch,), generator=torch.Generator().manual_seed(0)).tolist()
+        gen.last = torch.randint(0, spec.vocab, (max(batch, 1),), generator=torch.Generator().manual_seed(my_group)).tolist()[:batch]
         torch.cuda.synchronize()
         setup_s = time.time() - t0
+        idle = StepShape(0, 0, 1, 0, 1)
+        # colocated ranks line up on the host before each phase; in a split layout the expert ranks are already serving (they
+        # cannot join a host barrier) and the attention ranks meet through them every layer anyway
+        sync = dist.barrier if dep.colocated else (lambda: None)
+
+        def e2e_step():
+            if batch:
+                gen.decode_step(use_graph)
+            else:
+                eng._ensure_meta(16)
+                eng.run(idle, use_graph)
         # end-to-end arm
+        sync()
         for _ in range(args.warmup):
-            gen.decode_step(use_graph)
+            e2e_step()
         torch.cuda.synchronize()
+        sync()
         gen.h2d_bytes = gen.d2h_bytes = 0
         t1 = time.perf_counter()
         for _ in range(args.steps):
-            gen.decode_step(use_graph)
+            e2e_step()
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t1
         # device arm
-        kv_len = [s.length + 1 for s in gen.seqs]
-        sh = StepShape(T=batch, n_seq=batch, max_q_len=1, n_logits=batch, attn_splits=eng.attn_splits_for(batch, 1, max(kv_len)))
+        if batch:
+            kv_len = [s.length + 1 for s in gen.seqs]
+            sh = StepShape(T=batch, n_seq=batch, max_q_len=1, n_logits=batch, attn_splits=eng.attn_splits_for(batch, 1, max(kv_len)), uniform=True)
+        else:
+            sh = idle
         for _ in range(args.warmup):
             eng.run(sh, use_graph)
         torch.cuda.synchronize()
+        sync()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        clocks.start()
+        if rank == 0:
+            clocks.start()
         time.sleep(0.2)
         torch.cuda.synchronize()
+        sync()
         run.control(OP_TIMER_START)          # expert ranks start their own device timers right before the first timed step
         ev0.record()
         for _ in range(args.steps):
@@ -163,35 +235,35 @@ def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, l
         torch.cuda.synchronize()
         dev_ms = ev0.elapsed_time(ev1)
         run.control(OP_TIMER_STOP)
-        clk = clocks.stop()
+        if rank == 0:
+            clk = clocks.stop()
         run.control(OP_STOP)
         run.check()
-        launches = eng.launches_per_step
+        launches = eng.launches_per_step + (run.worker.launches_per_step if run.worker is not None else 0)
         h2d, d2h = gen.h2d_bytes // args.steps, gen.d2h_bytes // args.steps
     else:
         dev_ms = run.serve_loop()
         run.check()
-        setup_s, e2e_s, clk, launches, h2d, d2h = 0.0, 0.0, None, run.worker.launches_per_step, 0, 0
-    # max over ranks of the device time; launches summed over ranks
-    t = torch.tensor([dev_ms, float(launches)], dtype=torch.float64, device=run.dev)
+        launches = run.worker.launches_per_step
+    # max over ranks of the device and wall times; launches and copied bytes summed over ranks
+    t = torch.tensor([dev_ms, e2e_s, float(launches), float(h2d), float(d2h)], dtype=torch.float64, device=run.dev)
     tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
     tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
     if rank == 0:
-        ms = float(tmax[0])
-        dep = run.dep
+        ms, e2e = float(tmax[0]), float(tmax[1])
         res = {
             "metric": "decode_tokens_per_s", "value": round(batch_total * args.steps / (ms / 1e3), 2), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
             "higher_is_better": True, "scaling": "weak" if not getattr(args, "batch_total", 0) else "strong", "vs_baseline": None,
-            "dtype": f"bf16 activations, {spec.quant.experts} experts / {spec.quant.dense} dense (dense runs as bf16 when the format has no kernel yet)",
+            "dtype": f"bf16 activations, {spec.quant.experts} experts / {spec.quant.dense} dense",
             "data": "synthetic token ids, random-init weights, context KV random-filled",
             "config": {"model": spec.name + (f" (DEBUG {args.layers} layers: INVALID)" if args.layers else ""), "global_batch": batch_total,
-                       "seq_len": args.context, "parallelism": f"afd {dep.describe()} ({comm})", "layers": spec.n_layers,
+                       "seq_len": args.context, "parallelism": f"{dep.describe()}, {lay['n_micro']} micro-batch(es) ({comm})", "layers": spec.n_layers,
                        "l2": "inputs (weights + KV) far larger than L2; no flush needed", "setup_s": round(setup_s, 1)},
             "clocks": clk,
-            "e2e": {"value": round(batch_total * args.steps / e2e_s, 2), "unit": "tokens/s", "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(float(tsum[1])) * args.steps,
+            "e2e": {"value": round(batch_total * args.steps / e2e, 2), "unit": "tokens/s", "ms_per_step": round(e2e * 1e3 / args.steps, 4),
+                    "h2d_bytes_per_step": int(float(tsum[3])), "d2h_bytes_per_step": int(float(tsum[4]))},
+            "gpu_launches": int(float(tsum[2])) * args.steps,
         }
     run.close()
     return res

@@ -34,15 +34,15 @@ def test_groups_need_an_expert_rank():
 
 def test_dispatch_flag_slots_are_distinct_per_group_and_tp_rank():
     from cuteafd_b200.config import tiny_spec
-    from cuteafd_b200.parallel.afd import PH_COMBINE, PH_DISPATCH, PH_TP, flag_offset
-    spec = tiny_spec()
+    from cuteafd_b200.parallel.afd import NFLAG, PH_COMBINE, PH_DISPATCH, PH_TP, flag_offset, n_flag_layers
+    spec = tiny_spec().replace(mtp_layers=1)
     d = default_deployment(8, 2)
     offs = set()
     for ph in (PH_DISPATCH, PH_COMBINE, PH_TP):
-        for layer in range(spec.n_layers):
-            for src in range(8):
+        for layer in range(n_flag_layers(spec)):            # the MTP draft layer has its own words
+            for src in range(NFLAG):
                 offs.add(flag_offset(spec, ph, layer, src))
-    assert len(offs) == 3 * spec.n_layers * 8 and max(offs) < 3 * spec.n_layers * 8 * 4
+    assert len(offs) == 3 * n_flag_layers(spec) * NFLAG and max(offs) < 3 * n_flag_layers(spec) * NFLAG * 4
     assert {g * d.tp + t for g in range(d.attn_groups) for t in range(d.tp)} == {0, 1, 2, 3}
 
 
@@ -60,39 +60,54 @@ def test_plan_deployment_decisions_for_two_attention_groups():
 
 
 def test_flag_words_of_every_layout_are_disjoint_and_pair_up():
-    """Host-side fixture of the peer-flag protocol: for every layout the benchmark uses, each (phase, layer, publisher)
+    """Host-side fixture of the peer-flag protocol: for every layout and micro-batch count, each (phase, layer, publisher)
     has its own flag word inside the flags region, and every waiter's range covers exactly its publishers."""
-    from cuteafd_b200.config import default_deployment, tiny_spec
-    from cuteafd_b200.parallel.afd import PH_COMBINE, PH_DISPATCH, PH_TP, flag_offset
+    from cuteafd_b200.config import colocated_deployment, default_deployment, tiny_spec
+    from cuteafd_b200.parallel.afd import NFLAG, PH_COMBINE, PH_DISPATCH, PH_TP, LanePlan, block_regions, flag_offset
     spec = tiny_spec().replace(n_layers=5)
-    region = 3 * spec.n_layers * 8 * 4
-    for world, groups in ((2, 1), (4, 1), (4, 2), (8, 1), (8, 2), (8, 4)):
-        dep = default_deployment(world, groups)
+    cases = [(default_deployment(w, g), m, mg) for w, g in ((2, 1), (4, 1), (4, 2), (8, 1), (8, 2)) for m in (1, 2) for mg in (False, True)]
+    cases += [(colocated_deployment(w), m, True) for w in (2, 4, 8) for m in (1, 2) if w * m <= 8]
+    for dep, n_micro, merged in cases:
+        plan = LanePlan(dep, t_cap=16, n_micro=n_micro, merged=merged)
+        plan.check()
+        region = block_regions(spec, plan, 1)["flags"]
         for li in range(spec.n_layers):
             seen = {}
-            # dispatch: every attention rank raises its own word on the expert ranks; an expert rank waits, per group, on
-            # `tp` consecutive words starting at the group's first slot
+            # dispatch: attention rank (group g, tp rank t) raises word lane * tp + t on every expert rank for each of its
+            # micro-batch lanes; an expert rank waits on the tp words of one lane, or on all lanes * tp words when merged
             pub = {}
             for r in dep.attn_ranks:
                 g = dep.group_of(r)
-                src = g * dep.tp + list(dep.group_ranks(g)).index(r)
-                off = flag_offset(spec, PH_DISPATCH, li, src)
-                assert off not in seen and 0 <= off < region and off % 4 == 0
-                seen[off] = ("dispatch", r)
-                pub.setdefault(g, set()).add(off)
-            for g in range(dep.attn_groups):
-                first = flag_offset(spec, PH_DISPATCH, li, g * dep.tp)
-                assert {first + 4 * i for i in range(dep.tp)} == pub[g]
-            # combine: every expert rank raises word `ep_rank` on the attention ranks, which wait on `ep` consecutive words
-            for i, r in enumerate(dep.expert_ranks):
-                off = flag_offset(spec, PH_COMBINE, li, i)
-                assert off not in seen and off < region
-                seen[off] = ("combine", r)
-            first = flag_offset(spec, PH_COMBINE, li, 0)
-            assert {first + 4 * i for i in range(dep.ep)} == {o for o, (k, _) in seen.items() if k == "combine"}
-            # tensor-parallel pair: rank t raises word t on its partner and waits on word 1 - t of its own block
-            for t in range(min(2, dep.tp)):
-                off = flag_offset(spec, PH_TP, li, t)
-                assert off not in seen and off < region
-                seen[off] = ("tp", t)
-        assert dep.attn_groups * dep.tp <= 8 and dep.ep <= 8            # the region has eight words per (phase, layer)
+                t = list(dep.group_ranks(g)).index(r)
+                for mb in range(n_micro):
+                    lane = plan.lane(g, mb)
+                    off = flag_offset(spec, PH_DISPATCH, li, lane * dep.tp + t)
+                    assert off not in seen and 0 <= off < region and off % 4 == 0
+                    seen[off] = ("dispatch", r, mb)
+                    pub.setdefault(lane, set()).add(off)
+            runs = [(0, plan.n_lanes)] if merged else [(lane, 1) for lane in range(plan.n_lanes)]
+            covered = set()
+            for lane0, n in runs:
+                first = flag_offset(spec, PH_DISPATCH, li, lane0 * dep.tp)
+                waits = {first + 4 * i for i in range(n * dep.tp)}
+                assert waits == set().union(*(pub[l] for l in range(lane0, lane0 + n)))
+                covered |= waits
+            assert covered == {o for o, v in seen.items() if v[0] == "dispatch"}
+            # combine: expert rank e raises word mb * 8 + e on the attention ranks of a lane; micro-batch mb of an attention
+            # rank waits on `ep` consecutive words starting at mb * 8
+            for mb in range(n_micro):
+                words = set()
+                for e in range(dep.ep):
+                    off = flag_offset(spec, PH_COMBINE, li, mb * 8 + e)
+                    assert off not in seen and off < region
+                    seen[off] = ("combine", e, mb)
+                    words.add(off)
+                first = flag_offset(spec, PH_COMBINE, li, mb * 8)
+                assert {first + 4 * i for i in range(dep.ep)} == words
+            # tensor-parallel pair: rank t raises word mb * 2 + t on its partner and waits on word mb * 2 + (1 - t) of its own block
+            for mb in range(n_micro):
+                for t in range(min(2, dep.tp)):
+                    off = flag_offset(spec, PH_TP, li, mb * 2 + t)
+                    assert off not in seen and off < region
+                    seen[off] = ("tp", t, mb)
+        assert plan.n_lanes * dep.tp <= 8 and dep.ep <= 8 and n_micro * 8 <= NFLAG
