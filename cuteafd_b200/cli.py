@@ -2,7 +2,8 @@
 
     python -m cuteafd_b200.cli plan qwen3-235b --layout
     python -m cuteafd_b200.cli serve --model tiny --listen 127.0.0.1:8000
-    python -m torch.distributed.run --nproc-per-node 8 -m cuteafd_b200.cli serve --model qwen3-235b   (attention TP2 + experts EP6)
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m cuteafd_b200.cli serve --model deepseek-v3
+        (attention TP2 on ranks 0-1 + experts on ranks 2-7; rank 0 runs the scheduler and the HTTP server, see serving/split.py)
 
 `serve` auto-detects the family from a snapshot's config.json (or takes a named synthetic shape), sizes the KV pool
 with the placement solver, builds the engine, and starts the HTTP server once the scheduler thread is ready.
@@ -80,8 +81,14 @@ def cmd_fabric(a) -> int:
 
 
 def build_serving(a):
-    """Engine + scheduler + prefix cache for a model name or snapshot (single GPU)."""
+    """Engine + scheduler + prefix cache for a model name or snapshot.  One process: a single-GPU engine.  Under torchrun
+    (WORLD_SIZE > 1): the attention/expert split; only the leader gets a scheduler back, the other ranks serve inside this call
+    and it returns None for them when the leader stops."""
     import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        from .serving.split import build_split_serving
+        return build_split_serving(a, world)
     from .config import spec_from_snapshot, spec_by_name, NAMED_SPECS, QuantSpec
     from .engine.engine import Engine
     from .engine.kv import PagePool
@@ -155,7 +162,10 @@ def cmd_serve(a) -> int:
     from .loader.tokenizer import load_tokenizer
     from .serving.api import ServingLoop, build_app
     from .serving.chat_templates import template_for
-    spec, sched = build_serving(a)
+    built = build_serving(a)
+    if built is None:            # a follower or expert rank of a multi-GPU layout: it has served and is done
+        return 0
+    spec, sched = built
     loop = ServingLoop(sched).start()
     keys = set(open(a.api_key_file).read().split()) if a.api_key_file else None
     usage = thermal = None
@@ -354,6 +364,7 @@ def main(argv=None) -> int:
     p.add_argument("--chat-template", default="", help="chat template family (chatml / qwen3-coder / deepseek / glm / plain); default: by model name")
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
+    p.add_argument("--n-micro", type=int, default=0, help="multi-GPU: micro-batches the attention ranks keep in flight (0 = the layout's default)")
     p.set_defaults(fn=cmd_serve)
     p = sub.add_parser("card")
     p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--device", type=int, default=0)

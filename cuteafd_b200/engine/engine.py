@@ -472,30 +472,47 @@ class Engine:
         return max(1, min(pages, 32, (2 * self.sm_count) // ctas))
 
     def run(self, sh: StepShape, use_graph: bool = True) -> Lane:
-        """Run a step, replaying a captured graph when one exists for this exact shape."""
+        """Run a step, replaying a captured graph when one exists for this exact shape.  A new shape in graph mode executes
+        twice (an eager warm-up, then the first replay of the capture); `on_real_step(sh, replay)` is told of each execution."""
         hook = getattr(self, "on_real_step", None)      # multi-rank runs announce every executed step to their peers
         if not use_graph:
             if hook:
-                hook(sh)
+                hook(sh, False)
             self.census.ran_eager(sh.key())
             return self.forward(sh)
         key = sh.key()
-        g = self.graphs.get(key)
-        if g is None:
+        if key not in self.graphs:
             if hook:
-                hook(sh)
+                hook(sh, False)
             self.forward(sh)                    # warm-up launch outside capture (loads modules, sizes scratch)
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                lane = self.forward(sh)
-            self.graphs[key] = g = (graph, lane, self.launches_per_step)
-            self.graph_captures += 1
-            self.census.captured(key, self.launches_per_step)
+            self._capture(sh)
         if hook:
-            hook(sh)
+            hook(sh, True)
+        g = self.graphs[key]
         g[0].replay()
         self.census.replayed(key)
+        self.launches_per_step = g[2]
+        return g[1]
+
+    def _capture(self, sh: StepShape):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            lane = self.forward(sh)
+        self.graphs[sh.key()] = (graph, lane, self.launches_per_step)
+        self.graph_captures += 1
+        self.census.captured(sh.key(), self.launches_per_step)
+
+    def execute(self, sh: StepShape, replay: bool) -> Lane:
+        """Exactly ONE execution of a step, eager or from its graph (captured first if need be, which executes nothing): what
+        a rank does that mirrors another rank's `run` call by call."""
+        if not replay:
+            return self.forward(sh)
+        if sh.key() not in self.graphs:
+            torch.cuda.synchronize()
+            self._capture(sh)
+        g = self.graphs[sh.key()]
+        g[0].replay()
         self.launches_per_step = g[2]
         return g[1]
 

@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..ref.ops import greedy_verify
+from .. import ops
 from .engine import Engine, StepShape
 from .kv import PagePool, SeqKV
 
@@ -45,6 +45,7 @@ class MtpSpeculator:
         self.seqs: list[_Seq] = []
         self.rounds = 0
         self._host = None
+        self._acc = None
         self.use_graph = use_graph       # replay draft and verify steps from CUDA graphs (steady-state serving / benchmarks)
 
     # ------------------------------------------------------------------ helpers
@@ -54,6 +55,22 @@ class MtpSpeculator:
         self._host[:n].copy_(dev_tokens[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self._host[:n].tolist()
+
+    def _read_many(self, parts: list) -> list:
+        """Several device int32 tensors -> host lists with one synchronisation."""
+        total = sum(n for _, n in parts)
+        if self._host is None or self._host.numel() < total:
+            self._host = torch.zeros(max(total, 256), dtype=torch.int32).pin_memory()
+        o = 0
+        for t, n in parts:
+            self._host[o:o + n].copy_(t[:n], non_blocking=True)
+            o += n
+        torch.cuda.current_stream().synchronize()
+        out, o = [], 0
+        for _, n in parts:
+            out.append(self._host[o:o + n].tolist())
+            o += n
+        return out
 
     def _mtp_step(self, rows_per_seq: list[list], want_logits: bool):
         """One MTP step.  rows_per_seq[i] = [(token, position, hidden)], possibly empty.  Returns (first-draft token
@@ -126,12 +143,21 @@ class MtpSpeculator:
         sh = StepShape(T=T, n_seq=len(self.seqs), max_q_len=nd + 1, n_logits=T, attn_splits=eng.attn_splits_for(len(self.seqs), nd + 1, max(kv_len)),
                        uniform=True)
         lane = eng.run(sh, use_graph=self.use_graph)
-        target = self._read(lane.next_tok, T)
+        # acceptance on the device (longest draft prefix the target agrees with, per sequence), read back with the target's
+        # tokens in one transfer; `ref.ops.greedy_verify` is the host statement of the same rule
+        n = len(self.seqs)
+        if self._acc is None or self._acc.numel() < 2 * n:
+            self._acc = torch.zeros(2 * max(n, 64), dtype=torch.int32, device=lane.next_tok.device)
+        acc_dev, emit_dev = self._acc[:n], self._acc[n:2 * n]
+        ops.verify_accept(eng.md["tokens"][:T].view(n, nd + 1), lane.next_tok[:T].view(n, nd + 1), None, acc_dev, emit_dev)
+        both = self._read_many([(lane.next_tok, T), (self._acc, 2 * n)])
+        target, acc_host, emit_host = both[0], both[1][:n], both[1][n:2 * n]
         vh = lane.x[:T].clone()
         for i, (s, dr) in enumerate(zip(self.seqs, drafts)):
             a0 = q_start[i]
             inputs = [s.anchor] + dr
-            accepted, emitted, _, _ = greedy_verify(inputs, target[a0:a0 + len(inputs)], None, 1 << 30)
+            accepted = acc_host[i]
+            emitted = target[a0:a0 + emit_host[i]]
             s.accepted.append(accepted - 1)
             s.out += emitted
             s.pending = [(inputs[j], s.length + j, vh[a0 + j - 1]) for j in range(1, accepted)]

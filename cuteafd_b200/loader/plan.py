@@ -19,10 +19,11 @@ from .safetensors_io import catalog
 # what each kernel family can run today: (operand format) -> kernel
 EXECUTABLE = {
     "bf16": "tc_linear kind::f16", "nvfp4": "tc_linear kind::mxf4nvf4 (W4A4)", "mxfp4": "tc_linear kind::mxf4 (W4A4)",
-    "fp8_block128": "tc_linear kind::f8f6f4 + block promotion", "fp8_block32": "tc_linear kind::mxf8f6f4",
+    "fp8_block128": "fp8_linear kind::f8f6f4 with per-stage block scales",
     "f32": "cast to bf16 at load", "f16": "cast to bf16 at load",
 }
 HINTS = {
+    "fp8_block32": "FP8 with 32 x 32 UE8M0 block scales has no kernel yet (tcgen05 kind::mxf8f6f4 scales along K only); re-quantise to 128 x 128 blocks with `cuteafd quantize`",
     "exl3": "EXL3 trellis weights are decoded by the dequant-GEMM path (K2-K5); check `cuteafd doctor` for the kernel",
 }
 
@@ -73,7 +74,9 @@ def deployment_decisions(layout: "placement.Layout", model: str, port: int = 295
         roles.append(entry)
     return {"parallelism": dep.describe(), "world": dep.world, "attention_groups": groups, "expert_ranks": list(dep.expert_ranks),
             "pool_tokens_per_group": layout.pool_tokens, "ranks": roles,
-            "launch": {"serve": f"python -m cuteafd_b200.cli serve --model {model}" if dep.world == 1 else None,
+            "launch": {"serve": f"python -m cuteafd_b200.cli serve --model {model}" if dep.world == 1 else
+                                (f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {dep.world} --master-addr 127.0.0.1 --master-port {port} "
+                                 f"-m cuteafd_b200.cli serve --model {model}") if dep.attn_groups == 1 and not dep.colocated else None,
                        "decode_bench": (f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {dep.world} --master-addr 127.0.0.1 "
                                         f"--master-port {port} bench.py --gpus {dep.world} --attn-groups {dep.attn_groups}") if dep.world > 1
                                        else "python bench.py --gpus 1"},

@@ -292,6 +292,22 @@ class AttnRankEngine(Engine):
         self._ctx_cache[key] = ctxs
         return ctxs
 
+    def set_inputs(self, *args, **kw):
+        n = super().set_inputs(*args, **kw)
+        hook = getattr(self, "on_inputs", None)     # a leader forwards the packed input block to the ranks that mirror its steps
+        if hook:
+            hook(self.meta_host)
+        return n
+
+    def load_inputs(self, block: torch.Tensor):
+        """Mirror side of `set_inputs`: `block` is the leader's packed int32 input block (same engine geometry)."""
+        need = (block.numel() - 3 * self.max_seqs - self.max_seqs * self.max_pages) // 4
+        self._ensure_meta(need)
+        if block.numel() != self.meta_host.numel():
+            raise ValueError(f"input block of {block.numel()} words does not fit this engine's layout ({self.meta_host.numel()})")
+        self.meta_host.copy_(block)
+        self.meta_dev.copy_(self.meta_host, non_blocking=True)
+
     def _ensure_meta(self, T: int):
         before = self._meta_cap
         super()._ensure_meta(T)

@@ -25,7 +25,7 @@ from ..ops import KIND_BY_NAME
 from .afd import AttnRankEngine, ExpertRankWorker, LanePlan, MlaAttnRankEngine, capture_expert_graph, make_block
 from .mailbox import Mailbox
 
-OP_STOP, OP_STEP, OP_TIMER_START, OP_TIMER_STOP, OP_MTP = 0, 1, 2, 3, 4
+OP_STOP, OP_STEP, OP_TIMER_START, OP_TIMER_STOP, OP_MTP, OP_INPUTS = 0, 1, 2, 3, 4, 5
 
 
 class AfdRunner:
@@ -50,10 +50,10 @@ class AfdRunner:
             name = [f"cuteafd_{os.getpid()}_{int(time.time() * 1e3) & 0xFFFFFF}" if rank == self.root else None]
             dist.broadcast_object_list(name, src=self.root)
             if rank == self.root:
-                self.mail = Mailbox(name[0], create=True)
+                self.mail = Mailbox(name[0], create=True, slots=32, payload_bytes=1 << 20)
             dist.barrier()
-            if rank != self.root and self.is_expert:
-                self.mail = Mailbox(name[0], create=False)
+            if rank != self.root:
+                self.mail = Mailbox(name[0], create=False, slots=32, payload_bytes=1 << 20)
         self.engine = self.worker = None
         if self.is_attn:
             cls = MlaAttnRankEngine if spec.attn.kind == "mla" else AttnRankEngine
@@ -76,8 +76,33 @@ class AfdRunner:
         if self.mail is not None and self.rank == self.root:
             self.mail.post(op, a, b)
 
-    def _announce(self, sh: StepShape):
-        self._post(OP_STEP, sh.T)
+    def _announce(self, sh: StepShape, replay: bool = False):
+        if self.mail is not None and self.rank == self.root:
+            import numpy as np
+            self.mail.post(OP_STEP, sh.T, 1 if replay else 0,
+                           np.array([sh.T, sh.n_seq, sh.max_q_len, sh.n_logits, sh.attn_splits, int(sh.uniform)], dtype=np.int64))
+
+    def mirror_inputs(self, on: bool = True):
+        """Leader of a serving deployment: forward every step's packed input block to the attention ranks that mirror it (its
+        tensor-parallel partner).  Benchmarks and self-tests run the same host code on every attention rank and need none."""
+        if self.engine is not None and self.rank == self.root:
+            self.engine.on_inputs = (lambda block: self.mail.post(OP_INPUTS, block.numel(), 0, block.numpy())) if on else None
+
+    def follow_loop(self, timeout_s: float = 3600.0):
+        """Attention ranks other than the leader, serving: mirror the leader's steps one execution at a time."""
+        import numpy as np
+        eng = self.engine
+        while True:
+            op, a, b, payload = self.mail.read(timeout_s)
+            if op == OP_STOP:
+                break
+            if op == OP_INPUTS:
+                eng.load_inputs(torch.from_numpy(np.frombuffer(payload, dtype=np.int32).copy()))
+            elif op == OP_STEP:
+                f = np.frombuffer(payload, dtype=np.int64)
+                sh = StepShape(T=int(f[0]), n_seq=int(f[1]), max_q_len=int(f[2]), n_logits=int(f[3]), attn_splits=int(f[4]), uniform=bool(f[5]))
+                eng.execute(sh, bool(b))
+        torch.cuda.synchronize()
 
     def _announce_mtp(self, depth: int, sh: StepShape):
         self._post(OP_MTP, sh.T, depth)
@@ -105,6 +130,8 @@ class AfdRunner:
                 torch.cuda.synchronize()
                 self.timer_ms = ev0.elapsed_time(ev1)
                 continue
+            if op == OP_INPUTS:
+                continue                                    # step inputs concern the attention ranks only
             layers = None if op == OP_STEP else [self.spec.n_layers + b]
             if self.comm != "p2p":
                 w.step_nccl(a, layers)

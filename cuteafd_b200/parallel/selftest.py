@@ -102,7 +102,9 @@ def run_selftest(rank: int, world: int, local: int, *, layout: str = "split", gr
         run.control(OP_STOP)
         run.check()
         if want is not None:
-            ok = tokens_agree(out, want, top2, exact=dep.tp == 1 or spec.attn.kind != "mla")
+            # heads split over two ranks sum two bf16-rounded partial projections: a near tie of the reference may flip there;
+            # every other layout computes exactly what the single-GPU engine computes
+            ok = tokens_agree(out, want, top2, exact=dep.tp == 1)
             if verbose:
                 print(f"[selftest] model={model} comm={comm} experts={experts} world={world} layout={dep.describe()} micro={n_micro} "
                       f"rank={rank}: {'OK' if ok else 'MISMATCH'} {out if not ok else ''} {want if not ok else ''}", flush=True)

@@ -92,8 +92,11 @@ class EngineRunner:
         self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages)
         max_q = max(q_len)
         decode_like = max_q <= 8
+        # regular decode / verify rounds (every sequence the same number of rows, logits for every row or none) may be cut into
+        # micro-batches by a multi-GPU engine
+        uniform = decode_like and all(q == max_q for q in q_len) and (not logit_rows or logit_rows == list(range(len(tokens))))
         sh = StepShape(T=len(tokens), n_seq=len(rows), max_q_len=max_q, n_logits=len(logit_rows),
-                       attn_splits=eng.attn_splits_for(len(rows), max_q, max(kv_len)) if decode_like else 1)
+                       attn_splits=eng.attn_splits_for(len(rows), max_q, max(kv_len)) if decode_like else 1, uniform=uniform)
         lane = eng.run(sh, use_graph=decode_like)
         if self.keep_hidden:
             for r, qs, ql in zip(rows, q_start, q_len):
