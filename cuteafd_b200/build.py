@@ -22,9 +22,6 @@ LIB = OUT / "libcuteafd_b200.so"
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math=false", "-Xptxas", "-v"]
-# sources whose kernels use TMA loads with cluster multicast (single-GPU only); they are linked into a
-# separate library so multi-GPU runs never load them.
-SINGLE_GPU_ONLY: set[str] = set()
 
 
 def nvcc_path() -> str:
@@ -45,7 +42,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     OUT.mkdir(exist_ok=True)
     nvcc = nvcc_path()
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    sources = sorted(p for p in CSRC.glob("*.cu") if p.name not in SINGLE_GPU_ONLY)
+    sources = sorted(CSRC.glob("*.cu"))
     flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
     jobs = []
     for src in sources:

@@ -56,28 +56,15 @@ def cmd_doctor(a) -> int:
 
 
 def cmd_fabric(a) -> int:
-    """Peer-to-peer probe between two GPUs: copy-engine copy and SM push, one way (reference: `cuteafd fabric --p2p`)."""
-    import torch
-    if torch.cuda.device_count() < 2:
-        print(json.dumps({"error": "fabric probe needs two GPUs"}))
+    """NVLink link probes (copy engine vs SM push vs SM pull, one-way vs duplex, eager vs graph, flag round trip, all-to-all):
+    `python -m torch.distributed.run --nproc-per-node N -m cuteafd_b200.cli fabric [--all-to-all]`.  Reference: `cuteafd fabric --p2p`."""
+    if int(os.environ.get("WORLD_SIZE", "1")) < 2:
+        print(json.dumps({"error": "the fabric probe runs one rank per GPU: python -m torch.distributed.run --nproc-per-node 2 "
+                                   "--master-addr 127.0.0.1 -m cuteafd_b200.cli fabric"}))
         return 2
-    n = a.mib << 20
-    src = torch.empty(n, dtype=torch.uint8, device="cuda:0")
-    dst = torch.empty(n, dtype=torch.uint8, device="cuda:1")
-    out = {}
-    for name, fn in (("copy_engine", lambda: dst.copy_(src, non_blocking=True)),):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(10):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        out[name + "_gbs"] = round(10 * n / (e0.elapsed_time(e1) / 1e3) / 1e9, 1)
-    print(json.dumps(out))
-    return 0
+    from .bench import fabric
+    sys.argv = ["fabric"] + (["--all-to-all"] if a.all_to_all else []) + (["--sizes", a.sizes] if a.sizes else [])
+    return fabric.main()
 
 
 def build_serving(a):
@@ -344,7 +331,8 @@ def main(argv=None) -> int:
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
     p = sub.add_parser("run"); p.add_argument("--config", required=True); p.add_argument("--set", action="append", default=[])
     p.add_argument("--print", action="store_true"); p.set_defaults(fn=cmd_run, subparsers=sub.choices)
-    p = sub.add_parser("fabric"); p.add_argument("--p2p", action="store_true"); p.add_argument("--mib", type=int, default=256); p.set_defaults(fn=cmd_fabric)
+    p = sub.add_parser("fabric"); p.add_argument("--p2p", action="store_true"); p.add_argument("--all-to-all", action="store_true")
+    p.add_argument("--sizes", default="", help="comma-separated message sizes in bytes"); p.set_defaults(fn=cmd_fabric)
     p = sub.add_parser("serve")
     p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--listen", default="127.0.0.1:8000")
     p.add_argument("--device", type=int, default=0); p.add_argument("--max-context", type=int, default=32768)

@@ -488,3 +488,55 @@ extern "C" int cuteafd_combine_push_lanes(const void* y, const int* src_route, c
   CA_CHECK_LAUNCH("combine_push_lanes");
   return CA_OK;
 }
+
+// ---------------------------------------------------------------- link probes
+// SM-issued copy between any two addresses (either may be peer memory): 16-byte loads and stores, grid chosen by the caller.
+// dst = peer, src = local is an SM push; dst = local, src = peer an SM pull.  (Reference: the p2p probe modes of
+// native/shared/include/cuteafd_peer_exchange.h:121-138, 353-371.)
+__global__ void peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int cuteafd_peer_copy(void* dst, const void* src, size_t bytes, int blocks, cudaStream_t s) {
+  CA_REQUIRE(bytes % 16 == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0, "peer_copy: 16-byte alignment");
+  if (!bytes) return CA_OK;
+  const size_t n16 = bytes / 16;
+  if (blocks < 1) { size_t b = (n16 + 255) / 256; blocks = (int)(b < 1184 ? b : 1184); }
+  peer_copy_kernel<<<blocks, 256, 0, s>>>((const uint4*)src, (uint4*)dst, n16);
+  CA_CHECK_LAUNCH("peer_copy");
+  return CA_OK;
+}
+
+// Copy-engine copy between two device addresses (peer addresses included): no SM involved.
+extern "C" int cuteafd_copy_engine(void* dst, const void* src, size_t bytes, cudaStream_t s) {
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s);
+  if (e != cudaSuccess) return ca_cuda(e, "cudaMemcpyAsync(peer)");
+  return CA_OK;
+}
+
+// Flag ping-pong between two GPUs (one launch on each, at the same time, one thread): the initiator releases i into the
+// peer's flag and waits for i in its own; the responder waits, then answers.  `out_ns[0]` = nanoseconds for `iters` round
+// trips on this side.  Every wait is bounded; a wait that runs out sets the status word and ends the loop.
+__global__ void flag_pingpong_kernel(uint32_t* my_flag, uint32_t* peer_flag, uint32_t base, int iters, int initiator,
+                                     unsigned long long timeout_ns, int* status, unsigned long long* out_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  for (int i = 1; i <= iters; ++i) {
+    const uint32_t v = base + (uint32_t)i;
+    if (initiator) {
+      st_release_sys(peer_flag, v);
+      if (!wait_flag_bounded(my_flag, v, timeout_ns)) { ca_dev_fail(status, CA_DEV_TIMEOUT_FLAG, i); break; }
+    } else {
+      if (!wait_flag_bounded(my_flag, v, timeout_ns)) { ca_dev_fail(status, CA_DEV_TIMEOUT_FLAG, i); break; }
+      st_release_sys(peer_flag, v);
+    }
+  }
+  out_ns[0] = globaltimer_ns() - t0;
+}
+
+extern "C" int cuteafd_flag_pingpong(void* my_flag, void* peer_flag, unsigned base, int iters, int initiator, unsigned long long timeout_ns,
+                                     int* status, void* out_ns, cudaStream_t s) {
+  CA_REQUIRE(my_flag && peer_flag && iters >= 1 && out_ns, "flag_pingpong: flags, iterations and an output word");
+  flag_pingpong_kernel<<<1, 1, 0, s>>>((uint32_t*)my_flag, (uint32_t*)peer_flag, base, iters, initiator, timeout_ns, status, (unsigned long long*)out_ns);
+  CA_CHECK_LAUNCH("flag_pingpong");
+  return CA_OK;
+}

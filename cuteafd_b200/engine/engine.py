@@ -137,6 +137,19 @@ class Engine:
             self.kv_tmaps = ops.encode_kv_tmaps(self.kv) if a.head_dim == 128 and 128 % (a.n_heads // a.n_kv_heads) == 0 else None
         else:
             self._alloc_attention_state()
+        # memory ledger: what this engine holds, by category (reported by `/v1/stats` and `cuteafd doctor`)
+        from ..utils.memory_ledger import LEDGER
+        with LEDGER.scope("weights"):
+            LEDGER.charge_tree(weights, "model weights")
+        with LEDGER.scope("kv"):
+            LEDGER.charge(self.kv.numel() * self.kv.element_size(), "paged KV store")
+        # optional instrumentation of eager steps: per-layer device time (CUDA events, read after the step) and NVTX ranges
+        self.layer_clock = None
+        if os.environ.get("CUTEAFD_LAYER_CLOCK", "0") == "1":
+            from ..utils.trace import DeviceClock
+            self.layer_clock = DeviceClock()
+        self._nvtx = os.environ.get("CUTEAFD_NVTX", "0") == "1"
+        self._l2_prefetch = os.environ.get("CUTEAFD_L2_PREFETCH", "0") == "1"
         self.lanes: dict[int, Lane] = {}
         self.mtp_lanes: dict[int, Lane] = {}
         self.graphs: dict = {}
@@ -369,11 +382,17 @@ class Engine:
         self._pre_normed = False
         ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
         self.launches_per_step += 1
+        import contextlib
+        from ..utils.trace import nvtx
+        timed = self.layer_clock is not None and not torch.cuda.is_current_stream_capturing()
         for li in range(spec.n_layers):
             lw = self.weights.layer(li)
             self._next_lw = self.weights.layer(li + 1) if li + 1 < spec.n_layers else None
-            self._attention_layer(li, lw, L, sh)
-            self._moe_layer(lw, L, T)
+            with (self.layer_clock.span(f"layer{li}") if timed else contextlib.nullcontext()), (nvtx(f"layer{li}") if self._nvtx else contextlib.nullcontext()):
+                self._attention_layer(li, lw, L, sh)
+                if self._l2_prefetch and self._next_lw is not None and getattr(self._next_lw, "wqkv", None) is not None:
+                    ops.l2_prefetch(self._next_lw.wqkv.data)       # the next layer's first weights ride into L2 under this layer's experts
+                self._moe_layer(lw, L, T)
         if sh.n_logits:
             ops.gather_rows(L.x, self.md["logit_rows"], None, L.xl, sh.n_logits)
             ops.add_rmsnorm(L.xl, None, self.weights.final_norm, L.xln, spec.rms_eps, rows=sh.n_logits)
@@ -515,6 +534,13 @@ class Engine:
         g[0].replay()
         self.launches_per_step = g[2]
         return g[1]
+
+    def layer_times(self) -> dict:
+        """Device milliseconds per layer of the eager steps since the last call (needs CUTEAFD_LAYER_CLOCK=1; synchronises)."""
+        if self.layer_clock is None:
+            return {}
+        torch.cuda.synchronize()
+        return self.layer_clock.collect()
 
     def check_status(self):
         word = int(self.status[0])

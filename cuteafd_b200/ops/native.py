@@ -67,6 +67,9 @@ _PROTOS = {
     "cuteafd_wait_add": [P, P, P, P, C.c_size_t, I, P, P, C.c_uint, C.c_ulonglong, P, P],
     "cuteafd_dispatch_push": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
     "cuteafd_combine_push": [P, P, P, P, P, P, P, I, I, I, C.c_uint, P],
+    "cuteafd_peer_copy": [P, P, C.c_size_t, I, P],
+    "cuteafd_copy_engine": [P, P, C.c_size_t, P],
+    "cuteafd_flag_pingpong": [P, P, C.c_uint, I, I, C.c_ulonglong, P, P, P],
     "cuteafd_dispatch_tok_push": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
     "cuteafd_combine_push_lanes": [P, P, P, P, P, P, P, I, I, I, I, I, I, C.c_uint, P, P],
     "cuteafd_tc_linear": [I, I, I, P, P, P, P, P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, I, P, P],

@@ -35,6 +35,9 @@ class SymmetricBlock:
             off += -(-nbytes // 256) * 256
         self.nbytes = max(off, 256)
         self.buf = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
+        from ..utils.memory_ledger import LEDGER
+        with LEDGER.scope("peer-split"):
+            LEDGER.charge(self.nbytes, "symmetric block")
         self.base = [0] * world
         self.base[rank] = self.buf.data_ptr()
         self._opened: list = []

@@ -190,6 +190,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         key = (authorization or "").removeprefix("Bearer ").strip() or (x_api_key or "")
         if key not in api_keys:
             raise HTTPException(401, "invalid API key")
+        return key
 
     def sampling_from(body: dict) -> SamplingParams:
         try:
@@ -437,15 +438,22 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         return app
 
     # ------------------------------------------------------------------ OpenAI Responses
-    stored: dict = {}              # response id -> {"response": ..., "messages": conversation including the answer}
+    # response id -> {"response": ..., "messages": conversation including the answer, "owner": API key that created it}.
+    # Bounded (the oldest entries go first) and scoped: a response is visible only to the key that stored it.
+    stored: dict = {}
 
-    def responses_messages(body):
+    def stored_entry(response_id, owner):
+        e = stored.get(response_id)
+        if e is None or e["owner"] != owner:
+            raise HTTPException(404, f"no stored response {response_id}")
+        stored[response_id] = stored.pop(response_id)       # most recently used last
+        return e
+
+    def responses_messages(body, owner=None):
         msgs = []
         prev = body.get("previous_response_id")
         if prev:
-            if prev not in stored:
-                raise HTTPException(404, f"no stored response {prev}")
-            msgs += stored[prev]["messages"]
+            msgs += stored_entry(prev, owner)["messages"]
         inp = body.get("input")
         if isinstance(inp, str):
             msgs.append({"role": "user", "content": inp})
@@ -481,9 +489,9 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
 
     @app.post("/v1/responses")
     async def responses(http: HttpRequest, authorization: str = Header(None)):
-        auth(authorization)
+        owner = auth(authorization)
         body = await http.json()
-        msgs, tools = responses_messages(body)
+        msgs, tools = responses_messages(body, owner)
         if not msgs:
             raise HTTPException(400, "input is required")
         thinking, stops = chat_options(body)
@@ -503,7 +511,7 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                 answer = {"role": "assistant", "content": parsed["content"]}
                 if parsed["tool_calls"]:
                     answer["tool_calls"] = openai_calls(parsed["tool_calls"])
-                stored[resp["id"]] = {"response": resp, "messages": msgs + [answer]}
+                stored[resp["id"]] = {"response": resp, "messages": msgs + [answer], "owner": owner}
                 while len(stored) > 256:
                     stored.pop(next(iter(stored)))
             return resp, parsed
@@ -557,16 +565,12 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
 
     @app.get("/v1/responses/{response_id}")
     async def get_response(response_id: str, authorization: str = Header(None)):
-        auth(authorization)
-        if response_id not in stored:
-            raise HTTPException(404, "no such response")
-        return stored[response_id]["response"]
+        return stored_entry(response_id, auth(authorization))["response"]
 
     @app.delete("/v1/responses/{response_id}")
     async def delete_response(response_id: str, authorization: str = Header(None)):
-        auth(authorization)
-        if stored.pop(response_id, None) is None:
-            raise HTTPException(404, "no such response")
+        stored_entry(response_id, auth(authorization))
+        stored.pop(response_id, None)
         return {"id": response_id, "object": "response", "deleted": True}
 
     def anthropic_prompt(body):

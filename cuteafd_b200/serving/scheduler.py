@@ -357,9 +357,10 @@ class Scheduler:
 
     def snapshot(self) -> dict:
         census = getattr(getattr(self.runner, "eng", None), "census", None)
+        from ..utils.memory_ledger import LEDGER
         return dict(self.stats, active=len(self.active), queued=len(self.queue),
                     prefilling=sum(1 for s in self.active if s.prefilled < len(s.req.prompt)),
                     prefix=self.prefix.snapshot() if self.prefix else None, draft_policy=self.policy.snapshot(),
-                    free_pages=self.pool.n_free, fatal=self.fatal, phases=self.profile.snapshot(),
+                    free_pages=self.pool.n_free, fatal=self.fatal, phases=self.profile.snapshot(), memory=LEDGER.report(),
                     draft_acceptance_by_position=[round(a / o, 3) if o else None for o, a in self.accept_by_pos],
                     graphs=census.snapshot() if census is not None else None)

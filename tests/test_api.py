@@ -317,3 +317,23 @@ def test_tool_choice_forces_a_call_with_schema_checked_arguments():
         assert m["finish_reason"] == "tool_calls" and json.loads(m["message"]["tool_calls"][0]["function"]["arguments"]) == {"city": "Oslo"}
     finally:
         loop.stop()
+
+
+def test_stored_responses_belong_to_the_key_that_created_them():
+    """A response id is no capability: another API key can neither read it, chain onto it, nor delete it."""
+    from cuteafd_b200.serving.chat_templates import template_for
+    runner = FakeRunner(vocab=258)
+    runner.next_token = lambda prefix: 257 if len(prefix) % 7 == 0 else 65
+    loop = ServingLoop(Scheduler(runner, PagePool(512)), Health()).start()
+    try:
+        c = TestClient(build_app(loop, model_id="plain", template=template_for("plain"), api_keys={"alice", "bob"}))
+        a, b = {"authorization": "Bearer alice"}, {"authorization": "Bearer bob"}
+        r1 = c.post("/v1/responses", json={"input": "hi", "max_output_tokens": 20}, headers=a).json()
+        assert c.get("/v1/responses/" + r1["id"], headers=a).status_code == 200
+        assert c.get("/v1/responses/" + r1["id"], headers=b).status_code == 404
+        assert c.post("/v1/responses", json={"input": "more", "previous_response_id": r1["id"], "max_output_tokens": 20}, headers=b).status_code == 404
+        assert c.delete("/v1/responses/" + r1["id"], headers=b).status_code == 404
+        assert c.post("/v1/responses", json={"input": "more", "previous_response_id": r1["id"], "max_output_tokens": 20}, headers=a).status_code == 200
+        assert c.delete("/v1/responses/" + r1["id"], headers=a).json()["deleted"]
+    finally:
+        loop.stop()
