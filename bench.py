@@ -114,13 +114,44 @@ def deepseek_headline(args, rank: int, world: int, local: int) -> dict | None:
             "selftest": None if ok is None else ("ok" if ok else "FAILED"), "results": out, "clocks": main.get("clocks")}
 
 
+def deepseek_ttft(args, rank: int, world: int, local: int) -> dict | None:
+    """Long-prefill + exact prefix-cache workload on the DeepSeek-V3 shape through the serving stack on the split (scheduler,
+    chunked prefill, prefix cache on the attention leader; its TP partner mirrors it; expert ranks serve): sessions share a
+    28k-token prefix and append 4k unique tokens; cold TTFT, prefix-restore TTFT (p50), then decode tokens per session."""
+    import argparse as ap
+    import torch
+    import torch.distributed as dist
+    from cuteafd_b200.bench.ttft import measure_sessions
+    from cuteafd_b200.serving.split import build_split_serving
+    prompt, shared, decode = args.ttft_prompt, args.ttft_shared, args.ttft_decode
+    a = ap.Namespace(model="deepseek-v3", device=local, layers=args.layers, pool_tokens=(prompt + decode + 512) * 3 // 64 * 64, max_sequences=2,
+                     max_context=prompt + decode + 256, prefill_batch_tokens=4096, host_cache_gib=0.0, host_cache_headroom_gib=0.0,
+                     host_cache_min_tokens=512, prefix_cache_entries=16, prefix_cache_min_tokens=64, draft="off", decode_share=0.2, draft_limit=3,
+                     http_queue=16, queue_wait_s=0, n_micro=args.n_micro or 1)
+    built = build_split_serving(a, world)
+    res = None
+    if built is not None:
+        spec, sched = built
+        res = measure_sessions(sched, spec.vocab, prompt=prompt, shared=shared, sessions=args.ttft_sessions, decode=decode)
+        sched.runner.eng.check_status()
+        res.update(model=spec.name + (f" (DEBUG {args.layers} layers: INVALID)" if args.layers else ""), layers=spec.n_layers,
+                   parallelism=sched.afd_runner.dep.describe(), prefix_cache=sched.prefix.snapshot(),
+                   timing="host clock from submit to first token (device synchronised), through Scheduler + EngineRunner on the split",
+                   data="synthetic token ids, random-init weights")
+        sched.afd_runner.shutdown()
+    dist.barrier()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="qwen3-235b-decode", choices=["qwen3-235b-decode", "deepseek-v3-decode"])
+    ap.add_argument("--config", default="qwen3-235b-decode", choices=["qwen3-235b-decode", "deepseek-v3-decode", "deepseek-v3-ttft"])
+    ap.add_argument("--ttft-prompt", type=int, default=32768); ap.add_argument("--ttft-shared", type=int, default=28672)
+    ap.add_argument("--ttft-sessions", type=int, default=8); ap.add_argument("--ttft-decode", type=int, default=256)
     ap.add_argument("--batch-per-gpu", type=int, default=16)
     ap.add_argument("--batch-total", type=int, default=0, help="fixed global batch instead of a per-GPU batch (DeepSeek-V3 decode: 1 or 64)")
     ap.add_argument("--context", type=int, default=4096)
@@ -130,10 +161,13 @@ def main():
     ap.add_argument("--layout", default=None, choices=["split", "colocated"],
                     help="multi-GPU layout: disjoint attention / expert ranks, or both roles on every GPU (default: per model, see parallel.runner.default_layout)")
     ap.add_argument("--n-micro", type=int, default=0, help="micro-batches an attention rank keeps in flight (0 = the layout's default)")
+    ap.add_argument("--expert-tp", action="store_true",
+                    help="expert ranks hold a slice of every expert's intermediate dimension (rows broadcast, rank-ordered partial sums) instead of whole experts")
     ap.add_argument("--no-selftest", action="store_true", help="skip the token-exactness check of the layout on the tiny model (N > 1)")
     ap.add_argument("--no-nccl-baseline", action="store_true", help="skip the NCCL-only arm that N > 1 runs report beside the main number")
     ap.add_argument("--real-prefill", action="store_true", help="build the context by running prefill instead of filling KV")
     ap.add_argument("--mtp", type=int, default=3, help="deepseek-v3-decode: draft tokens the MTP module proposes per round")
+    ap.add_argument("--no-ttft", action="store_true", help="8 GPUs, default config: skip the 32k-prefill / prefix-restore sub-result")
     ap.add_argument("--no-headline", action="store_true",
                     help="8 GPUs, default config: skip the DeepSeek-V3-shape sub-results (batch 1 and 64 at 8k with the MTP drafter)")
     args = ap.parse_args()
@@ -153,6 +187,16 @@ def main():
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
 
+    if args.config == "deepseek-v3-ttft":
+        res = deepseek_ttft(args, rank, world, local)
+        if rank == 0:
+            print(json.dumps({"metric": "ttft_s", "value": res["cold_ttft_s"], "unit": "s", "n_gpus": world, "steps": res["sessions"], "warmup": 0,
+                              "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations, mxfp4 experts / fp8_block128 dense",
+                              "data": res["data"], "config": {"model": res["model"], "global_batch": 1, "seq_len": res["prompt_tokens"],
+                                                               "parallelism": res["parallelism"]}, "results": res}))
+        import torch.distributed as dist
+        dist.destroy_process_group()
+        return 0
     if args.config == "deepseek-v3-decode":
         res = deepseek_headline(args, rank, world, local)
         if rank == 0:
@@ -202,6 +246,17 @@ def main():
             headline = deepseek_headline(args, rank, world, local)
         except Exception as e:           # the main record must survive a failure of the sub-results
             headline = {"error": f"{type(e).__name__}: {e}"}
+        if not args.no_ttft:
+            gc.collect(); torch.cuda.empty_cache()
+            try:
+                import copy
+                a3 = copy.copy(args)
+                a3.ttft_sessions, a3.ttft_decode = min(args.ttft_sessions, 3), min(args.ttft_decode, 32)    # bounded: 1 cold + 2 restores
+                ttft = deepseek_ttft(a3, rank, world, local)
+            except Exception as e:
+                ttft = {"error": f"{type(e).__name__}: {e}"}
+            if rank == 0 and headline is not None:
+                headline["ttft_32k"] = ttft
     if rank == 0:
         if headline is not None:
             res["deepseek_v3_headline"] = headline

@@ -4,9 +4,11 @@ intermediate 2048, MXFP4 expert weights, bf16 activations, N(0,1) router logits)
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m cuteafd_b200.bench.ep_microbench \
         --tokens 1,16,128,1024,4096 --comm p2p
 
-All `world` ranks are both senders and expert owners (EP = world).  Per iteration every rank: routes its tokens,
-quantises and scatters its rows into the owners' slabs (peer stores + flags), runs the grouped MXFP4 FC1(SwiGLU) +
-FC2 on what it received, pushes the output rows back to the token owners, and forms the ordered weighted top-k sum.
+All `world` ranks are both senders and expert owners (EP = world).  Per iteration every rank: quantises each of its tokens
+once and stores the row into the lane slab of every rank that owns one of its experts (peer stores + flags; routing rows and
+token counts travel with them), waits in-kernel for all lanes, packs and gathers the received rows into expert order, runs the
+grouped MXFP4 FC1 (SwiGLU, FP4 output) + FC2, pushes the output rows back to the token owners, and forms the ordered weighted
+top-k sum (waiting in-kernel for the owners' flags).
 `--comm nccl` is the baseline: all_to_all_single of bf16 rows both ways around the same local GEMMs.
 Time is CUDA-event device time, max over ranks; the roofline is the slowest of the GEMM flops at the measured bf16
 peak (an under-estimate for FP4), the bytes that must cross NVLink at 770 GB/s per direction, and the expert weight bytes that
@@ -24,8 +26,9 @@ import torch.distributed as dist
 
 from .. import ops
 from ..config import ep_microbench_spec
-from ..ops import ActBuffer, KIND_BF16, KIND_MXFP4, TcWeight, pick_tn
+from ..ops import ActBuffer, KIND_BF16, KIND_MXFP4, TcWeight, native, pick_tn
 from ..parallel import peer_ops
+from ..parallel.afd import PtrTable
 from ..parallel.symm import SymmetricBlock
 
 
@@ -65,7 +68,7 @@ def main() -> int:
         status, ctl, done = i32(4), i32(4), i32(8)
         inv_gs = torch.ones(1, device=dev)
         sf_ld = H // 32
-        block = SymmetricBlock({"slab_q": rows_cap * H // 2, "slab_sf": rows_cap * sf_ld, "idx": rows_cap * 4, "y_recv": rows_cap * H * 2,
+        block = SymmetricBlock({"slab_q": Tg * H // 2, "slab_sf": Tg * (-(-H // 256) * 8), "idx": Tg * k * 4, "lane_T": 256, "y_recv": T * k * H * 2,
                                 "flags": 64 * 4}, dev, None, rank, world) if a.comm == "p2p" else None
         h1 = torch.zeros(rows_cap, I, dtype=torch.bfloat16, device=dev)
         h1q = ActBuffer.alloc(KIND_MXFP4, rows_cap, I, tn, dev)
@@ -74,29 +77,38 @@ def main() -> int:
         ident = torch.arange(rows_cap, dtype=torch.int32, device=dev).view(Tg, k).contiguous()
         ranks = list(range(world))
         if a.comm == "p2p":
-            data = block.local("slab_q", torch.uint8, (rows_cap, H // 2))
-            xs = ActBuffer(KIND_MXFP4, rows_cap, H, tn, data, ops.encode_tmap(data, tn), block.local("slab_sf", torch.uint8, (rows_cap, sf_ld)))
-            slab_q_tbl, slab_sf_tbl, idx_tbl = block.ptr_table(ranks, "slab_q"), block.ptr_table(ranks, "slab_sf"), block.ptr_table(ranks, "idx")
-            recv_tbl = block.ptr_table(ranks, "y_recv")
-            f_disp, f_comb = block.ptr_table(ranks, "flags", rank * 4), block.ptr_table(ranks, "flags", (16 + rank) * 4)
-            y_recv = block.local("y_recv", torch.bfloat16, (rows_cap, H))
-            idx_local = block.local("idx", torch.int32, (Tg, k))
+            # token-major lanes: rank r is lane r on every rank (slab rows [r * T, (r + 1) * T)); each token crosses NVLink once per
+            # destination rank, the expert side gathers rows into expert order itself
+            sf_pad = -(-H // 256) * 8
+            slab_q = block.local("slab_q", torch.uint8, (Tg, H // 2))
+            slab_sf = block.local("slab_sf", torch.uint8)[:Tg * sf_pad].view(Tg, sf_pad)
+            idx_tab = block.local("idx", torch.int32, (Tg, k))
+            lane_T = block.local("lane_T", torch.int32)[:world]
+            xs = ActBuffer.alloc(KIND_MXFP4, rows_cap, H, tn, dev)
+            mk = lambda name, off: PtrTable([block.peer_ptr(r, name, off) for r in ranks])
+            q_tbl, sf_tbl, i_tbl, t_tbl = mk("slab_q", rank * T * (H // 2)), mk("slab_sf", rank * T * sf_pad), mk("idx", rank * T * k * 4), mk("lane_T", rank * 4)
+            f_disp = mk("flags", rank * 4)
+            recv_tbl = PtrTable([block.peer_ptr(r, "y_recv") for r in ranks])        # lane r's rows return to rank r
+            f_comb = PtrTable([block.peer_ptr(r, "flags", (16 + rank) * 4) for r in ranks])
+            y_recv = block.local("y_recv", torch.bfloat16, (T * k, H))
+            x_mine, idx_mine = x_all[rank * T:(rank + 1) * T].contiguous(), idx[rank * T:(rank + 1) * T].contiguous()
+            ident_mine = torch.arange(T * k, dtype=torch.int32, device=dev).view(T, k).contiguous()
+            wait_d = native.flag_wait(block.peer_ptr(rank, "flags", 0), world, 1, ctl, status)
+            wait_c = native.flag_wait(block.peer_ptr(rank, "flags", 16 * 4), world, 1, ctl, status)
         else:
             xs = ActBuffer.alloc(KIND_MXFP4, rows_cap, H, tn, dev)
 
         def step_p2p():
             peer_ops.step_begin(ctl)
-            ops.route_pack(idx, g_src, g_slot, g_cnt, g_off, g_tiles, g_nt, g_nr, Tg, k, 0, E, 1 << 20, E + 2)
-            peer_ops.dispatch_push(x_all, idx, g_slot, g_off, slab_q_tbl, slab_sf_tbl, idx_tbl, f_disp, inv_gs, ctl, done[0:1],
-                                   rank * T, (rank + 1) * T, H, k, E, world, KIND_MXFP4, sf_ld, rows_cap, 0, status)
-            peer_ops.wait_flags(block.peer_ptr(rank, "flags", 0), world, 1, ctl, 0, status)
-            ops.route_pack(idx_local, l_src, l_slot, l_cnt, l_off, l_tiles, l_nt, l_nr, Tg, k, e_lo, e_hi, tn, max_tiles, src_route=l_route)
-            ops.tc_linear(wg, xs, h1, rows=rows_cap, w_up=wu, tiles=l_tiles, n_tiles=l_nt, max_tiles=max_tiles, status=status)
-            ops.quant_fp4_rows(h1, h1q, n_rows_dev=l_nr, rows=rows_cap)
+            peer_ops.dispatch_tok_push(x_mine, idx_mine, q_tbl.arr, sf_tbl.arr, i_tbl.arr, t_tbl.arr, f_disp.arr, inv_gs, ctl, done[0:1], 0, T, T, H, k, E,
+                                       world, KIND_MXFP4, sf_pad, 0, status)
+            ops.route_pack(idx_tab, l_src, l_slot, l_cnt, l_off, l_tiles, l_nt, l_nr, Tg, k, e_lo, e_hi, tn, max_tiles, src_route=l_route,
+                           wait=wait_d, lane_T=lane_T, t_cap=T)
+            ops.route_gather(slab_q, slab_sf, l_src, l_nr, xs, rows_cap, status)
+            ops.tc_linear(wg, xs, None, rows=rows_cap, w_up=wu, tiles=l_tiles, n_tiles=l_nt, max_tiles=max_tiles, status=status, quant_out=h1q)
             ops.tc_linear(wd, h1q, y2, rows=rows_cap, tiles=l_tiles, n_tiles=l_nt, max_tiles=max_tiles, status=status)
-            peer_ops.combine_push(y2, l_route, l_nr, recv_tbl, f_comb, ctl, done[1:2], H, world, rows_cap, 0)
-            peer_ops.wait_flags(block.peer_ptr(rank, "flags", 16 * 4), world, 1, ctl, 0, status)
-            ops.moe_combine(y_recv[rank * T * k:(rank + 1) * T * k], ident[:T], wts[rank * T:(rank + 1) * T], None, None, out[:T], T, k)
+            peer_ops.combine_push_lanes(y2, l_route, l_nr, recv_tbl.arr, f_comb.arr, ctl, done[1:2], H, k, T, 1, world, rows_cap, 0, status)
+            ops.moe_combine(y_recv, ident_mine, wts[rank * T:(rank + 1) * T], None, None, out[:T], T, k, wait=wait_c)
 
         def step_nccl():
             # baseline: every rank already holds the routing table; exchange bf16 rows with all_to_all, GEMMs local

@@ -43,7 +43,8 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
     if own:
         t_cap = max(16, -(-batch * width // lay["n_micro"]))
         runner = AfdRunner(spec, rank, world, local, t_cap=t_cap, n_pages=batch * (ctx_pages + 1) + 2, max_seqs=max(batch, 1),
-                           max_pages_per_seq=ctx_pages + 1, comm=comm, layout=lay["layout"], attn_groups=lay["attn_groups"], n_micro=lay["n_micro"])
+                           max_pages_per_seq=ctx_pages + 1, comm=comm, layout=lay["layout"], attn_groups=lay["attn_groups"], n_micro=lay["n_micro"],
+                           expert_tp=bool(getattr(args, "expert_tp", False)))
     run = runner
     res = None
     stats = [0.0] * 6

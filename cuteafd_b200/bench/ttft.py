@@ -15,6 +15,41 @@ import time
 import torch
 
 
+def measure_sessions(sched, vocab: int, *, prompt: int, shared: int, sessions: int, decode: int, after_session=None) -> dict:
+    """Runs `sessions` requests one after the other through a scheduler: each prompt = a common prefix of `shared` tokens + its own
+    tail up to `prompt` tokens, then `decode` generated tokens.  Returns per-session time to first token (host clock from submit to
+    the first token, device synchronised) and decode rates.  The first session is the cold prefill; later ones restore the prefix."""
+    from ..serving.scheduler import Request
+    g = torch.Generator().manual_seed(0)
+    common = torch.randint(0, vocab, (shared,), generator=g).tolist()
+    ttfts, outs, decode_s = [], [], []
+    for s in range(sessions):
+        p = common + torch.randint(0, vocab, (prompt - shared,), generator=g).tolist()
+        t_first, toks = [None], []
+        t0 = time.perf_counter()
+
+        def cb(new, done, reason):
+            if new and t_first[0] is None:
+                torch.cuda.synchronize()
+                t_first[0] = time.perf_counter() - t0
+            toks.extend(new)
+        sched.submit(Request(f"s{s}", p, max_tokens=decode, on_token=cb))
+        sched.run_until_idle()
+        torch.cuda.synchronize()
+        total = time.perf_counter() - t0
+        ttfts.append(t_first[0])
+        outs.append(len(toks))
+        decode_s.append(total - (t_first[0] or 0.0))
+        if after_session is not None:
+            after_session(s)
+    warm = sorted(ttfts[1:])
+    dec_tokens = sum(max(0, n - 1) for n in outs)
+    return {"prompt_tokens": prompt, "shared_prefix_tokens": shared, "sessions": sessions, "cold_ttft_s": round(ttfts[0], 4),
+            "cold_prefill_tok_s": round(prompt / ttfts[0], 1), "restore_ttft_s_p50": round(warm[len(warm) // 2], 4) if warm else None,
+            "restore_ttfts_s": [round(t, 4) for t in ttfts[1:]], "decoded_per_session": outs,
+            "decode_tok_s_per_session": round(dec_tokens / max(sum(decode_s), 1e-9), 2)}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen3-235b")
@@ -49,33 +84,12 @@ def main() -> int:
         host = attach_host_tier(eng, a.host_tier_gib)
     cache = PrefixCache(pool, max_entries=64, min_tokens=64, max_cached_pages=n_pages, host=host)
     sched = Scheduler(runner, pool, max_seqs=1, prefill_chunk=a.chunk, prefix=cache)
-    g = torch.Generator().manual_seed(0)
-    shared = torch.randint(0, spec.vocab, (a.shared,), generator=g).tolist()
-    ttfts, outs = [], []
-    for s in range(a.sessions):
-        prompt = shared + torch.randint(0, spec.vocab, (a.prompt - a.shared,), generator=g).tolist()
-        t_first, toks = [None], []
-        t0 = time.perf_counter()
-
-        def cb(new, done, reason):
-            if new and t_first[0] is None:
-                torch.cuda.synchronize()
-                t_first[0] = time.perf_counter() - t0
-            toks.extend(new)
-        sched.submit(Request(f"s{s}", prompt, max_tokens=a.decode, on_token=cb))
-        sched.run_until_idle()
-        ttfts.append(t_first[0])
-        outs.append(len(toks))
-        if host is not None:
-            cache.evict(n_pages)            # the device tier forgets everything: the next session restores from the host tier
+    res = measure_sessions(sched, spec.vocab, prompt=a.prompt, shared=a.shared, sessions=a.sessions, decode=a.decode,
+                           after_session=(lambda s: cache.evict(n_pages)) if host is not None else None)   # host tier: the device tier forgets everything
     eng.check_status()
-    warm = sorted(ttfts[1:])
-    print(json.dumps({"bench": "ttft_prefix_restore", "model": spec.name, "layers": spec.n_layers, "prompt_tokens": a.prompt,
-                      "shared_prefix_tokens": a.shared, "sessions": a.sessions, "cold_ttft_s": round(ttfts[0], 4),
-                      "cold_prefill_tok_s": round(a.prompt / ttfts[0], 1),
-                      "restore_ttft_s_p50": round(warm[len(warm) // 2], 4) if warm else None, "restore_ttfts_s": [round(t, 4) for t in ttfts[1:]],
-                      "decoded_per_session": outs, "prefix_cache": cache.snapshot(),
-                      "host_tier": (dict(host.snapshot(), copy_launches=host.copy.launches) if host is not None else None), "data": "synthetic tokens, random-init weights"}))
+    print(json.dumps(dict(res, bench="ttft_prefix_restore", model=spec.name, layers=spec.n_layers, prefix_cache=cache.snapshot(),
+                          host_tier=(dict(host.snapshot(), copy_launches=host.copy.launches) if host is not None else None),
+                          data="synthetic tokens, random-init weights")))
     return 0
 
 

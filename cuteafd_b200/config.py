@@ -32,6 +32,11 @@ class AttentionSpec:
     v_head_dim: int = 0
     window: int = 0                 # sliding window (0 = full)
     sink: bool = False              # learned attention sink logit per head
+    # Hybrid stacks (MiMo-V2 style: full causal layers interleaved with sliding-window layers that carry the sinks): with
+    # full_every = n > 0, layers i with i % n == 0 are full attention (no window, no sink, `rope_theta`), the others use `window`,
+    # the sink and `swa_rope_theta` (0 = the same theta).  0 = every layer as configured above.
+    full_every: int = 0
+    swa_rope_theta: float = 0.0
 
     @property
     def q_dim(self) -> int:
@@ -96,6 +101,28 @@ class ModelSpec:
 
     def replace(self, **kw) -> "ModelSpec":
         return dataclasses.replace(self, **kw)
+
+    # ---- per-layer attention program ---------------------------------------
+    def layer_is_full(self, layer: int) -> bool:
+        """Full causal attention (True) or the sliding-window variant (False); MTP draft layers (>= n_layers) are full."""
+        a = self.attn
+        if a.full_every <= 0:
+            return a.window == 0
+        return layer >= self.n_layers or layer % a.full_every == 0
+
+    def layer_window(self, layer: int) -> int:
+        a = self.attn
+        return a.window if (a.full_every <= 0 or not self.layer_is_full(layer)) else 0
+
+    def layer_has_sink(self, layer: int) -> bool:
+        a = self.attn
+        return a.sink and (a.full_every <= 0 or not self.layer_is_full(layer))
+
+    def layer_rope_theta(self, layer: int) -> float:
+        a = self.attn
+        if a.full_every > 0 and a.swa_rope_theta and not self.layer_is_full(layer):
+            return a.swa_rope_theta
+        return a.rope_theta
 
     # ---- derived sizes -------------------------------------------------
     def is_moe_layer(self, layer: int) -> bool:
@@ -257,7 +284,17 @@ def from_hf_config(cfg: dict | str | Path) -> ModelSpec:
                              head_dim=cfg.get("head_dim") or hidden // heads,
                              rope_theta=cfg.get("rope_theta", 1e4), rope_interleaved=False,
                              qk_norm=family in ("qwen3_moe", "qwen3_dense"),
-                             window=cfg.get("sliding_window") or 0)
+                             window=cfg.get("sliding_window_size") or cfg.get("sliding_window") or 0)
+        pattern = cfg.get("hybrid_layer_pattern")            # MiMo-V2: 0 = full attention, 1 = sliding window (+ sinks)
+        if pattern is None and cfg.get("layer_types"):
+            pattern = [0 if t == "full_attention" else 1 for t in cfg["layer_types"]]
+        if pattern and any(pattern):
+            full = [i for i, p in enumerate(pattern) if not p]
+            period = (full[1] - full[0]) if len(full) > 1 else len(pattern)
+            if not full or full[0] != 0 or any(bool(p) == (i % period == 0) for i, p in enumerate(pattern)):
+                raise ValueError("unsupported layer pattern: full-attention layers must sit at layer 0 and every n-th layer after it")
+            attn = dataclasses.replace(attn, full_every=period, swa_rope_theta=float(cfg.get("swa_rope_theta") or 0.0),
+                                       sink=bool(cfg.get("add_swa_attention_sink_bias", True)))
     n_exp = cfg.get("n_routed_experts") or cfg.get("num_experts") or cfg.get("num_local_experts") or 0
     moe = MoESpec(
         n_experts=n_exp, top_k=cfg.get("num_experts_per_tok", 1),

@@ -272,18 +272,22 @@ extern "C" int cuteafd_gather_rows(const void* x, const int* src_rows, const int
 // ---------------------------------------------------------------- FP8 wire rows (E4M3 + UE8M0 / 32)
 // Activation hand-off format between attention ranks and expert ranks: BF16-rounded input, amax floor 1e-4,
 // scale = 2^ceil(log2(amax / 448)).  One warp-lane group of 4 threads per 32 elements (8 each).
-__global__ void act_quant_fp8_ue8m0_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int rows, int H) {
+__global__ void act_quant_fp8_ue8m0_kernel(const bf16* __restrict__ x, const int* __restrict__ src_rows, const int* __restrict__ n_rows_dev,
+                                           uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int rows, int H, int ldx, int ldsf) {
+  pdl_launch(); pdl_wait();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int per_row = H / 8;
   if (gid >= (long long)rows * per_row) return;
   const int r = (int)(gid / per_row), c = (int)(gid % per_row);
-  uint4 a = *(const uint4*)(x + (size_t)r * H + c * 8);
+  if (n_rows_dev && r >= *n_rows_dev) return;           // whole groups of 4 lanes leave together (one row per group)
+  const int sr = src_rows ? src_rows[r] : r;
+  uint4 a = *(const uint4*)(x + (size_t)sr * ldx + c * 8);
   const bf16* e = (const bf16*)&a;
   float v[8], amax = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) { v[j] = __bfloat162float(e[j]); amax = fmaxf(amax, fabsf(v[j])); }
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 2));
   amax = fmaxf(amax, 1e-4f);
   const uint8_t sb = ue8m0_ceil(amax / 448.f);
   const float inv = 1.f / ue8m0_to_float(sb);
@@ -291,15 +295,18 @@ __global__ void act_quant_fp8_ue8m0_kernel(const bf16* __restrict__ x, uint8_t* 
 #pragma unroll
   for (int j = 0; j < 4; ++j) { w0 |= (uint32_t)float_to_e4m3(v[j] * inv) << (8 * j); w1 |= (uint32_t)float_to_e4m3(v[4 + j] * inv) << (8 * j); }
   *(uint2*)(q + (size_t)r * H + c * 8) = make_uint2(w0, w1);
-  if ((c & 3) == 0) sf[(size_t)r * (H / 32) + (c >> 2)] = sb;
+  if ((c & 3) == 0) sf[(size_t)r * ldsf + (c >> 2)] = sb;
 }
 
-extern "C" int cuteafd_act_quant_fp8_ue8m0(const void* x, void* q, void* sf, int rows, int H, cudaStream_t s) {
-  CA_REQUIRE(H % 32 == 0, "act_quant_fp8_ue8m0: H must be a multiple of 32");
+// `src_rows` (optional) gathers: output row r quantises input row src_rows[r]; `n_rows_dev` (optional) bounds the live rows
+// on the device; `ldx` is the input row pitch in elements, `ldsf` the scale row pitch in bytes (>= H / 32).
+extern "C" int cuteafd_act_quant_fp8_ue8m0(const void* x, const int* src_rows, const int* n_rows_dev, void* q, void* sf, int rows, int H,
+                                           int ldx, int ldsf, cudaStream_t s) {
+  CA_REQUIRE(H % 32 == 0 && ldsf >= H / 32 && ldx >= H && ldx % 8 == 0, "act_quant_fp8_ue8m0: H %% 32 == 0, scale pitch >= H / 32");
   if (rows <= 0) return CA_OK;
   const long long n = (long long)rows * (H / 8);
-  act_quant_fp8_ue8m0_kernel<<<(int)((n + 255) / 256), 256, 0, s>>>((const bf16*)x, (uint8_t*)q, (uint8_t*)sf, rows, H);
-  CA_CHECK_LAUNCH("act_quant_fp8_ue8m0");
+  CA_LAUNCH_PDL(act_quant_fp8_ue8m0_kernel, (int)((n + 255) / 256), 256, 0, s, (const bf16*)x, src_rows, n_rows_dev, (uint8_t*)q, (uint8_t*)sf,
+                rows, H, ldx, ldsf);
   return CA_OK;
 }
 

@@ -296,7 +296,7 @@ struct DispatchTokArgs {
   FlagPtrs flags;
   const float* inv_gs;
   uint32_t* ctl; uint32_t* done_counter;
-  int T0, T1, T, H, k, E, n_ep, kind, sf_ld;
+  int T0, T1, T, H, k, E, n_ep, kind, sf_ld, broadcast;
   uint32_t step_offset;
   int* status;
 };
@@ -304,6 +304,26 @@ struct DispatchTokArgs {
 __device__ __forceinline__ void quant_row_to_smem(const bf16* xr, int H, int kind, float inv_gs, uint8_t* pay, uint8_t* sfs) {
   if (kind == 0) {
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) ((uint4*)pay)[i] = ((const uint4*)xr)[i];
+    return;
+  }
+  if (kind == 4) {      // FP8 E4M3 + one UE8M0 scale per 32 elements (amax floor 1e-4, scale 2^ceil(log2(amax / 448)))
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+      uint4 a = ((const uint4*)xr)[c];
+      const bf16* e = (const bf16*)&a;
+      float v[8], amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[j] = __bfloat162float(e[j]); amax = fmaxf(amax, fabsf(v[j])); }
+      amax = fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(__activemask(), amax, 2));
+      amax = fmaxf(amax, 1e-4f);
+      const uint8_t sb = ue8m0_ceil(amax / 448.f);
+      const float inv = 1.f / ue8m0_to_float(sb);
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { w0 |= (uint32_t)float_to_e4m3(v[j] * inv) << (8 * j); w1 |= (uint32_t)float_to_e4m3(v[4 + j] * inv) << (8 * j); }
+      ((uint2*)pay)[c] = make_uint2(w0, w1);
+      if ((c & 3) == 0) sfs[c >> 2] = sb;
+    }
     return;
   }
   for (int c = threadIdx.x; c < H / 16; c += blockDim.x) {
@@ -338,7 +358,7 @@ __global__ void dispatch_tok_push_kernel(const DispatchTokArgs a) {
   const int t = a.T0 + blockIdx.x;
   const bool live = t < a.T1 && !a.ctl[0];
   const int H = a.H;
-  const int row_bytes = a.kind == 0 ? H * 2 : H / 2;
+  const int row_bytes = a.kind == 0 ? H * 2 : (a.kind == 4 ? H : H / 2);
   const int n_sf = a.kind == 0 ? 0 : (a.kind == 1 ? H / 16 : H / 32);
   uint8_t* pay = sh; uint8_t* sfs = sh + row_bytes;
   if (threadIdx.x == 0) owners = 0u;
@@ -349,7 +369,8 @@ __global__ void dispatch_tok_push_kernel(const DispatchTokArgs a) {
       const int e = a.idx[(size_t)t * a.k + threadIdx.x];
       int owner = -1;
       for (int o = 0; o < a.n_ep; ++o) if (e >= (o * a.E) / a.n_ep && e < ((o + 1) * a.E) / a.n_ep) owner = o;
-      if (owner < 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, t); else atomicOr(&owners, 1u << owner);
+      if (owner < 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, t);
+      else atomicOr(&owners, a.broadcast ? ((1u << a.n_ep) - 1u) : (1u << owner));   // expert TP: every rank holds a slice of every expert
       for (int d = 0; d < a.n_ep; ++d) ((int*)a.idx_dst.p[d])[(size_t)t * a.k + threadIdx.x] = e;
     }
   }
@@ -374,10 +395,10 @@ __global__ void dispatch_tok_push_kernel(const DispatchTokArgs a) {
 extern "C" int cuteafd_dispatch_tok_push(const void* x, const int* idx, const void* const* slab_q, const void* const* slab_sf,
                                          const void* const* idx_dst, const void* const* lane_t_dst, const void* const* flags,
                                          const float* inv_gs, void* ctl, void* done_counter, int T0, int T1, int T, int H, int k, int E,
-                                         int n_ep, int kind, int sf_ld, unsigned step_offset, int* status, cudaStream_t s) {
+                                         int n_ep, int kind, int sf_ld, int broadcast, unsigned step_offset, int* status, cudaStream_t s) {
   CA_REQUIRE(n_ep >= 1 && n_ep <= MAX_PEERS, "dispatch_tok_push: 1..8 expert ranks");
   CA_REQUIRE(H % 256 == 0 && k >= 1 && k <= 32, "dispatch_tok_push: hidden must be a multiple of 256 and k <= 32");
-  CA_REQUIRE(kind >= 0 && kind <= 2 && (kind == 0 || (slab_sf && sf_ld % 4 == 0)), "dispatch_tok_push: FP4 rows need a scale slab");
+  CA_REQUIRE(((kind >= 0 && kind <= 2) || kind == 4) && (kind == 0 || (slab_sf && sf_ld % 4 == 0)), "dispatch_tok_push: quantised rows need a scale slab");
   CA_REQUIRE(T0 >= 0 && T1 >= T0 && T1 <= T, "dispatch_tok_push: my share [T0, T1) must lie inside the lane's T tokens");
   DispatchTokArgs a;
   a.x = (const bf16*)x; a.idx = idx; a.inv_gs = inv_gs;
@@ -386,9 +407,9 @@ extern "C" int cuteafd_dispatch_tok_push(const void* x, const int* idx, const vo
     a.idx_dst.p[i] = const_cast<void*>(idx_dst[i]); a.lane_t_dst.p[i] = const_cast<void*>(lane_t_dst[i]); a.flags.p[i] = (uint32_t*)flags[i];
   }
   a.ctl = (uint32_t*)ctl; a.done_counter = (uint32_t*)done_counter; a.T0 = T0; a.T1 = T1; a.T = T; a.H = H; a.k = k; a.E = E;
-  a.n_ep = n_ep; a.kind = kind; a.sf_ld = sf_ld; a.step_offset = step_offset; a.status = status;
+  a.n_ep = n_ep; a.kind = kind; a.sf_ld = sf_ld; a.broadcast = broadcast; a.step_offset = step_offset; a.status = status;
   const int blocks = T1 > T0 ? T1 - T0 : 1;
-  const size_t smem = (kind == 0 ? (size_t)H * 2 : (size_t)H / 2 + H / 16);
+  const size_t smem = (kind == 0 ? (size_t)H * 2 : (kind == 4 ? (size_t)H + H / 32 : (size_t)H / 2 + H / 16));
   static bool attr_set[64] = {false};
   int dev = 0; cudaGetDevice(&dev);
   if (smem > 48 * 1024 && !attr_set[dev & 63]) {

@@ -102,13 +102,18 @@ int cuteafd_set_pdl(int mask) {
 int cuteafd_tmap_encode_kmajor(void* out128, const void* base, int elem_bytes, uint64_t k_elems, uint64_t rows,
                                uint64_t groups, uint64_t row_stride_bytes, uint64_t group_stride_bytes,
                                uint32_t box_rows) {
-  CA_REQUIRE(elem_bytes == 1 || elem_bytes == 2, "elem_bytes must be 1 or 2");
+  // elem_bytes 0: packed 4-bit elements (two per byte in global memory) that TMA unpacks into 8-bit containers, 16 elements
+  // per 16-byte chunk, as tcgen05 kind::f8f6f4 / mxf8f6f4 want their sub-byte operands; k_elems then counts 4-bit elements.
+  CA_REQUIRE(elem_bytes == 0 || elem_bytes == 1 || elem_bytes == 2, "elem_bytes must be 0 (packed 4-bit), 1 or 2");
   CA_REQUIRE(box_rows >= 1 && box_rows <= 256, "box_rows out of range");
+  CA_REQUIRE(elem_bytes != 0 || (k_elems % 128 == 0 && row_stride_bytes % 32 == 0 && ((uintptr_t)base & 31) == 0),
+             "packed 4-bit operands need K %% 128 == 0, 32-byte aligned rows and base");
   CUtensorMap m;
-  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : (elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B);
   uint64_t gs = groups > 1 ? group_stride_bytes : row_stride_bytes * rows;
   int rc = ca_encode_tmap_3d(&m, base, dt, k_elems, rows, groups ? groups : 1, row_stride_bytes, gs,
-                             128 / elem_bytes, box_rows, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+                             elem_bytes ? 128 / elem_bytes : 128, box_rows, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   memcpy(out128, &m, sizeof(m));
   return CA_OK;

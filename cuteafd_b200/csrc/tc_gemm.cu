@@ -24,7 +24,10 @@
 #define CA_PDL_CLASS 1
 #include "common.cuh"
 
-enum { KIND_BF16 = 0, KIND_NVFP4 = 1, KIND_MXFP4 = 2 };
+// KIND_W4A8: MXFP4 weights (E2M1 + UE8M0 / 32, unpacked by TMA into 8-bit containers) x FP8 E4M3 activations with UE8M0 / 32
+// scales, kind::mxf8f6f4 (K = 32 per instruction) - the reference's default expert arithmetic
+// (python/tools/aot/export_b12x_v41_experts_aot.py:21-93).  3 is the separate FP8 128x128 block-scaled kernel's kind.
+enum { KIND_BF16 = 0, KIND_NVFP4 = 1, KIND_MXFP4 = 2, KIND_W4A8 = 4 };
 enum { EPI_BF16 = 0, EPI_BF16_RESIDUAL = 1, EPI_F32 = 3 };
 
 struct TcArgs {
@@ -75,7 +78,7 @@ struct TcCfg {
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = TN * 128;
   static constexpr int NBLK = TN > 128 ? 2 : 1;                      // 128-token scale blocks
-  static constexpr int SF_CHUNKS = KIND == KIND_NVFP4 ? 4 : (KIND == KIND_MXFP4 ? 2 : 0);  // 512 B chunks / stage
+  static constexpr int SF_CHUNKS = KIND == KIND_NVFP4 ? 4 : (KIND == KIND_MXFP4 ? 2 : (KIND == KIND_W4A8 ? 1 : 0));  // 512 B chunks / stage
   static constexpr int SFA_BYTES = SF_CHUNKS * 512;
   static constexpr int SFB_BYTES = SF_CHUNKS * 512 * NBLK;
   static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + NA * SFA_BYTES + SFB_BYTES;
@@ -89,7 +92,7 @@ struct TcCfg {
   static constexpr int NACC = (2 * ACC_COLS <= 384) ? 2 : 1;
   static constexpr int TMEM_COLS = OCC == 2 ? 256 : 512;
   static constexpr int SFA_COL = TMEM_COLS - 64, SFA2_COL = TMEM_COLS - 48, SFB_COL = TMEM_COLS - 32;   // tensor-memory columns of the scales
-  static constexpr int K_ELEMS = KIND == KIND_BF16 ? 64 : 256;         // K elements per stage (128 bytes per row)
+  static constexpr int K_ELEMS = KIND == KIND_BF16 ? 64 : (KIND == KIND_W4A8 ? 128 : 256);   // K elements per stage (128 bytes of shared memory per row)
   static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024;
   static_assert(NSTAGE >= 2, "tile too large for shared memory");
   static_assert(ACC_COLS * NACC <= SFA_COL, "accumulators overlap the scale columns");
@@ -101,6 +104,12 @@ __device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) 
     d |= 1u << 4;            // fp32 accumulator
     d |= 1u << 7;            // A = bf16
     d |= 1u << 10;           // B = bf16
+  } else if (kind == KIND_W4A8) {
+    d |= sf_id << 4;         // B scale-factor id: which byte of the 32-bit scale column this K = 32 step uses
+    d |= 5u << 7;            // A = E2M1 (kind::mxf8f6f4 numbering: E4M3 0, E5M2 1, E2M3 3, E3M2 4, E2M1 5)
+    d |= 0u << 10;           // B = E4M3
+    d |= 1u << 23;           // UE8M0 scales
+    d |= sf_id << 29;        // A scale-factor id
   } else {
     d |= sf_id << 4;         // B scale-factor id
     d |= 1u << 7;            // A = E2M1
@@ -287,6 +296,10 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
               const uint32_t id = make_idesc(KIND_NVFP4, TN, 0);
               tc_mma_nvf4(d0, adesc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA_COL + 4 * k, tmem + C::SFB_COL + 4 * C::NBLK * k);
               if (SWIGLU) tc_mma_nvf4(d0 + TN, a2desc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA2_COL + 4 * k, tmem + C::SFB_COL + 4 * C::NBLK * k);
+            } else if (KIND == KIND_W4A8) {
+              const uint32_t id = make_idesc(KIND_W4A8, TN, k);       // one scale column per stage, byte k of it per K = 32 step
+              tc_mma_mxf8f6f4(d0, adesc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA_COL, tmem + C::SFB_COL);
+              if (SWIGLU) tc_mma_mxf8f6f4(d0 + TN, a2desc + 2 * k, bdesc + 2 * k, id, accum, tmem + C::SFA2_COL, tmem + C::SFB_COL);
             } else {
               const uint32_t id = make_idesc(KIND_MXFP4, TN, (k & 1) * 2);
               const int q = k >> 1;
@@ -328,7 +341,33 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
         tmem_ld_x16(tbase + c0, r);
         if (SWIGLU) tmem_ld_x16(tbase + TN + c0, r2);
         tc_wait_ld();
-        if (QOUT && KIND != KIND_BF16 && a.q_out) {
+        if (QOUT && KIND == KIND_W4A8 && a.q_out) {
+          // FP8 output for the next GEMM (E4M3 + one UE8M0 scale per 32 features): this lane holds output feature n of 16
+          // tokens and the 32 lanes of the warp are exactly one scale block, so amax is a warp reduction.  Same arithmetic
+          // as the stand-alone quantiser on the bf16-rounded value (amax floor 1e-4, scale 2^ceil(log2(amax / 448))).
+          if (c0 < nrows) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int c = c0 + j;
+              if (c < nrows) {                       // warp-uniform
+                float v = __uint_as_float(r[j]) * al;
+                if (SWIGLU) {
+                  const float u = __uint_as_float(r2[j]) * al2;
+                  v = v / (1.f + __expf(-v)) * u;
+                }
+                const bf16 vb = __float2bfloat16(n_ok ? v : 0.f);
+                v = __bfloat162float(vb);
+                const float am = fmaxf(warp_max(fabsf(v)), 1e-4f);
+                const uint8_t sb = ue8m0_ceil(am / 448.f);
+                const uint8_t qb = float_to_e4m3(v / ue8m0_to_float(sb));
+                const size_t row = (size_t)(row0 + c);
+                if (n_ok) a.q_out[row * a.N + n] = qb;
+                if (n_ok && lane == 0) a.sf_out[row * a.ldsf_out + n / 32] = sb;
+                if (a.Y && n_ok) ((bf16*)a.Y)[row * a.ldy + n] = vb;
+              }
+            }
+          }
+        } else if (QOUT && KIND != KIND_BF16 && a.q_out) {
           // FP4 output for the next GEMM: this lane holds output feature n of 16 tokens; a quantisation block is 16
           // (NVFP4) or 32 (MXFP4) consecutive features = adjacent lanes, so amax and the nibble packing are shuffles.
           // Same arithmetic as the stand-alone quantiser on the bf16-rounded value.
@@ -755,7 +794,7 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   // [rows, N / 2], scales [rows, ldsf_out]; Y may then be null), and/or stores of the bf16 output tiles into 1-2 peers'
   // buffers (row r -> row peer_row_map[r] when a map is given) with the peers' flags released with step number peer_ctl[1]
   // once the whole GEMM has been written (`peer_done`: a zeroed device counter).
-  CA_REQUIRE(kind >= 0 && kind <= 2, "tc_linear: bad kind %d", kind);
+  CA_REQUIRE((kind >= 0 && kind <= 2) || kind == KIND_W4A8, "tc_linear: bad kind %d", kind);
   void* q_out = extra ? extra->q_out : nullptr; void* sf_out = extra ? extra->sf_out : nullptr;
   const float* inv_gs_out = extra ? extra->inv_gs_out : nullptr; const int ldsf_out = extra ? extra->ldsf_out : 0;
   struct { void* y[2]; void* flags[2]; const int* row_map; void* ctl; void* done; int ld, n; } peer = {};
@@ -787,6 +826,7 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.q_out = (uint8_t*)q_out; a.sf_out = (uint8_t*)sf_out; a.inv_gs_out = inv_gs_out; a.ldsf_out = ldsf_out;
   a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;
   const int n_nt = (N + 127) / 128;
+  if (kind == KIND_W4A8 && !tiles && !swiglu && a.splits > 1 && tn <= 32) a.splits = 1;       // no cluster split-K variant of this kind: one CTA per tile
   if (!tiles && !swiglu && (tn == 16 || tn == 32) && (a.splits == 2 || a.splits == 4 || (a.splits == 8 && tn == 16))) {
     {
       const int grid_c = ((rows_total + tn - 1) / tn) * n_nt * a.splits;
@@ -801,5 +841,6 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   if (grid < 1) grid = 1;
   if (kind == KIND_BF16) return swiglu ? launch_tn<KIND_BF16, true>(tn, a, grid, stream) : launch_tn<KIND_BF16, false>(tn, a, grid, stream);
   if (kind == KIND_NVFP4) return swiglu ? launch_tn<KIND_NVFP4, true>(tn, a, grid, stream) : launch_tn<KIND_NVFP4, false>(tn, a, grid, stream);
+  if (kind == KIND_W4A8) return swiglu ? launch_tn<KIND_W4A8, true>(tn, a, grid, stream) : launch_tn<KIND_W4A8, false>(tn, a, grid, stream);
   return swiglu ? launch_tn<KIND_MXFP4, true>(tn, a, grid, stream) : launch_tn<KIND_MXFP4, false>(tn, a, grid, stream);
 }

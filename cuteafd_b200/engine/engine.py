@@ -275,19 +275,20 @@ class Engine:
         md = self.md
         xq = self._norm_in(lw, L, T)
         self._dense(lw.wqkv, xq, L.qkv, T)
+        window = spec.layer_window(li)                # hybrid stacks: full and sliding-window layers differ in window, sink and theta
         ops.qk_norm_rope_kvwrite(L.qkv, md["positions"], md["slot_map"], lw.q_norm, lw.k_norm, self.kv[li], T,
-                                 a.n_heads, a.n_kv_heads, a.head_dim, a.rope_theta, a.rope_interleaved, spec.rms_eps, self.status)
+                                 a.n_heads, a.n_kv_heads, a.head_dim, spec.layer_rope_theta(li), a.rope_interleaved, spec.rms_eps, self.status)
         fused_q = False
         if self.kv_tmaps is not None:
             fused_q = ops.paged_attention_tc(L.qkv, self.kv_tmaps[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
                                              T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
                                              Hkv=a.n_kv_heads, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
-                                             window=a.window, sink=lw.sink, status=self.status, quant=L.attn_q, inv_gs=lw.wo.inv_act_gs)
+                                             window=window, sink=lw.sink, status=self.status, quant=L.attn_q, inv_gs=lw.wo.inv_act_gs)
         else:
             ops.paged_attention(L.qkv, self.kv[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
                                 T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
                                 Hkv=a.n_kv_heads, D=a.head_dim, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,
-                                window=a.window, sink=lw.sink)
+                                window=window, sink=lw.sink)
         oq = L.attn_q if fused_q else self._quant(L.attn, L.attn_q, T, lw.wo.inv_act_gs)
         self._attn_out(li, lw, oq, L, T)
         self.launches_per_step += 2 + (1 if sh.attn_splits > 1 else 0)

@@ -46,7 +46,7 @@ def layer_stems(spec: ModelSpec, i: int, prefix: str | None = None) -> dict:
         s.update(wq=f"{p}.self_attn.q_proj", wk=f"{p}.self_attn.k_proj", wv=f"{p}.self_attn.v_proj", wo=f"{p}.self_attn.o_proj")
         if a.qk_norm:
             s.update(q_norm=f"{p}.self_attn.q_norm", k_norm=f"{p}.self_attn.k_norm")
-        if a.sink:
+        if spec.layer_has_sink(i):
             s.update(sink=f"{p}.self_attn.sinks")
     if spec.is_moe_layer(i):
         s.update(router=f"{p}.mlp.gate")
@@ -249,9 +249,10 @@ def _tc_from_operands(group: list, device, act_gs: float):
         alpha = torch.tensor([g * act_gs for g in gs], dtype=torch.float32, device=device)
         return TcWeight._finish(K.KIND_NVFP4, G, N, Kd, data, sf, alpha, act_gs)
     if f == "mxfp4":
+        kind = K.KIND_BY_NAME["mxfp4"]          # W4A8 (FP8 activations) or W4A4, same stored payload and scales
         data = torch.stack([rd(o, "blocks").reshape(N, Kd // 2) for o in group]).to(device).contiguous()
-        sf = torch.stack([swizzle_sf(rd(o, "scales").to(device), 8) for o in group]).contiguous()
-        return TcWeight._finish(K.KIND_MXFP4, G, N, Kd, data, sf, torch.ones(G, dtype=torch.float32, device=device), act_gs)
+        sf = torch.stack([swizzle_sf(rd(o, "scales").to(device), K.SF_PER_STAGE[kind]) for o in group]).contiguous()
+        return TcWeight._finish(kind, G, N, Kd, data, sf, torch.ones(G, dtype=torch.float32, device=device), act_gs)
     raise NotImplementedError(f"{group[0].stem}: format {f} has no tensor-core operand form (EXL3 linears load as ops.Exl3Weight)")
 
 

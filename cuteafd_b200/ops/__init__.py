@@ -15,7 +15,12 @@ from . import native
 from .native import call, ptr, stream
 
 KIND_BF16, KIND_NVFP4, KIND_MXFP4, KIND_FP8B = 0, 1, 2, 3      # FP8B: E4M3 with fp32 scales per 128 x 128 (weights) / 1 x 128 (activations)
-KIND_BY_NAME = {"bf16": KIND_BF16, "nvfp4": KIND_NVFP4, "mxfp4": KIND_MXFP4, "fp8_block128": KIND_FP8B}
+KIND_W4A8 = 4      # MXFP4 weights x FP8 E4M3 activations, UE8M0 scales per 32 on both (tcgen05 kind::mxf8f6f4)
+# MXFP4 checkpoints run W4A8 (the reference's default expert arithmetic) unless CUTEAFD_MXFP4_ACT=fp4 asks for FP4 activations
+import os as _os
+MXFP4_ACT = _os.environ.get("CUTEAFD_MXFP4_ACT", "fp4")
+KIND_BY_NAME = {"bf16": KIND_BF16, "nvfp4": KIND_NVFP4, "mxfp4": KIND_W4A8 if MXFP4_ACT == "fp8" else KIND_MXFP4, "mxfp4_w4a4": KIND_MXFP4,
+                "mxfp4_w4a8": KIND_W4A8, "fp8_block128": KIND_FP8B}
 FP4_KINDS = (KIND_NVFP4, KIND_MXFP4)
 EPI_BF16, EPI_BF16_RESIDUAL, EPI_F32 = 0, 1, 3
 SCORING = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}
@@ -39,9 +44,10 @@ def tc_trace(buf: torch.Tensor | None, units: int = 0) -> None:
 
 
 # ------------------------------------------------------------------ TMA descriptors
-def encode_tmap(t: torch.Tensor, box_rows: int) -> torch.Tensor:
+def encode_tmap(t: torch.Tensor, box_rows: int, unpack4: bool = False) -> torch.Tensor:
     """Descriptor array (uint8 [G, 128], on t's device) for a K-major operand [G, rows, K] or [rows, K].
-    bf16 tensors describe K elements; uint8 tensors describe K bytes (packed fp4 / fp8)."""
+    bf16 tensors describe K elements; uint8 tensors describe K bytes (packed fp4 / fp8).  `unpack4`: a uint8 tensor of packed
+    4-bit elements whose tiles TMA expands into 8-bit containers in shared memory (the weight operand of the W4A8 kind)."""
     if t.dim() == 2:
         t = t.unsqueeze(0)
     G, rows, kdim = t.shape
@@ -50,8 +56,11 @@ def encode_tmap(t: torch.Tensor, box_rows: int) -> torch.Tensor:
         raise ValueError("operand must be K-contiguous")
     host = torch.zeros(G, 128, dtype=torch.uint8)
     for g in range(G):
-        call("cuteafd_tmap_encode_kmajor", host[g].data_ptr(), t[g].data_ptr(), eb, kdim, rows, 1,
-             t.stride(1) * eb, 0, box_rows)
+        if unpack4:
+            call("cuteafd_tmap_encode_kmajor", host[g].data_ptr(), t[g].data_ptr(), 0, kdim * 2, rows, 1, t.stride(1), 0, box_rows)
+        else:
+            call("cuteafd_tmap_encode_kmajor", host[g].data_ptr(), t[g].data_ptr(), eb, kdim, rows, 1,
+                 t.stride(1) * eb, 0, box_rows)
     return host.to(t.device)
 
 
@@ -107,7 +116,7 @@ class TcWeight:
                 p, s = quant.mxfp4_quantize(w[g])
                 alphas.append(1.0)
             packs.append(p)
-            sfs.append(swizzle_sf(s, 16 if kind == KIND_NVFP4 else 8))
+            sfs.append(swizzle_sf(s, SF_PER_STAGE[kind]))
         data = torch.stack(packs).to(device).contiguous()
         sf = torch.stack(sfs).to(device).contiguous()
         return TcWeight._finish(kind, G, N, K, data, sf, torch.tensor(alphas, dtype=torch.float32, device=device), act_gs)
@@ -133,7 +142,8 @@ class TcWeight:
             return TcWeight(kind, hi - lo, N, K, data, encode_tmap(data, 128), sw)
         data = cut(torch.randint(0, 256, (G, N, K // 2), dtype=torch.uint8, device=device, generator=gen))
         vec = 16 if kind == KIND_NVFP4 else 32
-        nsf = (-(-N // 128) * 128) * (-(-K // 256) * (256 // vec))
+        kstage = 128 if kind == KIND_W4A8 else 256
+        nsf = (-(-N // 128) * 128) * (-(-K // kstage) * (kstage // vec))
         if kind == KIND_NVFP4:   # E4M3 scales in [0.5, 1.875]
             sf = cut(torch.randint(0x30, 0x40, (G, nsf), dtype=torch.uint8, device=device, generator=gen))
             alpha = torch.full((hi - lo,), std / 3.4 * act_gs, dtype=torch.float32, device=device)
@@ -146,7 +156,7 @@ class TcWeight:
     def _finish(kind, G, N, K, data, sf, alpha, act_gs):
         sf_ptrs = torch.tensor([sf[g].data_ptr() for g in range(G)], dtype=torch.int64, device=data.device)
         inv = torch.tensor([1.0 / act_gs], dtype=torch.float32, device=data.device)
-        return TcWeight(kind, G, N, K, data, encode_tmap(data, 128), sf, sf_ptrs, alpha, inv)
+        return TcWeight(kind, G, N, K, data, encode_tmap(data, 128, unpack4=kind == KIND_W4A8), sf, sf_ptrs, alpha, inv)
 
     def dequantize(self) -> torch.Tensor:
         """fp32 [G, N, K] on CPU, without the activation scale folded into alpha (test helper)."""
@@ -156,9 +166,10 @@ class TcWeight:
         if self.kind == KIND_FP8B:
             return torch.stack([quant.fp8_block_dequantize(self.data[g].cpu(), self.sf[g].cpu()) for g in range(self.G)])
         vec = 16 if self.kind == KIND_NVFP4 else 32
+        kstage = 128 if self.kind == KIND_W4A8 else 256
         out = []
         for g in range(self.G):
-            s = quant.unswizzle_sf_128x4(self.sf[g].cpu(), self.N, -(-self.K // 256) * (256 // vec))[:, :self.K // vec]
+            s = quant.unswizzle_sf_128x4(self.sf[g].cpu(), self.N, -(-self.K // kstage) * (kstage // vec))[:, :self.K // vec]
             if self.kind == KIND_NVFP4:
                 gs = float(self.alpha[g]) * float(self.inv_act_gs[0])
                 out.append(quant.nvfp4_dequantize(self.data[g].cpu(), s, gs))
@@ -187,6 +198,9 @@ class ActBuffer:
         if kind == KIND_FP8B:    # E4M3 bytes + one fp32 scale per row and 128 channels
             data = torch.zeros(rows, K, dtype=torch.uint8, device=device)
             return ActBuffer(kind, rows, K, tn, data, encode_tmap(data, tn), torch.zeros(rows, -(-K // 128), dtype=torch.float32, device=device))
+        if kind == KIND_W4A8:    # E4M3 bytes + one UE8M0 scale per row and 32 channels (scale rows padded to whole 128-channel stages)
+            data = torch.zeros(rows, K, dtype=torch.uint8, device=device)
+            return ActBuffer(kind, rows, K, tn, data, encode_tmap(data, tn), torch.zeros(rows, -(-K // 128) * 4, dtype=torch.uint8, device=device))
         vec = 16 if kind == KIND_NVFP4 else 32
         data = torch.zeros(rows, K // 2, dtype=torch.uint8, device=device)
         sf = torch.zeros(rows, -(-K // 256) * (256 // vec), dtype=torch.uint8, device=device)   # padded to whole stages
@@ -196,6 +210,9 @@ class ActBuffer:
     def wrap_bf16(x: torch.Tensor, tn: int) -> "ActBuffer":
         _chk(x, torch.bfloat16, "x")
         return ActBuffer(KIND_BF16, x.shape[0], x.shape[1], tn, x, encode_tmap(x, tn))
+
+
+SF_PER_STAGE = {KIND_NVFP4: 16, KIND_MXFP4: 8, KIND_W4A8: 4}        # weight block scales per row and pipeline stage
 
 
 def pick_tn(rows: int, swiglu: bool = False) -> int:
@@ -346,6 +363,10 @@ def qk_norm_rope_kvwrite(qkv, positions, slot_map, q_norm, k_norm, kv_cache, T, 
 def quant_fp4_rows(x: torch.Tensor, out: ActBuffer, *, src_rows: torch.Tensor | None = None, n_rows_dev: torch.Tensor | None = None,
                    rows: int | None = None, inv_gs: torch.Tensor | None = None):
     _chk(x, torch.bfloat16, "x")
+    if out.kind == KIND_W4A8:
+        call("cuteafd_act_quant_fp8_ue8m0", ptr(x), ptr(src_rows), ptr(n_rows_dev), ptr(out.data), ptr(out.sf), out.rows if rows is None else rows,
+             out.K, x.stride(0), out.sf.shape[1], stream())
+        return out
     if out.kind == KIND_FP8B:
         if src_rows is not None or n_rows_dev is not None:
             raise ValueError("FP8 activation quantisation has no gather form")
@@ -377,7 +398,7 @@ def l2_prefetch(t):
 
 
 def act_quant_fp8_ue8m0(x, q, sf):
-    call("cuteafd_act_quant_fp8_ue8m0", ptr(x), ptr(q), ptr(sf), x.shape[0], x.shape[1], stream())
+    call("cuteafd_act_quant_fp8_ue8m0", ptr(x), None, None, ptr(q), ptr(sf), x.shape[0], x.shape[1], x.stride(0), sf.shape[1], stream())
 
 
 def silu_mul(g, u, out, limit: float = 0.0):

@@ -32,7 +32,7 @@ _PROTOS = {
     "cuteafd_qk_norm_rope_kvwrite": [P, P, P, P, P, P, I, I, I, I, F, I, F, I, P, P],
     "cuteafd_quant_fp4_rows": [I, P, P, P, P, P, I, I, I, I, P, P],
     "cuteafd_gather_rows": [P, P, P, P, I, I, P],
-    "cuteafd_act_quant_fp8_ue8m0": [P, P, P, I, I, P],
+    "cuteafd_act_quant_fp8_ue8m0": [P, P, P, P, P, I, I, I, I, P],
     "cuteafd_kv_pages_copy": [P, L, I, I, P, I, P, L, I, P],
     "cuteafd_attn_merge": [P, P, P, P, I, I, I, P],
     "cuteafd_router_logits": [P, P, P, I, I, I, P],
@@ -70,7 +70,7 @@ _PROTOS = {
     "cuteafd_peer_copy": [P, P, C.c_size_t, I, P],
     "cuteafd_copy_engine": [P, P, C.c_size_t, P],
     "cuteafd_flag_pingpong": [P, P, C.c_uint, I, I, C.c_ulonglong, P, P, P],
-    "cuteafd_dispatch_tok_push": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
+    "cuteafd_dispatch_tok_push": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
     "cuteafd_combine_push_lanes": [P, P, P, P, P, P, P, I, I, I, I, I, I, C.c_uint, P, P],
     "cuteafd_tc_linear": [I, I, I, P, P, P, P, P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, I, P, P],
 }

@@ -45,7 +45,7 @@ from .. import ops
 from ..config import Deployment, ModelSpec
 from ..engine.engine import Engine, Lane, StepShape
 from ..models.weights import DeviceWeights
-from ..ops import ActBuffer, KIND_BF16, KIND_BY_NAME, KIND_NVFP4, native, pick_tn
+from ..ops import ActBuffer, KIND_BF16, KIND_BY_NAME, KIND_NVFP4, KIND_W4A8, native, pick_tn
 from . import peer_ops
 from .shard import attention_masters, expert_masters, local_attention_spec
 from .symm import SymmetricBlock
@@ -63,6 +63,15 @@ class LanePlan:
     t_cap: int                  # token rows a lane can carry per step
     n_micro: int = 1            # micro-batches per attention group
     merged: bool = False        # expert ranks run all lanes as one grouped GEMM (needs every lane each layer)
+    # Expert TP: every expert rank holds a slice of the intermediate dimension of EVERY expert (instead of whole experts of a
+    # range); rows are broadcast to all expert ranks, each returns per-route partial sums, the attention rank adds the ranks in
+    # fixed order.  One token's experts then stream from all expert ranks at once - the layout for very small batches.
+    expert_tp: bool = False
+
+    @property
+    def planes(self) -> int:
+        """Receive planes per micro-batch on an attention rank (one per expert rank under expert TP)."""
+        return self.dep.ep if self.expert_tp else 1
 
     @property
     def n_lanes(self) -> int:
@@ -87,16 +96,25 @@ def flag_offset(spec: ModelSpec, phase: int, layer: int, slot: int) -> int:
 
 
 def sf_row_bytes(H: int, kind: int) -> int:
-    return 0 if kind == KIND_BF16 else -(-H // 256) * (256 // (16 if kind == KIND_NVFP4 else 32))
+    """Bytes of block scales per dispatched row (padded to whole pipeline stages of the GEMM that reads them)."""
+    if kind == KIND_BF16:
+        return 0
+    if kind == KIND_W4A8:
+        return -(-H // 128) * 4
+    return -(-H // 256) * (256 // (16 if kind == KIND_NVFP4 else 32))
+
+
+def payload_row_bytes(H: int, kind: int) -> int:
+    return H * 2 if kind == KIND_BF16 else (H if kind == KIND_W4A8 else H // 2)
 
 
 def block_regions(spec: ModelSpec, plan: LanePlan, expert_kind: int) -> dict:
     """Symmetric regions (same layout on every rank; each role uses its part)."""
     H, k, L, t = spec.hidden, spec.moe.top_k, plan.n_lanes, plan.t_cap
-    row_bytes = H * 2 if expert_kind == KIND_BF16 else H // 2
+    row_bytes = payload_row_bytes(H, expert_kind)
     return {
         "slab_q": L * t * row_bytes, "slab_sf": max(256, L * t * sf_row_bytes(H, expert_kind)), "idx": L * t * k * 4, "lane_T": 256,
-        "y_recv": plan.n_micro * t * k * H * 2, "tp_recv": plan.n_micro * 2 * t * H * 2,
+        "y_recv": plan.n_micro * plan.planes * t * k * H * 2, "tp_recv": plan.n_micro * 2 * t * H * 2,
         "flags": 3 * n_flag_layers(spec) * NFLAG * 4,
     }
 
@@ -155,7 +173,7 @@ class AttnRankEngine(Engine):
         self.part = torch.zeros(plan.t_cap, H, dtype=torch.bfloat16, device=device)
         if block is not None:
             self.sf_ld = sf_row_bytes(H, expert_kind)
-            row_bytes = H * 2 if expert_kind == KIND_BF16 else H // 2
+            row_bytes = payload_row_bytes(H, expert_kind)
             t = plan.t_cap
             self.lane_tbls = []
             for mb in range(plan.n_micro):
@@ -163,7 +181,12 @@ class AttnRankEngine(Engine):
                 tb = lambda name, off: PtrTable([block.peer_ptr(r, name, off) for r in dep.expert_ranks])
                 self.lane_tbls.append({"slab_q": tb("slab_q", lane * t * row_bytes), "slab_sf": tb("slab_sf", lane * t * self.sf_ld) if self.sf_ld else None,
                                        "idx": tb("idx", lane * t * k * 4), "lane_T": tb("lane_T", lane * 4), "lane": lane})
-            self.y_recv = block.local("y_recv", torch.bfloat16, (plan.n_micro, t * k, H))
+            self.y_recv = block.local("y_recv", torch.bfloat16, (plan.n_micro, plan.planes * t * k, H))
+            if plan.expert_tp:
+                # pseudo-slots of the rank-ordered sum: slot s of rank e reads row e * (t * k) + token * k + s
+                P = plan.planes
+                base = self.identity_rows.view(t, k, 1) + (torch.arange(P, dtype=torch.int32, device=device) * (t * k)).view(1, 1, P)
+                self.identity_rows_tp = base.reshape(t, k * P).contiguous()
             self.tp_recv = block.local("tp_recv", torch.bfloat16, (plan.n_micro, 2, t, H))
 
     def _make_weights(self, spec, device, seed, act_gs, masters):
@@ -405,7 +428,7 @@ class AttnRankEngine(Engine):
         idx = L.r_idx if T else self.identity_rows
         peer_ops.dispatch_tok_push(x, idx, tb["slab_q"].arr, tb["slab_sf"].arr if tb["slab_sf"] else None, tb["idx"].arr, tb["lane_T"].arr,
                                    flags.arr, self.expert_inv_gs.get(li, self.inv_gs), self.ctl, self.done[1:2], t0, t1, T, spec.hidden, m.top_k,
-                                   m.n_experts, self.dep.ep, self.remote_kind, self.sf_ld, 0, self.status)
+                                   m.n_experts, self.dep.ep, self.remote_kind, self.sf_ld, 0, self.status, broadcast=self.plan.expert_tp)
         peer_ops.note_published(flags.addrs)
         self.launches_per_step += 1
         c.shared = None
@@ -426,7 +449,18 @@ class AttnRankEngine(Engine):
             return
         self._next_lw = next_lw
         wait = native.flag_wait(base, self.dep.ep, 1, self.ctl, self.status, peer_ops.wait_ns())
-        self._combine(self.y_recv[c.mb], self.identity_rows, L.r_wts, c.shared, L, T, self.full_spec.moe.top_k, wait=wait)
+        k = self.full_spec.moe.top_k
+        if self.plan.expert_tp:
+            # every expert rank returned a partial sum per route: fold the ranks into the ordered weighted sum (slot-major,
+            # rank-minor, fp32, one rounding) by treating (slot, rank) as k * ranks slots with the slot's weight repeated
+            P = self.plan.planes
+            if getattr(L, "r_wts_x", None) is None:
+                L.r_wts_x = torch.zeros(L.cap, k * P, dtype=torch.float32, device=self.device)
+            L.r_wts_x.view(L.cap, k, P)[:T].copy_(L.r_wts[:T].unsqueeze(-1).expand(T, k, P))
+            self._combine(self.y_recv[c.mb], self.identity_rows_tp, L.r_wts_x, c.shared, L, T, k * P, wait=wait)
+            self.launches_per_step += 2
+            return
+        self._combine(self.y_recv[c.mb], self.identity_rows, L.r_wts, c.shared, L, T, k, wait=wait)
         self.launches_per_step += 1
 
     def _moe_nccl(self, li, lw, L, T):
@@ -532,7 +566,10 @@ class ExpertRankWorker:
         self.spec, self.plan, self.dep, self.rank, self.comm, self.block, self.device = spec, plan, dep, rank, comm, block, device
         self.ep_rank = dep.expert_ranks.index(rank)
         m = spec.moe
-        self.e_lo, self.e_hi = (self.ep_rank * m.n_experts) // dep.ep, ((self.ep_rank + 1) * m.n_experts) // dep.ep
+        if plan.expert_tp:
+            self.e_lo, self.e_hi = 0, m.n_experts           # every expert, a slice of its intermediate dimension
+        else:
+            self.e_lo, self.e_hi = (self.ep_rank * m.n_experts) // dep.ep, ((self.ep_rank + 1) * m.n_experts) // dep.ep
         self.e_local = self.e_hi - self.e_lo
         self.layers = self._make_weights(spec, device, seed, act_gs, masters)         # per layer (main + MTP): (w_gate, w_up, w_down) or None
         self.kind = next(l[0].kind for l in self.layers if l is not None)
@@ -548,16 +585,17 @@ class ExpertRankWorker:
         self.src_token, self.src_route, self.slot_row = i32(rows), i32(rows), i32(n_run * t, k)
         self.counts, self.offsets = i32(self.e_local), i32(self.e_local)
         self.tiles, self.n_tiles, self.n_rows = i32(self.max_tiles, 4), i32(1), i32(1)
+        self.I_local = next(l[0].N for l in self.layers if l is not None)      # intermediate rows this rank computes
         self.xs = ActBuffer.alloc(self.kind, rows, H, self.tn, device)
-        self.h1 = torch.zeros(rows, m.intermediate, dtype=torch.bfloat16, device=device)
-        self.h1_q = (ActBuffer.alloc(self.kind, rows, m.intermediate, self.tn, device) if self.kind != KIND_BF16
+        self.h1 = torch.zeros(rows, self.I_local, dtype=torch.bfloat16, device=device)
+        self.h1_q = (ActBuffer.alloc(self.kind, rows, self.I_local, self.tn, device) if self.kind != KIND_BF16
                      else ActBuffer.wrap_bf16(self.h1, self.tn))
         self.y2 = torch.zeros(rows, H, dtype=torch.bfloat16, device=device)
         self.launches_per_step = 0
         self._keep = []
         if block is not None:
             L = plan.n_lanes
-            row_bytes = H * 2 if self.kind == KIND_BF16 else H // 2
+            row_bytes = payload_row_bytes(H, self.kind)
             self.sf_ld = sf_row_bytes(H, self.kind)
             self.slab_q = block.local("slab_q", torch.uint8, (L, t, row_bytes))
             self.slab_sf = block.local("slab_sf", torch.uint8)[:L * t * self.sf_ld].view(L, t, self.sf_ld) if self.sf_ld else None
@@ -567,21 +605,29 @@ class ExpertRankWorker:
             self.recv_addrs, self.lane_ranks = [], []
             for lane in range(L):
                 g, mb = lane // plan.n_micro, lane % plan.n_micro
+                plane = self.ep_rank if plan.expert_tp else 0
                 for r in dep.group_ranks(g):
-                    self.recv_addrs.append(block.peer_ptr(r, "y_recv", mb * t * k * H * 2))
+                    self.recv_addrs.append(block.peer_ptr(r, "y_recv", (mb * plan.planes + plane) * t * k * H * 2))
                     self.lane_ranks.append((r, mb))
 
     def _make_weights(self, spec, device, seed, act_gs, masters):
         from ..ops import TcWeight
         from ..models.weights import _expert_kind
+        tp = self.plan.expert_tp
+        granule = 128 if KIND_BY_NAME[_expert_kind(spec)] == KIND_W4A8 else 32
         if masters is not None:
             ek = _expert_kind(spec)
             out = []
-            for lw in expert_masters(spec, masters, self.e_lo, self.e_hi):
+            from .shard import expert_tp_masters
+            shards = expert_tp_masters(spec, masters, self.ep_rank, self.dep.ep, granule) if tp else expert_masters(spec, masters, self.e_lo, self.e_hi)
+            for lw in shards:
                 out.append(None if lw is None else tuple(TcWeight.from_master(lw[k], ek, device, act_gs) for k in ("w_gate", "w_up", "w_down")))
             return out
+        if tp:      # synthetic benchmarks: random slices of the padded intermediate dimension (no single-GPU twin to match)
+            from .shard import expert_tp_slice
+            sl = expert_tp_slice(spec.moe.intermediate, self.dep.ep, granule)
+            return _random_expert_layers(spec, device, seed + 100 * (self.ep_rank + 1), act_gs, 0, spec.moe.n_experts, intermediate=sl)
         if spec.attn.kind == "mla":
-            from ..engine.mla import mla_weights_random
             # expert-only layer sets of an MLA model come from the same generator as the attention ranks' (same seeds per layer)
             return _random_expert_layers(spec, device, seed, act_gs, self.e_lo, self.e_hi)
         dw = DeviceWeights.random(spec, device, seed=seed, experts_range=(self.e_lo, self.e_hi), with_attention=False, act_gs=act_gs)
@@ -613,7 +659,7 @@ class ExpertRankWorker:
                        lane_T=self.lane_T[lane0:lane0 + n], t_cap=t)
         ops.route_gather(self.slab_q[lane0:lane0 + n], self.slab_sf[lane0:lane0 + n] if self.slab_sf is not None else None, self.src_token,
                          self.n_rows, self.xs, rows, self.status)
-        if self.kind != KIND_BF16 and m.intermediate % 32 == 0:      # FC1 writes its output quantised for FC2
+        if self.kind != KIND_BF16 and self.I_local % 32 == 0:      # FC1 writes its output quantised for FC2
             ops.tc_linear(w_gate, self.xs, None, rows=rows, w_up=w_up, tiles=self.tiles, n_tiles=self.n_tiles, max_tiles=self.max_tiles,
                           status=self.status, quant_out=self.h1_q, inv_gs_out=w_down.inv_act_gs)
         else:
@@ -680,12 +726,13 @@ class ExpertRankWorker:
             self._layer_nccl(li, T)
 
 
-def _random_expert_layers(spec: ModelSpec, device, seed: int, act_gs: float, e_lo: int, e_hi: int) -> list:
+def _random_expert_layers(spec: ModelSpec, device, seed: int, act_gs: float, e_lo: int, e_hi: int, intermediate: int = 0) -> list:
     """Routed experts [e_lo, e_hi) of every layer of an MLA model (+ its MTP draft layers), generated with the per-layer
     seeds `engine.mla.mla_weights_random` uses, so any expert split holds the experts a single-GPU model would."""
     from ..models.weights import _expert_kind
     from ..ops import TcWeight
     m, h, ek = spec.moe, spec.hidden, _expert_kind(spec)
+    inter = intermediate or m.intermediate
     out = []
     for i in range(spec.n_layers + spec.mtp_layers):
         if not spec.is_moe_layer(i):
@@ -693,7 +740,7 @@ def _random_expert_layers(spec: ModelSpec, device, seed: int, act_gs: float, e_l
             continue
         s = seed * 1000 + i * 32
         RE = lambda N, K, j: TcWeight.random(m.n_experts, N, K, ek, device, spec.init_std, act_gs, s + j, groups=(e_lo, e_hi))
-        out.append((RE(m.intermediate, h, 8), RE(m.intermediate, h, 9), RE(h, m.intermediate, 10)))
+        out.append((RE(inter, h, 8), RE(inter, h, 9), RE(h, inter, 10)))
     return out
 
 

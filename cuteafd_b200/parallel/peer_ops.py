@@ -59,12 +59,13 @@ def combine_push(y, src_route, n_rows, recv_tbl, flag_tbl, ctl, done_counter, H,
 
 
 def dispatch_tok_push(x, idx, slab_q_tbl, slab_sf_tbl, idx_tbl, lane_t_tbl, flag_tbl, inv_gs, ctl, done_counter, T0, T1, T, H, k, E, n_ep, kind,
-                      sf_ld, step_offset, status):
+                      sf_ld, step_offset, status, broadcast: bool = False):
     """Token-major dispatch of rows [T0, T1) of a lane that holds T tokens: each row is quantised once and stored into the slab
-    of every expert rank owning one of its experts; the routing rows and T go to every rank; then one flag per rank."""
+    of every expert rank owning one of its experts (`broadcast`: of every expert rank - they each hold a slice of every
+    expert); the routing rows and T go to every rank; then one flag per rank."""
     call("cuteafd_dispatch_tok_push", ptr(x), ptr(idx), C.addressof(slab_q_tbl), C.addressof(slab_sf_tbl) if slab_sf_tbl is not None else None,
          C.addressof(idx_tbl), C.addressof(lane_t_tbl), C.addressof(flag_tbl), ptr(inv_gs), ptr(ctl), ptr(done_counter), T0, T1, T, H, k, E,
-         n_ep, kind, sf_ld, step_offset, ptr(status), stream())
+         n_ep, kind, sf_ld, 1 if broadcast else 0, step_offset, ptr(status), stream())
 
 
 def combine_push_lanes(y, src_route, n_rows, recv_tbl, flag_tbl, ctl, done_counter, H, k, t_cap, tp, n_dst, rows_cap, step_offset, status):

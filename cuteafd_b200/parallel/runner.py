@@ -31,13 +31,13 @@ OP_STOP, OP_STEP, OP_TIMER_START, OP_TIMER_STOP, OP_MTP, OP_INPUTS = 0, 1, 2, 3,
 class AfdRunner:
     def __init__(self, spec: ModelSpec, rank: int, world: int, local: int, *, t_cap: int, n_pages: int, max_seqs: int,
                  max_pages_per_seq: int, comm: str = "p2p", seed: int = 1, layout: str = "split", attn_groups: int = 1, n_micro: int = 1,
-                 merged: bool | None = None, masters: dict | None = None):
+                 merged: bool | None = None, masters: dict | None = None, expert_tp: bool = False):
         self.spec, self.rank, self.world = spec, rank, world
         self.dev = torch.device("cuda", local)
         self.dep = dep = deployment_by_name(layout, world, attn_groups)
         if comm == "nccl" and (dep.colocated or n_micro > 1):
             raise ValueError("the NCCL-only baseline runs the split layout with one micro-batch")
-        self.plan = LanePlan(dep, t_cap=t_cap, n_micro=n_micro, merged=dep.colocated if merged is None else merged)
+        self.plan = LanePlan(dep, t_cap=t_cap, n_micro=n_micro, merged=dep.colocated if merged is None else merged, expert_tp=expert_tp)
         self.comm = comm
         self.tp_group = dist.new_group(list(dep.attn_ranks)) if comm == "nccl" else None
         self.is_attn, self.is_expert = rank in dep.attn_ranks, rank in dep.expert_ranks
@@ -198,7 +198,7 @@ def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, l
     t_cap = max(16, -(-max_batch // lay["n_micro"]))
     t0 = time.time()
     run = AfdRunner(spec, rank, world, local, t_cap=t_cap, n_pages=pages, max_seqs=max(max_batch, 1), max_pages_per_seq=ctx_pages + 1, comm=comm,
-                    layout=lay["layout"], attn_groups=lay["attn_groups"], n_micro=lay["n_micro"])
+                    layout=lay["layout"], attn_groups=lay["attn_groups"], n_micro=lay["n_micro"], expert_tp=bool(getattr(args, "expert_tp", False)))
     use_graph = comm == "p2p"
     res = None
     dev_ms, setup_s, e2e_s, clk, launches, h2d, d2h = 0.0, 0.0, 0.0, None, 0, 0, 0
@@ -285,7 +285,7 @@ def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, l
             "dtype": f"bf16 activations, {spec.quant.experts} experts / {spec.quant.dense} dense",
             "data": "synthetic token ids, random-init weights, context KV random-filled",
             "config": {"model": spec.name + (f" (DEBUG {args.layers} layers: INVALID)" if args.layers else ""), "global_batch": batch_total,
-                       "seq_len": args.context, "parallelism": f"{dep.describe()}, {lay['n_micro']} micro-batch(es) ({comm})", "layers": spec.n_layers,
+                       "seq_len": args.context, "parallelism": f"{dep.describe()}, {lay['n_micro']} micro-batch(es){', expert TP' if run.plan.expert_tp else ''} ({comm})", "layers": spec.n_layers,
                        "l2": "inputs (weights + KV) far larger than L2; no flush needed", "setup_s": round(setup_s, 1)},
             "clocks": clk,
             "e2e": {"value": round(batch_total * args.steps / e2e, 2), "unit": "tokens/s", "ms_per_step": round(e2e * 1e3 / args.steps, 4),

@@ -68,3 +68,39 @@ def expert_masters(spec: ModelSpec, masters: dict, e_lo: int, e_hi: int) -> list
     for lw in layers:
         out.append({k: lw[k][e_lo:e_hi].contiguous() for k in EXPERT_KEYS} if "w_gate" in lw else None)
     return out
+
+
+def expert_tp_slice(intermediate: int, n_ranks: int, granule: int = 32) -> int:
+    """Rows of the intermediate dimension each rank of an expert-TP group holds: equal slices rounded up to `granule`; the
+    padding beyond the true intermediate size is zero weights (reference: zero-pad of the intermediate dimension to the tile
+    size, native/shared/cuda/expert_pack.cu:9)."""
+    per = -(-intermediate // n_ranks)
+    return -(-per // granule) * granule
+
+
+def expert_tp_masters(spec: ModelSpec, masters: dict, rank: int, n_ranks: int, granule: int = 32) -> list:
+    """Per layer (main layers, then MTP draft layers): rank `rank`'s intermediate-dimension slice of EVERY routed expert -
+    rows [rank * s, (rank + 1) * s) of gate / up and the matching columns of down, zero-padded past the true size - or None.
+    Every rank then returns, per route, a partial sum over its slice; the attention rank adds the ranks in fixed order
+    (reference: expert TP, native/shared/include/cuteafd_experts.h:13-23; cuteafd-transport/src/expert.rs:162-198)."""
+    I = spec.moe.intermediate
+    sl = expert_tp_slice(I, n_ranks, granule)
+    lo, hi = rank * sl, (rank + 1) * sl
+    layers = list(masters["layers"]) + [mw["layer"] for mw in masters.get("mtp", [])]
+    out = []
+    for lw in layers:
+        if "w_gate" not in lw:
+            out.append(None)
+            continue
+        E, _, H = lw["w_gate"].shape
+
+        def rows(w):
+            part = torch.zeros(E, sl, H, dtype=w.dtype)
+            a, b = min(lo, I), min(hi, I)
+            part[:, :b - a] = w[:, a:b]
+            return part
+        down = torch.zeros(E, H, sl, dtype=lw["w_down"].dtype)
+        a, b = min(lo, I), min(hi, I)
+        down[:, :, :b - a] = lw["w_down"][:, :, a:b]
+        out.append({"w_gate": rows(lw["w_gate"]), "w_up": rows(lw["w_up"]), "w_down": down})
+    return out

@@ -45,7 +45,7 @@ def init_layer(spec: ModelSpec, gen: torch.Generator, layer: int, force_dense: b
         if a.qk_norm:
             w["q_norm"] = torch.ones(a.head_dim)
             w["k_norm"] = torch.ones(a.head_dim)
-        if a.sink:
+        if spec.layer_has_sink(layer):
             w["sink"] = _randn(gen, a.n_heads, std=1.0)
     if spec.is_moe_layer(layer) and not force_dense:
         w["router"] = _randn(gen, m.n_experts, h, std=s)
@@ -141,10 +141,12 @@ class RefModel:
             if a.qk_norm:
                 q = ops.rmsnorm(q, lw["q_norm"], spec.rms_eps)
                 k = ops.rmsnorm(k, lw["k_norm"], spec.rms_eps)
-            q = ops.apply_rope(q, pos, a.rope_theta, a.rope_interleaved)
-            k = ops.apply_rope(k, pos, a.rope_theta, a.rope_interleaved)
+            li = key if isinstance(key, int) else spec.n_layers         # MTP draft layers count as layers past the stack
+            theta = spec.layer_rope_theta(li)
+            q = ops.apply_rope(q, pos, theta, a.rope_interleaved)
+            k = ops.apply_rope(k, pos, theta, a.rope_interleaved)
             k, v, kpos = cache.append(key, k, v, pos)
-            o = ops.attention(q, k, v, pos, kpos, window=a.window, sink=lw.get("sink")).reshape(T, -1)
+            o = ops.attention(q, k, v, pos, kpos, window=spec.layer_window(li), sink=lw.get("sink")).reshape(T, -1)
         return x + self._aq(o, "dense") @ lw["wo"].T
 
     def ffn_block(self, lw: dict, x: torch.Tensor, routes_out: list | None = None) -> torch.Tensor:

@@ -4,8 +4,9 @@ A constraint object has `mask(tokens) -> int32 bit words [ceil(vocab / 32)] | No
 what the runner hands to the masked argmax / sampler kernels for rows that carry one.  Two grammars are built in:
 
   * `JsonConstraint`: the completion must be one JSON value (optionally an object / array at the top, for
-    `response_format = json_object`), or follow a `json_schema` in the subset `SchemaPrefix` enforces (types, properties,
-    required, closed objects, items, string enums), then end of sequence;
+    `response_format = json_object`), or follow a `json_schema` in the subset `SchemaPrefix` / `SchemaSet` enforce (types,
+    properties, required, closed objects, items, string enums and `const`, string `pattern`, local `$ref` incl. recursive
+    schemas, `anyOf` / `oneOf` unions), or match a regular expression as a whole (`guided_regex`), then end of sequence;
   * `ChoiceConstraint`: the completion must be exactly one of a list of strings (tool_choice by name, enums).
 
 Both work on the decoded text of single tokens, so they run with any tokenizer that can decode one id at a time.  The
@@ -190,6 +191,9 @@ class JsonPrefix:
                 return False
         return True
 
+    def finished(self) -> bool:
+        return self.complete and not self.stack and self.mode == "after"
+
 
 _FIRST = {"object": "{", "array": "[", "string": '"', "number": "-0123456789", "integer": "-0123456789", "boolean": "tf", "null": "n"}
 
@@ -199,23 +203,46 @@ class SchemaPrefix:
     `response_format` schemas: `type` (also a list of types), `properties`, `required`, `additionalProperties: false`,
     `items`, string `enum`, `integer` vs `number`.  Anything else in a schema is ignored (not enforced)."""
 
-    def __init__(self, schema: dict):
+    def __init__(self, schema: dict, root: dict | None = None):
         self.j = JsonPrefix()
         self.frames: list = []            # [schema, kind, seen keys, key being typed or None]
-        self.cur = schema if isinstance(schema, dict) else {}
+        self.root = root if root is not None else (schema if isinstance(schema, dict) else {})
+        self.cur = resolve_ref(schema if isinstance(schema, dict) else {}, self.root)
         self.enum: list | None = None     # inside a string value restricted to choices: [choices, typed so far]
+        self.pattern: list | None = None  # inside a string value restricted by `pattern`: [compiled regex, typed so far]
         self.integer = False
 
     def copy(self) -> "SchemaPrefix":
         c = SchemaPrefix.__new__(SchemaPrefix)
-        c.j, c.cur, c.integer = self.j.copy(), self.cur, self.integer
+        c.j, c.cur, c.integer, c.root = self.j.copy(), self.cur, self.integer, self.root
         c.frames = [[f[0], f[1], set(f[2]), f[3]] for f in self.frames]
         c.enum = None if self.enum is None else [self.enum[0], self.enum[1]]
+        c.pattern = None if self.pattern is None else [self.pattern[0], self.pattern[1]]
         return c
 
     def signature(self):
         return (self.j.signature(), tuple((id(f[0]), f[1], frozenset(f[2]), f[3]) for f in self.frames), id(self.cur),
-                None if self.enum is None else self.enum[1], self.integer)
+                None if self.enum is None else self.enum[1], None if self.pattern is None else self.pattern[1], self.integer)
+
+    def finished(self) -> bool:
+        return self.j.complete and not self.j.stack and self.j.mode == "after"
+
+    def _sub(self, schema) -> dict:
+        return resolve_ref(schema if isinstance(schema, dict) else {}, self.root)
+
+    def alternatives(self):
+        """At the start of a value whose schema is a union (`anyOf` / `oneOf`): one copy of this state per branch."""
+        if self.j.mode not in ("value", "value_or_end"):
+            return None
+        alts = self.cur.get("anyOf") or self.cur.get("oneOf")
+        if not isinstance(alts, list) or not alts:
+            return None
+        out = []
+        for a in alts:
+            c = self.copy()
+            c.cur = self._sub(a)
+            out.append(c)
+        return out
 
     @property
     def stack(self):
@@ -240,14 +267,22 @@ class SchemaPrefix:
         types = self._types(self.cur)
         if types and not any(ch in _FIRST.get(t, "") for t in types):
             return False
+        if "const" in self.cur and isinstance(self.cur["const"], str) and ch != '"':
+            return False
         if ch == "{":
             self.frames.append([self.cur, "{", set(), None])
         elif ch == "[":
             self.frames.append([self.cur, "[", set(), None])
-            self.cur = self.cur.get("items") if isinstance(self.cur.get("items"), dict) else {}
+            self.cur = self._sub(self.cur.get("items"))
         elif ch == '"':
             e = self.cur.get("enum")
+            if "const" in self.cur and isinstance(self.cur["const"], str):
+                e = [self.cur["const"]]
             self.enum = [[x for x in e if isinstance(x, str)], ""] if isinstance(e, list) and e else None
+            pat = self.cur.get("pattern")
+            self.pattern = None
+            if self.enum is None and isinstance(pat, str):
+                self.pattern = [_compile_pattern(pat), ""]
         elif ch in "-0123456789":
             self.integer = "integer" in types and "number" not in types
         return True
@@ -263,7 +298,11 @@ class SchemaPrefix:
         elif ch == "]" and kind == "[":
             self.frames.pop()
         elif ch == "," and kind == "[":
-            self.cur = schema.get("items") if isinstance(schema.get("items"), dict) else {}
+            self.cur = self._sub(schema.get("items"))
+        elif ch == "," and kind == "{":
+            props = schema.get("properties") if isinstance(schema.get("properties"), dict) else None
+            if props is not None and schema.get("additionalProperties") is False and all(k in seen for k in props):
+                return False                # a closed object with every property written: nothing can follow a comma
         return True
 
     def feed(self, ch: str) -> bool:
@@ -281,7 +320,7 @@ class SchemaPrefix:
                 if key in f[2] or (closed and key not in props):
                     return False
                 f[2].add(key)
-                self.cur = (props or {}).get(key, {}) if isinstance((props or {}).get(key, {}), dict) else {}
+                self.cur = self._sub((props or {}).get(key, {}))
                 f[3] = None
             else:
                 if closed and ch == "\\":
@@ -298,6 +337,17 @@ class SchemaPrefix:
                 self.enum[1] += ch
                 if ch == "\\" or not any(c.startswith(self.enum[1]) for c in self.enum[0]):
                     return False
+        elif m == "string" and self.pattern is not None:
+            rx, typed = self.pattern
+            if ch == '"':
+                if rx is not None and rx.fullmatch(typed) is None:
+                    return False
+                self.pattern = None
+            else:
+                typed += ch
+                if ch == "\\" or (rx is not None and rx.fullmatch(typed, partial=True) is None):
+                    return False
+                self.pattern[1] = typed
         elif ch not in WS:
             if m in ("value", "value_or_end") and not (m == "value_or_end" and ch == "]"):
                 if not self._start_ok(ch):
@@ -312,6 +362,116 @@ class SchemaPrefix:
             if not self.feed(ch):
                 return False
         return True
+
+
+def resolve_ref(schema: dict, root: dict, depth: int = 0) -> dict:
+    """Follows local `$ref`s (`#/$defs/name`, `#/definitions/name`, `#`) to the schema they name; recursive schemas resolve
+    lazily because only the node being entered is resolved."""
+    while isinstance(schema, dict) and isinstance(schema.get("$ref"), str) and depth < 32:
+        ref, node = schema["$ref"], root
+        if not ref.startswith("#"):
+            return {}
+        for part in [p for p in ref[1:].split("/") if p]:
+            node = node.get(part.replace("~1", "/").replace("~0", "~")) if isinstance(node, dict) else None
+            if node is None:
+                return {}
+        schema, depth = node, depth + 1
+    return schema if isinstance(schema, dict) else {}
+
+
+_PATTERNS: dict = {}
+
+
+def _compile_pattern(pat: str):
+    """Compiled `pattern` of a string schema (JSON-schema patterns search unless anchored: an unanchored side may be anything).
+    Prefix decisions use the `regex` module's partial matching.  An invalid pattern is not enforced."""
+    if pat not in _PATTERNS:
+        try:
+            import regex
+            body = pat
+            body = body[1:] if body.startswith("^") else "(?s:.*?)" + body
+            body = body[:-1] if body.endswith("$") and not body.endswith("\\$") else body + "(?s:.*)"
+            _PATTERNS[pat] = regex.compile(body)
+        except Exception:
+            _PATTERNS[pat] = None
+    return _PATTERNS[pat]
+
+
+class SchemaSet:
+    """Several `SchemaPrefix` states followed at once: a schema with `anyOf` / `oneOf` forks one state per branch where the
+    value starts and keeps the branches the text still fits.  Same interface as a single state."""
+
+    def __init__(self, schema: dict | None = None, states: list | None = None):
+        self.states = states if states is not None else [SchemaPrefix(schema)]
+        self._expand()
+
+    def _expand(self):
+        todo, out, guard = list(self.states), [], 0
+        while todo and guard < 256:
+            st = todo.pop()
+            alts = st.alternatives()
+            guard += 1
+            if alts is None:
+                out.append(st)
+            else:
+                todo.extend(alts)
+        uniq = {}
+        for st in out:
+            uniq.setdefault(st.signature(), st)
+        self.states = list(uniq.values())
+
+    def copy(self) -> "SchemaSet":
+        c = SchemaSet.__new__(SchemaSet)
+        c.states = [st.copy() for st in self.states]
+        return c
+
+    def signature(self):
+        return tuple(sorted((repr(st.signature()) for st in self.states)))
+
+    def feed(self, ch: str) -> bool:
+        self.states = [st for st in self.states if st.feed(ch)]
+        self._expand()
+        return bool(self.states)
+
+    def feed_text(self, text: str) -> bool:
+        for ch in text:
+            if not self.feed(ch):
+                return False
+        return True
+
+    @property
+    def complete(self) -> bool:
+        return any(st.complete for st in self.states)
+
+    def finished(self) -> bool:
+        return bool(self.states) and all(st.finished() for st in self.states)
+
+
+class RegexPrefix:
+    """The completion must match a regular expression as a whole (`guided_regex`-style requests)."""
+
+    def __init__(self, pattern: str):
+        import regex
+        self.rx, self.text = regex.compile(pattern), ""
+
+    def copy(self):
+        c = RegexPrefix.__new__(RegexPrefix)
+        c.rx, c.text = self.rx, self.text
+        return c
+
+    def signature(self):
+        return self.text
+
+    def feed_text(self, text: str) -> bool:
+        self.text += text
+        return self.rx.fullmatch(self.text, partial=True) is not None
+
+    @property
+    def complete(self) -> bool:
+        return self.rx.fullmatch(self.text) is not None
+
+    def finished(self) -> bool:
+        return False                    # a longer match may exist; the end of sequence token is allowed once `complete`
 
 
 def _pack_bits(allowed: list[bool]) -> torch.Tensor:
@@ -355,14 +515,16 @@ def token_pieces(tokenizer, vocab_size: int) -> list:
 
 class JsonConstraint(_TextConstraint):
     def __init__(self, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None = None, top: str | None = "object",
-                 schema: dict | None = None):
+                 schema: dict | None = None, regex: str | None = None):
         super().__init__(tokenizer, vocab_size, prompt_len, eos_id)
-        self.top, self.schema = top, schema
+        self.top, self.schema, self.regex = top, schema, regex
         self.state, self.seen = self._fresh(), 0
         self.cache: dict = {}
 
     def _fresh(self):
-        return SchemaPrefix(self.schema) if self.schema else JsonPrefix(self.top)
+        if self.regex:
+            return RegexPrefix(self.regex)
+        return SchemaSet(self.schema) if self.schema else JsonPrefix(self.top)
 
     def _advance(self, tokens):
         gen = tokens[self.prompt_len:]
@@ -378,7 +540,7 @@ class JsonConstraint(_TextConstraint):
         sig = self.state.signature()
         m = self.cache.get(sig)
         if m is None:
-            done = self.state.complete and not self.state.stack and self.state.mode == "after"
+            done = self.state.finished()
             allowed = [False] * self.vocab_size
             if not done:
                 for i, piece in enumerate(self.pieces):
@@ -444,6 +606,9 @@ class ToolCallPrefix:
     def complete(self) -> bool:
         return self.phase == 5
 
+    def finished(self) -> bool:
+        return self.phase == 5
+
     def _literal(self, lit: str, ch: str, nxt: int) -> bool:
         if ch != lit[self.pos]:
             return False
@@ -460,7 +625,7 @@ class ToolCallPrefix:
                 if self.name not in self.tools:
                     return False
                 schema = self.tools[self.name] if isinstance(self.tools[self.name], dict) else {}
-                self.args = SchemaPrefix(dict(schema, type="object"))
+                self.args = SchemaSet(dict(schema, type="object"))      # tool parameter schemas may use $ref / anyOf too
                 self.phase, self.pos = 2, 1              # the quote is the first character of `mid`
                 return True
             self.name += ch
@@ -470,7 +635,7 @@ class ToolCallPrefix:
         if self.phase == 3:
             if not self.args.feed(ch):
                 return False
-            if self.args.complete and not self.args.stack:
+            if self.args.finished():
                 self.phase = 4
             return True
         if self.phase == 4:
@@ -518,8 +683,13 @@ def constraint_from_request(body: dict, tokenizer, vocab_size: int, prompt_len: 
             import json
             return ChoiceConstraint(tokenizer, vocab_size, prompt_len, [json.dumps(e) for e in schema["enum"]], eos_id)
         top = {"object": "object", "array": "array"}.get(schema.get("type"))
-        enforce = any(k in schema for k in ("properties", "items", "required", "type"))
+        enforce = any(k in schema for k in ("properties", "items", "required", "type", "anyOf", "oneOf", "$ref", "const", "pattern"))
         return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, top=top, schema=schema if enforce else None)
+    if kind == "regex" or isinstance(body.get("guided_regex"), str):
+        # the completion as a whole must match a regular expression (vLLM-style `guided_regex`, or response_format.type = "regex")
+        pattern = body.get("guided_regex") or (rf.get("regex") or rf.get("pattern") if isinstance(rf, dict) else None)
+        if isinstance(pattern, str) and pattern:
+            return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, regex=pattern)
     return None
 
 

@@ -64,7 +64,14 @@ def build_split_serving(a, world: int):
     eng = run.engine
     if run.dep.tp > 1:
         run.mirror_inputs(True)
-    atexit.register(lambda: (run.control(OP_STOP), run.close()))
+    def shutdown():
+        """Releases the follower and expert ranks (they leave their loops on OP_STOP); safe to call more than once."""
+        if not getattr(run, "_stopped", False):
+            run._stopped = True
+            run.control(OP_STOP)
+            run.close()
+    run.shutdown = shutdown
+    atexit.register(shutdown)
     pool = PagePool(n_pages)
     runner = attach_pool(EngineRunner(eng, max_rows=a.prefill_batch_tokens), pool)
     host = None

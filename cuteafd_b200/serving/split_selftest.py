@@ -64,10 +64,7 @@ def main() -> int:
     print(f"[serve-selftest] world={world} layout={sched.afd_runner.dep.describe()} prefix_hit_tokens={hit} drafted={drafted} "
           f"{'OK' if ok else 'MISMATCH'} cold={cold} warm={warm} plain={plain} want={want[0]} other={other} other_plain={other_plain} want1={want[1][:8]}",
           flush=True)
-    sched.afd_runner.control(0)                      # OP_STOP: followers and expert ranks leave their loops
-    sched.afd_runner.close()
-    import atexit
-    atexit._clear()
+    sched.afd_runner.shutdown()                      # OP_STOP: followers and expert ranks leave their loops
     dist.destroy_process_group()
     return 0 if ok else 1
 

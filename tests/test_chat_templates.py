@@ -207,3 +207,53 @@ def test_template_round_trip_of_assistant_tool_calls():
         got = parse_completion(t, seg)
         assert [(c["name"], c["arguments"]) for c in got["tool_calls"]] == [("get_weather", {"city": "Oslo", "days": 3, "units": ["C", "F"]})], model
         assert got["content"].strip() == "Looking it up.", model
+
+
+REF_SCHEMA = {"type": "object", "additionalProperties": False, "required": ["v"],
+              "properties": {"v": {"anyOf": [{"type": "integer"}, {"type": "string", "pattern": "^[a-c]+$"}, {"type": "null"}]},
+                             "kind": {"const": "leaf"}, "node": {"$ref": "#/$defs/n"}},
+              "$defs": {"n": {"type": "object", "additionalProperties": False,
+                              "properties": {"next": {"$ref": "#/$defs/n"}, "tag": {"oneOf": [{"type": "boolean"}, {"type": "string", "enum": ["x", "yy"]}]}}}}}
+
+
+def test_schema_refs_unions_const_and_patterns():
+    """`$ref` (recursive), `anyOf` / `oneOf`, `const` and string `pattern` are enforced; prefixes are judged character by character."""
+    from cuteafd_b200.serving.constraints import SchemaSet
+
+    def run(text):
+        s = SchemaSet(REF_SCHEMA)
+        return s.feed_text(text), s.complete
+    assert run('{"v": 12}') == (True, True) and run('{"v": null}') == (True, True) and run('{"v": "abca"}') == (True, True)
+    assert run('{"v": "ab')[0] and not run('{"v": "abd')[0] and not run('{"v": 1.5')[0] and not run('{"v": tr')[0]
+    assert run('{"v": 3, "kind": "leaf"}') == (True, True) and not run('{"v": 3, "kind": "lead')[0] and not run('{"v": 3, "kind": 1')[0]
+    assert run('{"v": 3, "node": {"next": {"next": {"tag": "yy"}}, "tag": true}}') == (True, True)
+    assert not run('{"v": 3, "node": {"next": {"nex": ')[0] and not run('{"v": 3, "node": {"tag": "z')[0] and not run('{"v": 3, "node": {"tag": 7')[0]
+    assert not run('{"node": {}}')[0]                       # required key missing at the close
+
+
+def test_union_schema_random_walk_and_whole_text_regex():
+    tok, rng, done = ByteTokenizer(), random.Random(5), 0
+    for _ in range(12):
+        c, toks = JsonConstraint(tok, 258, 0, eos_id=257, schema=REF_SCHEMA), []
+        for _ in range(500):
+            allowed = [i for i, a in enumerate(unpack_bits(c.mask(toks), 258)) if a]
+            assert allowed
+            closers = [a for a in allowed if a in (257, ord("}"), ord("]"), ord('"'), ord(","), ord(":"))]
+            toks.append(rng.choice(closers) if closers and rng.random() < 0.7 else rng.choice(allowed))
+            if toks[-1] == 257:
+                break
+        if toks[-1] == 257:
+            v = json.loads(tok.decode(toks[:-1]))
+            assert "v" in v and (v["v"] is None or isinstance(v["v"], int) or set(v["v"]) <= set("abc")) and v.get("kind", "leaf") == "leaf"
+            done += 1
+    assert done >= 1
+    # the completion as a whole matches a regular expression
+    c = constraint_from_request({"guided_regex": r"(yes|no), \d{2}"}, tok, 258, 0, 257)
+    toks = []
+    for _ in range(20):
+        allowed = [i for i, a in enumerate(unpack_bits(c.mask(toks), 258)) if a]
+        toks.append(rng.choice(allowed))
+        if toks[-1] == 257:
+            break
+    import re
+    assert toks[-1] == 257 and re.fullmatch(r"(yes|no), \d{2}", tok.decode(toks[:-1]))

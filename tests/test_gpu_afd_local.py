@@ -91,6 +91,29 @@ def test_mla_split_generates_the_single_gpu_tokens():
         assert tokens_agree(flat, want, top2, exact=dep.tp == 1), (dep.describe(), flat, want)
 
 
+@pytest.mark.parametrize("experts", ["nvfp4", "bf16"])
+def test_expert_tp_layouts(experts):
+    """Expert TP: every expert rank holds an intermediate-dimension slice of every expert; rows are broadcast, the attention
+    rank adds the ranks' partial sums in fixed order.  Three expert ranks make the slices uneven (zero-padded)."""
+    from cuteafd_b200.config import Deployment
+    from cuteafd_b200.parallel.afd import LanePlan
+    from cuteafd_b200.parallel.local import LocalWorld, generate_local
+    from cuteafd_b200.parallel.selftest import reference_tokens, tokens_agree
+    spec = tiny_spec().replace(quant=QuantSpec(experts=experts, dense="bf16"))
+    masters = init_weights(spec, 5)
+    prompts = _prompts(spec, 31, n=3)
+    want, top2 = reference_tokens(spec, masters, prompts, 6, DEV)
+    deps = [(default_deployment(2), 1), (Deployment(world=4, attn_ranks=(0,), expert_ranks=(1, 2, 3), colocated=False), 2), (colocated_deployment(2), 1)]
+    for dep, n_micro in deps:
+        plan = LanePlan(dep, t_cap=128, n_micro=n_micro, merged=dep.colocated, expert_tp=True)
+        world = LocalWorld(spec, plan, DEV, n_pages=32, max_seqs=8, max_pages_per_seq=4, masters=masters)
+        groups = [prompts] if dep.attn_groups == 1 else [prompts[:2], prompts[2:]]
+        got = generate_local(world, groups, 6)
+        flat = [o for g in got for o in g]
+        # each rank rounds its partial FC2 sum to bf16 before the ranks are added: a near tie of the reference may flip
+        assert tokens_agree(flat, want, top2, exact=False), (dep.describe(), flat, want)
+
+
 def test_scheduler_refuses_a_wait_without_a_push():
     """The single-GPU scheduler never launches a kernel whose flags nobody publishes: it raises instead."""
     from cuteafd_b200.parallel.local import Deadlock, run_programs

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from cuteafd_b200 import ops
-from cuteafd_b200.ops import ActBuffer, TcWeight, KIND_BF16, KIND_NVFP4, KIND_MXFP4, KIND_FP8B
+from cuteafd_b200.ops import ActBuffer, TcWeight, KIND_BF16, KIND_NVFP4, KIND_MXFP4, KIND_FP8B, KIND_W4A8
 from cuteafd_b200.ref import ops as rops, quant, sampler
 
 pytestmark = pytest.mark.gpu
@@ -104,6 +104,30 @@ def test_tc_linear_fp4_dense(kind, T, N, K):
     assert rel_err(xd, xo) < 2e-2
 
 
+@pytest.mark.parametrize("T,N,K", [(3, 128, 256), (16, 384, 512), (70, 256, 1024), (200, 130, 768), (33, 256, 7168)])
+def test_tc_linear_w4a8_dense(T, N, K):
+    """MXFP4 weights x FP8 activations (kind::mxf8f6f4): against the dequantised operands, and the GPU quantiser against the oracle."""
+    g = torch.Generator().manual_seed(K + T)
+    w = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(T, K, generator=g) * 3.0
+    W = TcWeight.from_master(w, KIND_W4A8, DEV)
+    tn = ops.pick_tn(T)
+    xq = ActBuffer.alloc(KIND_W4A8, T, K, tn, DEV)
+    xb = x.to(torch.bfloat16).to(DEV).contiguous()
+    ops.quant_fp4_rows(xb, xq)
+    y = torch.zeros(T, N, dtype=torch.float32, device=DEV)
+    st = status_word()
+    ops.tc_linear(W, xq, y, status=st)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    xd = _dequant_act(xq, T, W)
+    ref = xd @ W.dequantize()[0].T
+    assert rel_err(y.cpu(), ref) < 2e-3
+    qo, so = quant.act_quant_fp8_ue8m0(xb.float().cpu())
+    assert torch.equal(xq.data.cpu(), qo) and torch.equal(xq.sf.cpu()[:, :K // 32], so)
+    assert rel_err(xd, xb.float().cpu()) < 0.05          # FP8 activations: far closer to the input than FP4 ones
+
+
 @pytest.mark.parametrize("kind", ["bf16", "nvfp4", "mxfp4"])
 @pytest.mark.parametrize("T,splits", [(5, 2), (16, 4), (16, 8), (30, 4), (9, 3)])
 def test_tc_linear_split_k_variants_match_unsplit(kind, T, splits):
@@ -133,7 +157,19 @@ def test_tc_linear_split_k_variants_match_unsplit(kind, T, splits):
     assert torch.equal(y2, y3)
 
 
-@pytest.mark.parametrize("kind", ["bf16", "nvfp4", "mxfp4"])
+def _dequant_act(buf, rows, W):
+    """fp32 rows of an activation buffer as the GEMM reads them (whatever quantiser wrote them)."""
+    K = buf.K
+    if buf.kind == KIND_NVFP4:
+        return quant.nvfp4_dequantize(buf.data[:rows].cpu(), buf.sf[:rows].cpu()[:, :K // 16], 1.0 / float(W.inv_act_gs[0]))
+    if buf.kind == KIND_MXFP4:
+        return quant.mxfp4_dequantize(buf.data[:rows].cpu(), buf.sf[:rows].cpu()[:, :K // 32])
+    vals = quant.e4m3_decode(buf.data[:rows].cpu())
+    sc = quant.ue8m0_decode(buf.sf[:rows].cpu()[:, :K // 32])
+    return (vals.reshape(rows, K // 32, 32) * sc.unsqueeze(-1)).reshape(rows, K)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "nvfp4", "mxfp4", "mxfp4_w4a8"])
 def test_tc_linear_grouped_swiglu_and_down(kind):
     E, H, I, T, k = 8, 256, 256, 37, 2
     g = torch.Generator().manual_seed(3)
@@ -175,8 +211,23 @@ def test_tc_linear_grouped_swiglu_and_down(kind):
     assert torch.equal(src.cpu()[slot.cpu().long()], torch.arange(T).repeat_interleave(k).view(T, k).to(torch.int32))
     dq = lambda W: W.dequantize()
     ref = rops.moe_forward(bf16r(x), dq(Wg), dq(Wu), dq(Wd), idx.long(), wts)
-    tol = 3e-2 if kind == "bf16" else 0.25      # fp4 activations are re-quantised twice on the GPU path
+    tol = 3e-2 if kind == "bf16" else 0.25      # quantised activations: loose end-to-end bound, the exact check follows
     assert rel_err(out.float().cpu() - resid.float().cpu(), ref) < tol
+    if Wg.kind != KIND_BF16:
+        # exact oracle: dequantise the rows the GPU quantisers wrote (packed order) and multiply by the dequantised weights;
+        # a wrong scale column, a swapped nibble or a mis-tiled expert cannot hide behind quantisation noise here
+        e_of_row = torch.empty(rows, dtype=torch.long)
+        for t in range(T):
+            for j in range(k):
+                e_of_row[int(slot[t, j])] = int(idx[t, j])
+        xd = _dequant_act(xs, rows, Wg)
+        g1 = torch.einsum("rh,rih->ri", xd, dq(Wg)[e_of_row])
+        u1 = torch.einsum("rh,rih->ri", xd, dq(Wu)[e_of_row])
+        h1_ref = torch.nn.functional.silu(g1) * u1
+        assert rel_err(h1.float().cpu(), h1_ref) < 6e-3          # bf16 output rounding
+        hd = _dequant_act(h1q, rows, Wd)
+        y2_ref = torch.einsum("ri,rhi->rh", hd, dq(Wd)[e_of_row])
+        assert rel_err(y2.float().cpu(), y2_ref) < 6e-3
     if Wg.kind != KIND_BF16:
         # FC1 can write its output already quantised for FC2: same bytes as bf16 output + stand-alone quantiser
         h1f, h1qf = torch.zeros_like(h1), ActBuffer.alloc(Wg.kind, rows, I, tn, DEV)
@@ -186,6 +237,7 @@ def test_tc_linear_grouped_swiglu_and_down(kind):
         torch.cuda.synchronize()
         nsf = I // (16 if Wg.kind == KIND_NVFP4 else 32)
         assert int(st[0]) == 0 and torch.equal(h1f, h1)
+        assert torch.equal(h1qf.data[:rows], h1q.data[:rows]), "fused FC1 quantised output differs from the stand-alone quantiser"
         for o in (h1qf, h1qn):
             assert torch.equal(o.data, h1q.data) and torch.equal(o.sf[:, :nsf], h1q.sf[:, :nsf])
 
@@ -644,3 +696,45 @@ def test_router_logits_simt_matches_fp32_matmul(T, E, H):
     ref = x[:T].float() @ w.to(torch.bfloat16).float().t()
     assert torch.allclose(logits[:T].cpu(), ref, atol=2e-3, rtol=2e-3)
     assert bool((logits[T:] == 7.0).all())                     # rows beyond T are not touched
+
+
+def test_hash_router_and_route_gather():
+    """Hash routing (experts fixed per token id, sqrt-softplus gate weights) against the oracle, and the byte-row gather that
+    puts token-major dispatched rows into expert order."""
+    T, E, k, V = 9, 32, 4, 50
+    g = torch.Generator().manual_seed(2)
+    logits = torch.randn(T, E, generator=g) * 2
+    tid2eid = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(V)]).to(torch.int32)
+    tokens = torch.randint(0, V, (T,), generator=g).to(torch.int32)
+    idx, wts = torch.zeros(T, k, dtype=torch.int32, device=DEV), torch.zeros(T, k, device=DEV)
+    st = status_word()
+    ops.router_hash_select(logits.to(DEV), tid2eid.to(DEV), tokens.to(DEV), idx, wts, T, k, route_scale=1.5, status=st)
+    torch.cuda.synchronize()
+    want_idx = rops.hash_route(tokens, tid2eid)
+    sc = torch.sqrt(torch.nn.functional.softplus(logits.gather(1, want_idx.long())))
+    want_w = sc / sc.sum(-1, keepdim=True) * 1.5
+    assert int(st[0]) == 0 and torch.equal(idx.cpu(), want_idx.to(torch.int32)) and torch.allclose(wts.cpu(), want_w, atol=1e-5)
+    # gather: payload rows of 64 bytes + 8 scale bytes
+    rows, n = 12, 7
+    src_q = torch.randint(0, 255, (rows, 64), dtype=torch.uint8, generator=g).to(DEV)
+    src_sf = torch.randint(0, 255, (rows, 8), dtype=torch.uint8, generator=g).to(DEV)
+    order = torch.tensor([5, 0, 11, 3, 3, 7, 1, 0, 0, 0, 0, 0], dtype=torch.int32, device=DEV)
+    dst = ActBuffer.alloc(KIND_MXFP4, rows, 256, 16, DEV)
+    dst.data.fill_(9)
+    ops.route_gather(src_q, src_sf, order, torch.tensor([n], dtype=torch.int32, device=DEV), dst, rows, st)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    assert torch.equal(dst.data[:n, :64].cpu(), src_q.cpu()[order.cpu()[:n].long()]) and torch.equal(dst.sf[:n, :8].cpu(), src_sf.cpu()[order.cpu()[:n].long()])
+    assert bool((dst.data[n:] == 9).all())
+
+
+def test_mtp_round_uses_device_acceptance():
+    """`verify_accept` on the device agrees with the host rule for every acceptance length."""
+    from cuteafd_b200.ref.ops import greedy_verify
+    inputs = [[5, 6, 7, 8], [5, 6, 7, 8], [1, 2, 3, 4], [9, 9, 9, 9]]
+    target = [[6, 7, 9, 1], [6, 7, 8, 2], [9, 9, 9, 9], [9, 9, 9, 3]]
+    acc, emit = torch.zeros(4, dtype=torch.int32, device=DEV), torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.verify_accept(torch.tensor(inputs, dtype=torch.int32, device=DEV), torch.tensor(target, dtype=torch.int32, device=DEV), None, acc, emit)
+    for i in range(4):
+        a, emitted, _, _ = greedy_verify(inputs[i], target[i], None, 1 << 30)
+        assert int(acc[i]) == a and int(emit[i]) == len(emitted)

@@ -59,3 +59,38 @@ def test_decode_graph_replay_matches_eager():
     b = generate(eng, prompts, 8, use_graph=True)
     assert a == b
     assert eng.graph_captures >= 1
+
+
+@pytest.mark.parametrize("head_dim,heads,kv", [(32, 8, 2), (128, 4, 2)])
+def test_hybrid_full_and_sliding_window_stack_matches_oracle(head_dim, heads, kv):
+    """MiMo-V2-style stack: layers 0, 2 are full causal attention, layers 1, 3 slide a 16-token window with per-head sinks and
+    their own RoPE base.  Prompts longer than the window, on both attention kernels (SIMT for 32-wide heads, tcgen05 for 128)."""
+    import dataclasses
+    base = tiny_spec()
+    spec = base.replace(n_layers=4, attn=dataclasses.replace(base.attn, n_heads=heads, n_kv_heads=kv, head_dim=head_dim, window=16, sink=True,
+                                                             full_every=2, swa_rope_theta=5000.0))
+    assert [spec.layer_window(i) for i in range(5)] == [0, 16, 0, 16, 0] and [spec.layer_has_sink(i) for i in range(4)] == [False, True, False, True]
+    masters = init_weights(spec, 3)
+    assert "sink" not in masters["layers"][0] and "sink" in masters["layers"][1]
+    dw = DeviceWeights.from_masters(spec, masters, DEV)
+    eng = Engine(dw, n_pages=32, max_seqs=8, max_pages_per_seq=4)
+    ref = RefModel(spec, dw.dequantized_masters())
+    prompts = _prompts(spec, 2, 50)
+    gen = BatchGenerator(eng)
+    gen.prefill(prompts)
+    lane = eng.lane(100)
+    torch.cuda.synchronize()
+    eng.check_status()
+    for i, p in enumerate(prompts):
+        rl, _ = ref.forward(torch.tensor(p), 0, RefCache())
+        got = lane.logits[i].float().cpu()
+        assert float((got - rl[-1]).norm() / rl[-1].norm()) < 0.05
+    gen.release()
+    out = generate(eng, prompts, 10)
+    for i, p in enumerate(prompts):
+        want, rows = ref.generate_greedy(torch.tensor(p), 10)
+        for j, (a, b) in enumerate(zip(out[i], want)):
+            if a != b:
+                top2 = rows[j].topk(2).values
+                assert float(top2[0] - top2[1]) < 0.05, f"prompt {i} step {j}: {a} != {b}"
+                break

@@ -206,3 +206,33 @@ def test_exl3_greedy_encoder_tracks_target_and_hadamard_is_orthonormal():
     assert np.allclose(exl3.hadamard128(exl3.hadamard128(x)), x, atol=1e-10)
     w = exl3.dequantize(tr, np.ones(128), np.ones(128))
     assert w.shape == (128, 128)
+
+
+def test_hybrid_layer_pattern_facts_and_config_detection():
+    """Full / sliding-window layer pattern: per-layer window, sink and RoPE base, read from a MiMo-V2-style config."""
+    import dataclasses
+    from cuteafd_b200.config import from_hf_config, tiny_spec
+    base = tiny_spec()
+    spec = base.replace(n_layers=6, attn=dataclasses.replace(base.attn, window=8, sink=True, full_every=3, swa_rope_theta=777.0))
+    assert [spec.layer_is_full(i) for i in range(7)] == [True, False, False, True, False, False, True]
+    assert spec.layer_rope_theta(0) == base.attn.rope_theta and spec.layer_rope_theta(1) == 777.0
+    cfg = {"architectures": ["MiMoV2FlashForCausalLM"], "hidden_size": 256, "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 32,
+           "num_hidden_layers": 6, "vocab_size": 100, "hybrid_layer_pattern": [0, 1, 1, 0, 1, 1], "sliding_window_size": 128,
+           "rope_theta": 5e6, "swa_rope_theta": 1e4, "n_routed_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 64,
+           "scoring_func": "sigmoid"}
+    s = from_hf_config(cfg)
+    assert s.family == "mimo_v2" and s.attn.full_every == 3 and s.attn.window == 128 and s.attn.sink and s.attn.swa_rope_theta == 1e4
+    import pytest
+    with pytest.raises(ValueError):
+        from_hf_config(dict(cfg, hybrid_layer_pattern=[0, 1, 0, 0, 1, 1]))
+    # the window changes what the oracle computes beyond its length, and only in the sliding layers
+    import torch
+    from cuteafd_b200.ref.model import RefCache, RefModel, init_weights
+    small = base.replace(n_layers=2, attn=dataclasses.replace(base.attn, window=4, sink=True, full_every=2))
+    w = init_weights(small, 1)
+    toks = torch.arange(12) % small.vocab
+    a, _ = RefModel(small, w).forward(toks, 0, RefCache())
+    full = small.replace(attn=dataclasses.replace(small.attn, window=0, full_every=0, sink=False))
+    w2 = {**w, "layers": [{k: v for k, v in l.items() if k != "sink"} for l in w["layers"]]}
+    b, _ = RefModel(full, w2).forward(toks, 0, RefCache())
+    assert not torch.allclose(a[-1], b[-1], atol=1e-4)
