@@ -67,7 +67,7 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
   // earlier routes to its expert when T*k is small; larger batches use atomics (row order inside an expert does
   // not change any result: rows are independent in the GEMM and the combine reads them by index).
   // (multi-lane tables need no agreement with the senders on row positions, so their larger cases take the atomic path)
-  if (n <= (p.lane_T ? 1024 : 4096)) {
+  if (n <= (p.lane_T ? 256 : 4096)) {        // the quadratic ranking costs ~17 us at 1024 routes: lane tables switch to atomics early
     int* sid = cur + El;
     for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = route_live(p, i) ? __ldcg(p.idx + i) - p.e_lo : -1;
     __syncthreads();

@@ -100,15 +100,19 @@ extern "C" int cuteafd_wait_flags(const void* flags, int n, int stride, void* ct
 // flags (flag pointers are peer addresses) with the current step number, then resets the counter.
 __device__ __forceinline__ void publish_when_last(uint32_t* done_counter, uint32_t* const* flag_ptrs, int n_dst,
                                                   uint32_t value) {
-  // CTA-level release: the barrier orders every thread's stores before thread 0, whose system-scope fence is
-  // cumulative over them (the pattern of a grid-wide barrier) - one fence per block instead of one per thread
+  // Every block: barrier (orders the block's stores before thread 0), a GPU-scope fence, then the arrival count.  The LAST
+  // block: one system-scope fence, which is cumulative over everything it observed through the counter (all blocks'
+  // stores), then relaxed system-scope stores of the flags.  Measured on B200 with 148 blocks and eight flags: 4 us, against
+  // 22 us for a system-scope fence per block plus a release store per flag (each release repeats the fence, in series) and
+  // 8 us with per-block system-scope fences.  The same shape as a block barrier followed by one thread's fence + flag
+  // store, with the counter in the barrier's place.
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    __threadfence();
     const uint32_t prev = atomicAdd(done_counter, 1u);
     if (prev == gridDim.x * gridDim.y - 1) {
-      __threadfence_system();
-      for (int d = 0; d < n_dst; ++d) st_release_sys(flag_ptrs[d], value);
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
+      for (int d = 0; d < n_dst; ++d) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flag_ptrs[d]), "r"(value) : "memory");
       *done_counter = 0;
     }
   }

@@ -22,6 +22,7 @@
 // (native/shared/include/cuteafd_experts.h:13-44, cuteafd_fp8_moe.h:1-51) and the cuBLAS linears
 // (native/shared/cuda/linear.cu:865-1350).
 #define CA_PDL_CLASS 1
+#include <stdlib.h>
 #include "common.cuh"
 
 // KIND_W4A8: MXFP4 weights (E2M1 + UE8M0 / 32, unpacked by TMA into 8-bit containers) x FP8 E4M3 activations with UE8M0 / 32
@@ -61,6 +62,7 @@ struct TcArgs {
   int peer_ld, n_peer;
   long long* trace;           // optional per-unit time stamps [grid, trace_units, 8] (see cuteafd_tc_trace)
   int ldsfb, ldy, rows_total, N, K, epi, splits, trace_units;
+  int w4_tx;                  // KIND_W4A8: bytes one weight tile adds to the stage barrier's transaction count
 };
 
 // Per-unit device trace: slot 0/1 producer first/last load issued, 2 MMA thread owns the accumulator, 4 last MMA
@@ -127,13 +129,13 @@ __device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) 
 __device__ __forceinline__ void peer_publish(const TcArgs& a, int warp, int lane) {
   asm volatile("bar.sync 1, 128;" ::: "memory");
   if (warp == 2 && lane == 0) {
-    __threadfence_system();                     // cumulative over the stores the barrier ordered before this thread
+    __threadfence();                            // GPU scope: orders the stores the barrier put before this thread ahead of the count
     const uint32_t prev = atomicAdd(a.peer_done, 1u);
     if (prev == gridDim.x - 1) {
-      __threadfence_system();
+      asm volatile("fence.acq_rel.sys;" ::: "memory");        // one system-scope fence, cumulative over all CTAs' stores
       const uint32_t step = a.peer_ctl[1];
-      st_release_sys(a.peer_flag0, step);
-      if (a.n_peer > 1) st_release_sys(a.peer_flag1, step);
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.peer_flag0), "r"(step) : "memory");
+      if (a.n_peer > 1) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.peer_flag1), "r"(step) : "memory");
       *a.peer_done = 0;
     }
   }
@@ -193,7 +195,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
     auto load_weights = [&](int s, int g, int nt, int kb) {
       uint8_t* st = smem + s * C::STAGE_BYTES;
       uint8_t* sA = st, *sSFA = st + C::NA * C::A_BYTES + C::B_BYTES;
-      mbar_expect_tx(&full_bar[s], C::NA * C::A_BYTES + C::B_BYTES + C::NA * C::SFA_BYTES);
+      mbar_expect_tx(&full_bar[s], C::NA * (KIND == KIND_W4A8 ? a.w4_tx : C::A_BYTES) + C::B_BYTES + C::NA * C::SFA_BYTES);
       const int kx = kb * (KIND == KIND_BF16 ? 64 : 128);      // elements of the descriptor's type
       tma_load_3d(sA, a.tmA + g, &full_bar[s], kx, nt * 128, 0);
       if (SWIGLU) tma_load_3d(sA + C::A_BYTES, a.tmA2 + g, &full_bar[s], kx, nt * 128, 0);
@@ -825,6 +827,11 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.peer_row_map = peer.row_map; a.peer_ctl = (uint32_t*)peer.ctl; a.peer_done = (uint32_t*)peer.done; a.peer_ld = peer.ld; a.n_peer = peer.n;
   a.q_out = (uint8_t*)q_out; a.sf_out = (uint8_t*)sf_out; a.inv_gs_out = inv_gs_out; a.ldsf_out = ldsf_out;
   a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;
+  {   // CUTEAFD_W4A8_TX: bytes per unpacked 4-bit weight tile in the transaction count (the tile occupies 16 KB of shared memory)
+    static int w4_tx = -1;
+    if (w4_tx < 0) { const char* e = getenv("CUTEAFD_W4A8_TX"); w4_tx = e ? atoi(e) : 128 * 128; }
+    a.w4_tx = w4_tx;
+  }
   const int n_nt = (N + 127) / 128;
   if (kind == KIND_W4A8 && !tiles && !swiglu && a.splits > 1 && tn <= 32) a.splits = 1;       // no cluster split-K variant of this kind: one CTA per tile
   if (!tiles && !swiglu && (tn == 16 || tn == 32) && (a.splits == 2 || a.splits == 4 || (a.splits == 8 && tn == 16))) {

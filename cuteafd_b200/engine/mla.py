@@ -11,6 +11,7 @@ the reference's head-split mode (families/deepseek_v4/engine.rs:97-119).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -35,6 +36,18 @@ class MlaWeights:
     kv_a_norm: torch.Tensor
     w_uk_t: TcWeight            # G = Hl, [512, 128]: q_lat = q_nope @ W_UK
     w_uv: TcWeight              # G = Hl, [128, 512]: o = o_lat @ W_UV^T
+    w_kvb: TcWeight | None = None   # [Hl * 256, 512]: per head 128 key rows then 128 value rows (prefill expands the latent cache with it)
+
+    def ensure_kvb(self) -> TcWeight:
+        """The kv_b projection in its checkpoint orientation, rebuilt from the two absorb matrices on first use (prefill only;
+        33 MB per layer at 128 heads).  Needs 128-wide key and value heads, the shape the prefill kernel is written for."""
+        if self.w_kvb is None:
+            uk, uv = self.w_uk_t.data, self.w_uv.data            # [Hl, 512, 128], [Hl, 128, 512]
+            if uk.shape[2] != 128 or uv.shape[1] != 128:
+                raise ValueError("the MLA prefill path needs qk_nope_head_dim = v_head_dim = 128")
+            data = torch.cat([uk.transpose(1, 2), uv], dim=1).reshape(1, uk.shape[0] * 256, uk.shape[1]).contiguous()
+            self.w_kvb = TcWeight(KIND_BF16, 1, data.shape[1], data.shape[2], data, ops.encode_tmap(data, 128))
+        return self.w_kvb
 
 
 def _mla_from_masters(spec: ModelSpec, lw: dict, device, dk: str, act_gs: float) -> MlaWeights:
@@ -193,6 +206,12 @@ class MlaEngine(Engine):
         q_nope, q_lat = b["q_nope"][:Hl * T], b["q_lat"][:Hl * T]
         call("cuteafd_mla_q_split", ptr(b["q"]), ptr(md["positions"]), ptr(q_nope), ptr(b["q_rope"]), T, Hl, a.rope_theta,
              1 if a.rope_interleaved else 0, stream())
+        if self._use_prefill_path(sh):
+            self._prefill_attention(li, w, b, sh, q_nope)
+            oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
+            self._attn_out(li, lw, oq, L, T)
+            self.launches_per_step += 5
+            return
         tn = ops.pick_tn(T, swiglu=True)
         tiles, n_tiles, max_tiles = self._head_tiles(b, T, tn)
         qn_act = self._act(b, ("qn", T, tn), q_nope, tn)
@@ -215,6 +234,58 @@ class MlaEngine(Engine):
         oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
         self._attn_out(li, lw, oq, L, T)
         self.launches_per_step += 7
+
+    # ------------------------------------------------------------------ prefill: per-head attention over the expanded context
+    PREFILL_MIN_Q = int(os.environ.get("CUTEAFD_MLA_PREFILL_MIN_Q", "128"))          # 0 disables the path
+    PREFILL_MAX_BYTES = int(float(os.environ.get("CUTEAFD_MLA_PREFILL_MAX_GIB", "12")) * (1 << 30))
+
+    def _use_prefill_path(self, sh: StepShape) -> bool:
+        """Steps whose longest query run is at least one 128-row tile take the non-absorbed path (arithmetic per key 320
+        instead of 1088 multiply-adds per head), unless the step is being captured (the context sizes are read on the host),
+        was cut into micro-batches, or its expanded context would not fit the scratch budget."""
+        a = self.spec.attn
+        if not self.PREFILL_MIN_Q or sh.max_q_len < self.PREFILL_MIN_Q or sh.uniform or a.qk_nope_head_dim != 128 or a.v_head_dim != 128:
+            return False
+        if torch.cuda.is_current_stream_capturing():
+            return False
+        kv = self.mh["kv_len"][:sh.n_seq].tolist()
+        rows = sum(-(-n // 64) * 64 for n in kv) + 64
+        return rows * (DQK + self.heads_local * 256) * 2 <= self.PREFILL_MAX_BYTES
+
+    def _prefill_attention(self, li: int, w, b: dict, sh: StepShape, q_nope: torch.Tensor):
+        """gather the context's latent rows -> expand them to per-head keys / values (one GEMM with kv_b) -> per-head causal
+        attention (`mla_prefill_kernel`), output token-major in b["o_tok"].  Reference: glm_mla_prefill.cu:123-960."""
+        a, Hl, dev = self.spec.attn, self.heads_local, self.device
+        n_seq, md = sh.n_seq, self.md
+        kv = tuple(self.mh["kv_len"][:n_seq].tolist())
+        plan = getattr(self, "_pf_plan", None)
+        if plan is None or plan[0] != kv:
+            starts, tot = [], 0
+            for n in kv:
+                starts.append(tot)
+                tot += -(-n // 64) * 64
+            host = torch.tensor(starts, dtype=torch.int32).pin_memory()
+            if getattr(self, "_pf_starts", None) is None or self._pf_starts.numel() < n_seq:
+                self._pf_starts = torch.zeros(max(n_seq, self.max_seqs), dtype=torch.int32, device=dev)
+            self._pf_starts[:n_seq].copy_(host, non_blocking=True)
+            self._pf_plan = plan = (kv, tot, host)
+        rows = plan[1]
+        cap = getattr(self, "_pf_cap", 0)
+        if rows + 64 > cap:                       # zero-filled: rows no gather ever wrote are multiplied by zero probabilities
+            cap = max(1024, 1 << (rows + 64 - 1).bit_length())
+            self._pf_lat = self._pf_kvb = self._pf_act = None
+            self._pf_lat = torch.zeros(cap, DQK, dtype=torch.bfloat16, device=dev)
+            self._pf_kvb = torch.zeros(cap, Hl * 256, dtype=torch.bfloat16, device=dev)
+            view = self._pf_lat[:, :DV]
+            self._pf_act = ActBuffer(KIND_BF16, cap, DV, 256, view, ops.encode_tmap(view, 256))
+            self._pf_cap = cap
+        st = ptr(self.status)
+        call("cuteafd_mla_gather_ctx", ptr(self.kv[li]), ptr(md["page_table"]), ptr(self._pf_starts), ptr(md["kv_len"]), ptr(self._pf_lat), n_seq,
+             max(kv), md["page_table"].shape[1], self.kv.shape[1], self._pf_cap, st, stream())
+        ops.tc_linear(w.ensure_kvb(), self._pf_act, self._pf_kvb, rows=rows, status=self.status)
+        scale = (a.qk_nope_head_dim + a.qk_rope_head_dim) ** -0.5
+        call("cuteafd_mla_prefill_attention", ptr(q_nope), ptr(b["q_rope"]), ptr(self._pf_kvb), ptr(self._pf_lat), self._pf_cap, ptr(self._pf_starts),
+             ptr(md["kv_len"]), ptr(md["q_start"]), ptr(md["q_len"]), ptr(b["o_tok"]), sh.T, n_seq, sh.max_q_len, Hl, scale, st, stream())
 
     def _attn_in_gs(self, lw):
         return lw.mla.wkv_a.inv_act_gs

@@ -52,6 +52,8 @@ _PROTOS = {
     "cuteafd_tmap_encode_kv": [P, P, I, U64],
     "cuteafd_mla_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P],
     "cuteafd_tmap_encode_latent": [P, P, U64],
+    "cuteafd_mla_gather_ctx": [P, P, P, P, P, I, I, I, L, L, P, P],
+    "cuteafd_mla_prefill_attention": [P, P, P, P, L, P, P, P, P, P, I, I, I, I, F, P, P],
     "cuteafd_mla_kv_prepare": [P, P, P, P, P, I, I, F, F, I, P, P],
     "cuteafd_mla_q_split": [P, P, P, P, I, I, F, I, P],
     "cuteafd_head_to_token_major": [P, P, I, I, I, P],

@@ -549,7 +549,8 @@ class MlaAttnRankEngine(AttnRankEngine):
 def _bind_mla(cls):
     """MLA attention methods come from MlaEngine; everything else (TP exchange, remote experts) from AttnRankEngine."""
     from ..engine.mla import MlaEngine
-    for name in ("_alloc_attention_state", "_mla_buf", "_head_tiles", "attn_splits_for", "_attention_layer", "_act", "_attn_in_gs"):
+    for name in ("_alloc_attention_state", "_mla_buf", "_head_tiles", "attn_splits_for", "_attention_layer", "_act", "_attn_in_gs",
+                 "_use_prefill_path", "_prefill_attention", "PREFILL_MIN_Q", "PREFILL_MAX_BYTES"):
         setattr(cls, name, getattr(MlaEngine, name))
     return cls
 

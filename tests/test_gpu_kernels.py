@@ -714,9 +714,9 @@ def test_hash_router_and_route_gather():
     sc = torch.sqrt(torch.nn.functional.softplus(logits.gather(1, want_idx.long())))
     want_w = sc / sc.sum(-1, keepdim=True) * 1.5
     assert int(st[0]) == 0 and torch.equal(idx.cpu(), want_idx.to(torch.int32)) and torch.allclose(wts.cpu(), want_w, atol=1e-5)
-    # gather: payload rows of 64 bytes + 8 scale bytes
+    # gather: payload rows of 128 bytes (256 MXFP4 elements) + 8 scale bytes
     rows, n = 12, 7
-    src_q = torch.randint(0, 255, (rows, 64), dtype=torch.uint8, generator=g).to(DEV)
+    src_q = torch.randint(0, 255, (rows, 128), dtype=torch.uint8, generator=g).to(DEV)
     src_sf = torch.randint(0, 255, (rows, 8), dtype=torch.uint8, generator=g).to(DEV)
     order = torch.tensor([5, 0, 11, 3, 3, 7, 1, 0, 0, 0, 0, 0], dtype=torch.int32, device=DEV)
     dst = ActBuffer.alloc(KIND_MXFP4, rows, 256, 16, DEV)
@@ -724,7 +724,7 @@ def test_hash_router_and_route_gather():
     ops.route_gather(src_q, src_sf, order, torch.tensor([n], dtype=torch.int32, device=DEV), dst, rows, st)
     torch.cuda.synchronize()
     assert int(st[0]) == 0
-    assert torch.equal(dst.data[:n, :64].cpu(), src_q.cpu()[order.cpu()[:n].long()]) and torch.equal(dst.sf[:n, :8].cpu(), src_sf.cpu()[order.cpu()[:n].long()])
+    assert torch.equal(dst.data[:n].cpu(), src_q.cpu()[order.cpu()[:n].long()]) and torch.equal(dst.sf[:n, :8].cpu(), src_sf.cpu()[order.cpu()[:n].long()])
     assert bool((dst.data[n:] == 9).all())
 
 
