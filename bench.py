@@ -90,7 +90,9 @@ def deepseek_headline(args, rank: int, world: int, local: int) -> dict | None:
     context = 8192 if args.context == 4096 else args.context
     ok = None
     if not args.no_selftest and args.comm == "p2p":
-        ok = run_selftest(rank, world, local, layout="split", groups=1, n_micro=args.n_micro or 2, comm="p2p", experts="mxfp4", model="mla", verbose=False)
+        lay = args.layout or "split"
+        ok = run_selftest(rank, world, local, layout=lay, groups=(world if lay == "colocated" else (args.attn_groups or 1)),
+                          n_micro=(1 if lay == "colocated" else (args.n_micro or 2)), comm="p2p", experts="mxfp4", model="mla", verbose=False)
     out = {}
     clocks = ClockSampler(local)
     for name, batch in (("bs64", args.batch_total or 64), ("bs1", 1)):
@@ -149,7 +151,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="qwen3-235b-decode", choices=["qwen3-235b-decode", "deepseek-v3-decode", "deepseek-v3-ttft"])
+    ap.add_argument("--config", default="qwen3-235b-decode", choices=["qwen3-235b-decode", "deepseek-v3-decode", "deepseek-v3-plain", "deepseek-v3-ttft"],
+                    help="deepseek-v3-plain: one-token-per-step decode of the DeepSeek-V3 shape through the generic path (any --layout; no drafter)")
     ap.add_argument("--ttft-prompt", type=int, default=32768); ap.add_argument("--ttft-shared", type=int, default=28672)
     ap.add_argument("--ttft-sessions", type=int, default=8); ap.add_argument("--ttft-decode", type=int, default=256)
     ap.add_argument("--batch-per-gpu", type=int, default=16)
@@ -237,7 +240,7 @@ def main():
             nccl = {"value": r2["value"], "unit": r2["unit"], "ms_per_step": r2["ms_per_step"], "steps": r2["steps"],
                     "parallelism": r2["config"]["parallelism"], "e2e_value": r2["e2e"]["value"]}
     headline = None
-    if world == 8 and args.comm == "p2p" and not args.no_headline and not args.layers:
+    if world == 8 and args.comm == "p2p" and not args.no_headline and not args.layers and args.config == "qwen3-235b-decode":
         # the DeepSeek-V3-shape configuration (attention TP2 + experts on six GPUs, one-layer MTP drafter) rides along as sub-results
         import gc
         import torch

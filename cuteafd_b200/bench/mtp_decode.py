@@ -35,6 +35,13 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
     same weights); otherwise one is built with the model's default layout."""
     comm = getattr(args, "comm", "p2p")
     lay = default_layout(spec, world, comm)
+    if getattr(args, "layout", None):
+        lay["layout"] = args.layout
+        lay["attn_groups"] = world if args.layout == "colocated" else 1
+        if args.layout == "colocated":
+            lay["n_micro"] = 1
+    if getattr(args, "attn_groups", 0) and lay["layout"] == "split":
+        lay["attn_groups"] = args.attn_groups
     if getattr(args, "n_micro", 0):
         lay["n_micro"] = args.n_micro
     width = n_draft + 1

@@ -4,15 +4,18 @@
 // that is 576 + 512 multiply-adds per head, fine while the step is bound by reading the cache.  A prefill chunk is bound by
 // arithmetic, and the per-head form needs 192 + 128 multiply-adds per key: the latent rows of the sequence's context are
 // first expanded once per chunk into per-head keys and values (one GEMM with the kv_b projection, `kvb` below), then
-//   S[128 x 64]  = [q_nope | q_rope] [k_nope | k_rope]^T      three 64-wide chunks, tcgen05.mma kind::f16
+//   S[128 x 128] = [q_nope | q_rope] [k_nope | k_rope]^T      three 64-wide chunks, tcgen05.mma kind::f16, N = 128 keys
 //   O[128 x 128] += softmax(S) V
+// (a tcgen05.mma of M = 128 costs ~130 cycles whatever its N up to 256, so key tiles are 128 wide: 12 score + 8 PV
+// instructions per 128 keys instead of 24 + 8 with 64-key tiles)
 // with a CTA owning 128 query tokens of ONE head.  k_rope is shared by all heads and comes straight from the gathered latent
 // rows (columns 512..575); k_nope and V come from the expanded buffer [rows, Hl * 256] (per head: 128 key columns, then 128
 // value columns).  Both buffers are contiguous per sequence (`ctx_start[seq]` + key index), so tiles need no page table.
 //
-// Structure (one CTA per SM, 192 threads): warp 0 streams K (24 KB) and V (16 KB) tiles through separate three-stage TMA
-// rings, warp 1 issues the MMAs (scores double-buffered in tensor memory), warps 2-5 run the softmax, one thread per row:
-// the exponentials of tile i are computed BEFORE the wait for the PV product of tile i - 1, so that product runs under them.
+// Structure (one CTA per SM, 192 threads): warp 0 streams K tiles (48 KB, two stages) and V tiles (32 KB, one stage: it is
+// only needed after the tile's softmax) by TMA, warp 1 issues the MMAs (scores double-buffered in tensor memory), warps 2-5
+// run the softmax, one thread per row in two passes over the tile's 128 score columns (maximum, then exponentials, which
+// are computed BEFORE the wait for the PV product of tile i - 1, so that product runs under them).
 // Every wait is bounded and reports through the status word.
 //
 // Reference: the dedicated MLA prefill kernels of the GLM5 family (native/families/glm5/cuda/glm_mla_prefill.cu:123, 539),
@@ -22,18 +25,20 @@
 #define CA_PDL_CLASS 2
 #include "common.cuh"
 
-#define PF_NS 3
+#define PF_KT 128                 // keys per tile
+#define PF_NS 2                   // K stages
+#define PF_NSV 1                  // V stages
 #define PF_Q_BYTES 49152          // 3 chunks x [128 rows x 128 B]
-#define PF_P_BYTES 16384          // [128 rows x 128 B]
-#define PF_K_STAGE 24576          // 3 chunks x [64 keys x 128 B]
-#define PF_V_STAGE 16384          // 2 chunks x [64 keys x 128 B]
-#define PF_SMEM (PF_Q_BYTES + PF_P_BYTES + PF_NS * (PF_K_STAGE + PF_V_STAGE) + 256)
+#define PF_P_BYTES 32768          // 2 chunks (64 keys each) x [128 rows x 128 B]
+#define PF_K_STAGE 49152          // 3 chunks x [128 keys x 128 B]
+#define PF_V_STAGE 32768          // 2 chunks (64 dims each) x [128 keys x 128 B]
+#define PF_SMEM (PF_Q_BYTES + PF_P_BYTES + PF_NS * PF_K_STAGE + PF_NSV * PF_V_STAGE + 256)
 
 struct MlaPrefillArgs {
   const bf16* q_nope;           // [Hl, T, 128] head-major
   const bf16* q_rope;           // [T, Hl, 64]
-  CUtensorMap kvb_map;          // {Hl * 256, rows, 1}, box {64, 64, 1}, 128-byte swizzle (encoded with rank 3: loads pass z = 0)
-  CUtensorMap lat_map;          // {576, rows, 1}, box {64, 64, 1}, 128-byte swizzle
+  CUtensorMap kvb_map;          // {Hl * 256, rows, 1}, box {64, 128, 1}, 128-byte swizzle (encoded with rank 3: loads pass z = 0)
+  CUtensorMap lat_map;          // {576, rows, 1}, box {64, 128, 1}, 128-byte swizzle
   const int* ctx_start;         // [n_seq] first row of the sequence's context in the two buffers
   const int* kv_len;
   const int* q_start;
@@ -69,13 +74,13 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
   uint8_t* sP = sQ + PF_Q_BYTES;
   uint8_t* sK = sP + PF_P_BYTES;
   uint8_t* sV = sK + PF_NS * PF_K_STAGE;
-  uint64_t* bars = (uint64_t*)(sV + PF_NS * PF_V_STAGE);
-  uint64_t* k_full = bars; uint64_t* k_empty = bars + PF_NS; uint64_t* v_full = bars + 2 * PF_NS; uint64_t* v_empty = bars + 3 * PF_NS;
-  uint64_t* s_full = bars + 4 * PF_NS;          // [2]
-  uint64_t* s_free = bars + 4 * PF_NS + 2;      // [2]: the softmax threads hold the scores of the buffer in registers
-  uint64_t& p_full = bars[4 * PF_NS + 4]; uint64_t& o_done = bars[4 * PF_NS + 5];
-  uint32_t& tmem_slot = *(uint32_t*)(bars + 4 * PF_NS + 6);
-  int& abort_flag = *(int*)(bars + 4 * PF_NS + 7);
+  uint64_t* bars = (uint64_t*)(sV + PF_NSV * PF_V_STAGE);
+  uint64_t* k_full = bars; uint64_t* k_empty = bars + 2; uint64_t* v_full = bars + 4; uint64_t* v_empty = bars + 6;     // [<= 2] each
+  uint64_t* s_full = bars + 8;          // [2]
+  uint64_t* s_free = bars + 10;         // [2]: the softmax threads are done with the score buffer
+  uint64_t& p_full = bars[12]; uint64_t& o_done = bars[13];
+  uint32_t& tmem_slot = *(uint32_t*)(bars + 14);
+  int& abort_flag = *(int*)(bars + 15);
   if (smem_u32(smem) & 1023) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, 0xA13); return; }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
@@ -89,17 +94,17 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
   const int row_base = a.q_start[seq] + tok0;
   const int first_pos = kvlen - qlen + tok0;
   const int hi = first_pos + R;
-  const int n_tiles = (hi + 63) / 64;
+  const int n_tiles = (hi + PF_KT - 1) / PF_KT;
   const int ctx0 = a.ctx_start[seq];
 
   if (tid == 0) {
-    for (int s = 0; s < PF_NS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 128); }
     mbar_init(&p_full, 128); mbar_init(&o_done, 1);
     abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 1) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
   // Q rows -> three swizzled K-major operand tiles (q_nope low / high half, q_rope)
   for (int i = tid; i < 128 * 24; i += 192) {
     const int r = i / 24, c = i % 24;                  // 16-byte chunk c (8 elements) of row r
@@ -117,31 +122,41 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
-  const uint32_t S0_COL = 0, O_COL = 64, S1_COL = 192;
+  const uint32_t S0_COL = 0, O_COL = 128, S1_COL = 256;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ K / V producer
-    for (int i = 0; i < n_tiles && !*abortp; ++i) {
+    // K runs one tile ahead of V in this warp's program order: the single V stage only frees when the previous PV product
+    // retires, and the K tile of the NEXT score pass must not queue behind that wait.
+    auto load_k = [&](int i) -> bool {
       const int s = i % PF_NS, ph = ((i / PF_NS) & 1) ^ 1;
-      const int row = ctx0 + i * 64;
-      if (!mbar_wait_bounded(&k_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
+      if (!mbar_wait_bounded(&k_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); return false; }
       if (lane == 0) {
+        const int row = ctx0 + i * PF_KT;
         mbar_expect_tx(&k_full[s], PF_K_STAGE);
         tma_load_3d(sK + s * PF_K_STAGE, &a.kvb_map, &k_full[s], head * 256, row, 0);
-        tma_load_3d(sK + s * PF_K_STAGE + 8192, &a.kvb_map, &k_full[s], head * 256 + 64, row, 0);
-        tma_load_3d(sK + s * PF_K_STAGE + 16384, &a.lat_map, &k_full[s], 512, row, 0);
+        tma_load_3d(sK + s * PF_K_STAGE + 16384, &a.kvb_map, &k_full[s], head * 256 + 64, row, 0);
+        tma_load_3d(sK + s * PF_K_STAGE + 32768, &a.lat_map, &k_full[s], 512, row, 0);
       }
-      if (!mbar_wait_bounded(&v_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, 0x1000 + i); break; }
+      __syncwarp();
+      return true;
+    };
+    bool okp = n_tiles > 0 ? load_k(0) : true;
+    for (int i = 0; okp && i < n_tiles && !*abortp; ++i) {
+      if (i + 1 < n_tiles && !load_k(i + 1)) break;
+      const int sv = i % PF_NSV, phv = ((i / PF_NSV) & 1) ^ 1;
+      if (!mbar_wait_bounded(&v_empty[sv], phv, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, 0x1000 + i); break; }
       if (lane == 0) {
-        mbar_expect_tx(&v_full[s], PF_V_STAGE);
-        tma_load_3d(sV + s * PF_V_STAGE, &a.kvb_map, &v_full[s], head * 256 + 128, row, 0);
-        tma_load_3d(sV + s * PF_V_STAGE + 8192, &a.kvb_map, &v_full[s], head * 256 + 192, row, 0);
+        const int row = ctx0 + i * PF_KT;
+        mbar_expect_tx(&v_full[sv], PF_V_STAGE);
+        tma_load_3d(sV + sv * PF_V_STAGE, &a.kvb_map, &v_full[sv], head * 256 + 128, row, 0);
+        tma_load_3d(sV + sv * PF_V_STAGE + 16384, &a.kvb_map, &v_full[sv], head * 256 + 192, row, 0);
       }
       __syncwarp();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t id_s = pf_idesc(64, 0), id_o = pf_idesc(128, 1);
+    const uint32_t id_s = pf_idesc(PF_KT, 0), id_o = pf_idesc(128, 1);
     auto issue_scores = [&](int j) -> bool {     // S[j & 1] = Q K(j)^T once the softmax threads have copied tile j - 2 out of it
       const int s = j % PF_NS;
       if (j >= 2 && !mbar_wait_bounded(&s_free[j & 1], ((j - 2) >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0x2000 + j); return false; }
@@ -153,7 +168,7 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
         for (int kb = 0; kb < 3; ++kb)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(d, umma_desc_sw128(smem_u32(sQ) + kb * 16384) + 2 * k, umma_desc_sw128(k0 + kb * 8192) + 2 * k, id_s, (kb | k) ? 1u : 0u);
+            tc_mma_f16(d, umma_desc_sw128(smem_u32(sQ) + kb * 16384) + 2 * k, umma_desc_sw128(k0 + kb * 16384) + 2 * k, id_s, (kb | k) ? 1u : 0u);
         tc_commit(&s_full[j & 1]);
         tc_commit(&k_empty[s]);
       }
@@ -163,16 +178,17 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
     bool ok = true;
     for (int j = 0; ok && j < min(2, n_tiles); ++j) ok = issue_scores(j);
     for (int i = 0; ok && i < n_tiles; ++i) {
-      const int s = i % PF_NS;
+      const int sv = i % PF_NSV;
       if (!mbar_wait_bounded(&p_full, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0x3000 + i); break; }
-      if (!mbar_wait_bounded(&v_full[s], (i / PF_NS) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0x4000 + i); break; }
+      if (!mbar_wait_bounded(&v_full[sv], (i / PF_NSV) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0x4000 + i); break; }
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t v0 = smem_u32(sV + s * PF_V_STAGE);
+        const uint32_t v0 = smem_u32(sV + sv * PF_V_STAGE);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_f16(tmem + O_COL, umma_desc_sw128(smem_u32(sP)) + 2 * k, pf_desc_mn_sw128(v0 + k * 2048, 8192, 1024), id_o, (i | k) ? 1u : 0u);
-        tc_commit(&v_empty[s]);
+        for (int k = 0; k < PF_KT / 16; ++k)       // 16 keys per MMA: P chunk k / 4 (64 keys per 128-byte row), V rows 16 k .. 16 k + 15
+          tc_mma_f16(tmem + O_COL, umma_desc_sw128(smem_u32(sP) + (k >> 2) * 16384) + 2 * (k & 3), pf_desc_mn_sw128(v0 + k * 2048, 16384, 1024), id_o,
+                     (i | k) ? 1u : 0u);
+        tc_commit(&v_empty[sv]);
         tc_commit(&o_done);
       }
       __syncwarp();
@@ -190,27 +206,21 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
     for (int i = 0; i < n_tiles; ++i) {
       if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
       tc_fence_after();
-      uint32_t sr[64];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_x16(tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL) + c * 16, sr + c * 16);
-      tc_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&s_free[i & 1]);
-      const int key0 = i * 64;
+      const uint32_t s_addr = tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL);
+      const int key0 = i * PF_KT;
+      const bool all_visible = key0 + PF_KT - 1 <= first_pos;      // CTA-uniform: every key of the tile is visible to every live row
+      // pass 1: row maximum over the tile's 128 scores (scaled to the exp2 domain)
       float mx = -INFINITY;
-      if (key0 + 63 <= first_pos && live) {              // every key of the tile is visible to every row of the CTA
+#pragma unroll 1
+      for (int c = 0; c < PF_KT / 32; ++c) {
+        uint32_t sr[32];
+        tmem_ld_x16(s_addr + c * 32, sr);
+        tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+        tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const float v = __uint_as_float(sr[j]) * sc2;
-          sr[j] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int kp = key0 + j;
-          const float v = (live && kp <= qpos) ? __uint_as_float(sr[j]) * sc2 : -INFINITY;
-          sr[j] = __float_as_uint(v);
+        for (int j = 0; j < 32; ++j) {
+          const int kp = key0 + c * 32 + j;
+          const float v = (live && (all_visible || kp <= qpos)) ? __uint_as_float(sr[j]) * sc2 : -INFINITY;
           mx = fmaxf(mx, v);
         }
       }
@@ -219,17 +229,28 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
         if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
         m_ref = mx;
       }
+      // pass 2: exponentials, packed to bf16 pairs (64 registers for the 128 probabilities)
       float psum = 0.f;
-      uint32_t pk[32];
+      uint32_t pk[PF_KT / 2];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float a0 = __uint_as_float(sr[2 * j]), a1 = __uint_as_float(sr[2 * j + 1]);
-        const float e0 = (m_ref == -INFINITY) ? 0.f : exp2f(a0 - m_ref), e1 = (m_ref == -INFINITY) ? 0.f : exp2f(a1 - m_ref);
-        psum += e0 + e1;
-        bf162 h = __floats2bfloat162_rn(e0, e1);
-        pk[j] = *(uint32_t*)&h;
+      for (int c = 0; c < PF_KT / 32; ++c) {
+        uint32_t sr[32];
+        tmem_ld_x16(s_addr + c * 32, sr);
+        tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int kp = key0 + c * 32 + 2 * j;
+          const bool v0 = live && (all_visible || kp <= qpos), v1 = live && (all_visible || kp + 1 <= qpos);
+          const float e0 = v0 ? exp2f(__uint_as_float(sr[2 * j]) * sc2 - m_ref) : 0.f, e1 = v1 ? exp2f(__uint_as_float(sr[2 * j + 1]) * sc2 - m_ref) : 0.f;
+          psum += e0 + e1;
+          bf162 h = __floats2bfloat162_rn(e0, e1);
+          pk[c * 16 + j] = *(uint32_t*)&h;
+        }
       }
       l += psum;
+      tc_fence_before();
+      mbar_arrive(&s_free[i & 1]);
       // the previous P V product must have finished before P is overwritten or O rescaled
       if (i > 0 && !mbar_wait_bounded(&o_done, (i - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, 0x1000 + i); ok = false; break; }
       tc_fence_after();
@@ -245,9 +266,10 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
+      // P: two K-major chunks of 64 keys; 16-byte unit u of a row holds keys 8 u .. 8 u + 7
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *(uint4*)(sP + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      for (int u = 0; u < PF_KT / 8; ++u)
+        *(uint4*)(sP + (u >> 3) * 16384 + r * 128 + (((u & 7) ^ (r & 7)) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full);
@@ -278,7 +300,7 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
   if (*abortp && warp == 0) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 200000) __nanosleep(1000); }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 256);
+  if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
 // Gathers the latent rows of every sequence's context out of the paged cache into one contiguous buffer:
@@ -313,10 +335,10 @@ extern "C" int cuteafd_mla_prefill_attention(const void* q_nope, const void* q_r
   CA_REQUIRE(Hl >= 1, "mla_prefill_attention: no heads");
   if (T <= 0 || n_seq <= 0) return CA_OK;
   MlaPrefillArgs a;
-  int rc = ca_encode_tmap_2d(&a.kvb_map, kvb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)Hl * 256, (uint64_t)rows, (uint64_t)Hl * 512, 64, 64,
+  int rc = ca_encode_tmap_2d(&a.kvb_map, kvb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)Hl * 256, (uint64_t)rows, (uint64_t)Hl * 512, 64, PF_KT,
                              CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  rc = ca_encode_tmap_2d(&a.lat_map, lat, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 576, (uint64_t)rows, 1152, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = ca_encode_tmap_2d(&a.lat_map, lat, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 576, (uint64_t)rows, 1152, 64, PF_KT, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   a.q_nope = (const bf16*)q_nope; a.q_rope = (const bf16*)q_rope; a.ctx_start = ctx_start; a.kv_len = kv_len; a.q_start = q_start; a.q_len = q_len;
   a.out = (bf16*)out; a.status = status; a.T = T; a.Hl = Hl; a.max_q_tiles = (max_q_len + 127) / 128; a.scale = scale;

@@ -91,13 +91,19 @@ struct TcCfg {
   static constexpr int NSTAGE_RAW = ((OCC == 2 ? 104 : 200) * 1024) / STAGE_BYTES;
   static constexpr int NSTAGE = NSTAGE_RAW > 8 ? 8 : NSTAGE_RAW;
   static constexpr int ACC_COLS = NA * TN;
-  static constexpr int NACC = (2 * ACC_COLS <= 384) ? 2 : 1;
+  // two accumulators let the next unit's MMAs run under this unit's epilogue; bf16 operands have no scale columns, so a
+  // 256-token tile can still double-buffer (2 x 256 = all 512 columns)
+  static constexpr int NACC = (2 * ACC_COLS <= (KIND == KIND_BF16 ? 512 : 384)) ? 2 : 1;
   static constexpr int TMEM_COLS = OCC == 2 ? 256 : 512;
   static constexpr int SFA_COL = TMEM_COLS - 64, SFA2_COL = TMEM_COLS - 48, SFB_COL = TMEM_COLS - 32;   // tensor-memory columns of the scales
   static constexpr int K_ELEMS = KIND == KIND_BF16 ? 64 : (KIND == KIND_W4A8 ? 128 : 256);   // K elements per stage (128 bytes of shared memory per row)
-  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024;
+  // Staging for the transposed epilogue store of 64+-token tiles: two buffers of [16 tokens][128 features] fp32.  In the
+  // swap-AB tile a lane owns ONE output feature, so direct stores are 2-byte elements, 64 contiguous bytes per warp
+  // instruction; through the staging buffer the four epilogue warps write whole 256-byte rows with 16-byte stores.
+  static constexpr int STG_BYTES = TN >= 64 ? 2 * 16 * 128 * 4 : 0;
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + STG_BYTES + 1024;
   static_assert(NSTAGE >= 2, "tile too large for shared memory");
-  static_assert(ACC_COLS * NACC <= SFA_COL, "accumulators overlap the scale columns");
+  static_assert(KIND == KIND_BF16 ? ACC_COLS * NACC <= TMEM_COLS : ACC_COLS * NACC <= SFA_COL, "accumulators overlap the scale columns");
 };
 
 __device__ __forceinline__ uint32_t make_idesc(int kind, int n, uint32_t sf_id) {
@@ -152,7 +158,7 @@ template <int KIND, int TN, bool SWIGLU, bool PEER, bool QOUT>
 __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_kernel(const __grid_constant__ TcArgs a) {
   using C = TcCfg<KIND, TN, SWIGLU>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[C::NSTAGE], empty_bar[C::NSTAGE], accf_bar[2], acce_bar[2];
+  __shared__ uint64_t full_bar[C::NSTAGE], empty_bar[C::NSTAGE], accf_bar[2], acce_bar[2], stg_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -162,6 +168,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::NSTAGE; ++s) { mbar_init(&full_bar[s], 33); mbar_init(&empty_bar[s], 1); }   // 1 expect_tx + 32 lanes
     for (int i = 0; i < 2; ++i) { mbar_init(&accf_bar[i], 1); mbar_init(&acce_bar[i], 128); }
+    mbar_init(&stg_bar, 128);
     abort_flag = 0;
     fence_barrier_init();
   }
@@ -321,7 +328,12 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q4 = warp & 3;                 // tensor-memory lane quarter this warp may read
     const int et = q4 * 32 + lane;           // 0..127: weight row inside the tile
-    uint32_t tc = 0;
+    uint32_t tc = 0, stg_uses = 0;
+    // staged (transposed) store: plain bf16 output of a 64+-token tile, 16-byte aligned rows
+    const bool stage_ok = C::STG_BYTES > 0 && splits == 1 && a.epi != EPI_F32 && a.Y != nullptr && !(QOUT && a.q_out) && !(PEER && a.n_peer) &&
+                          a.ldy % 8 == 0 && a.N % 8 == 0 && ((uintptr_t)a.Y & 15) == 0 && (a.epi != EPI_BF16_RESIDUAL || ((uintptr_t)a.R & 15) == 0);
+    float* stg = (float*)(smem + C::NSTAGE * C::STAGE_BYTES);
+    bool stg_fail = false;
     for (int w = w_begin; w < w_end && !*abortp; ++w, ++tc) {
       const int sp = w % splits, tile = w / splits, item = tile / n_nt, nt = tile % n_nt;
       int g = 0, row0 = item * TN, nrows = min(TN, a.rows_total - row0);
@@ -406,6 +418,44 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
               }
             }
           }
+        } else if (stage_ok) {
+          if (c0 < nrows) {                            // the same for all four epilogue warps: they meet at the barrier below
+            float* buf = stg + ((c0 >> 4) & 1) * (16 * 128);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = __uint_as_float(r[j]) * al;
+              if (SWIGLU) {
+                const float u = __uint_as_float(r2[j]) * al2;
+                v = v / (1.f + __expf(-v)) * u;
+              }
+              buf[j * 128 + et] = v;
+            }
+            mbar_arrive(&stg_bar);
+            if (!mbar_wait_bounded(&stg_bar, stg_uses & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, 0x7000 + w); stg_fail = true; break; }
+            ++stg_uses;
+            // 16 rows x 16 groups of 8 features; thread -> (row, group), two per thread.  A buffer is rewritten two chunks
+            // later, after every warp has passed the NEXT chunk's barrier, i.e. finished these reads.
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int idx = (warp - 2) * 32 + lane + h * 128, row = idx >> 4, grp = idx & 15;
+              const int c = c0 + row, nn = nt * 128 + grp * 8;
+              if (c < nrows && nn < a.N) {
+                const float4 f0 = *(const float4*)(buf + row * 128 + grp * 8), f1 = *(const float4*)(buf + row * 128 + grp * 8 + 4);
+                float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                const size_t o = (size_t)(row0 + c) * a.ldy + nn;
+                if (a.epi == EPI_BF16_RESIDUAL) {
+                  const uint4 rv = *(const uint4*)(a.R + o);
+                  const bf16* rb = (const bf16*)&rv;
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) f[q] += __bfloat162float(rb[q]);
+                }
+                uint32_t wv[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { bf162 hh = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]); wv[q] = *(uint32_t*)&hh; }
+                *(uint4*)((bf16*)a.Y + o) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+              }
+            }
+          }
         } else if (c0 < nrows && n_ok) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -429,6 +479,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
           }
         }
       }
+      if (stg_fail) break;
       tc_fence_before();
       mbar_arrive(&acce_bar[acc]);
       if (warp == 2) { TC_TRACE(6, clock64()); TC_TRACE(3, globaltimer_ns()); }
@@ -827,11 +878,10 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.peer_row_map = peer.row_map; a.peer_ctl = (uint32_t*)peer.ctl; a.peer_done = (uint32_t*)peer.done; a.peer_ld = peer.ld; a.n_peer = peer.n;
   a.q_out = (uint8_t*)q_out; a.sf_out = (uint8_t*)sf_out; a.inv_gs_out = inv_gs_out; a.ldsf_out = ldsf_out;
   a.ldsfb = ldsfb; a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits > 1 ? splits : 1;
-  {   // CUTEAFD_W4A8_TX: bytes per unpacked 4-bit weight tile in the transaction count (the tile occupies 16 KB of shared memory)
-    static int w4_tx = -1;
-    if (w4_tx < 0) { const char* e = getenv("CUTEAFD_W4A8_TX"); w4_tx = e ? atoi(e) : 128 * 128; }
-    a.w4_tx = w4_tx;
-  }
+  // A 128 x 128 tile of packed 4-bit weights that TMA expands into 16-byte groups of 16 elements (8 data bytes + 8 bytes of
+  // padding) occupies 16 KB of shared memory, but the barrier's transaction count receives the 8 KB of data that were copied
+  // (measured: with 16 KB expected the stage never completes).
+  a.w4_tx = 128 * 128 / 2;
   const int n_nt = (N + 127) / 128;
   if (kind == KIND_W4A8 && !tiles && !swiglu && a.splits > 1 && tn <= 32) a.splits = 1;       // no cluster split-K variant of this kind: one CTA per tile
   if (!tiles && !swiglu && (tn == 16 || tn == 32) && (a.splits == 2 || a.splits == 4 || (a.splits == 8 && tn == 16))) {
