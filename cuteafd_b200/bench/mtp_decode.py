@@ -48,20 +48,35 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
     ctx_pages = -(-(context + width * (rounds + warmup + 2) * 2 + 64) // PAGE)
     own = runner is None
     if own:
-        t_cap = max(16, -(-batch * width // lay["n_micro"]))
-        runner = AfdRunner(spec, rank, world, local, t_cap=t_cap, n_pages=batch * (ctx_pages + 1) + 2, max_seqs=max(batch, 1),
+        from ..config import deployment_by_name
+        groups = deployment_by_name(lay["layout"], world, lay["attn_groups"]).attn_groups
+        if batch < groups:          # fewer sequences than attention groups (batch 1): one group on the split serves them
+            lay = dict(default_layout(spec, world, comm), attn_groups=1)
+            if lay["layout"] != "split":
+                lay["layout"], lay["n_micro"] = "split", 1
+            groups = 1
+        per_group = -(-batch // groups)
+        t_cap = max(16, -(-per_group * width // lay["n_micro"]))
+        runner = AfdRunner(spec, rank, world, local, t_cap=t_cap, n_pages=per_group * (ctx_pages + 1) + 2, max_seqs=max(per_group, 1),
                            max_pages_per_seq=ctx_pages + 1, comm=comm, layout=lay["layout"], attn_groups=lay["attn_groups"], n_micro=lay["n_micro"],
                            expert_tp=bool(getattr(args, "expert_tp", False)))
     run = runner
     res = None
     stats = [0.0] * 6
+    total_batch = batch
+    if run.is_attn:
+        # this rank's share of the sequences: its group's slice (every rank of a tensor-parallel group holds the same ones)
+        g_all, my_g = run.dep.attn_groups, run.dep.group_of(rank)
+        base, extra = divmod(total_batch, g_all)
+        batch = base + (1 if my_g < extra else 0)
+        leader = run.dep.group_ranks(my_g)[0] == rank
     if run.is_attn:
         eng = run.engine
         pool = PagePool(eng.n_pages)
         gk = torch.Generator(device=eng.device).manual_seed(7)
         for li in range(eng.kv.shape[0]):
             eng.kv[li].normal_(0, 1, generator=gk)
-        g = torch.Generator().manual_seed(11)
+        g = torch.Generator().manual_seed(11 + my_g)
         first = torch.randint(0, spec.vocab, (batch,), generator=g).tolist()
         hid = torch.empty(batch, spec.hidden, dtype=torch.bfloat16, device=eng.device).normal_(0, 1, generator=gk)
 
@@ -105,7 +120,8 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
         torch.cuda.synchronize()
         dt_plain = time.perf_counter() - t1
         eng.check_status()
-        stats = [dt_spec, dt_plain, float(emitted), float(accepted), float(end_len), 0.0]
+        # times: the slowest rank counts; tokens: summed over the groups' leaders
+        stats = [dt_spec, dt_plain, float(emitted) if leader else 0.0, float(accepted) if leader else 0.0, float(end_len), 0.0]
         if own:
             run.control(OP_STOP)
             run.check()
@@ -114,8 +130,10 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
         run.check()
     if own:
         t = torch.tensor(stats, dtype=torch.float64, device=run.dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        stats = t.tolist()
+        tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        stats = [float(tmax[0]), float(tmax[1]), float(tsum[2]), float(tsum[3]), float(tmax[4]), 0.0]
+    batch = total_batch
     if rank == 0:
         dt_spec, dt_plain, emitted, accepted = stats[0], stats[1], stats[2], stats[3]
         round_ms = dt_spec * 1e3 / rounds

@@ -12,8 +12,9 @@
 // rows (columns 512..575); k_nope and V come from the expanded buffer [rows, Hl * 256] (per head: 128 key columns, then 128
 // value columns).  Both buffers are contiguous per sequence (`ctx_start[seq]` + key index), so tiles need no page table.
 //
-// Structure (one CTA per SM, 192 threads): warp 0 streams K tiles (48 KB, two stages) and V tiles (32 KB, one stage: it is
-// only needed after the tile's softmax) by TMA, warp 1 issues the MMAs (scores double-buffered in tensor memory), warps 2-5
+// Structure (one CTA per SM, 192 threads): warp 0 streams K tiles (48 KB, two stages) and V tiles (32 KB, two stages) by TMA;
+// the 128 x 192 query tile sits in tensor memory (96 columns) as the A operand of the score MMAs, which leaves the shared
+// memory to the K / V rings; warp 1 issues the MMAs (scores double-buffered in tensor memory), warps 2-5
 // run the softmax, one thread per row in two passes over the tile's 128 score columns (maximum, then exponentials, which
 // are computed BEFORE the wait for the PV product of tile i - 1, so that product runs under them).
 // Every wait is bounded and reports through the status word.
@@ -27,8 +28,8 @@
 
 #define PF_KT 128                 // keys per tile
 #define PF_NS 2                   // K stages
-#define PF_NSV 1                  // V stages
-#define PF_Q_BYTES 49152          // 3 chunks x [128 rows x 128 B]
+#define PF_NSV 2                  // V stages
+#define PF_Q_BYTES 0              // the query tile lives in tensor memory (A operand of the score MMAs)
 #define PF_P_BYTES 32768          // 2 chunks (64 keys each) x [128 rows x 128 B]
 #define PF_K_STAGE 49152          // 3 chunks x [128 keys x 128 B]
 #define PF_V_STAGE 32768          // 2 chunks (64 dims each) x [128 keys x 128 B]
@@ -70,8 +71,7 @@ __device__ __forceinline__ void pf_tmem_st_x16(uint32_t addr, const uint32_t* r)
 __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_constant__ MlaPrefillArgs a) {
   pdl_launch(); pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sQ = smem;
-  uint8_t* sP = sQ + PF_Q_BYTES;
+  uint8_t* sP = smem;
   uint8_t* sK = sP + PF_P_BYTES;
   uint8_t* sV = sK + PF_NS * PF_K_STAGE;
   uint64_t* bars = (uint64_t*)(sV + PF_NSV * PF_V_STAGE);
@@ -105,24 +105,35 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
-  // Q rows -> three swizzled K-major operand tiles (q_nope low / high half, q_rope)
-  for (int i = tid; i < 128 * 24; i += 192) {
-    const int r = i / 24, c = i % 24;                  // 16-byte chunk c (8 elements) of row r
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < R) {
-      const int t = row_base + r;
-      v = c < 16 ? *(const uint4*)(a.q_nope + ((size_t)head * a.T + t) * 128 + c * 8)
-                 : *(const uint4*)(a.q_rope + ((size_t)t * a.Hl + head) * 64 + (c - 16) * 8);
-    }
-    *(uint4*)(sQ + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-  }
-  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   volatile int* abortp = &abort_flag;
-  const uint32_t S0_COL = 0, O_COL = 128, S1_COL = 256;
+  const uint32_t S0_COL = 0, O_COL = 128, S1_COL = 256, Q_COL = 384;
+  // query rows -> tensor memory (row = lane, two bf16 per 32-bit column, 32 columns per 64-wide chunk: q_nope low / high, q_rope)
+  if (warp >= 2) {
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t dst = tmem + ((uint32_t)((warp & 3) * 32) << 16) + Q_COL;
+    const int t = row_base + (r < R ? r : 0);
+    const bf16* src_nope = a.q_nope + ((size_t)head * a.T + t) * 128;
+    const bf16* src_rope = a.q_rope + ((size_t)t * a.Hl + head) * 64;
+#pragma unroll 1
+    for (int g = 0; g < 6; ++g) {                  // 16 columns = 32 elements per store
+      const bf16* src = g < 4 ? src_nope + g * 32 : src_rope + (g - 4) * 32;
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = r < R ? *(const uint4*)(src + j * 8) : make_uint4(0, 0, 0, 0);
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
+      pf_tmem_st_x16(dst + g * 16, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ K / V producer
@@ -168,7 +179,7 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
         for (int kb = 0; kb < 3; ++kb)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(d, umma_desc_sw128(smem_u32(sQ) + kb * 16384) + 2 * k, umma_desc_sw128(k0 + kb * 16384) + 2 * k, id_s, (kb | k) ? 1u : 0u);
+            tc_mma_f16_ta(d, tmem + Q_COL + kb * 32 + k * 8, umma_desc_sw128(k0 + kb * 16384) + 2 * k, id_s, (kb | k) ? 1u : 0u);
         tc_commit(&s_full[j & 1]);
         tc_commit(&k_empty[s]);
       }
@@ -209,43 +220,73 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
       const uint32_t s_addr = tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL);
       const int key0 = i * PF_KT;
       const bool all_visible = key0 + PF_KT - 1 <= first_pos;      // CTA-uniform: every key of the tile is visible to every live row
-      // pass 1: row maximum over the tile's 128 scores (scaled to the exp2 domain)
+      // two passes over the tile's 128 score columns: row maximum, then exponentials packed to bf16 pairs (64 registers).
+      // Tiles below the diagonal need no mask (CTA-uniform test), which is all but the last one or two of a long context.
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < PF_KT / 32; ++c) {
-        uint32_t sr[32];
-        tmem_ld_x16(s_addr + c * 32, sr);
-        tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
-        tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int kp = key0 + c * 32 + j;
-          const float v = (live && (all_visible || kp <= qpos)) ? __uint_as_float(sr[j]) * sc2 : -INFINITY;
-          mx = fmaxf(mx, v);
-        }
-      }
-      float alpha = 1.f;
-      if (mx > m_ref + 8.f) {
-        if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
-        m_ref = mx;
-      }
-      // pass 2: exponentials, packed to bf16 pairs (64 registers for the 128 probabilities)
-      float psum = 0.f;
       uint32_t pk[PF_KT / 2];
+      float psum = 0.f;
+      float alpha = 1.f;
+      if (all_visible) {           // CTA-uniform (the tensor-memory loads below are warp collectives); rows past R hold zero queries
+#pragma unroll 1
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < PF_KT / 32; ++c) {
-        uint32_t sr[32];
-        tmem_ld_x16(s_addr + c * 32, sr);
-        tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
-        tc_wait_ld();
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sr[j]));
+        }
+        mx *= sc2;                                   // sc2 > 0: scaling commutes with the maximum
+        if (mx > m_ref + 8.f) {
+          if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
+          m_ref = mx;
+        }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int kp = key0 + c * 32 + 2 * j;
-          const bool v0 = live && (all_visible || kp <= qpos), v1 = live && (all_visible || kp + 1 <= qpos);
-          const float e0 = v0 ? exp2f(__uint_as_float(sr[2 * j]) * sc2 - m_ref) : 0.f, e1 = v1 ? exp2f(__uint_as_float(sr[2 * j + 1]) * sc2 - m_ref) : 0.f;
-          psum += e0 + e1;
-          bf162 h = __floats2bfloat162_rn(e0, e1);
-          pk[c * 16 + j] = *(uint32_t*)&h;
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float e0 = exp2f(fmaf(__uint_as_float(sr[2 * j]), sc2, -m_ref)), e1 = exp2f(fmaf(__uint_as_float(sr[2 * j + 1]), sc2, -m_ref));
+            psum += e0 + e1;
+            bf162 h = __floats2bfloat162_rn(e0, e1);
+            pk[c * 16 + j] = *(uint32_t*)&h;
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int kp = key0 + c * 32 + j;
+            if (live && kp <= qpos) mx = fmaxf(mx, __uint_as_float(sr[j]) * sc2);
+          }
+        }
+        if (mx > m_ref + 8.f) {
+          if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
+          m_ref = mx;
+        }
+#pragma unroll
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int kp = key0 + c * 32 + 2 * j;
+            const float e0 = (live && kp <= qpos) ? exp2f(fmaf(__uint_as_float(sr[2 * j]), sc2, -m_ref)) : 0.f;
+            const float e1 = (live && kp + 1 <= qpos) ? exp2f(fmaf(__uint_as_float(sr[2 * j + 1]), sc2, -m_ref)) : 0.f;
+            psum += e0 + e1;
+            bf162 h = __floats2bfloat162_rn(e0, e1);
+            pk[c * 16 + j] = *(uint32_t*)&h;
+          }
         }
       }
       l += psum;
