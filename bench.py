@@ -78,8 +78,9 @@ def reference_arm(args):
 
 
 def deepseek_headline(args, rank: int, world: int, local: int) -> dict | None:
-    """DeepSeek-V3-shape decode on the named split (attention TP2 + experts on the other GPUs) with the one-layer MTP drafter:
-    batch 64 and batch 1 at 8k context on the same weights.  Rank 0 gets the record."""
+    """DeepSeek-V3-shape decode with the one-layer MTP drafter, batch 64 and batch 1 at 8k context: batch 64 on the default
+    layout (colocated: every GPU attention + experts; `--layout split` selects the named attention TP2 + expert ranks), batch 1 on
+    the split (one sequence has one attention group).  Rank 0 gets the record."""
     import torch
     from cuteafd_b200.bench.mtp_decode import run_mtp_decode_bench
     from cuteafd_b200.config import deepseek_v3_spec
@@ -90,7 +91,8 @@ def deepseek_headline(args, rank: int, world: int, local: int) -> dict | None:
     context = 8192 if args.context == 4096 else args.context
     ok = None
     if not args.no_selftest and args.comm == "p2p":
-        lay = args.layout or "split"
+        from cuteafd_b200.parallel.runner import default_layout
+        lay = args.layout or default_layout(spec, world, args.comm)["layout"]
         ok = run_selftest(rank, world, local, layout=lay, groups=(world if lay == "colocated" else (args.attn_groups or 1)),
                           n_micro=(1 if lay == "colocated" else (args.n_micro or 2)), comm="p2p", experts="mxfp4", model="mla", verbose=False)
     out = {}

@@ -4,6 +4,7 @@ launches over DISTINCT weights (so nothing is served from L2) with CUDA events.
     python -m cuteafd_b200.bench.gemm --mode stream     # weight streaming: GB/s of large skinny GEMMs per format and K
     python -m cuteafd_b200.bench.gemm --mode small      # decode projections (QKV / O / router shapes) per split-K factor
     python -m cuteafd_b200.bench.gemm --mode trace      # device time stamps of the persistent kernel on small layers
+    python -m cuteafd_b200.bench.gemm --mode moe        # grouped FC1 (SwiGLU, FP4 output) and FC2 of a decode step, per kernel
 """
 from __future__ import annotations
 
@@ -117,13 +118,49 @@ def trace(dev, T: int = 16):
     print("status", st.tolist())
 
 
+def moe(dev, T: int = 16, E: int = 128, k: int = 8, H: int = 4096, I: int = 1536, kind: str = "nvfp4"):
+    """The two grouped expert GEMMs of one decode step (Qwen3-235B shape by default: 16 tokens x top-8 of 128 experts), each
+    timed alone over three distinct weight sets (nothing served from L2); GB/s counts the weights of the ACTIVE experts only."""
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    copies = 3
+    g = torch.Generator(device=dev).manual_seed(1)
+    logits = torch.randn(T, E, generator=g, device=dev)
+    idx, wts = torch.zeros(T, k, dtype=torch.int32, device=dev), torch.zeros(T, k, device=dev)
+    ops.router_select(logits, None, idx, wts, T, k, "softmax", True, 1.0)
+    rows = T * k
+    for tn in (16, 32):
+        max_tiles = E + rows // tn + 1
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows = i32(rows), i32(T, k), i32(E), i32(E), i32(max_tiles, 4), i32(1), i32(1)
+        ops.route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, 0, E, tn, max_tiles)
+        torch.cuda.synchronize()
+        active = int((counts > 0).sum())
+        Wg = [TcWeight.random(E, I, H, kind, dev, seed=10 + i) for i in range(copies)]
+        Wu = [TcWeight.random(E, I, H, kind, dev, seed=20 + i) for i in range(copies)]
+        Wd = [TcWeight.random(E, H, I, kind, dev, seed=30 + i) for i in range(copies)]
+        xs = ActBuffer.alloc(Wg[0].kind, rows, H, tn, dev)
+        h1q = ActBuffer.alloc(Wg[0].kind, rows, I, tn, dev)
+        y2 = torch.zeros(rows, H, dtype=torch.bfloat16, device=dev)
+        per_expert_fc1 = 2 * Wg[0].nbytes / E
+        per_expert_fc2 = Wd[0].nbytes / E
+        fc1 = [(lambda i=i: ops.tc_linear(Wg[i], xs, None, rows=rows, w_up=Wu[i], tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=st,
+                                          quant_out=h1q, inv_gs_out=Wd[i].inv_act_gs)) for i in range(copies)]
+        fc2 = [(lambda i=i: ops.tc_linear(Wd[i], h1q, y2, rows=rows, tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=st)) for i in range(copies)]
+        u1, u2 = graph_time_us(fc1), graph_time_us(fc2)
+        both = graph_time_us([f for pair in zip(fc1, fc2) for f in pair]) * 2
+        print(f"{kind} tn={tn} T={T} active experts {active}/{E}: FC1 {u1:7.1f} us {active * per_expert_fc1 / u1 / 1e3:7.1f} GB/s | "
+              f"FC2 {u2:7.1f} us {active * per_expert_fc2 / u2 / 1e3:7.1f} GB/s | FC1+FC2 back to back {both:7.1f} us", flush=True)
+        del Wg, Wu, Wd
+    print("status", st.tolist())
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="stream", choices=["stream", "small", "trace"])
+    ap.add_argument("--mode", default="stream", choices=["stream", "small", "trace", "moe"])
     ap.add_argument("--tokens", type=int, default=16)
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
-    {"stream": stream, "small": small, "trace": trace}[a.mode](dev, a.tokens)
+    {"stream": stream, "small": small, "trace": trace, "moe": moe}[a.mode](dev, a.tokens)
 
 
 if __name__ == "__main__":

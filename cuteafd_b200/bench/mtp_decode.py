@@ -42,6 +42,8 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
             lay["n_micro"] = 1
     if getattr(args, "attn_groups", 0) and lay["layout"] == "split":
         lay["attn_groups"] = args.attn_groups
+    if lay["layout"] == "split" and spec.attn.kind == "mla" and world >= 4 and comm == "p2p":
+        lay["n_micro"] = 2
     if getattr(args, "n_micro", 0):
         lay["n_micro"] = args.n_micro
     width = n_draft + 1

@@ -37,6 +37,12 @@ class AttentionSpec:
     # the sink and `swa_rope_theta` (0 = the same theta).  0 = every layer as configured above.
     full_every: int = 0
     swa_rope_theta: float = 0.0
+    # Sparse attention with a learned indexer (DSA of the DeepSeek-V3.2 / GLM-5 lines; MLA only): with index_topk = k > 0 every
+    # query token scores the visible cached positions with `index_heads` small heads of `index_dim` dimensions
+    # (score = sum_h w_h * relu(q_h . k)), and attends only to its k best positions once it can see more than k.
+    index_topk: int = 0
+    index_heads: int = 32
+    index_dim: int = 128
 
     @property
     def q_dim(self) -> int:

@@ -37,6 +37,11 @@ class MlaWeights:
     w_uk_t: TcWeight            # G = Hl, [512, 128]: q_lat = q_nope @ W_UK
     w_uv: TcWeight              # G = Hl, [128, 512]: o = o_lat @ W_UV^T
     w_kvb: TcWeight | None = None   # [Hl * 256, 512]: per head 128 key rows then 128 value rows (prefill expands the latent cache with it)
+    # sparse-attention indexer (AttentionSpec.index_topk > 0): index queries from the compressed query (or the hidden state),
+    # index keys and head weights (already scaled by index_heads ** -0.5) from the hidden state
+    wq_idx: TcWeight | None = None  # [Hi * Di, q_lora | H]
+    wk_idx: TcWeight | None = None  # [Di, H]
+    w_idx: TcWeight | None = None   # [Hi, H]
 
     def ensure_kvb(self) -> TcWeight:
         """The kv_b projection in its checkpoint orientation, rebuilt from the two absorb matrices on first use (prefill only;
@@ -62,7 +67,10 @@ def _mla_from_masters(spec: ModelSpec, lw: dict, device, dk: str, act_gs: float)
         q_a_norm=f32(lw["q_a_norm"]) if "q_a_norm" in lw else None,
         wq_b=TcWeight.from_master(lw["wq_b"] if "wq_b" in lw else lw["wq"], dk, device, act_gs),
         wkv_a=TcWeight.from_master(lw["wkv_a"], dk, device, act_gs), kv_a_norm=f32(lw["kv_a_norm"]),
-        w_uk_t=TcWeight.from_master(w_uk_t, "bf16", device), w_uv=TcWeight.from_master(w_uv, "bf16", device))
+        w_uk_t=TcWeight.from_master(w_uk_t, "bf16", device), w_uv=TcWeight.from_master(w_uv, "bf16", device),
+        wq_idx=TcWeight.from_master(lw["wq_idx"], dk, device, act_gs) if "wq_idx" in lw else None,
+        wk_idx=TcWeight.from_master(lw["wk_idx"], dk, device, act_gs) if "wk_idx" in lw else None,
+        w_idx=TcWeight.from_master(lw["w_idx"] * (a.index_heads ** -0.5), dk, device, act_gs) if "w_idx" in lw else None)
 
 
 def mla_weights_from_masters(spec: ModelSpec, masters: dict, device, act_gs: float = 1.0 / 64) -> DeviceWeights:
@@ -117,6 +125,9 @@ def mla_weights_random(spec: ModelSpec, device, *, heads_local: int | None = Non
                              wq_b=R(1, Hl * qk, a.q_lora_rank or h, dk, 3), wkv_a=R(1, a.kv_lora_rank + a.qk_rope_head_dim, h, dk, 4),
                              kv_a_norm=ones(a.kv_lora_rank), w_uk_t=R(Hl, a.kv_lora_rank, a.qk_nope_head_dim, "bf16", 5),
                              w_uv=R(Hl, a.v_head_dim, a.kv_lora_rank, "bf16", 6))
+        if a.index_topk:
+            out.mla.wq_idx = R(1, a.index_heads * a.index_dim, a.q_lora_rank or h, dk, 14)
+            out.mla.wk_idx, out.mla.w_idx = R(1, a.index_dim, h, dk, 15), R(1, a.index_heads, h, dk, 16)
         if spec.is_moe_layer(i):
             out.router = R(1, m.n_experts, h, "bf16", 7)
             if m.use_bias:
@@ -155,6 +166,17 @@ class MlaEngine(Engine):
             call("cuteafd_tmap_encode_latent", host[l].data_ptr(), self.kv[l].data_ptr(), self.n_pages * PAGE)
         self.kv_tmaps = host.to(self.device)
         self.mla_bufs: dict = {}
+        a = spec.attn
+        if a.index_topk:
+            if a.index_dim != 128 or a.index_heads % 16 or a.index_heads > 64:
+                raise ValueError("the sparse-attention indexer is built for 128-wide index keys and 16..64 index heads (a multiple of 16)")
+            # index-key cache: one 128-wide bf16 row per token and layer, same slots as the latent cache
+            self.idx_kv = torch.zeros(n_kv, self.n_pages * PAGE, a.index_dim, dtype=torch.bfloat16, device=self.device)
+            host = torch.zeros(n_kv, 128, dtype=torch.uint8)
+            for l in range(n_kv):
+                call("cuteafd_tmap_encode_index_keys", host[l].data_ptr(), self.idx_kv[l].data_ptr(), self.n_pages * PAGE)
+            self.idx_tmaps = host.to(self.device)
+            self._dsa: dict = {}
 
     def _mla_buf(self, L: Lane):
         if getattr(L, "mla_buf", None) is None:
@@ -164,6 +186,9 @@ class MlaEngine(Engine):
             b = {"q_a": bf(cap, max(a.q_lora_rank, 8)), "q_an": bf(cap, max(a.q_lora_rank, 8)), "q": bf(cap, Hl * 192), "kv_a": bf(cap, DQK),
                  "q_nope": bf(Hl * cap, 128), "q_rope": bf(cap, Hl, 64), "q_lat": bf(Hl * cap, DV), "o_lat": bf(Hl * cap, DV),
                  "o_head": bf(Hl * cap, a.v_head_dim), "o_tok": bf(cap, Hl * a.v_head_dim)}
+            if a.index_topk:
+                b["q_idx"], b["k_idx"] = bf(cap, a.index_heads * a.index_dim), bf(cap, a.index_dim)
+                b["w_idx"] = torch.zeros(cap, a.index_heads, dtype=torch.float32, device=dev)
             b["q_an_act"] = (ActBuffer.alloc(self.dense_kind, cap, a.q_lora_rank, L.tn, dev) if self.dense_kind != KIND_BF16 and a.q_lora_rank
                              else ActBuffer.wrap_bf16(b["q_an"], L.tn))
             b["o_tok_act"] = (ActBuffer.alloc(self.dense_kind, cap, Hl * a.v_head_dim, L.tn, dev) if self.dense_kind != KIND_BF16
@@ -193,6 +218,7 @@ class MlaEngine(Engine):
         Hl = self.heads_local
         b = self._mla_buf(L)
         xq = self._norm_in(lw, L, T)
+        qa = None
         if w.wq_a is not None:
             self._dense(w.wq_a, xq, b["q_a"], T)
             ops.add_rmsnorm(b["q_a"], None, w.q_a_norm, b["q_an"], spec.rms_eps, rows=T)
@@ -200,12 +226,35 @@ class MlaEngine(Engine):
             self._dense(w.wq_b, qa, b["q"], T)
         else:
             self._dense(w.wq_b, xq, b["q"], T)
+        if a.index_topk and w.wq_idx is not None:
+            # indexer operands of this step's tokens; the index keys join the paged index-key cache at the tokens' slots
+            self._dense(w.wq_idx, qa if qa is not None else xq, b["q_idx"], T)
+            self._dense(w.wk_idx, xq, b["k_idx"], T)
+            self._dense(w.w_idx, xq, b["w_idx"], T)
+            call("cuteafd_dsa_scatter_rows", ptr(b["k_idx"]), ptr(md["slot_map"]), ptr(self.idx_kv[li]), T, self.idx_kv.shape[1], a.index_dim * 2,
+                 ptr(self.status), stream())
+            self.launches_per_step += 1
         self._dense(w.wkv_a, xq, b["kv_a"], T)
         call("cuteafd_mla_kv_prepare", ptr(b["kv_a"]), ptr(w.kv_a_norm), ptr(md["positions"]), ptr(md["slot_map"]), ptr(self.kv[li]), T,
              self.kv.shape[1], a.rope_theta, spec.rms_eps, 1 if a.rope_interleaved else 0, ptr(self.status), stream())
         q_nope, q_lat = b["q_nope"][:Hl * T], b["q_lat"][:Hl * T]
         call("cuteafd_mla_q_split", ptr(b["q"]), ptr(md["positions"]), ptr(q_nope), ptr(b["q_rope"]), T, Hl, a.rope_theta,
              1 if a.rope_interleaved else 0, stream())
+        if a.index_topk and w.wq_idx is not None and self._sparse_step(sh):
+            tn = ops.pick_tn(T, swiglu=True)
+            tiles, n_tiles, max_tiles = self._head_tiles(b, T, tn)
+            qn_act = self._act(b, ("qn", T, tn), q_nope, tn)
+            ops.tc_linear(w.w_uk_t, qn_act, q_lat, rows=Hl * T, tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=self.status)
+            o_lat = b["o_lat"][:Hl * T]
+            self._sparse_attention(li, b, sh, q_lat, o_lat)
+            o_head = b["o_head"][:Hl * T]
+            ol_act = self._act(b, ("ol", T, tn), o_lat, tn)
+            ops.tc_linear(w.w_uv, ol_act, o_head, rows=Hl * T, tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=self.status)
+            call("cuteafd_head_to_token_major", ptr(o_head), ptr(b["o_tok"]), T, Hl, a.v_head_dim, stream())
+            oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
+            self._attn_out(li, lw, oq, L, T)
+            self.launches_per_step += 10
+            return
         if self._use_prefill_path(sh):
             self._prefill_attention(li, w, b, sh, q_nope)
             oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
@@ -234,6 +283,74 @@ class MlaEngine(Engine):
         oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
         self._attn_out(li, lw, oq, L, T)
         self.launches_per_step += 7
+
+    # ------------------------------------------------------------------ sparse attention over the indexer's selection
+    SPARSE_MAX_Q = 8          # decode and verify steps (at most this many query rows per sequence) always take the sparse path
+
+    def _sparse_step(self, sh: StepShape) -> bool:
+        """Decode / verify steps of a model with an indexer always run score -> top-k -> gather -> attention (a row that sees at
+        most k positions selects all of them, which is dense attention), so a captured graph stays valid as contexts grow past
+        k.  Longer query runs (prefill chunks) attend densely while every context of the step has at most k tokens; beyond that
+        they are refused (per-row selection for prefill chunks is not built)."""
+        a = self.spec.attn
+        if sh.T == 0:
+            return False
+        if sh.max_q_len <= self.SPARSE_MAX_Q:
+            return True
+        if not torch.cuda.is_current_stream_capturing() and max(self.mh["kv_len"][:sh.n_seq].tolist()) > a.index_topk:
+            raise NotImplementedError(f"prefill chunks over contexts longer than index_topk = {a.index_topk} need per-row selection, which is not built")
+        return False
+
+    def _sparse_attention(self, li: int, b: dict, sh: StepShape, q_lat: torch.Tensor, o_lat: torch.Tensor):
+        """index scores of every query row over its sequence's cached index keys -> top-k positions per row -> gather of the
+        selected latent rows into per-row pseudo-pages -> the absorbed attention kernel with one "sequence" per query row.
+        Reference: v41_index_scores.cu:37, v41_index_topk.cu:25-57, v41_sparse_attention.cu:89."""
+        a, Hl, dev, T, md = self.spec.attn, self.heads_local, self.device, sh.T, self.md
+        k, kp = a.index_topk, -(-a.index_topk // PAGE) * PAGE
+        ld = -(-(self.max_pages * PAGE) // 128) * 128
+        key = (T, sh.n_seq, sh.max_q_len, sh.uniform)
+        st = self._dsa.get(key)
+        if st is None:
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+            st = {"seq_of_row": i32([r // sh.max_q_len for r in range(T)]), "q_start": i32(list(range(T))), "q_len": i32([1] * T),
+                  "pages": i32([[r * (kp // PAGE) + j for j in range(kp // PAGE)] for r in range(T)]),
+                  "sel": torch.zeros(T, k, dtype=torch.int32, device=dev), "count": torch.zeros(T, dtype=torch.int32, device=dev)}
+            self._dsa[key] = st
+        if not sh.uniform:           # ragged step (eager only): rows -> sequences from the host copy of the step's description
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("a ragged sparse-attention step cannot be captured")
+            qs, ql = self.mh["q_start"][:sh.n_seq].tolist(), self.mh["q_len"][:sh.n_seq].tolist()
+            rows = [0] * T
+            for sq, (q0, n) in enumerate(zip(qs, ql)):
+                rows[q0:q0 + n] = [sq] * n
+            st["seq_of_row"].copy_(torch.tensor(rows, dtype=torch.int32).pin_memory(), non_blocking=True)
+        if self._dsa.get("rows", 0) < T:          # shared scratch, grown to the largest step (zero-filled: unselected rows stay finite)
+            self._dsa["scores"] = torch.zeros(T, ld, dtype=torch.float32, device=dev)
+            self._dsa["gather"] = torch.zeros(T * kp, DQK, dtype=torch.bfloat16, device=dev)
+            host = torch.zeros(128, dtype=torch.uint8)
+            call("cuteafd_tmap_encode_latent", host.data_ptr(), self._dsa["gather"].data_ptr(), T * kp)
+            self._dsa["gmap"] = host.to(dev)
+            self._dsa["rows"] = T
+            self.graphs.clear()                    # captured graphs hold the old scratch addresses
+        scores, gather = self._dsa["scores"], self._dsa["gather"]
+        sp = ptr(self.status)
+        call("cuteafd_dsa_index_scores", ptr(b["q_idx"]), ptr(b["w_idx"]), ptr(self.idx_tmaps[li]), ptr(md["page_table"]), ptr(md["kv_len"]),
+             ptr(md["q_start"]), ptr(md["q_len"]), ptr(scores), T, sh.n_seq, sh.max_q_len, self.max_pages * PAGE, a.index_heads, ld,
+             md["page_table"].shape[1], sp, stream())
+        call("cuteafd_dsa_topk", ptr(scores), ld, ptr(md["positions"]), T, k, 1, ptr(st["sel"]), ptr(st["count"]), stream())
+        call("cuteafd_dsa_gather_rows", ptr(self.kv[li]), ptr(md["page_table"]), ptr(st["seq_of_row"]), ptr(st["sel"]), ptr(st["count"]), ptr(gather),
+             T, k, kp, md["page_table"].shape[1], self.kv.shape[1], DQK * 2, sp, stream())
+        splits = self.attn_splits_for(T, 1, k)
+        po = pml = None
+        if splits > 1:
+            need = splits * T * Hl
+            if getattr(self, "mla_part_o", None) is None or self.mla_part_o.numel() < need * DV:
+                self.mla_part_o = torch.empty(need * DV, dtype=torch.float32, device=dev)
+                self.mla_part_ml = torch.empty(need * 2, dtype=torch.float32, device=dev)
+            po, pml = self.mla_part_o, self.mla_part_ml
+        scale = (a.qk_nope_head_dim + a.qk_rope_head_dim) ** -0.5
+        call("cuteafd_mla_attention", ptr(q_lat), ptr(b["q_rope"]), ptr(self._dsa["gmap"]), ptr(st["pages"]), ptr(st["count"]), ptr(st["q_start"]),
+             ptr(st["q_len"]), ptr(o_lat), ptr(po), ptr(pml), T, T, 1, Hl, kp // PAGE, splits, scale, sp, stream())
 
     # ------------------------------------------------------------------ prefill: per-head attention over the expanded context
     PREFILL_MIN_Q = int(os.environ.get("CUTEAFD_MLA_PREFILL_MIN_Q", "128"))          # 0 disables the path

@@ -160,14 +160,15 @@ class AfdRunner:
 
 
 def default_layout(spec: ModelSpec, world: int, comm: str) -> dict:
-    """Layout a benchmark or a server uses when none is named.  GQA models whose weights fit every GPU several times over run
-    colocated (data-parallel attention + expert-parallel FFN on every GPU: nothing idles, every expert's weights stream once
-    per layer for the whole batch); MLA models keep the named split, attention TP2 + experts on the other GPUs, with two
-    micro-batches in flight so the expert round trip hides behind the other micro-batch's attention."""
+    """Layout a benchmark uses when none is named: colocated (data-parallel attention + expert-parallel FFN on every GPU: nothing
+    idles, every expert's weights stream once per layer for the whole batch, and attention splits its KV range over the SMs the
+    small per-GPU batch leaves free).  Measured on 4 GPUs with the DeepSeek-V3 shape at batch 64 @ 8k (16 layers): 9.8 ms per
+    step colocated against 25.0 ms on attention TP2 + EP2 with two micro-batches.  An MLA model on fewer than four GPUs keeps the
+    split (its weights do not fit twice).  The NCCL-only arm always runs the split."""
     if comm == "nccl":
         return {"layout": "split", "attn_groups": 1, "n_micro": 1}
-    if spec.attn.kind == "mla":
-        return {"layout": "split", "attn_groups": 1, "n_micro": 2 if world >= 4 else 1}
+    if spec.attn.kind == "mla" and world < 4:
+        return {"layout": "split", "attn_groups": 1, "n_micro": 1}
     return {"layout": "colocated", "attn_groups": world, "n_micro": 1}
 
 
@@ -178,6 +179,8 @@ def run_decode_bench_distributed(args, spec: ModelSpec, rank: int, world: int, l
         lay["layout"] = args.layout
         if args.layout == "split":
             lay["attn_groups"] = 1
+            if spec.attn.kind == "mla" and world >= 4 and comm == "p2p":
+                lay["n_micro"] = 2         # the named split hides the expert round trip behind a second micro-batch
     if getattr(args, "attn_groups", 0) and lay["layout"] == "split":
         lay["attn_groups"] = args.attn_groups
     if getattr(args, "n_micro", 0):

@@ -37,6 +37,10 @@ def init_layer(spec: ModelSpec, gen: torch.Generator, layer: int, force_dense: b
         w["kv_a_norm"] = torch.ones(a.kv_lora_rank)
         w["wkv_b"] = _randn(gen, a.n_heads * (a.qk_nope_head_dim + a.v_head_dim), a.kv_lora_rank, std=s)
         w["wo"] = _randn(gen, h, a.n_heads * a.v_head_dim, std=s)
+        if a.index_topk:        # indexer: queries from the compressed query (or the hidden state), keys and head weights from the hidden state
+            w["wq_idx"] = _randn(gen, a.index_heads * a.index_dim, a.q_lora_rank or h, std=s)
+            w["wk_idx"] = _randn(gen, a.index_dim, h, std=s)
+            w["w_idx"] = _randn(gen, a.index_heads, h, std=s)
     else:
         w["wq"] = _randn(gen, a.n_heads * a.head_dim, h, std=s)
         w["wk"] = _randn(gen, a.n_kv_heads * a.head_dim, h, std=s)
@@ -119,6 +123,7 @@ class RefModel:
         xn = self._aq(ops.rmsnorm(x, lw["attn_norm"], spec.rms_eps), "dense")
         if a.kind == "mla":
             nope, rope, dv = a.qk_nope_head_dim, a.qk_rope_head_dim, a.v_head_dim
+            qa = None
             if "wq_a" in lw:
                 qa = ops.rmsnorm(xn @ lw["wq_a"].T, lw["q_a_norm"], spec.rms_eps)
                 q = self._aq(qa, "dense") @ lw["wq_b"].T
@@ -132,7 +137,18 @@ class RefModel:
             ckv, kr, kpos = cache.append(key, ckv, kr, pos)
             kvb = (ckv @ lw["wkv_b"].T).reshape(-1, a.n_heads, nope + dv)
             k = torch.cat([kvb[..., :nope], kr[:, None, :].expand(-1, a.n_heads, -1)], -1)
-            o = ops.attention(q, k, kvb[..., nope:], pos, kpos, scale=1.0 / math.sqrt(nope + rope))
+            allowed = None
+            if a.index_topk and "wq_idx" in lw:
+                # the indexer's operands are bf16 on the device (its score product runs on the tensor cores): round them here too
+                b16 = lambda t: t.to(torch.bfloat16).float()
+                src = self._aq(qa, "dense") if qa is not None else xn
+                q_idx = b16((src @ lw["wq_idx"].T).reshape(T, a.index_heads, a.index_dim))
+                k_new = b16(xn @ lw["wk_idx"].T)
+                w_idx = (xn @ lw["w_idx"].T) * (a.index_heads ** -0.5)
+                k_idx, _, _ = cache.append(("idx", key), k_new, k_new[:, :1], pos)
+                if k_idx.shape[0] > a.index_topk:
+                    allowed = ops.topk_mask(ops.index_scores(q_idx, w_idx, k_idx, pos, kpos), a.index_topk)
+            o = ops.attention(q, k, kvb[..., nope:], pos, kpos, scale=1.0 / math.sqrt(nope + rope), allowed=allowed)
             o = o.reshape(T, a.n_heads * dv)
         else:
             q = (xn @ lw["wq"].T).reshape(T, a.n_heads, a.head_dim)

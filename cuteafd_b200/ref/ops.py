@@ -44,9 +44,34 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, theta: float = 10000.0,
     return out.to(x.dtype)
 
 
+def index_scores(q_idx: torch.Tensor, w: torch.Tensor, k_idx: torch.Tensor, q_pos: torch.Tensor, k_pos: torch.Tensor) -> torch.Tensor:
+    """Indexer scores of sparse attention: q_idx [Tq, Hi, Di], w [Tq, Hi], k_idx [Tk, Di] ->
+    [Tq, Tk] = sum_h w[t, h] * relu(q_idx[t, h] . k_idx[s]), -inf where the key lies in the query's future."""
+    dots = torch.einsum("qhd,kd->qhk", q_idx.float(), k_idx.float())
+    s = (torch.relu(dots) * w.float()[:, :, None]).sum(1)
+    return s.masked_fill(k_pos[None, :] > q_pos[:, None], float("-inf"))
+
+
+def topk_mask(scores: torch.Tensor, k: int) -> torch.Tensor:
+    """[Tq, Tk] bool: the k best finite entries of every row (all of them when a row has at most k); ties at the threshold
+    resolve to the lowest key index (the device kernel's rule)."""
+    Tq, Tk = scores.shape
+    out = torch.zeros(Tq, Tk, dtype=torch.bool)
+    for t in range(Tq):
+        row = scores[t]
+        vis = torch.isfinite(row)
+        n = int(vis.sum())
+        if n <= k:
+            out[t] = vis
+            continue
+        order = sorted(range(Tk), key=lambda i: (-float(row[i]), i))        # best first, lowest index among equals
+        out[t, torch.tensor(order[:k])] = True
+    return out
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor,
               k_pos: torch.Tensor, scale: float | None = None, window: int = 0,
-              sink: torch.Tensor | None = None) -> torch.Tensor:
+              sink: torch.Tensor | None = None, allowed: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention by absolute position.  q: [Tq, Hq, D], k: [Tk, Hkv, D], v: [Tk, Hkv, Dv].
     Query at position p sees keys with position <= p (and > p - window when window > 0).
     `sink` ([Hq]) adds one extra softmax logit per head whose value contribution is zero."""
@@ -60,6 +85,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Te
     mask = k_pos[None, :] > q_pos[:, None]
     if window > 0:
         mask |= k_pos[None, :] <= (q_pos[:, None] - window)
+    if allowed is not None:                 # sparse attention: [Tq, Tk] bool, keys a query may attend to
+        mask = mask | ~allowed
     s = s.masked_fill(mask[None], float("-inf"))
     if sink is not None:
         s = torch.cat([s, sink.float()[:, None, None].expand(Hq, Tq, 1)], -1)

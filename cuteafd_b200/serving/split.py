@@ -48,6 +48,7 @@ def build_split_serving(a, world: int):
         masters = init_weights(spec, 0)
     lay = default_layout(spec, world, "p2p")
     lay["layout"], lay["attn_groups"] = "split", 1           # one scheduler drives one attention group
+    lay["n_micro"] = 2 if spec.attn.kind == "mla" and world >= 4 else 1
     if getattr(a, "n_micro", 0):
         lay["n_micro"] = a.n_micro
     n_pages = a.pool_tokens // 64 if a.pool_tokens else 4096
