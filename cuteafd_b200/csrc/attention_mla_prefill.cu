@@ -344,6 +344,347 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The same structure for paged GQA prefill (head_dim 128): a CTA owns 128 query rows of one KV head (row = token_in_tile * G +
+// head_in_group) and walks the sequence's pages two at a time (128-key tiles), K and V straight from the paged store.  Causal
+// mask, optional sliding window and sink logit as in the decode kernel (attention_tc.cu), no split-KV: a prefill chunk has
+// enough query tiles to fill the GPU.  The 64-key decode kernel spends 8 + 4 tcgen05.mma per 64 keys; this one 8 + 8 per 128 keys.
+#define GQ_K_STAGE 32768          // 2 chunks (64 dims each) x [128 keys x 128 B]
+struct GqaPrefillArgs {
+  const bf16* q;
+  const CUtensorMap* kv_map;    // 3-D {128, 2 * Hkv, slots}, box {64, 1, 64}, 128-byte swizzle (the decode kernel's descriptor)
+  const int* page_table; const int* kv_len; const int* q_start; const int* q_len;
+  const float* sink;
+  bf16* out;
+  int* status;
+  int q_stride, Hq, Hkv, max_pages, window, max_q_tiles;
+  float scale;
+};
+
+__global__ void __launch_bounds__(192, 1) gqa_prefill_kernel(const __grid_constant__ GqaPrefillArgs a) {
+  pdl_launch(); pdl_wait();
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sP = smem;
+  uint8_t* sK = sP + PF_P_BYTES;
+  uint8_t* sV = sK + PF_NS * GQ_K_STAGE;
+  uint64_t* bars = (uint64_t*)(sV + PF_NSV * PF_V_STAGE);
+  uint64_t* k_full = bars; uint64_t* k_empty = bars + 2; uint64_t* v_full = bars + 4; uint64_t* v_empty = bars + 6;     // [<= 2] each
+  uint64_t* s_full = bars + 8;          // [2]
+  uint64_t* s_free = bars + 10;         // [2]: the softmax threads are done with the score buffer
+  uint64_t& p_full = bars[12]; uint64_t& o_done = bars[13];
+  uint32_t& tmem_slot = *(uint32_t*)(bars + 14);
+  int& abort_flag = *(int*)(bars + 15);
+  if (smem_u32(smem) & 1023) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, 0xA14); return; }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+
+  // the heaviest query tiles (most visible keys) are scheduled first
+  const int G = a.Hq / a.Hkv, tok_per_tile = 128 / G;
+  const int kvh = blockIdx.x;
+  const int seq = blockIdx.y / a.max_q_tiles, qt = a.max_q_tiles - 1 - blockIdx.y % a.max_q_tiles;
+  const int qlen = a.q_len[seq], kvlen = a.kv_len[seq];
+  const int tok0 = qt * tok_per_tile;
+  if (tok0 >= qlen) return;
+  const int ntok = min(tok_per_tile, qlen - tok0);
+  const int R = ntok * G;                                   // row = token_in_tile * G + head_in_group
+  const int row_base = a.q_start[seq] + tok0;
+  const int first_pos = kvlen - qlen + tok0;
+  const int hi = first_pos + ntok;
+  const int lo = a.window > 0 ? max(0, first_pos - a.window + 1) : 0;
+  const int tile0 = lo / PF_KT;
+  const int n_tiles = max(0, (hi + PF_KT - 1) / PF_KT - tile0);
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 128); }
+    mbar_init(&p_full, 128); mbar_init(&o_done, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  const uint32_t S0_COL = 0, O_COL = 128, S1_COL = 256, Q_COL = 384;
+  // query rows -> tensor memory (row = lane, two bf16 per 32-bit column, 64 columns for the 128-wide head)
+  if (warp >= 2) {
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t dst = tmem + ((uint32_t)((warp & 3) * 32) << 16) + Q_COL;
+    const int rr = r < R ? r : 0;
+    const bf16* src = a.q + (size_t)(row_base + rr / G) * a.q_stride + (size_t)(kvh * G + rr % G) * 128;
+#pragma unroll 1
+    for (int g = 0; g < 4; ++g) {                  // 16 columns = 32 elements per store
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = r < R ? *(const uint4*)(src + g * 32 + j * 8) : make_uint4(0, 0, 0, 0);
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
+      pf_tmem_st_x16(dst + g * 16, w);
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ K / V producer
+    // K runs one tile ahead of V in this warp's program order: the single V stage only frees when the previous PV product
+    // retires, and the K tile of the NEXT score pass must not queue behind that wait.
+    auto page_of = [&](int key) -> int {                   // pages past the sequence's table are read as page 0 (finite rows, masked keys)
+      const int pi = key / 64;
+      return pi < a.max_pages ? a.page_table[(size_t)seq * a.max_pages + pi] : 0;
+    };
+    auto load_k = [&](int i) -> bool {
+      const int s = i % PF_NS, ph = ((i / PF_NS) & 1) ^ 1;
+      if (!mbar_wait_bounded(&k_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); return false; }
+      if (lane == 0) {
+        const int key0 = (tile0 + i) * PF_KT;
+        mbar_expect_tx(&k_full[s], GQ_K_STAGE);
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int slot0 = page_of(key0 + p * 64) * 64;
+          tma_load_3d(sK + s * GQ_K_STAGE + p * 8192, a.kv_map, &k_full[s], 0, kvh, slot0);
+          tma_load_3d(sK + s * GQ_K_STAGE + 16384 + p * 8192, a.kv_map, &k_full[s], 64, kvh, slot0);
+        }
+      }
+      __syncwarp();
+      return true;
+    };
+    bool okp = n_tiles > 0 ? load_k(0) : true;
+    for (int i = 0; okp && i < n_tiles && !*abortp; ++i) {
+      if (i + 1 < n_tiles && !load_k(i + 1)) break;
+      const int sv = i % PF_NSV, phv = ((i / PF_NSV) & 1) ^ 1;
+      if (!mbar_wait_bounded(&v_empty[sv], phv, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, 0x1000 + i); break; }
+      if (lane == 0) {
+        const int key0 = (tile0 + i) * PF_KT;
+        mbar_expect_tx(&v_full[sv], PF_V_STAGE);
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          const int slot0 = page_of(key0 + p * 64) * 64;
+          tma_load_3d(sV + sv * PF_V_STAGE + p * 8192, a.kv_map, &v_full[sv], 0, a.Hkv + kvh, slot0);
+          tma_load_3d(sV + sv * PF_V_STAGE + 16384 + p * 8192, a.kv_map, &v_full[sv], 64, a.Hkv + kvh, slot0);
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t id_s = pf_idesc(PF_KT, 0), id_o = pf_idesc(128, 1);
+    auto issue_scores = [&](int j) -> bool {     // S[j & 1] = Q K(j)^T once the softmax threads have copied tile j - 2 out of it
+      const int s = j % PF_NS;
+      if (j >= 2 && !mbar_wait_bounded(&s_free[j & 1], ((j - 2) >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0x2000 + j); return false; }
+      if (!mbar_wait_bounded(&k_full[s], (j / PF_NS) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, j); return false; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t k0 = smem_u32(sK + s * GQ_K_STAGE), d = tmem + ((j & 1) ? S1_COL : S0_COL);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f16_ta(d, tmem + Q_COL + kb * 32 + k * 8, umma_desc_sw128(k0 + kb * 16384) + 2 * k, id_s, (kb | k) ? 1u : 0u);
+        tc_commit(&s_full[j & 1]);
+        tc_commit(&k_empty[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = true;
+    for (int j = 0; ok && j < min(2, n_tiles); ++j) ok = issue_scores(j);
+    for (int i = 0; ok && i < n_tiles; ++i) {
+      const int sv = i % PF_NSV;
+      if (!mbar_wait_bounded(&p_full, i & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0x3000 + i); break; }
+      if (!mbar_wait_bounded(&v_full[sv], (i / PF_NSV) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, 0x4000 + i); break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t v0 = smem_u32(sV + sv * PF_V_STAGE);
+#pragma unroll
+        for (int k = 0; k < PF_KT / 16; ++k)       // 16 keys per MMA: P chunk k / 4 (64 keys per 128-byte row), V rows 16 k .. 16 k + 15
+          tc_mma_f16(tmem + O_COL, umma_desc_sw128(smem_u32(sP) + (k >> 2) * 16384) + 2 * (k & 3), pf_desc_mn_sw128(v0 + k * 2048, 16384, 1024), id_o,
+                     (i | k) ? 1u : 0u);
+        tc_commit(&v_empty[sv]);
+        tc_commit(&o_done);
+      }
+      __syncwarp();
+      if (i + 2 < n_tiles) ok = issue_scores(i + 2);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue: thread = query row
+    const int q4 = warp & 3, r = q4 * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+    const bool live = r < R;
+    const int qpos = live ? first_pos + r / G : -1;
+    const int wlo = a.window > 0 ? qpos - a.window : -1;           // keys at or below this position are outside the row's window
+    const float sc2 = a.scale * 1.4426950408889634f;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      if (!mbar_wait_bounded(&s_full[i & 1], (i >> 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, i); ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_addr + ((i & 1) ? S1_COL : S0_COL);
+      const int key0 = (tile0 + i) * PF_KT;
+      // CTA-uniform: every key of the tile is visible to every live row (below the diagonal and inside every row's window)
+      const bool all_visible = key0 + PF_KT - 1 <= first_pos && (a.window <= 0 || key0 > first_pos + ntok - 1 - a.window);
+      // two passes over the tile's 128 score columns: row maximum, then exponentials packed to bf16 pairs (64 registers).
+      // Tiles below the diagonal need no mask (CTA-uniform test), which is all but the last one or two of a long context.
+      float mx = -INFINITY;
+      uint32_t pk[PF_KT / 2];
+      float psum = 0.f;
+      float alpha = 1.f;
+      if (all_visible) {           // CTA-uniform (the tensor-memory loads below are warp collectives); rows past R hold zero queries
+#pragma unroll 1
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sr[j]));
+        }
+        mx *= sc2;                                   // sc2 > 0: scaling commutes with the maximum
+        if (mx > m_ref + 8.f) {
+          if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
+          m_ref = mx;
+        }
+#pragma unroll
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float e0 = exp2f(fmaf(__uint_as_float(sr[2 * j]), sc2, -m_ref)), e1 = exp2f(fmaf(__uint_as_float(sr[2 * j + 1]), sc2, -m_ref));
+            psum += e0 + e1;
+            bf162 h = __floats2bfloat162_rn(e0, e1);
+            pk[c * 16 + j] = *(uint32_t*)&h;
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int kp = key0 + c * 32 + j;
+            if (live && kp <= qpos && kp > wlo) mx = fmaxf(mx, __uint_as_float(sr[j]) * sc2);
+          }
+        }
+        if (mx > m_ref + 8.f) {
+          if (m_ref != -INFINITY) { alpha = exp2f(m_ref - mx); l *= alpha; }
+          m_ref = mx;
+        }
+#pragma unroll
+        for (int c = 0; c < PF_KT / 32; ++c) {
+          uint32_t sr[32];
+          tmem_ld_x16(s_addr + c * 32, sr);
+          tmem_ld_x16(s_addr + c * 32 + 16, sr + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int kp = key0 + c * 32 + 2 * j;
+            const float e0 = (live && kp <= qpos && kp > wlo) ? exp2f(fmaf(__uint_as_float(sr[2 * j]), sc2, -m_ref)) : 0.f;
+            const float e1 = (live && kp + 1 <= qpos && kp + 1 > wlo) ? exp2f(fmaf(__uint_as_float(sr[2 * j + 1]), sc2, -m_ref)) : 0.f;
+            psum += e0 + e1;
+            bf162 h = __floats2bfloat162_rn(e0, e1);
+            pk[c * 16 + j] = *(uint32_t*)&h;
+          }
+        }
+      }
+      l += psum;
+      tc_fence_before();
+      mbar_arrive(&s_free[i & 1]);
+      // the previous P V product must have finished before P is overwritten or O rescaled
+      if (i > 0 && !mbar_wait_bounded(&o_done, (i - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, 0x1000 + i); ok = false; break; }
+      tc_fence_after();
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {      // warp-uniform: tcgen05.ld/st are warp collectives
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[16];
+          tmem_ld_x16(tmem + lane_addr + O_COL + c * 16, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          pf_tmem_st_x16(tmem + lane_addr + O_COL + c * 16, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+      // P: two K-major chunks of 64 keys; 16-byte unit u of a row holds keys 8 u .. 8 u + 7
+#pragma unroll
+      for (int u = 0; u < PF_KT / 8; ++u)
+        *(uint4*)(sP + (u >> 3) * 16384 + r * 128 + (((u & 7) ^ (r & 7)) << 4)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&p_full);
+    }
+    if (ok && n_tiles > 0 && !mbar_wait_bounded(&o_done, (n_tiles - 1) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, 999); ok = false; }
+    tc_fence_after();
+    if (__all_sync(0xffffffffu, ok)) {
+      const int rr = live ? r : 0;
+      const int t = row_base + rr / G, h = kvh * G + rr % G;
+      float scale_o = 1.f, lt = l;
+      if (a.sink) {                                     // learned sink logit: one more softmax term with a zero value
+        const float m_nat = (m_ref == -INFINITY) ? -INFINITY : m_ref * 0.6931471805599453f;
+        const float sk = a.sink[h], m2 = fmaxf(m_nat, sk);
+        const float e1 = (m_nat == -INFINITY) ? 0.f : __expf(m_nat - m2);
+        lt = l * e1 + __expf(sk - m2); scale_o = e1;
+      }
+      const float inv = lt > 0.f ? scale_o / lt : 0.f;
+      bf16* dst = a.out + ((size_t)t * a.Hq + h) * 128;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t o[16];
+        if (n_tiles > 0) { tmem_ld_x16(tmem + lane_addr + O_COL + c * 16, o); tc_wait_ld(); }
+        else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = 0;
+        }
+        if (!live) continue;
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { bf162 hh = __floats2bfloat162_rn(__uint_as_float(o[2 * j]) * inv, __uint_as_float(o[2 * j + 1]) * inv); w[j] = *(uint32_t*)&hh; }
+        *(uint4*)(dst + c * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        *(uint4*)(dst + c * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+    }
+  }
+  if (*abortp && warp == 0) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 200000) __nanosleep(1000); }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+
+extern "C" int cuteafd_gqa_prefill_attention(const void* q, const void* kv_map, const int* page_table, const int* kv_len, const int* q_start,
+                                             const int* q_len, const float* sink, void* out, int T, int n_seq, int max_q_len, int q_stride, int Hq,
+                                             int Hkv, int max_pages, int window, float scale, int* status, cudaStream_t s) {
+  CA_REQUIRE(q && kv_map && page_table && kv_len && q_start && q_len && out, "gqa_prefill_attention: null argument");
+  CA_REQUIRE(Hq % Hkv == 0 && 128 % (Hq / Hkv) == 0 && q_stride % 8 == 0, "gqa_prefill_attention: group size %d unsupported", Hq / Hkv);
+  if (T <= 0 || n_seq <= 0) return CA_OK;
+  GqaPrefillArgs a;
+  a.q = (const bf16*)q; a.kv_map = (const CUtensorMap*)kv_map; a.page_table = page_table; a.kv_len = kv_len; a.q_start = q_start; a.q_len = q_len;
+  a.sink = sink; a.out = (bf16*)out; a.status = status; a.q_stride = q_stride; a.Hq = Hq; a.Hkv = Hkv; a.max_pages = max_pages; a.window = window;
+  a.scale = scale;
+  const int tpt = 128 / (Hq / Hkv);
+  a.max_q_tiles = (max_q_len + tpt - 1) / tpt;
+  const int smem = PF_P_BYTES + PF_NS * GQ_K_STAGE + PF_NSV * PF_V_STAGE + 256;
+  static bool attr_set[64] = {false};
+  int dev = 0; cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gqa_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(gqa_prefill)");
+    attr_set[dev & 63] = true;
+  }
+  CA_LAUNCH_PDL(gqa_prefill_kernel, dim3(Hkv, n_seq * a.max_q_tiles), 192, smem, s, a);
+  CA_CHECK_LAUNCH("gqa_prefill_attention");
+  return CA_OK;
+}
+
 // Gathers the latent rows of every sequence's context out of the paged cache into one contiguous buffer:
 // dst[ctx_start[s] + j] = cache[page_table[s][j / 64] * 64 + j % 64] for j < kv_len[s]; rows of 576 bf16 = 72 x 16 bytes.
 __global__ void mla_gather_ctx_kernel(const uint4* __restrict__ cache, const int* __restrict__ page_table, const int* __restrict__ ctx_start,

@@ -22,10 +22,13 @@ import torch
 from .. import ops
 from ..config import ModelSpec
 from ..models.weights import DeviceWeights, LayerWeights
-from ..ops import ActBuffer, FP4_KINDS, KIND_BF16, KIND_FP8B, pick_tn
+from ..ops import ActBuffer, FP4_KINDS, KIND_BF16, KIND_FP8B, native, pick_tn
+from ..ops.native import ptr
 from ..utils.graph_census import GraphCensus
 
 PAGE = 64
+# query rows per sequence from which a step's GQA attention takes the prefill kernel (128-key tiles); 0 = never
+PREFILL_ATTN_MIN_Q = int(os.environ.get("CUTEAFD_PREFILL_ATTN_MIN_Q", "64"))
 
 
 @dataclass
@@ -279,7 +282,13 @@ class Engine:
         ops.qk_norm_rope_kvwrite(L.qkv, md["positions"], md["slot_map"], lw.q_norm, lw.k_norm, self.kv[li], T,
                                  a.n_heads, a.n_kv_heads, a.head_dim, spec.layer_rope_theta(li), a.rope_interleaved, spec.rms_eps, self.status)
         fused_q = False
-        if self.kv_tmaps is not None:
+        if self.kv_tmaps is not None and sh.attn_splits == 1 and sh.max_q_len >= PREFILL_ATTN_MIN_Q > 0:
+            # prefill chunks: 128-key tiles with the query tile in tensor memory (8 + 8 tcgen05.mma per 128 keys instead of
+            # 2 x (8 + 4) of the 64-key decode kernel)
+            native.call("cuteafd_gqa_prefill_attention", ptr(L.qkv), ptr(self.kv_tmaps[li]), ptr(md["page_table"]), ptr(md["kv_len"]), ptr(md["q_start"]),
+                        ptr(md["q_len"]), ptr(lw.sink), ptr(L.attn), T, sh.n_seq, sh.max_q_len, L.qkv.shape[1], a.n_heads, a.n_kv_heads,
+                        md["page_table"].shape[1], window, a.head_dim ** -0.5, ptr(self.status), native.stream())
+        elif self.kv_tmaps is not None:
             fused_q = ops.paged_attention_tc(L.qkv, self.kv_tmaps[li], md["page_table"], md["kv_len"], md["q_start"], md["q_len"], L.attn,
                                              T=T, n_seq=sh.n_seq, max_q_len=sh.max_q_len, q_stride=L.qkv.shape[1], Hq=a.n_heads,
                                              Hkv=a.n_kv_heads, n_splits=sh.attn_splits, part_o=self.part_o, part_ml=self.part_ml,

@@ -52,11 +52,14 @@ _PROTOS = {
     "cuteafd_tmap_encode_kv": [P, P, I, U64],
     "cuteafd_mla_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P],
     "cuteafd_tmap_encode_latent": [P, P, U64],
+    "cuteafd_gated_delta_step": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
+    "cuteafd_short_conv4": [P, P, P, P, P, P, P, I, I, I, P, P],
     "cuteafd_dsa_index_scores": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "cuteafd_tmap_encode_index_keys": [P, P, U64],
     "cuteafd_dsa_topk": [P, I, P, I, I, I, P, P, P],
     "cuteafd_dsa_gather_rows": [P, P, P, P, P, P, I, I, I, I, L, I, P, P],
     "cuteafd_dsa_scatter_rows": [P, P, P, I, L, I, P, P],
+    "cuteafd_gqa_prefill_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P],
     "cuteafd_mla_gather_ctx": [P, P, P, P, P, I, I, I, L, L, P, P],
     "cuteafd_mla_prefill_attention": [P, P, P, P, L, P, P, P, P, P, I, I, I, I, F, P, P],
     "cuteafd_mla_kv_prepare": [P, P, P, P, P, I, I, F, F, I, P, P],

@@ -185,3 +185,32 @@ def greedy_verify(inputs: list[int], target_next: list[int], eos: int | None, re
         if not matched or hit_eos or hit_len:
             break
     return accepted, emitted, hit_eos, hit_len
+
+
+def gated_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                     state: torch.Tensor | None = None):
+    """Recurrent gated delta rule of the GDN / KDA linear-attention layers, one sequence: q, k [T, H, dk], v [T, H, dv],
+    g [T, H] (one decay per head) or [T, H, dk] (per key channel), beta [T, H]; state [H, dk, dv] or None (zeros).
+    Returns (o [T, H, dv] fp32, final state, list of the states after every token)."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    S = torch.zeros(H, dk, dv) if state is None else state.float().clone()
+    out, snaps = [], []
+    for t in range(T):
+        gt = g[t].float()
+        S = S * (gt[:, :, None] if gt.dim() == 2 else gt[:, None, None])
+        u = torch.einsum("hkv,hk->hv", S, k[t].float())
+        d = beta[t].float()[:, None] * (v[t].float() - u)
+        S = S + k[t].float()[:, :, None] * d[:, None, :]
+        out.append(torch.einsum("hkv,hk->hv", S, q[t].float()))
+        snaps.append(S.clone())
+    return torch.stack(out), S, snaps
+
+
+def short_conv4(x: torch.Tensor, w: torch.Tensor, carry: torch.Tensor | None = None):
+    """Causal depthwise convolution of width 4 + SiLU over one sequence: x [T, C], w [C, 4], carry [3, C] (the three inputs before
+    x, zeros when None).  Returns (y [T, C] fp32, new carry [3, C])."""
+    T, C = x.shape
+    hist = torch.cat([torch.zeros(3, C) if carry is None else carry.float(), x.float()])
+    y = sum(hist[i:i + T] * w[:, i].float()[None, :] for i in range(4))
+    return F.silu(y), hist[-3:]

@@ -460,6 +460,51 @@ def test_paged_attention_tc(Hq, Hkv, window, use_sink, splits):
             assert torch.equal(fused.data, sep.data) and torch.equal(fused.sf[:, :nsf], sep.sf[:, :nsf])
 
 
+@pytest.mark.parametrize("Hq,Hkv,window,use_sink", [(16, 1, 0, False), (64, 4, 0, False), (8, 8, 0, True), (32, 2, 100, True)])
+def test_gqa_prefill_attention(Hq, Hkv, window, use_sink):
+    """The 128-key-tile prefill kernel against the fp32 oracle: a chunk over a cached prefix, a ragged query tile and ragged last
+    key tiles, a sequence that is all chunk, with sliding window and sink variants."""
+    from cuteafd_b200.ops.native import call, ptr, stream
+    D = 128
+    g = torch.Generator().manual_seed(Hq * 5 + window)
+    lens, qlens = [500, 129, 200, 64], [200, 129, 7, 64]
+    n_pages = 24
+    cache = torch.zeros(1, n_pages * 64, 2, Hkv, D)
+    perm = torch.randperm(n_pages - 1, generator=g) + 1
+    tables, p, ks, vs = [], 0, [], []
+    for L in lens:
+        npg = -(-L // 64)
+        pages = perm[p:p + npg].tolist()
+        p += npg
+        tables.append(pages)
+        k, v = torch.randn(L, Hkv, D, generator=g), torch.randn(L, Hkv, D, generator=g)
+        ks.append(k), vs.append(v)
+        slots = torch.tensor([pages[t // 64] * 64 + t % 64 for t in range(L)])
+        cache[0, slots, 0], cache[0, slots, 1] = k, v
+    T = sum(qlens)
+    q = torch.randn(T, Hq, D, generator=g)
+    sink = torch.randn(Hq, generator=g) if use_sink else None
+    pt = torch.zeros(len(lens), 8, dtype=torch.int32)
+    for i, row in enumerate(tables):
+        pt[i, :len(row)] = torch.tensor(row)
+    q_start = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)[:-1]), dtype=torch.int32)
+    kv_dev = cache.to(torch.bfloat16).to(DEV).contiguous()
+    maps = ops.encode_kv_tmaps(kv_dev)
+    out = torch.zeros(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+    st = status_word()
+    qd, ptd, sinkd = q.to(torch.bfloat16).to(DEV).view(T, -1).contiguous(), pt.to(DEV), sink.to(DEV) if use_sink else None
+    kvl, qsd, qld = torch.tensor(lens, dtype=torch.int32, device=DEV), q_start.to(DEV), torch.tensor(qlens, dtype=torch.int32, device=DEV)
+    call("cuteafd_gqa_prefill_attention", ptr(qd), ptr(maps[0]), ptr(ptd), ptr(kvl), ptr(qsd), ptr(qld), ptr(sinkd), ptr(out), T, len(lens), max(qlens),
+         Hq * D, Hq, Hkv, 8, window, D ** -0.5, ptr(st), stream())
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    got = out.float().cpu().view(T, Hq, D)
+    for i, (L, ql) in enumerate(zip(lens, qlens)):
+        qs = int(q_start[i])
+        ref = rops.attention(bf16r(q[qs:qs + ql]), bf16r(ks[i]), bf16r(vs[i]), torch.arange(L - ql, L), torch.arange(L), window=window, sink=sink)
+        assert torch.allclose(got[qs:qs + ql], ref, atol=3e-2, rtol=3e-2), f"seq {i}: max err {(got[qs:qs + ql] - ref).abs().max()}"
+
+
 # ------------------------------------------------------------------ bounded flag waits (failure detection without a fault)
 def test_flag_wait_runs_out_and_reports_status():
     from cuteafd_b200.parallel import peer_ops
