@@ -573,3 +573,27 @@ def sample_rows(logits, params_dev, tok, status, *, masks=None):
 def verify_accept(inputs, target, n_drafts, accepted, n_emit, eos: int = -1):
     n_seq, width = inputs.shape
     call("cuteafd_verify_accept", ptr(inputs), ptr(target), ptr(n_drafts), ptr(accepted), ptr(n_emit), n_seq, width, eos, stream())
+
+
+# ------------------------------------------------------------------ linear attention (GDN / KDA recurrent layers)
+def gated_delta_step(q, k, v, g, beta, state, slot_of_seq, q_start, q_len, out, *, snapshots=None, status=None):
+    """Gated delta rule over runs of tokens: q, k, v, out bf16 [T, H, 128]; g fp32 [T, H] (decay per head) or [T, H, 128] (per key
+    channel); beta fp32 [T, H]; state fp32 [slots, H, 128, 128] updated in place for the slots named by `slot_of_seq`; run s covers
+    rows [q_start[s], q_start[s] + q_len[s]).  `snapshots` (fp32 [T, H, 128, 128]) receives the state after every token."""
+    _chk(q, torch.bfloat16, "q"); _chk(k, torch.bfloat16, "k"); _chk(v, torch.bfloat16, "v"); _chk(out, torch.bfloat16, "out")
+    _chk(g, torch.float32, "g"); _chk(beta, torch.float32, "beta"); _chk(state, torch.float32, "state")
+    T, H, D = q.shape
+    if D != 128 or v.shape[-1] != 128 or state.shape[1:] != (H, 128, 128):
+        raise ValueError("gated_delta_step: heads are 128 x 128")
+    call("cuteafd_gated_delta_step", ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(state), ptr(slot_of_seq), ptr(q_start), ptr(q_len), ptr(out),
+         ptr(snapshots), slot_of_seq.numel(), H, 1 if g.dim() == 3 else 0, state.shape[0], ptr(status), stream())
+    return out
+
+
+def short_conv4(x, w, carry, slot_of_seq, q_start, q_len, y, *, status=None):
+    """Causal depthwise convolution of width 4 + SiLU: x, y bf16 [T, C]; w fp32 [C, 4]; carry bf16 [slots, 3, C] (the last three
+    inputs of every sequence, updated in place)."""
+    _chk(x, torch.bfloat16, "x"); _chk(y, torch.bfloat16, "y"); _chk(w, torch.float32, "w"); _chk(carry, torch.bfloat16, "carry")
+    call("cuteafd_short_conv4", ptr(x), ptr(w), ptr(carry), ptr(slot_of_seq), ptr(q_start), ptr(q_len), ptr(y), slot_of_seq.numel(), x.shape[1],
+         carry.shape[0], ptr(status), stream())
+    return y

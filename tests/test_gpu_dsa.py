@@ -77,7 +77,8 @@ def test_index_scores_topk_and_gather():
     lat_d = d(lat)
     kp = 64
     dst = torch.zeros(T * kp, 576, dtype=torch.bfloat16, device=DEV)
-    call("cuteafd_dsa_gather_rows", ptr(lat_d), ptr(table_d), ptr(d(torch.tensor(seq_of_row, dtype=torch.int32))), ptr(sel), ptr(cnt), ptr(dst), T, k, kp,
+    sor_d = d(torch.tensor(seq_of_row, dtype=torch.int32))
+    call("cuteafd_dsa_gather_rows", ptr(lat_d), ptr(table_d), ptr(sor_d), ptr(sel), ptr(cnt), ptr(dst), T, k, kp,
          max_pages, n_pages * 64, 1152, ptr(status), stream())
     torch.cuda.synchronize()
     assert status.tolist() == [0, 0, 0, 0]

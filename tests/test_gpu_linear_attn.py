@@ -34,7 +34,8 @@ def test_gated_delta_rule_matches_reference(per_channel):
     starts = [0, lens[0], lens[0] + lens[1]]
     i32 = lambda v_: torch.tensor(v_, dtype=torch.int32, device=DEV)
     d_slots, d_starts, d_lens = i32(slots), i32(starts), i32(lens)
-    call("cuteafd_gated_delta_step", ptr(qd), ptr(kd), ptr(vd), ptr(d(gate)), ptr(d(beta)), ptr(state), ptr(d_slots), ptr(d_starts), ptr(d_lens),
+    gd, bd = d(gate), d(beta)
+    call("cuteafd_gated_delta_step", ptr(qd), ptr(kd), ptr(vd), ptr(gd), ptr(bd), ptr(state), ptr(d_slots), ptr(d_starts), ptr(d_lens),
          ptr(out), ptr(snaps), len(lens), H, 1 if per_channel else 0, n_slots, ptr(status), stream())
     torch.cuda.synchronize()
     assert status.tolist() == [0, 0, 0, 0]
