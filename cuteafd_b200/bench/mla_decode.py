@@ -54,7 +54,7 @@ def main():
         gen.decode_step()                                   # fills the step metadata, captures the graph
     torch.cuda.synchronize()
     eng.check_status()
-    sh = StepShape(T=a.batch, n_seq=a.batch, max_q_len=1, n_logits=a.batch, attn_splits=eng.attn_splits_for(a.batch, 1, a.context + 1))
+    sh = StepShape(T=a.batch, n_seq=a.batch, max_q_len=1, n_logits=a.batch, attn_splits=eng.attn_splits_for(a.batch, 1, a.context + 1), uniform=True)
     for _ in range(a.warmup):
         eng.run(sh)
     torch.cuda.synchronize()
