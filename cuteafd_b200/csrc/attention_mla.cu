@@ -844,3 +844,33 @@ extern "C" int cuteafd_head_to_token_major(const void* in, void* out, int T, int
   CA_CHECK_LAUNCH("head_to_token_major");
   return CA_OK;
 }
+
+// The same transpose writing the token-major row ALSO as the FP8 operand of the output projection (E4M3 + one fp32 scale per
+// 128 channels = one head's 128 values): one warp per (token, head), 4 elements per lane as in the stand-alone quantiser.
+__global__ void head_to_token_major_fp8b_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, uint8_t* __restrict__ q, float* __restrict__ sa,
+                                                int T, int Hl) {
+  pdl_launch(); pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+  const uint2 raw = *(const uint2*)(in + ((size_t)h * T + t) * 128 + lane * 4);
+  if (out) *(uint2*)(out + ((size_t)t * Hl + h) * 128 + lane * 4) = raw;
+  const bf16* e = (const bf16*)&raw;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(e[j]);
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-4f) / 448.f;
+  uint32_t pk = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) pk |= (uint32_t)float_to_e4m3(v[j] / scale) << (8 * j);
+  *(uint32_t*)(q + ((size_t)t * Hl + h) * 128 + lane * 4) = pk;
+  if (lane == 0) sa[(size_t)t * Hl + h] = scale;
+}
+
+extern "C" int cuteafd_head_to_token_major_fp8b(const void* in, void* out, void* q, float* sa, int T, int Hl, int D, cudaStream_t s) {
+  CA_REQUIRE(in && q && sa && D == 128, "head_to_token_major_fp8b: heads of 128 values");
+  if (T <= 0) return CA_OK;
+  CA_LAUNCH_PDL(head_to_token_major_fp8b_kernel, dim3(T, Hl), 32, 0, s, (const bf16*)in, (bf16*)out, (uint8_t*)q, sa, T, Hl);
+  CA_CHECK_LAUNCH("head_to_token_major_fp8b");
+  return CA_OK;
+}

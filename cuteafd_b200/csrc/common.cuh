@@ -174,6 +174,23 @@ __device__ __forceinline__ void quant8_store(const float* v, int qkind, float in
   }
 }
 
+// FP8 activation rows for the 128 x 128 block-scaled GEMM (qkind 3): this thread holds 8 consecutive elements starting at
+// column i, 16 consecutive lanes hold one 128-channel block; E4M3 bytes go to q_row[i .. i + 8), the block's fp32 scale
+// (amax floored at 1e-4, / 448: the stand-alone quantiser's arithmetic) to sa_row[i / 128].  All 32 lanes must call it.
+__device__ __forceinline__ void quant8_store_fp8b(const float* v, uint8_t* q_row, float* sa_row, int i) {
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1)); amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4)); amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+  const float scale = fmaxf(amax, 1e-4f) / 448.f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { lo |= (uint32_t)float_to_e4m3(v[j] / scale) << (8 * j); hi |= (uint32_t)float_to_e4m3(v[4 + j] / scale) << (8 * j); }
+  *(uint2*)(q_row + i) = make_uint2(lo, hi);
+  if (((i >> 3) & 15) == 0) sa_row[i >> 7] = scale;
+}
+
 // ------------------------------------------------------------------ PTX: smem / mbarrier
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -75,7 +75,8 @@ __global__ void add_rmsnorm_kernel(bf16* __restrict__ x, const bf16* __restrict_
         float f[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(o[j]);
-        quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)blockIdx.x * (H / 2), sf + (size_t)blockIdx.x * ldsf, i);
+        if (qkind == 3) quant8_store_fp8b(f, q + (size_t)blockIdx.x * H, (float*)sf + (size_t)blockIdx.x * ldsf, i);
+        else quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)blockIdx.x * (H / 2), sf + (size_t)blockIdx.x * ldsf, i);
       }
     }
   }
@@ -88,10 +89,11 @@ extern "C" int cuteafd_add_rmsnorm(void* x, const void* delta, const float* w, v
   return add_rmsnorm_launch(x, delta, w, y, T, H, eps, nullptr, nullptr, 0, nullptr, 0, s);
 }
 
-// add_rmsnorm that also (or only, y == null) writes the row quantised to FP4: qkind 1 = NVFP4, 2 = MXFP4.
+// add_rmsnorm that also (or only, y == null) writes the row quantised: qkind 1 = NVFP4, 2 = MXFP4, 3 = FP8 E4M3 with one fp32
+// scale per 128 channels (sf then points at floats, ldsf counts floats).
 extern "C" int cuteafd_add_rmsnorm_quant(void* x, const void* delta, const float* w, void* y, int T, int H, float eps, void* q, void* sf,
                                          int ldsf, const float* inv_gs, int qkind, cudaStream_t s) {
-  CA_REQUIRE((qkind == 1 || qkind == 2) && q && sf && H % 256 == 0, "add_rmsnorm_quant: needs FP4 outputs and hidden %% 256 == 0");
+  CA_REQUIRE(qkind >= 1 && qkind <= 3 && q && sf && H % 256 == 0, "add_rmsnorm_quant: needs quantised outputs and hidden %% 256 == 0");
   return add_rmsnorm_launch(x, delta, w, y, T, H, eps, q, sf, ldsf, inv_gs, qkind, s);
 }
 
@@ -325,5 +327,35 @@ extern "C" int cuteafd_silu_mul(const void* g, const void* u, void* o, long long
   if (n <= 0) return CA_OK;
   silu_mul_kernel<<<(int)((n / 2 + 255) / 256), 256, 0, s>>>((const bf16*)g, (const bf16*)u, (bf16*)o, n, limit);
   CA_CHECK_LAUNCH("silu_mul");
+  return CA_OK;
+}
+
+// silu(gate) * up written as the FP8 operand of the GEMM that follows (E4M3 + one fp32 scale per 128 channels), with the same
+// bf16 rounding of the product as the two-kernel form (silu_mul, then the quantiser).  g, u: [rows, N] bf16 (row pitch ld);
+// q: [rows, N] bytes; sa: [rows, N / 128].  One warp per 256 channels of a row; N % 256 == 0.
+__global__ void silu_mul_quant_fp8b_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u, uint8_t* __restrict__ q, float* __restrict__ sa,
+                                           int rows, int N, int ld) {
+  pdl_launch(); pdl_wait();
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31, per_row = N / 256;
+  if (w >= (long long)rows * per_row) return;
+  const int r = (int)(w / per_row), i = (int)(w % per_row) * 256 + lane * 8;
+  const uint4 gq = *(const uint4*)(g + (size_t)r * ld + i), uq = *(const uint4*)(u + (size_t)r * ld + i);
+  const bf16* ge = (const bf16*)&gq; const bf16* ue = (const bf16*)&uq;
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float a = __bfloat162float(ge[j]), b = __bfloat162float(ue[j]);
+    f[j] = __bfloat162float(__float2bfloat16(a / (1.f + __expf(-a)) * b));
+  }
+  quant8_store_fp8b(f, q + (size_t)r * N, sa + (size_t)r * (N / 128), i);
+}
+
+extern "C" int cuteafd_silu_mul_quant_fp8b(const void* g, const void* u, void* q, float* sa, int rows, int N, int ld, cudaStream_t s) {
+  CA_REQUIRE(g && u && q && sa && N % 256 == 0 && ld % 8 == 0, "silu_mul_quant_fp8b: N must be a multiple of 256");
+  if (rows <= 0) return CA_OK;
+  const long long warps = (long long)rows * (N / 256);
+  CA_LAUNCH_PDL(silu_mul_quant_fp8b_kernel, (int)((warps * 32 + 255) / 256), 256, 0, s, (const bf16*)g, (const bf16*)u, (uint8_t*)q, sa, rows, N, ld);
+  CA_CHECK_LAUNCH("silu_mul_quant_fp8b");
   return CA_OK;
 }

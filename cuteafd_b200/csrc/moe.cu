@@ -445,7 +445,8 @@ __global__ void moe_combine_norm_kernel(const bf16* __restrict__ y, const int* _
         float f[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(o[j]);
-        quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)t * (H / 2), sf + (size_t)t * ldsf, i);
+        if (qkind == 3) quant8_store_fp8b(f, q + (size_t)t * H, (float*)sf + (size_t)t * ldsf, i);
+        else quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)t * (H / 2), sf + (size_t)t * ldsf, i);
       }
     }
   }
@@ -456,7 +457,7 @@ extern "C" int cuteafd_moe_combine_norm(const void* y, const int* slot_row, cons
                                         int ldsf, const float* inv_gs, int qkind, const CaFlagWaitArg* wait, cudaStream_t s) {
   const FlagWait fw = ca_flag_wait_from(wait);
   CA_REQUIRE(H % 8 == 0 && H <= 32768 && norm_w, "moe_combine_norm: bad arguments");
-  CA_REQUIRE(qkind == 0 || ((qkind == 1 || qkind == 2) && q && sf && H % 256 == 0), "moe_combine_norm: FP4 output needs buffers and hidden %% 256 == 0");
+  CA_REQUIRE(qkind == 0 || (qkind >= 1 && qkind <= 3 && q && sf && H % 256 == 0), "moe_combine_norm: quantised output needs buffers and hidden %% 256 == 0");
   if (T <= 0) return CA_OK;
   const int vecs = H / 8;
   int threads = vecs >= 1024 ? 1024 : ((vecs + 31) / 32) * 32;

@@ -22,7 +22,7 @@ import torch
 from .. import ops
 from ..config import ModelSpec
 from ..models.weights import DeviceWeights, LayerWeights
-from ..ops import ActBuffer, FP4_KINDS, KIND_BF16, KIND_FP8B, native, pick_tn
+from ..ops import ActBuffer, FP4_KINDS, FUSED_QUANT_KINDS, KIND_BF16, KIND_FP8B, native, pick_tn
 from ..ops.native import ptr
 from ..utils.graph_census import GraphCensus
 
@@ -251,7 +251,7 @@ class Engine:
         if self._pre_normed:
             self._pre_normed = False
             return L.xq
-        if L.xq.kind in FP4_KINDS:
+        if L.xq.kind in FUSED_QUANT_KINDS and self.spec.hidden % 256 == 0:
             ops.add_rmsnorm(L.x, None, lw.attn_norm, None, self.spec.rms_eps, rows=T, quant=L.xq, inv_gs=self._attn_in_gs(lw))
         else:
             ops.add_rmsnorm(L.x, None, lw.attn_norm, L.xn, self.spec.rms_eps, rows=T)
@@ -266,7 +266,7 @@ class Engine:
         if nxt is None:
             ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, wait=wait)
             return
-        fp4 = L.xq.kind in FP4_KINDS
+        fp4 = L.xq.kind in FUSED_QUANT_KINDS and self.spec.hidden % 256 == 0      # the quantised operand rides in the same launch
         ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, norm_w=nxt.attn_norm, eps=self.spec.rms_eps, xn=None if fp4 else L.xn,
                         quant=L.xq if fp4 else None, inv_gs=self._attn_in_gs(nxt) if fp4 else None, wait=wait)
         if not fp4:
@@ -302,6 +302,16 @@ class Engine:
         self._attn_out(li, lw, oq, L, T)
         self.launches_per_step += 2 + (1 if sh.attn_splits > 1 else 0)
 
+    _ffn_in_quantised = False
+
+    def _ffn_norm(self, lw: LayerWeights, L: Lane, T: int):
+        """RMSNorm in front of the FFN block -> L.xn (router, dispatch and gather read bf16 rows); when a dense or shared expert
+        with FP8 operands follows, its quantised input is written by the same launch."""
+        fuse = L.xq.kind == KIND_FP8B and self.spec.hidden % 256 == 0 and lw.ws_gate is not None and lw.ws_gate.kind == KIND_FP8B
+        ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, self.spec.rms_eps, rows=T, quant=L.xq if fuse else None)
+        self._ffn_in_quantised = fuse
+        self.launches_per_step += 1
+
     def _attn_out(self, li: int, lw: LayerWeights, oq: ActBuffer, L: Lane, T: int):
         """Output projection + residual (a tensor-parallel rank overrides this with partial sum + exchange)."""
         self._dense(lw.wo, oq, L.x, T, residual=L.x)
@@ -309,7 +319,10 @@ class Engine:
     def _ffn(self, lw: LayerWeights, L: Lane, T: int, out, residual):
         """Shared expert / dense FFN: out = residual + down(silu(gate x) * up x)."""
         s1, s_act = L.ffn_buf(self, lw.ws_gate.N)
-        xq = self._quant(L.xn, L.xq, T, lw.ws_gate.inv_act_gs)
+        if self._ffn_in_quantised:                 # the FFN norm already wrote the FP8 operand (same launch)
+            xq, self._ffn_in_quantised = L.xq, False
+        else:
+            xq = self._quant(L.xn, L.xq, T, lw.ws_gate.inv_act_gs)
         if lw.ws_gate.kind == KIND_FP8B:      # no fused SwiGLU epilogue in the FP8 kernel: two GEMMs + silu(g) * u
             key = ("up", lw.ws_gate.N)
             if key not in L.ffn_bufs:
@@ -317,17 +330,20 @@ class Engine:
             s_up = L.ffn_bufs[key]
             self._dense(lw.ws_gate, xq, s1, T)
             self._dense(lw.ws_up, xq, s_up, T)
-            ops.silu_mul(s1[:T], s_up[:T], s1[:T])
             self.launches_per_step += 1
+            if s_act.kind == KIND_FP8B and s1.shape[1] % 256 == 0:       # silu(g) * u straight into the FP8 operand of the down projection
+                native.call("cuteafd_silu_mul_quant_fp8b", ptr(s1), ptr(s_up), ptr(s_act.data), ptr(s_act.sf), T, s1.shape[1], s1.stride(0), native.stream())
+            else:
+                ops.silu_mul(s1[:T], s_up[:T], s1[:T])
+                self._quant(s1, s_act, T, lw.ws_down.inv_act_gs)
         else:
             self._dense(lw.ws_gate, xq, s1, T, w_up=lw.ws_up)
-        self._quant(s1, s_act, T, lw.ws_down.inv_act_gs)
+            self._quant(s1, s_act, T, lw.ws_down.inv_act_gs)
         self._dense(lw.ws_down, s_act, out, T, residual=residual)
 
     def _moe_layer(self, lw: LayerWeights, L: Lane, T: int):
         spec, m = self.spec, self.spec.moe
-        ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, spec.rms_eps, rows=T)
-        self.launches_per_step += 1
+        self._ffn_norm(lw, L, T)
         if lw.router is None:
             self._ffn(lw, L, T, L.x, L.x)
             return

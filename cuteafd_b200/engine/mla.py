@@ -221,8 +221,12 @@ class MlaEngine(Engine):
         qa = None
         if w.wq_a is not None:
             self._dense(w.wq_a, xq, b["q_a"], T)
-            ops.add_rmsnorm(b["q_a"], None, w.q_a_norm, b["q_an"], spec.rms_eps, rows=T)
-            qa = self._quant(b["q_an"], b["q_an_act"], T, w.wq_b.inv_act_gs)
+            if b["q_an_act"].kind in ops.FUSED_QUANT_KINDS and a.q_lora_rank % 256 == 0:      # norm + operand quantisation in one launch
+                ops.add_rmsnorm(b["q_a"], None, w.q_a_norm, None, spec.rms_eps, rows=T, quant=b["q_an_act"], inv_gs=w.wq_b.inv_act_gs)
+                qa = b["q_an_act"]
+            else:
+                ops.add_rmsnorm(b["q_a"], None, w.q_a_norm, b["q_an"], spec.rms_eps, rows=T)
+                qa = self._quant(b["q_an"], b["q_an_act"], T, w.wq_b.inv_act_gs)
             self._dense(w.wq_b, qa, b["q"], T)
         else:
             self._dense(w.wq_b, xq, b["q"], T)
@@ -250,8 +254,7 @@ class MlaEngine(Engine):
             o_head = b["o_head"][:Hl * T]
             ol_act = self._act(b, ("ol", T, tn), o_lat, tn)
             ops.tc_linear(w.w_uv, ol_act, o_head, rows=Hl * T, tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=self.status)
-            call("cuteafd_head_to_token_major", ptr(o_head), ptr(b["o_tok"]), T, Hl, a.v_head_dim, stream())
-            oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
+            oq = self._o_tok(b, o_head, T, lw)
             self._attn_out(li, lw, oq, L, T)
             self.launches_per_step += 10
             return
@@ -279,10 +282,19 @@ class MlaEngine(Engine):
         o_head = b["o_head"][:Hl * T]
         ol_act = self._act(b, ("ol", T, tn), o_lat, tn)
         ops.tc_linear(w.w_uv, ol_act, o_head, rows=Hl * T, tiles=tiles, n_tiles=n_tiles, max_tiles=max_tiles, status=self.status)
-        call("cuteafd_head_to_token_major", ptr(o_head), ptr(b["o_tok"]), T, Hl, a.v_head_dim, stream())
-        oq = self._quant(b["o_tok"], b["o_tok_act"], T, lw.wo.inv_act_gs)
+        oq = self._o_tok(b, o_head, T, lw)
         self._attn_out(li, lw, oq, L, T)
         self.launches_per_step += 7
+
+    def _o_tok(self, b: dict, o_head: torch.Tensor, T: int, lw: LayerWeights) -> ActBuffer:
+        """Per-head attention outputs [Hl, T, 128] -> the output projection's operand (token-major; FP8 operands are written by the
+        same launch as the transpose)."""
+        a, Hl, act = self.spec.attn, self.heads_local, b["o_tok_act"]
+        if act.kind == ops.KIND_FP8B and a.v_head_dim == 128:
+            call("cuteafd_head_to_token_major_fp8b", ptr(o_head), None, ptr(act.data), ptr(act.sf), T, Hl, 128, stream())
+            return act
+        call("cuteafd_head_to_token_major", ptr(o_head), ptr(b["o_tok"]), T, Hl, a.v_head_dim, stream())
+        return self._quant(b["o_tok"], act, T, lw.wo.inv_act_gs)
 
     # ------------------------------------------------------------------ sparse attention over the indexer's selection
     SPARSE_MAX_Q = 8          # decode and verify steps (at most this many query rows per sequence) always take the sparse path

@@ -16,12 +16,17 @@ from .native import call, ptr, stream
 
 KIND_BF16, KIND_NVFP4, KIND_MXFP4, KIND_FP8B = 0, 1, 2, 3      # FP8B: E4M3 with fp32 scales per 128 x 128 (weights) / 1 x 128 (activations)
 KIND_W4A8 = 4      # MXFP4 weights x FP8 E4M3 activations, UE8M0 scales per 32 on both (tcgen05 kind::mxf8f6f4)
-# MXFP4 checkpoints run W4A8 (the reference's default expert arithmetic) unless CUTEAFD_MXFP4_ACT=fp4 asks for FP4 activations
+# MXFP4 expert weights run with MXFP4 activations (W4A4) unless CUTEAFD_MXFP4_ACT=fp8 selects FP8 activations (W4A8, the
+# reference's default expert arithmetic; also reachable per model as the "mxfp4_w4a8" format name)
 import os as _os
 MXFP4_ACT = _os.environ.get("CUTEAFD_MXFP4_ACT", "fp4")
 KIND_BY_NAME = {"bf16": KIND_BF16, "nvfp4": KIND_NVFP4, "mxfp4": KIND_W4A8 if MXFP4_ACT == "fp8" else KIND_MXFP4, "mxfp4_w4a4": KIND_MXFP4,
                 "mxfp4_w4a8": KIND_W4A8, "fp8_block128": KIND_FP8B}
 FP4_KINDS = (KIND_NVFP4, KIND_MXFP4)
+# activation formats the norm kernels (add_rmsnorm, moe_combine with the next layer's norm) can write in the same launch, and the
+# code the native side knows them by
+FUSED_QUANT_KINDS = (KIND_NVFP4, KIND_MXFP4, KIND_FP8B)
+_QKIND = {KIND_NVFP4: 1, KIND_MXFP4: 2, KIND_FP8B: 3}
 EPI_BF16, EPI_BF16_RESIDUAL, EPI_F32 = 0, 1, 3
 SCORING = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}
 
@@ -346,9 +351,9 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, y:
     rows are also written quantised in the same launch (y may then be None)."""
     _chk(x, torch.bfloat16, "x"); _chk(w, torch.float32, "w")
     n = x.shape[0] if rows is None else rows
-    if quant is not None and quant.kind in FP4_KINDS:
+    if quant is not None and quant.kind in FUSED_QUANT_KINDS:
         call("cuteafd_add_rmsnorm_quant", ptr(x), ptr(delta), ptr(w), ptr(y), n, x.shape[1], eps, ptr(quant.data), ptr(quant.sf),
-             quant.sf.shape[1], ptr(inv_gs), 2 if quant.kind == KIND_MXFP4 else 1, stream())
+             quant.sf.shape[1], ptr(inv_gs), _QKIND[quant.kind], stream())
     else:
         call("cuteafd_add_rmsnorm", ptr(x), ptr(delta), ptr(w), ptr(y), n, x.shape[1], eps, stream())
     return y
@@ -472,10 +477,10 @@ def moe_combine(y, slot_row, wts, shared, residual, out, T, k, *, norm_w=None, e
     if norm_w is None:
         call("cuteafd_moe_combine", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, w, stream())
         return out
-    fp4 = quant is not None and quant.kind in FP4_KINDS
+    fp4 = quant is not None and quant.kind in FUSED_QUANT_KINDS
     call("cuteafd_moe_combine_norm", ptr(y), ptr(slot_row), ptr(wts), ptr(shared), ptr(residual), ptr(out), T, y.shape[1], k, ptr(norm_w),
          eps, ptr(xn), ptr(quant.data) if fp4 else None, ptr(quant.sf) if fp4 else None, quant.sf.shape[1] if fp4 else 0,
-         ptr(inv_gs) if fp4 else None, (2 if quant.kind == KIND_MXFP4 else 1) if fp4 else 0, w, stream())
+         ptr(inv_gs) if fp4 else None, _QKIND[quant.kind] if fp4 else 0, w, stream())
     return out
 
 

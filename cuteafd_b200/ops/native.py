@@ -65,6 +65,8 @@ _PROTOS = {
     "cuteafd_mla_kv_prepare": [P, P, P, P, P, I, I, F, F, I, P, P],
     "cuteafd_mla_q_split": [P, P, P, P, I, I, F, I, P],
     "cuteafd_head_to_token_major": [P, P, I, I, I, P],
+    "cuteafd_head_to_token_major_fp8b": [P, P, P, P, I, I, I, P],
+    "cuteafd_silu_mul_quant_fp8b": [P, P, P, P, I, I, I, P],
     "cuteafd_argmax_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_sample_rows": [P, I, I, I, P, I, P, P, P, P],
     "cuteafd_verify_accept": [P, P, P, P, P, I, I, I, P],

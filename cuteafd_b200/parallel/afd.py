@@ -405,7 +405,8 @@ class AttnRankEngine(Engine):
             return
         if T:
             self._routing_bufs(L)
-            ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, spec.rms_eps, rows=T)
+            self._ffn_norm(lw, L, T)
+            self.launches_per_step -= 1
             if T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K \
                     and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1":
                 ops.router_logits(L.xn, lw.router, L.r_logits, T)      # same kernel as the single-GPU engine (token-exact layouts)
