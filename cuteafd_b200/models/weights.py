@@ -16,8 +16,6 @@ nvfp4_scale.cu:22 do the equivalent one-time device-side preparation).
 """
 from __future__ import annotations
 
-import os
-
 from dataclasses import dataclass, field
 
 import torch
@@ -27,13 +25,7 @@ from ..ops import TcWeight, KIND_BF16, KIND_BY_NAME
 
 
 def _dense_kind(spec: ModelSpec) -> str:
-    """Storage / execution format of the dense (attention, shared-expert, dense-FFN) projections.  CUTEAFD_FP8_DENSE_EXEC=bf16 keeps
-    FP8 128 x 128 checkpoints' dense weights dequantised in bf16 (twice the bytes, no activation quantisation, the bf16 GEMM
-    kernel): an execution option for small decode batches, where the FP8 kernel's per-K-block rescaling chain is the bound."""
-    kind = {"bf16": "bf16", "nvfp4": "nvfp4", "mxfp4": "mxfp4", "fp8_block128": "fp8_block128"}.get(spec.quant.dense, "bf16")
-    if kind == "fp8_block128" and os.environ.get("CUTEAFD_FP8_DENSE_EXEC", "fp8") == "bf16":
-        return "bf16"
-    return kind
+    return {"bf16": "bf16", "nvfp4": "nvfp4", "mxfp4": "mxfp4", "fp8_block128": "fp8_block128"}.get(spec.quant.dense, "bf16")
 
 
 def _expert_kind(spec: ModelSpec) -> str:

@@ -548,11 +548,12 @@ class MlaAttnRankEngine(AttnRankEngine):
 
 
 def _bind_mla(cls):
-    """MLA attention methods come from MlaEngine; everything else (TP exchange, remote experts) from AttnRankEngine."""
+    """MLA attention comes from MlaEngine - every method and class constant it defines (attention layer, its prefill and sparse
+    paths, buffers, cache state) - everything else (TP exchange, remote experts) from AttnRankEngine."""
     from ..engine.mla import MlaEngine
-    for name in ("_alloc_attention_state", "_mla_buf", "_head_tiles", "attn_splits_for", "_attention_layer", "_act", "_attn_in_gs",
-                 "_use_prefill_path", "_prefill_attention", "PREFILL_MIN_Q", "PREFILL_MAX_BYTES"):
-        setattr(cls, name, getattr(MlaEngine, name))
+    for name, value in vars(MlaEngine).items():
+        if not name.startswith("__"):
+            setattr(cls, name, value)
     return cls
 
 
