@@ -209,9 +209,40 @@ def cmd_usage(a) -> int:
     return 0
 
 
+def _golden_masters(model: str):
+    """(spec, fp32 masters) of a model the CPU oracle can evaluate: the tiny model or a snapshot directory."""
+    import os
+    from .config import spec_from_snapshot, tiny_spec
+    from .ref.model import init_weights
+    if model == "tiny":
+        spec = tiny_spec()
+        return spec, init_weights(spec, 0)
+    if not os.path.isdir(model):
+        raise SystemExit(f"golden windows need fp32 masters: give the tiny model or a snapshot directory, not {model!r}")
+    from .loader.checkpoint import read_masters
+    spec = spec_from_snapshot(model)
+    return spec, read_masters(model, spec)
+
+
 def cmd_golden(a) -> int:
-    """Teacher-forced comparison of the GPU engine against the CPU oracle on the tiny model (per-prompt logits error)."""
+    """`golden --write FILE [--model M]`: seal golden windows from the fp32 oracle.  `golden --check FILE [--model M]`: check the GPU
+    engine's logits against a golden file.  Without either: teacher-forced comparison of the tiny model against the oracle."""
     import torch
+    if getattr(a, "write", None):
+        from .bench.golden import write_golden
+        spec, masters = _golden_masters(a.model)
+        gold = write_golden(a.write, spec, masters, n=a.windows, length=a.window_tokens, seed=a.seed or 2026)
+        print(json.dumps({"wrote": a.write, "model": gold["model"], "digest": gold["digest"], "windows": len(gold["windows"])}))
+        return 0
+    if getattr(a, "check", None):
+        from .bench.golden import check_logits, engine_logits_fn, read_golden
+        import argparse
+        ns = argparse.Namespace(model=a.model, device=0, max_context=4096, max_sequences=4, pool_tokens=0, prefill_batch_tokens=4096, decode_share=0.2,
+                                prefix_cache_entries=4, prefix_cache_min_tokens=64, draft="off", draft_limit=0, layers=0, host_cache_gib=0.0)
+        spec, sched = build_serving(ns)
+        rep = check_logits(engine_logits_fn(sched.runner.eng), read_golden(a.check), spec=spec)
+        print(json.dumps(rep))
+        return 0 if rep["pass"] else 1
     from .config import tiny_spec, QuantSpec
     from .engine.engine import Engine
     from .engine.generate import BatchGenerator
@@ -278,6 +309,13 @@ def cmd_card(a) -> int:
                     prefill_tokens=a.prefill_tokens)
     card["model"] = state["spec"].name
     card["layers"] = state["spec"].n_layers
+    if getattr(a, "golden", None):          # logit fidelity against sealed golden windows (`cuteafd golden --write`)
+        from .bench.golden import check_logits, engine_logits_fn, read_golden
+        rep = check_logits(engine_logits_fn(state["eng"]), read_golden(a.golden), spec=state["spec"])
+        card["quality"]["logit_fidelity"] = rep["pass"]
+        card["quality"]["logit_fidelity_windows"] = rep["windows"]
+    from .serving.chat_templates import template_round_trip
+    card["quality"]["template_round_trip"] = template_round_trip(state["spec"].family)
     torch.cuda.synchronize()
     print(json.dumps(card))
     return 0
@@ -362,6 +400,7 @@ def main(argv=None) -> int:
     p.add_argument("--prefix-cache-min-tokens", type=int, default=64); p.add_argument("--draft", default="ngram", choices=["off", "ngram"])
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--layers", type=int, default=0)
     p.add_argument("--c1-tokens", type=int, default=320); p.add_argument("--prefill-tokens", type=int, default=8192)
+    p.add_argument("--golden", default=None, help="golden-window file: adds the logit-fidelity gate to the card's quality section")
     p.set_defaults(fn=cmd_card)
     p = sub.add_parser("gateway"); p.add_argument("--listen", default="127.0.0.1:8020"); p.add_argument("--model-id", default="cuteafd-b200")
     p.add_argument("--official-model-names", default=""); p.add_argument("--official-model-names-file", default="")
@@ -373,7 +412,11 @@ def main(argv=None) -> int:
     p = sub.add_parser("usage"); p.add_argument("action", choices=["clear", "clear-log", "export-csv", "demo"])
     p.add_argument("--dir", default=os.path.expanduser("~/.cache/cuteafd-b200/usage")); p.add_argument("--range", default="7d", choices=["1h", "6h", "24h", "7d"])
     p.add_argument("--out", default=""); p.add_argument("--listen", default="127.0.0.1:8010"); p.set_defaults(fn=cmd_usage)
-    p = sub.add_parser("golden"); p.add_argument("--experts", default="bf16"); p.add_argument("--seed", type=int, default=0); p.set_defaults(fn=cmd_golden)
+    p = sub.add_parser("golden"); p.add_argument("--experts", default="bf16"); p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--write", default=None, help="seal golden windows of --model (tiny or a snapshot directory) into this file, from the fp32 oracle")
+    p.add_argument("--check", default=None, help="check the GPU engine of --model against this golden file")
+    p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--windows", type=int, default=8)
+    p.add_argument("--window-tokens", type=int, default=64); p.set_defaults(fn=cmd_golden)
     p = sub.add_parser("expertd"); p.add_argument("--listen", default="127.0.0.1:7000"); p.add_argument("--rank", type=int, default=0); p.set_defaults(fn=cmd_expertd)
     p = sub.add_parser("bench"); p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
     a = ap.parse_args(argv)

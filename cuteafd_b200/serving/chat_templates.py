@@ -384,3 +384,30 @@ def parse_completion(template: ChatTemplate, text: str, thinking: bool = False) 
     for s in skip:
         content = content.replace(s, "")
     return {"content": content.strip("\n") if p.calls else content, "reasoning": join("reasoning"), "tool_calls": p.calls}
+
+
+# ---------------------------------------------------------------------------------------------- round-trip check
+_ASSISTANT_SPAN = {"ChatMLTemplate": ("<|im_start|>assistant\n", "<|im_end|>"), "DeepSeekTemplate": ("<｜Assistant｜>", "<｜end▁of▁sentence｜>"),
+                   "GlmTemplate": ("<|assistant|>\n", "<|user|>")}
+
+
+def template_round_trip(model: str | None) -> bool:
+    """Quality gate of the baseline card: an assistant turn with text and a tool call, rendered by the model's template, parses
+    back to the same text and the same call (reference: the chat-template round trip of cuteafd-bench/src/baseline.rs:1-6).
+    Families without a tool-call syntax (the plain template) pass when the text survives."""
+    import json
+    t = template_for(model)
+    args = {"city": "Oslo", "days": 3, "units": ["C", "F"]}
+    tools = [{"type": "function", "function": {"name": "get_weather", "description": "weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}, "units": {"type": "array", "items": {"type": "string"}}}}}}]
+    call = {"id": "c1", "type": "function", "function": {"name": "get_weather", "arguments": json.dumps(args)}}
+    msgs = [{"role": "user", "content": "q"}, {"role": "assistant", "content": "Looking it up.", "tool_calls": [call]}, {"role": "user", "content": "next"}]
+    span = _ASSISTANT_SPAN.get(type(t).__name__)
+    if span is None:
+        return "Looking it up." in t.render(msgs[:1] + [{"role": "assistant", "content": "Looking it up."}])
+    text = t.render(msgs, tools=tools)
+    if span[0] not in text:
+        return False
+    seg = text.split(span[0], 1)[1].split(span[1], 1)[0]
+    got = parse_completion(t, seg)
+    return [(c["name"], c["arguments"]) for c in got["tool_calls"]] == [("get_weather", args)] and got["content"].strip() == "Looking it up."

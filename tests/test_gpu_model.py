@@ -94,3 +94,16 @@ def test_hybrid_full_and_sliding_window_stack_matches_oracle(head_dim, heads, kv
                 top2 = rows[j].topk(2).values
                 assert float(top2[0] - top2[1]) < 0.05, f"prompt {i} step {j}: {a} != {b}"
                 break
+
+
+def test_engine_passes_golden_windows(tmp_path):
+    """The GPU engine's teacher-forced logits against golden windows sealed from the fp32 oracle; an engine with other weights fails."""
+    from cuteafd_b200.bench.golden import check_logits, engine_logits_fn, write_golden
+    spec = tiny_spec()
+    masters = init_weights(spec, 0)
+    gold = write_golden(str(tmp_path / "g.json"), spec, masters, n=4, length=40, tail=12, topk=6)
+    eng = Engine(DeviceWeights.from_masters(spec, masters, DEV), n_pages=16, max_seqs=4, max_pages_per_seq=4)
+    rep = check_logits(engine_logits_fn(eng), gold, spec=spec, max_rel_l2=0.05)
+    assert rep["pass"], rep
+    other = Engine(DeviceWeights.from_masters(spec, init_weights(spec, 3), DEV), n_pages=16, max_seqs=4, max_pages_per_seq=4)
+    assert not check_logits(engine_logits_fn(other), gold, spec=spec)["pass"]
