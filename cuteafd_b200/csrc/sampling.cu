@@ -61,9 +61,68 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int ld, int
   }
 }
 
+// Large vocabularies with few rows (decode): one block per row leaves most SMs idle and takes ~70 us for 16 x 152k logits.
+// Split variant: AM_SPLIT blocks per row scan a slice each and leave (value, index, non-finite) in a scratch slot; the block that
+// arrives last on the row's counter reduces the slices (same tie rule: lowest index) and re-arms the counter.
+#define AM_SPLIT 8
+#define AM_MAX_ROWS 8192
+static __device__ float am_val[AM_MAX_ROWS * AM_SPLIT];
+static __device__ int am_idx[AM_MAX_ROWS * AM_SPLIT];
+static __device__ int am_bad[AM_MAX_ROWS * AM_SPLIT];
+static __device__ unsigned int am_cnt[AM_MAX_ROWS];
+
+__global__ void __launch_bounds__(512) argmax_rows_split_kernel(const float* __restrict__ logits, int ld, int V, const uint32_t* __restrict__ masks,
+                                                                int mask_words, int* __restrict__ tok, int* __restrict__ status) {
+  pdl_launch(); pdl_wait();
+  __shared__ float sv[16]; __shared__ int si[16]; __shared__ int is_last;
+  const int t = blockIdx.x, part = blockIdx.y;
+  const float* x = logits + (size_t)t * ld;
+  const uint32_t* m = masks ? masks + (size_t)t * mask_words : nullptr;
+  const int per = ((V + AM_SPLIT - 1) / AM_SPLIT + 3) & ~3, i0 = part * per, i1 = min(V, i0 + per);
+  float bv = -INFINITY; int bi = 0x7fffffff; int bad = 0;
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+    const float v = x[i];
+    if (!isfinite(v)) bad = 1;
+    if (allowed(m, i) && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  bad = __syncthreads_or(bad);
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    am_val[t * AM_SPLIT + part] = bv; am_idx[t * AM_SPLIT + part] = bi; am_bad[t * AM_SPLIT + part] = bad;
+    __threadfence();
+    is_last = atomicAdd(&am_cnt[t], 1u) == AM_SPLIT - 1;
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x == 0) {
+    __threadfence();
+    float fv = -INFINITY; int fi = 0x7fffffff, fb = 0;
+    for (int p = 0; p < AM_SPLIT; ++p) {
+      const float v = __ldcg(&am_val[t * AM_SPLIT + p]); const int i = __ldcg(&am_idx[t * AM_SPLIT + p]);
+      fb |= __ldcg(&am_bad[t * AM_SPLIT + p]);
+      if (v > fv || (v == fv && i < fi)) { fv = v; fi = i; }
+    }
+    tok[t] = fi < V ? fi : 0;
+    if (status) status[t] = fb ? 1 : (fi >= V ? 2 : 0);
+    am_cnt[t] = 0;
+  }
+}
+
 extern "C" int cuteafd_argmax_rows(const float* logits, int ld, int T, int V, const uint32_t* masks, int mask_words, int* tok,
                                    float* logprob, int* status, cudaStream_t s) {
   if (T <= 0) return CA_OK;
+  if (!logprob && V >= 32768 && T <= 256) {      // shares one scratch area: calls on different streams at the same time are not supported
+    CA_LAUNCH_PDL(argmax_rows_split_kernel, dim3(T, AM_SPLIT), 512, 0, s, logits, ld, V, masks, mask_words, tok, status);
+    CA_CHECK_LAUNCH("argmax_rows_split");
+    return CA_OK;
+  }
   CA_LAUNCH_PDL(argmax_rows_kernel, T, 1024, 0, s, logits, ld, V, masks, mask_words, tok, logprob, status);
   CA_CHECK_LAUNCH("argmax_rows");
   return CA_OK;

@@ -366,6 +366,16 @@ def test_argmax_mask_logprob_and_verify():
         mask[:, a // 32] |= (1 << (a % 32)) if a % 32 != 31 else -(1 << 31)
     ops.argmax_rows(d, tok, masks=mask.to(DEV))
     assert all(t in allowed for t in tok.cpu().tolist())
+    # the split variant (no logprob, large vocabulary): same tokens, same tie rule, status words, ties across slice boundaries
+    st = torch.zeros(T, dtype=torch.int32, device=DEV)
+    big = torch.randn(T, 151936)
+    big[0, 150000] = big[0, 19] = 60.0                 # equal maxima in different slices -> the lowest id
+    big[2, 5] = float("inf")
+    tok2 = torch.zeros(T, dtype=torch.int32, device=DEV)
+    for _ in range(2):                                 # twice: the arrival counters re-arm themselves
+        ops.argmax_rows(big.to(DEV), tok2, status=st)
+        torch.cuda.synchronize()
+        assert tok2.cpu().tolist() == big.argmax(-1).tolist() and int(tok2[0]) == 19 and st.cpu().tolist() == [0, 0, 1, 0]
     inputs = torch.tensor([[5, 6, 7, 8], [5, 6, 7, 8], [1, 2, 3, 4]], dtype=torch.int32, device=DEV)
     target = torch.tensor([[6, 7, 9, 1], [6, 7, 8, 2], [9, 9, 9, 9]], dtype=torch.int32, device=DEV)
     acc, emit = torch.zeros(3, dtype=torch.int32, device=DEV), torch.zeros(3, dtype=torch.int32, device=DEV)
