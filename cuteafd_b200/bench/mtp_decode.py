@@ -93,6 +93,7 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
         for _ in range(warmup):
             spec_dec.round()
         torch.cuda.synchronize()
+        spec_dec.seconds_drafting = spec_dec.seconds_verifying = 0.0
         n0 = sum(len(s.out) for s in spec_dec.seqs)
         a0 = sum(sum(s.accepted) for s in spec_dec.seqs)
         if rank == 0:
@@ -123,7 +124,7 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
         dt_plain = time.perf_counter() - t1
         eng.check_status()
         # times: the slowest rank counts; tokens: summed over the groups' leaders
-        stats = [dt_spec, dt_plain, float(emitted) if leader else 0.0, float(accepted) if leader else 0.0, float(end_len), 0.0]
+        stats = [dt_spec, dt_plain, float(emitted) if leader else 0.0, float(accepted) if leader else 0.0, float(end_len), spec_dec.seconds_drafting]
         if own:
             run.control(OP_STOP)
             run.check()
@@ -134,13 +135,14 @@ def run_mtp_decode_bench(args, spec: ModelSpec, rank: int, world: int, local: in
         t = torch.tensor(stats, dtype=torch.float64, device=run.dev)
         tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        stats = [float(tmax[0]), float(tmax[1]), float(tsum[2]), float(tsum[3]), float(tmax[4]), 0.0]
+        stats = [float(tmax[0]), float(tmax[1]), float(tsum[2]), float(tsum[3]), float(tmax[4]), float(tmax[5])]
     batch = total_batch
     if rank == 0:
         dt_spec, dt_plain, emitted, accepted = stats[0], stats[1], stats[2], stats[3]
         round_ms = dt_spec * 1e3 / rounds
         res = {"batch": batch, "context": context, "n_draft": n_draft, "rounds": rounds, "warmup": warmup,
-               "round_ms": round(round_ms, 3), "tokens_per_s_measured": round(emitted / dt_spec, 2),
+               "round_ms": round(round_ms, 3), "draft_steps_ms_per_round": round(stats[5] * 1e3 / rounds, 3),
+               "verify_step_ms_per_round": round(round_ms - stats[5] * 1e3 / rounds, 3), "tokens_per_s_measured": round(emitted / dt_spec, 2),
                "accepted_drafts_per_round_per_seq": round(accepted / (rounds * max(batch, 1)), 3),
                "tokens_per_round_per_seq": round(emitted / (rounds * max(batch, 1)), 3),
                "plain_decode": {"ms_per_step": round(dt_plain * 1e3 / rounds, 3), "tokens_per_s": round(batch * rounds / dt_plain, 2)},

@@ -44,6 +44,7 @@ class MtpSpeculator:
         self.eng, self.pool, self.n_draft, self.depth = engine, pool or PagePool(engine.n_pages), n_draft, depth
         self.seqs: list[_Seq] = []
         self.rounds = 0
+        self.seconds_drafting = self.seconds_verifying = 0.0     # host clock, split at the last draft token's read-back
         self._host = None
         self._acc = None
         self.use_graph = use_graph       # replay draft and verify steps from CUDA graphs (steady-state serving / benchmarks)
@@ -118,6 +119,8 @@ class MtpSpeculator:
     def round(self):
         """One draft/verify round for every sequence."""
         eng, nd = self.eng, self.n_draft
+        import time as _time
+        t_start = _time.perf_counter()
         for s in self.seqs:
             s.kv.ensure(self.pool, s.length + nd + 2)
         # drafts: the pending rows first (repairs the draft cache, last row = first draft), then one row at a time
@@ -128,6 +131,7 @@ class MtpSpeculator:
             _, toks, h = self._mtp_step(rows, True)
             for i, t in enumerate(toks):
                 drafts[i].append(t)
+        t_drafted = _time.perf_counter()         # every draft step ends with a token read-back, so host clocks bracket device work
         # verify anchor + drafts in one target step
         tokens, positions, slots, kv_len, q_start, q_len = [], [], [], [], [], []
         for s, dr in zip(self.seqs, drafts):
@@ -165,6 +169,9 @@ class MtpSpeculator:
             s.length += accepted
             s.anchor = emitted[-1]
         self.rounds += 1
+        t_end = _time.perf_counter()
+        self.seconds_drafting += t_drafted - t_start
+        self.seconds_verifying += t_end - t_drafted
 
     def generate(self, prompts: list[list[int]], n_new: int) -> list[list[int]]:
         self.prefill(prompts)
