@@ -125,6 +125,25 @@ def _aliases(a) -> dict:
     return {n: "served" for n in names}
 
 
+def _search_provider(a):
+    """--search-corpus FILE (JSON list of {title, url, text}) | --searxng URL | --exa-key-file FILE; none = no search endpoint."""
+    from .serving.gateway_extras import CorpusProvider, ExaProvider, SearxngProvider
+    if getattr(a, "search_corpus", ""):
+        return CorpusProvider(json.load(open(a.search_corpus)))
+    if getattr(a, "searxng", ""):
+        return SearxngProvider(a.searxng)
+    if getattr(a, "exa_key_file", ""):
+        return ExaProvider(open(a.exa_key_file).read().strip())
+    return None
+
+
+def _gateway_args(p):
+    p.add_argument("--record", default="", help="append every POST request / response pair to this JSONL file")
+    p.add_argument("--search-corpus", default="", help="JSON file of documents served by /v1/alpha/search (offline provider)")
+    p.add_argument("--searxng", default="", help="base URL of a SearXNG instance for /v1/alpha/search")
+    p.add_argument("--exa-key-file", default="", help="file holding an Exa API key for /v1/alpha/search")
+
+
 def cmd_gateway(a) -> int:
     """The gateway surfaces (Anthropic Messages, OpenAI Responses, aliases, CORS) over a CPU stand-in model: lets
     client integrations be developed without a GPU.  With a GPU the same surfaces are part of `serve --gateway on`.
@@ -138,7 +157,13 @@ def cmd_gateway(a) -> int:
     runner.next_token = lambda prefix: 257 if len(prefix) % 97 == 0 else 32 + (sum(prefix[-3:]) % 90)
     loop = ServingLoop(Scheduler(runner, PagePool(1024))).start()
     app = build_app(loop, model_id=a.model_id, template=template_for(a.chat_template or "plain"), model_aliases=_aliases(a),
-                    allow_origin=a.gateway_allow_origin or None, enable_bench=True)
+                    allow_origin=a.gateway_allow_origin or None, enable_bench=True, search=_search_provider(a), record_path=a.record or None)
+    if a.replay:                 # play a recorded session back against the stand-in model (or --replay-url) and report differences
+        from .serving.gateway_extras import replay
+        rep = replay(a.replay_url or app, a.replay)
+        print(json.dumps(rep))
+        loop.stop()
+        return 0 if not rep["mismatches"] else 1
     host, port = a.listen.rsplit(":", 1)
     import uvicorn
     uvicorn.run(app, host=host, port=int(port), log_level="info")
@@ -168,7 +193,8 @@ def cmd_serve(a) -> int:
     app = build_app(loop, model_id=a.model_id or spec.name, tokenizer=load_tokenizer(a.model if os.path.isdir(a.model) else None),
                     api_keys=keys, max_output=a.max_output, template=template_for(a.chat_template or spec.name),
                     usage=usage, enable_bench=a.enable_bench, thermal=thermal, gateway=a.gateway == "on",
-                    model_aliases=_aliases(a), allow_origin=a.gateway_allow_origin or None)
+                    model_aliases=_aliases(a), allow_origin=a.gateway_allow_origin or None, search=_search_provider(a),
+                    record_path=a.record or None)
     host, port = a.listen.rsplit(":", 1)
     import uvicorn
     uvicorn.run(app, host=host, port=int(port), log_level="info")
@@ -388,6 +414,7 @@ def main(argv=None) -> int:
     p.add_argument("--gateway", default="on", choices=["on", "off"]); p.add_argument("--official-model-names", default="")
     p.add_argument("--official-model-names-file", default=""); p.add_argument("--gateway-allow-origin", default="")
     p.add_argument("--chat-template", default="", help="chat template family (chatml / qwen3-coder / deepseek / glm / plain); default: by model name")
+    _gateway_args(p)
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.add_argument("--n-micro", type=int, default=0, help="multi-GPU: micro-batches the attention ranks keep in flight (0 = the layout's default)")
@@ -404,7 +431,10 @@ def main(argv=None) -> int:
     p.set_defaults(fn=cmd_card)
     p = sub.add_parser("gateway"); p.add_argument("--listen", default="127.0.0.1:8020"); p.add_argument("--model-id", default="cuteafd-b200")
     p.add_argument("--official-model-names", default=""); p.add_argument("--official-model-names-file", default="")
-    p.add_argument("--gateway-allow-origin", default=""); p.add_argument("--chat-template", default=""); p.set_defaults(fn=cmd_gateway)
+    p.add_argument("--gateway-allow-origin", default=""); p.add_argument("--chat-template", default="")
+    p.add_argument("--replay", default="", help="replay a recorded JSONL session instead of serving; exit code 1 on differences")
+    p.add_argument("--replay-url", default="", help="replay against this server instead of the in-process stand-in")
+    _gateway_args(p); p.set_defaults(fn=cmd_gateway)
     p = sub.add_parser("quantize"); p.add_argument("src"); p.add_argument("dst")
     p.add_argument("--dense", default="nvfp4", choices=["bf16", "fp8_block128", "nvfp4", "mxfp4"])
     p.add_argument("--experts", default="mxfp4", choices=["bf16", "fp8_block128", "nvfp4", "mxfp4"])

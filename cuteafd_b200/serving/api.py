@@ -150,13 +150,15 @@ except ImportError:      # pragma: no cover - the HTTP layer is optional
 
 def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=None, api_keys=None, max_output: int = 4096, template=None,
               usage=None, enable_bench: bool = False, thermal=None, gateway: bool = True, model_aliases: dict | None = None,
-              allow_origin: str | None = None):
+              allow_origin: str | None = None, search=None, record_path: str | None = None):
     """`usage`: a `UsageStore` that gets one row per finished request and backs `/usage`.  `enable_bench` turns on the
     probe header `x-cuteafd-probe` (JSON: `skip_cache`, `no_drafts`, `token_ids`) that benchmarks use to pin what a
     request exercises (cuteafd-api/src/openai/probe.rs).  `thermal`: object with `.sample()` for `/v1/thermal`.
     `gateway` adds the surfaces other clients speak, mapped onto the same scheduler: Anthropic Messages and OpenAI
     Responses (`/v1/responses`, stored responses with `previous_response_id` chaining); `model_aliases` lists
-    official model names that clients may ask for and that are answered by the served model (gateway/models.rs)."""
+    official model names that clients may ask for and that are answered by the served model (gateway/models.rs).  `search`: a
+    provider for `/v1/alpha/search` (see `gateway_extras.SearchProvider`); `record_path`: every request / response pair of the
+    JSON endpoints is appended to this JSONL file (`gateway_extras.replay` plays such a file back)."""
     if FastAPI is None:
         raise RuntimeError("fastapi is not installed")
 
@@ -684,4 +686,8 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
                 loop.cancel(rid)
         return StreamingResponse(sse(), media_type="text/event-stream")
 
+    if gateway:
+        from .gateway_extras import install_gateway_extras
+        install_gateway_extras(app, tok=tok, tmpl=tmpl, auth=auth, start_generation=start_generation, collect=collect, loop=loop,
+                               served_name=served_name, search=search, record_path=record_path)
     return app
