@@ -153,7 +153,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="qwen3-235b-decode", choices=["qwen3-235b-decode", "deepseek-v3-decode", "deepseek-v3-plain", "deepseek-v3-ttft"],
+    ap.add_argument("--config", default="qwen3-235b-decode", choices=["qwen3-235b-decode", "deepseek-v3-decode", "deepseek-v3-plain", "deepseek-v3-ttft", "hybrid-gdn-decode", "hybrid-kda-decode"],
                     help="deepseek-v3-plain: one-token-per-step decode of the DeepSeek-V3 shape through the generic path (any --layout; no drafter)")
     ap.add_argument("--ttft-prompt", type=int, default=32768); ap.add_argument("--ttft-shared", type=int, default=28672)
     ap.add_argument("--ttft-sessions", type=int, default=8); ap.add_argument("--ttft-decode", type=int, default=256)

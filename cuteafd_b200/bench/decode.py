@@ -41,6 +41,9 @@ def run_decode_bench(args, rank: int, world: int, local: int, clocks) -> dict:
         spec = deepseek_v3_spec(args.layers or 61)
         if world == 1:
             raise SystemExit("the DeepSeek-V3 shape needs the attention/expert split (run with --gpus 4 or 8)")
+    elif args.config.startswith("hybrid-"):
+        from ..config import hybrid_gdn_spec
+        spec = hybrid_gdn_spec(args.layers or 48, per_channel=args.config.startswith("hybrid-kda"))
     else:
         spec = qwen3_235b_spec(args.layers or 94)
     batch = getattr(args, "batch_total", 0) or args.batch_per_gpu * world

@@ -99,6 +99,8 @@ def engine_logits_fn(eng):
         T = len(tokens)
         s = SeqKV()
         s.ensure(pool, T + 1)
+        if getattr(eng, "lin_layers", None):
+            eng.reset_state_slots([0])
         eng.set_inputs(tokens, list(range(T)), [s.slot(p) for p in range(T)], list(range(T)), [T], [0], [T], [s.pages])
         lane = eng.run(StepShape(T=T, n_seq=1, max_q_len=T, n_logits=T, attn_splits=1), use_graph=False)
         out = lane.logits[:T].float().cpu()

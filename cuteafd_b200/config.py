@@ -43,6 +43,15 @@ class AttentionSpec:
     index_topk: int = 0
     index_heads: int = 32
     index_dim: int = 128
+    # Hybrid stacks with linear-attention layers (the Qwen 3.8 / GLM 5.3 Flash lines; GQA models only): with linear_every = n > 0,
+    # layer i is a full-attention layer when (i + 1) % n == 0 and a gated delta-rule layer otherwise (n = 4: three linear layers,
+    # then one full).  Linear layers have `linear_k_heads` query / key heads and `linear_v_heads` value heads of 128 dimensions,
+    # a width-4 causal convolution in front of q / k / v, and a per-sequence recurrent state instead of KV pages.
+    # `linear_per_channel`: one decay per key channel (KDA) instead of one per head (GDN).
+    linear_every: int = 0
+    linear_k_heads: int = 2
+    linear_v_heads: int = 4
+    linear_per_channel: bool = False
 
     @property
     def q_dim(self) -> int:
@@ -115,6 +124,11 @@ class ModelSpec:
         if a.full_every <= 0:
             return a.window == 0
         return layer >= self.n_layers or layer % a.full_every == 0
+
+    def layer_is_linear(self, layer: int) -> bool:
+        """A gated delta-rule (linear attention) layer; MTP draft layers (>= n_layers) are full-attention layers."""
+        n = self.attn.linear_every
+        return n > 0 and layer < self.n_layers and (layer + 1) % n != 0
 
     def layer_window(self, layer: int) -> int:
         a = self.attn
@@ -217,8 +231,22 @@ def ep_microbench_spec() -> ModelSpec:
                      quant=QuantSpec(experts="mxfp4"))
 
 
+def hybrid_gdn_spec(n_layers: int = 48, per_channel: bool = False) -> ModelSpec:
+    """Hybrid linear-attention MoE shape (the Qwen-Next line): three gated delta-rule layers (16 q/k heads, 32 value heads of 128)
+    then one full GQA layer (16q/2kv/128), hidden 2048, 128 experts top-8 I=768 + 1 shared, vocab 151936, bf16 dense projections and
+    NVFP4 experts.  `per_channel`: one decay per key channel (the KDA variant of the GLM Flash line) instead of one per head."""
+    return ModelSpec(
+        name="hybrid-kda-shape" if per_channel else "hybrid-gdn-shape", family="hybrid_linear", vocab=151936, hidden=2048, n_layers=n_layers, rms_eps=1e-6,
+        attn=AttentionSpec(kind="gqa", n_heads=16, n_kv_heads=2, head_dim=128, rope_theta=1e6, rope_interleaved=False, qk_norm=True,
+                           linear_every=4, linear_k_heads=16, linear_v_heads=32, linear_per_channel=per_channel),
+        moe=MoESpec(n_experts=128, top_k=8, intermediate=768, n_shared=1, scoring="softmax", normalize=True),
+        quant=QuantSpec(experts="nvfp4", dense="bf16", kv="bf16"))
+
+
 NAMED_SPECS = {
     "tiny": tiny_spec,
+    "hybrid-gdn": hybrid_gdn_spec,
+    "hybrid-kda": lambda **kw: hybrid_gdn_spec(per_channel=True, **kw),
     "deepseek-v3": deepseek_v3_spec,
     "qwen3-235b": qwen3_235b_spec,
     "ep-microbench": ep_microbench_spec,

@@ -99,6 +99,22 @@ class Lane:
             self.h1_q = (ActBuffer.alloc(ek, rows, m.intermediate, self.tn_g, dev) if ek != KIND_BF16
                          else ActBuffer.wrap_bf16(self.h1, self.tn_g))
             self.y2 = bf(rows, H)
+        if a.linear_every:
+            self.lin_buf(eng)
+
+    def lin_buf(self, eng) -> dict:
+        """Buffers of the linear-attention layers of a hybrid stack."""
+        if getattr(self, "_lin", None) is None:
+            a, dev, cap = eng.spec.attn, eng.device, self.cap
+            Hk, Hv = a.linear_k_heads, a.linear_v_heads
+            bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+            f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
+            nb = Hv + (Hv * 128 if a.linear_per_channel else Hv)
+            on = bf(cap, Hv * 128)
+            self._lin = {"qkvz": bf(cap, (2 * Hk + 2 * Hv) * 128), "ba": f32(cap, nb), "conv": bf(cap, (2 * Hk + Hv) * 128), "q": bf(cap, Hv, 128),
+                         "k": bf(cap, Hv, 128), "v": bf(cap, Hv, 128), "g": f32(cap, Hv, 128) if a.linear_per_channel else f32(cap, Hv),
+                         "beta": f32(cap, Hv), "o": bf(cap, Hv, 128), "on": on, "on_act": ActBuffer.wrap_bf16(on, self.tn)}
+        return self._lin
 
     def ffn_buf(self, eng, inter: int):
         if inter not in self.ffn_bufs:
@@ -120,7 +136,7 @@ class Engine:
                 raise NotImplementedError("Engine runs GQA models; MLA models use engine.mla.MlaEngine")
             self.dense_kind = weights.layers[0].wo.kind
         else:
-            self.dense_kind = weights.layers[0].wqkv.kind
+            self.dense_kind = weights.layers[0].wo.kind
         first_moe = next((l for l in weights.layers if l.w_gate is not None), None)
         self.expert_kind = first_moe.w_gate.kind if first_moe is not None else KIND_BF16
         self.expert_range = expert_range or (0, spec.moe.n_experts)
@@ -140,6 +156,15 @@ class Engine:
             self.kv_tmaps = ops.encode_kv_tmaps(self.kv) if a.head_dim == 128 and 128 % (a.n_heads // a.n_kv_heads) == 0 else None
         else:
             self._alloc_attention_state()
+        # hybrid stacks: gated delta-rule layers keep a recurrent state and the last three convolution inputs per sequence slot
+        self.lin_layers = [i for i in range(spec.n_layers) if spec.layer_is_linear(i)]
+        if self.lin_layers:
+            if a.kind != "gqa" or a.linear_v_heads % a.linear_k_heads:
+                raise ValueError("linear-attention layers: GQA stacks with linear_v_heads a multiple of linear_k_heads")
+            self.lin_index = {li: j for j, li in enumerate(self.lin_layers)}
+            C = (2 * a.linear_k_heads + a.linear_v_heads) * 128
+            self.lin_state = torch.zeros(len(self.lin_layers), max_seqs, a.linear_v_heads, 128, 128, dtype=torch.float32, device=self.device)
+            self.lin_carry = torch.zeros(len(self.lin_layers), max_seqs, 3, C, dtype=torch.bfloat16, device=self.device)
         # memory ledger: what this engine holds, by category (reported by `/v1/stats` and `cuteafd doctor`)
         from ..utils.memory_ledger import LEDGER
         with LEDGER.scope("weights"):
@@ -175,7 +200,7 @@ class Engine:
             return
         cap = 1 << (cap - 1).bit_length()
         S, MP = self.max_seqs, self.max_pages
-        n = 4 * cap + 3 * S + S * MP
+        n = 4 * cap + 4 * S + S * MP
         self.meta_host = torch.zeros(n, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else torch.zeros(n, dtype=torch.int32)
         self.meta_dev = torch.zeros(n, dtype=torch.int32, device=self.device)
 
@@ -183,7 +208,7 @@ class Engine:
             o = 0
             out = {}
             for name, cnt in (("tokens", cap), ("positions", cap), ("slot_map", cap), ("logit_rows", cap),
-                              ("kv_len", S), ("q_start", S), ("q_len", S)):
+                              ("kv_len", S), ("q_start", S), ("q_len", S), ("state_slot", S)):
                 out[name] = buf[o:o + cnt]
                 o += cnt
             out["page_table"] = buf[o:o + S * MP].view(S, MP)
@@ -193,8 +218,9 @@ class Engine:
         self.graphs.clear()     # views moved: captured graphs are stale
         self.census.invalidate()
 
-    def set_inputs(self, tokens, positions, slot_map, logit_rows, kv_len, q_start, q_len, page_table_rows):
-        """Fill the pinned host block and enqueue ONE host-to-device copy."""
+    def set_inputs(self, tokens, positions, slot_map, logit_rows, kv_len, q_start, q_len, page_table_rows, state_slots=None):
+        """Fill the pinned host block and enqueue ONE host-to-device copy.  `state_slots`: per sequence of the step, the slot of its
+        recurrent state (hybrid stacks with linear-attention layers); default: the sequence's index in the step."""
         T, S = len(tokens), len(kv_len)
         self._ensure_meta(T)
         mh = self.mh
@@ -206,6 +232,7 @@ class Engine:
         mh["kv_len"][:S] = torch.as_tensor(kv_len, dtype=torch.int32)
         mh["q_start"][:S] = torch.as_tensor(q_start, dtype=torch.int32)
         mh["q_len"][:S] = torch.as_tensor(q_len, dtype=torch.int32)
+        mh["state_slot"][:S] = torch.as_tensor(list(state_slots) if state_slots is not None else list(range(S)), dtype=torch.int32)
         for s, row in enumerate(page_table_rows):
             mh["page_table"][s, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
         self.meta_dev.copy_(self.meta_host, non_blocking=True)
@@ -273,9 +300,42 @@ class Engine:
             self._quant(L.xn, L.xq, T, None)              # FP8 operands: separate quantiser (no-op for bf16)
         self._pre_normed = True
 
+    def reset_state_slots(self, slots):
+        """A new sequence takes over these recurrent-state slots: zero state, zero convolution history."""
+        if getattr(self, "lin_layers", None) and len(slots):
+            idx = torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
+            self.lin_state.index_fill_(1, idx, 0.0)
+            self.lin_carry.index_fill_(1, idx, 0.0)
+
+    def _linear_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
+        """Gated delta-rule layer: fused projection -> width-4 causal convolution + SiLU -> normalised q / k, gates -> recurrence over
+        the sequences' state slots -> gated RMSNorm -> output projection (+ residual).  Oracle: `RefModel.linear_attention`."""
+        spec, a, T, md = self.spec, self.spec.attn, sh.T, self.md
+        Hk, Hv = a.linear_k_heads, a.linear_v_heads
+        C, Nq, j = (2 * Hk + Hv) * 128, (2 * Hk + 2 * Hv) * 128, self.lin_index[li]
+        b = L.lin_buf(self)
+        xq = self._norm_in(lw, L, T)
+        self._dense(lw.lin_qkvz, xq, b["qkvz"], T)
+        if xq.kind != KIND_BF16:           # the gate projection stays bf16: it needs the bf16 normalised rows
+            raise NotImplementedError("linear-attention layers run with bf16 dense projections")
+        self._dense(lw.lin_ba, L.xn_act, b["ba"], T)
+        st, n_seq = ptr(self.status), sh.n_seq
+        native.call("cuteafd_short_conv4", ptr(b["qkvz"]), ptr(lw.lin_conv), ptr(self.lin_carry[j]), ptr(md["state_slot"]), ptr(md["q_start"]),
+                    ptr(md["q_len"]), ptr(b["conv"]), n_seq, C, Nq, self.max_seqs, st, native.stream())
+        native.call("cuteafd_linear_prepare", ptr(b["conv"]), ptr(b["ba"]), ptr(lw.lin_a_log), ptr(lw.lin_dt_bias), ptr(b["q"]), ptr(b["k"]), ptr(b["v"]),
+                    ptr(b["g"]), ptr(b["beta"]), T, Hk, Hv, b["ba"].shape[1], 1 if a.linear_per_channel else 0, native.stream())
+        native.call("cuteafd_gated_delta_step", ptr(b["q"]), ptr(b["k"]), ptr(b["v"]), ptr(b["g"]), ptr(b["beta"]), ptr(self.lin_state[j]),
+                    ptr(md["state_slot"]), ptr(md["q_start"]), ptr(md["q_len"]), ptr(b["o"]), None, n_seq, Hv, 1 if a.linear_per_channel else 0,
+                    self.max_seqs, st, native.stream())
+        native.call("cuteafd_gated_rmsnorm", ptr(b["o"]), ptr(b["qkvz"]), ptr(lw.lin_norm), ptr(b["on"]), T, Hv, Nq, C, spec.rms_eps, native.stream())
+        self._attn_out(li, lw, b["on_act"], L, T)
+        self.launches_per_step += 7
+
     def _attention_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
         spec, a, T = self.spec, self.spec.attn, sh.T
         md = self.md
+        if lw.lin_qkvz is not None:
+            return self._linear_layer(li, lw, L, sh)
         xq = self._norm_in(lw, L, T)
         self._dense(lw.wqkv, xq, L.qkv, T)
         window = spec.layer_window(li)                # hybrid stacks: full and sliding-window layers differ in window, sink and theta
@@ -529,8 +589,13 @@ class Engine:
         if key not in self.graphs:
             if hook:
                 hook(sh, False)
+            # the warm-up execution must not advance the recurrent state of linear-attention layers (KV writes repeat harmlessly)
+            saved = (self.lin_state.clone(), self.lin_carry.clone()) if getattr(self, "lin_layers", None) else None
             self.forward(sh)                    # warm-up launch outside capture (loads modules, sizes scratch)
             torch.cuda.synchronize()
+            if saved is not None:
+                self.lin_state.copy_(saved[0])
+                self.lin_carry.copy_(saved[1])
             self._capture(sh)
         if hook:
             hook(sh, True)

@@ -41,6 +41,7 @@ class BatchGenerator:
         self.seqs = [SeqKV() for _ in prompts]
         for s, p in zip(self.seqs, prompts):
             s.ensure(self.pool, len(p) + 1)
+        eng.reset_state_slots(range(len(prompts)))       # hybrid stacks: sequence i owns recurrent-state slot i
         first = [0] * len(prompts)
         # sequences are prefetched one chunk at a time, several sequences per step while rows fit
         pending = [(i, 0) for i in range(len(prompts))]
@@ -68,7 +69,8 @@ class BatchGenerator:
                 if off + take == len(prompts[i]):
                     finals.append((i, len(logit_rows)))
                     logit_rows.append(len(tokens) - 1)
-            self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, self._page_rows(seqs))
+            self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, self._page_rows(seqs),
+                                             state_slots=[i for i, _, _ in batch])
             sh = StepShape(T=len(tokens), n_seq=len(batch), max_q_len=max(q_len), n_logits=len(logit_rows), attn_splits=1)
             lane = eng.run(sh, use_graph=use_graph)
             if finals:
@@ -111,6 +113,7 @@ class BatchGenerator:
         """Stages ONE step that ingests every prompt whole (short prompts; `prefill` chunks long ones)."""
         eng = self.eng
         self.seqs = [SeqKV() for _ in prompts]
+        eng.reset_state_slots(range(len(prompts)))
         tokens, positions, slots, logit_rows, kv_len, q_start, q_len = [], [], [], [], [], [], []
         for s, p in zip(self.seqs, prompts):
             s.ensure(self.pool, len(p) + 1)

@@ -41,6 +41,8 @@ class MtpSpeculator:
     def __init__(self, engine: Engine, pool: PagePool | None = None, n_draft: int = 3, depth: int = 0, use_graph: bool = False):
         if not engine.weights.mtp:
             raise ValueError("this model has no MTP module")
+        if getattr(engine, "lin_layers", None):
+            raise NotImplementedError("speculation needs recurrent-state snapshots per draft row: not wired for linear-attention stacks")
         self.eng, self.pool, self.n_draft, self.depth = engine, pool or PagePool(engine.n_pages), n_draft, depth
         self.seqs: list[_Seq] = []
         self.rounds = 0

@@ -49,6 +49,14 @@ class LayerWeights:
     ws_gate: TcWeight | None = None     # shared expert, or the dense FFN of a non-MoE layer
     ws_up: TcWeight | None = None
     ws_down: TcWeight | None = None
+    # gated delta-rule (linear attention) layers: fused q / k / v / z projection, gate projection (fp32 output), convolution taps,
+    # decay parameters, output norm; `wo` is then [hidden, Hv * 128] and `wqkv` is None
+    lin_qkvz: TcWeight | None = None
+    lin_ba: TcWeight | None = None
+    lin_conv: torch.Tensor | None = None
+    lin_dt_bias: torch.Tensor | None = None
+    lin_a_log: torch.Tensor | None = None
+    lin_norm: torch.Tensor | None = None
 
     def nbytes(self) -> int:
         n = 0
@@ -86,10 +94,16 @@ class DeviceWeights:
         def layer_from(lw: dict) -> LayerWeights:
             if spec.attn.kind != "gqa":
                 raise NotImplementedError("from_masters: MLA layers are built by models.mla")
-            wqkv = torch.cat([lw["wq"], lw["wk"], lw["wv"]], 0)
-            out = LayerWeights(attn_norm=f32(lw["attn_norm"]), ffn_norm=f32(lw["ffn_norm"]),
-                               wqkv=TcWeight.from_master(wqkv, dk, device, act_gs),
-                               wo=TcWeight.from_master(lw["wo"], dk, device, act_gs))
+            if "w_qkvz" in lw:       # linear-attention layer
+                out = LayerWeights(attn_norm=f32(lw["attn_norm"]), ffn_norm=f32(lw["ffn_norm"]), wqkv=None,
+                                   wo=TcWeight.from_master(lw["wo"], dk, device, act_gs),
+                                   lin_qkvz=TcWeight.from_master(lw["w_qkvz"], dk, device, act_gs), lin_ba=TcWeight.from_master(lw["w_ba"], "bf16", device),
+                                   lin_conv=f32(lw["conv_w"]), lin_dt_bias=f32(lw["dt_bias"]), lin_a_log=f32(lw["a_log"]), lin_norm=f32(lw["lin_norm"]))
+            else:
+                wqkv = torch.cat([lw["wq"], lw["wk"], lw["wv"]], 0)
+                out = LayerWeights(attn_norm=f32(lw["attn_norm"]), ffn_norm=f32(lw["ffn_norm"]),
+                                   wqkv=TcWeight.from_master(wqkv, dk, device, act_gs),
+                                   wo=TcWeight.from_master(lw["wo"], dk, device, act_gs))
             if "q_norm" in lw:
                 out.q_norm, out.k_norm = f32(lw["q_norm"]), f32(lw["k_norm"])
             if "sink" in lw:
@@ -128,9 +142,14 @@ class DeviceWeights:
         nq, nk = a.n_heads * a.head_dim, a.n_kv_heads * a.head_dim
 
         def layer_to(l: LayerWeights) -> dict:
-            qkv = l.wqkv.dequantize()[0]
-            d = {"attn_norm": l.attn_norm.cpu(), "ffn_norm": l.ffn_norm.cpu(), "wq": qkv[:nq], "wk": qkv[nq:nq + nk],
-                 "wv": qkv[nq + nk:], "wo": l.wo.dequantize()[0]}
+            if l.lin_qkvz is not None:
+                d = {"attn_norm": l.attn_norm.cpu(), "ffn_norm": l.ffn_norm.cpu(), "w_qkvz": l.lin_qkvz.dequantize()[0], "w_ba": l.lin_ba.dequantize()[0],
+                     "conv_w": l.lin_conv.cpu(), "dt_bias": l.lin_dt_bias.cpu(), "a_log": l.lin_a_log.cpu(), "lin_norm": l.lin_norm.cpu(),
+                     "wo": l.wo.dequantize()[0]}
+            else:
+                qkv = l.wqkv.dequantize()[0]
+                d = {"attn_norm": l.attn_norm.cpu(), "ffn_norm": l.ffn_norm.cpu(), "wq": qkv[:nq], "wk": qkv[nq:nq + nk],
+                     "wv": qkv[nq + nk:], "wo": l.wo.dequantize()[0]}
             if l.q_norm is not None:
                 d["q_norm"], d["k_norm"] = l.q_norm.cpu(), l.k_norm.cpu()
             if l.sink is not None:
@@ -162,6 +181,8 @@ class DeviceWeights:
         a, m, h = spec.attn, spec.moe, spec.hidden
         dk, ek = _dense_kind(spec), _expert_kind(spec)
         n_sets = spec.n_layers if distinct_layers <= 0 else min(distinct_layers, spec.n_layers)
+        if a.linear_every and n_sets < spec.n_layers and n_sets % a.linear_every:
+            raise ValueError("random: with linear-attention layers, distinct_layers must be a multiple of linear_every (the weight sets repeat)")
         ones = lambda n: torch.ones(n, dtype=torch.float32, device=device)
         e_lo, e_hi = experts_range if experts_range else (0, m.n_experts)
 
@@ -169,9 +190,20 @@ class DeviceWeights:
             s = seed * 1000 + i * 16
             R = lambda G, N, K, kind, j: TcWeight.random(G, N, K, kind, device, spec.init_std, act_gs, s + j)
             RE = lambda N, K, j: TcWeight.random(m.n_experts, N, K, ek, device, spec.init_std, act_gs, s + j, groups=(e_lo, e_hi))
-            out = LayerWeights(attn_norm=ones(h), ffn_norm=ones(h),
-                               wqkv=R(1, (a.n_heads + 2 * a.n_kv_heads) * a.head_dim, h, dk, 0) if with_attention else None,
-                               wo=R(1, h, a.n_heads * a.head_dim, dk, 1) if with_attention else None)
+            if with_attention and spec.layer_is_linear(i):
+                Hk, Hv = a.linear_k_heads, a.linear_v_heads
+                C = (2 * Hk + Hv) * 128
+                gl = torch.Generator(device=device).manual_seed(s + 9)
+                nb = Hv + (Hv * 128 if a.linear_per_channel else Hv)
+                out = LayerWeights(attn_norm=ones(h), ffn_norm=ones(h), wqkv=None, wo=R(1, h, Hv * 128, dk, 1),
+                                   lin_qkvz=R(1, (2 * Hk + 2 * Hv) * 128, h, dk, 0), lin_ba=R(1, nb, h, "bf16", 10),
+                                   lin_conv=torch.empty(C, 4, device=device).normal_(0, 0.5, generator=gl),
+                                   lin_dt_bias=torch.empty(Hv * 128 if a.linear_per_channel else Hv, device=device).normal_(0, 0.5, generator=gl),
+                                   lin_a_log=torch.empty(Hv, device=device).normal_(0, 0.5, generator=gl), lin_norm=ones(128))
+            else:
+                out = LayerWeights(attn_norm=ones(h), ffn_norm=ones(h),
+                                   wqkv=R(1, (a.n_heads + 2 * a.n_kv_heads) * a.head_dim, h, dk, 0) if with_attention else None,
+                                   wo=R(1, h, a.n_heads * a.head_dim, dk, 1) if with_attention else None)
             if not with_attention:      # expert rank: routed experts only
                 if spec.is_moe_layer(i) and e_hi > e_lo:
                     out.w_gate, out.w_up, out.w_down = RE(m.intermediate, h, 3), RE(m.intermediate, h, 4), RE(h, m.intermediate, 5)

@@ -598,7 +598,7 @@ def gated_delta_step(q, k, v, g, beta, state, slot_of_seq, q_start, q_len, out, 
 def short_conv4(x, w, carry, slot_of_seq, q_start, q_len, y, *, status=None):
     """Causal depthwise convolution of width 4 + SiLU: x, y bf16 [T, C]; w fp32 [C, 4]; carry bf16 [slots, 3, C] (the last three
     inputs of every sequence, updated in place)."""
-    _chk(x, torch.bfloat16, "x"); _chk(y, torch.bfloat16, "y"); _chk(w, torch.float32, "w"); _chk(carry, torch.bfloat16, "carry")
-    call("cuteafd_short_conv4", ptr(x), ptr(w), ptr(carry), ptr(slot_of_seq), ptr(q_start), ptr(q_len), ptr(y), slot_of_seq.numel(), x.shape[1],
-         carry.shape[0], ptr(status), stream())
+    _chk(y, torch.bfloat16, "y"); _chk(w, torch.float32, "w"); _chk(carry, torch.bfloat16, "carry")      # x may be a column slice of wider rows
+    call("cuteafd_short_conv4", ptr(x), ptr(w), ptr(carry), ptr(slot_of_seq), ptr(q_start), ptr(q_len), ptr(y), slot_of_seq.numel(), y.shape[1],
+         x.stride(0), carry.shape[0], ptr(status), stream())
     return y

@@ -53,7 +53,9 @@ _PROTOS = {
     "cuteafd_mla_attention": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P],
     "cuteafd_tmap_encode_latent": [P, P, U64],
     "cuteafd_gated_delta_step": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P, P],
-    "cuteafd_short_conv4": [P, P, P, P, P, P, P, I, I, I, P, P],
+    "cuteafd_linear_prepare": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "cuteafd_gated_rmsnorm": [P, P, P, P, I, I, I, I, F, P],
+    "cuteafd_short_conv4": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "cuteafd_dsa_index_scores": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "cuteafd_tmap_encode_index_keys": [P, P, U64],
     "cuteafd_dsa_topk": [P, I, P, I, I, I, P, P, P],

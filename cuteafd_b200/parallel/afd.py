@@ -153,6 +153,8 @@ class AttnRankEngine(Engine):
         dep = plan.dep
         self.full_spec, self.plan, self.dep, self.rank, self.comm, self.block = spec, plan, dep, rank, comm, block
         self.tp, self.tp_rank = dep.tp, dep.attn_ranks.index(rank) % dep.tp
+        if self.tp > 1 and spec.attn.linear_every:
+            raise NotImplementedError("hybrid stacks with linear-attention layers run with attention TP 1 (data-parallel attention ranks)")
         self.group = dep.group_of(rank)
         self.group_ranks = dep.group_ranks(self.group)
         lw = self._make_weights(spec, device, seed, act_gs, masters)
@@ -308,7 +310,7 @@ class AttnRankEngine(Engine):
                 msh = StepShape(T=t1 - t0, n_seq=s1 - s0, max_q_len=q, n_logits=nl, attn_splits=splits, uniform=True)
                 mmd = {"tokens": md["tokens"][t0:t1], "positions": md["positions"][t0:t1], "slot_map": md["slot_map"][t0:t1],
                        "logit_rows": self._iota[:max(nl, 1)], "kv_len": md["kv_len"][s0:s1], "q_start": self._qstart[q][:max(s1 - s0, 1)],
-                       "q_len": md["q_len"][s0:s1], "page_table": md["page_table"][s0:s1]}
+                       "q_len": md["q_len"][s0:s1], "state_slot": md["state_slot"][s0:s1], "page_table": md["page_table"][s0:s1]}
                 ctxs.append(MicroCtx(mb, msh, mmd, self._mb_lane(max(t1 - t0, 1), mb, main, t0), t0, s0))
         for c in ctxs:
             c.main = main
@@ -324,7 +326,7 @@ class AttnRankEngine(Engine):
 
     def load_inputs(self, block: torch.Tensor):
         """Mirror side of `set_inputs`: `block` is the leader's packed int32 input block (same engine geometry)."""
-        need = (block.numel() - 3 * self.max_seqs - self.max_seqs * self.max_pages) // 4
+        need = (block.numel() - 4 * self.max_seqs - self.max_seqs * self.max_pages) // 4
         self._ensure_meta(need)
         if block.numel() != self.meta_host.numel():
             raise ValueError(f"input block of {block.numel()} words does not fit this engine's layout ({self.meta_host.numel()})")

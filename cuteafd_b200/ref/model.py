@@ -41,6 +41,15 @@ def init_layer(spec: ModelSpec, gen: torch.Generator, layer: int, force_dense: b
             w["wq_idx"] = _randn(gen, a.index_heads * a.index_dim, a.q_lora_rank or h, std=s)
             w["wk_idx"] = _randn(gen, a.index_dim, h, std=s)
             w["w_idx"] = _randn(gen, a.index_heads, h, std=s)
+    elif spec.layer_is_linear(layer):
+        Hk, Hv = a.linear_k_heads, a.linear_v_heads
+        w["w_qkvz"] = _randn(gen, (2 * Hk + 2 * Hv) * 128, h, std=s)          # rows: q [Hk x 128], k [Hk x 128], v [Hv x 128], z [Hv x 128]
+        w["w_ba"] = _randn(gen, Hv + (Hv * 128 if a.linear_per_channel else Hv), h, std=s)   # rows: b [Hv], a [Hv] (or a per channel [Hv x 128])
+        w["conv_w"] = _randn(gen, (2 * Hk + Hv) * 128, 4, std=0.5)
+        w["dt_bias"] = _randn(gen, Hv * 128 if a.linear_per_channel else Hv, std=0.5)
+        w["a_log"] = _randn(gen, Hv, std=0.5)
+        w["lin_norm"] = torch.ones(128)
+        w["wo"] = _randn(gen, h, Hv * 128, std=s)
     else:
         w["wq"] = _randn(gen, a.n_heads * a.head_dim, h, std=s)
         w["wk"] = _randn(gen, a.n_kv_heads * a.head_dim, h, std=s)
@@ -100,6 +109,8 @@ class RefCache:
     def truncate(self, length: int):
         """Drop cached rows at position >= length (rejected speculative rows)."""
         for key, (k, v, p) in list(self.layers.items()):
+            if isinstance(key, tuple) and key[0] == "lin":
+                raise NotImplementedError("rows of a linear-attention layer cannot be dropped: the recurrent state has absorbed them")
             keep = p < length
             self.layers[key] = (k[keep], v[keep], p[keep])
 
@@ -150,6 +161,8 @@ class RefModel:
                     allowed = ops.topk_mask(ops.index_scores(q_idx, w_idx, k_idx, pos, kpos), a.index_topk)
             o = ops.attention(q, k, kvb[..., nope:], pos, kpos, scale=1.0 / math.sqrt(nope + rope), allowed=allowed)
             o = o.reshape(T, a.n_heads * dv)
+        elif "w_qkvz" in lw:
+            o = self.linear_attention(lw, xn, cache, key)
         else:
             q = (xn @ lw["wq"].T).reshape(T, a.n_heads, a.head_dim)
             k = (xn @ lw["wk"].T).reshape(T, a.n_kv_heads, a.head_dim)
@@ -164,6 +177,40 @@ class RefModel:
             k, v, kpos = cache.append(key, k, v, pos)
             o = ops.attention(q, k, v, pos, kpos, window=spec.layer_window(li), sink=lw.get("sink")).reshape(T, -1)
         return x + self._aq(o, "dense") @ lw["wo"].T
+
+    def linear_attention(self, lw: dict, xn: torch.Tensor, cache: RefCache, key) -> torch.Tensor:
+        """Gated delta-rule layer (GDN: decay per head; KDA: per key channel): projections -> width-4 causal convolution + SiLU over
+        q / k / v -> L2-normalised q (scaled by dk^-1/2) and k -> recurrence over the sequence's carried state -> RMSNorm gated by
+        silu(z).  The state and the convolution's last three inputs live in the cache entry ("lin", key).  Intermediate tensors are
+        rounded to bf16 where the device path stores them in bf16."""
+        a = self.spec.attn
+        Hk, Hv, T = a.linear_k_heads, a.linear_v_heads, xn.shape[0]
+        b16 = lambda t: t.to(torch.bfloat16).float()
+        qkvz = b16(xn @ lw["w_qkvz"].T)
+        ba = xn @ lw["w_ba"].T
+        C = (2 * Hk + Hv) * 128
+        st = cache.layers.get(("lin", key))
+        state, carry = (st[0], st[1]) if st is not None else (None, None)
+        conv, carry = ops.short_conv4(qkvz[:, :C], lw["conv_w"], carry)
+        conv = b16(conv)
+        q = conv[:, :Hk * 128].reshape(T, Hk, 128)
+        k = conv[:, Hk * 128:2 * Hk * 128].reshape(T, Hk, 128)
+        v = conv[:, 2 * Hk * 128:].reshape(T, Hv, 128)
+        z = qkvz[:, C:].reshape(T, Hv, 128)
+        rep = Hv // Hk
+        qn = torch.nn.functional.normalize(q, dim=-1, eps=1e-6) * 128 ** -0.5
+        kn = torch.nn.functional.normalize(k, dim=-1, eps=1e-6)
+        qe, ke = b16(qn.repeat_interleave(rep, 1)), b16(kn.repeat_interleave(rep, 1))
+        beta = torch.sigmoid(ba[:, :Hv])
+        if a.linear_per_channel:
+            g = torch.exp(-torch.exp(lw["a_log"])[None, :, None] * torch.nn.functional.softplus(ba[:, Hv:].reshape(T, Hv, 128) + lw["dt_bias"].reshape(Hv, 128)))
+        else:
+            g = torch.exp(-torch.exp(lw["a_log"])[None, :] * torch.nn.functional.softplus(ba[:, Hv:2 * Hv] + lw["dt_bias"]))
+        o, state, _ = ops.gated_delta_rule(qe, ke, v, g, beta, state)
+        cache.layers[("lin", key)] = (state, b16(carry), torch.zeros(0))
+        o = b16(o)
+        o = ops.rmsnorm(o, lw["lin_norm"], self.spec.rms_eps) * torch.nn.functional.silu(z)
+        return b16(o).reshape(T, Hv * 128)
 
     def ffn_block(self, lw: dict, x: torch.Tensor, routes_out: list | None = None) -> torch.Tensor:
         m, spec = self.spec.moe, self.spec

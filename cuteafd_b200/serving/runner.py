@@ -63,6 +63,11 @@ class EngineRunner:
         # MTP drafter pairs with the next tokens (serving.mtp_drafter)
         self.keep_hidden = False
         self.records: dict = {}
+        # hybrid stacks (linear-attention layers): every live sequence owns one recurrent-state slot of the engine
+        self._recurrent = bool(getattr(engine, "lin_layers", None))
+        self._state_slot: dict = {}
+        self._state_pos: dict = {}
+        self._free_slots = list(range(getattr(engine, "max_seqs", 0)))[::-1] if self._recurrent else []
         self._tok_host = torch.zeros(max(64, max_rows), dtype=torch.int32)
         if torch.cuda.is_available():
             self._tok_host = self._tok_host.pin_memory()
@@ -70,6 +75,33 @@ class EngineRunner:
     @property
     def max_rows(self) -> int:
         return self._max_rows
+
+    def forget(self, state):
+        """The scheduler finished this sequence: its recurrent-state slot and hidden records are free again."""
+        slot = self._state_slot.pop(id(state), None)
+        self._state_pos.pop(id(state), None)
+        if slot is not None:
+            self._free_slots.append(slot)
+        self.records.pop(id(state), None)
+
+    def _slots_of(self, rows: list[Row]) -> list[int]:
+        out, fresh = [], []
+        for r in rows:
+            slot = self._state_slot.get(id(r.state))
+            if slot is None or r.start_pos == 0:
+                if slot is None:
+                    if r.start_pos != 0:
+                        raise RuntimeError("a linear-attention stack cannot resume a sequence from cached pages: run it without the prefix cache")
+                    if not self._free_slots:
+                        raise RuntimeError("more live sequences than recurrent-state slots (engine max_seqs)")
+                    slot = self._state_slot[id(r.state)] = self._free_slots.pop()
+                fresh.append(slot)
+            elif r.start_pos != self._state_pos.get(id(r.state)):      # a rejected draft would need the state of an earlier position
+                raise RuntimeError("a linear-attention stack cannot step back: run it without speculation")
+            self._state_pos[id(r.state)] = r.start_pos + len(r.tokens)
+            out.append(slot)
+        self.eng.reset_state_slots(fresh)
+        return out
 
     def run(self, rows: list[Row]) -> list[list[int]]:
         from ..engine.engine import StepShape
@@ -89,7 +121,8 @@ class EngineRunner:
             kv_len.append(r.start_pos + n)
             q_len.append(n)
             pages.append(seq.pages)
-        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages)
+        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages,
+                                         **({"state_slots": self._slots_of(rows)} if self._recurrent else {}))
         max_q = max(q_len)
         decode_like = max_q <= 8
         # regular decode / verify rounds (every sequence the same number of rows, logits for every row or none) may be cut into

@@ -307,6 +307,9 @@ class Scheduler:
             self.prefix.release(st.seq)
         else:
             st.seq.release(self.pool)
+        forget = getattr(self.runner, "forget", None)
+        if forget is not None:
+            forget(st)
         self.stats["finished"] += 1
         self.recent.append({"rid": st.req.rid, "prompt": len(st.req.prompt), "generated": len(st.out), "cache_hit": st.cache_hit, "reason": reason})
         self._event("finish", rid=st.req.rid, reason=reason, generated=len(st.out))

@@ -66,7 +66,7 @@ def test_short_conv4_carries_its_history():
         xd = b16(x).to(DEV)
         y = torch.zeros(x.shape[0], C, dtype=torch.bfloat16, device=DEV)
         d_slot, d_start, d_len = i32([1]), i32([0]), i32([x.shape[0]])
-        call("cuteafd_short_conv4", ptr(xd), ptr(wd), ptr(carry), ptr(d_slot), ptr(d_start), ptr(d_len), ptr(y), 1, C, n_slots, ptr(status), stream())
+        call("cuteafd_short_conv4", ptr(xd), ptr(wd), ptr(carry), ptr(d_slot), ptr(d_start), ptr(d_len), ptr(y), 1, C, C, n_slots, ptr(status), stream())
         torch.cuda.synchronize()
         assert status.tolist() == [0, 0, 0, 0]
         assert float((y.float().cpu() - want).abs().max()) < 2e-2

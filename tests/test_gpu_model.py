@@ -107,3 +107,50 @@ def test_engine_passes_golden_windows(tmp_path):
     assert rep["pass"], rep
     other = Engine(DeviceWeights.from_masters(spec, init_weights(spec, 3), DEV), n_pages=16, max_seqs=4, max_pages_per_seq=4)
     assert not check_logits(engine_logits_fn(other), gold, spec=spec)["pass"]
+
+
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_hybrid_linear_attention_stack_matches_oracle(per_channel):
+    """Hybrid stack: layers 0, 2 are gated delta-rule layers (GDN: decay per head; KDA: per key channel), layers 1, 3 full GQA.  The
+    prompts are ingested in chunks (the recurrent state and the convolution history cross the chunk boundary), then decoded."""
+    import dataclasses
+    base = tiny_spec()
+    spec = base.replace(n_layers=4, attn=dataclasses.replace(base.attn, n_heads=4, n_kv_heads=2, head_dim=128, linear_every=2, linear_k_heads=1,
+                                                             linear_v_heads=2, linear_per_channel=per_channel))
+    assert [spec.layer_is_linear(i) for i in range(4)] == [True, False, True, False]
+    masters = init_weights(spec, 5)
+    dw = DeviceWeights.from_masters(spec, masters, DEV)
+    eng = Engine(dw, n_pages=32, max_seqs=8, max_pages_per_seq=4)
+    ref = RefModel(spec, dw.dequantized_masters())
+    prompts = _prompts(spec, 3, 50)
+    gen = BatchGenerator(eng, prefill_chunk=32)
+    gen.prefill(prompts)
+    torch.cuda.synchronize()
+    eng.check_status()
+    gen.release()
+    gen = BatchGenerator(eng)            # whole prompts in one step: logits of every prompt's last row sit in one lane
+    gen.prefill(prompts)
+    lane = eng.lane(150)
+    torch.cuda.synchronize()
+    eng.check_status()
+    for i, p in enumerate(prompts):
+        rl, _ = ref.forward(torch.tensor(p), 0, RefCache())
+        got = lane.logits[i].float().cpu()
+        err = float((got - rl[-1]).norm() / rl[-1].norm())
+        assert err < 0.05, f"prompt {i}: logits rel err {err}"
+    gen.release()
+    for chunk in (4096, 32):             # chunked prefill must reach the same tokens as whole-prompt prefill
+        g = BatchGenerator(eng, prefill_chunk=chunk)
+        g.prefill(prompts)
+        out = [[t] for t in g.last]
+        for _ in range(9):
+            for o, t in zip(out, g.decode_step(use_graph=(chunk == 32))):
+                o.append(t)
+        g.release()
+        for i, p in enumerate(prompts):
+            want, rows = ref.generate_greedy(torch.tensor(p), 10)
+            for j, (a, b) in enumerate(zip(out[i], want)):
+                if a != b:
+                    top2 = rows[j].topk(2).values
+                    assert float(top2[0] - top2[1]) < 0.05, f"chunk {chunk} prompt {i} step {j}: {a} != {b}"
+                    break
