@@ -227,7 +227,10 @@ class Scheduler:
         plan = []
         for st in states:
             drafts = []
-            if self.drafter is not None and st.req.allow_drafts and st.req.sampling.greedy and st.req.constraint is None:
+            # Sampled requests verify too: every verify row is sampled with the (seed, position) generator, and a draft is accepted
+            # when it equals its row's sample.  With deterministic proposals that is exact speculative sampling - P(accept) = p(draft),
+            # and a rejection emits a sample of p given "not the draft" - and it reproduces the undrafted token stream.
+            if self.drafter is not None and st.req.allow_drafts and st.req.constraint is None:
                 width = self.policy.width(st.req.rid, budget - (len(states) - len(plan)))
                 room = st.req.max_tokens - len(st.out) - 1
                 if width > 0 and room > 0:

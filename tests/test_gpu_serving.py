@@ -64,6 +64,22 @@ def test_sampling_depends_only_on_seed_and_position():
     assert c[0] != a[0]
 
 
+def test_sampled_requests_are_drafted_and_verified_losslessly():
+    """Sampled verification: a sampling request with the n-gram drafter yields the token stream of the same request without drafts
+    (verify rows are sampled with the (seed, position) generator; a draft is accepted when it equals its row's sample)."""
+    sp = SamplingParams(temperature=0.4, top_p=0.95, top_k=40, seed=12)
+    g = torch.Generator().manual_seed(3)
+    spec = tiny_spec()
+    base = torch.randint(0, spec.vocab, (12,), generator=g).tolist()
+    prompts = [base * 4, base[:7] * 6]
+    _, _, plain, _ = build(prefix=False)
+    want = run_requests(plain, prompts, 24, sampling=sp)
+    _, _, sched, _ = build(drafter=NgramDrafter(), prefix=False)
+    got = run_requests(sched, prompts, 24, sampling=sp)
+    assert got == want
+    assert sched.stats["drafted"] > 0
+
+
 def test_scheduler_with_mtp_drafter_is_lossless():
     """The model's own MTP module drafts inside the serving loop (chunked prefill, several sequences): the output must
     equal plain greedy generation, and drafts must have been proposed and verified."""

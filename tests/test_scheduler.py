@@ -61,6 +61,30 @@ def test_speculation_is_lossless_and_accepts_repetitive_text():
     assert spec.stats["accepted"] > 0 and spec.stats["steps"] < base.stats["steps"]
 
 
+def test_sampling_requests_draft_too_and_keep_their_token_stream():
+    """A sampling request is drafted and verified (a draft is accepted when it equals its row's sample); a request with a grammar
+    constraint is not."""
+    from cuteafd_b200.ref.sampler import SamplingParams
+    sp = SamplingParams(temperature=0.8, top_p=0.9, top_k=50, seed=4)
+    base, r0, _ = make()
+    spec, r1, _ = make(drafter=NgramDrafter(), policy=SimpleDraftPolicy(3))
+    r0.next_token = r1.next_token = lambda prefix: (prefix[-1] * 7 + 3) % 11      # stands for "the sample at this position"
+    a, b = {}, {}
+    base.submit(Request("x", [1, 2, 3, 4, 5], max_tokens=30, on_token=collect(a, "x"), sampling=sp))
+    spec.submit(Request("x", [1, 2, 3, 4, 5], max_tokens=30, on_token=collect(b, "x"), sampling=sp))
+    base.run_until_idle(), spec.run_until_idle()
+    assert a["x"]["tokens"] == b["x"]["tokens"] and spec.stats["accepted"] > 0
+
+    class Anything:
+        def mask(self, prefix):
+            return None
+    spec2, r2, _ = make(drafter=NgramDrafter(), policy=SimpleDraftPolicy(3))
+    r2.next_token = r0.next_token
+    spec2.submit(Request("y", [1, 2, 3, 4, 5], max_tokens=12, on_token=collect({}, "y"), constraint=Anything()))
+    spec2.run_until_idle()
+    assert spec2.stats["drafted"] == 0
+
+
 def test_prefix_cache_restores_exactly_and_skips_recompute():
     pool = PagePool(64)
     runner = FakeRunner()
