@@ -168,9 +168,13 @@ class EngineRunner:
         logits = lane.logits[off:off + k]
         mask = None
         if st.req.constraint is not None:
-            m = st.req.constraint.mask(st.tokens)
-            if m is not None:
-                mask = m.to(logits.device).view(1, -1).expand(k, -1).contiguous()
+            # one mask per row: row i follows the sequence's history plus the step's inputs up to i (drafts included)
+            history = st.tokens[:r.start_pos]
+            ms = [st.req.constraint.mask(history + list(r.tokens[:i + 1])) for i in r.want_logits]
+            if any(m is not None for m in ms):
+                ref = next(m for m in ms if m is not None)
+                ms = [m if m is not None else torch.full_like(ref, -1) for m in ms]
+                mask = torch.stack([m.view(-1) for m in ms]).to(logits.device).contiguous()
         p = st.req.sampling
         if p.greedy:
             ops.argmax_rows(logits, lane.next_tok[off:off + k], masks=mask, status=lane.tok_status[off:off + k])

@@ -230,7 +230,9 @@ class Scheduler:
             # Sampled requests verify too: every verify row is sampled with the (seed, position) generator, and a draft is accepted
             # when it equals its row's sample.  With deterministic proposals that is exact speculative sampling - P(accept) = p(draft),
             # and a rejection emits a sample of p given "not the draft" - and it reproduces the undrafted token stream.
-            if self.drafter is not None and st.req.allow_drafts and st.req.constraint is None:
+            # A grammar constraint masks every verify row with the state its own prefix (drafts included) leads to, so a draft the
+            # grammar forbids simply fails to match.
+            if self.drafter is not None and st.req.allow_drafts:
                 width = self.policy.width(st.req.rid, budget - (len(states) - len(plan)))
                 room = st.req.max_tokens - len(st.out) - 1
                 if width > 0 and room > 0:

@@ -62,8 +62,8 @@ def test_speculation_is_lossless_and_accepts_repetitive_text():
 
 
 def test_sampling_requests_draft_too_and_keep_their_token_stream():
-    """A sampling request is drafted and verified (a draft is accepted when it equals its row's sample); a request with a grammar
-    constraint is not."""
+    """A sampling request is drafted and verified (a draft is accepted when it equals its row's sample), and so is a request with a
+    grammar constraint."""
     from cuteafd_b200.ref.sampler import SamplingParams
     sp = SamplingParams(temperature=0.8, top_p=0.9, top_k=50, seed=4)
     base, r0, _ = make()
@@ -75,14 +75,24 @@ def test_sampling_requests_draft_too_and_keep_their_token_stream():
     base.run_until_idle(), spec.run_until_idle()
     assert a["x"]["tokens"] == b["x"]["tokens"] and spec.stats["accepted"] > 0
 
-    class Anything:
+    # with a grammar constraint every verify row is masked by the state of ITS prefix: drafted and undrafted streams agree
+    import torch
+
+    class NoSixAfterEven:
         def mask(self, prefix):
-            return None
+            words = torch.full((1000 // 32 + 1,), -1, dtype=torch.int32)
+            if prefix[-1] % 2 == 0:
+                words[0] &= ~(1 << 6)
+            return words
+    c, d = {}, {}
+    base2, r3, _ = make()
     spec2, r2, _ = make(drafter=NgramDrafter(), policy=SimpleDraftPolicy(3))
-    r2.next_token = r0.next_token
-    spec2.submit(Request("y", [1, 2, 3, 4, 5], max_tokens=12, on_token=collect({}, "y"), constraint=Anything()))
-    spec2.run_until_idle()
-    assert spec2.stats["drafted"] == 0
+    r2.next_token = r3.next_token = r0.next_token
+    base2.submit(Request("y", [1, 2, 3, 4, 5], max_tokens=30, on_token=collect(c, "y"), constraint=NoSixAfterEven()))
+    spec2.submit(Request("y", [1, 2, 3, 4, 5], max_tokens=30, on_token=collect(d, "y"), constraint=NoSixAfterEven()))
+    base2.run_until_idle(), spec2.run_until_idle()
+    assert c["y"]["tokens"] == d["y"]["tokens"] and spec2.stats["drafted"] > 0
+    assert all(not (a % 2 == 0 and b == 6) for a, b in zip(c["y"]["tokens"], c["y"]["tokens"][1:]))
 
 
 def test_prefix_cache_restores_exactly_and_skips_recompute():
