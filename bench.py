@@ -157,6 +157,7 @@ def main():
                     help="deepseek-v3-plain: one-token-per-step decode of the DeepSeek-V3 shape through the generic path (any --layout; no drafter)")
     ap.add_argument("--ttft-prompt", type=int, default=32768); ap.add_argument("--ttft-shared", type=int, default=28672)
     ap.add_argument("--ttft-sessions", type=int, default=8); ap.add_argument("--ttft-decode", type=int, default=256)
+    ap.add_argument("--hyper-streams", type=int, default=0, help="1 GPU: run the shape with this many residual streams (hyper-connections; 4)")
     ap.add_argument("--batch-per-gpu", type=int, default=16)
     ap.add_argument("--batch-total", type=int, default=0, help="fixed global batch instead of a per-GPU batch (DeepSeek-V3 decode: 1 or 64)")
     ap.add_argument("--context", type=int, default=4096)

@@ -46,6 +46,8 @@ def run_decode_bench(args, rank: int, world: int, local: int, clocks) -> dict:
         spec = hybrid_gdn_spec(args.layers or 48, per_channel=args.config.startswith("hybrid-kda"))
     else:
         spec = qwen3_235b_spec(args.layers or 94)
+    if getattr(args, "hyper_streams", 0):          # the same shape with four residual streams (hyper-connections), single GPU
+        spec = spec.replace(hyper_streams=args.hyper_streams, name=spec.name + f"+mhc{args.hyper_streams}")
     batch = getattr(args, "batch_total", 0) or args.batch_per_gpu * world
     if world > 1:
         from ..parallel.runner import run_decode_bench_distributed

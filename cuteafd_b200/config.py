@@ -110,6 +110,10 @@ class ModelSpec:
     moe: MoESpec = field(default_factory=MoESpec)
     quant: QuantSpec = field(default_factory=QuantSpec)
     mtp_layers: int = 0             # native next-n (MTP) draft layers
+    # Hyper-connections (the V4 line): 0 = one residual stream; 4 = four streams mixed at every sub-layer boundary by per-token
+    # coefficients (collapse weights, spread weights and a Sinkhorn-normalised 4 x 4 stream mix from 24 projections of the row)
+    hyper_streams: int = 0
+    hyper_sinkhorn_iters: int = 20
     init_std: float = 0.02
     tie_embeddings: bool = False
     max_context: int = 1 << 20

@@ -101,6 +101,10 @@ class Lane:
             self.y2 = bf(rows, H)
         if a.linear_every:
             self.lin_buf(eng)
+        if spec.hyper_streams:       # hyper-connections: the residual streams, the open sub-layer's output and its spread / mix coefficients
+            self.res = bf(cap, spec.hyper_streams, H)
+            self.sub = bf(cap, H)
+            self.hc_coef = torch.zeros(cap, 20, dtype=torch.float32, device=dev)
 
     def lin_buf(self, eng) -> dict:
         """Buffers of the linear-attention layers of a hybrid stack."""
@@ -156,6 +160,10 @@ class Engine:
             self.kv_tmaps = ops.encode_kv_tmaps(self.kv) if a.head_dim == 128 and 128 % (a.n_heads // a.n_kv_heads) == 0 else None
         else:
             self._alloc_attention_state()
+        if spec.hyper_streams:
+            if spec.hyper_streams != 4 or a.kind != "gqa" or weights.hc_head is None or weights.mtp:
+                raise NotImplementedError("hyper-connections: four streams, on the single-GPU GQA engine, without an MTP module")
+        self._hc_pending = None
         # hybrid stacks: gated delta-rule layers keep a recurrent state and the last three convolution inputs per sequence slot
         self.lin_layers = [i for i in range(spec.n_layers) if spec.layer_is_linear(i)]
         if self.lin_layers:
@@ -270,11 +278,16 @@ class Engine:
 
     def _attn_in_gs(self, lw: LayerWeights):
         """Activation global scale of the first projection of the attention block (NVFP4)."""
-        return lw.wqkv.inv_act_gs
+        return (lw.wqkv if lw.wqkv is not None else lw.lin_qkvz).inv_act_gs
 
     def _norm_in(self, lw: LayerWeights, L: Lane, T: int) -> ActBuffer:
         """Input of the attention block: RMSNorm of the residual stream as the GEMM operand (bf16 or FP4, quantised in
         the same launch) - unless the previous layer's combine already produced it."""
+        if self.spec.hyper_streams:
+            self._hc_boundary(L, T, lw.hc_attn, lw.attn_norm)
+            if L.xq.kind != KIND_BF16:
+                self._quant(L.xn, L.xq, T, None if L.xq.kind == KIND_FP8B else self._attn_in_gs(lw))
+            return L.xq
         if self._pre_normed:
             self._pre_normed = False
             return L.xq
@@ -290,6 +303,9 @@ class Engine:
         """Weighted top-k sum + shared expert + residual; when another layer follows, its input norm (and FP4
         quantisation) rides in the same launch.  `wait`: the kernel first waits for the peers that deliver `y`."""
         nxt = self._next_lw
+        if self.spec.hyper_streams:       # the block's output stays apart: the next boundary spreads it over the streams
+            ops.moe_combine(y, rows, wts, shared, None, L.sub, T, k, wait=wait)
+            return
         if nxt is None:
             ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, wait=wait)
             return
@@ -367,6 +383,10 @@ class Engine:
     def _ffn_norm(self, lw: LayerWeights, L: Lane, T: int):
         """RMSNorm in front of the FFN block -> L.xn (router, dispatch and gather read bf16 rows); when a dense or shared expert
         with FP8 operands follows, its quantised input is written by the same launch."""
+        if self.spec.hyper_streams:
+            self._hc_boundary(L, T, lw.hc_ffn, lw.ffn_norm)
+            self._ffn_in_quantised = False
+            return
         fuse = L.xq.kind == KIND_FP8B and self.spec.hidden % 256 == 0 and lw.ws_gate is not None and lw.ws_gate.kind == KIND_FP8B
         ops.add_rmsnorm(L.x, None, lw.ffn_norm, L.xn, self.spec.rms_eps, rows=T, quant=L.xq if fuse else None)
         self._ffn_in_quantised = fuse
@@ -374,7 +394,23 @@ class Engine:
 
     def _attn_out(self, li: int, lw: LayerWeights, oq: ActBuffer, L: Lane, T: int):
         """Output projection + residual (a tensor-parallel rank overrides this with partial sum + exchange)."""
+        if self.spec.hyper_streams:
+            self._dense(lw.wo, oq, L.sub, T)
+            return
         self._dense(lw.wo, oq, L.x, T, residual=L.x)
+
+    def _hc_boundary(self, L: Lane, T: int, hc: tuple, norm_w: torch.Tensor, head: bool = False):
+        """Hyper-connections, one launch per sub-layer boundary: close the open sub-layer (spread its output over the four residual
+        streams, mix the streams), open the next one (coefficients from 24 projections of the row) and hand its collapsed, normalised
+        input to L.xn.  The step's first boundary spreads the embedding; the head's boundary has collapse weights only and also
+        leaves the un-normalised hidden rows in L.x."""
+        fn, scale, base = hc
+        init = self._hc_pending == "init"
+        native.call("cuteafd_mhc_boundary", ptr(L.res), ptr(L.x if init else L.sub), None if init else ptr(L.hc_coef), ptr(fn), ptr(scale), ptr(base),
+                    ptr(norm_w), ptr(L.x) if head else None, ptr(L.xn), None if head else ptr(L.hc_coef), T, self.spec.hidden, 4 if head else 24,
+                    1 if init else 0, self.spec.hyper_sinkhorn_iters, self.spec.rms_eps, native.stream())
+        self._hc_pending = "sub"
+        self.launches_per_step += 1
 
     def _ffn(self, lw: LayerWeights, L: Lane, T: int, out, residual):
         """Shared expert / dense FFN: out = residual + down(silu(gate x) * up x)."""
@@ -405,7 +441,10 @@ class Engine:
         spec, m = self.spec, self.spec.moe
         self._ffn_norm(lw, L, T)
         if lw.router is None:
-            self._ffn(lw, L, T, L.x, L.x)
+            if self.spec.hyper_streams:
+                self._ffn(lw, L, T, L.sub, None)
+            else:
+                self._ffn(lw, L, T, L.x, L.x)
             return
         if T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1":
             ops.router_logits(L.xn, lw.router, L.router_logits, T)         # decode / verify: SIMT dot products, one block per expert
@@ -468,6 +507,7 @@ class Engine:
         self._pre_normed = False
         ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
         self.launches_per_step += 1
+        self._hc_pending = "init" if spec.hyper_streams else None
         import contextlib
         from ..utils.trace import nvtx
         timed = self.layer_clock is not None and not torch.cuda.is_current_stream_capturing()
@@ -479,9 +519,14 @@ class Engine:
                 if self._l2_prefetch and self._next_lw is not None and getattr(self._next_lw, "wqkv", None) is not None:
                     ops.l2_prefetch(self._next_lw.wqkv.data)       # the next layer's first weights ride into L2 under this layer's experts
                 self._moe_layer(lw, L, T)
+        if spec.hyper_streams:      # close the last block, collapse the streams for the head: hidden rows -> L.x, normalised -> L.xn
+            self._hc_boundary(L, T, self.weights.hc_head, self.weights.final_norm, head=True)
         if sh.n_logits:
-            ops.gather_rows(L.x, self.md["logit_rows"], None, L.xl, sh.n_logits)
-            ops.add_rmsnorm(L.xl, None, self.weights.final_norm, L.xln, spec.rms_eps, rows=sh.n_logits)
+            if spec.hyper_streams:
+                ops.gather_rows(L.xn, self.md["logit_rows"], None, L.xln, sh.n_logits)
+            else:
+                ops.gather_rows(L.x, self.md["logit_rows"], None, L.xl, sh.n_logits)
+                ops.add_rmsnorm(L.xl, None, self.weights.final_norm, L.xln, spec.rms_eps, rows=sh.n_logits)
             ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=sh.n_logits, status=self.status)
             ops.argmax_rows(L.logits, L.next_tok, rows=sh.n_logits, status=L.tok_status)
             self.launches_per_step += 4

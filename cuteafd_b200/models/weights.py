@@ -57,6 +57,9 @@ class LayerWeights:
     lin_dt_bias: torch.Tensor | None = None
     lin_a_log: torch.Tensor | None = None
     lin_norm: torch.Tensor | None = None
+    # hyper-connections: (fn [24, 4H] fp32, scale [3], base [24]) of the boundary in front of the attention and of the FFN block
+    hc_attn: tuple | None = None
+    hc_ffn: tuple | None = None
 
     def nbytes(self) -> int:
         n = 0
@@ -65,6 +68,8 @@ class LayerWeights:
                 n += v.nbytes
             elif isinstance(v, torch.Tensor):
                 n += v.numel() * v.element_size()
+            elif isinstance(v, tuple):
+                n += sum(t.numel() * t.element_size() for t in v)
         return n
 
 
@@ -78,6 +83,7 @@ class DeviceWeights:
     layer_map: list = field(default_factory=list)  # layer index -> index into `layers`
     mtp: list = field(default_factory=list)        # [(enorm, hnorm, eh_proj TcWeight, LayerWeights, norm)]
     act_gs: float = 1.0 / 64
+    hc_head: tuple | None = None                   # hyper-connections: (fn [4, 4H], scale [3], base [4]) of the head's collapse
 
     def layer(self, i: int) -> LayerWeights:
         return self.layers[self.layer_map[i]]
@@ -104,6 +110,9 @@ class DeviceWeights:
                 out = LayerWeights(attn_norm=f32(lw["attn_norm"]), ffn_norm=f32(lw["ffn_norm"]),
                                    wqkv=TcWeight.from_master(wqkv, dk, device, act_gs),
                                    wo=TcWeight.from_master(lw["wo"], dk, device, act_gs))
+            if "hc_attn_fn" in lw:
+                out.hc_attn = tuple(f32(lw[f"hc_attn_{k}"]) for k in ("fn", "scale", "base"))
+                out.hc_ffn = tuple(f32(lw[f"hc_ffn_{k}"]) for k in ("fn", "scale", "base"))
             if "q_norm" in lw:
                 out.q_norm, out.k_norm = f32(lw["q_norm"]), f32(lw["k_norm"])
             if "sink" in lw:
@@ -131,6 +140,8 @@ class DeviceWeights:
                            lm_head=TcWeight.from_master(masters["lm_head"], "bf16", device), act_gs=act_gs)
         dw.layers = [layer_from(lw) for lw in masters["layers"]]
         dw.layer_map = list(range(spec.n_layers))
+        if "hc_head_fn" in masters:
+            dw.hc_head = tuple(f32(masters[f"hc_head_{k}"]) for k in ("fn", "scale", "base"))
         for mw in masters.get("mtp", []):
             dw.mtp.append((f32(mw["enorm"]), f32(mw["hnorm"]), TcWeight.from_master(mw["eh_proj"], "bf16", device),
                            layer_from(mw["layer"]), f32(mw["norm"])))
@@ -150,6 +161,9 @@ class DeviceWeights:
                 qkv = l.wqkv.dequantize()[0]
                 d = {"attn_norm": l.attn_norm.cpu(), "ffn_norm": l.ffn_norm.cpu(), "wq": qkv[:nq], "wk": qkv[nq:nq + nk],
                      "wv": qkv[nq + nk:], "wo": l.wo.dequantize()[0]}
+            if l.hc_attn is not None:
+                for blk, t in (("attn", l.hc_attn), ("ffn", l.hc_ffn)):
+                    d[f"hc_{blk}_fn"], d[f"hc_{blk}_scale"], d[f"hc_{blk}_base"] = (x.cpu() for x in t)
             if l.q_norm is not None:
                 d["q_norm"], d["k_norm"] = l.q_norm.cpu(), l.k_norm.cpu()
             if l.sink is not None:
@@ -167,6 +181,8 @@ class DeviceWeights:
 
         m = {"embed": self.embed.float().cpu(), "final_norm": self.final_norm.cpu(), "lm_head": self.lm_head.dequantize()[0],
              "layers": [layer_to(self.layer(i)) for i in range(spec.n_layers)]}
+        if self.hc_head is not None:
+            m["hc_head_fn"], m["hc_head_scale"], m["hc_head_base"] = (x.cpu() for x in self.hc_head)
         if self.mtp:
             m["mtp"] = [{"enorm": e.cpu(), "hnorm": h.cpu(), "eh_proj": p.dequantize()[0], "layer": layer_to(l), "norm": n.cpu()}
                         for e, h, p, l, n in self.mtp]
@@ -204,6 +220,12 @@ class DeviceWeights:
                 out = LayerWeights(attn_norm=ones(h), ffn_norm=ones(h),
                                    wqkv=R(1, (a.n_heads + 2 * a.n_kv_heads) * a.head_dim, h, dk, 0) if with_attention else None,
                                    wo=R(1, h, a.n_heads * a.head_dim, dk, 1) if with_attention else None)
+            if spec.hyper_streams and with_attention:
+                S = spec.hyper_streams
+                gh = torch.Generator(device=device).manual_seed(s + 11)
+                mk = lambda: (torch.empty(S * (S + 2), S * h, device=device).normal_(0, 2.0 / (S * h) ** 0.5, generator=gh),
+                              torch.full((3,), 0.5, device=device), torch.empty(S * (S + 2), device=device).normal_(0, 0.5, generator=gh))
+                out.hc_attn, out.hc_ffn = mk(), mk()
             if not with_attention:      # expert rank: routed experts only
                 if spec.is_moe_layer(i) and e_hi > e_lo:
                     out.w_gate, out.w_up, out.w_down = RE(m.intermediate, h, 3), RE(m.intermediate, h, 4), RE(h, m.intermediate, 5)
@@ -233,4 +255,8 @@ class DeviceWeights:
         dw = DeviceWeights(spec=spec, embed=embed, final_norm=ones(h), lm_head=head, act_gs=act_gs)
         dw.layers = [make_layer(i) for i in range(n_sets)]
         dw.layer_map = [i % n_sets for i in range(spec.n_layers)]
+        if spec.hyper_streams and with_attention:
+            S = spec.hyper_streams
+            dw.hc_head = (torch.empty(S, S * h, device=device).normal_(0, 2.0 / (S * h) ** 0.5, generator=gen), torch.full((3,), 0.5, device=device),
+                          torch.empty(S, device=device).normal_(0, 0.5, generator=gen))
         return dw

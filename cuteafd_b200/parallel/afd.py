@@ -153,6 +153,8 @@ class AttnRankEngine(Engine):
         dep = plan.dep
         self.full_spec, self.plan, self.dep, self.rank, self.comm, self.block = spec, plan, dep, rank, comm, block
         self.tp, self.tp_rank = dep.tp, dep.attn_ranks.index(rank) % dep.tp
+        if spec.hyper_streams:
+            raise NotImplementedError("hyper-connections run on the single-GPU engine (the lanes carry one residual stream)")
         if self.tp > 1 and spec.attn.linear_every:
             raise NotImplementedError("hybrid stacks with linear-attention layers run with attention TP 1 (data-parallel attention ranks)")
         self.group = dep.group_of(rank)

@@ -60,6 +60,12 @@ def init_layer(spec: ModelSpec, gen: torch.Generator, layer: int, force_dense: b
             w["k_norm"] = torch.ones(a.head_dim)
         if spec.layer_has_sink(layer):
             w["sink"] = _randn(gen, a.n_heads, std=1.0)
+    if spec.hyper_streams:
+        S = spec.hyper_streams
+        for blk in ("attn", "ffn"):        # projections wide enough to move the coefficients off their base values
+            w[f"hc_{blk}_fn"] = _randn(gen, S * (S + 2), S * h, std=2.0 / math.sqrt(S * h))
+            w[f"hc_{blk}_scale"] = torch.tensor([0.5, 0.5, 0.5])
+            w[f"hc_{blk}_base"] = _randn(gen, S * (S + 2), std=0.5)
     if spec.is_moe_layer(layer) and not force_dense:
         w["router"] = _randn(gen, m.n_experts, h, std=s)
         if m.use_bias:
@@ -86,6 +92,11 @@ def init_weights(spec: ModelSpec, seed: int = 0) -> dict:
          "layers": [init_layer(spec, gen, i) for i in range(spec.n_layers)],
          "final_norm": torch.ones(spec.hidden)}
     w["lm_head"] = w["embed"] if spec.tie_embeddings else _randn(gen, spec.vocab, spec.hidden, std=spec.init_std)
+    if spec.hyper_streams:
+        S = spec.hyper_streams
+        w["hc_head_fn"] = _randn(gen, S, S * spec.hidden, std=2.0 / math.sqrt(S * spec.hidden))
+        w["hc_head_scale"] = torch.tensor([0.5, 0.5, 0.5])
+        w["hc_head_base"] = _randn(gen, S, std=0.5)
     if spec.mtp_layers:
         w["mtp"] = [{"enorm": torch.ones(spec.hidden), "hnorm": torch.ones(spec.hidden),
                      "eh_proj": _randn(gen, spec.hidden, 2 * spec.hidden, std=spec.init_std),
@@ -128,7 +139,7 @@ class RefModel:
     def _aq(self, x, kind):
         return self.act_quant(x, kind) if self.act_quant else x
 
-    def attention_block(self, lw: dict, x: torch.Tensor, pos: torch.Tensor, cache: RefCache, key) -> torch.Tensor:
+    def attention_block(self, lw: dict, x: torch.Tensor, pos: torch.Tensor, cache: RefCache, key, add_residual: bool = True) -> torch.Tensor:
         a, spec = self.spec.attn, self.spec
         T = x.shape[0]
         xn = self._aq(ops.rmsnorm(x, lw["attn_norm"], spec.rms_eps), "dense")
@@ -176,7 +187,8 @@ class RefModel:
             k = ops.apply_rope(k, pos, theta, a.rope_interleaved)
             k, v, kpos = cache.append(key, k, v, pos)
             o = ops.attention(q, k, v, pos, kpos, window=spec.layer_window(li), sink=lw.get("sink")).reshape(T, -1)
-        return x + self._aq(o, "dense") @ lw["wo"].T
+        out = self._aq(o, "dense") @ lw["wo"].T
+        return x + out if add_residual else out
 
     def linear_attention(self, lw: dict, xn: torch.Tensor, cache: RefCache, key) -> torch.Tensor:
         """Gated delta-rule layer (GDN: decay per head; KDA: per key channel): projections -> width-4 causal convolution + SiLU over
@@ -212,7 +224,7 @@ class RefModel:
         o = ops.rmsnorm(o, lw["lin_norm"], self.spec.rms_eps) * torch.nn.functional.silu(z)
         return b16(o).reshape(T, Hv * 128)
 
-    def ffn_block(self, lw: dict, x: torch.Tensor, routes_out: list | None = None) -> torch.Tensor:
+    def ffn_block(self, lw: dict, x: torch.Tensor, routes_out: list | None = None, add_residual: bool = True) -> torch.Tensor:
         m, spec = self.spec.moe, self.spec
         xn = ops.rmsnorm(x, lw["ffn_norm"], spec.rms_eps)
         if "router" in lw:
@@ -225,16 +237,39 @@ class RefModel:
                 y = y + ops.expert_ffn(self._aq(xn, "dense"), lw["ws_gate"], lw["ws_up"], lw["ws_down"])
         else:
             y = ops.expert_ffn(self._aq(xn, "dense"), lw["wd_gate"], lw["wd_up"], lw["wd_down"])
-        return x + y
+        return x + y if add_residual else y
 
     # ---- passes ---------------------------------------------------------
     def hidden_states(self, tokens: torch.Tensor, start: int, cache: RefCache, routes_out=None) -> torch.Tensor:
         pos = torch.arange(start, start + tokens.numel())
         x = self.w["embed"][tokens.long()].float()
+        if self.spec.hyper_streams:
+            return self._hyper_hidden_states(x, pos, cache, routes_out)
         for i, lw in enumerate(self.w["layers"]):
             x = self.attention_block(lw, x, pos, cache, i)
             x = self.ffn_block(lw, x, routes_out)
         return x
+
+    def _hyper_hidden_states(self, x: torch.Tensor, pos: torch.Tensor, cache: RefCache, routes_out=None) -> torch.Tensor:
+        """The stack with hyper-connections: S residual streams, closed and re-opened around every sub-layer; the streams and the
+        sub-layer outputs are rounded to bf16 where the device stores them.  Returns the head's collapse of the streams."""
+        spec, S = self.spec, self.spec.hyper_streams
+        b16 = lambda t: t.to(torch.bfloat16).float()
+        res = b16(x)[:, None, :].expand(-1, S, -1).contiguous()
+        sub = post = comb = None
+        for i, lw in enumerate(self.w["layers"]):
+            for blk in ("attn", "ffn"):
+                if sub is not None:
+                    res = b16(ops.mhc_close(res, sub, post, comb))
+                pre, post, comb = ops.mhc_mixes(res, lw[f"hc_{blk}_fn"], lw[f"hc_{blk}_scale"], lw[f"hc_{blk}_base"], spec.hyper_sinkhorn_iters)
+                y = (pre[:, :, None] * res).sum(1)
+                if blk == "attn":
+                    sub = b16(self.attention_block(lw, y, pos, cache, i, add_residual=False))
+                else:
+                    sub = b16(self.ffn_block(lw, y, routes_out, add_residual=False))
+        res = b16(ops.mhc_close(res, sub, post, comb))
+        pre, _, _ = ops.mhc_mixes(res, self.w["hc_head_fn"], self.w["hc_head_scale"], self.w["hc_head_base"])
+        return (pre[:, :, None] * res).sum(1)
 
     def logits_from_hidden(self, x: torch.Tensor) -> torch.Tensor:
         return ops.rmsnorm(x, self.w["final_norm"], self.spec.rms_eps).float() @ self.w["lm_head"].float().T

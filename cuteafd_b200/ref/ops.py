@@ -214,3 +214,29 @@ def short_conv4(x: torch.Tensor, w: torch.Tensor, carry: torch.Tensor | None = N
     hist = torch.cat([torch.zeros(3, C) if carry is None else carry.float(), x.float()])
     y = sum(hist[i:i + T] * w[:, i].float()[None, :] for i in range(4))
     return F.silu(y), hist[-3:]
+
+
+def mhc_mixes(res: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: torch.Tensor, iters: int = 20):
+    """Hyper-connection coefficients of one boundary.  res [T, S, H] (the residual streams), fn [P, S*H] with P = S*(S+2)
+    (collapse, spread and stream-mix projections) or P = S (collapse only), scale [3], base [P].
+    Returns (pre [T, S], post [T, S] | None, comb [T, S, S] | None); comb[t, s, d] is the weight of source stream s in
+    destination stream d, made doubly stochastic by `iters` Sinkhorn sweeps.
+    Reference: native/families/deepseek_v41/cuda/v41_hc.cu (mixes_kernel)."""
+    T, S, H = res.shape
+    flat = res.reshape(T, S * H).float()
+    proj = (flat @ fn.float().T) * torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + 1e-20)
+    pre = torch.sigmoid(proj[:, :S] * scale[0] + base[:S]) + 1e-6
+    if fn.shape[0] == S:
+        return pre, None, None
+    post = 2 * torch.sigmoid(proj[:, S:2 * S] * scale[1] + base[S:2 * S])
+    c = torch.softmax((proj[:, 2 * S:] * scale[2] + base[2 * S:]).reshape(T, S, S), -1) + 1e-6
+    c = c / (c.sum(1, keepdim=True) + 1e-6)
+    for _ in range(iters - 1):
+        c = c / (c.sum(2, keepdim=True) + 1e-6)
+        c = c / (c.sum(1, keepdim=True) + 1e-6)
+    return pre, post, c
+
+
+def mhc_close(res: torch.Tensor, sub: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+    """res'[t, d] = post[t, d] * sub[t] + sum_s comb[t, s, d] * res[t, s]."""
+    return post[:, :, None] * sub[:, None, :].float() + torch.einsum("tsd,tsh->tdh", comb, res.float())

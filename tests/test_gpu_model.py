@@ -154,3 +154,86 @@ def test_hybrid_linear_attention_stack_matches_oracle(per_channel):
                     top2 = rows[j].topk(2).values
                     assert float(top2[0] - top2[1]) < 0.05, f"chunk {chunk} prompt {i} step {j}: {a} != {b}"
                     break
+
+
+def test_mhc_boundary_kernel_matches_oracle():
+    """One hyper-connection boundary: spread the embedding (init), open; then close with a sub-layer output and re-open; then the head's
+    collapse.  Coefficients, streams and the normalised collapse against the fp32 oracle; one and two rows per CTA."""
+    from cuteafd_b200.ops import native
+    from cuteafd_b200.ops.native import ptr
+    from cuteafd_b200.ref import ops as rops
+    g = torch.Generator().manual_seed(0)
+    for T, H in ((5, 256), (600, 512), (3, 7168)):
+        W = 4 * H
+        emb = (torch.randn(T, H, generator=g) * 0.5).to(torch.bfloat16)
+        sub = (torch.randn(T, H, generator=g) * 0.3).to(torch.bfloat16)
+        fns = [torch.randn(24, W, generator=g) * (2.0 / W ** 0.5) for _ in range(2)] + [torch.randn(4, W, generator=g) * (2.0 / W ** 0.5)]
+        scale = torch.tensor([0.5, 0.7, 0.9])
+        bases = [torch.randn(24, generator=g) * 0.5, torch.randn(24, generator=g) * 0.5, torch.randn(4, generator=g) * 0.5]
+        nw = torch.rand(H, generator=g) + 0.5
+        d = lambda t: t.to(DEV).contiguous()
+        res, coef = torch.zeros(T, 4, H, dtype=torch.bfloat16, device=DEV), torch.zeros(T, 20, device=DEV)
+        y_raw, y_norm = torch.zeros(T, H, dtype=torch.bfloat16, device=DEV), torch.zeros(T, H, dtype=torch.bfloat16, device=DEV)
+        emb_d, sub_d, scale_d, nw_d = d(emb), d(sub), d(scale), d(nw)
+        fn_d, base_d = [d(f) for f in fns], [d(b) for b in bases]
+        b16 = lambda t: t.to(torch.bfloat16).float()
+
+        def check(r_want, pre, post, comb, n_proj):
+            y = (pre[:, :, None] * r_want).sum(1)
+            want = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + 1e-5) * nw
+            torch.cuda.synchronize()
+            assert torch.equal(res.float().cpu(), r_want) or float((res.float().cpu() - r_want).abs().max()) < 0.02
+            assert float((y_norm.float().cpu() - want).norm() / want.norm()) < 0.01
+            if n_proj == 24:
+                got = coef.cpu()
+                assert float((got[:, :4] - post).abs().max()) < 2e-3 and float((got[:, 4:].reshape(T, 4, 4) - comb).abs().max()) < 2e-3
+
+        # 1: init + open
+        native.call("cuteafd_mhc_boundary", ptr(res), ptr(emb_d), None, ptr(fn_d[0]), ptr(scale_d), ptr(base_d[0]), ptr(nw_d), None, ptr(y_norm), ptr(coef),
+                    T, H, 24, 1, 20, 1e-5, native.stream())
+        r0 = emb.float()[:, None, :].expand(-1, 4, -1).contiguous()
+        pre, post, comb = rops.mhc_mixes(r0, fns[0], scale, bases[0])
+        check(r0, pre, post, comb, 24)
+        # 2: close with `sub`, re-open
+        native.call("cuteafd_mhc_boundary", ptr(res), ptr(sub_d), ptr(coef), ptr(fn_d[1]), ptr(scale_d), ptr(base_d[1]), ptr(nw_d), None, ptr(y_norm), ptr(coef),
+                    T, H, 24, 0, 20, 1e-5, native.stream())
+        r1 = b16(rops.mhc_close(r0, sub.float(), post, comb))
+        pre, post, comb = rops.mhc_mixes(r1, fns[1], scale, bases[1])
+        check(r1, pre, post, comb, 24)
+        # 3: close, head collapse (4 projections), un-normalised rows too
+        native.call("cuteafd_mhc_boundary", ptr(res), ptr(sub_d), ptr(coef), ptr(fn_d[2]), ptr(scale_d), ptr(base_d[2]), ptr(nw_d), ptr(y_raw), ptr(y_norm), None,
+                    T, H, 4, 0, 20, 1e-5, native.stream())
+        r2 = b16(rops.mhc_close(r1, sub.float(), post, comb))
+        pre, _, _ = rops.mhc_mixes(r2, fns[2], scale, bases[2])
+        check(r2, pre, None, None, 4)
+        y = (pre[:, :, None] * r2).sum(1)
+        assert float((y_raw.float().cpu() - y).norm() / y.norm()) < 0.01
+
+
+def test_hyper_connection_stack_matches_oracle():
+    """Tiny model with four residual streams (hyper-connections around every sub-layer): prefill logits and greedy decode vs the oracle."""
+    spec = tiny_spec().replace(n_layers=3, hyper_streams=4)
+    masters = init_weights(spec, 6)
+    dw = DeviceWeights.from_masters(spec, masters, DEV)
+    eng = Engine(dw, n_pages=32, max_seqs=8, max_pages_per_seq=4)
+    ref = RefModel(spec, dw.dequantized_masters())
+    prompts = _prompts(spec, 2, 40)
+    gen = BatchGenerator(eng)
+    gen.prefill(prompts)
+    lane = eng.lane(80)
+    torch.cuda.synchronize()
+    eng.check_status()
+    for i, p in enumerate(prompts):
+        rl, _ = ref.forward(torch.tensor(p), 0, RefCache())
+        got = lane.logits[i].float().cpu()
+        err = float((got - rl[-1]).norm() / rl[-1].norm())
+        assert err < 0.05, f"prompt {i}: logits rel err {err}"
+    gen.release()
+    out = generate(eng, prompts, 10)
+    for i, p in enumerate(prompts):
+        want, rows = ref.generate_greedy(torch.tensor(p), 10)
+        for j, (a, b) in enumerate(zip(out[i], want)):
+            if a != b:
+                top2 = rows[j].topk(2).values
+                assert float(top2[0] - top2[1]) < 0.05, f"prompt {i} step {j}: {a} != {b}"
+                break
