@@ -158,12 +158,12 @@ def test_hybrid_linear_attention_stack_matches_oracle(per_channel):
 
 def test_mhc_boundary_kernel_matches_oracle():
     """One hyper-connection boundary: spread the embedding (init), open; then close with a sub-layer output and re-open; then the head's
-    collapse.  Coefficients, streams and the normalised collapse against the fp32 oracle; one and two rows per CTA."""
+    collapse.  Coefficients, streams and the normalised collapse against the fp32 oracle; a cluster per token, one and two rows per CTA."""
     from cuteafd_b200.ops import native
     from cuteafd_b200.ops.native import ptr
     from cuteafd_b200.ref import ops as rops
     g = torch.Generator().manual_seed(0)
-    for T, H in ((5, 256), (600, 512), (3, 7168)):
+    for T, H in ((5, 256), (300, 256), (600, 512), (3, 7168), (16, 4096)):
         W = 4 * H
         emb = (torch.randn(T, H, generator=g) * 0.5).to(torch.bfloat16)
         sub = (torch.randn(T, H, generator=g) * 0.3).to(torch.bfloat16)
