@@ -336,6 +336,169 @@ extern "C" int cuteafd_router_hash_select(const float* logits, const int* tid2ei
   return CA_OK;
 }
 
+// ---------------------------------------------------------------- whole router in one launch (decode / verify steps)
+// logits -> selection -> route packing used to be two launches around a [T, E] fp32 round trip; on a decode step both are
+// launch-latency sized.  Here one block per expert (512 threads: one 16-byte weight chunk per thread at H = 4096) computes that
+// expert's logit for every token; the block that arrives last at the ticket then selects with one warp per token (scores in that
+// warp's slice of shared memory) and packs the routes with the whole block.
+#define RF_THREADS 512
+#define RF_WARPS (RF_THREADS / 32)
+
+// One warp, one token: scores, optional group-limited routing, k rounds of argmax (value desc, expert id asc), gate weights.
+__device__ __forceinline__ void router_select_warp(const float* lg, const float* __restrict__ bias, float* score, float* choice, int E, int k,
+                                                   int scoring, int normalize, float route_scale, int n_group, int topk_group,
+                                                   int* idx_out, float* wts_out) {
+  const int lane = threadIdx.x & 31;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, __ldcg(lg + e));
+  float denom = 1.f;
+  if (scoring == SCORE_SOFTMAX) {
+    mx = warp_max(mx);
+    float s = 0.f;
+    for (int e = lane; e < E; e += 32) s += expf(__ldcg(lg + e) - mx);
+    denom = warp_sum(s);
+  }
+  for (int e = lane; e < E; e += 32) {
+    const float x = __ldcg(lg + e);
+    float sc;
+    if (scoring == SCORE_SIGMOID) sc = 1.f / (1.f + expf(-x));
+    else if (scoring == SCORE_SOFTMAX) sc = expf(x - mx) / denom;
+    else sc = sqrtf(x > 20.f ? x : log1pf(expf(x)));
+    score[e] = sc;
+    choice[e] = sc + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  if (n_group > 1 && topk_group < n_group) {
+    const int per = E / n_group;
+    float gs = -INFINITY;                       // lane g: sum of the two best biased scores of group g
+    if (lane < n_group) {
+      float a = -INFINITY, b = -INFINITY;
+      for (int j = 0; j < per; ++j) { const float v = choice[lane * per + j]; if (v > a) { b = a; a = v; } else if (v > b) b = v; }
+      gs = a + b;
+    }
+    unsigned keep = 0;
+    for (int r = 0; r < topk_group; ++r) {      // best groups first, lowest group id among equals
+      float bv = (lane < n_group && !(keep >> lane & 1)) ? gs : -INFINITY;
+      int bi = (lane < n_group && !(keep >> lane & 1)) ? lane : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+      }
+      if (bi != 0x7fffffff) keep |= 1u << bi;
+    }
+    for (int e = lane; e < E; e += 32) if (!(keep >> (e / per) & 1)) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  float wsum = 0.f, myw = 0.f; int mye = 0;
+  for (int r = 0; r < k; ++r) {
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) { const float v = choice[e]; if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; } }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (bi >= E) bi = 0;
+    const float w = score[bi];
+    wsum += w;
+    if (lane == r) { mye = bi; myw = w; }
+    __syncwarp();
+    if (lane == 0) choice[bi] = -INFINITY;
+    __syncwarp();
+  }
+  const float inv = normalize ? 1.f / fmaxf(wsum, 1e-12f) : 1.f;
+  if (lane < k) { idx_out[lane] = mye; wts_out[lane] = myw * inv * route_scale; }
+}
+
+__global__ void __launch_bounds__(RF_THREADS) router_fused_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits,
+                                                                  const float* __restrict__ bias, int* __restrict__ idx, float* __restrict__ wts,
+                                                                  int T, int E, int H, int k, int scoring, int normalize, float route_scale,
+                                                                  int n_group, int topk_group, const RoutePack pack, int do_pack) {
+  pdl_launch(); pdl_wait();
+  extern __shared__ int rf_sh[];                       // select: [warps][2][E] floats; pack: route_pack_smem ints (the larger of the two)
+  __shared__ float red[RL_TOK][RF_WARPS];
+  __shared__ int is_last;
+  const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bf16* wr = w + (size_t)e * H;
+  for (int t0 = 0; t0 < T; t0 += RL_TOK) {
+    float acc[RL_TOK];
+#pragma unroll
+    for (int j = 0; j < RL_TOK; ++j) acc[j] = 0.f;
+    for (int c = tid; c < H / 8; c += RF_THREADS) {
+      const uint4 wv = *(const uint4*)(wr + c * 8);
+      const bf162* wp = (const bf162*)&wv;
+      float wf[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(wp[q]); wf[2 * q] = f.x; wf[2 * q + 1] = f.y; }
+#pragma unroll
+      for (int j = 0; j < RL_TOK; ++j) {
+        if (t0 + j < T) {
+          const uint4 xv = *(const uint4*)(x + (size_t)(t0 + j) * H + c * 8);
+          const bf162* xp = (const bf162*)&xv;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(xp[q]); acc[j] = fmaf(f.x, wf[2 * q], acc[j]); acc[j] = fmaf(f.y, wf[2 * q + 1], acc[j]); }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < RL_TOK; ++j) {
+      const float v = warp_sum(acc[j]);
+      if (lane == 0) red[j][warp] = v;
+    }
+    __syncthreads();
+    if (tid < RL_TOK && t0 + tid < T) {
+      float v = 0.f;
+#pragma unroll
+      for (int q = 0; q < RF_WARPS; ++q) v += red[tid][q];
+      logits[(size_t)(t0 + tid) * E + e] = v;
+    }
+    __syncthreads();
+  }
+  // the block that arrives last sees every expert's logits
+  if (tid == 0) {
+    __threadfence();
+    is_last = (atomicAdd(pack.ticket, 1) == (int)gridDim.x - 1);
+    __threadfence();
+  }
+  __syncthreads();
+  if (!is_last) return;
+  float* sc = (float*)rf_sh + (size_t)warp * 2 * E;
+  for (int t = warp; t < T; t += RF_WARPS)
+    router_select_warp(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
+                       wts + (size_t)t * k);
+  __syncthreads();                                     // idx is complete (block-scope visibility is enough: the same block packs)
+  if (do_pack) route_pack_body(pack, rf_sh);
+  if (tid == 0) *pack.ticket = 0;
+}
+
+// logits [T, E] fp32 are still written (tracing, tests).  `src_token == null` skips the packing (attention ranks of a multi-GPU
+// layout select only: their experts live elsewhere).
+extern "C" int cuteafd_router_fused(const void* x, const void* w, float* logits, const float* bias, int* idx, float* wts, int T, int E, int H, int k,
+                                    int scoring, int normalize, float route_scale, int n_group, int topk_group, int* src_token, int* slot_row,
+                                    int* counts, int* offsets, void* tiles, int* n_tiles, int* n_rows, int e_lo, int e_hi, int tn, int max_tiles,
+                                    int* src_route, int* ticket, cudaStream_t s) {
+  CA_REQUIRE(x && w && logits && idx && wts && ticket, "router_fused: null argument");
+  CA_REQUIRE(H % 8 == 0 && E >= k && E <= 512 && k >= 1 && k <= 16, "router_fused: need hidden %% 8 == 0, k <= 16 and E <= 512 (E=%d k=%d)", E, k);
+  CA_REQUIRE(n_group >= 1 && n_group <= 32 && E % n_group == 0, "router_fused: bad group count");
+  const int do_pack = src_token != nullptr;
+  CA_REQUIRE(!do_pack || (e_hi > e_lo && e_hi - e_lo <= 512 && tn >= 1 && T * k <= 4096), "router_fused: bad pack arguments");
+  if (T <= 0) return CA_OK;
+  RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, ticket,
+              FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0}, nullptr, 0};
+  size_t smem = (size_t)RF_WARPS * 2 * E * sizeof(float);
+  if (do_pack && route_pack_smem(T, k, e_lo, e_hi) > smem) smem = route_pack_smem(T, k, e_lo, e_hi);
+  CA_REQUIRE(smem <= 96 * 1024, "router_fused: too many routes for one block");
+  if (smem > 48 * 1024) {
+    cudaError_t ce = cudaFuncSetAttribute(router_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (ce != cudaSuccess) return ca_cuda(ce, "router_fused: shared memory size");
+  }
+  CA_LAUNCH_PDL(router_fused_kernel, E, RF_THREADS, smem, s, (const bf16*)x, (const bf16*)w, logits, bias, idx, wts, T, E, H, k, scoring, normalize,
+                route_scale, n_group, topk_group, p, do_pack);
+  CA_CHECK_LAUNCH("router_fused");
+  return CA_OK;
+}
+
 // Router selection and route packing in one launch: the select block that finishes last packs the routes.
 extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k,
                                           int scoring, int normalize, float route_scale, int n_group, int topk_group,

@@ -31,6 +31,9 @@ PAGE = 64
 PREFILL_ATTN_MIN_Q = int(os.environ.get("CUTEAFD_PREFILL_ATTN_MIN_Q", "64"))
 
 
+ROUTER_FUSED = os.environ.get("CUTEAFD_ROUTER_FUSED", "1") != "0"      # decode-sized steps: router logits + selection + packing in one launch
+
+
 @dataclass
 class StepShape:
     """Static shape of a captured step."""
@@ -446,13 +449,25 @@ class Engine:
             else:
                 self._ffn(lw, L, T, L.x, L.x)
             return
-        if T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1":
-            ops.router_logits(L.xn, lw.router, L.router_logits, T)         # decode / verify: SIMT dot products, one block per expert
+        e_lo, e_hi = self.expert_range
+        fused = False
+        simt = T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1"
+        if simt and T * m.top_k <= 1024 and e_hi - e_lo <= 512 and m.n_experts <= 512 and ROUTER_FUSED:
+            # decode / verify: logits, selection and packing in ONE launch (the block that finishes its expert's logits last selects and packs)
+            ops.router_fused(L.xn, lw.router, L.router_logits, lw.router_bias, L.idx, L.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                             m.n_group, m.topk_group, pack={"src_token": L.src_token, "slot_row": L.slot_row, "counts": L.counts, "offsets": L.offsets,
+                                                            "tiles": L.tiles, "n_tiles": L.n_tiles, "n_rows": L.n_rows, "e_lo": e_lo, "e_hi": e_hi,
+                                                            "tn": L.tn_g, "max_tiles": L.max_tiles})
+            self.launches_per_step -= 1
+            fused = True
+        elif simt:
+            ops.router_logits(L.xn, lw.router, L.router_logits, T)         # SIMT dot products, one block per expert
             self.launches_per_step += 1
         else:
             self._dense(lw.router, L.xn_act, L.router_logits, T)
-        e_lo, e_hi = self.expert_range
-        if T * m.top_k <= 1024 and e_hi - e_lo <= 512:     # decode / verify steps: select and pack in one launch
+        if fused:
+            pass
+        elif T * m.top_k <= 1024 and e_hi - e_lo <= 512:     # decode / verify steps: select and pack in one launch
             ops.router_select_pack(L.router_logits, lw.router_bias, L.idx, L.wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
                                    m.n_group, m.topk_group, L.src_token, L.slot_row, L.counts, L.offsets, L.tiles, L.n_tiles, L.n_rows,
                                    e_lo, e_hi, L.tn_g, L.max_tiles)

@@ -441,6 +441,22 @@ def router_select_pack(logits, bias, idx, wts, T, k, scoring, normalize, route_s
          ptr(tiles), ptr(n_tiles), ptr(n_rows), e_lo, e_hi, tn, max_tiles, ptr(src_route), ptr(_TICKETS[dev]), stream())
 
 
+def router_fused(x, w: "TcWeight", logits, bias, idx, wts, T, k, scoring, normalize, route_scale, n_group=1, topk_group=1, pack: dict | None = None):
+    """The whole router of a decode-sized step in one launch: fp32 logits of `T` bf16 rows against the bf16 router weight, top-k
+    selection with gate weights, and - with `pack` (src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, e_lo, e_hi, tn,
+    max_tiles, optional src_route) - the expert-order route packing and tile table."""
+    assert w.kind == KIND_BF16 and w.G == 1 and x.dtype == torch.bfloat16 and x.stride(0) == w.K and logits.stride(0) == w.N
+    dev = logits.device
+    if dev not in _TICKETS:
+        _TICKETS[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    pk = pack or {}
+    g = lambda name: ptr(pk.get(name))
+    call("cuteafd_router_fused", ptr(x), ptr(w.data), ptr(logits), ptr(bias), ptr(idx), ptr(wts), T, w.N, w.K, k, SCORING[scoring],
+         1 if normalize else 0, route_scale, n_group, topk_group, g("src_token"), g("slot_row"), g("counts"), g("offsets"), g("tiles"),
+         g("n_tiles"), g("n_rows"), pk.get("e_lo", 0), pk.get("e_hi", 0), pk.get("tn", 1), pk.get("max_tiles", 0), g("src_route"),
+         ptr(_TICKETS[dev]), stream())
+
+
 def route_pack(idx, src_token, slot_row, counts, offsets, tiles, n_tiles, n_rows, T, k, e_lo, e_hi, tn, max_tiles, src_route=None, *,
                wait=None, lane_T=None, t_cap: int = 0):
     """Packs the routes of `T` tokens into expert order.  `wait` (a `native.FlagWaitArg`) makes the kernel wait for the peers

@@ -43,7 +43,7 @@ import torch
 
 from .. import ops
 from ..config import Deployment, ModelSpec
-from ..engine.engine import Engine, Lane, StepShape
+from ..engine.engine import ROUTER_FUSED, Engine, Lane, StepShape
 from ..models.weights import DeviceWeights
 from ..ops import ActBuffer, KIND_BF16, KIND_BY_NAME, KIND_NVFP4, KIND_W4A8, native, pick_tn
 from . import peer_ops
@@ -411,14 +411,21 @@ class AttnRankEngine(Engine):
             self._routing_bufs(L)
             self._ffn_norm(lw, L, T)
             self.launches_per_step -= 1
-            if T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K \
-                    and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1":
-                ops.router_logits(L.xn, lw.router, L.r_logits, T)      # same kernel as the single-GPU engine (token-exact layouts)
+            simt = T <= 64 and lw.router.kind == KIND_BF16 and lw.router.G == 1 and L.xn.stride(0) == lw.router.K \
+                and os.environ.get("CUTEAFD_ROUTER_GEMM", "0") != "1"
+            if simt and ROUTER_FUSED and m.n_experts <= 512:
+                # logits + selection in one launch (same arithmetic as the single-GPU engine's fused router: token-exact layouts)
+                ops.router_fused(L.xn, lw.router, L.r_logits, lw.router_bias, L.r_idx, L.r_wts, T, m.top_k, m.scoring, m.normalize, m.route_scale,
+                                 m.n_group, m.topk_group)
+                self.launches_per_step += 2
             else:
-                self._dense(lw.router, L.xn_act, L.r_logits, T)
-                self.launches_per_step -= 1
-            ops.router_select(L.r_logits, lw.router_bias, L.r_idx, L.r_wts, T, m.top_k, m.scoring, m.normalize, m.route_scale, m.n_group, m.topk_group)
-            self.launches_per_step += 3
+                if simt:
+                    ops.router_logits(L.xn, lw.router, L.r_logits, T)
+                else:
+                    self._dense(lw.router, L.xn_act, L.r_logits, T)
+                    self.launches_per_step -= 1
+                ops.router_select(L.r_logits, lw.router_bias, L.r_idx, L.r_wts, T, m.top_k, m.scoring, m.normalize, m.route_scale, m.n_group, m.topk_group)
+                self.launches_per_step += 3
         if self.comm == "nccl":
             if T:
                 self._moe_nccl(li, lw, L, T)

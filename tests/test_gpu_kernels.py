@@ -793,3 +793,49 @@ def test_mtp_round_uses_device_acceptance():
     for i in range(4):
         a, emitted, _, _ = greedy_verify(inputs[i], target[i], None, 1 << 30)
         assert int(acc[i]) == a and int(emit[i]) == len(emitted)
+
+
+@pytest.mark.parametrize("T,E,H,k,scoring,ng,tg,bias,e_lo,e_hi", [(16, 128, 4096, 8, "softmax", 1, 1, False, 0, 128), (1, 16, 256, 4, "sigmoid", 1, 1, False, 0, 16),
+                                                                    (37, 256, 7168, 8, "sigmoid", 8, 4, True, 64, 128), (64, 128, 2048, 8, "softmax", 1, 1, False, 16, 32),
+                                                                    (5, 512, 1024, 6, "sqrtsoftplus", 1, 1, False, 0, 512)])
+def test_router_fused_matches_the_three_kernels(T, E, H, k, scoring, ng, tg, bias, e_lo, e_hi):
+    """Router logits + selection + route packing in one launch against the separate kernels (which the oracle tests cover): same
+    logits, experts, gate weights, packed rows and tile table; twice, so the arrival counter is left at zero."""
+    g = torch.Generator().manual_seed(T + E + H)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+    W = TcWeight.from_master(torch.randn(E, H, generator=g) * 0.05, "bf16", DEV)
+    b = (torch.randn(E, generator=g) * 0.1).to(DEV) if bias else None
+    tn, rows = 16, T * k
+    max_tiles = (e_hi - e_lo) + rows // tn + 1
+    i32 = lambda *s: torch.full(s, -7, dtype=torch.int32, device=DEV)
+
+    def bufs():
+        return dict(lg=torch.zeros(T, E, device=DEV), idx=i32(T, k), wts=torch.zeros(T, k, device=DEV), src=i32(rows), slot=i32(T, k), cnt=i32(e_hi - e_lo),
+                    off=i32(e_hi - e_lo), tiles=i32(max_tiles, 4), nt=i32(1), nr=i32(1), route=i32(rows))
+    a, c = bufs(), bufs()
+    ops.router_logits(x, W, a["lg"], T)
+    ops.router_select(a["lg"], b, a["idx"], a["wts"], T, k, scoring, True, 2.5, ng, tg)
+    ops.route_pack(a["idx"], a["src"], a["slot"], a["cnt"], a["off"], a["tiles"], a["nt"], a["nr"], T, k, e_lo, e_hi, tn, max_tiles, src_route=a["route"])
+    for _ in range(2):
+        ops.router_fused(x, W, c["lg"], b, c["idx"], c["wts"], T, k, scoring, True, 2.5, ng, tg,
+                         pack={"src_token": c["src"], "slot_row": c["slot"], "counts": c["cnt"], "offsets": c["off"], "tiles": c["tiles"], "n_tiles": c["nt"],
+                               "n_rows": c["nr"], "e_lo": e_lo, "e_hi": e_hi, "tn": tn, "max_tiles": max_tiles, "src_route": c["route"]})
+    torch.cuda.synchronize()
+    assert torch.allclose(a["lg"], c["lg"], atol=1e-4, rtol=1e-4)
+    # selection on the fused kernel's own logits (summation order differs in the last bits) must agree with the oracle's rule
+    ri, rw = rops.route_topk(c["lg"].cpu(), torch.eye(E), k, scoring, True, 2.5, b.cpu() if bias else None, ng, tg)
+    assert torch.equal(c["idx"].cpu().long(), ri) and torch.allclose(c["wts"].cpu(), rw, rtol=1e-4, atol=1e-6)
+    d = bufs()
+    ops.route_pack(c["idx"], d["src"], d["slot"], d["cnt"], d["off"], d["tiles"], d["nt"], d["nr"], T, k, e_lo, e_hi, tn, max_tiles, src_route=d["route"])
+    torch.cuda.synchronize()
+    n_rows, n_tiles = int(d["nr"][0]), int(d["nt"][0])
+    assert int(c["nr"][0]) == n_rows and int(c["nt"][0]) == n_tiles
+    for key in ("slot", "cnt", "off"):
+        assert torch.equal(c[key], d[key]), key
+    assert torch.equal(c["src"][:n_rows], d["src"][:n_rows]) and torch.equal(c["route"][:n_rows], d["route"][:n_rows])
+    assert torch.equal(c["tiles"][:n_tiles], d["tiles"][:n_tiles])
+    # selection only (no packing): the form attention ranks of a multi-GPU layout use
+    e = bufs()
+    ops.router_fused(x, W, e["lg"], b, e["idx"], e["wts"], T, k, scoring, True, 2.5, ng, tg)
+    torch.cuda.synchronize()
+    assert torch.equal(e["idx"], c["idx"]) and torch.equal(e["wts"], c["wts"]) and bool((e["slot"] == -7).all())
