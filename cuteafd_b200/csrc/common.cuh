@@ -37,8 +37,16 @@ typedef __nv_bfloat162 bf162;
 // and must execute pdl_wait() before touching anything an earlier kernel produced and before their first
 // global write.  pdl_launch() lets the NEXT kernel in the stream start its own prologue.  Both are no-ops
 // for a kernel launched the ordinary way, so a kernel may be launched either way.
+#ifdef CA_PDL_AFTER_WAIT
+// Variant: a kernel releases its dependents only once it has itself been released, so at most ONE later kernel of the stream is
+// resident early (with the release at kernel entry a whole chain of later kernels can cascade onto the SMs and hold shared / tensor
+// memory that the running kernel's remaining CTAs need).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n\tgriddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() {}
+#else
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 // Classes: bit 0 glue kernels (norm, quant, routing, sampling), bit 1 GEMM, bit 2 attention; a file names its class
 // with CA_PDL_CLASS before including this header.
 int ca_pdl_enabled(int cls);

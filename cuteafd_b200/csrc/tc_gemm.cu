@@ -457,6 +457,10 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
             }
           }
         } else if (c0 < nrows && n_ok) {
+          float res[16];        // residual rows ahead of the stores (R may alias Y: loads after a store would serialise)
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            res[j] = (a.epi == EPI_BF16_RESIDUAL && splits <= 1 && c0 + j < nrows) ? __bfloat162float(a.R[(size_t)(row0 + c0 + j) * a.ldy + n]) : 0.f;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int c = c0 + j;
@@ -470,7 +474,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
               if (splits > 1) ws[(size_t)(row0 + c) * a.N + n] = v;
               else if (a.epi == EPI_F32) ((float*)a.Y)[o] = v;
               else {
-                if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
+                v += res[j];
                 const bf16 vb = __float2bfloat16(v);
                 if (a.Y) ((bf16*)a.Y)[o] = vb;
                 if (PEER && a.n_peer) peer_store(a, row0 + c, n, vb);
@@ -511,6 +515,10 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
 #pragma unroll
                   for (int p = 0; p < 8; ++p) v[j] += t[j][p];
               }
+              float res4[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                res4[j] = (a.epi == EPI_BF16_RESIDUAL && c + j < nrows) ? __bfloat162float(a.R[(size_t)(row0 + c + j) * a.ldy + n]) : 0.f;
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 if (c + j >= nrows) break;
@@ -518,7 +526,7 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
                 float r = v[j];
                 if (a.epi == EPI_F32) ((float*)a.Y)[o] = r;
                 else {
-                  if (a.epi == EPI_BF16_RESIDUAL) r += __bfloat162float(a.R[o]);
+                  r += res4[j];
                   const bf16 rb = __float2bfloat16(r);
                   if (a.Y) ((bf16*)a.Y)[o] = rb;
                   if (PEER && a.n_peer) peer_store(a, row0 + c + j, n, rb);
@@ -596,9 +604,9 @@ struct ClCfg {
   static constexpr int TMEM_COLS = 128;
   static constexpr int SFA_COL = 64, SFB_COL = 96;
   static constexpr int SMEM_BYTES = BUDGET + 1024;
-  // Pipeline stages left beside the staging area of an S-way split ((S - 1) partial tiles of 128 x TN fp32).
+  // Pipeline stages left beside the staging area of an S-way split (S partial tiles of 128 x TN fp32: ranks 1..S-1, then rank 0's own).
   __host__ __device__ static constexpr int ring(int S) {
-    return (BUDGET - (S - 1) * 128 * TN * 4) / B::STAGE_BYTES > MAX_RING ? MAX_RING : (BUDGET - (S - 1) * 128 * TN * 4) / B::STAGE_BYTES;
+    return (BUDGET - S * 128 * TN * 4) / B::STAGE_BYTES > MAX_RING ? MAX_RING : (BUDGET - S * 128 * TN * 4) / B::STAGE_BYTES;
   }
   static_assert(TN <= 32, "cluster split-K is for decode-sized token tiles");
 };
@@ -617,6 +625,11 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+// Device trace of the cluster kernel (cuteafd_tc_trace(buf, -N): launches with this N record, per CTA, eight global-timer stamps:
+// 0 entry, 1 rank 0: accumulator read back after the barrier, 2 producer released by the previous kernel, 3 first stage landed, 4 last MMA committed,
+// 5 accumulator complete, 6 cluster barrier passed, 7 epilogue done).
+#define CL_TRACE(slot) do { if (a.trace && a.trace_units == -a.N) a.trace[(size_t)blockIdx.x * 8 + (slot)] = (long long)globaltimer_ns(); } while (0)
+
 template <int KIND, int TN, bool PEER>
 __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_constant__ TcArgs a) {
   using C = TcCfg<KIND, TN, false>;
@@ -632,6 +645,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    CL_TRACE(0);
     for (int s = 0; s < L::MAX_RING; ++s) { mbar_init(&full_bar[s], 33); mbar_init(&empty_bar[s], 1); }
     mbar_init(&accf_bar, 1);
     abort_flag = 0;
@@ -670,6 +684,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
     if (lane == 0)
       for (int i = 0; i < npre; ++i) load_weights(i, kb0 + i);
     pdl_wait();
+    if (lane == 0) CL_TRACE(2);
     for (int kb = kb0, it = 0; kb < kb1 && !*abortp; ++kb, ++it) {
       const int s = it % ring;
       if (it >= ring) {
@@ -705,6 +720,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
       for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
         const int s = it % ring;
         if (!mbar_wait_bounded(&full_bar[s], (it / ring) & 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_MMA, (int)blockIdx.x); ok = false; break; }
+        if (it == 0) CL_TRACE(3);
         tc_fence_after();
         if (KIND != KIND_BF16) fence_proxy_async_smem();
         const uint32_t st = smem_base + s * C::STAGE_BYTES;
@@ -730,6 +746,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
         tc_commit(&empty_bar[s]);
       }
       if (ok) tc_commit(&accf_bar);
+      CL_TRACE(4);
     }
     __syncwarp();
   } else {
@@ -739,12 +756,47 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
   // ---- partial tiles of ranks 1..S-1 travel to rank 0's staging area
   const int q4 = warp & 3, et = q4 * 32 + lane;
   const uint32_t tbase = tmem + ((uint32_t)(q4 * 32) << 16);
+  // Everything the last step of the chain reads from global memory is fetched NOW, under the main loop: the output scale and the
+  // residual rows of rank 0's tile (R may alias Y, so these loads must also come before the stores).  After the cluster barrier
+  // only tensor-memory loads, shared-memory adds and the stores remain.
+  // Rank 0 finishes the tile row-wise when the output allows 16-byte accesses: its own partial goes to the staging area too, and
+  // after the barrier every thread owns (token, 8 consecutive features) items - two float4 reads per partial, one 16-byte store -
+  // instead of sixteen 2-byte stores behind sixteen unrolled copies of the adds (short code: this tail runs once per launch, from a
+  // cold instruction cache).
+  const bool vec_ok = !(PEER && a.n_peer) && a.Y && a.N % 8 == 0 && a.ldy % 8 == 0 && ((uintptr_t)a.Y & 15) == 0 &&
+                      (a.epi != EPI_BF16_RESIDUAL || ((uintptr_t)a.R & 15) == 0);
+  constexpr int ITEMS = TN / 8;                              // items of one thread: TN rows x 16 feature groups / 128 threads
+  const int tid128 = (warp >= 2) ? (warp - 2) * 32 + lane : 0;
+  float al_pre = 1.f, res_pre[TN];
+  uint4 rv_pre[ITEMS];
+#pragma unroll
+  for (int j = 0; j < TN; ++j) res_pre[j] = 0.f;
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) rv_pre[j] = make_uint4(0u, 0u, 0u, 0u);
+  if (warp >= 2) {
+    if (a.alpha) al_pre = a.alpha[0];
+    const int n_pre = nt * 128 + et;
+    if (sp == 0 && a.epi == EPI_BF16_RESIDUAL) {
+      if (vec_ok) {
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+          const int i = tid128 + it * 128, c = i >> 4, nn = nt * 128 + (i & 15) * 8;
+          if (c < nrows && nn < a.N) rv_pre[it] = *(const uint4*)(a.R + (size_t)(row0 + c) * a.ldy + nn);
+        }
+      } else if (n_pre < a.N) {
+#pragma unroll
+        for (int j = 0; j < TN; ++j)
+          if (j < nrows) res_pre[j] = __bfloat162float(a.R[(size_t)(row0 + j) * a.ldy + n_pre]);
+      }
+    }
+  }
   bool have_acc = false;
   if (warp >= 2) {
     have_acc = (kb1 > kb0) && mbar_wait_bounded(&accf_bar, 0, abortp);
     have_acc = __all_sync(0xffffffffu, have_acc);      // tensor-memory loads below must be warp-uniform
     if (!have_acc && kb1 > kb0) ca_dev_fail(a.status, CA_DEV_TIMEOUT_EPILOGUE, (int)blockIdx.x);
     tc_fence_after();
+    if (warp == 2 && lane == 0) CL_TRACE(5);
     if (sp != 0) {
       const uint32_t remote = map_to_rank(smem_u32(staging), 0) + (uint32_t)(sp - 1) * (128 * TN * 4);
 #pragma unroll 1
@@ -754,19 +806,63 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
 #pragma unroll
         for (int j = 0; j < 16; ++j) st_cluster_f32(remote + (uint32_t)((c0 + j) * 128 + et) * 4, have_acc ? __uint_as_float(r[j]) : 0.f);
       }
+    } else if (vec_ok) {
+      float* own = staging + (size_t)(S - 1) * (128 * TN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        uint32_t r[16];
+        if (have_acc) { tmem_ld_x16(tbase + c0, r); tc_wait_ld(); }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) own[(c0 + j) * 128 + et] = have_acc ? __uint_as_float(r[j]) : 0.f;
+      }
     }
   }
   __syncwarp();
   cluster_sync_all();                      // every thread of every CTA of the cluster, exactly once
-  if (warp >= 2 && sp == 0) {
+  if (warp == 2 && lane == 0) CL_TRACE(6);
+  if (warp >= 2 && sp == 0 && vec_ok) {
+    const float* own = staging + (size_t)(S - 1) * (128 * TN);
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int i = tid128 + it * 128, c = i >> 4, g8 = (i & 15) * 8, nn = nt * 128 + g8;
+      if (c < nrows && nn < a.N) {
+        const float4 o0 = *(const float4*)(own + c * 128 + g8), o1 = *(const float4*)(own + c * 128 + g8 + 4);
+        float f[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll 1
+        for (int p = 1; p < S; ++p) {                                  // rank order, as the scalar path adds them
+          const float* sp_ = staging + (size_t)(p - 1) * (128 * TN) + c * 128 + g8;
+          const float4 p0 = *(const float4*)sp_, p1 = *(const float4*)(sp_ + 4);
+          f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w; f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] *= al_pre;
+        const size_t o = (size_t)(row0 + c) * a.ldy + nn;
+        if (a.epi == EPI_F32) {
+          *(float4*)((float*)a.Y + o) = make_float4(f[0], f[1], f[2], f[3]);
+          *(float4*)((float*)a.Y + o + 4) = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
+          const bf16* rb = (const bf16*)&rv_pre[it];
+          uint32_t wv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const bf162 hh = __floats2bfloat162_rn(f[2 * q] + __bfloat162float(rb[2 * q]), f[2 * q + 1] + __bfloat162float(rb[2 * q + 1]));
+            wv[q] = *(const uint32_t*)&hh;
+          }
+          *(uint4*)((bf16*)a.Y + o) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
+      }
+    }
+  } else if (warp >= 2 && sp == 0) {
     const int n = nt * 128 + et;
     const bool n_ok = n < a.N;
-    const float al = a.alpha ? a.alpha[0] : 1.f;
-#pragma unroll 1
+    const float al = al_pre;
+#pragma unroll
     for (int c0 = 0; c0 < TN; c0 += 16) {
       uint32_t r[16];
       if (have_acc) { tmem_ld_x16(tbase + c0, r); tc_wait_ld(); }
+      if (c0 == 0 && warp == 2 && lane == 0) CL_TRACE(1);
       if (c0 < nrows && n_ok) {
+        const float* res = res_pre + c0;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int c = c0 + j;
@@ -777,7 +873,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
             const size_t o = (size_t)(row0 + c) * a.ldy + n;
             if (a.epi == EPI_F32) ((float*)a.Y)[o] = v;
             else {
-              if (a.epi == EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
+              v += res[j];
               const bf16 vb = __float2bfloat16(v);
               if (a.Y) ((bf16*)a.Y)[o] = vb;
               if (PEER && a.n_peer) peer_store(a, row0 + c, n, vb);
@@ -787,6 +883,7 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
       }
     }
   }
+  if (warp == 2 && lane == 0) CL_TRACE(7);
   if (PEER && warp >= 2 && a.n_peer) peer_publish(a, warp, lane);      // every CTA counts in; only rank 0 of a cluster stored
   if (*abortp && warp == 0) {
     const uint64_t t0 = globaltimer_ns();
@@ -822,6 +919,34 @@ static int launch_cluster_p(const TcArgs& a, int grid, cudaStream_t stream) {
   return CA_OK;
 }
 
+// How many clusters of `splits` CTAs of the split-K kernel the device can hold at once (a cluster needs `splits` free SMs inside
+// ONE GPC, so the answer is well below SMs / splits for sizes that do not divide the GPCs evenly): a split whose cluster count
+// exceeds this runs in two waves.
+template <int KIND, int TN>
+static int cluster_capacity(int splits, int* out) {
+  using L = ClCfg<KIND, TN>;
+  auto kern = tc_linear_cluster_kernel<KIND, TN, false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM_BYTES);
+  if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(tc_linear_cluster)");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits * 64); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = L::SMEM_BYTES;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  e = cudaOccupancyMaxActiveClusters(out, kern, &cfg);
+  if (e != cudaSuccess) return ca_cuda(e, "cudaOccupancyMaxActiveClusters");
+  return CA_OK;
+}
+
+extern "C" int cuteafd_tc_cluster_capacity(int kind, int tn, int splits, int* out) {
+  CA_REQUIRE(out && (tn == 16 || tn == 32) && splits >= 1 && splits <= (tn == 16 ? 8 : 4), "tc_cluster_capacity: bad arguments");
+  if (kind == KIND_BF16) return tn == 16 ? cluster_capacity<KIND_BF16, 16>(splits, out) : cluster_capacity<KIND_BF16, 32>(splits, out);
+  if (kind == KIND_NVFP4) return tn == 16 ? cluster_capacity<KIND_NVFP4, 16>(splits, out) : cluster_capacity<KIND_NVFP4, 32>(splits, out);
+  if (kind == KIND_MXFP4) return tn == 16 ? cluster_capacity<KIND_MXFP4, 16>(splits, out) : cluster_capacity<KIND_MXFP4, 32>(splits, out);
+  return ca_fail(CA_ERR_UNSUPPORTED, "tc_cluster_capacity: no cluster kernel for this kind");
+}
+
 template <int KIND, int TN>
 static int launch_cluster(const TcArgs& a, int grid, cudaStream_t stream) {
   return a.n_peer ? launch_cluster_p<KIND, TN, true>(a, grid, stream) : launch_cluster_p<KIND, TN, false>(a, grid, stream);
@@ -833,7 +958,7 @@ static long long* g_trace = nullptr;
 static int g_trace_units = 0;
 extern "C" int cuteafd_tc_trace(void* buf, int units) {
   g_trace = (long long*)buf;
-  g_trace_units = buf ? units : 0;
+  g_trace_units = buf ? units : 0;         // units < 0: the cluster split-K kernel's launches with N == -units record instead
   return CA_OK;
 }
 
@@ -884,7 +1009,7 @@ extern "C" int cuteafd_tc_linear(int kind, int swiglu, int tn, const void* tmA, 
   a.w4_tx = 128 * 128 / 2;
   const int n_nt = (N + 127) / 128;
   if (kind == KIND_W4A8 && !tiles && !swiglu && a.splits > 1 && tn <= 32) a.splits = 1;       // no cluster split-K variant of this kind: one CTA per tile
-  if (!tiles && !swiglu && (tn == 16 || tn == 32) && (a.splits == 2 || a.splits == 4 || (a.splits == 8 && tn == 16))) {
+  if (!tiles && !swiglu && (tn == 16 || tn == 32) && a.splits >= 2 && a.splits <= (tn == 16 ? 8 : 4)) {
     {
       const int grid_c = ((rows_total + tn - 1) / tn) * n_nt * a.splits;
       if (kind == KIND_BF16) return tn == 16 ? launch_cluster<KIND_BF16, 16>(a, grid_c, stream) : launch_cluster<KIND_BF16, 32>(a, grid_c, stream);

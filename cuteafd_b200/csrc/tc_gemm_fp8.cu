@@ -93,6 +93,10 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
 #pragma unroll
   for (int j = 0; j < TN; ++j) acc[j] = 0.f;
   const int q4 = warp & 3, et = q4 * 32 + lane;
+  constexpr bool RES_PRE = TN <= 32;
+  float res_pre[RES_PRE ? TN : 1];
+#pragma unroll
+  for (int j = 0; j < (RES_PRE ? TN : 1); ++j) res_pre[j] = 0.f;
 
   if (warp == 0) {
     // ---- producer: weight tiles first (static data), then wait for the previous kernel, then activation tiles
@@ -137,6 +141,12 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
   } else {
     // ---- epilogue warps: scaled accumulation of every finished stage into registers
     pdl_wait();
+    if (RES_PRE && sp == 0 && a.epi == F8_EPI_BF16_RESIDUAL && nt * 128 + et < a.N) {
+      // decode-sized tiles: the residual rows are fetched under the main loop (and ahead of every store: R may alias Y)
+#pragma unroll
+      for (int j = 0; j < (RES_PRE ? TN : 1); ++j)
+        if (j < nrows) res_pre[j] = __bfloat162float(a.R[(size_t)(row0 + j) * a.ldy + nt * 128 + et]);
+    }
     const uint32_t tbase = tmem + ((uint32_t)(q4 * 32) << 16);
     bool ok = true;
     if (use_tab) {
@@ -190,18 +200,30 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
   if (warp >= 2 && sp == 0) {
     const int n = nt * 128 + et;
     if (n < a.N) {
+      // residual rows first, all in flight together: R may alias Y (in-place residual stream), so loads issued after a store
+      // would wait for it, one L2 round trip per token row
 #pragma unroll
-      for (int j = 0; j < TN; ++j) {
+      for (int j0 = 0; j0 < TN; j0 += 16) {
+      float res[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (RES_PRE) res[j] = res_pre[(j0 + j) < (RES_PRE ? TN : 1) ? (j0 + j) : 0];
+        else res[j] = (a.epi == F8_EPI_BF16_RESIDUAL && j0 + j < nrows) ? __bfloat162float(a.R[(size_t)(row0 + j0 + j) * a.ldy + n]) : 0.f;
+      }
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        const int j = j0 + jj;
         if (j < nrows) {
           float v = acc[j];
           for (int p = 1; p < S; ++p) v += staging[(size_t)(p - 1) * (128 * TN) + j * 128 + et];
           const size_t o = (size_t)(row0 + j) * a.ldy + n;
           if (a.epi == F8_EPI_F32) ((float*)a.Y)[o] = v;
           else {
-            if (a.epi == F8_EPI_BF16_RESIDUAL) v += __bfloat162float(a.R[o]);
+            v += res[jj];
             ((bf16*)a.Y)[o] = __float2bfloat16(v);
           }
         }
+      }
       }
     }
   }

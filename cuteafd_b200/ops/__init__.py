@@ -43,6 +43,19 @@ def set_pdl(mask: int) -> None:
     native.lib().cuteafd_set_pdl(int(mask))
 
 
+_CLUSTER_CAP: dict = {}
+
+
+def cluster_capacity(kind: int, tn: int, splits: int) -> int:
+    """Clusters of `splits` CTAs of the cluster split-K GEMM that fit the device at once (cached per device)."""
+    key = (torch.cuda.current_device(), kind, tn, splits)
+    if key not in _CLUSTER_CAP:
+        out = ctypes.c_int(0)
+        call("cuteafd_tc_cluster_capacity", kind, tn, splits, ctypes.addressof(out))
+        _CLUSTER_CAP[key] = out.value
+    return _CLUSTER_CAP[key]
+
+
 def tc_trace(buf: torch.Tensor | None, units: int = 0) -> None:
     """Per-unit device time stamps of later `tc_linear` launches: int64 [grid, units, 8] (None = off)."""
     call("cuteafd_tc_trace", ptr(buf), units)
