@@ -39,9 +39,11 @@ struct Fp8Cfg {
   // sa[token, kb] * sw[n / 128, kb] of this CTA's K slice (one fp32 per token and stage; without the table every stage
   // exposed two dependent global loads, ~0.5 us, in the epilogue warps).
   __host__ __device__ static constexpr int table_bytes(int nk) { return nk * TN * 4 <= 64 * 1024 ? nk * TN * 4 : 0; }
+  // decode-sized tiles keep one more staging tile: rank 0's own partial, so that the tile can be finished row-wise (16-byte stores)
+  static constexpr int OWN = TN <= 32 ? 1 : 0;
   __host__ __device__ static constexpr int ring(int S, int nk) {
-    return (BUDGET - (S - 1) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES > MAX_RING
-               ? MAX_RING : (BUDGET - (S - 1) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES;
+    return (BUDGET - (S - 1 + OWN) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES > MAX_RING
+               ? MAX_RING : (BUDGET - (S - 1 + OWN) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES;
   }
 };
 
@@ -63,7 +65,7 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
   const int nk_max = ((a.K + 127) / 128 + S - 1) / S;                      // stages of the longest K slice
   const int ring = C::ring(S, nk_max);
   float* staging = (float*)(smem + ring * C::STAGE_BYTES);                 // [S-1][TN][128] fp32 on cluster rank 0
-  float* sc_tab = staging + (size_t)(S - 1) * 128 * TN;                    // [stages of my slice][TN] combined scales
+  float* sc_tab = staging + (size_t)(S - 1 + C::OWN) * 128 * TN;           // [stages of my slice][TN] combined scales
   const bool use_tab = C::table_bytes(nk_max) > 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -97,6 +99,14 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
   float res_pre[RES_PRE ? TN : 1];
 #pragma unroll
   for (int j = 0; j < (RES_PRE ? TN : 1); ++j) res_pre[j] = 0.f;
+  // row-wise finish of a decode-sized tile by rank 0 (see the staging tile above): (token, 8 features) items, 16-byte accesses
+  constexpr int ITEMS = RES_PRE ? TN / 8 : 1;
+  const bool vec_ok = RES_PRE && a.N % 8 == 0 && a.ldy % 8 == 0 && ((uintptr_t)a.Y & 15) == 0 &&
+                      (a.epi != F8_EPI_BF16_RESIDUAL || ((uintptr_t)a.R & 15) == 0);
+  const int tid128 = warp >= 2 ? (warp - 2) * 32 + lane : 0;
+  uint4 rv_pre[ITEMS];
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) rv_pre[j] = make_uint4(0u, 0u, 0u, 0u);
 
   if (warp == 0) {
     // ---- producer: weight tiles first (static data), then wait for the previous kernel, then activation tiles
@@ -141,8 +151,14 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
   } else {
     // ---- epilogue warps: scaled accumulation of every finished stage into registers
     pdl_wait();
-    if (RES_PRE && sp == 0 && a.epi == F8_EPI_BF16_RESIDUAL && nt * 128 + et < a.N) {
+    if (vec_ok && sp == 0 && a.epi == F8_EPI_BF16_RESIDUAL) {
       // decode-sized tiles: the residual rows are fetched under the main loop (and ahead of every store: R may alias Y)
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const int i = tid128 + it * 128, c = i >> 4, nn = nt * 128 + (i & 15) * 8;
+        if (c < nrows && nn < a.N) rv_pre[it] = *(const uint4*)(a.R + (size_t)(row0 + c) * a.ldy + nn);
+      }
+    } else if (RES_PRE && sp == 0 && a.epi == F8_EPI_BF16_RESIDUAL && nt * 128 + et < a.N) {
 #pragma unroll
       for (int j = 0; j < (RES_PRE ? TN : 1); ++j)
         if (j < nrows) res_pre[j] = __bfloat162float(a.R[(size_t)(row0 + j) * a.ldy + nt * 128 + et]);
@@ -193,11 +209,46 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
 #pragma unroll
       for (int j = 0; j < TN; ++j)
         asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)(j * 128 + et) * 4), "f"(acc[j]) : "memory");
+    } else if (vec_ok) {
+      float* own = staging + (size_t)(S - 1) * (128 * TN);
+#pragma unroll
+      for (int j = 0; j < TN; ++j) own[j * 128 + et] = acc[j];
+      if (S == 1) asm volatile("bar.sync 2, 128;" ::: "memory");     // the four epilogue warps; clusters meet at the barrier below
     }
   }
   __syncwarp();
   if (S > 1) f8_cluster_sync();              // every thread of every CTA of the cluster, exactly once
-  if (warp >= 2 && sp == 0) {
+  if (warp >= 2 && sp == 0 && vec_ok) {
+    const float* own = staging + (size_t)(S - 1) * (128 * TN);
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int i = tid128 + it * 128, c = i >> 4, g8 = (i & 15) * 8, nn = nt * 128 + g8;
+      if (c < nrows && nn < a.N) {
+        const float4 o0 = *(const float4*)(own + c * 128 + g8), o1 = *(const float4*)(own + c * 128 + g8 + 4);
+        float f[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll 1
+        for (int p = 1; p < S; ++p) {                                  // rank order, as the scalar path adds them
+          const float* pp = staging + (size_t)(p - 1) * (128 * TN) + c * 128 + g8;
+          const float4 p0 = *(const float4*)pp, p1 = *(const float4*)(pp + 4);
+          f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w; f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
+        }
+        const size_t o = (size_t)(row0 + c) * a.ldy + nn;
+        if (a.epi == F8_EPI_F32) {
+          *(float4*)((float*)a.Y + o) = make_float4(f[0], f[1], f[2], f[3]);
+          *(float4*)((float*)a.Y + o + 4) = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
+          const bf16* rb = (const bf16*)&rv_pre[it];
+          uint32_t wv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const bf162 hh = __floats2bfloat162_rn(f[2 * q] + __bfloat162float(rb[2 * q]), f[2 * q + 1] + __bfloat162float(rb[2 * q + 1]));
+            wv[q] = *(const uint32_t*)&hh;
+          }
+          *(uint4*)((bf16*)a.Y + o) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
+      }
+    }
+  } else if (warp >= 2 && sp == 0) {
     const int n = nt * 128 + et;
     if (n < a.N) {
       // residual rows first, all in flight together: R may alias Y (in-place residual stream), so loads issued after a store
