@@ -133,20 +133,22 @@ __global__ void __launch_bounds__(192, 2) paged_attn_tc_kernel(const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------------ K/V producer (separate K and V rings:
     // a K stage is free as soon as its score MMA retires, long before the matching V stage)
+    // a decode step reads every K/V byte once: stream it through L2; with several query tiles per sequence the pages are shared
+    const uint64_t kvpol = a.max_q_tiles == 1 ? l2_policy_stream() : l2_policy_normal();
     for (int i = 0; i < n_tiles && !*abortp; ++i) {
       const int s = i & 1, ph = ((i >> 1) & 1) ^ 1;
       const int page = a.page_table[(size_t)seq * a.max_pages + p0 + i];
       if (!mbar_wait_bounded(&k_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
       if (lane == 0) {
         mbar_expect_tx(&k_full[s], 16384);
-        tma_load_3d(sK + s * 16384, a.kv_map, &k_full[s], 0, kvh, page * APAGE);
-        tma_load_3d(sK + s * 16384 + 8192, a.kv_map, &k_full[s], 64, kvh, page * APAGE);
+        tma_load_3d_hint(sK + s * 16384, a.kv_map, &k_full[s], 0, kvh, page * APAGE, kvpol);
+        tma_load_3d_hint(sK + s * 16384 + 8192, a.kv_map, &k_full[s], 64, kvh, page * APAGE, kvpol);
       }
       if (!mbar_wait_bounded(&v_empty[s], ph, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, i); break; }
       if (lane == 0) {
         mbar_expect_tx(&v_full[s], 16384);
-        tma_load_3d(sV + s * 16384, a.kv_map, &v_full[s], 0, a.Hkv + kvh, page * APAGE);
-        tma_load_3d(sV + s * 16384 + 8192, a.kv_map, &v_full[s], 64, a.Hkv + kvh, page * APAGE);
+        tma_load_3d_hint(sV + s * 16384, a.kv_map, &v_full[s], 0, a.Hkv + kvh, page * APAGE, kvpol);
+        tma_load_3d_hint(sV + s * 16384 + 8192, a.kv_map, &v_full[s], 64, a.Hkv + kvh, page * APAGE, kvpol);
       }
       __syncwarp();
     }

@@ -35,21 +35,45 @@ static __global__ void attn_merge8_kernel(const float* __restrict__ part_o, cons
   const int t = blockIdx.x, vi = blockIdx.y * blockDim.x + threadIdx.x, vpr = D / 8;
   if (vi >= Hq * vpr) return;                     // whole warps leave together (Hq * D / 8 is a multiple of 32 with FP4 output)
   const int h = vi / vpr, d0 = (vi % vpr) * 8;
-  float M = sink ? sink[h] : -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(((size_t)s * T + t) * Hq + h) * 2]);
-  float L = sink ? __expf(sink[h] - M) : 0.f;
+  // Up to eight splits at a time, every load issued before the first use: the (m, l) pairs and the partial rows of all splits are
+  // in flight together (a loop that reads m, branches, then loads the row is one L2 round trip per split on a decode step's
+  // critical path).  Partial rows of empty splits (m = -inf) are loaded but not used; the buffers always cover every split.
+  const float sk = sink ? sink[h] : -INFINITY;
+  float M = sk, L = 0.f;
   float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int s = 0; s < n_splits; ++s) {
-    const float* ml = part_ml + (((size_t)s * T + t) * Hq + h) * 2;
-    const float m = ml[0];
-    if (m == -INFINITY) continue;
-    const float e = __expf(m - M);
-    L += ml[1] * e;
-    const float4* po = (const float4*)(part_o + (((size_t)s * T + t) * Hq + h) * D + d0);
-    const float4 a = po[0], b = po[1];
-    o[0] += a.x * e; o[1] += a.y * e; o[2] += a.z * e; o[3] += a.w * e;
-    o[4] += b.x * e; o[5] += b.y * e; o[6] += b.z * e; o[7] += b.w * e;
+  for (int s0 = 0; s0 < n_splits; s0 += 8) {
+    float2 ml[8]; float4 pa[8], pb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int s = min(s0 + j, n_splits - 1);
+      const size_t row = ((size_t)s * T + t) * Hq + h;
+      ml[j] = *(const float2*)(part_ml + row * 2);
+      const float4* po = (const float4*)(part_o + row * D + d0);
+      pa[j] = po[0]; pb[j] = po[1];
+    }
+    float Mn = M;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) if (s0 + j < n_splits) Mn = fmaxf(Mn, ml[j].x);
+    if (s0 == 0) {
+      if (sink) L = __expf(sk - Mn);                  // the sink's share first, as the one-pass form adds it
+    } else if (Mn != M && M != -INFINITY) {           // a later batch raised the maximum: rescale what was accumulated
+      const float r = __expf(M - Mn);
+      L *= r;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) o[q] *= r;
+    }
+    M = Mn;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (s0 + j < n_splits && ml[j].x != -INFINITY) {
+        const float e = __expf(ml[j].x - M);
+        L += ml[j].y * e;
+        o[0] += pa[j].x * e; o[1] += pa[j].y * e; o[2] += pa[j].z * e; o[3] += pa[j].w * e;
+        o[4] += pb[j].x * e; o[5] += pb[j].y * e; o[6] += pb[j].z * e; o[7] += pb[j].w * e;
+      }
+    }
   }
+
   const float inv = L > 0.f ? 1.f / L : 0.f;
   bf16 ob[8];
 #pragma unroll

@@ -267,6 +267,31 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(smem_u32(dst)), "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
+// Streamed operands (expert / projection weights, their scales, the KV pages of a decode step) are read once per step and are far
+// larger than L2: loaded with an evict-first policy they pass through without pushing out what the step's small kernels keep
+// re-reading from L2 between the big loads (activations, routing tables, norm weights - and the kernels' own instructions).
+__device__ __forceinline__ uint64_t l2_policy_stream() {
+  uint64_t p;
+#ifndef CA_NO_STREAM_HINT
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+#else
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+#endif
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_normal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_3d_hint(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, uint64_t pol) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+               ::"r"(smem_u32(dst)), "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(smem_u32(dst)), "l"((uint64_t)src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol) : "memory");
+}
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

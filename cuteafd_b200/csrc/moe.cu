@@ -28,7 +28,8 @@ __device__ __forceinline__ bool route_live(const RoutePack& p, int i) {
   return (tok % p.t_cap) < __ldcg(p.lane_T + tok / p.t_cap);
 }
 
-__device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
+// `ids_sh`: the routing table idx [T * k] when the calling block holds it in shared memory (it then need not come back from L2).
+__device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh, const int* ids_sh = nullptr) {
   // sh: [E_local] counts, [E_local] offsets/cursors, [T*k] staged ids (small batches)
   const int El = p.e_hi - p.e_lo;
   int* cnt = sh; int* cur = sh + El;
@@ -37,7 +38,7 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
   const int n = p.T * p.k;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     if (!route_live(p, i)) continue;
-    const int e = __ldcg(p.idx + i) - p.e_lo;
+    const int e = (ids_sh ? ids_sh[i] : __ldcg(p.idx + i)) - p.e_lo;
     if (e >= 0 && e < El) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
@@ -69,7 +70,7 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
   // (multi-lane tables need no agreement with the senders on row positions, so their larger cases take the atomic path)
   if (n <= (p.lane_T ? 256 : 4096)) {        // the quadratic ranking costs ~17 us at 1024 routes: lane tables switch to atomics early
     int* sid = cur + El;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = route_live(p, i) ? __ldcg(p.idx + i) - p.e_lo : -1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = route_live(p, i) ? (ids_sh ? ids_sh[i] : __ldcg(p.idx + i)) - p.e_lo : -1;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int e = sid[i];
@@ -82,7 +83,7 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh) {
     }
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const int e = route_live(p, i) ? __ldcg(p.idx + i) - p.e_lo : -1;
+      const int e = route_live(p, i) ? (ids_sh ? ids_sh[i] : __ldcg(p.idx + i)) - p.e_lo : -1;
       if (e >= 0 && e < El) { const int c = atomicAdd(&cur[e], 1); p.src_token[c] = i / p.k; p.slot_row[i] = c; if (p.src_route) p.src_route[c] = i; } else p.slot_row[i] = -1;
     }
   }
@@ -200,17 +201,18 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
 // path needs an 8-CTA cluster split-K to spread this 1 MB weight and still spends most of its ~14 us in launch and
 // cluster overheads; here 128 blocks read 8 KB of weights each and the token rows from L2.
 #define RL_TOK 16
-__global__ void __launch_bounds__(128) router_logits_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits,
+__global__ void __launch_bounds__(512) router_logits_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits,
                                                              int T, int E, int H) {
   pdl_launch(); pdl_wait();
-  __shared__ float red[RL_TOK][4];
+  __shared__ float red[RL_TOK][16];
+  const int nw = blockDim.x >> 5;
   const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bf16* wr = w + (size_t)e * H;
   for (int t0 = 0; t0 < T; t0 += RL_TOK) {
     float acc[RL_TOK];
 #pragma unroll
     for (int j = 0; j < RL_TOK; ++j) acc[j] = 0.f;
-    for (int c = tid; c < H / 8; c += 128) {
+    for (int c = tid; c < H / 8; c += blockDim.x) {
       const uint4 wv = *(const uint4*)(wr + c * 8);
       const bf162* wp = (const bf162*)&wv;
       float wf[8];
@@ -234,7 +236,11 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const bf16* __restri
       if (lane == 0) red[j][warp] = v;
     }
     __syncthreads();
-    if (tid < RL_TOK && t0 + tid < T) logits[(size_t)(t0 + tid) * E + e] = red[tid][0] + red[tid][1] + red[tid][2] + red[tid][3];
+    if (tid < RL_TOK && t0 + tid < T) {
+      float v = 0.f;
+      for (int q = 0; q < nw; ++q) v += red[tid][q];
+      logits[(size_t)(t0 + tid) * E + e] = v;
+    }
     __syncthreads();
   }
 }
@@ -242,16 +248,23 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const bf16* __restri
 extern "C" int cuteafd_router_logits(const void* x, const void* w, float* logits, int T, int E, int H, cudaStream_t s) {
   CA_REQUIRE(H % 8 == 0 && E >= 1, "router_logits: hidden size must be a multiple of 8");
   if (T <= 0) return CA_OK;
-  CA_LAUNCH_PDL(router_logits_kernel, E, 128, 0, s, (const bf16*)x, (const bf16*)w, logits, T, E, H);
+  // one 16-byte weight chunk per thread where the row allows it: every load of a token row is in flight at once
+  const int threads = H / 8 >= 512 ? 512 : (H / 8 >= 256 ? 256 : 128);
+  CA_LAUNCH_PDL(router_logits_kernel, E, threads, 0, s, (const bf16*)x, (const bf16*)w, logits, T, E, H);
   CA_CHECK_LAUNCH("router_logits");
   return CA_OK;
 }
+
+static int launch_router_select_warps(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k, int scoring, int normalize,
+                                      float route_scale, int n_group, int topk_group, cudaStream_t s);
 
 extern "C" int cuteafd_router_select(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k,
                                      int scoring, int normalize, float route_scale, int n_group, int topk_group, cudaStream_t s) {
   CA_REQUIRE(E >= k && E <= 512 && k >= 1 && k <= 16, "router_select: need k <= 16 and E <= 512 (E=%d k=%d)", E, k);
   CA_REQUIRE(n_group >= 1 && n_group <= 32 && E % n_group == 0, "router_select: bad group count");
   if (T <= 0) return CA_OK;
+  // decode / verify steps: the warp-per-token selection that the one-block select + pack kernel uses (identical picks and weights)
+  if (T <= 64) return launch_router_select_warps(logits, bias, idx, wts, T, E, k, scoring, normalize, route_scale, n_group, topk_group, s);
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
   RoutePack none{};
   none.wait = FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0};
@@ -347,7 +360,7 @@ extern "C" int cuteafd_router_hash_select(const float* logits, const int* tid2ei
 // One warp, one token: scores, optional group-limited routing, k rounds of argmax (value desc, expert id asc), gate weights.
 __device__ __forceinline__ void router_select_warp(const float* lg, const float* __restrict__ bias, float* score, float* choice, int E, int k,
                                                    int scoring, int normalize, float route_scale, int n_group, int topk_group,
-                                                   int* idx_out, float* wts_out) {
+                                                   int* idx_out, float* wts_out, int* sel_sh = nullptr) {
   const int lane = threadIdx.x & 31;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, __ldcg(lg + e));
@@ -408,7 +421,7 @@ __device__ __forceinline__ void router_select_warp(const float* lg, const float*
     __syncwarp();
   }
   const float inv = normalize ? 1.f / fmaxf(wsum, 1e-12f) : 1.f;
-  if (lane < k) { idx_out[lane] = mye; wts_out[lane] = myw * inv * route_scale; }
+  if (lane < k) { idx_out[lane] = mye; wts_out[lane] = myw * inv * route_scale; if (sel_sh) sel_sh[lane] = mye; }
 }
 
 __global__ void __launch_bounds__(RF_THREADS) router_fused_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits,
@@ -499,6 +512,49 @@ extern "C" int cuteafd_router_fused(const void* x, const void* w, float* logits,
   return CA_OK;
 }
 
+// Selection and packing of a decode-sized step by ONE block: a warp per token selects from the logits (no block barriers, no
+// arrival counter, no fences), the chosen experts stay in shared memory and the same block packs them - the chain is one round
+// trip to L2 for the logits instead of logits -> selections -> counter -> selections read back twice.
+__global__ void __launch_bounds__(RF_THREADS) router_select_block_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                                         int* __restrict__ idx, float* __restrict__ wts, int T, int E, int k,
+                                                                         int scoring, int normalize, float route_scale, int n_group,
+                                                                         int topk_group, const RoutePack pack) {
+  pdl_launch(); pdl_wait();
+  extern __shared__ int rs_sh[];                       // [T * k] chosen experts | [warps][2][E] scores | route-pack scratch
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* ids = rs_sh;
+  float* sc = (float*)(rs_sh + T * k) + (size_t)warp * 2 * E;
+  for (int t = warp; t < T; t += RF_WARPS) {
+    router_select_warp(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
+                       wts + (size_t)t * k, ids + t * k);
+    __syncwarp();
+  }
+  __syncthreads();
+  route_pack_body(pack, rs_sh + T * k + RF_WARPS * 2 * E, ids);
+}
+
+// Selection only, the same warp-per-token arithmetic (ranks of a multi-GPU layout whose experts live elsewhere must pick exactly
+// what the single-GPU engine picks): four tokens per block.
+__global__ void __launch_bounds__(128) router_select_warps_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx,
+                                                                  float* __restrict__ wts, int T, int E, int k, int scoring, int normalize,
+                                                                  float route_scale, int n_group, int topk_group) {
+  pdl_launch(); pdl_wait();
+  extern __shared__ int rs_sh[];
+  const int warp = threadIdx.x >> 5, t = blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  float* sc = (float*)rs_sh + (size_t)warp * 2 * E;
+  router_select_warp(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
+                     wts + (size_t)t * k);
+}
+
+static int launch_router_select_warps(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k, int scoring, int normalize,
+                                      float route_scale, int n_group, int topk_group, cudaStream_t s) {
+  CA_LAUNCH_PDL(router_select_warps_kernel, (T + 3) / 4, 128, (size_t)4 * 2 * E * sizeof(float), s, logits, bias, idx, wts, T, E, k, scoring, normalize,
+                route_scale, n_group, topk_group);
+  CA_CHECK_LAUNCH("router_select_warps");
+  return CA_OK;
+}
+
 // Router selection and route packing in one launch: the select block that finishes last packs the routes.
 extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k,
                                           int scoring, int normalize, float route_scale, int n_group, int topk_group,
@@ -512,9 +568,45 @@ extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias
   const int threads = E <= 64 ? 64 : (E <= 128 ? 128 : 256);
   RoutePack p{idx, src_token, slot_row, counts, offsets, (int4*)tiles, n_tiles, n_rows, src_route, T, k, e_lo, e_hi, tn, max_tiles, ticket,
               FlagWait{nullptr, nullptr, nullptr, 0ull, 0, 0}, nullptr, 0};
+  if (T <= 64) {      // decode / verify steps: one block selects (a warp per token) and packs from shared memory
+    const size_t smem = ((size_t)T * k + (size_t)RF_WARPS * 2 * E) * 4 + route_pack_smem(T, k, e_lo, e_hi);
+    if (smem <= 96 * 1024) {
+      if (smem > 48 * 1024) {
+        cudaError_t ce = cudaFuncSetAttribute(router_select_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (ce != cudaSuccess) return ca_cuda(ce, "router_select_pack: shared memory size");
+      }
+      p.ticket = nullptr;
+      CA_LAUNCH_PDL(router_select_block_kernel, 1, RF_THREADS, smem, s, logits, bias, idx, wts, T, E, k, scoring, normalize, route_scale, n_group,
+                    topk_group, p);
+      CA_CHECK_LAUNCH("router_select_block");
+      return CA_OK;
+    }
+  }
   CA_LAUNCH_PDL(router_select_kernel, T, threads, route_pack_smem(T, k, e_lo, e_hi), s, logits, bias, idx, wts, E, k, scoring, normalize, route_scale,
                 n_group, topk_group, p);
   return CA_OK;
+}
+
+// acc[0..8) += sum over the token's routes (slot order) of w * y[row][i .. i+8).  The routes are taken eight at a time: their row
+// numbers and weights first, then all eight rows in flight together - a loop that looks up one route, then loads its row, is a
+// chain of 2 k dependent round trips to L2 (about 10 us of the decode step's combine at k = 8).
+__device__ __forceinline__ void combine_routes8(const bf16* __restrict__ y, const int* __restrict__ rows, const float* __restrict__ wts, int k, int H,
+                                                int i, float* acc) {
+  for (int s0 = 0; s0 < k; s0 += 8) {
+    int r[8]; float w[8]; uint4 qv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { r[j] = (s0 + j < k) ? rows[s0 + j] : -1; w[j] = (s0 + j < k) ? wts[s0 + j] : 0.f; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) qv[j] = (r[j] >= 0) ? *(const uint4*)(y + (size_t)r[j] * H + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (r[j] >= 0) {
+        const bf16* e = (const bf16*)&qv[j];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += w[j] * __bfloat162float(e[q]);
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------- ordered weighted combine
@@ -530,15 +622,7 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ y, const int* __rest
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int sl = 0; sl < k; ++sl) {
-      const int r = slot_row[(size_t)t * k + sl];
-      if (r < 0) continue;
-      const float w = wts[(size_t)t * k + sl];
-      uint4 q = *(const uint4*)(y + (size_t)r * H + i);
-      const bf16* e = (const bf16*)&q;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += w * __bfloat162float(e[j]);
-    }
+    combine_routes8(y, slot_row + (size_t)t * k, wts + (size_t)t * k, k, H, i, acc);
     if (shared) { uint4 q = *(const uint4*)(shared + (size_t)t * H + i); const bf16* e = (const bf16*)&q;
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(e[j]); }
@@ -566,23 +650,19 @@ __global__ void moe_combine_norm_kernel(const bf16* __restrict__ y, const int* _
   if (!flag_wait_block(fw)) return;
   const int t = blockIdx.x;
   float v[VEC * 8];
+  float4 nw[VEC * 2];                 // the norm weights of this thread's elements, fetched with the rows (not after the reduction)
   float ss = 0.f;
+  const float inv_gs = (qkind == 1 && inv_gs_ptr) ? *inv_gs_ptr : 1.f;
 #pragma unroll
   for (int kk = 0; kk < VEC; ++kk) {
     const int i = (threadIdx.x + kk * blockDim.x) * 8;
+    nw[2 * kk] = nw[2 * kk + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < H) {
+      nw[2 * kk] = *(const float4*)(norm_w + i); nw[2 * kk + 1] = *(const float4*)(norm_w + i + 4);
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int sl = 0; sl < k; ++sl) {
-        const int r = slot_row[(size_t)t * k + sl];
-        if (r < 0) continue;
-        const float w = wts[(size_t)t * k + sl];
-        uint4 qv = *(const uint4*)(y + (size_t)r * H + i);
-        const bf16* e = (const bf16*)&qv;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += w * __bfloat162float(e[j]);
-      }
+      combine_routes8(y, slot_row + (size_t)t * k, wts + (size_t)t * k, k, H, i, acc);
       if (shared) { uint4 qv = *(const uint4*)(shared + (size_t)t * H + i); const bf16* e = (const bf16*)&qv;
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(e[j]); }
@@ -602,14 +682,14 @@ __global__ void moe_combine_norm_kernel(const bf16* __restrict__ y, const int* _
     if (i < H) {
       bf16 o[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16(v[kk * 8 + j] * inv * norm_w[i + j]);
+      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16(v[kk * 8 + j] * inv * ((const float*)&nw[2 * kk])[j]);
       if (xn) *(uint4*)(xn + (size_t)t * H + i) = *(uint4*)o;
       if (qkind) {
         float f[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(o[j]);
         if (qkind == 3) quant8_store_fp8b(f, q + (size_t)t * H, (float*)sf + (size_t)t * ldsf, i);
-        else quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)t * (H / 2), sf + (size_t)t * ldsf, i);
+        else quant8_store(f, qkind, qkind == 1 ? inv_gs : (inv_gs_ptr ? *inv_gs_ptr : 1.f), q + (size_t)t * (H / 2), sf + (size_t)t * ldsf, i);
       }
     }
   }

@@ -198,18 +198,21 @@ __global__ void __launch_bounds__(192, TcCfg<KIND, TN, SWIGLU>::OCC) tc_linear_k
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     uint32_t it = 0, npre = 0;
+    // decode-sized steps read every weight byte once: stream it through L2 without displacing the step's small data; larger steps
+    // re-read a weight tile for every token tile and want it kept
+    const uint64_t wpol = (dense ? a.rows_total <= TN : a.rows_total <= 1024) ? l2_policy_stream() : l2_policy_normal();
     // weight-side loads of one stage (static data: legal before the previous kernel has finished)
     auto load_weights = [&](int s, int g, int nt, int kb) {
       uint8_t* st = smem + s * C::STAGE_BYTES;
       uint8_t* sA = st, *sSFA = st + C::NA * C::A_BYTES + C::B_BYTES;
       mbar_expect_tx(&full_bar[s], C::NA * (KIND == KIND_W4A8 ? a.w4_tx : C::A_BYTES) + C::B_BYTES + C::NA * C::SFA_BYTES);
       const int kx = kb * (KIND == KIND_BF16 ? 64 : 128);      // elements of the descriptor's type
-      tma_load_3d(sA, a.tmA + g, &full_bar[s], kx, nt * 128, 0);
-      if (SWIGLU) tma_load_3d(sA + C::A_BYTES, a.tmA2 + g, &full_bar[s], kx, nt * 128, 0);
+      tma_load_3d_hint(sA, a.tmA + g, &full_bar[s], kx, nt * 128, 0, wpol);
+      if (SWIGLU) tma_load_3d_hint(sA + C::A_BYTES, a.tmA2 + g, &full_bar[s], kx, nt * 128, 0, wpol);
       if (KIND != KIND_BF16) {
         const size_t off = ((size_t)nt * nkb_all + (size_t)kb) * C::SF_CHUNKS * 512;   // scales are padded to whole stages
-        bulk_load_1d(sSFA, a.sfa[g] + off, C::SFA_BYTES, &full_bar[s]);
-        if (SWIGLU) bulk_load_1d(sSFA + C::SFA_BYTES, a.sfa2[g] + off, C::SFA_BYTES, &full_bar[s]);
+        bulk_load_1d_hint(sSFA, a.sfa[g] + off, C::SFA_BYTES, &full_bar[s], wpol);
+        if (SWIGLU) bulk_load_1d_hint(sSFA + C::SFA_BYTES, a.sfa2[g] + off, C::SFA_BYTES, &full_bar[s], wpol);
       }
     };
     if (dense) {
@@ -672,13 +675,14 @@ __global__ void __launch_bounds__(192, 1) tc_linear_cluster_kernel(const __grid_
 
   if (warp == 0) {
     // ---- producer: weights first (static), then wait for the previous kernel, then activations
+    const uint64_t wpol = a.rows_total <= TN ? l2_policy_stream() : l2_policy_normal();
     auto load_weights = [&](int s, int kb) {
       uint8_t* st = smem + s * C::STAGE_BYTES;
       uint8_t* sA = st, *sSFA = st + C::A_BYTES + C::B_BYTES;
       mbar_expect_tx(&full_bar[s], C::A_BYTES + C::B_BYTES + C::SFA_BYTES);
-      tma_load_3d(sA, a.tmA, &full_bar[s], kb * (KIND == KIND_BF16 ? 64 : 128), nt * 128, 0);
+      tma_load_3d_hint(sA, a.tmA, &full_bar[s], kb * (KIND == KIND_BF16 ? 64 : 128), nt * 128, 0, wpol);
       if (KIND != KIND_BF16)
-        bulk_load_1d(sSFA, a.sfa[0] + ((size_t)nt * nkb_all + (size_t)kb) * C::SF_CHUNKS * 512, C::SFA_BYTES, &full_bar[s]);
+        bulk_load_1d_hint(sSFA, a.sfa[0] + ((size_t)nt * nkb_all + (size_t)kb) * C::SF_CHUNKS * 512, C::SFA_BYTES, &full_bar[s], wpol);
     };
     const int npre = min(ring, kb1 - kb0);
     if (lane == 0)
