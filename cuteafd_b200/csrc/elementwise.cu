@@ -40,11 +40,15 @@ __global__ void add_rmsnorm_kernel(bf16* __restrict__ x, const bf16* __restrict_
   __shared__ float red[32];
   const size_t base = (size_t)blockIdx.x * H;
   float v[VEC * 8];
+  float4 nw[VEC * 2];                  // norm weights and the activation scale are fetched with the row, not after the reduction
+  const float inv_gs_pre = (qkind == 1 && inv_gs_ptr) ? *inv_gs_ptr : 1.f;
   float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
     const int i = (threadIdx.x + k * blockDim.x) * 8;
+    nw[2 * k] = nw[2 * k + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < H) {
+      nw[2 * k] = *(const float4*)(w + i); nw[2 * k + 1] = *(const float4*)(w + i + 4);
       uint4 q = *(const uint4*)(x + base + i);
       const bf16* e = (const bf16*)&q;
       if (delta) {
@@ -69,14 +73,14 @@ __global__ void add_rmsnorm_kernel(bf16* __restrict__ x, const bf16* __restrict_
     if (i < H) {
       bf16 o[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16(v[k * 8 + j] * inv * w[i + j]);
+      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16(v[k * 8 + j] * inv * ((const float*)&nw[2 * k])[j]);
       if (y) *(uint4*)(y + base + i) = *(uint4*)o;
       if (qkind) {      // H is a multiple of 256 here, so whole warps take this branch together
         float f[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(o[j]);
         if (qkind == 3) quant8_store_fp8b(f, q + (size_t)blockIdx.x * H, (float*)sf + (size_t)blockIdx.x * ldsf, i);
-        else quant8_store(f, qkind, inv_gs_ptr ? *inv_gs_ptr : 1.f, q + (size_t)blockIdx.x * (H / 2), sf + (size_t)blockIdx.x * ldsf, i);
+        else quant8_store(f, qkind, qkind == 1 ? inv_gs_pre : (inv_gs_ptr ? *inv_gs_ptr : 1.f), q + (size_t)blockIdx.x * (H / 2), sf + (size_t)blockIdx.x * ldsf, i);
       }
     }
   }
@@ -100,6 +104,7 @@ extern "C" int cuteafd_add_rmsnorm_quant(void* x, const void* delta, const float
 static int add_rmsnorm_launch(void* x, const void* delta, const float* w, void* y, int T, int H, float eps, void* q, void* sf, int ldsf,
                               const float* inv_gs, int qkind, cudaStream_t s) {
   CA_REQUIRE(H % 8 == 0 && H <= 32768, "add_rmsnorm: hidden %d unsupported", H);
+  CA_REQUIRE(((uintptr_t)w & 15) == 0, "add_rmsnorm: the norm weights must be 16-byte aligned");
   if (T <= 0) return CA_OK;
   const int vecs = H / 8;
   int threads = vecs >= 1024 ? 1024 : ((vecs + 31) / 32) * 32;
@@ -128,8 +133,13 @@ __global__ void qk_norm_rope_kvwrite_kernel(bf16* __restrict__ qkv, const int* _
   const bool is_q = h < Hq, is_k = !is_q && h < Hq + Hkv;
   // Each lane owns up to 4 rotation pairs.  Pair p is (2p, 2p+1) when interleaved, (p, p + D/2) otherwise.
   const int n_pairs = D / 2, ppl = (n_pairs + 31) / 32;
-  float a[4], b[4];
+  float a[4], b[4], wa[4], wb[4];
   int ia[4], ib[4];
+  // everything this warp reads from global memory is requested up front (row, norm weights, position, slot): one round trip to
+  // L2 instead of four in a row on the decode step's critical path
+  const float* nw = is_q ? q_norm : (is_k ? k_norm : nullptr);
+  const int pos_i = positions[t];
+  const int slot_pre = is_q ? 0 : slot_map[t];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int p = lane * ppl + j;
@@ -138,18 +148,19 @@ __global__ void qk_norm_rope_kvwrite_kernel(bf16* __restrict__ qkv, const int* _
     ib[j] = on ? (interleaved ? 2 * p + 1 : p + n_pairs) : -1;
     a[j] = on ? __bfloat162float(row[ia[j]]) : 0.f;
     b[j] = on ? __bfloat162float(row[ib[j]]) : 0.f;
+    wa[j] = (on && nw) ? nw[ia[j]] : 1.f;
+    wb[j] = (on && nw) ? nw[ib[j]] : 1.f;
   }
   if (is_q || is_k) {
-    const float* nw = is_q ? q_norm : k_norm;
     if (nw) {
       float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) ss += a[j] * a[j] + b[j] * b[j];
       const float inv = rsqrtf(warp_sum(ss) / D + eps);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) if (ia[j] >= 0) { a[j] *= inv * nw[ia[j]]; b[j] *= inv * nw[ib[j]]; }
+      for (int j = 0; j < 4; ++j) if (ia[j] >= 0) { a[j] *= inv * wa[j]; b[j] *= inv * wb[j]; }
     }
-    const float pos = (float)positions[t];
+    const float pos = (float)pos_i;
 #pragma unroll
     for (int j = 0; j < 4; ++j) if (ia[j] >= 0) {
       const int p = lane * ppl + j;
@@ -162,7 +173,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(bf16* __restrict__ qkv, const int* _
   }
   bf16* dst = row;
   if (!is_q) {
-    const int slot = slot_map[t];
+    const int slot = slot_pre;
     if (slot < 0 || slot >= n_slots) { if (lane == 0) ca_dev_fail(status, CA_DEV_BAD_INDEX, t); return; }
     dst = kv_cache + ((size_t)slot * 2 + (is_k ? 0 : 1)) * Hkv * D + (size_t)(h - Hq - (is_k ? 0 : Hkv)) * D;
   }
@@ -194,11 +205,16 @@ __global__ void quant_fp4_rows_kernel(const bf16* __restrict__ x, const int* __r
   pdl_launch(); pdl_wait();
   const int per_row = K / 16;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int n_rows = n_rows_dev ? min(*n_rows_dev, rows) : rows;
   const int r = (int)(gid / per_row), c = (int)(gid % per_row);
+  // the row count, the row's source and the activation scale are independent loads: issue them together (a decode step's quantiser
+  // is a chain of L2 round trips, not bandwidth)
+  const int n_dev = n_rows_dev ? *n_rows_dev : rows;
+  const int src_any = (r < rows) ? (src_rows ? src_rows[r] : r) : -1;
+  const float inv_gs_pre = (!MX && inv_gs_ptr) ? *inv_gs_ptr : 1.f;
+  const int n_rows = min(n_dev, rows);
   const bool active = r < n_rows;
   float v[16];
-  int src = active ? (src_rows ? src_rows[r] : r) : -1;
+  int src = active ? src_any : -1;
   if (src >= 0) {
     const uint4* p = (const uint4*)(x + (size_t)src * ldx + c * 16);
     uint4 a = p[0], b = p[1];
@@ -222,7 +238,7 @@ __global__ void quant_fp4_rows_kernel(const bf16* __restrict__ x, const int* __r
     sb = (uint8_t)e;
     eff = ue8m0_to_float(sb);
   } else {
-    const float inv_gs = inv_gs_ptr ? *inv_gs_ptr : 1.f;
+    const float inv_gs = inv_gs_pre;
     const float target = fminf(amax * inv_gs / 6.f, 448.f);
     sb = float_to_e4m3(target);
     eff = e4m3_to_float(sb) / inv_gs;

@@ -68,7 +68,38 @@ __device__ __forceinline__ void route_pack_body(const RoutePack& p, int* sh, con
   // earlier routes to its expert when T*k is small; larger batches use atomics (row order inside an expert does
   // not change any result: rows are independent in the GEMM and the combine reads them by index).
   // (multi-lane tables need no agreement with the senders on row positions, so their larger cases take the atomic path)
-  if (n <= (p.lane_T ? 256 : 4096)) {        // the quadratic ranking costs ~17 us at 1024 routes: lane tables switch to atomics early
+  if (n <= 256 && blockDim.x >= 256 && (blockDim.x & 31) == 0) {
+    // Decode-sized tables: stable ranks without the quadratic walk.  Each warp owns 32 consecutive routes; a route's rank inside its
+    // expert = routes to that expert in earlier warps (a per-warp histogram, summed) + lanes below it in its own warp with the same
+    // expert (match + population count).  The walk below costs ~2.5 us at 128 routes, this a few hundred cycles.
+    int* hist = cur + El;                                    // [8][El] routes per (warp chunk, expert); sized with the ids scratch
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nch = (n + 31) >> 5;
+    for (int i = threadIdx.x; i < nch * El; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    int e_mine = -1, below = 0;
+    if (warp < nch) {
+      const int i = warp * 32 + lane;
+      if (i < n && route_live(p, i)) e_mine = (ids_sh ? ids_sh[i] : __ldcg(p.idx + i)) - p.e_lo;
+      if (e_mine < 0 || e_mine >= El) e_mine = -1;
+      const unsigned same = __match_any_sync(0xffffffffu, e_mine);
+      below = __popc(same & ((1u << lane) - 1u));
+      if (e_mine >= 0 && below == 0) hist[warp * El + e_mine] = __popc(same);      // the lowest lane of each expert's group records it
+    }
+    __syncthreads();
+    if (warp < nch) {
+      const int i = warp * 32 + lane;
+      if (i < n) {
+        if (e_mine < 0) p.slot_row[i] = -1;
+        else {
+          int rank = below;
+          for (int w = 0; w < warp; ++w) rank += hist[w * El + e_mine];
+          const int c = cur[e_mine] + rank;
+          p.src_token[c] = i / p.k; p.slot_row[i] = c;
+          if (p.src_route) p.src_route[c] = i;
+        }
+      }
+    }
+  } else if (n <= (p.lane_T ? 256 : 4096)) {        // the quadratic ranking costs ~17 us at 1024 routes: lane tables switch to atomics early
     int* sid = cur + El;
     for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = route_live(p, i) ? (ids_sh ? ids_sh[i] : __ldcg(p.idx + i)) - p.e_lo : -1;
     __syncthreads();
@@ -99,7 +130,12 @@ __global__ void route_pack_kernel(const RoutePack p) {
   route_pack_body(p, sh);
 }
 
-static size_t route_pack_smem(int T, int k, int e_lo, int e_hi) { return (size_t)(2 * (e_hi - e_lo) + (T * k <= 4096 ? T * k : 0)) * sizeof(int); }
+static size_t route_pack_smem(int T, int k, int e_lo, int e_hi) {
+  const int El = e_hi - e_lo, n = T * k;
+  int extra = n <= 4096 ? n : 0;                               // staged ids of the quadratic ranking
+  if (n <= 256 && 8 * El > extra) extra = 8 * El;              // per-warp histograms of the decode-sized ranking
+  return (size_t)(2 * El + extra) * sizeof(int);
+}
 
 
 // One block per token.  logits fp32 [T, E] (E <= 512).  Selection uses score + bias (bias may be null),
@@ -358,21 +394,30 @@ extern "C" int cuteafd_router_hash_select(const float* logits, const int* tid2ei
 #define RF_WARPS (RF_THREADS / 32)
 
 // One warp, one token: scores, optional group-limited routing, k rounds of argmax (value desc, expert id asc), gate weights.
+template <int NQ>       // logits per lane: E <= 32 * NQ (short, straight code: this runs once per launch from a cold instruction cache)
 __device__ __forceinline__ void router_select_warp(const float* lg, const float* __restrict__ bias, float* score, float* choice, int E, int k,
                                                    int scoring, int normalize, float route_scale, int n_group, int topk_group,
                                                    int* idx_out, float* wts_out, int* sel_sh = nullptr) {
   const int lane = threadIdx.x & 31;
+  float lv[NQ];                                 // this lane's logits, one trip to L2 for all of them
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) lv[q] = (lane + 32 * q < E) ? __ldcg(lg + lane + 32 * q) : -INFINITY;
   float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, __ldcg(lg + e));
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) mx = fmaxf(mx, lv[q]);
   float denom = 1.f;
   if (scoring == SCORE_SOFTMAX) {
     mx = warp_max(mx);
     float s = 0.f;
-    for (int e = lane; e < E; e += 32) s += expf(__ldcg(lg + e) - mx);
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) if (lane + 32 * q < E) s += expf(lv[q] - mx);
     denom = warp_sum(s);
   }
-  for (int e = lane; e < E; e += 32) {
-    const float x = __ldcg(lg + e);
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    const int e = lane + 32 * q;
+    if (e >= E) continue;
+    const float x = lv[q];
     float sc;
     if (scoring == SCORE_SIGMOID) sc = 1.f / (1.f + expf(-x));
     else if (scoring == SCORE_SOFTMAX) sc = expf(x - mx) / denom;
@@ -478,8 +523,8 @@ __global__ void __launch_bounds__(RF_THREADS) router_fused_kernel(const bf16* __
   if (!is_last) return;
   float* sc = (float*)rf_sh + (size_t)warp * 2 * E;
   for (int t = warp; t < T; t += RF_WARPS)
-    router_select_warp(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
-                       wts + (size_t)t * k);
+    router_select_warp<16>(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
+                           wts + (size_t)t * k);
   __syncthreads();                                     // idx is complete (block-scope visibility is enough: the same block packs)
   if (do_pack) route_pack_body(pack, rf_sh);
   if (tid == 0) *pack.ticket = 0;
@@ -515,6 +560,7 @@ extern "C" int cuteafd_router_fused(const void* x, const void* w, float* logits,
 // Selection and packing of a decode-sized step by ONE block: a warp per token selects from the logits (no block barriers, no
 // arrival counter, no fences), the chosen experts stay in shared memory and the same block packs them - the chain is one round
 // trip to L2 for the logits instead of logits -> selections -> counter -> selections read back twice.
+template <int NQ>
 __global__ void __launch_bounds__(RF_THREADS) router_select_block_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                                                          int* __restrict__ idx, float* __restrict__ wts, int T, int E, int k,
                                                                          int scoring, int normalize, float route_scale, int n_group,
@@ -525,8 +571,8 @@ __global__ void __launch_bounds__(RF_THREADS) router_select_block_kernel(const f
   int* ids = rs_sh;
   float* sc = (float*)(rs_sh + T * k) + (size_t)warp * 2 * E;
   for (int t = warp; t < T; t += RF_WARPS) {
-    router_select_warp(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
-                       wts + (size_t)t * k, ids + t * k);
+    router_select_warp<NQ>(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
+                           wts + (size_t)t * k, ids + t * k);
     __syncwarp();
   }
   __syncthreads();
@@ -535,6 +581,7 @@ __global__ void __launch_bounds__(RF_THREADS) router_select_block_kernel(const f
 
 // Selection only, the same warp-per-token arithmetic (ranks of a multi-GPU layout whose experts live elsewhere must pick exactly
 // what the single-GPU engine picks): four tokens per block.
+template <int NQ>
 __global__ void __launch_bounds__(128) router_select_warps_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx,
                                                                   float* __restrict__ wts, int T, int E, int k, int scoring, int normalize,
                                                                   float route_scale, int n_group, int topk_group) {
@@ -543,14 +590,16 @@ __global__ void __launch_bounds__(128) router_select_warps_kernel(const float* _
   const int warp = threadIdx.x >> 5, t = blockIdx.x * 4 + warp;
   if (t >= T) return;
   float* sc = (float*)rs_sh + (size_t)warp * 2 * E;
-  router_select_warp(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
-                     wts + (size_t)t * k);
+  router_select_warp<NQ>(logits + (size_t)t * E, bias, sc, sc + E, E, k, scoring, normalize, route_scale, n_group, topk_group, idx + (size_t)t * k,
+                         wts + (size_t)t * k);
 }
 
 static int launch_router_select_warps(const float* logits, const float* bias, int* idx, float* wts, int T, int E, int k, int scoring, int normalize,
                                       float route_scale, int n_group, int topk_group, cudaStream_t s) {
-  CA_LAUNCH_PDL(router_select_warps_kernel, (T + 3) / 4, 128, (size_t)4 * 2 * E * sizeof(float), s, logits, bias, idx, wts, T, E, k, scoring, normalize,
-                route_scale, n_group, topk_group);
+#define CA_RSW(NQ) CA_LAUNCH_PDL(router_select_warps_kernel<NQ>, (T + 3) / 4, 128, (size_t)4 * 2 * E * sizeof(float), s, logits, bias, idx, wts, T, E, k, \
+                                 scoring, normalize, route_scale, n_group, topk_group)
+  if (E <= 128) CA_RSW(4); else if (E <= 256) CA_RSW(8); else CA_RSW(16);
+#undef CA_RSW
   CA_CHECK_LAUNCH("router_select_warps");
   return CA_OK;
 }
@@ -571,13 +620,17 @@ extern "C" int cuteafd_router_select_pack(const float* logits, const float* bias
   if (T <= 64) {      // decode / verify steps: one block selects (a warp per token) and packs from shared memory
     const size_t smem = ((size_t)T * k + (size_t)RF_WARPS * 2 * E) * 4 + route_pack_smem(T, k, e_lo, e_hi);
     if (smem <= 96 * 1024) {
-      if (smem > 48 * 1024) {
-        cudaError_t ce = cudaFuncSetAttribute(router_select_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        if (ce != cudaSuccess) return ca_cuda(ce, "router_select_pack: shared memory size");
-      }
       p.ticket = nullptr;
-      CA_LAUNCH_PDL(router_select_block_kernel, 1, RF_THREADS, smem, s, logits, bias, idx, wts, T, E, k, scoring, normalize, route_scale, n_group,
-                    topk_group, p);
+#define CA_RSB(NQ) do {                                                                                                                              \
+        if (smem > 48 * 1024) {                                                                                                                      \
+          cudaError_t ce = cudaFuncSetAttribute(router_select_block_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);             \
+          if (ce != cudaSuccess) return ca_cuda(ce, "router_select_pack: shared memory size");                                                       \
+        }                                                                                                                                            \
+        CA_LAUNCH_PDL(router_select_block_kernel<NQ>, 1, RF_THREADS, smem, s, logits, bias, idx, wts, T, E, k, scoring, normalize, route_scale,      \
+                      n_group, topk_group, p);                                                                                                       \
+      } while (0)
+      if (E <= 128) CA_RSB(4); else if (E <= 256) CA_RSB(8); else CA_RSB(16);
+#undef CA_RSB
       CA_CHECK_LAUNCH("router_select_block");
       return CA_OK;
     }
@@ -699,7 +752,7 @@ extern "C" int cuteafd_moe_combine_norm(const void* y, const int* slot_row, cons
                                         void* out, int T, int H, int k, const float* norm_w, float eps, void* xn, void* q, void* sf,
                                         int ldsf, const float* inv_gs, int qkind, const CaFlagWaitArg* wait, cudaStream_t s) {
   const FlagWait fw = ca_flag_wait_from(wait);
-  CA_REQUIRE(H % 8 == 0 && H <= 32768 && norm_w, "moe_combine_norm: bad arguments");
+  CA_REQUIRE(H % 8 == 0 && H <= 32768 && norm_w && ((uintptr_t)norm_w & 15) == 0, "moe_combine_norm: bad arguments (hidden %% 8, 16-byte aligned norm weights)");
   CA_REQUIRE(qkind == 0 || (qkind >= 1 && qkind <= 3 && q && sf && H % 256 == 0), "moe_combine_norm: quantised output needs buffers and hidden %% 256 == 0");
   if (T <= 0) return CA_OK;
   const int vecs = H / 8;

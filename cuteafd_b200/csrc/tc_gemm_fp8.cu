@@ -110,11 +110,12 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
 
   if (warp == 0) {
     // ---- producer: weight tiles first (static data), then wait for the previous kernel, then activation tiles
+    const uint64_t wpol = a.rows_total <= TN ? l2_policy_stream() : l2_policy_normal();    // one token tile: every weight byte is read once
     const int npre = min(ring, kb1 - kb0);
     if (lane == 0)
       for (int i = 0; i < npre; ++i) {
         mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
-        tma_load_3d(smem + i * C::STAGE_BYTES, a.tmA, &full_bar[i], (kb0 + i) * 128, nt * 128, 0);
+        tma_load_3d_hint(smem + i * C::STAGE_BYTES, a.tmA, &full_bar[i], (kb0 + i) * 128, nt * 128, 0, wpol);
       }
     pdl_wait();
     for (int kb = kb0, it = 0; kb < kb1 && !*abortp; ++kb, ++it) {
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
         if (!mbar_wait_bounded(&empty_bar[s], ((it / ring) & 1) ^ 1, abortp)) { ca_dev_fail(a.status, CA_DEV_TIMEOUT_PRODUCER, (int)blockIdx.x); break; }
         if (lane == 0) {
           mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
-          tma_load_3d(smem + s * C::STAGE_BYTES, a.tmA, &full_bar[s], kb * 128, nt * 128, 0);
+          tma_load_3d_hint(smem + s * C::STAGE_BYTES, a.tmA, &full_bar[s], kb * 128, nt * 128, 0, wpol);
         }
       }
       if (lane == 0) tma_load_3d(smem + s * C::STAGE_BYTES + C::A_BYTES, a.tmB, &full_bar[s], kb * 128, row0, 0);
