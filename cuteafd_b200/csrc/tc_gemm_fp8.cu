@@ -26,6 +26,7 @@ struct Fp8Args {
   const bf16* R;
   int* status;
   int ldy, rows_total, N, K, epi, splits;
+  int budget;               // bytes of shared memory for ring + staging + scale table: 200 KB (one CTA per SM) or 100 KB (two per SM)
 };
 
 template <int TN>
@@ -41,9 +42,9 @@ struct Fp8Cfg {
   __host__ __device__ static constexpr int table_bytes(int nk) { return nk * TN * 4 <= 64 * 1024 ? nk * TN * 4 : 0; }
   // decode-sized tiles keep one more staging tile: rank 0's own partial, so that the tile can be finished row-wise (16-byte stores)
   static constexpr int OWN = TN <= 32 ? 1 : 0;
-  __host__ __device__ static constexpr int ring(int S, int nk) {
-    return (BUDGET - (S - 1 + OWN) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES > MAX_RING
-               ? MAX_RING : (BUDGET - (S - 1 + OWN) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES;
+  __host__ __device__ static constexpr int ring(int S, int nk, int budget = BUDGET) {
+    return (budget - (S - 1 + OWN) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES > MAX_RING
+               ? MAX_RING : (budget - (S - 1 + OWN) * 128 * TN * 4 - table_bytes(nk)) / STAGE_BYTES;
   }
 };
 
@@ -54,7 +55,7 @@ __device__ __forceinline__ void f8_cluster_sync() {
 }
 
 template <int TN>
-__global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constant__ Fp8Args a) {
+__global__ void __launch_bounds__(192, (TN <= 32 ? 2 : 1)) fp8_linear_kernel(const __grid_constant__ Fp8Args a) {
   using C = Fp8Cfg<TN>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[C::MAX_RING], empty_bar[C::MAX_RING], accf_bar[C::NACC], acce_bar[C::NACC];
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(192, 1) fp8_linear_kernel(const __grid_constan
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int S = a.splits > 1 ? a.splits : 1;
   const int nk_max = ((a.K + 127) / 128 + S - 1) / S;                      // stages of the longest K slice
-  const int ring = C::ring(S, nk_max);
+  const int ring = C::ring(S, nk_max, a.budget);
   float* staging = (float*)(smem + ring * C::STAGE_BYTES);                 // [S-1][TN][128] fp32 on cluster rank 0
   float* sc_tab = staging + (size_t)(S - 1 + C::OWN) * 128 * TN;           // [stages of my slice][TN] combined scales
   const bool use_tab = C::table_bytes(nk_max) > 0;
@@ -301,7 +302,7 @@ static int fp8_launch(const Fp8Args& a, int grid, cudaStream_t stream) {
     attr_set[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = C::SMEM_BYTES; cfg.stream = stream;
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = a.budget + 1024; cfg.stream = stream;
   cudaLaunchAttribute at[2];
   int n_at = 0;
   if (a.splits > 1) {
@@ -320,6 +321,41 @@ static int fp8_launch(const Fp8Args& a, int grid, cudaStream_t stream) {
   return CA_OK;
 }
 
+static int fp8_budget(int tn, int splits, int K) {
+  if (tn <= 32) {
+    const int nk = ((K + 127) / 128 + splits - 1) / splits;
+    const int r = tn == 16 ? Fp8Cfg<16>::ring(splits, nk, 100 * 1024) : Fp8Cfg<32>::ring(splits, nk, 100 * 1024);
+    if (r >= 3) return 100 * 1024;
+  }
+  return 200 * 1024;
+}
+
+// Clusters of `splits` CTAs of the FP8 kernel that the device holds at once for this shape (a cluster needs its CTAs inside one GPC):
+// a split whose tile count exceeds this runs in two waves.
+template <int TN>
+static int fp8_capacity(int splits, int budget, int* out) {
+  auto kern = fp8_linear_kernel<TN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fp8Cfg<TN>::SMEM_BYTES);
+  if (e != cudaSuccess) return ca_cuda(e, "cudaFuncSetAttribute(fp8_linear)");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits * 64); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = budget + 1024;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  e = cudaOccupancyMaxActiveClusters(out, kern, &cfg);
+  if (e != cudaSuccess) return ca_cuda(e, "cudaOccupancyMaxActiveClusters");
+  return CA_OK;
+}
+
+extern "C" int cuteafd_fp8_cluster_capacity(int tn, int splits, int K, int* out) {
+  CA_REQUIRE(out && splits >= 1 && splits <= 8 && (tn == 16 || tn == 32 || tn == 64), "fp8_cluster_capacity: bad arguments");
+  const int budget = fp8_budget(tn, splits, K);
+  if (tn == 16) return fp8_capacity<16>(splits, budget, out);
+  if (tn == 32) return fp8_capacity<32>(splits, budget, out);
+  return fp8_capacity<64>(splits, budget, out);
+}
+
 extern "C" int cuteafd_fp8_linear(int tn, const void* tmA, const void* tmB, const float* sw, const float* sa, void* Y, const void* R,
                                   int ldy, int rows_total, int N, int K, int epi, int splits, int* status, cudaStream_t stream) {
   CA_REQUIRE(tmA && tmB && sw && sa && Y, "fp8_linear: null operand");
@@ -327,12 +363,15 @@ extern "C" int cuteafd_fp8_linear(int tn, const void* tmA, const void* tmB, cons
   CA_REQUIRE(epi == F8_EPI_BF16 || epi == F8_EPI_BF16_RESIDUAL || epi == F8_EPI_F32, "fp8_linear: bad epilogue %d", epi);
   CA_REQUIRE(epi != F8_EPI_BF16_RESIDUAL || R, "fp8_linear: residual epilogue needs R");
   if (splits < 1) splits = 1;
-  CA_REQUIRE(splits == 1 || ((splits == 2 || splits == 4 || (splits == 8 && tn == 16)) && tn <= 64),
-             "fp8_linear: split-K is 2- or 4-way for token tiles of up to 64 rows (8-way for 16 rows)");
+  CA_REQUIRE(splits == 1 || (splits >= 2 && splits <= (tn == 16 ? 8 : 4) && tn <= 64),
+             "fp8_linear: split-K is up to 4-way for token tiles of up to 64 rows (up to 8-way for 16 rows)");
   if (rows_total <= 0 || N <= 0) return CA_OK;
   Fp8Args a;
   a.tmA = (const CUtensorMap*)tmA; a.tmB = (const CUtensorMap*)tmB; a.sw = sw; a.sa = sa; a.Y = Y; a.R = (const bf16*)R; a.status = status;
   a.ldy = ldy; a.rows_total = rows_total; a.N = N; a.K = K; a.epi = epi; a.splits = splits;
+  // Decode-sized tiles: two CTAs per SM (half the shared memory each) when the split's staging area leaves a ring of >= 3 stages -
+  // the kernel is bound by its chain of tcgen05.mma issues per stage, and two CTAs run two such chains per SM.
+  a.budget = fp8_budget(tn, splits, K);
   const int grid = ((rows_total + tn - 1) / tn) * ((N + 127) / 128) * splits;
   switch (tn) {
     case 16: return fp8_launch<16>(a, grid, stream);

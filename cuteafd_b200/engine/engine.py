@@ -33,6 +33,7 @@ PREFILL_ATTN_MIN_Q = int(os.environ.get("CUTEAFD_PREFILL_ATTN_MIN_Q", "64"))
 
 # Decode-sized steps: router logits + selection + packing in one launch.  Opt-in: measured equal to the two-launch form on one GPU
 # (265.3 vs 265.4 us per layer) and 0.6 % slower on the multi-GPU layouts (one block selects for every token instead of a block per token).
+CLUSTER_KINDS = (KIND_BF16,) + tuple(FP4_KINDS)       # operand kinds with a cluster split-K kernel besides FP8
 ROUTER_FUSED = os.environ.get("CUTEAFD_ROUTER_FUSED", "0") == "1"
 
 
@@ -254,15 +255,27 @@ class Engine:
     # ------------------------------------------------------------------ kernels
     def _splits(self, N: int, K: int, T: int, tn: int, kind: int) -> int:
         """Split-K factor of a dense layer.  Decode-sized token tiles (<= 32 rows) split over a thread-block cluster
-        (2, 4 or 8 CTAs reduce through distributed shared memory): the largest power of two that still fits one wave
-        and leaves every CTA at least two pipeline stages of K."""
+        (up to 8 CTAs reduce through distributed shared memory): the largest split that still fits one wave - asked of the
+        device, since a cluster must sit inside one GPC - and leaves every CTA at least two pipeline stages of K."""
         tiles = -(-N // 128) * -(-T // tn)
         nkb = K // (64 if kind == KIND_BF16 else (128 if kind == KIND_FP8B else 256))
         if tiles >= self.sm_count or nkb < 4:
             return 1
+        if kind == KIND_FP8B and tn <= 32:
+            # decode-sized FP8 tiles run two CTAs per SM for splits of up to 4 (the kernel is bound by its per-stage chain of MMA issues):
+            # few tiles spread K over the widest cluster, otherwise the largest split that still fits one wave of 2 x SMs CTAs
+            # (a cluster needs its CTAs inside one GPC: the device holds e.g. only 15 clusters of 8, so the fit is asked, not computed)
+            if tn == 16:
+                for s in (8, 7, 6, 5):
+                    if nkb // s >= 2 and tiles <= ops.fp8_cluster_capacity(tn, s, K):
+                        return s
+            for s in (4, 2):      # measured: 224 CTAs of a 4-way split (two rounds of clusters) beat 112 CTAs of a 2-way split on the wo shape
+                if tiles * s <= 2 * self.sm_count and nkb // s >= 2:
+                    return s
+            return 1
         if tn <= 32 or (kind == KIND_FP8B and tn <= 64):      # the FP8 kernel's cluster reduction also takes 64-row tiles
             for s in ((8, 4, 2) if tn == 16 else (4, 2)):
-                if tiles * s <= self.sm_count and nkb // s >= 2:
+                if tiles * s <= self.sm_count and nkb // s >= 2 and (kind == KIND_FP8B or kind not in CLUSTER_KINDS or tiles <= ops.cluster_capacity(kind, tn, s)):
                     return s
             return 1
         # larger token tiles: global-memory fix-up (measured on B200: its cost grows with the split count, the sweet

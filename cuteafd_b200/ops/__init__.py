@@ -56,6 +56,16 @@ def cluster_capacity(kind: int, tn: int, splits: int) -> int:
     return _CLUSTER_CAP[key]
 
 
+def fp8_cluster_capacity(tn: int, splits: int, K: int) -> int:
+    """Clusters of `splits` CTAs of the FP8 block-scaled GEMM that fit the device at once for this K (cached per device)."""
+    key = (torch.cuda.current_device(), "fp8", tn, splits, K)
+    if key not in _CLUSTER_CAP:
+        out = ctypes.c_int(0)
+        call("cuteafd_fp8_cluster_capacity", tn, splits, K, ctypes.addressof(out))
+        _CLUSTER_CAP[key] = out.value
+    return _CLUSTER_CAP[key]
+
+
 def tc_trace(buf: torch.Tensor | None, units: int = 0) -> None:
     """Per-unit device time stamps of later `tc_linear` launches: int64 [grid, units, 8] (None = off)."""
     call("cuteafd_tc_trace", ptr(buf), units)
@@ -276,7 +286,7 @@ def tc_linear(w: TcWeight, x: ActBuffer, y: torch.Tensor | None, *, rows: int | 
     if w.kind == KIND_FP8B:
         if w_up is not None or tiles is not None or quant_out is not None or w.G != 1:
             raise ValueError("tc_linear: the FP8 block-scaled kernel is dense only (no SwiGLU / grouped / FP4 output)")
-        if splits not in (1, 2, 4, 8) or (splits > 1 and x.tn > 64) or (splits == 8 and x.tn != 16):
+        if splits < 1 or (splits > 1 and x.tn > 64) or splits > (8 if x.tn == 16 else 4):
             splits = 1
         call("cuteafd_fp8_linear", x.tn, ptr(w.tmap), ptr(x.tmap), ptr(w.sf), ptr(x.sf), ptr(y), ptr(residual), y.stride(0), rows, w.N, w.K,
              epi, splits, ptr(status), stream())

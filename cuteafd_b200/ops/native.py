@@ -46,6 +46,7 @@ _PROTOS = {
     "cuteafd_route_pack": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, P],
     "cuteafd_route_gather": [P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "cuteafd_tc_cluster_capacity": [I, I, I, P],
+    "cuteafd_fp8_cluster_capacity": [I, I, I, P],
     "cuteafd_router_fused": [P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P, P, P, P, P, P, P, I, I, I, I, P, P, P],
     "cuteafd_router_hash_select": [P, P, P, P, P, I, I, I, I, F, P, P],
     "cuteafd_moe_combine": [P, P, P, P, P, P, I, I, I, P, P],
