@@ -67,7 +67,10 @@ def fp8_cluster_capacity(tn: int, splits: int, K: int) -> int:
 
 
 def tc_trace(buf: torch.Tensor | None, units: int = 0) -> None:
-    """Per-unit device time stamps of later `tc_linear` launches: int64 [grid, units, 8] (None = off)."""
+    """Per-unit device time stamps of later `tc_linear` launches: int64 [grid, units, 8] (None = off).  `units < 0`: the cluster
+    split-K kernel records instead - its launches with N == -units write eight global-timer stamps per CTA into int64 [grid, 8]
+    (entry, -, released by the previous kernel, first stage landed, last MMA committed, accumulator complete, cluster barrier
+    passed, epilogue done); usable inside a replayed step graph, where the last such launch of the step survives."""
     call("cuteafd_tc_trace", ptr(buf), units)
 
 
