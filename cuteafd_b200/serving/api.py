@@ -179,7 +179,10 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         if vocab_size is None:
             return None
         eos = getattr(tok, "eos_id", None)
-        c = constraint_from_request(body, tok, vocab_size, prompt_len, eos)
+        try:
+            c = constraint_from_request(body, tok, vocab_size, prompt_len, eos)
+        except ValueError as e:          # a grammar or pattern that does not compile is the client's error
+            raise HTTPException(400, f"invalid response format: {e}") from None
         if c is None and isinstance(body.get("guided_choice"), list):
             c = ChoiceConstraint(tok, vocab_size, prompt_len, [str(x) for x in body["guided_choice"]], eos)
         if c is None and body.get("tools") and body.get("tool_choice") not in (None, "auto", "none"):

@@ -515,13 +515,16 @@ def token_pieces(tokenizer, vocab_size: int) -> list:
 
 class JsonConstraint(_TextConstraint):
     def __init__(self, tokenizer, vocab_size: int, prompt_len: int, eos_id: int | None = None, top: str | None = "object",
-                 schema: dict | None = None, regex: str | None = None):
+                 schema: dict | None = None, regex: str | None = None, grammar=None):
         super().__init__(tokenizer, vocab_size, prompt_len, eos_id)
-        self.top, self.schema, self.regex = top, schema, regex
+        self.top, self.schema, self.regex, self.grammar = top, schema, regex, grammar
         self.state, self.seen = self._fresh(), 0
         self.cache: dict = {}
 
     def _fresh(self):
+        if self.grammar is not None:
+            from .grammar import GrammarPrefix
+            return GrammarPrefix(self.grammar)
         if self.regex:
             return RegexPrefix(self.regex)
         return SchemaSet(self.schema) if self.schema else JsonPrefix(self.top)
@@ -685,6 +688,12 @@ def constraint_from_request(body: dict, tokenizer, vocab_size: int, prompt_len: 
         top = {"object": "object", "array": "array"}.get(schema.get("type"))
         enforce = any(k in schema for k in ("properties", "items", "required", "type", "anyOf", "oneOf", "$ref", "const", "pattern"))
         return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, top=top, schema=schema if enforce else None)
+    if kind == "grammar" or isinstance(body.get("guided_grammar"), str):
+        # the completion must be a sentence of an EBNF grammar (vLLM-style `guided_grammar`, or response_format.type = "grammar")
+        text = body.get("guided_grammar") or (rf.get("grammar") if isinstance(rf, dict) else None)
+        if isinstance(text, str) and text.strip():
+            from .grammar import Grammar
+            return JsonConstraint(tokenizer, vocab_size, prompt_len, eos_id, grammar=Grammar(text))      # compiled once per request; GrammarError -> 400
     if kind == "regex" or isinstance(body.get("guided_regex"), str):
         # the completion as a whole must match a regular expression (vLLM-style `guided_regex`, or response_format.type = "regex")
         pattern = body.get("guided_regex") or (rf.get("regex") or rf.get("pattern") if isinstance(rf, dict) else None)

@@ -1,0 +1,112 @@
+"""EBNF grammars for constrained decoding: parsing, the pushdown recogniser, token masks through the constraint interface."""
+import random
+import re
+
+import pytest
+
+from cuteafd_b200.serving.constraints import constraint_from_request, unpack_bits
+from cuteafd_b200.serving.grammar import Grammar, GrammarError, GrammarPrefix
+
+SQL = r'''
+# a toy SELECT statement
+root   ::= "SELECT " column (", " column)* " FROM " ident ( " WHERE " cond )? ";"
+column ::= ident | "*"
+cond   ::= ident " " op " " value
+op     ::= "=" | "<" | ">" | "<=" | ">="
+value  ::= [0-9]+ | "'" [^'\n]* "'"
+ident  ::= [a-zA-Z_] [a-zA-Z0-9_]*
+'''
+
+EXPR = r'''
+root ::= expr
+expr ::= term (("+" | "-") term)*
+term ::= factor (("*" | "/") factor)*
+factor ::= [0-9]+ | "(" expr ")"
+'''
+
+
+def accepts(g, text):
+    p = GrammarPrefix(g)
+    return p.feed_text(text) and p.complete
+
+
+def viable(g, text):
+    return GrammarPrefix(g).feed_text(text)
+
+
+def test_sentences_prefixes_and_rejections():
+    g = Grammar(SQL)
+    assert accepts(g, "SELECT a, b_2, * FROM t;")
+    assert accepts(g, "SELECT x FROM t WHERE x >= 10;") and accepts(g, "SELECT x FROM t WHERE name = 'o k';")
+    assert viable(g, "SELECT a, b") and not accepts(g, "SELECT a, b")
+    assert not viable(g, "SELECT 1") and not viable(g, "SELECT a FROM t WHERE x => 1")
+    assert not viable(g, "select")
+    p = GrammarPrefix(g)
+    assert p.feed_text("SELECT a FROM t;") and p.complete and p.finished()          # nothing may follow the semicolon
+    q = GrammarPrefix(g)
+    assert q.feed_text("SELECT a FROM t") and not q.complete and not q.finished()
+    # nesting is exact: a pushdown language no regular expression describes
+    e = Grammar(EXPR)
+    assert accepts(e, "((1+2)*(3-4))/5") and viable(e, "((1+2") and not accepts(e, "((1+2)") and not viable(e, "(1+2))")
+
+
+def test_repetition_bounds_escapes_and_any_char():
+    g = Grammar(r'root ::= "id-" [0-9]{2,4} ("\t" | "\x41" | "é") .{1} "\"" ')
+    assert accepts(g, 'id-12\tz"') and accepts(g, 'id-1234Aq"') and accepts(g, 'id-123é!"')
+    assert not viable(g, "id-1\t") and not viable(g, "id-12345") and viable(g, "id-12")
+    h = Grammar('root ::= ("ab")+ "c"? ')
+    assert accepts(h, "abab") and accepts(h, "abc") and not viable(h, "aa") and not accepts(h, "")
+    assert accepts(Grammar('root ::= "x"{3}'), "xxx") and not viable(Grammar('root ::= "x"{3}'), "xxxx")
+    assert accepts(Grammar('root ::= "x"{2,}'), "xxxxx") and not accepts(Grammar('root ::= "x"{2,}'), "x")
+
+
+def test_grammar_errors():
+    for bad in ('root ::= a', 'r ::= "x"', 'root ::= "x', 'root ::= [a-', 'root ::= ("x"', 'root ::= "a" root2\nroot ::= "b"', 'root ::= root "a" | "b"',
+                'root ::= [z-a]', 'root = "x"', 'root ::= "x"{3,2}'):
+        with pytest.raises(GrammarError):
+            Grammar(bad)
+
+
+class ByteTok:
+    """One token per byte value, plus a few multi-character tokens and the end-of-sequence token."""
+    extra = ["SELECT ", " FROM ", ", ", "ab", "  "]
+
+    def decode(self, ids):
+        return "".join(self.piece(i) for i in ids)
+
+    def piece(self, i):
+        return chr(i) if i < 256 else (self.extra[i - 256] if i - 256 < len(self.extra) else "")
+
+    def convert_ids_to_tokens(self, ids):
+        return [self.piece(i) for i in ids]
+
+
+def test_token_masks_drive_generation_to_a_sentence():
+    tok = ByteTok()
+    V, eos = 256 + len(ByteTok.extra) + 1, 256 + len(ByteTok.extra)
+    rng = random.Random(3)
+    done = 0
+    for trial in range(6):
+        c = constraint_from_request({"guided_grammar": SQL}, tok, V, 0, eos)
+        assert c is not None
+        toks = []
+        for _ in range(200):
+            allowed = [i for i, a in enumerate(unpack_bits(c.mask(toks), V)) if a]
+            assert allowed
+            closing = [a for a in allowed if a == eos or tok.piece(a) in (";", " FROM ", "t")]
+            toks.append(rng.choice(closing) if closing and rng.random() < 0.5 else rng.choice(allowed))
+            if toks[-1] == eos:
+                break
+        if toks[-1] == eos:
+            text = tok.decode(toks[:-1])
+            assert re.fullmatch(r"SELECT .* FROM [a-zA-Z_][a-zA-Z0-9_]*( WHERE .*)?;", text), text
+            assert GrammarPrefix(Grammar(SQL)).feed_text(text)
+            done += 1
+    assert done >= 1
+    # response_format form, and a multi-character token that the grammar allows only as a whole
+    c = constraint_from_request({"response_format": {"type": "grammar", "grammar": 'root ::= "SELECT " "ab"'}}, tok, V, 0, eos)
+    first = [i for i, a in enumerate(unpack_bits(c.mask([]), V)) if a]
+    assert set(first) == {ord("S"), 256}
+    after = [i for i, a in enumerate(unpack_bits(c.mask([256]), V)) if a]
+    assert set(after) == {ord("a"), 259}
+    assert [i for i, a in enumerate(unpack_bits(c.mask([256, 259]), V)) if a] == [eos]
