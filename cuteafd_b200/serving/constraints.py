@@ -198,10 +198,46 @@ class JsonPrefix:
 _FIRST = {"object": "{", "array": "[", "string": '"', "number": "-0123456789", "integer": "-0123456789", "boolean": "tf", "null": "n"}
 
 
+def _int_bounds(schema: dict):
+    """(lowest, highest) integer a schema's minimum / maximum / exclusive bounds allow, None for an open side."""
+    import math
+    lo = hi = None
+    for key, excl in (("minimum", False), ("exclusiveMinimum", True)):
+        v = schema.get(key)
+        if isinstance(v, (int, float)) and not isinstance(v, bool):
+            b = math.floor(v) + 1 if excl else math.ceil(v)
+            lo = b if lo is None else max(lo, b)
+    for key, excl in (("maximum", False), ("exclusiveMaximum", True)):
+        v = schema.get(key)
+        if isinstance(v, (int, float)) and not isinstance(v, bool):
+            b = math.ceil(v) - 1 if excl else math.floor(v)
+            hi = b if hi is None else min(hi, b)
+    return lo, hi
+
+
+def _int_prefix_ok(text: str, lo, hi) -> bool:
+    """Can the digits typed so far (optionally after a minus sign) still grow into an integer inside [lo, hi]?"""
+    neg = text.startswith("-")
+    d = text[1:] if neg else text
+    if not d:
+        return lo is None or lo <= 0                      # "-" so far: "-0" or a negative number must be allowed
+    base = int(d)
+    for extra in range(0, 24):
+        a, b = base * 10 ** extra, base * 10 ** extra + 10 ** extra - 1
+        if neg:
+            a, b = -b, -a
+        if (hi is None or a <= hi) and (lo is None or b >= lo):
+            return True
+        if d == "0" or (not neg and hi is not None and a > hi) or (neg and lo is not None and b < lo):
+            break                                         # a leading zero cannot grow; longer numbers only move further out
+    return False
+
+
 class SchemaPrefix:
     """`JsonPrefix` plus a cursor into a JSON schema, for the subset that covers tool arguments and typical
     `response_format` schemas: `type` (also a list of types), `properties`, `required`, `additionalProperties: false`,
-    `items`, string `enum`, `integer` vs `number`.  Anything else in a schema is ignored (not enforced)."""
+    `items`, string `enum`, `integer` vs `number`, `minimum` / `maximum` (also exclusive) of integers.  Anything else in a schema
+    is ignored (not enforced)."""
 
     def __init__(self, schema: dict, root: dict | None = None):
         self.j = JsonPrefix()
@@ -211,10 +247,12 @@ class SchemaPrefix:
         self.enum: list | None = None     # inside a string value restricted to choices: [choices, typed so far]
         self.pattern: list | None = None  # inside a string value restricted by `pattern`: [compiled regex, typed so far]
         self.integer = False
+        self.irange = None                # inside an integer with bounds: [lowest, highest, digits typed so far]
 
     def copy(self) -> "SchemaPrefix":
         c = SchemaPrefix.__new__(SchemaPrefix)
         c.j, c.cur, c.integer, c.root = self.j.copy(), self.cur, self.integer, self.root
+        c.irange = None if self.irange is None else list(self.irange)
         c.frames = [[f[0], f[1], set(f[2]), f[3]] for f in self.frames]
         c.enum = None if self.enum is None else [self.enum[0], self.enum[1]]
         c.pattern = None if self.pattern is None else [self.pattern[0], self.pattern[1]]
@@ -222,7 +260,8 @@ class SchemaPrefix:
 
     def signature(self):
         return (self.j.signature(), tuple((id(f[0]), f[1], frozenset(f[2]), f[3]) for f in self.frames), id(self.cur),
-                None if self.enum is None else self.enum[1], None if self.pattern is None else self.pattern[1], self.integer)
+                None if self.enum is None else self.enum[1], None if self.pattern is None else self.pattern[1], self.integer,
+                None if self.irange is None else tuple(self.irange))
 
     def finished(self) -> bool:
         return self.j.complete and not self.j.stack and self.j.mode == "after"
@@ -254,6 +293,10 @@ class SchemaPrefix:
 
     @property
     def complete(self) -> bool:
+        if self.j.complete and self.irange is not None:       # a top-level integer that may end here: only inside its bounds
+            lo, hi, typed = self.irange
+            if typed in ("", "-") or (lo is not None and int(typed) < lo) or (hi is not None and int(typed) > hi):
+                return False
         return self.j.complete
 
     @staticmethod
@@ -285,6 +328,13 @@ class SchemaPrefix:
                 self.pattern = [_compile_pattern(pat), ""]
         elif ch in "-0123456789":
             self.integer = "integer" in types and "number" not in types
+            self.irange = None
+            if self.integer:
+                lo, hi = _int_bounds(self.cur)
+                if lo is not None or hi is not None:
+                    self.irange = [lo, hi, ch]
+                    if not _int_prefix_ok(ch, lo, hi):
+                        return False
         return True
 
     def _close_ok(self, ch: str) -> bool:
@@ -309,8 +359,17 @@ class SchemaPrefix:
         m = self.j.mode
         if m == "number" and not (ch.isdigit() or ch in ".eE+-"):
             m = "after"                                         # the number ends here; `ch` is judged as what follows a value
+            if self.irange is not None:
+                lo, hi, typed = self.irange
+                self.irange = None
+                if typed in ("", "-") or (lo is not None and int(typed) < lo) or (hi is not None and int(typed) > hi):
+                    return False
         if m == "number" and self.integer and ch in ".eE":
             return False
+        if m == "number" and self.irange is not None and ch.isdigit():
+            self.irange[2] += ch
+            if not _int_prefix_ok(self.irange[2], self.irange[0], self.irange[1]):
+                return False
         if m == "key":
             f = self.frames[-1]
             props = f[0].get("properties") if isinstance(f[0].get("properties"), dict) else None

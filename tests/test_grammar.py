@@ -110,3 +110,24 @@ def test_token_masks_drive_generation_to_a_sentence():
     after = [i for i, a in enumerate(unpack_bits(c.mask([256]), V)) if a]
     assert set(after) == {ord("a"), 259}
     assert [i for i, a in enumerate(unpack_bits(c.mask([256, 259]), V)) if a] == [eos]
+
+
+def test_integer_bounds_of_a_json_schema():
+    from cuteafd_b200.serving.constraints import SchemaSet, _int_prefix_ok
+    assert _int_prefix_ok("1", 10, 99) and _int_prefix_ok("9", 10, 99) and not _int_prefix_ok("100", 10, 99) and not _int_prefix_ok("0", 10, 99)
+    assert _int_prefix_ok("-", -5, 5) and _int_prefix_ok("-5", -5, 5) and not _int_prefix_ok("-6", -5, 5) and not _int_prefix_ok("-", 1, 5)
+    assert _int_prefix_ok("12", 1000, None) and not _int_prefix_ok("12", None, 11) and _int_prefix_ok("-12", None, -100)
+    schema = {"type": "object", "properties": {"age": {"type": "integer", "minimum": 18, "maximum": 120}, "delta": {"type": "integer", "exclusiveMinimum": -3, "exclusiveMaximum": 3}},
+              "required": ["age"], "additionalProperties": False}
+
+    def ok(text, whole=True):
+        st = SchemaSet(schema)
+        return st.feed_text(text) and (st.complete or not whole)
+    assert ok('{"age": 18}') and ok('{"age":120, "delta": -2}') and ok('{"age": 42,"delta":0}')
+    assert not ok('{"age": 17}') and not ok('{"age": 121}') and not ok('{"age": 1}') and not ok('{"age": 30, "delta": 3}') and not ok('{"age": 30, "delta": -3}')
+    assert ok('{"age": 1', whole=False) and ok('{"age": 12', whole=False) and not ok('{"age": 13', whole=False) and not ok('{"age": 0', whole=False)
+    assert not ok('{"age": -', whole=False) and ok('{"age": 20, "delta": -', whole=False)
+    top = SchemaSet({"type": "integer", "minimum": 5, "maximum": 50})
+    assert top.feed_text("4") and not top.complete
+    top = SchemaSet({"type": "integer", "minimum": 5, "maximum": 50})
+    assert top.feed_text("42") and top.complete and not SchemaSet({"type": "integer", "minimum": 5, "maximum": 50}).feed_text("51")
