@@ -235,6 +235,12 @@ def ep_microbench_spec() -> ModelSpec:
                      quant=QuantSpec(experts="mxfp4"))
 
 
+def deepseek_v32_spec(n_layers: int = 61) -> ModelSpec:
+    """DeepSeek-V3.2-shape: the V3 shape with the sparse-attention indexer (64 index heads of 128, 2048 positions kept per query)."""
+    base = deepseek_v3_spec(n_layers)
+    return base.replace(name="deepseek-v32-shape", attn=dataclasses.replace(base.attn, index_topk=2048, index_heads=64, index_dim=128))
+
+
 def hybrid_gdn_spec(n_layers: int = 48, per_channel: bool = False) -> ModelSpec:
     """Hybrid linear-attention MoE shape (the Qwen-Next line): three gated delta-rule layers (16 q/k heads, 32 value heads of 128)
     then one full GQA layer (16q/2kv/128), hidden 2048, 128 experts top-8 I=768 + 1 shared, vocab 151936, bf16 dense projections and
@@ -252,6 +258,7 @@ NAMED_SPECS = {
     "hybrid-gdn": hybrid_gdn_spec,
     "hybrid-kda": lambda **kw: hybrid_gdn_spec(per_channel=True, **kw),
     "deepseek-v3": deepseek_v3_spec,
+    "deepseek-v32": deepseek_v32_spec,
     "qwen3-235b": qwen3_235b_spec,
     "ep-microbench": ep_microbench_spec,
 }
@@ -277,6 +284,7 @@ FAMILY_BY_ARCH = {
     "GlmMoeDsaForCausalLM": "glm_moe",
     "MiMoV2FlashForCausalLM": "mimo_v2",
     "MixtralForCausalLM": "mixtral",
+    "Qwen3NextForCausalLM": "hybrid_linear",
 }
 
 
@@ -316,15 +324,26 @@ def from_hf_config(cfg: dict | str | Path) -> ModelSpec:
                              rope_theta=cfg.get("rope_theta", 1e4),
                              q_lora_rank=cfg.get("q_lora_rank") or 0, kv_lora_rank=cfg["kv_lora_rank"],
                              qk_nope_head_dim=cfg["qk_nope_head_dim"], qk_rope_head_dim=cfg["qk_rope_head_dim"],
-                             v_head_dim=cfg["v_head_dim"])
+                             v_head_dim=cfg["v_head_dim"],
+                             # sparse attention with a learned indexer (the V3.2 / GLM-5 line)
+                             index_topk=cfg.get("index_topk") or 0, index_heads=cfg.get("index_n_heads") or 0,
+                             index_dim=cfg.get("index_head_dim") or 0)
     else:
         attn = AttentionSpec(kind="gqa", n_heads=heads, n_kv_heads=cfg.get("num_key_value_heads", heads),
                              head_dim=cfg.get("head_dim") or hidden // heads,
                              rope_theta=cfg.get("rope_theta", 1e4), rope_interleaved=False,
                              qk_norm=family in ("qwen3_moe", "qwen3_dense"),
                              window=cfg.get("sliding_window_size") or cfg.get("sliding_window") or 0)
+        if cfg.get("full_attention_interval") and cfg.get("linear_num_value_heads"):
+            # hybrid linear-attention stack (the Qwen-Next line): gated delta-rule layers, every n-th layer full attention
+            if cfg.get("linear_key_head_dim", 128) != 128 or cfg.get("linear_value_head_dim", 128) != 128 or cfg.get("linear_conv_kernel_dim", 4) != 4:
+                raise ValueError("linear-attention layers: 128-wide key / value heads and a width-4 convolution are supported")
+            attn = dataclasses.replace(attn, linear_every=int(cfg["full_attention_interval"]), linear_k_heads=int(cfg["linear_num_key_heads"]),
+                                       linear_v_heads=int(cfg["linear_num_value_heads"]), qk_norm=True)
         pattern = cfg.get("hybrid_layer_pattern")            # MiMo-V2: 0 = full attention, 1 = sliding window (+ sinks)
-        if pattern is None and cfg.get("layer_types"):
+        if attn.linear_every:
+            pattern = None                                    # `layer_types` then names the linear layers, not sliding windows
+        if pattern is None and cfg.get("layer_types") and not attn.linear_every:
             pattern = [0 if t == "full_attention" else 1 for t in cfg["layer_types"]]
         if pattern and any(pattern):
             full = [i for i, p in enumerate(pattern) if not p]

@@ -63,3 +63,23 @@ def test_runner_assigns_and_recycles_state_slots():
     assert r._slots_of([row(c, 0, 2)]) == [s[0]] and resets[-1] == [s[0]]
     # a preempted sequence restarts from position 0 in its own slot
     assert r._slots_of([row(b, 0, 4)]) == [s[1]] and resets[-1] == [s[1]]
+
+
+def test_hf_configs_of_hybrid_and_sparse_families_map_to_specs():
+    from cuteafd_b200.config import from_hf_config
+    s = from_hf_config({"architectures": ["Qwen3NextForCausalLM"], "hidden_size": 2048, "num_attention_heads": 16, "num_key_value_heads": 2, "head_dim": 128,
+                        "num_hidden_layers": 48, "vocab_size": 151936, "full_attention_interval": 4, "linear_num_key_heads": 16,
+                        "linear_num_value_heads": 32, "linear_key_head_dim": 128, "linear_value_head_dim": 128, "linear_conv_kernel_dim": 4,
+                        "num_experts": 512, "num_experts_per_tok": 10, "moe_intermediate_size": 512,
+                        "layer_types": ["linear_attention"] * 3 + ["full_attention"]})
+    assert s.family == "hybrid_linear" and (s.attn.linear_every, s.attn.linear_k_heads, s.attn.linear_v_heads) == (4, 16, 32)
+    assert [s.layer_is_linear(i) for i in range(8)] == [True, True, True, False] * 2 and s.attn.full_every == 0
+    with pytest.raises(ValueError):
+        from_hf_config({"architectures": ["Qwen3NextForCausalLM"], "hidden_size": 2048, "num_attention_heads": 16, "num_hidden_layers": 4, "vocab_size": 1000,
+                        "full_attention_interval": 4, "linear_num_key_heads": 16, "linear_num_value_heads": 32, "linear_key_head_dim": 256})
+    d = from_hf_config({"architectures": ["DeepseekV32ForCausalLM"], "hidden_size": 7168, "num_attention_heads": 128, "kv_lora_rank": 512, "q_lora_rank": 1536,
+                        "qk_nope_head_dim": 128, "qk_rope_head_dim": 64, "v_head_dim": 128, "num_hidden_layers": 61, "vocab_size": 129280,
+                        "index_topk": 2048, "index_n_heads": 64, "index_head_dim": 128, "n_routed_experts": 256, "num_experts_per_tok": 8,
+                        "moe_intermediate_size": 2048})
+    assert (d.attn.index_topk, d.attn.index_heads, d.attn.index_dim) == (2048, 64, 128)
+    assert spec_by_name("deepseek-v32", n_layers=4).attn.index_topk == 2048
