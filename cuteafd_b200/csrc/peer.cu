@@ -360,7 +360,11 @@ __global__ void dispatch_tok_push_kernel(const DispatchTokArgs a) {
   extern __shared__ uint8_t sh[];
   __shared__ unsigned owners;
   const int t = a.T0 + blockIdx.x;
-  const bool live = t < a.T1 && !a.ctl[0];
+  // the abort word, the activation scale and this token's routes are independent reads: requested together, ahead of the row
+  const uint32_t abort_w = a.ctl[0];
+  const float inv_gs_pre = (a.kind == 1 && a.inv_gs) ? *a.inv_gs : 1.f;
+  const int e_pre = (t < a.T1 && (int)threadIdx.x < a.k) ? a.idx[(size_t)t * a.k + threadIdx.x] : -1;
+  const bool live = t < a.T1 && !abort_w;
   const int H = a.H;
   const int row_bytes = a.kind == 0 ? H * 2 : (a.kind == 4 ? H : H / 2);
   const int n_sf = a.kind == 0 ? 0 : (a.kind == 1 ? H / 16 : H / 32);
@@ -368,9 +372,9 @@ __global__ void dispatch_tok_push_kernel(const DispatchTokArgs a) {
   if (threadIdx.x == 0) owners = 0u;
   __syncthreads();
   if (live) {
-    quant_row_to_smem(a.x + (size_t)t * H, H, a.kind, (a.kind == 1 && a.inv_gs) ? *a.inv_gs : 1.f, pay, sfs);
+    quant_row_to_smem(a.x + (size_t)t * H, H, a.kind, inv_gs_pre, pay, sfs);
     if ((int)threadIdx.x < a.k) {
-      const int e = a.idx[(size_t)t * a.k + threadIdx.x];
+      const int e = e_pre;
       int owner = -1;
       for (int o = 0; o < a.n_ep; ++o) if (e >= (o * a.E) / a.n_ep && e < ((o + 1) * a.E) / a.n_ep) owner = o;
       if (owner < 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, t);
@@ -378,7 +382,7 @@ __global__ void dispatch_tok_push_kernel(const DispatchTokArgs a) {
       for (int d = 0; d < a.n_ep; ++d) ((int*)a.idx_dst.p[d])[(size_t)t * a.k + threadIdx.x] = e;
     }
   }
-  if (blockIdx.x == 0 && threadIdx.x == 32 && !a.ctl[0])
+  if (blockIdx.x == 0 && threadIdx.x == 32 && !abort_w)
     for (int d = 0; d < a.n_ep; ++d) *(int*)a.lane_t_dst.p[d] = a.T;
   __syncthreads();
   if (live) {
@@ -422,7 +426,7 @@ extern "C" int cuteafd_dispatch_tok_push(const void* x, const int* idx, const vo
     attr_set[dev & 63] = true;
   }
   CA_REQUIRE(smem <= 64 * 1024, "dispatch_tok_push: row does not fit shared memory");
-  dispatch_tok_push_kernel<<<blocks, 128, smem, s>>>(a);
+  dispatch_tok_push_kernel<<<blocks, 256, smem, s>>>(a);      // one 16-element group per thread at hidden 4096: the row is one round of loads
   CA_CHECK_LAUNCH("dispatch_tok_push");
   return CA_OK;
 }
@@ -481,10 +485,14 @@ struct CombineLanesArgs {
 };
 
 __global__ void combine_push_lanes_kernel(const CombineLanesArgs a) {
-  const int n = min(*a.n_rows, a.rows_cap);
-  if (!a.ctl[0]) {
+  // row count, abort word and this block's first route are independent reads (the first route's slot is always inside the buffer)
+  const int n_dev = *a.n_rows;
+  const uint32_t abort_w = a.ctl[0];
+  const int route0 = ((int)blockIdx.x < a.rows_cap) ? a.src_route[blockIdx.x] : -1;
+  const int n = min(n_dev, a.rows_cap);
+  if (!abort_w) {
     for (int r = blockIdx.x; r < n; r += gridDim.x) {
-      const int route = a.src_route[r];
+      const int route = (r == (int)blockIdx.x) ? route0 : a.src_route[r];
       const int tok = route / a.k, slot = route - tok * a.k;
       const int lane = tok / a.t_cap, t = tok - lane * a.t_cap;
       if (route < 0 || (lane + 1) * a.tp > a.n_dst) { if (threadIdx.x == 0) ca_dev_fail(a.status, CA_DEV_BAD_INDEX, r); continue; }
