@@ -129,7 +129,7 @@ def test_tc_linear_w4a8_dense(T, N, K):
 
 
 @pytest.mark.parametrize("kind", ["bf16", "nvfp4", "mxfp4"])
-@pytest.mark.parametrize("T,splits", [(5, 2), (16, 4), (16, 8), (30, 4), (9, 3)])
+@pytest.mark.parametrize("T,splits", [(5, 2), (16, 4), (16, 8), (30, 4), (9, 3), (16, 5), (12, 6), (16, 7), (30, 3)])
 def test_tc_linear_split_k_variants_match_unsplit(kind, T, splits):
     """Cluster split-K (2/4/8-way, reduced through distributed shared memory; K slices longer than the stage ring
     recycle stages) and the global-memory fix-up (3-way) against the unsplit kernel: same values up to the
@@ -622,6 +622,7 @@ def test_router_select_pack_matches_two_kernels(T, E, k, e_lo, e_hi):
 
 # ------------------------------------------------------------------ FP8 with 128 x 128 / 1 x 128 fp32 block scales
 @pytest.mark.parametrize("T,N,K,splits", [(3, 128, 256, 1), (16, 384, 512, 2), (16, 256, 7168, 8), (70, 256, 1024, 1), (128, 130, 768, 1),
+                                          (16, 2048, 7168, 6), (11, 640, 7168, 7), (16, 256, 2048, 5), (30, 384, 1536, 3), (16, 7168, 2048, 4), (1, 24576, 1536, 1),
                                           (30, 256, 2048, 4), (9, 1536, 7168, 8), (64, 256, 7168, 4), (50, 1536, 1536, 2)])
 def test_fp8_block_linear(T, N, K, splits):
     g = torch.Generator().manual_seed(T + N + K)
@@ -839,3 +840,13 @@ def test_router_fused_matches_the_three_kernels(T, E, H, k, scoring, ng, tg, bia
     ops.router_fused(x, W, e["lg"], b, e["idx"], e["wts"], T, k, scoring, True, 2.5, ng, tg)
     torch.cuda.synchronize()
     assert torch.equal(e["idx"], c["idx"]) and torch.equal(e["wts"], c["wts"]) and bool((e["slot"] == -7).all())
+
+
+def test_cluster_capacity_queries():
+    """How many split-K clusters the device holds at once: monotone in the cluster size, never above SMs / size (x2 for the FP8 kernel's
+    two-CTA form), and small enough for 8-CTA clusters that the split heuristics must ask instead of dividing."""
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    caps = [ops.cluster_capacity(ops.KIND_NVFP4, 16, s) for s in range(1, 9)]
+    assert caps[0] == sm and all(a >= b for a, b in zip(caps, caps[1:])) and all(1 <= c <= sm // (i + 1) for i, c in enumerate(caps))
+    f8 = [ops.fp8_cluster_capacity(16, s, 7168) for s in range(1, 9)]
+    assert all(a >= b for a, b in zip(f8, f8[1:])) and all(1 <= c <= 2 * sm // (i + 1) for i, c in enumerate(f8))
