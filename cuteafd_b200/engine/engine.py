@@ -33,6 +33,7 @@ PREFILL_ATTN_MIN_Q = int(os.environ.get("CUTEAFD_PREFILL_ATTN_MIN_Q", "64"))
 
 # Decode-sized steps: router logits + selection + packing in one launch.  Opt-in: measured equal to the two-launch form on one GPU
 # (265.3 vs 265.4 us per layer) and 0.6 % slower on the multi-GPU layouts (one block selects for every token instead of a block per token).
+FP8_FUSE_GATE_UP = os.environ.get("CUTEAFD_FP8_FUSE_GATE_UP", "1") != "0"      # FP8 dense FFNs: gate and up projections as one GEMM
 CLUSTER_KINDS = (KIND_BF16,) + tuple(FP4_KINDS)       # operand kinds with a cluster split-K kernel besides FP8
 ROUTER_FUSED = os.environ.get("CUTEAFD_ROUTER_FUSED", "0") == "1"
 
@@ -437,7 +438,21 @@ class Engine:
             xq, self._ffn_in_quantised = L.xq, False
         else:
             xq = self._quant(L.xn, L.xq, T, lw.ws_gate.inv_act_gs)
-        if lw.ws_gate.kind == KIND_FP8B:      # no fused SwiGLU epilogue in the FP8 kernel: two GEMMs + silu(g) * u
+        inter = lw.ws_gate.N
+        if lw.ws_gate.kind == KIND_FP8B and s_act.kind == KIND_FP8B and inter % 256 == 0 and FP8_FUSE_GATE_UP:
+            # no SwiGLU epilogue in the FP8 kernel, but gate and up read the same operand: ONE GEMM over the stacked weight, then
+            # silu(g) * u straight into the FP8 operand of the down projection
+            gu = getattr(lw, "ws_gate_up", None)
+            if gu is None:
+                gu = lw.ws_gate_up = ops.TcWeight.fuse_rows_fp8(lw.ws_gate, lw.ws_up)
+            key = ("gu", inter)
+            if key not in L.ffn_bufs:
+                L.ffn_bufs[key] = torch.zeros(L.cap, 2 * inter, dtype=torch.bfloat16, device=self.device)
+            s_gu = L.ffn_bufs[key]
+            self._dense(gu, xq, s_gu, T)
+            native.call("cuteafd_silu_mul_quant_fp8b", ptr(s_gu), ptr(s_gu) + inter * 2, ptr(s_act.data), ptr(s_act.sf), T, inter, 2 * inter, native.stream())
+            self.launches_per_step += 1
+        elif lw.ws_gate.kind == KIND_FP8B:    # two GEMMs + silu(g) * u
             key = ("up", lw.ws_gate.N)
             if key not in L.ffn_bufs:
                 L.ffn_bufs[key] = torch.zeros_like(s1)

@@ -63,7 +63,9 @@ class LayerWeights:
 
     def nbytes(self) -> int:
         n = 0
-        for v in vars(self).values():
+        for name, v in vars(self).items():
+            if name == "ws_gate_up":         # the fused gate + up weight: ws_gate and ws_up are views into it
+                continue
             if isinstance(v, TcWeight):
                 n += v.nbytes
             elif isinstance(v, torch.Tensor):

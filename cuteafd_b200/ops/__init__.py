@@ -153,6 +153,21 @@ class TcWeight:
         return TcWeight._finish(kind, G, N, K, data, sf, torch.tensor(alphas, dtype=torch.float32, device=device), act_gs)
 
     @staticmethod
+    def fuse_rows_fp8(a: "TcWeight", b: "TcWeight") -> "TcWeight":
+        """One FP8 block-scaled weight [N_a + N_b, K] out of two with the same K (gate and up projections read the same operand:
+        one GEMM instead of two).  `a` and `b` become views into the fused storage, so nothing is held twice."""
+        if a.kind != KIND_FP8B or b.kind != KIND_FP8B or a.G != 1 or b.G != 1 or a.K != b.K or a.N % 128 or b.N % 128:
+            raise ValueError("fuse_rows_fp8: two dense FP8 weights with the same K and row counts that are multiples of 128")
+        data = torch.cat([a.data, b.data], 1).contiguous()
+        sf = torch.cat([a.sf, b.sf], 1).contiguous()
+        fused = TcWeight(KIND_FP8B, 1, a.N + b.N, a.K, data, encode_tmap(data, 128), sf)
+        na, ra = a.N, a.N // 128
+        a.data, a.sf = data[:, :na], sf[:, :ra]
+        b.data, b.sf = data[:, na:], sf[:, ra:]
+        a.tmap, b.tmap = encode_tmap(a.data, 128), encode_tmap(b.data, 128)
+        return fused
+
+    @staticmethod
     def random(G: int, N: int, K: int, kind: str | int, device, std: float = 0.02, act_gs: float = 1.0 / 64,
                seed: int = 0, groups: tuple | None = None) -> "TcWeight":
         """Random-init weights generated directly in the storage format on the device (large synthetic models).
