@@ -42,12 +42,21 @@ def layer_stems(spec: ModelSpec, i: int, prefix: str | None = None) -> dict:
             s.update(wq=f"{p}.self_attn.q_proj")
         s.update(wkv_a=f"{p}.self_attn.kv_a_proj_with_mqa", kv_a_norm=f"{p}.self_attn.kv_a_layernorm",
                  wkv_b=f"{p}.self_attn.kv_b_proj", wo=f"{p}.self_attn.o_proj")
+        if a.index_topk:           # sparse-attention indexer
+            s.update(wq_idx=f"{p}.self_attn.indexer.wq_b", wk_idx=f"{p}.self_attn.indexer.wk", w_idx=f"{p}.self_attn.indexer.weights_proj")
+    elif spec.layer_is_linear(i) and prefix is None:      # gated delta-rule layer (MTP draft layers are full-attention layers)
+        q = f"{p}.linear_attn"
+        s.update(w_qkvz=f"{q}.in_proj_qkvz", w_ba=f"{q}.in_proj_ba", conv_w=f"{q}.conv1d", dt_bias=f"{q}.dt_bias", a_log=f"{q}.A_log",
+                 lin_norm=f"{q}.norm", wo=f"{q}.out_proj")
     else:
         s.update(wq=f"{p}.self_attn.q_proj", wk=f"{p}.self_attn.k_proj", wv=f"{p}.self_attn.v_proj", wo=f"{p}.self_attn.o_proj")
         if a.qk_norm:
             s.update(q_norm=f"{p}.self_attn.q_norm", k_norm=f"{p}.self_attn.k_norm")
         if spec.layer_has_sink(i):
             s.update(sink=f"{p}.self_attn.sinks")
+    if spec.hyper_streams:          # hyper-connections: projection / scale / base of the boundary in front of each block
+        for blk in ("attn", "ffn"):
+            s.update({f"hc_{blk}_fn": f"{p}.hc_{blk}.fn", f"hc_{blk}_scale": f"{p}.hc_{blk}.scale", f"hc_{blk}_base": f"{p}.hc_{blk}.base"})
     if spec.is_moe_layer(i):
         s.update(router=f"{p}.mlp.gate")
         if m.use_bias:
@@ -63,7 +72,9 @@ def layer_stems(spec: ModelSpec, i: int, prefix: str | None = None) -> dict:
     return s
 
 
-VECTORS = ("attn_norm", "ffn_norm", "q_norm", "k_norm", "q_a_norm", "kv_a_norm", "sink", "router_bias")
+VECTORS = ("attn_norm", "ffn_norm", "q_norm", "k_norm", "q_a_norm", "kv_a_norm", "sink", "router_bias", "lin_norm")
+# small fp32 tensors stored as they are (`<stem>.weight`, F32): convolution taps, decay parameters, hyper-connection coefficients
+PLAIN_F32 = ("conv_w", "dt_bias", "a_log", "hc_attn_fn", "hc_attn_scale", "hc_attn_base", "hc_ffn_fn", "hc_ffn_scale", "hc_ffn_base")
 
 
 def _is_expert(key: str) -> bool:
@@ -108,6 +119,9 @@ def export_snapshot(spec: ModelSpec, masters: dict, path: str | Path, *, dense: 
     out, dt = shard(0)
     out["model.embed_tokens.weight"] = masters["embed"].to(torch.bfloat16)
     out["model.norm.weight"] = masters["final_norm"].to(torch.bfloat16)
+    if spec.hyper_streams:
+        for k in ("fn", "scale", "base"):
+            out[f"model.hc_head.{k}.weight"] = masters[f"hc_head_{k}"].to(torch.float32).contiguous()
     if not spec.tie_embeddings:
         out["lm_head.weight"] = masters["lm_head"].to(torch.bfloat16)
 
@@ -119,6 +133,10 @@ def export_snapshot(spec: ModelSpec, masters: dict, path: str | Path, *, dense: 
             if key in VECTORS:
                 name = stem if key == "router_bias" or key == "sink" else f"{stem}.weight"
                 out[name] = lw[key].to(torch.float32 if key in ("router_bias", "sink") else torch.bfloat16)
+            elif key in PLAIN_F32:
+                out[f"{stem}.weight"] = lw[key].to(torch.float32).contiguous()
+            elif key in ("w_ba", "wq_idx", "wk_idx", "w_idx"):      # projections the kernels keep in bf16 whatever the dense format
+                _emit(out, dt, stem, lw[key], "bf16")
             elif _is_expert(key):
                 _emit(out, dt, stem, lw[base][int(key.split(".")[1])], experts, input_amax)
             elif key == "router" or key == "wkv_b":
@@ -194,7 +212,7 @@ def read_masters(snapshot: str | Path, spec: ModelSpec) -> dict:
         lw, stems = {}, layer_stems(spec, i, prefix)
         experts: dict = {}
         for key, stem in stems.items():
-            if key in VECTORS:
+            if key in VECTORS or key in PLAIN_F32:
                 lw[key] = _vector(ops, stem, key)
             elif _is_expert(key):
                 experts.setdefault(key.split(".")[0], []).append(_dequant(ops[stem]))
@@ -208,6 +226,9 @@ def read_masters(snapshot: str | Path, spec: ModelSpec) -> dict:
          "final_norm": read_tensor(ops["model.norm"].members["weight"]).float(),
          "layers": [layer(i) for i in range(spec.n_layers)]}
     w["lm_head"] = w["embed"] if spec.tie_embeddings else read_tensor(ops["lm_head"].members["weight"]).float()
+    if spec.hyper_streams:
+        for k in ("fn", "scale", "base"):
+            w[f"hc_head_{k}"] = _vector(ops, f"model.hc_head.{k}", "")
     if spec.mtp_layers:
         w["mtp"] = []
         for d in range(spec.mtp_layers):
@@ -296,6 +317,11 @@ def load_device_weights(snapshot: str | Path, spec: ModelSpec, device, *, expert
     from ..ops import TcWeight
     if spec.attn.kind != "gqa":
         raise NotImplementedError("load_device_weights builds GQA decoders; MLA snapshots go through read_masters + engine.mla")
+    if spec.attn.linear_every or spec.hyper_streams:
+        # stacks with gated delta-rule layers or hyper-connections: decoded on the host and re-packed (their projections are bf16)
+        if experts_range is not None:
+            raise NotImplementedError("expert ranges of hybrid / hyper-connection snapshots")
+        return DeviceWeights.from_masters(spec, read_masters(snapshot, spec), device, act_gs)
     ops = _ops_of(snapshot)
     m = spec.moe
     e_lo, e_hi = experts_range if experts_range is not None else (0, m.n_experts)

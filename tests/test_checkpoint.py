@@ -92,3 +92,29 @@ def test_plan_lists_the_files_each_rank_reads(tmp_path, capsys):
     assert attn[0]["bytes"] + sum(p["bytes"] for p in exp) == total            # every tensor has exactly one kind of reader
     assert cli.main(["plan", str(tmp_path), "--gpus", "4", "--rank", "3"]) == 0
     assert '"role": "experts"' in capsys.readouterr().out
+
+
+def test_hybrid_linear_and_hyper_connection_snapshots_round_trip(tmp_path):
+    """Snapshots of stacks with gated delta-rule layers (per-head and per-channel decay) and hyper-connections: every weight comes back
+    (bf16-rounded projections, fp32 taps / decay parameters / mixing coefficients exactly) and the oracle gives the same logits."""
+    import dataclasses
+    from cuteafd_b200.ref.model import RefCache, RefModel
+    base = tiny_spec()
+    lin = dataclasses.replace(base.attn, n_heads=4, n_kv_heads=2, head_dim=128, linear_every=2, linear_k_heads=1, linear_v_heads=2)
+    for name, spec in (("gdn", base.replace(n_layers=4, attn=lin)),
+                       ("kda_hyper", base.replace(n_layers=2, hyper_streams=4, attn=dataclasses.replace(lin, linear_per_channel=True)))):
+        masters = init_weights(spec, 3)
+        from cuteafd_b200.config import spec_from_snapshot
+        ck.export_snapshot(spec, masters, tmp_path / name)
+        back = ck.read_masters(tmp_path / name, spec_from_snapshot(tmp_path / name))
+        assert set(back["layers"][0]) == set(masters["layers"][0])
+        b16 = lambda t: t.to(torch.bfloat16).float()
+        for key in ("conv_w", "dt_bias", "a_log"):
+            assert torch.equal(back["layers"][0][key], masters["layers"][0][key])
+        assert torch.equal(back["layers"][0]["w_qkvz"], b16(masters["layers"][0]["w_qkvz"]))
+        if spec.hyper_streams:
+            assert torch.equal(back["hc_head_fn"], masters["hc_head_fn"]) and torch.equal(back["layers"][1]["hc_ffn_base"], masters["layers"][1]["hc_ffn_base"])
+        p = torch.randint(0, spec.vocab, (9,), generator=torch.Generator().manual_seed(0))
+        a, _ = RefModel(spec, masters).forward(p, 0, RefCache())
+        c, _ = RefModel(spec_from_snapshot(tmp_path / name), back).forward(p, 0, RefCache())
+        assert float((a[-1] - c[-1]).abs().max()) < 0.2          # the snapshot holds bf16-rounded projections
