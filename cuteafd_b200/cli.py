@@ -105,8 +105,15 @@ def build_serving(a):
         from .serving.hostcache import attach_host_tier
         host = attach_host_tier(eng, max(0.0, a.host_cache_gib - a.host_cache_headroom_gib), min_tokens=a.host_cache_min_tokens)
     prefix = PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens, host=host)
+    recurrent = bool(spec.attn.linear_every)
+    if recurrent:
+        # gated delta-rule layers carry a recurrent state per sequence: no resuming from cached pages, no stepping back after a rejected draft
+        prefix = None
+        print(f"[serve] {spec.name}: linear-attention layers - drafts and the prefix cache are off", file=sys.stderr)
     drafter = None
-    if a.draft == "ngram":
+    if recurrent:
+        pass
+    elif a.draft == "ngram":
         drafter = NgramDrafter()
     elif a.draft == "mtp":
         from .serving.mtp_drafter import MtpDrafter
