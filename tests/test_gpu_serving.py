@@ -157,3 +157,28 @@ def test_json_grammar_mask_steers_the_real_sampler_and_argmax():
         assert all(t < 258 for t in outs) and text.lstrip().startswith("{") and JsonPrefix("object").feed_text(text), text
         if outs and outs[-1] == 257:
             assert isinstance(json.loads(text), dict)
+
+
+def test_scheduler_serves_a_hybrid_linear_attention_model():
+    """Continuous batching over a stack with gated delta-rule layers: every live sequence owns a recurrent-state slot of the engine
+    (assigned at its first chunk, freed when it finishes, reused by later requests); chunked prefill, more requests than slots in
+    flight at once, and the tokens of plain generation."""
+    import dataclasses
+    base = tiny_spec()
+    spec = base.replace(n_layers=4, attn=dataclasses.replace(base.attn, n_heads=4, n_kv_heads=2, head_dim=128, linear_every=2, linear_k_heads=1,
+                                                             linear_v_heads=2))
+    masters = init_weights(spec, 9)
+    n_pages = 64
+    eng = Engine(DeviceWeights.from_masters(spec, masters, DEV), n_pages=n_pages, max_seqs=4, max_pages_per_seq=8)
+    pool = PagePool(n_pages)
+    runner = attach_pool(EngineRunner(eng, max_rows=256), pool)
+    sched = Scheduler(runner, pool, max_seqs=3, prefill_chunk=40)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, spec.vocab, (n,), generator=g).tolist() for n in (9, 75, 30, 52, 18)]
+    ref_eng = Engine(DeviceWeights.from_masters(spec, masters, DEV), n_pages=n_pages, max_seqs=8, max_pages_per_seq=8)
+    want = generate(ref_eng, prompts, 10, use_graph=False)
+    got = run_requests(sched, prompts, 10)
+    assert got == want
+    assert not runner._state_slot and sorted(runner._free_slots) == [0, 1, 2, 3]      # every slot came back
+    again = run_requests(sched, prompts[:2], 6)                                         # reused slots start from a zero state
+    assert again == [w[:6] for w in want[:2]]
