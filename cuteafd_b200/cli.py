@@ -107,15 +107,14 @@ def build_serving(a):
     prefix = PrefixCache(pool, max_entries=a.prefix_cache_entries, min_tokens=a.prefix_cache_min_tokens, host=host)
     recurrent = bool(spec.attn.linear_every)
     if recurrent:
-        # gated delta-rule layers carry a recurrent state per sequence: no resuming from cached pages, no stepping back after a rejected draft
+        # gated delta-rule layers carry a recurrent state per sequence: a request cannot resume from cached pages (drafted steps are
+        # fine: they leave the state alone and the accepted rows are replayed into it)
         prefix = None
-        print(f"[serve] {spec.name}: linear-attention layers - drafts and the prefix cache are off", file=sys.stderr)
+        print(f"[serve] {spec.name}: linear-attention layers - the prefix cache is off", file=sys.stderr)
     drafter = None
-    if recurrent:
-        pass
-    elif a.draft == "ngram":
+    if a.draft == "ngram":
         drafter = NgramDrafter()
-    elif a.draft == "mtp":
+    elif a.draft == "mtp" and not recurrent:
         from .serving.mtp_drafter import MtpDrafter
         drafter = MtpDrafter(runner)                           # the model's own MTP module (needs MTP weights)
     sched = Scheduler(runner, pool, max_seqs=a.max_sequences, prefill_chunk=a.prefill_batch_tokens, decode_share=a.decode_share,

@@ -27,7 +27,7 @@ struct LinAttnArgs {
   const int* slot_of_seq; const int* q_start; const int* q_len;
   bf16* out;                                      // [T, H, 128]
   float* snapshots;                               // optional [T, H, dk, dv]: the state AFTER each token (verify rollback), or null
-  int H, per_channel, n_slots;
+  int H, per_channel, n_slots;             // per_channel: bit 0 = one decay per key channel, bit 1 = do not write the state back
   int* status;
 };
 
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(LA_DV) gated_delta_kernel(const LinAttnArgs a)
     __syncthreads();                                   // the previous token's readers are done with sq / sk / sg
     sq[j] = __bfloat162float(a.q[th * LA_DK + j]);
     sk[j] = __bfloat162float(a.k[th * LA_DK + j]);
-    sg[j] = a.per_channel ? a.g[th * LA_DK + j] : a.g[th];
+    sg[j] = (a.per_channel & 1) ? a.g[th * LA_DK + j] : a.g[th];
     __syncthreads();
     const float vj = __bfloat162float(a.v[th * LA_DV + j]), bt = a.beta[th];
     float u = 0.f;
@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(LA_DV) gated_delta_kernel(const LinAttnArgs a)
       for (int i = 0; i < LA_DK; ++i) snap[(size_t)i * LA_DV + j] = col[i];
     }
   }
+  if (a.per_channel & 2) return;          // verify rows of a speculative step: outputs only, the state is committed later by a replay
 #pragma unroll
   for (int i = 0; i < LA_DK; ++i) S[(size_t)i * LA_DV + j] = col[i];
 }
@@ -86,6 +87,7 @@ extern "C" int cuteafd_gated_delta_step(const void* q, const void* k, const void
 // Causal depthwise convolution of width 4 over the token axis with a per-sequence carry of the last three inputs (the short
 // convolution in front of q / k / v in these layers), SiLU on the output.  x: [T, C] bf16 with row pitch ldx, y: [T, C]; w: [C, 4] fp32; carry: [slots, 3, C]
 // bf16, updated in place to the last three inputs of each sequence.
+template <bool UPDATE>
 __global__ void short_conv4_kernel(const bf16* __restrict__ x, const float* __restrict__ w, bf16* __restrict__ carry, const int* __restrict__ slot_of_seq,
                                    const int* __restrict__ q_start, const int* __restrict__ q_len, bf16* __restrict__ y, int C, int ldx, int n_slots, int* status) {
   pdl_launch(); pdl_wait();
@@ -103,16 +105,28 @@ __global__ void short_conv4_kernel(const bf16* __restrict__ x, const float* __re
     y[(size_t)t * C + c] = __float2bfloat16(acc / (1.f + __expf(-acc)));
     h0 = h1; h1 = h2; h2 = xt;
   }
-  cr[c] = __float2bfloat16(h0); cr[C + c] = __float2bfloat16(h1); cr[2 * C + c] = __float2bfloat16(h2);
+  if (UPDATE) { cr[c] = __float2bfloat16(h0); cr[C + c] = __float2bfloat16(h1); cr[2 * C + c] = __float2bfloat16(h2); }
 }
 
 extern "C" int cuteafd_short_conv4(const void* x, const float* w, void* carry, const int* slot_of_seq, const int* q_start, const int* q_len, void* y,
                                    int n_seq, int C, int ldx, int n_slots, int* status, cudaStream_t s) {
   CA_REQUIRE(x && w && carry && slot_of_seq && q_start && q_len && y && C >= 1 && ldx >= C, "short_conv4: bad arguments");
   if (n_seq <= 0) return CA_OK;
-  CA_LAUNCH_PDL(short_conv4_kernel, dim3((C + 255) / 256, n_seq), 256, 0, s, (const bf16*)x, w, (bf16*)carry, slot_of_seq, q_start, q_len, (bf16*)y, C,
+  CA_LAUNCH_PDL(short_conv4_kernel<true>, dim3((C + 255) / 256, n_seq), 256, 0, s, (const bf16*)x, w, (bf16*)carry, slot_of_seq, q_start, q_len, (bf16*)y, C,
                 ldx, n_slots, status);
   CA_CHECK_LAUNCH("short_conv4");
+  return CA_OK;
+}
+
+// The same convolution without touching the carry: the verify rows of a speculative step (the accepted prefix is replayed through
+// `cuteafd_short_conv4` afterwards, which then moves the carry).
+extern "C" int cuteafd_short_conv4_peek(const void* x, const float* w, const void* carry, const int* slot_of_seq, const int* q_start, const int* q_len,
+                                        void* y, int n_seq, int C, int ldx, int n_slots, int* status, cudaStream_t s) {
+  CA_REQUIRE(x && w && carry && slot_of_seq && q_start && q_len && y && C >= 1 && ldx >= C, "short_conv4_peek: bad arguments");
+  if (n_seq <= 0) return CA_OK;
+  CA_LAUNCH_PDL(short_conv4_kernel<false>, dim3((C + 255) / 256, n_seq), 256, 0, s, (const bf16*)x, w, (bf16*)carry, slot_of_seq, q_start, q_len, (bf16*)y,
+                C, ldx, n_slots, status);
+  CA_CHECK_LAUNCH("short_conv4_peek");
   return CA_OK;
 }
 

@@ -50,9 +50,12 @@ class StepShape:
     # sequence s owns rows [s * max_q_len, (s + 1) * max_q_len), and rows that need logits are listed in ascending order.  Such a
     # step can be cut into micro-batches at sequence boundaries.
     uniform: bool = False
+    # Speculative verify step of a stack with recurrent (linear-attention) layers: those layers compute their outputs but leave the
+    # state and the convolution history as they were; `Engine.commit_state` replays the accepted rows afterwards.
+    defer_state: bool = False
 
     def key(self):
-        return (self.T, self.n_seq, self.max_q_len, self.n_logits, self.attn_splits, self.uniform)
+        return (self.T, self.n_seq, self.max_q_len, self.n_logits, self.attn_splits, self.uniform, self.defer_state)
 
 
 class Lane:
@@ -126,6 +129,19 @@ class Lane:
                          "k": bf(cap, Hv, 128), "v": bf(cap, Hv, 128), "g": f32(cap, Hv, 128) if a.linear_per_channel else f32(cap, Hv),
                          "beta": f32(cap, Hv), "o": bf(cap, Hv, 128), "on": on, "on_act": ActBuffer.wrap_bf16(on, self.tn)}
         return self._lin
+
+    def lin_save(self, eng) -> list:
+        """Per linear-attention layer, what a deferred (speculative verify) step keeps for the replay of its accepted rows."""
+        if getattr(self, "_lin_save", None) is None:
+            if self.cap > 256:
+                raise NotImplementedError("deferred recurrent state is for decode / verify sized steps (<= 256 rows)")
+            a, dev, cap = eng.spec.attn, eng.device, self.cap
+            Hk, Hv = a.linear_k_heads, a.linear_v_heads
+            bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+            f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
+            self._lin_save = [{"qkvz": bf(cap, (2 * Hk + 2 * Hv) * 128), "k": bf(cap, Hv, 128), "v": bf(cap, Hv, 128),
+                               "g": f32(cap, Hv, 128) if a.linear_per_channel else f32(cap, Hv), "beta": f32(cap, Hv)} for _ in eng.lin_layers]
+        return self._lin_save
 
     def ffn_buf(self, eng, inter: int):
         if inter not in self.ffn_bufs:
@@ -349,22 +365,55 @@ class Engine:
         Hk, Hv = a.linear_k_heads, a.linear_v_heads
         C, Nq, j = (2 * Hk + Hv) * 128, (2 * Hk + 2 * Hv) * 128, self.lin_index[li]
         b = L.lin_buf(self)
+        pc = 1 if a.linear_per_channel else 0
+        # a deferred (speculative verify) step keeps what the replay of the accepted rows needs, per layer: the convolution's input
+        # rows and the recurrence's k / v / decay / beta; state and history stay untouched
+        sv = L.lin_save(self)[j] if sh.defer_state else None
+        qkvz = sv["qkvz"] if sv else b["qkvz"]
+        k_, v_, g_, beta_ = (sv["k"], sv["v"], sv["g"], sv["beta"]) if sv else (b["k"], b["v"], b["g"], b["beta"])
         xq = self._norm_in(lw, L, T)
-        self._dense(lw.lin_qkvz, xq, b["qkvz"], T)
+        self._dense(lw.lin_qkvz, xq, qkvz, T)
         if xq.kind != KIND_BF16:           # the gate projection stays bf16: it needs the bf16 normalised rows
             raise NotImplementedError("linear-attention layers run with bf16 dense projections")
         self._dense(lw.lin_ba, L.xn_act, b["ba"], T)
         st, n_seq = ptr(self.status), sh.n_seq
-        native.call("cuteafd_short_conv4", ptr(b["qkvz"]), ptr(lw.lin_conv), ptr(self.lin_carry[j]), ptr(md["state_slot"]), ptr(md["q_start"]),
-                    ptr(md["q_len"]), ptr(b["conv"]), n_seq, C, Nq, self.max_seqs, st, native.stream())
-        native.call("cuteafd_linear_prepare", ptr(b["conv"]), ptr(b["ba"]), ptr(lw.lin_a_log), ptr(lw.lin_dt_bias), ptr(b["q"]), ptr(b["k"]), ptr(b["v"]),
-                    ptr(b["g"]), ptr(b["beta"]), T, Hk, Hv, b["ba"].shape[1], 1 if a.linear_per_channel else 0, native.stream())
-        native.call("cuteafd_gated_delta_step", ptr(b["q"]), ptr(b["k"]), ptr(b["v"]), ptr(b["g"]), ptr(b["beta"]), ptr(self.lin_state[j]),
-                    ptr(md["state_slot"]), ptr(md["q_start"]), ptr(md["q_len"]), ptr(b["o"]), None, n_seq, Hv, 1 if a.linear_per_channel else 0,
+        native.call("cuteafd_short_conv4_peek" if sv else "cuteafd_short_conv4", ptr(qkvz), ptr(lw.lin_conv), ptr(self.lin_carry[j]), ptr(md["state_slot"]),
+                    ptr(md["q_start"]), ptr(md["q_len"]), ptr(b["conv"]), n_seq, C, Nq, self.max_seqs, st, native.stream())
+        native.call("cuteafd_linear_prepare", ptr(b["conv"]), ptr(b["ba"]), ptr(lw.lin_a_log), ptr(lw.lin_dt_bias), ptr(b["q"]), ptr(k_), ptr(v_),
+                    ptr(g_), ptr(beta_), T, Hk, Hv, b["ba"].shape[1], pc, native.stream())
+        native.call("cuteafd_gated_delta_step", ptr(b["q"]), ptr(k_), ptr(v_), ptr(g_), ptr(beta_), ptr(self.lin_state[j]),
+                    ptr(md["state_slot"]), ptr(md["q_start"]), ptr(md["q_len"]), ptr(b["o"]), None, n_seq, Hv, pc | (2 if sv else 0),
                     self.max_seqs, st, native.stream())
-        native.call("cuteafd_gated_rmsnorm", ptr(b["o"]), ptr(b["qkvz"]), ptr(lw.lin_norm), ptr(b["on"]), T, Hv, Nq, C, spec.rms_eps, native.stream())
+        native.call("cuteafd_gated_rmsnorm", ptr(b["o"]), ptr(qkvz), ptr(lw.lin_norm), ptr(b["on"]), T, Hv, Nq, C, spec.rms_eps, native.stream())
         self._attn_out(li, lw, b["on_act"], L, T)
         self.launches_per_step += 7
+
+    def commit_state(self, sh: StepShape, accepted):
+        """After a deferred step (`sh.defer_state`): absorb the first `accepted[s]` rows of every sequence s of that step into the
+        recurrent state and the convolution history of every linear-attention layer, by replaying the convolution and the recurrence
+        over the rows the step kept.  Must run before the next `set_inputs` (it reads that step's sequence layout)."""
+        if not getattr(self, "lin_layers", None):
+            return
+        if not sh.defer_state or len(accepted) != sh.n_seq:
+            raise ValueError("commit_state follows a deferred step and takes one accepted-row count per sequence of it")
+        a, md, L = self.spec.attn, self.md, self.lane(sh.T)
+        Hk, Hv, pc = a.linear_k_heads, a.linear_v_heads, 1 if a.linear_per_channel else 0
+        C, Nq = (2 * Hk + Hv) * 128, (2 * Hk + 2 * Hv) * 128
+        if getattr(self, "_acc_host", None) is None:
+            self._acc_host = torch.zeros(self.max_seqs, dtype=torch.int32)
+            if torch.cuda.is_available():
+                self._acc_host = self._acc_host.pin_memory()
+            self._acc_dev = torch.zeros(self.max_seqs, dtype=torch.int32, device=self.device)
+        self._acc_host[:sh.n_seq] = torch.as_tensor([max(0, min(int(n), sh.max_q_len)) for n in accepted], dtype=torch.int32)
+        self._acc_dev.copy_(self._acc_host, non_blocking=True)
+        b, save, st = L.lin_buf(self), L.lin_save(self), ptr(self.status)
+        for j, li in enumerate(self.lin_layers):
+            lw, sv = self.weights.layer(li), save[j]
+            native.call("cuteafd_short_conv4", ptr(sv["qkvz"]), ptr(lw.lin_conv), ptr(self.lin_carry[j]), ptr(md["state_slot"]), ptr(md["q_start"]),
+                        ptr(self._acc_dev), ptr(b["conv"]), sh.n_seq, C, Nq, self.max_seqs, st, native.stream())
+            native.call("cuteafd_gated_delta_step", ptr(sv["k"]), ptr(sv["k"]), ptr(sv["v"]), ptr(sv["g"]), ptr(sv["beta"]), ptr(self.lin_state[j]),
+                        ptr(md["state_slot"]), ptr(md["q_start"]), ptr(self._acc_dev), ptr(b["o"]), None, sh.n_seq, Hv, pc, self.max_seqs, st,
+                        native.stream())
 
     def _attention_layer(self, li: int, lw: LayerWeights, L: Lane, sh: StepShape):
         spec, a, T = self.spec, self.spec.attn, sh.T

@@ -59,6 +59,7 @@ _PROTOS = {
     "cuteafd_linear_prepare": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "cuteafd_gated_rmsnorm": [P, P, P, P, I, I, I, I, F, P],
     "cuteafd_short_conv4": [P, P, P, P, P, P, P, I, I, I, I, P, P],
+    "cuteafd_short_conv4_peek": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "cuteafd_mhc_boundary": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P],
     "cuteafd_dsa_index_scores": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "cuteafd_tmap_encode_index_keys": [P, P, U64],

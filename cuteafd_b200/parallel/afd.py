@@ -350,6 +350,8 @@ class AttnRankEngine(Engine):
     # ------------------------------------------------------------------ the step
     def program(self, sh: StepShape):
         spec = self.spec
+        if sh.defer_state:
+            raise NotImplementedError("speculative steps over linear-attention layers run on the single-GPU engine")
         self._keep = []
         self.launches_per_step = 0
         base_md = self.md

@@ -67,6 +67,7 @@ class EngineRunner:
         self._recurrent = bool(getattr(engine, "lin_layers", None))
         self._state_slot: dict = {}
         self._state_pos: dict = {}
+        self._deferred = None             # (step shape, [(state id, start position, rows)]) of a speculative step awaiting `commit`
         self._free_slots = list(range(getattr(engine, "max_seqs", 0)))[::-1] if self._recurrent else []
         self._tok_host = torch.zeros(max(64, max_rows), dtype=torch.int32)
         if torch.cuda.is_available():
@@ -96,17 +97,35 @@ class EngineRunner:
                         raise RuntimeError("more live sequences than recurrent-state slots (engine max_seqs)")
                     slot = self._state_slot[id(r.state)] = self._free_slots.pop()
                 fresh.append(slot)
-            elif r.start_pos != self._state_pos.get(id(r.state)):      # a rejected draft would need the state of an earlier position
-                raise RuntimeError("a linear-attention stack cannot step back: run it without speculation")
+            elif r.start_pos != self._state_pos.get(id(r.state)):      # the recurrent state sits at another position
+                raise RuntimeError("a linear-attention stack cannot step back (was a speculative step left uncommitted?)")
             self._state_pos[id(r.state)] = r.start_pos + len(r.tokens)
             out.append(slot)
         self.eng.reset_state_slots(fresh)
         return out
 
+    def commit(self, accepted: list):
+        """The scheduler verified a speculative step: `accepted` = [(sequence state, accepted input rows)].  Stacks with recurrent
+        layers now absorb exactly those rows (the step itself left their state untouched)."""
+        if self._deferred is None:
+            return
+        sh, order = self._deferred
+        self._deferred = None
+        by_state = {id(st): n for st, n in accepted}
+        counts = []
+        for sid, start, n in order:
+            k = by_state.get(sid, n)
+            counts.append(k)
+            if sid in self._state_pos:
+                self._state_pos[sid] = start + k
+        self.eng.commit_state(sh, counts)
+
     def run(self, rows: list[Row]) -> list[list[int]]:
         from ..engine.engine import StepShape
         from .. import ops
         eng = self.eng
+        if self._deferred is not None:
+            raise RuntimeError("the previous speculative step of a linear-attention stack was not committed")
         tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages = [], [], [], [], [], [], [], []
         for r in rows:
             seq = r.state.seq
@@ -128,9 +147,12 @@ class EngineRunner:
         # regular decode / verify rounds (every sequence the same number of rows, logits for every row or none) may be cut into
         # micro-batches by a multi-GPU engine
         uniform = decode_like and all(q == max_q for q in q_len) and (not logit_rows or logit_rows == list(range(len(tokens))))
+        # drafted rows over recurrent layers: the step leaves their state alone, `commit` absorbs what the scheduler accepts
+        defer = self._recurrent and decode_like and any(len(r.tokens) > 1 and len(r.want_logits) == len(r.tokens) for r in rows)
         sh = StepShape(T=len(tokens), n_seq=len(rows), max_q_len=max_q, n_logits=len(logit_rows),
-                       attn_splits=eng.attn_splits_for(len(rows), max_q, max(kv_len)) if decode_like else 1, uniform=uniform)
+                       attn_splits=eng.attn_splits_for(len(rows), max_q, max(kv_len)) if decode_like else 1, uniform=uniform, defer_state=defer)
         lane = eng.run(sh, use_graph=decode_like)
+        pending = (sh, [(id(r.state), r.start_pos, len(r.tokens)) for r in rows]) if defer else None
         if self.keep_hidden:
             for r, qs, ql in zip(rows, q_start, q_len):
                 recs = self.records.setdefault(id(r.state), [])
@@ -158,6 +180,7 @@ class EngineRunner:
         for r in rows:
             out.append(flat[base:base + len(r.want_logits)])
             base += len(r.want_logits)
+        self._deferred = pending          # only a step that completed waits for its commit
         return out
 
     def _select_special(self, lane, off: int, r: Row):

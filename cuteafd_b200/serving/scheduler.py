@@ -248,9 +248,11 @@ class Scheduler:
         if outs is None:
             return
         step_ms = (time.perf_counter() - t0) * 1e3
+        verified = []
         for (st, inputs), target in zip(plan, outs):
             remaining = st.req.max_tokens - len(st.out)
             accepted, emitted, _, _ = greedy_verify(inputs, target, st.req.eos_id, max(1, remaining))
+            verified.append((st, accepted))
             st.seq.length += accepted
             self.stats["verify_rows"] += len(inputs)
             self.stats["drafted"] += len(inputs) - 1
@@ -262,6 +264,9 @@ class Scheduler:
                 self.spec_trace.record(st.req.rid, len(inputs) - 1, accepted - 1, step_ms)
             self.policy.observe(st.req.rid, len(inputs) - 1, accepted - 1)
             self._emit(st, emitted)
+        commit = getattr(self.runner, "commit", None)
+        if commit is not None:              # engines with recurrent layers absorb exactly the accepted rows now
+            commit(verified)
         self._event("decode", rows=sum(len(i) for _, i in plan), seqs=len(plan), ms=round(step_ms, 3))
 
     def _run(self, rows: list[Row]):

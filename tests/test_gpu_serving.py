@@ -182,3 +182,33 @@ def test_scheduler_serves_a_hybrid_linear_attention_model():
     assert not runner._state_slot and sorted(runner._free_slots) == [0, 1, 2, 3]      # every slot came back
     again = run_requests(sched, prompts[:2], 6)                                         # reused slots start from a zero state
     assert again == [w[:6] for w in want[:2]]
+
+
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_drafted_decoding_over_linear_attention_layers_is_lossless(per_channel):
+    """Speculation on a hybrid stack: verify steps leave the recurrent state and the convolution history alone, the accepted rows are
+    replayed into them (`Engine.commit_state`), so drafted greedy and sampled decoding reproduce the undrafted token streams -
+    with drafts accepted (repetitive prompts) and rejected."""
+    import dataclasses
+    base = tiny_spec()
+    spec = base.replace(n_layers=4, attn=dataclasses.replace(base.attn, n_heads=4, n_kv_heads=2, head_dim=128, linear_every=2, linear_k_heads=1,
+                                                             linear_v_heads=2, linear_per_channel=per_channel))
+    masters = init_weights(spec, 11)
+
+    def make(drafter):
+        eng = Engine(DeviceWeights.from_masters(spec, masters, DEV), n_pages=64, max_seqs=4, max_pages_per_seq=8)
+        pool = PagePool(64)
+        runner = attach_pool(EngineRunner(eng, max_rows=256), pool)
+        return Scheduler(runner, pool, max_seqs=3, prefill_chunk=48, drafter=drafter), runner
+    g = torch.Generator().manual_seed(2)
+    rep = torch.randint(0, spec.vocab, (9,), generator=g).tolist()
+    prompts = [rep * 5, torch.randint(0, spec.vocab, (33,), generator=g).tolist(), rep[:4] * 9]
+    plain, _ = make(None)
+    want = run_requests(plain, prompts, 20)
+    spec_sched, runner = make(NgramDrafter())
+    got = run_requests(spec_sched, prompts, 20)
+    assert got == want
+    assert spec_sched.stats["drafted"] > 0 and spec_sched.stats["drafted"] > spec_sched.stats["accepted"] >= 0
+    assert runner._deferred is None
+    sp = SamplingParams(temperature=0.5, top_p=0.9, top_k=30, seed=3)
+    assert run_requests(make(NgramDrafter())[0], prompts, 16, sampling=sp) == run_requests(make(None)[0], prompts, 16, sampling=sp)
