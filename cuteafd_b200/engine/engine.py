@@ -184,8 +184,8 @@ class Engine:
         else:
             self._alloc_attention_state()
         if spec.hyper_streams:
-            if spec.hyper_streams != 4 or a.kind != "gqa" or weights.hc_head is None or weights.mtp:
-                raise NotImplementedError("hyper-connections: four streams, on the single-GPU GQA engine, without an MTP module")
+            if spec.hyper_streams != 4 or weights.hc_head is None or weights.mtp:
+                raise NotImplementedError("hyper-connections: four streams, on the single-GPU engines, without an MTP module")
         self._hc_pending = None
         # hybrid stacks: gated delta-rule layers keep a recurrent state and the last three convolution inputs per sequence slot
         self.lin_layers = [i for i in range(spec.n_layers) if spec.layer_is_linear(i)]

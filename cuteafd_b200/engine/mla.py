@@ -83,6 +83,9 @@ def mla_weights_from_masters(spec: ModelSpec, masters: dict, device, act_gs: flo
         out = LayerWeights(attn_norm=f32(lw["attn_norm"]), ffn_norm=f32(lw["ffn_norm"]), wqkv=None,
                            wo=TcWeight.from_master(lw["wo"], dk, device, act_gs))
         out.mla = _mla_from_masters(spec, lw, device, dk, act_gs)
+        if "hc_attn_fn" in lw:         # hyper-connections (the V4 line pairs them with latent attention)
+            out.hc_attn = tuple(f32(lw[f"hc_attn_{k}"]) for k in ("fn", "scale", "base"))
+            out.hc_ffn = tuple(f32(lw[f"hc_ffn_{k}"]) for k in ("fn", "scale", "base"))
         if "router" in lw:
             out.router = TcWeight.from_master(lw["router"], "bf16", device)
             if "router_bias" in lw:
@@ -97,6 +100,8 @@ def mla_weights_from_masters(spec: ModelSpec, masters: dict, device, act_gs: flo
 
     dw.layers = [layer_from(lw) for lw in masters["layers"]]
     dw.layer_map = list(range(spec.n_layers))
+    if "hc_head_fn" in masters:
+        dw.hc_head = tuple(f32(masters[f"hc_head_{k}"]) for k in ("fn", "scale", "base"))
     for mw in masters.get("mtp", []):
         dw.mtp.append((f32(mw["enorm"]), f32(mw["hnorm"]), TcWeight.from_master(mw["eh_proj"], "bf16", device), layer_from(mw["layer"]),
                        f32(mw["norm"])))

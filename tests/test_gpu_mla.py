@@ -146,3 +146,32 @@ def test_mla_engine_prefill_path_matches_oracle():
                 top2 = rows[j].topk(2).values
                 assert float(top2[0] - top2[1]) < 0.05, f"prompt {i} step {j}: {a_} != {b_}"
                 break
+
+
+def test_mla_engine_with_hyper_connections_matches_oracle():
+    """Latent attention under four residual streams (the V4 line's pairing): prefill logits and greedy decode against the oracle."""
+    spec = small_mla_spec(4, 64).replace(hyper_streams=4)
+    masters = bf16_round(init_weights(spec, 2))
+    eng = MlaEngine(mla_weights_from_masters(spec, masters, DEV), n_pages=32, max_seqs=8, max_pages_per_seq=6)
+    ref = RefModel(spec, masters)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, spec.vocab, (n,), generator=g).tolist() for n in (40, 21)]
+    gen = BatchGenerator(eng)
+    gen.prefill(prompts)
+    torch.cuda.synchronize()
+    eng.check_status()
+    lane = eng.lane(sum(len(p) for p in prompts))
+    for i, p in enumerate(prompts):
+        rl, _ = ref.forward(torch.tensor(p), 0, RefCache())
+        got = lane.logits[i].float().cpu()
+        err = float((got - rl[-1]).norm() / rl[-1].norm())
+        assert err < 0.06, f"prompt {i}: logits rel err {err}"
+    gen.release()
+    out = generate(eng, prompts, 6)
+    for i, p in enumerate(prompts):
+        want, rows = ref.generate_greedy(torch.tensor(p), 6)
+        for j, (a_, b_) in enumerate(zip(out[i], want)):
+            if a_ != b_:
+                top2 = rows[j].topk(2).values
+                assert float(top2[0] - top2[1]) < 0.05, f"prompt {i} step {j}: {a_} != {b_}"
+                break
