@@ -348,7 +348,8 @@ __global__ void __launch_bounds__(192, 1) mla_prefill_kernel(const __grid_consta
 // The same structure for paged GQA prefill (head_dim 128): a CTA owns 128 query rows of one KV head (row = token_in_tile * G +
 // head_in_group) and walks the sequence's pages two at a time (128-key tiles), K and V straight from the paged store.  Causal
 // mask, optional sliding window and sink logit as in the decode kernel (attention_tc.cu), no split-KV: a prefill chunk has
-// enough query tiles to fill the GPU.  The 64-key decode kernel spends 8 + 4 tcgen05.mma per 64 keys; this one 8 + 8 per 128 keys.
+// enough query tiles to fill the GPU.  window < 0 drops the causal mask (bidirectional attention of a vision / audio encoder:
+// every query row sees keys [0, kvlen)).  The 64-key decode kernel spends 8 + 4 tcgen05.mma per 64 keys; this one 8 + 8 per 128 keys.
 #define GQ_K_STAGE 32768          // 2 chunks (64 dims each) x [128 keys x 128 B]
 struct GqaPrefillArgs {
   const bf16* q;
@@ -387,8 +388,9 @@ __global__ void __launch_bounds__(192, 1) gqa_prefill_kernel(const __grid_consta
   const int ntok = min(tok_per_tile, qlen - tok0);
   const int R = ntok * G;                                   // row = token_in_tile * G + head_in_group
   const int row_base = a.q_start[seq] + tok0;
-  const int first_pos = kvlen - qlen + tok0;
-  const int hi = first_pos + ntok;
+  const bool bidir = a.window < 0;                          // encoder towers: every row sees all kvlen keys
+  const int first_pos = bidir ? kvlen - 1 : kvlen - qlen + tok0;
+  const int hi = bidir ? kvlen : first_pos + ntok;
   const int lo = a.window > 0 ? max(0, first_pos - a.window + 1) : 0;
   const int tile0 = lo / PF_KT;
   const int n_tiles = max(0, (hi + PF_KT - 1) / PF_KT - tile0);
@@ -515,7 +517,7 @@ __global__ void __launch_bounds__(192, 1) gqa_prefill_kernel(const __grid_consta
     const int q4 = warp & 3, r = q4 * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
     const bool live = r < R;
-    const int qpos = live ? first_pos + r / G : -1;
+    const int qpos = live ? (bidir ? first_pos : first_pos + r / G) : -1;
     const int wlo = a.window > 0 ? qpos - a.window : -1;           // keys at or below this position are outside the row's window
     const float sc2 = a.scale * 1.4426950408889634f;
     float m_ref = -INFINITY, l = 0.f;

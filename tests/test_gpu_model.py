@@ -237,3 +237,32 @@ def test_hyper_connection_stack_matches_oracle():
                 top2 = rows[j].topk(2).values
                 assert float(top2[0] - top2[1]) < 0.05, f"prompt {i} step {j}: {a} != {b}"
                 break
+
+
+@pytest.mark.parametrize("variant", ["layernorm-gelu-pos", "rmsnorm-swiglu-qknorm"])
+def test_vision_tower_matches_oracle(variant):
+    """ViT encoder (bf16 tcgen05 GEMMs, bidirectional attention over heads padded to 128, fused glue) against the fp32 oracle:
+    two images of different grids in one batch; patch width 14 exercises the padded patch rows."""
+    from cuteafd_b200.models.vision import VisionTower
+    from cuteafd_b200.ref.vision import VisionSpec, init_vision_weights, rgb_to_patches, vision_bf16_round, vision_forward
+    if variant == "layernorm-gelu-pos":
+        spec = VisionSpec(hidden=128, depth=2, n_heads=2, head_dim=64, intermediate=192, patch=14, out_hidden=256, pos_grid=6)
+    else:
+        spec = VisionSpec(hidden=192, depth=2, n_heads=4, head_dim=48, intermediate=256, patch=16, out_hidden=128, norm="rmsnorm", mlp="swiglu",
+                          qk_norm=True, qkv_bias=False)
+    w = vision_bf16_round(init_vision_weights(spec, 3))
+    tower = VisionTower(spec, w, DEV, max_patches=1024, max_images=4)
+    g = torch.Generator().manual_seed(5)
+    P = spec.patch
+    images = [torch.randint(0, 256, (gh * P, gw * P, 3), generator=g, dtype=torch.uint8) for gh, gw in ((12, 16), (6, 4))]
+    outs = tower.encode(images)
+    torch.cuda.synchronize()
+    for im, got in zip(images, outs):
+        gh, gw = im.shape[0] // P, im.shape[1] // P
+        want = vision_forward(spec, w, rgb_to_patches(im, spec).bfloat16().float(), gh, gw)
+        assert got.shape == want.shape
+        err = float((got.float().cpu() - want).norm() / want.norm())
+        assert err < 0.03, f"{variant}: {gh}x{gw} rel err {err}"
+    # a second call reuses the buffers and the scratch store: same rows for the same image alone
+    again = tower.encode([images[1]])[0]
+    assert float((again.float() - outs[1].float()).abs().max()) < 2e-2
