@@ -196,7 +196,8 @@ def cmd_serve(a) -> int:
         thermal = ThermalMonitor()
     except Exception:
         thermal = None
-    app = build_app(loop, model_id=a.model_id or spec.name, tokenizer=load_tokenizer(a.model if os.path.isdir(a.model) else None),
+    vision = _vision_front_end(a, spec)
+    app = build_app(loop, model_id=a.model_id or spec.name, tokenizer=load_tokenizer(a.model if os.path.isdir(a.model) else None), vision=vision,
                     api_keys=keys, max_output=a.max_output, template=template_for(a.chat_template or spec.name),
                     usage=usage, enable_bench=a.enable_bench, thermal=thermal, gateway=a.gateway == "on",
                     model_aliases=_aliases(a), allow_origin=a.gateway_allow_origin or None, search=_search_provider(a),
@@ -205,6 +206,37 @@ def cmd_serve(a) -> int:
     import uvicorn
     uvicorn.run(app, host=host, port=int(port), log_level="info")
     return 0
+
+
+def _vision_front_end(a, spec):
+    """The vision tower of `serve`: `--vision auto` builds it when the snapshot has a `vision_config` and `visual.*` tensors, `--vision
+    random:DEPTH` builds a randomly initialised tower of the Qwen-VL shape for shape / throughput work, `--vision off` (and multi-GPU
+    layouts, whose engines take token ids only) serve text alone.  Reference: cuteafd-daemon/src/cli.rs (vision / audio encoder flags)."""
+    mode = getattr(a, "vision", "auto")
+    if mode == "off" or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return None
+    import torch
+    from .models.vision import VisionTower
+    from .serving.vision import VisionFrontEnd
+    dev = torch.device("cuda", a.device)
+    if mode.startswith("random"):
+        from .ref.vision import VisionSpec, init_vision_weights
+        depth = int(mode.split(":", 1)[1]) if ":" in mode else 2
+        vs = VisionSpec(hidden=1152, depth=depth, n_heads=16, head_dim=72, intermediate=4304, patch=16, out_hidden=spec.hidden, pos_grid=48)
+        tower = VisionTower(vs, init_vision_weights(vs, 0), dev, max_patches=a.vision_max_patches)
+        return VisionFrontEnd(tower, pad_id=min(spec.vocab - 1, 151655), start_id=None, end_id=None, max_images=a.vision_max_images)
+    if not os.path.isdir(a.model):
+        return None
+    from .loader.vision_checkpoint import read_vision_masters, vision_spec_from_snapshot
+    found = vision_spec_from_snapshot(a.model)
+    if found is None:
+        return None
+    vs, ids = found
+    if vs.out_hidden != spec.hidden:
+        raise SystemExit(f"vision tower emits rows of {vs.out_hidden}, the decoder's hidden size is {spec.hidden}")
+    tower = VisionTower(vs, read_vision_masters(a.model, vs), dev, max_patches=a.vision_max_patches)
+    print(f"vision tower: depth {vs.depth}, hidden {vs.hidden}, {tower.nbytes() / 2**20:.0f} MiB", flush=True)
+    return VisionFrontEnd(tower, pad_id=int(ids["pad"]), start_id=ids["start"], end_id=ids["end"], max_images=a.vision_max_images)
 
 
 def cmd_usage(a) -> int:
@@ -424,6 +456,9 @@ def main(argv=None) -> int:
     p.add_argument("--draft-limit", type=int, default=3); p.add_argument("--api-key-file"); p.add_argument("--model-id")
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.add_argument("--n-micro", type=int, default=0, help="multi-GPU: micro-batches the attention ranks keep in flight (0 = the layout's default)")
+    p.add_argument("--vision", default="auto", help="auto (tower of the snapshot, if it has one) | off | random[:DEPTH]")
+    p.add_argument("--vision-max-patches", type=int, default=16384, help="patches of all images of one request")
+    p.add_argument("--vision-max-images", type=int, default=8)
     p.set_defaults(fn=cmd_serve)
     p = sub.add_parser("card")
     p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--device", type=int, default=0)

@@ -269,6 +269,28 @@ class Engine:
         self.meta_dev.copy_(self.meta_host, non_blocking=True)
         return self.meta_host.numel() * 4
 
+    def set_input_embeds(self, rows, vals: torch.Tensor | None):
+        """Rows of the NEXT eager step whose token embedding is replaced by `vals` (bf16 [n, hidden] on this device): the image rows
+        a vision tower produced for the placeholder tokens of a prompt.  One-shot: the step that consumes them clears them.
+        Reference: native/families/deepseek_v41/cuda/v41_vision.cu (`image_embed_kernel`: features scattered into the residual)."""
+        if vals is None or not len(rows):
+            self._embed_over = None
+            return
+        if vals.dtype != torch.bfloat16 or vals.shape != (len(rows), self.spec.hidden) or vals.device != self.device:
+            raise ValueError("set_input_embeds: bf16 [len(rows), hidden] rows on the engine's device")
+        self._embed_over = (torch.as_tensor(rows, dtype=torch.int32).to(self.device), vals.contiguous())
+
+    def _apply_input_embeds(self, x: torch.Tensor, T: int):
+        over = getattr(self, "_embed_over", None)
+        if over is None:
+            return
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("input embeddings belong to eager (prefill) steps, not to a captured graph")
+        self._embed_over = None
+        rows, vals = over
+        native.call("cuteafd_dsa_scatter_rows", ptr(vals), ptr(rows), ptr(x), len(rows), T, self.spec.hidden * 2, ptr(self.status), native.stream())
+        self.launches_per_step += 1
+
     # ------------------------------------------------------------------ kernels
     def _splits(self, N: int, K: int, T: int, tn: int, kind: int) -> int:
         """Split-K factor of a dense layer.  Decode-sized token tiles (<= 32 rows) split over a thread-block cluster
@@ -601,6 +623,7 @@ class Engine:
         self._pre_normed = False
         ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
         self.launches_per_step += 1
+        self._apply_input_embeds(L.x, T)
         self._hc_pending = "init" if spec.hyper_streams else None
         import contextlib
         from ..utils.trace import nvtx

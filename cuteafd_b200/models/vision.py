@@ -114,6 +114,7 @@ class VisionTower:
         self.cs = torch.zeros(N, hd, dtype=torch.float32, device=dev)
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self._acts: dict = {}
+        self._grids: dict = {}
         self.encodes = 0
 
     # ------------------------------------------------------------------
@@ -167,9 +168,14 @@ class VisionTower:
             np_ = -(-c // PAGE)
             page_table[i, :np_] = torch.arange(page, page + np_, dtype=torch.int32)
             slots.append(page * PAGE + torch.arange(c, dtype=torch.int32))
-            cs_rows.append(rope_table(gh, gw, spec))
+            if (gh, gw) not in self._grids:          # rotary angles and resampled position rows depend on the grid only
+                if len(self._grids) >= 64:
+                    self._grids.clear()
+                self._grids[(gh, gw)] = (rope_table(gh, gw, spec).to(self.device),
+                                         position_rows(self.pos_embed.float(), gh, gw, spec).to(self.device) if self.pos_embed is not None else None)
+            cs_rows.append(self._grids[(gh, gw)][0])
             if self.pos_embed is not None:
-                pos_rows.append(position_rows(self.pos_embed.float(), gh, gw, spec))
+                pos_rows.append(self._grids[(gh, gw)][1])
             off += c
             page += np_
         dev = self.device

@@ -35,11 +35,14 @@ def _anthropic_to_openai(body: dict) -> tuple[list, list]:
         if not isinstance(content, list):
             msgs.append({"role": m.get("role", "user"), "content": content})
             continue
-        text, calls = [], []
+        text, calls, images = [], [], False
         for b in content:
             kind = b.get("type")
             if kind == "text":
                 text.append(b.get("text", ""))
+            elif kind == "image":                   # stays a content part: the vision front end takes it out of the prompt
+                text.append(b)
+                images = True
             elif kind == "tool_use":
                 calls.append({"id": b.get("id"), "function": {"name": b.get("name"), "arguments": b.get("input", {})}})
             elif kind == "tool_result":
@@ -48,7 +51,8 @@ def _anthropic_to_openai(body: dict) -> tuple[list, list]:
                     inner = "".join(x.get("text", "") for x in inner if isinstance(x, dict))
                 msgs.append({"role": "tool", "tool_call_id": b.get("tool_use_id"), "content": inner or ""})
         if text or calls:
-            msg = {"role": m.get("role", "user"), "content": "".join(text)}
+            msg = {"role": m.get("role", "user"),
+                   "content": [x if isinstance(x, dict) else {"type": "text", "text": x} for x in text] if images else "".join(text)}
             if calls:
                 msg["tool_calls"] = calls
             msgs.append(msg)
@@ -150,7 +154,7 @@ except ImportError:      # pragma: no cover - the HTTP layer is optional
 
 def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=None, api_keys=None, max_output: int = 4096, template=None,
               usage=None, enable_bench: bool = False, thermal=None, gateway: bool = True, model_aliases: dict | None = None,
-              allow_origin: str | None = None, search=None, record_path: str | None = None):
+              allow_origin: str | None = None, search=None, record_path: str | None = None, vision=None):
     """`usage`: a `UsageStore` that gets one row per finished request and backs `/usage`.  `enable_bench` turns on the
     probe header `x-cuteafd-probe` (JSON: `skip_cache`, `no_drafts`, `token_ids`) that benchmarks use to pin what a
     request exercises (cuteafd-api/src/openai/probe.rs).  `thermal`: object with `.sample()` for `/v1/thermal`.
@@ -158,7 +162,9 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
     Responses (`/v1/responses`, stored responses with `previous_response_id` chaining); `model_aliases` lists
     official model names that clients may ask for and that are answered by the served model (gateway/models.rs).  `search`: a
     provider for `/v1/alpha/search` (see `gateway_extras.SearchProvider`); `record_path`: every request / response pair of the
-    JSON endpoints is appended to this JSONL file (`gateway_extras.replay` plays such a file back)."""
+    JSON endpoints is appended to this JSONL file (`gateway_extras.replay` plays such a file back).  `vision`: a
+    `serving.vision.VisionFrontEnd`; with it image content parts (OpenAI `image_url` / `input_image`, Anthropic `image`) are encoded by
+    the tower and take the place of placeholder tokens in the prompt; without it they are refused."""
     if FastAPI is None:
         raise RuntimeError("fastapi is not installed")
 
@@ -227,7 +233,21 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         except json.JSONDecodeError:
             raise HTTPException(400, "x-cuteafd-probe is not JSON")
 
-    def start_generation(prompt_ids, body, max_tokens, constraint=None, probe=None):
+    async def build_prompt(msgs, **render_kw):
+        """(prompt ids, image rows of the request or None)."""
+        image_kinds = ("image_url", "input_image", "image")
+        has_image = any(isinstance(m, dict) and isinstance(m.get("content"), list)
+                        and any(isinstance(p, dict) and p.get("type") in image_kinds for p in m["content"]) for m in msgs)
+        if not has_image:
+            return tok.encode(tmpl.render(msgs, **render_kw)), None
+        if vision is None:
+            raise HTTPException(400, "this server has no vision tower: image inputs are not accepted")
+        try:
+            return await asyncio.to_thread(vision.prepare, msgs, lambda m: tmpl.render(m, **render_kw), tok.encode)
+        except (ValueError, OSError) as e:          # undecodable image, too many images, remote URL
+            raise HTTPException(400, f"invalid image input: {e}") from None
+
+    def start_generation(prompt_ids, body, max_tokens, constraint=None, probe=None, embeds=None):
         if not loop.healthy():
             raise HTTPException(503, loop.died or loop.sched.fatal or "unavailable")
         events: asyncio.Queue = asyncio.Queue()
@@ -242,8 +262,8 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
             aloop.call_soon_threadsafe(events.put_nowait, (toks, done, reason))
         req = Request(rid, prompt_ids, max_tokens=max(1, min(max_tokens, max_output)), sampling=sampling_from(body),
                       eos_id=getattr(tok, "eos_id", None), stop_ids=tuple(getattr(tok, "stop_ids", ()) or ()), on_token=on_token,
-                      constraint=constraint,
-                      use_cache=not (probe or {}).get("skip_cache", False), allow_drafts=not (probe or {}).get("no_drafts", False))
+                      constraint=constraint, embeds=embeds,
+                      use_cache=embeds is None and not (probe or {}).get("skip_cache", False), allow_drafts=not (probe or {}).get("no_drafts", False))
         if not loop.submit(req):
             raise HTTPException(429, "admission queue is full")
         return rid, events
@@ -342,10 +362,13 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         tools = body.get("tools") if body.get("tool_choice") != "none" else None
         probe = probe_of(http)
         ids_given = probe.get("token_ids")
-        prompt_ids = [int(x) for x in ids_given] if isinstance(ids_given, list) and ids_given else tok.encode(tmpl.render(msgs, tools=tools, thinking=thinking))
+        if isinstance(ids_given, list) and ids_given:
+            prompt_ids, embeds = [int(x) for x in ids_given], None
+        else:
+            prompt_ids, embeds = await build_prompt(msgs, tools=tools, thinking=thinking)
         max_tokens = int(body.get("max_completion_tokens") or body.get("max_tokens") or 256)
         t0, key = time.time(), key_of(authorization)
-        rid, events = start_generation(prompt_ids, body, max_tokens, constraint_for(body, len(prompt_ids)), probe)
+        rid, events = start_generation(prompt_ids, body, max_tokens, constraint_for(body, len(prompt_ids)), probe, embeds)
         created, cid = int(time.time()), "chatcmpl-" + rid
 
         if not body.get("stream"):
@@ -467,7 +490,11 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
             if kind == "message":
                 content = item.get("content")
                 if isinstance(content, list):
-                    content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
+                    if any(isinstance(p, dict) and p.get("type") == "input_image" for p in content):     # kept as parts for the vision front end
+                        content = [p if p.get("type") == "input_image" else {"type": "text", "text": p.get("text", "")}
+                                   for p in content if isinstance(p, dict)]
+                    else:
+                        content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
                 msgs.append({"role": item.get("role", "user"), "content": content})
             elif kind == "function_call":
                 msgs.append({"role": "assistant", "content": "", "tool_calls": [{"id": item.get("call_id"), "function": {
@@ -502,10 +529,10 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         thinking, stops = chat_options(body)
         if (body.get("reasoning") or {}).get("effort") not in (None, "none", "minimal"):
             thinking = True
-        prompt_ids = tok.encode(tmpl.render(msgs, tools=tools or None, system=body.get("instructions"), thinking=thinking))
+        prompt_ids, embeds = await build_prompt(msgs, tools=tools or None, system=body.get("instructions"), thinking=thinking)
         t0, key = time.time(), key_of(authorization)
         rf = {"response_format": (body.get("text") or {}).get("format")} if isinstance((body.get("text") or {}).get("format"), dict) else {}
-        rid, events = start_generation(prompt_ids, body, int(body.get("max_output_tokens") or 256), constraint_for(rf, len(prompt_ids)))
+        rid, events = start_generation(prompt_ids, body, int(body.get("max_output_tokens") or 256), constraint_for(rf, len(prompt_ids)), None, embeds)
 
         def finish(ids, reason):
             text, _ = _cut_at_stop(tok.decode(ids), stops)
@@ -578,18 +605,19 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         stored.pop(response_id, None)
         return {"id": response_id, "object": "response", "deleted": True}
 
-    def anthropic_prompt(body):
+    async def anthropic_prompt(body):
         msgs, tools = _anthropic_to_openai(body)
         system = body.get("system")
         if isinstance(system, list):
             system = "".join(b.get("text", "") for b in system if isinstance(b, dict))
         thinking, stops = chat_options(body)
-        return tok.encode(tmpl.render(msgs, tools=tools or None, system=system or None, thinking=thinking)), thinking, stops
+        ids, embeds = await build_prompt(msgs, tools=tools or None, system=system or None, thinking=thinking)
+        return ids, thinking, stops, embeds
 
     @app.post("/v1/messages/count_tokens")
     async def count_tokens(http: HttpRequest, authorization: str = Header(None), x_api_key: str = Header(None)):
         auth(authorization, x_api_key)
-        return {"input_tokens": len(anthropic_prompt(await http.json())[0])}
+        return {"input_tokens": len((await anthropic_prompt(await http.json()))[0])}
 
     @app.post("/v1/messages")
     async def messages(http: HttpRequest, authorization: str = Header(None), x_api_key: str = Header(None)):
@@ -597,9 +625,9 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
         body = await http.json()
         if "max_tokens" not in body:
             raise HTTPException(400, "max_tokens is required")
-        prompt_ids, thinking, stops = anthropic_prompt(body)
+        prompt_ids, thinking, stops, embeds = await anthropic_prompt(body)
         t0, key = time.time(), key_of(authorization, x_api_key)
-        rid, events = start_generation(prompt_ids, body, int(body["max_tokens"]))
+        rid, events = start_generation(prompt_ids, body, int(body["max_tokens"]), None, None, embeds)
         mid = "msg_" + rid
 
         def blocks_of(parsed):

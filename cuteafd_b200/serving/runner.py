@@ -9,6 +9,7 @@ cuteafd-transport/src/synthetic.rs:128-131).
 """
 from __future__ import annotations
 
+import bisect
 import hashlib
 
 import torch
@@ -127,10 +128,18 @@ class EngineRunner:
         if self._deferred is not None:
             raise RuntimeError("the previous speculative step of a linear-attention stack was not committed")
         tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages = [], [], [], [], [], [], [], []
+        over_rows, over_vals = [], []           # step rows whose embedding is an image row of the request
         for r in rows:
             seq = r.state.seq
             q_start.append(len(tokens))
             n = len(r.tokens)
+            emb = getattr(r.state.req, "embeds", None)
+            if emb is not None and r.start_pos <= emb["positions"][-1]:
+                pos = emb["positions"]
+                lo, hi = bisect.bisect_left(pos, r.start_pos), bisect.bisect_left(pos, r.start_pos + n)
+                if hi > lo:
+                    over_rows += [len(tokens) + p - r.start_pos for p in pos[lo:hi]]
+                    over_vals.append(emb["rows"][lo:hi])
             seq.ensure(eng_pool(self), r.start_pos + n)
             for i, t in enumerate(r.tokens):
                 tokens.append(t)
@@ -151,7 +160,9 @@ class EngineRunner:
         defer = self._recurrent and decode_like and any(len(r.tokens) > 1 and len(r.want_logits) == len(r.tokens) for r in rows)
         sh = StepShape(T=len(tokens), n_seq=len(rows), max_q_len=max_q, n_logits=len(logit_rows),
                        attn_splits=eng.attn_splits_for(len(rows), max_q, max(kv_len)) if decode_like else 1, uniform=uniform, defer_state=defer)
-        lane = eng.run(sh, use_graph=decode_like)
+        if over_rows:
+            eng.set_input_embeds(over_rows, torch.cat(over_vals) if len(over_vals) > 1 else over_vals[0])
+        lane = eng.run(sh, use_graph=decode_like and not over_rows)
         pending = (sh, [(id(r.state), r.start_pos, len(r.tokens)) for r in rows]) if defer else None
         if self.keep_hidden:
             for r, qs, ql in zip(rows, q_start, q_len):

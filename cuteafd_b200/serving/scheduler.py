@@ -36,6 +36,7 @@ class Request:
     constraint: object | None = None        # object with .mask(prefix_tokens) -> allowed-token bitmask or None
     use_cache: bool = True
     allow_drafts: bool = True
+    embeds: dict | None = None              # {"positions": sorted prompt positions, "rows": bf16 [n, hidden]}: image rows of a vision tower
     arrived: float = field(default_factory=time.time)
 
 

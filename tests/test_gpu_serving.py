@@ -212,3 +212,28 @@ def test_drafted_decoding_over_linear_attention_layers_is_lossless(per_channel):
     assert runner._deferred is None
     sp = SamplingParams(temperature=0.5, top_p=0.9, top_k=30, seed=3)
     assert run_requests(make(NgramDrafter())[0], prompts, 16, sampling=sp) == run_requests(make(None)[0], prompts, 16, sampling=sp)
+
+
+def test_image_rows_replace_placeholder_embeddings_exactly():
+    """Rows handed in for placeholder positions (a vision tower's output) enter the model exactly like token embeddings: a prompt
+    whose placeholders carry the embedding rows of other tokens generates what the prompt with those tokens generates - across
+    prefill chunks, and in a short last chunk that would otherwise replay a captured graph."""
+    spec, eng, sched, _ = build(prefix=False)
+    g = torch.Generator().manual_seed(21)
+    real = torch.randint(1, spec.vocab, (100,), generator=g).tolist()
+    positions = list(range(10, 30)) + [60, 61] + [97, 98]
+    holder = list(real)
+    for p in positions:
+        holder[p] = 0
+    rows = eng.weights.embed[torch.tensor([real[p] for p in positions], device=DEV)].contiguous()
+    want = run_requests(sched, [real], 10)
+    got = run_requests(sched, [holder], 10, embeds={"positions": positions, "rows": rows}, use_cache=False)
+    assert got == want
+    assert run_requests(sched, [holder], 10) != want            # the placeholders alone are a different prompt
+    # two requests in one round, one with image rows, one without
+    res = {0: [], 1: []}
+    sched.submit(Request("img", holder, max_tokens=6, on_token=lambda t, d, r: res[0].extend(t), use_cache=False,
+                         embeds={"positions": positions, "rows": rows}))
+    sched.submit(Request("txt", real[:40], max_tokens=6, on_token=lambda t, d, r: res[1].extend(t), use_cache=False))
+    sched.run_until_idle()
+    assert res[0] == want[0][:6] and res[1] == run_requests(sched, [real[:40]], 6)[0]

@@ -65,3 +65,123 @@ def test_forward_is_invariant_to_which_image_shares_the_batch_and_depends_on_all
         p2[-1] += 1.0                                     # the last patch belongs to the second merge group
         out2 = vision_forward(spec, w, p2, 4, 2)
         assert (out2[0] - out[0]).abs().max() > 1e-6      # bidirectional: the first group's row sees it too
+
+
+# ---------------------------------------------------------------- image inputs of the API (fake tower, fake runner)
+def _png(w, h, seed=0):
+    import io
+
+    import numpy as np
+    from PIL import Image
+    rng = np.random.default_rng(seed)
+    buf = io.BytesIO()
+    Image.fromarray(rng.integers(0, 256, (h, w, 3), dtype=np.uint8)).save(buf, format="PNG")
+    return buf.getvalue()
+
+
+class _FakeTower:
+    device = None
+
+    def __init__(self, spec):
+        self.spec, self.encodes, self.seen = spec, 0, []
+
+    def encode(self, images):
+        self.encodes += 1
+        self.seen += [tuple(im.shape) for im in images]
+        P, m = self.spec.patch, self.spec.merge
+        return [torch.zeros((im.shape[0] // P) * (im.shape[1] // P) // m ** 2, self.spec.out_hidden, dtype=torch.bfloat16) for im in images]
+
+
+def test_expand_prompt_places_pads_between_the_text_pieces():
+    from cuteafd_b200.serving.vision import IMAGE_MARK, expand_prompt, split_images
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "ab"}, {"type": "image_url", "image_url": {"url": "data:image/png;base64,QUJD"}},
+                                         {"type": "text", "text": "cd"}, {"type": "image", "source": {"type": "base64", "data": "QUJD"}}]},
+            {"role": "assistant", "content": "ok"}]
+    out, images = split_images(msgs)
+    assert len(images) == 2 and images[1] == b"ABC"
+    assert out[0]["content"][1] == {"type": "text", "text": IMAGE_MARK} and out[1] is msgs[1]
+    enc = lambda s: [ord(c) for c in s]
+    ids, pos = expand_prompt("ab" + IMAGE_MARK + "cd" + IMAGE_MARK, [3, 2], enc, 900, 901, 902)
+    assert ids == [97, 98, 900, 901, 901, 901, 902, 99, 100, 900, 901, 901, 902]
+    assert pos == [3, 4, 5, 10, 11]
+
+
+def test_chat_with_image_parts_runs_the_tower_and_bypasses_the_prefix_cache():
+    import base64
+
+    import pytest
+    pytest.importorskip("fastapi")
+    from fastapi.testclient import TestClient
+
+    from cuteafd_b200.engine.kv import PagePool
+    from cuteafd_b200.parallel.health import Health
+    from cuteafd_b200.ref.vision import VisionSpec
+    from cuteafd_b200.serving.api import ServingLoop, build_app
+    from cuteafd_b200.serving.prefix import PrefixCache
+    from cuteafd_b200.serving.runner import FakeRunner
+    from cuteafd_b200.serving.scheduler import Scheduler
+    from cuteafd_b200.serving.vision import VisionFrontEnd
+    spec = VisionSpec(patch=16, merge=2, out_hidden=8, max_tokens=64)
+    tower = _FakeTower(spec)
+    pool = PagePool(256)
+    runner = FakeRunner(vocab=96)
+    runner.next_token = lambda prefix: 32 + (sum(prefix[-3:]) % 60)
+    seen = []
+    real_run = runner.run
+    runner.run = lambda rows: (seen.extend((r.state.req.embeds, list(r.tokens), r.state.req.use_cache) for r in rows), real_run(rows))[1]
+    cache = PrefixCache(pool)
+    loop = ServingLoop(Scheduler(runner, pool, prefix=cache), Health()).start()
+    try:
+        url = "data:image/png;base64," + base64.b64encode(_png(96, 64)).decode()
+        plain = TestClient(build_app(loop))
+        body = {"model": "m", "max_tokens": 4, "messages": [{"role": "user", "content": [{"type": "text", "text": "what is this? "},
+                                                                                      {"type": "image_url", "image_url": {"url": url}}]}]}
+        assert plain.post("/v1/chat/completions", json=body).status_code == 400            # no tower: refused, not ignored
+        c = TestClient(build_app(loop, vision=VisionFrontEnd(tower, pad_id=90, start_id=91, end_id=92)))
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        assert tower.encodes == 1 and tower.seen == [(64, 96, 3)]                         # 96 x 64 pixels = 6 x 4 patches = 6 tokens
+        emb, toks, use_cache = next(s for s in seen if s[0] is not None)
+        assert toks.count(90) == 6 and toks.count(91) == 1 and toks.count(92) == 1
+        assert emb["rows"].shape == (6, 8) and [toks[p] for p in emb["positions"]] == [90] * 6
+        assert use_cache is False and cache.stats["hits"] == 0
+        assert r.json()["usage"]["prompt_tokens"] == len(toks)
+        # Anthropic surface: base64 image block
+        a = c.post("/v1/messages", json={"model": "m", "max_tokens": 3, "messages": [{"role": "user", "content": [
+            {"type": "image", "source": {"type": "base64", "media_type": "image/png", "data": base64.b64encode(_png(32, 32, 1)).decode()}},
+            {"type": "text", "text": "describe"}]}]})
+        assert a.status_code == 200, a.text
+        assert tower.encodes == 2
+        bad = c.post("/v1/chat/completions", json={"model": "m", "messages": [{"role": "user", "content": [
+            {"type": "image_url", "image_url": {"url": "https://example.com/cat.png"}}]}]})
+        assert bad.status_code == 400 and "not fetched" in bad.text
+    finally:
+        loop.stop()
+
+
+def test_vision_snapshot_round_trip(tmp_path):
+    """`visual.*` tensors written the way checkpoints ship them (patch convolution with a temporal axis, gate / up / down MLP) read
+    back into masters that give the same tower output."""
+    import json
+
+    from cuteafd_b200.loader.vision_checkpoint import read_vision_masters, vision_spec_from_snapshot, write_vision_snapshot
+    for kw in (dict(pos_grid=3), dict(norm="rmsnorm", mlp="swiglu", qk_norm=True, qkv_bias=False)):
+        spec = VisionSpec(hidden=32, depth=2, n_heads=2, head_dim=16, intermediate=48, patch=4, out_hidden=24, **kw)
+        w = init_vision_weights(spec, 7)
+        d = tmp_path / ("a" if "pos_grid" in kw else "b")
+        d.mkdir()
+        write_vision_snapshot(d / "model-vision.safetensors", spec, w)
+        (d / "config.json").write_text(json.dumps({"hidden_size": 24, "image_token_id": 77, "vision_start_token_id": 78, "vision_end_token_id": 79,
+            "vision_config": {"hidden_size": 32, "depth": 2, "num_heads": 2, "intermediate_size": 48, "patch_size": 4, "spatial_merge_size": 2,
+                              "hidden_act": "silu" if spec.mlp == "swiglu" else "gelu", "qk_norm": spec.qk_norm,
+                              "num_position_embeddings": spec.pos_grid ** 2}}))
+        got_spec, ids = vision_spec_from_snapshot(d)
+        assert ids == {"pad": 77, "start": 78, "end": 79}
+        want = (32, 2, 16, spec.mlp, spec.norm, spec.pos_grid, 24)
+        assert (got_spec.hidden, got_spec.depth, got_spec.head_dim, got_spec.mlp, got_spec.norm, got_spec.pos_grid, got_spec.out_hidden) == want
+        back = read_vision_masters(d, got_spec)
+        g = torch.Generator().manual_seed(1)
+        p = rgb_to_patches(torch.randint(0, 256, (8, 8, 3), generator=g, dtype=torch.uint8), spec)
+        a = vision_forward(spec, w, p, 2, 2)
+        b = vision_forward(got_spec.replace(qkv_bias=spec.qkv_bias), back, p, 2, 2)
+        assert torch.allclose(a, b, atol=1e-5)
