@@ -183,6 +183,46 @@ extern "C" int cuteafd_wait_add(const void* mine, const void* theirs, const void
   return CA_OK;
 }
 
+// ---------------------------------------------------------------- vocabulary-parallel LM head on a TP pair
+// Each rank multiplies the logit rows by ITS share of the vocabulary into a contiguous staging buffer and pushes it to the partner
+// (push_bytes); this kernel waits for the partner's share and writes the full rows out[r] = [share of rank 0 | share of rank 1],
+// so selection and sampling run on complete rows and both ranks hold the same bits.  Widths in float4 units.
+__global__ void wait_concat_kernel(const float4* __restrict__ mine, const float4* __restrict__ theirs, float4* __restrict__ out, int n_rows,
+                                   int w0, int w1, int my_rank, const uint32_t* flag, uint32_t* ctl, uint32_t step_offset,
+                                   unsigned long long timeout_ns, int* status) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) {
+    ok = 1;
+    if (ctl[0]) ok = 0;
+    else if (!wait_flag_bounded(flag, ctl[1] + step_offset, timeout_ns)) { ca_dev_fail(status, CA_DEV_TIMEOUT_FLAG, 200 + my_rank); atomicExch(&ctl[0], 1u); ok = 0; }
+  }
+  __syncthreads();
+  if (!ok) return;
+  const int W = w0 + w1;
+  const float4* first = my_rank == 0 ? mine : theirs;
+  const float4* second = my_rank == 0 ? theirs : mine;
+  const size_t n = (size_t)n_rows * W;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / W), c = (int)(i % W);
+    const float4* src = c < w0 ? first + (size_t)r * w0 + c : second + (size_t)r * w1 + (c - w0);
+    const bool remote = (c < w0) != (my_rank == 0);
+    out[i] = remote ? __ldcv(src) : *src;
+  }
+}
+
+extern "C" int cuteafd_wait_concat(const void* mine, const void* theirs, void* out, int n_rows, int w0, int w1, int my_rank, const void* flag,
+                                   void* ctl, unsigned step_offset, unsigned long long timeout_ns, int* status, cudaStream_t s) {
+  CA_REQUIRE(mine && theirs && out && flag && ctl && w0 > 0 && w1 > 0 && w0 % 4 == 0 && w1 % 4 == 0 && (my_rank == 0 || my_rank == 1),
+             "wait_concat: widths must be multiples of 4 floats");
+  if (n_rows <= 0) return CA_OK;
+  const size_t n = (size_t)n_rows * ((w0 + w1) / 4);
+  int blocks = (int)((n + 255) / 256); if (blocks > 296) blocks = 296; if (blocks < 1) blocks = 1;
+  wait_concat_kernel<<<blocks, 256, 0, s>>>((const float4*)mine, (const float4*)theirs, (float4*)out, n_rows, w0 / 4, w1 / 4, my_rank,
+                                             (const uint32_t*)flag, (uint32_t*)ctl, step_offset, timeout_ns, status);
+  CA_CHECK_LAUNCH("wait_concat");
+  return CA_OK;
+}
+
 // ---------------------------------------------------------------- dispatch: quantise + scatter rows to expert ranks
 // One block per (token of my share, route slot): the row is quantised into shared memory (FP4 payload + block scales,
 // or kept bf16) and copied to the slab of the rank that owns this slot's expert, at row (slot_row - base of that

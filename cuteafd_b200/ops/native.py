@@ -88,6 +88,7 @@ _PROTOS = {
     "cuteafd_wait_flags": [P, I, I, P, C.c_uint, C.c_ulonglong, P, P],
     "cuteafd_push_bytes": [P, P, C.c_size_t, P, P, C.c_uint, P, P],
     "cuteafd_wait_add": [P, P, P, P, C.c_size_t, I, P, P, C.c_uint, C.c_ulonglong, P, P],
+    "cuteafd_wait_concat": [P, P, P, I, I, I, I, P, P, C.c_uint, C.c_ulonglong, P, P],
     "cuteafd_dispatch_push": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, C.c_uint, P, P],
     "cuteafd_combine_push": [P, P, P, P, P, P, P, I, I, I, C.c_uint, P],
     "cuteafd_peer_copy": [P, P, C.c_size_t, I, P],

@@ -52,6 +52,10 @@ from .symm import SymmetricBlock
 
 PH_DISPATCH, PH_COMBINE, PH_TP = 0, 1, 2
 NFLAG = 32          # flag words per (phase, layer): dispatch lane * tp + tp_rank, combine micro * 8 + expert rank, TP micro * 2 + tp_rank
+# A TP pair splits the LM head over the vocabulary: each rank reads half of the head's weights and the halves of the logit rows are
+# exchanged over peer memory (reference: families/deepseek_v41/v41_target_head/distributed.rs, the vocab-sharded target head).
+VOCAB_PARALLEL = os.environ.get("CUTEAFD_VOCAB_PARALLEL", "1") == "1"
+HEAD_ROWS = 512     # logit rows per step the exchange buffers hold
 # GEMM epilogues can store straight into peer memory (output projection -> TP partner) and publish the flag themselves
 FUSED_PEER = os.environ.get("CUTEAFD_FUSED_PEER", "0") == "1"
 
@@ -116,7 +120,14 @@ def block_regions(spec: ModelSpec, plan: LanePlan, expert_kind: int) -> dict:
         "slab_q": L * t * row_bytes, "slab_sf": max(256, L * t * sf_row_bytes(H, expert_kind)), "idx": L * t * k * 4, "lane_T": 256,
         "y_recv": plan.n_micro * plan.planes * t * k * H * 2, "tp_recv": plan.n_micro * 2 * t * H * 2,
         "flags": 3 * n_flag_layers(spec) * NFLAG * 4,
+        "head_recv": min(t, HEAD_ROWS) * max(head_split(spec.vocab)) * 4 if plan.dep.tp == 2 and VOCAB_PARALLEL else 256,
     }
+
+
+def head_split(vocab: int) -> tuple[int, int]:
+    """Vocabulary shares of the two ranks of a TP pair (the cut sits on a 128-row weight tile)."""
+    v0 = max(128, (vocab // 2) // 128 * 128)
+    return v0, vocab - v0
 
 
 def make_block(spec: ModelSpec, plan: LanePlan, expert_kind: int, rank: int, device, group=None) -> SymmetricBlock:
@@ -192,6 +203,44 @@ class AttnRankEngine(Engine):
                 base = self.identity_rows.view(t, k, 1) + (torch.arange(P, dtype=torch.int32, device=device) * (t * k)).view(1, 1, P)
                 self.identity_rows_tp = base.reshape(t, k * P).contiguous()
             self.tp_recv = block.local("tp_recv", torch.bfloat16, (plan.n_micro, 2, t, H))
+        self.vocab_parallel = False
+        head = self.weights.lm_head
+        if (VOCAB_PARALLEL and self.tp == 2 and comm == "p2p" and block is not None and head is not None and head.kind == KIND_BF16
+                and spec.vocab % 8 == 0 and spec.vocab >= 256):
+            from ..ops import TcWeight, encode_tmap
+            self.vocab_parallel = True
+            self.head_w = head_split(spec.vocab)
+            lo = 0 if self.tp_rank == 0 else self.head_w[0]
+            rows = head.data[:, lo:lo + self.head_w[self.tp_rank]].contiguous()       # my share of the head; the full matrix is dropped
+            self.weights.lm_head = TcWeight(KIND_BF16, 1, rows.shape[1], rows.shape[2], rows, encode_tmap(rows, 128))
+            del head
+            self.head_rows = min(plan.t_cap, HEAD_ROWS)
+            self.head_stage = torch.zeros(self.head_rows, self.head_w[self.tp_rank], dtype=torch.float32, device=device)
+            self.head_recv = block.local("head_recv", torch.float32, (self.head_rows, self.head_w[1 - self.tp_rank]))
+
+    def _head(self, L, n: int, mb: int, t0: int, flag_layer: int):
+        """Logit rows of `n` gathered, normalised rows in L.xln -> L.logits and L.next_tok.  On a TP pair every rank multiplies by its share
+        of the vocabulary only (half the weight bytes per rank) and the two shares are exchanged over peer memory: both ranks end up
+        with the same full rows, so selection, sampling and grammar masks are unchanged."""
+        if not self.vocab_parallel:
+            ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=n, status=self.status)
+            ops.argmax_rows(L.logits, L.next_tok, rows=n, status=L.tok_status)
+            self.launches_per_step += 2
+            return
+        if t0 + n > self.head_rows:
+            raise ValueError(f"vocabulary-parallel head: {t0 + n} logit rows in a step (limit {self.head_rows}; CUTEAFD_VOCAB_PARALLEL=0 lifts it)")
+        peer, w = self.group_ranks[1 - self.tp_rank], self.head_w
+        mine = self.head_stage[t0:t0 + n]
+        ops.tc_linear(self.weights.lm_head, L.xln_act, mine, rows=n, status=self.status)
+        dst = self.block.peer_ptr(peer, "head_recv", t0 * w[self.tp_rank] * 4)
+        flag = self._flag(peer, PH_TP, flag_layer, 16 + mb * 2 + self.tp_rank)
+        peer_ops.push_bytes(mine, dst, n * w[self.tp_rank] * 4, flag, self.ctl, 0, self.done[0:1])
+        peer_ops.note_published([flag])
+        flag = self._flag(self.rank, PH_TP, flag_layer, 16 + mb * 2 + (1 - self.tp_rank))
+        yield [flag]
+        peer_ops.wait_concat(mine, self.head_recv[t0:t0 + n], L.logits, n, w[0], w[1], self.tp_rank, flag, self.ctl, 0, self.status)
+        ops.argmax_rows(L.logits, L.next_tok, rows=n, status=L.tok_status)
+        self.launches_per_step += 4
 
     def _make_weights(self, spec, device, seed, act_gs, masters):
         """This rank's share: attention heads split over the TP group, router / shared expert / dense layers replicated, no
@@ -383,9 +432,8 @@ class AttnRankEngine(Engine):
                     L, n = c.L, c.sh.n_logits
                     ops.gather_rows(L.x, c.md["logit_rows"], None, L.xl, n)
                     ops.add_rmsnorm(L.xl, None, self.weights.final_norm, L.xln, spec.rms_eps, rows=n)
-                    ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=n, status=self.status)
-                    ops.argmax_rows(L.logits, L.next_tok, rows=n, status=L.tok_status)
-                    self.launches_per_step += 4
+                    self.launches_per_step += 2
+                    yield from self._head(L, n, c.mb, c.t0 if c.sh.n_logits == c.sh.T else 0, spec.n_layers - 1)
                 self._unbind(c)
         finally:
             self.md = base_md
@@ -535,8 +583,7 @@ class AttnRankEngine(Engine):
         if sh.n_logits:
             ops.gather_rows(L.x, self.md["logit_rows"], None, L.xl, sh.n_logits)
             ops.add_rmsnorm(L.xl, None, norm, L.xln, spec.rms_eps, rows=sh.n_logits)
-            ops.tc_linear(self.weights.lm_head, L.xln_act, L.logits, rows=sh.n_logits, status=self.status)
-            ops.argmax_rows(L.logits, L.next_tok, rows=sh.n_logits, status=L.tok_status)
+            yield from self._head(L, sh.n_logits, 0, 0, li)
         yield L
 
     def mtp_forward(self, depth: int, sh: StepShape, prev_hidden: torch.Tensor) -> Lane:

@@ -46,6 +46,14 @@ def wait_add(mine, theirs, residual, out, elems: int, my_rank: int, flag_ptr: in
          timeout_ns, ptr(status), stream())
 
 
+def wait_concat(mine, theirs, out, n_rows: int, w0: int, w1: int, my_rank: int, flag_ptr: int, ctl, step_offset: int, status,
+                timeout_ns: int | None = None):
+    """out[r] = [share of rank 0 | share of rank 1] (fp32 rows) once the partner's share has landed (vocabulary-parallel head)."""
+    timeout_ns = wait_ns() if timeout_ns is None else timeout_ns
+    call("cuteafd_wait_concat", ptr(mine), ptr(theirs), ptr(out), n_rows, w0, w1, my_rank, flag_ptr, ptr(ctl), step_offset, timeout_ns,
+         ptr(status), stream())
+
+
 def dispatch_push(x, idx, slot_row, offsets, slab_q_tbl, slab_sf_tbl, idx_tbl, flag_tbl, inv_gs, ctl, done_counter, T0, T1, H, k,
                   E_local, n_ep, kind, sf_ld, rows_cap, step_offset, status):
     call("cuteafd_dispatch_push", ptr(x), ptr(idx), ptr(slot_row), ptr(offsets), C.addressof(slab_q_tbl),

@@ -124,3 +124,24 @@ def test_scheduler_refuses_a_wait_without_a_push():
 
     with pytest.raises(Deadlock):
         run_programs({"a": lonely()})
+
+
+def test_tp_pair_splits_the_head_over_the_vocabulary():
+    """On a TP pair each rank keeps and multiplies by its share of the LM head only; the shares of the logit rows are exchanged over
+    peer memory, so both ranks select from the same complete rows (tokens equal the single-GPU engine's: the layout test above).
+    Here: the split is engaged, the weights are halved, and both ranks hold bit-identical full logits after a step."""
+    from cuteafd_b200.parallel.afd import head_split
+    from cuteafd_b200.parallel.local import generate_local
+    spec = tiny_spec().replace(quant=QuantSpec(experts="bf16", dense="bf16"))
+    masters = init_weights(spec, 5)
+    dep = default_deployment(4)
+    world = _world(spec, masters, dep, 1, False)
+    a, b = (world.engines[r] for r in dep.attn_ranks[:2])
+    assert a.vocab_parallel and b.vocab_parallel
+    w = head_split(spec.vocab)
+    assert (a.weights.lm_head.N, b.weights.lm_head.N) == w and sum(w) == spec.vocab
+    prompts = [_prompts(spec, 3, n=3)]
+    got = generate_local(world, prompts, 4)
+    assert got[0] == _single_gpu_tokens(spec, masters, prompts[0], 4)
+    la, lb = a.lane(3).logits[:3], b.lane(3).logits[:3]
+    assert torch.equal(la, lb) and float(la.abs().max()) > 0
