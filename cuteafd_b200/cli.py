@@ -213,30 +213,38 @@ def _vision_front_end(a, spec):
     random:DEPTH` builds a randomly initialised tower of the Qwen-VL shape for shape / throughput work, `--vision off` (and multi-GPU
     layouts, whose engines take token ids only) serve text alone.  Reference: cuteafd-daemon/src/cli.rs (vision / audio encoder flags)."""
     mode = getattr(a, "vision", "auto")
-    if mode == "off" or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         return None
     import torch
     from .models.vision import VisionTower
     from .serving.vision import VisionFrontEnd
     dev = torch.device("cuda", a.device)
+    audio_kw = {}
+    amode = getattr(a, "audio", "off")
+    if amode.startswith("random"):          # a randomly initialised encoder of the Whisper-large shape (32 blocks by default)
+        from .models.audio import AudioTower
+        from .ref.audio import AudioSpec, init_audio_weights
+        depth = int(amode.split(":", 1)[1]) if ":" in amode else 2
+        asp = AudioSpec(hidden=1280, depth=depth, n_heads=20, head_dim=64, intermediate=5120, out_hidden=spec.hidden, n_mels=128)
+        audio_kw = dict(audio_tower=AudioTower(asp, init_audio_weights(asp, 0), dev), audio_pad_id=min(spec.vocab - 2, 151646))
     if mode.startswith("random"):
         from .ref.vision import VisionSpec, init_vision_weights
         depth = int(mode.split(":", 1)[1]) if ":" in mode else 2
         vs = VisionSpec(hidden=1152, depth=depth, n_heads=16, head_dim=72, intermediate=4304, patch=16, out_hidden=spec.hidden, pos_grid=48)
         tower = VisionTower(vs, init_vision_weights(vs, 0), dev, max_patches=a.vision_max_patches)
-        return VisionFrontEnd(tower, pad_id=min(spec.vocab - 1, 151655), start_id=None, end_id=None, max_images=a.vision_max_images)
-    if not os.path.isdir(a.model):
-        return None
+        return VisionFrontEnd(tower, pad_id=min(spec.vocab - 1, 151655), start_id=None, end_id=None, max_images=a.vision_max_images, **audio_kw)
+    if mode == "off" or not os.path.isdir(a.model):
+        return VisionFrontEnd(None, max_images=a.vision_max_images, **audio_kw) if audio_kw else None
     from .loader.vision_checkpoint import read_vision_masters, vision_spec_from_snapshot
     found = vision_spec_from_snapshot(a.model)
     if found is None:
-        return None
+        return VisionFrontEnd(None, max_images=a.vision_max_images, **audio_kw) if audio_kw else None
     vs, ids = found
     if vs.out_hidden != spec.hidden:
         raise SystemExit(f"vision tower emits rows of {vs.out_hidden}, the decoder's hidden size is {spec.hidden}")
     tower = VisionTower(vs, read_vision_masters(a.model, vs), dev, max_patches=a.vision_max_patches)
     print(f"vision tower: depth {vs.depth}, hidden {vs.hidden}, {tower.nbytes() / 2**20:.0f} MiB", flush=True)
-    return VisionFrontEnd(tower, pad_id=int(ids["pad"]), start_id=ids["start"], end_id=ids["end"], max_images=a.vision_max_images)
+    return VisionFrontEnd(tower, pad_id=int(ids["pad"]), start_id=ids["start"], end_id=ids["end"], max_images=a.vision_max_images, **audio_kw)
 
 
 def cmd_usage(a) -> int:
@@ -457,6 +465,7 @@ def main(argv=None) -> int:
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.add_argument("--n-micro", type=int, default=0, help="multi-GPU: micro-batches the attention ranks keep in flight (0 = the layout's default)")
     p.add_argument("--vision", default="auto", help="auto (tower of the snapshot, if it has one) | off | random[:DEPTH]")
+    p.add_argument("--audio", default="off", help="off | random[:DEPTH] (an audio encoder of the Whisper shape with random weights; `input_audio` parts accepted)")
     p.add_argument("--vision-max-patches", type=int, default=16384, help="patches of all images of one request")
     p.add_argument("--vision-max-images", type=int, default=8)
     p.set_defaults(fn=cmd_serve)

@@ -126,6 +126,29 @@ __global__ void vision_bias_act_kernel(const bf16* __restrict__ y, int ldy, cons
   }
 }
 
+// Width-3 convolution as a GEMM: dst[t, k * C + c] = src[t * stride + k - 1, c] (zero rows outside [0, T)); 16-byte vectors.
+// The audio tower's two convolutions over the frame axis (stride 1, then stride 2) read their operand rows from this.
+__global__ void audio_im2col3_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int T, int T_out, int C8, int stride) {
+  pdl_launch(); pdl_wait();
+  const size_t n = (size_t)T_out * 3 * C8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / (3 * C8)), r = (int)(i % (3 * C8)), k = r / C8, c = r % C8;
+    const int ts = t * stride + k - 1;
+    dst[i] = (ts >= 0 && ts < T) ? src[(size_t)ts * C8 + c] : make_uint4(0, 0, 0, 0);
+  }
+}
+
+extern "C" int cuteafd_audio_im2col3(const void* src, void* dst, int T, int C, int stride, cudaStream_t s) {
+  CA_REQUIRE(src && dst && C % 8 == 0 && (stride == 1 || stride == 2) && (stride == 1 || T % 2 == 0), "audio_im2col3: C %% 8 == 0, stride 1 or 2");
+  if (T <= 0) return CA_OK;
+  const int T_out = T / stride;
+  const size_t n = (size_t)T_out * 3 * (C / 8);
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  CA_LAUNCH_PDL(audio_im2col3_kernel, blocks, 256, 0, s, (const uint4*)src, (uint4*)dst, T, T_out, C / 8, stride);
+  CA_CHECK_LAUNCH("audio_im2col3");
+  return CA_OK;
+}
+
 extern "C" int cuteafd_vision_rgb_patches(const uint8_t* rgb, const float* lut, void* out, int gh, int gw, int P, int merge, int Kp,
                                           cudaStream_t s) {
   CA_REQUIRE(rgb && lut && out && gh > 0 && gw > 0 && P > 0 && merge > 0 && gh % merge == 0 && gw % merge == 0 && Kp >= 3 * P * P,

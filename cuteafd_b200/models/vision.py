@@ -55,34 +55,27 @@ def image_tokens(rgb: torch.Tensor, spec: VisionSpec) -> int:
     return (rgb.shape[0] // spec.patch) * (rgb.shape[1] // spec.patch) // spec.merge ** 2
 
 
-class VisionTower:
-    def __init__(self, spec: VisionSpec, masters: dict, device, max_patches: int = 16384, max_images: int = 16):
+class EncoderTower:
+    """Blocks, merger and buffers shared by the vision and audio towers; a subclass adds the front end that fills the fp32 residual
+    `x` and the first normed rows `h`.  `group`: rows concatenated by the merger (merge^2 patches, 2 audio frames)."""
+
+    def __init__(self, spec, masters: dict, device, max_rows: int, max_items: int, group: int):
         native.require_gpu_lib()
         if spec.head_dim > 128 or spec.head_dim % 4 or spec.hidden % 8 or spec.intermediate % 8 or spec.out_hidden % 8:
-            raise ValueError("vision tower: head_dim <= 128 and a multiple of 4; widths multiples of 8")
+            raise ValueError("encoder tower: head_dim <= 128 and a multiple of 4; widths multiples of 8")
         self.spec, self.device = spec, torch.device(device)
-        self.max_patches = N = -(-max_patches // 256) * 256
-        self.max_images = max_images
+        self.max_patches = N = -(-max_rows // 256) * 256
+        self.max_images = max_items
+        self.group = group
         H, nh, hd, I = spec.hidden, spec.n_heads, spec.head_dim, spec.intermediate
-        self.Kp = _pad8(spec.patch_dim)
         dev = self.device
-
-        def mat(w, k_pad=None):
-            w = w.float()
-            if k_pad and k_pad != w.shape[1]:
-                w = torch.cat([w, w.new_zeros(w.shape[0], k_pad - w.shape[1])], dim=1)
-            return TcWeight.from_master(w, KIND_BF16, dev)
-
-        def vec(v):
-            return None if v is None else v.float().to(dev).contiguous()
+        mat, vec = self._mat, self._vec
 
         def proj_padded(w):              # [H, nh * hd] -> [H, nh * 128]: zero columns where the attention output is padding
             out = w.new_zeros(w.shape[0], nh, 128)
             out[:, :, :hd] = w.reshape(w.shape[0], nh, hd)
             return out.reshape(w.shape[0], nh * 128)
 
-        self.patch_w, self.patch_b = mat(masters["patch_w"], self.Kp), vec(masters["patch_b"])
-        self.pos_embed = masters.get("pos_embed")
         self.blocks = []
         for b in masters["blocks"]:
             self.blocks.append({
@@ -91,13 +84,13 @@ class VisionTower:
                 "proj": mat(proj_padded(b["proj_w"].float())), "proj_b": vec(b["proj_b"]),
                 "fc1": mat(b["fc1_w"]), "fc1_b": vec(b["fc1_b"]), "fc2": mat(b["fc2_w"]), "fc2_b": vec(b["fc2_b"])})
         self.merger_norm = (vec(masters["merger_norm_w"]), vec(masters.get("merger_norm_b")))
-        self.mfc1, self.mfc1_b = mat(masters["merger_fc1_w"]), vec(masters["merger_fc1_b"])
+        self.mfc1 = self.mfc1_b = None              # a single projection (audio) or fc1 -> GELU -> fc2 (vision)
+        if "merger_fc1_w" in masters:
+            self.mfc1, self.mfc1_b = mat(masters["merger_fc1_w"]), vec(masters["merger_fc1_b"])
         self.mfc2, self.mfc2_b = mat(masters["merger_fc2_w"]), vec(masters["merger_fc2_b"])
-        self.lut = normalisation_lut(spec).to(dev).contiguous()
 
-        M, fc1_n = spec.merge ** 2 * H, (2 if spec.mlp == "swiglu" else 1) * I
+        M, fc1_n = group * H, (2 if spec.mlp == "swiglu" else 1) * I
         bf = dict(dtype=torch.bfloat16, device=dev)
-        self.patches = torch.zeros(N, self.Kp, **bf)
         self.x = torch.zeros(N, H, dtype=torch.float32, device=dev)
         self.h = torch.zeros(N, H, **bf)                          # normed rows: input of qkv / fc1 / (as [N / m^2, m^2 H]) the merger
         self.y = torch.zeros(N, H, **bf)                          # GEMM outputs that go into the residual
@@ -106,9 +99,9 @@ class VisionTower:
         self.attn = torch.zeros(N, nh * 128, **bf)
         self.f = torch.zeros(N, max(fc1_n, M), **bf)              # fc1 / merger fc1 output before the activation
         self.a = torch.zeros(N, max(I, M), **bf)                  # activated rows
-        self.out = torch.zeros(N // spec.merge ** 2, spec.out_hidden, **bf)
-        self.o_raw = torch.zeros(N // spec.merge ** 2, spec.out_hidden, **bf)
-        n_pages = N // PAGE + max_images
+        self.out = torch.zeros(N // group, spec.out_hidden, **bf)
+        self.o_raw = torch.zeros(N // group, spec.out_hidden, **bf)
+        n_pages = N // PAGE + max_items
         self.kv = torch.zeros(1, n_pages * PAGE, 2, nh, 128, **bf)
         self.kv_tmap = ops.encode_kv_tmaps(self.kv)[0]
         self.cs = torch.zeros(N, hd, dtype=torch.float32, device=dev)
@@ -118,9 +111,18 @@ class VisionTower:
         self.encodes = 0
 
     # ------------------------------------------------------------------
+    def _mat(self, w, k_pad=None):
+        w = w.float()
+        if k_pad and k_pad != w.shape[1]:
+            w = torch.cat([w, w.new_zeros(w.shape[0], k_pad - w.shape[1])], dim=1)
+        return TcWeight.from_master(w, KIND_BF16, self.device)
+
+    def _vec(self, v):
+        return None if v is None else v.float().to(self.device).contiguous()
+
     def nbytes(self) -> int:
-        w = self.patch_w.nbytes + self.mfc1.nbytes + self.mfc2.nbytes + sum(b[k].nbytes for b in self.blocks for k in ("qkv", "proj", "fc1", "fc2"))
-        s = sum(t.numel() * t.element_size() for t in (self.patches, self.x, self.h, self.y, self.qkv, self.q, self.attn, self.f, self.a,
+        w = (self.mfc1.nbytes if self.mfc1 else 0) + self.mfc2.nbytes + sum(b[k].nbytes for b in self.blocks for k in ("qkv", "proj", "fc1", "fc2"))
+        s = sum(t.numel() * t.element_size() for t in (self.x, self.h, self.y, self.qkv, self.q, self.attn, self.f, self.a,
                                                        self.out, self.o_raw, self.kv, self.cs))
         return w + s
 
@@ -141,7 +143,72 @@ class VisionTower:
     def _bias_act(self, y, bias, out, rows, n_out, act):
         native.call("cuteafd_vision_bias_act", ptr(y), y.stride(0), ptr(bias), ptr(out), out.stride(0), rows, n_out, ACTS[act], native.stream())
 
-    # ------------------------------------------------------------------
+    def _first_norm(self):
+        return self.blocks[0]["norm1"] if self.blocks else self.merger_norm
+
+    def _finish(self, counts: list[int]) -> list[torch.Tensor]:
+        """Blocks + merger over the rows a front end left in `x` (fp32 residual) and `h` (first norm applied); one sequence per item."""
+        spec, dev = self.spec, self.device
+        H, nh, hd, I, g = spec.hidden, spec.n_heads, spec.head_dim, spec.intermediate, self.group
+        N = sum(counts)
+        max_pages = max(-(-c // PAGE) for c in counts)
+        page_table = torch.zeros(len(counts), max_pages, dtype=torch.int32)
+        slots, page = [], 0
+        for i, c in enumerate(counts):
+            np_ = -(-c // PAGE)
+            page_table[i, :np_] = torch.arange(page, page + np_, dtype=torch.int32)
+            slots.append(page * PAGE + torch.arange(c, dtype=torch.int32))
+            page += np_
+        slot = torch.cat(slots).to(dev)
+        lens = torch.tensor(counts, dtype=torch.int32)
+        q_start = (torch.cumsum(lens, 0) - lens).to(torch.int32).to(dev)
+        lens_d, page_table = lens.to(dev), page_table.to(dev)
+        for li, b in enumerate(self.blocks):
+            self._linear(b["qkv"], "h", self.h, self.qkv, N)
+            native.call("cuteafd_vision_qkv_rope_store", ptr(self.qkv), ptr(b["qkv_b"]), ptr(self.cs), ptr(b["q_norm"]), ptr(b["k_norm"]), ptr(self.q),
+                        ptr(self.kv), ptr(slot), N, nh, hd, spec.eps, ptr(self.status), native.stream())
+            native.call("cuteafd_gqa_prefill_attention", ptr(self.q), ptr(self.kv_tmap), ptr(page_table), ptr(lens_d), ptr(q_start), ptr(lens_d), None,
+                        ptr(self.attn), N, len(counts), max(counts), nh * 128, nh, nh, max_pages, -1, hd ** -0.5, ptr(self.status), native.stream())
+            self._linear(b["proj"], "attn", self.attn, self.y, N)
+            self._add_norm(self.y, b["proj_b"], b["norm2"], self.h, N)
+            self._linear(b["fc1"], "h", self.h, self.f, N)
+            self._bias_act(self.f, b["fc1_b"], self.a, N, I, spec.mlp)
+            self._linear(b["fc2"], "a", self.a[:, :I], self.y, N)
+            nxt = self.blocks[li + 1]["norm1"] if li + 1 < len(self.blocks) else self.merger_norm
+            self._add_norm(self.y, b["fc2_b"], nxt, self.h, N)
+        Nm, M = N // g, g * H
+        if self.mfc1 is not None:
+            self._linear(self.mfc1, "hm", self.h.view(-1, M), self.f, Nm)
+            self._bias_act(self.f, self.mfc1_b, self.a, Nm, M, "gelu")
+            self._linear(self.mfc2, "am", self.a[:, :M], self.o_raw, Nm)
+        else:
+            self._linear(self.mfc2, "hm", self.h.view(-1, M), self.o_raw, Nm)
+        self._bias_act(self.o_raw, self.mfc2_b, self.out, Nm, spec.out_hidden, "none")
+        word = int(self.status[0])
+        if word:
+            self.status.zero_()
+            raise RuntimeError(f"encoder tower: device status {native.decode_status(word)}")
+        self.encodes += 1
+        outs, o = [], 0
+        for c in counts:
+            outs.append(self.out[o:o + c // g].clone())
+            o += c // g
+        return outs
+
+
+
+class VisionTower(EncoderTower):
+    def __init__(self, spec: VisionSpec, masters: dict, device, max_patches: int = 16384, max_images: int = 16):
+        super().__init__(spec, masters, device, max_patches, max_images, spec.merge ** 2)
+        self.Kp = _pad8(spec.patch_dim)
+        self.patch_w, self.patch_b = self._mat(masters["patch_w"], self.Kp), self._vec(masters["patch_b"])
+        self.pos_embed = masters.get("pos_embed")
+        self.lut = normalisation_lut(spec).to(self.device).contiguous()
+        self.patches = torch.zeros(self.max_patches, self.Kp, dtype=torch.bfloat16, device=self.device)
+
+    def nbytes(self) -> int:
+        return super().nbytes() + self.patch_w.nbytes + self.patches.numel() * 2
+
     @torch.no_grad()
     def encode(self, images: list[torch.Tensor]) -> list[torch.Tensor]:
         """`images`: resized uint8 [gh * P, gw * P, 3] tensors (`load_image`).  Returns one bf16 [tokens, out_hidden] tensor per image."""
@@ -156,18 +223,13 @@ class VisionTower:
         N = sum(counts)
         if N > self.max_patches:
             raise ValueError(f"vision tower: {N} patches in one call (limit {self.max_patches})")
-        max_pages = max(-(-c // PAGE) for c in counts)
-        page_table = torch.zeros(len(images), max_pages, dtype=torch.int32)
-        slots, cs_rows, pos_rows = [], [], []
-        off = page = 0
-        for i, (im, (gh, gw), c) in enumerate(zip(images, grids, counts)):
+        cs_rows, pos_rows = [], []
+        off = 0
+        for im, (gh, gw), c in zip(images, grids, counts):
             if im.dtype != torch.uint8 or im.shape[0] % (P * m) or im.shape[1] % (P * m) or im.shape[2] != 3:
                 raise ValueError("vision tower: images are uint8 [gh * P, gw * P, 3] with whole merge groups")
             rgb = im.contiguous().to(self.device)
             native.call("cuteafd_vision_rgb_patches", ptr(rgb), ptr(self.lut), ptr(self.patches[off:]), gh, gw, P, m, self.Kp, native.stream())
-            np_ = -(-c // PAGE)
-            page_table[i, :np_] = torch.arange(page, page + np_, dtype=torch.int32)
-            slots.append(page * PAGE + torch.arange(c, dtype=torch.int32))
             if (gh, gw) not in self._grids:          # rotary angles and resampled position rows depend on the grid only
                 if len(self._grids) >= 64:
                     self._grids.clear()
@@ -177,44 +239,9 @@ class VisionTower:
             if self.pos_embed is not None:
                 pos_rows.append(self._grids[(gh, gw)][1])
             off += c
-            page += np_
-        dev = self.device
-        slot = torch.cat(slots).to(dev)
         self.cs[:N].copy_(torch.cat(cs_rows))
-        lens = torch.tensor(counts, dtype=torch.int32)
-        q_start = (torch.cumsum(lens, 0) - lens).to(torch.int32).to(dev)
-        lens_d, page_table = lens.to(dev), page_table.to(dev)
-
         self._linear(self.patch_w, "patches", self.patches, self.y, N)
         if pos_rows:
             self.x[:N].copy_(torch.cat(pos_rows))
-        first_norm = self.blocks[0]["norm1"] if self.blocks else self.merger_norm
-        self._add_norm(self.y, self.patch_b, first_norm, self.h, N, init=not pos_rows)
-        for li, b in enumerate(self.blocks):
-            self._linear(b["qkv"], "h", self.h, self.qkv, N)
-            native.call("cuteafd_vision_qkv_rope_store", ptr(self.qkv), ptr(b["qkv_b"]), ptr(self.cs), ptr(b["q_norm"]), ptr(b["k_norm"]), ptr(self.q),
-                        ptr(self.kv), ptr(slot), N, nh, hd, spec.eps, ptr(self.status), native.stream())
-            native.call("cuteafd_gqa_prefill_attention", ptr(self.q), ptr(self.kv_tmap), ptr(page_table), ptr(lens_d), ptr(q_start), ptr(lens_d), None,
-                        ptr(self.attn), N, len(images), max(counts), nh * 128, nh, nh, max_pages, -1, hd ** -0.5, ptr(self.status), native.stream())
-            self._linear(b["proj"], "attn", self.attn, self.y, N)
-            self._add_norm(self.y, b["proj_b"], b["norm2"], self.h, N)
-            self._linear(b["fc1"], "h", self.h, self.f, N)
-            self._bias_act(self.f, b["fc1_b"], self.a, N, I, spec.mlp)
-            self._linear(b["fc2"], "a", self.a[:, :I], self.y, N)
-            nxt = self.blocks[li + 1]["norm1"] if li + 1 < len(self.blocks) else self.merger_norm
-            self._add_norm(self.y, b["fc2_b"], nxt, self.h, N)
-        Nm, M = N // m ** 2, m ** 2 * H
-        self._linear(self.mfc1, "hm", self.h.view(-1, M), self.f, Nm)
-        self._bias_act(self.f, self.mfc1_b, self.a, Nm, M, "gelu")
-        self._linear(self.mfc2, "am", self.a[:, :M], self.o_raw, Nm)
-        self._bias_act(self.o_raw, self.mfc2_b, self.out, Nm, spec.out_hidden, "none")
-        word = int(self.status[0])
-        if word:
-            self.status.zero_()
-            raise RuntimeError(f"vision tower: device status {native.decode_status(word)}")
-        self.encodes += 1
-        outs, o = [], 0
-        for c in counts:
-            outs.append(self.out[o:o + c // m ** 2].clone())
-            o += c // m ** 2
-        return outs
+        self._add_norm(self.y, self.patch_b, self._first_norm(), self.h, N, init=not pos_rows)
+        return self._finish(counts)

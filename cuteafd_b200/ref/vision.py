@@ -191,14 +191,24 @@ def vision_forward(spec: VisionSpec, w: dict, patches: torch.Tensor, gh: int, gw
     cs = rope_table(gh, gw, spec)
     if taps is not None:
         taps["embed"] = x.clone()
-    for i, b in enumerate(w["blocks"]):
+    x = encoder_blocks(spec, w["blocks"], x, cs, taps)
+    h = _norm(x, w["merger_norm_w"], w.get("merger_norm_b"), spec.eps).reshape(N // spec.merge ** 2, -1)
+    h = F.gelu(h @ w["merger_fc1_w"].T + w["merger_fc1_b"])
+    return h @ w["merger_fc2_w"].T + w["merger_fc2_b"]
+
+
+def encoder_blocks(spec, blocks: list, x: torch.Tensor, cs: torch.Tensor | None, taps: dict | None = None) -> torch.Tensor:
+    """Pre-norm bidirectional transformer blocks over one item's rows x [N, hidden]; `cs`: rotary table or None (no rotation)."""
+    N, nh, hd = x.shape[0], spec.n_heads, spec.head_dim
+    for i, b in enumerate(blocks):
         h = _norm(x, b["norm1_w"], b.get("norm1_b"), spec.eps)
         qkv = h @ b["qkv_w"].T + (b["qkv_b"] if "qkv_b" in b else 0)
         q, k, v = (t.reshape(N, nh, hd) for t in qkv.chunk(3, dim=-1))
         if spec.qk_norm:
             q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + spec.eps) * b["q_norm"]
             k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + spec.eps) * b["k_norm"]
-        q, k = _rotate(q, cs), _rotate(k, cs)
+        if cs is not None:
+            q, k = _rotate(q, cs), _rotate(k, cs)
         p = torch.softmax(torch.einsum("qhd,khd->hqk", q, k) * hd ** -0.5, dim=-1)
         o = torch.einsum("hqk,khd->qhd", p, v).reshape(N, nh * hd)
         x = x + o @ b["proj_w"].T + b["proj_b"]
@@ -206,6 +216,4 @@ def vision_forward(spec: VisionSpec, w: dict, patches: torch.Tensor, gh: int, gw
         x = x + _act(h @ b["fc1_w"].T + b["fc1_b"], spec.mlp) @ b["fc2_w"].T + b["fc2_b"]
         if taps is not None:
             taps[f"block{i}"] = x.clone()
-    h = _norm(x, w["merger_norm_w"], w.get("merger_norm_b"), spec.eps).reshape(N // spec.merge ** 2, -1)
-    h = F.gelu(h @ w["merger_fc1_w"].T + w["merger_fc1_b"])
-    return h @ w["merger_fc2_w"].T + w["merger_fc2_b"]
+    return x

@@ -235,17 +235,17 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
 
     async def build_prompt(msgs, **render_kw):
         """(prompt ids, image rows of the request or None)."""
-        image_kinds = ("image_url", "input_image", "image")
+        image_kinds = ("image_url", "input_image", "image", "input_audio")
         has_image = any(isinstance(m, dict) and isinstance(m.get("content"), list)
                         and any(isinstance(p, dict) and p.get("type") in image_kinds for p in m["content"]) for m in msgs)
         if not has_image:
             return tok.encode(tmpl.render(msgs, **render_kw)), None
         if vision is None:
-            raise HTTPException(400, "this server has no vision tower: image inputs are not accepted")
+            raise HTTPException(400, "this server has no vision tower: image / audio inputs are not accepted")
         try:
             return await asyncio.to_thread(vision.prepare, msgs, lambda m: tmpl.render(m, **render_kw), tok.encode)
         except (ValueError, OSError) as e:          # undecodable image, too many images, remote URL
-            raise HTTPException(400, f"invalid image input: {e}") from None
+            raise HTTPException(400, f"invalid image / audio input: {e}") from None
 
     def start_generation(prompt_ids, body, max_tokens, constraint=None, probe=None, embeds=None):
         if not loop.healthy():

@@ -266,3 +266,22 @@ def test_vision_tower_matches_oracle(variant):
     # a second call reuses the buffers and the scratch store: same rows for the same image alone
     again = tower.encode([images[1]])[0]
     assert float((again.float() - outs[1].float()).abs().max()) < 2e-2
+
+
+def test_audio_tower_matches_oracle():
+    """Audio encoder (convolution front end as GEMMs over im2col rows, shared encoder blocks without rotation, two-frame mean folded
+    into the projection GEMM) against the fp32 oracle: two clips of different lengths in one batch."""
+    from cuteafd_b200.models.audio import AudioTower
+    from cuteafd_b200.ref.audio import AudioSpec, audio_bf16_round, audio_forward, init_audio_weights, log_mel
+    spec = AudioSpec(hidden=128, depth=2, n_heads=2, head_dim=64, intermediate=256, out_hidden=192, n_mels=64)
+    w = audio_bf16_round(init_audio_weights(spec, 4))
+    tower = AudioTower(spec, w, DEV, max_frames=2048, max_clips=4)
+    g = torch.Generator().manual_seed(9)
+    clips = [log_mel(torch.randn(n, generator=g) * 0.3, spec) for n in (16000 * 3, 16000)]
+    outs = tower.encode(clips)
+    torch.cuda.synchronize()
+    for f, got in zip(clips, outs):
+        want = audio_forward(spec, w, f.bfloat16().float())
+        assert got.shape == want.shape == (f.shape[0] // 4, 192)
+        err = float((got.float().cpu() - want).norm() / want.norm())
+        assert err < 0.03, f"{f.shape[0]} frames: rel err {err}"

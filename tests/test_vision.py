@@ -185,3 +185,83 @@ def test_vision_snapshot_round_trip(tmp_path):
         a = vision_forward(spec, w, p, 2, 2)
         b = vision_forward(got_spec.replace(qkv_bias=spec.qkv_bias), back, p, 2, 2)
         assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_audio_oracle_front_end_and_im2col_weight_order():
+    """The convolution-as-GEMM layout the device uses (operand columns (tap, channel)) reproduces F.conv1d in the oracle's arithmetic,
+    and the mel front end gives whole groups of four frames."""
+    import torch.nn.functional as F
+
+    from cuteafd_b200.ref.audio import AudioSpec, audio_forward, init_audio_weights, log_mel, mel_filters
+    spec = AudioSpec(hidden=32, depth=1, n_heads=2, head_dim=16, intermediate=48, out_hidden=24, n_mels=16)
+    fb = mel_filters(spec)
+    assert fb.shape == (16, 201) and (fb >= 0).all() and (fb.sum(dim=1) > 0).all()
+    frames = log_mel(torch.randn(16000, generator=torch.Generator().manual_seed(0)), spec)
+    assert frames.shape == (100, 16)
+    w = init_audio_weights(spec, 1)
+    out = audio_forward(spec, w, frames)
+    assert out.shape == (25, 24) and torch.isfinite(out).all()
+    # im2col with zero rows at both ends, columns (tap, channel), against conv1d with padding 1 and stride 2
+    x = torch.randn(10, 32)
+    pad = torch.cat([torch.zeros(1, 32), x, torch.zeros(1, 32)])
+    rows = torch.stack([torch.cat([pad[2 * t + k] for k in range(3)]) for t in range(5)])
+    wg = w["conv2_w"].permute(0, 2, 1).reshape(32, -1)
+    want = F.conv1d(x.T[None], w["conv2_w"], None, stride=2, padding=1)[0].T
+    assert torch.allclose(rows @ wg.T, want, atol=1e-5)
+
+
+def test_chat_with_an_audio_clip_and_an_image_in_one_request():
+    import base64
+    import io
+    import wave
+
+    import numpy as np
+    import pytest
+    pytest.importorskip("fastapi")
+    from fastapi.testclient import TestClient
+
+    from cuteafd_b200.engine.kv import PagePool
+    from cuteafd_b200.parallel.health import Health
+    from cuteafd_b200.ref.audio import AudioSpec
+    from cuteafd_b200.ref.vision import VisionSpec
+    from cuteafd_b200.serving.api import ServingLoop, build_app
+    from cuteafd_b200.serving.runner import FakeRunner
+    from cuteafd_b200.serving.scheduler import Scheduler
+    from cuteafd_b200.serving.vision import VisionFrontEnd
+
+    class FakeAudio:
+        device = None
+        spec = AudioSpec(out_hidden=8, n_mels=16)
+        encodes = 0
+
+        def encode(self, clips):
+            self.encodes += 1
+            return [torch.ones(c.shape[0] // 4, 8, dtype=torch.bfloat16) for c in clips]
+
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as wf:
+        wf.setnchannels(1); wf.setsampwidth(2); wf.setframerate(8000)          # resampled to 16 kHz by the loader
+        wf.writeframes((np.sin(np.arange(8000) * 0.05) * 12000).astype("<i2").tobytes())
+    tower, audio = _FakeTower(VisionSpec(patch=16, merge=2, out_hidden=8, max_tokens=64)), FakeAudio()
+    runner = FakeRunner(vocab=96)
+    runner.next_token = lambda prefix: 32 + (sum(prefix[-3:]) % 60)
+    seen = []
+    real_run = runner.run
+    runner.run = lambda rows: (seen.extend((r.state.req.embeds, list(r.tokens)) for r in rows), real_run(rows))[1]
+    loop = ServingLoop(Scheduler(runner, PagePool(256)), Health()).start()
+    try:
+        c = TestClient(build_app(loop, vision=VisionFrontEnd(tower, pad_id=90, start_id=91, end_id=92, audio_tower=audio, audio_pad_id=93,
+                                                             audio_start_id=94, audio_end_id=95)))
+        url = "data:image/png;base64," + base64.b64encode(_png(64, 64)).decode()
+        r = c.post("/v1/chat/completions", json={"model": "m", "max_tokens": 3, "messages": [{"role": "user", "content": [
+            {"type": "input_audio", "input_audio": {"data": base64.b64encode(buf.getvalue()).decode(), "format": "wav"}},
+            {"type": "text", "text": " and "}, {"type": "image_url", "image_url": {"url": url}}]}]})
+        assert r.status_code == 200, r.text
+        emb, toks = next(s for s in seen if s[0] is not None)
+        assert toks.count(93) == 25 and toks.count(90) == 4                     # 1 s of audio = 100 frames = 25 tokens; 64 x 64 px = 4 tokens
+        assert toks.index(94) < toks.index(93) < toks.index(95) < toks.index(91) < toks.index(90)
+        rows = emb["rows"].float()
+        assert rows.shape == (29, 8) and bool((rows[:25] == 1).all()) and bool((rows[25:] == 0).all())      # prompt order: audio rows, then image rows
+        assert [toks[p] for p in emb["positions"]] == [93] * 25 + [90] * 4
+    finally:
+        loop.stop()
