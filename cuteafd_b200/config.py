@@ -114,12 +114,26 @@ class ModelSpec:
     # coefficients (collapse weights, spread weights and a Sinkhorn-normalised 4 x 4 stream mix from 24 projections of the row)
     hyper_streams: int = 0
     hyper_sinkhorn_iters: int = 20
+    # N-gram memory (the V4.1 line's "engram"): decoder layers whose input takes a gated projection of hashed table rows addressed by the
+    # 2- to 4-grams ending at the token; the tables have engram_prime_floor-sized heads (24 consecutive primes above it per layer)
+    engram_layers: tuple = ()
+    engram_row_dim: int = 256
+    engram_prime_floor: int = 500
+    engram_vocab: int = 0           # compressed vocabulary of the addressing (0: the model's vocabulary, identity map)
     init_std: float = 0.02
     tie_embeddings: bool = False
     max_context: int = 1 << 20
 
     def replace(self, **kw) -> "ModelSpec":
         return dataclasses.replace(self, **kw)
+
+    def engram_spec(self):
+        """Addressing / shape of the n-gram memory, or None for models without one."""
+        if not self.engram_layers:
+            return None
+        from .ref.engram import EngramSpec
+        return EngramSpec(layers=tuple(self.engram_layers), vocab=self.engram_vocab or self.vocab, pad_id=0, row_dim=self.engram_row_dim,
+                          prime_floor=self.engram_prime_floor, streams=1, hidden=self.hidden)
 
     # ---- per-layer attention program ---------------------------------------
     def layer_is_full(self, layer: int) -> bool:
@@ -380,6 +394,8 @@ def spec_to_json(spec: ModelSpec) -> dict:
 
 def spec_from_json(d: dict) -> ModelSpec:
     d = dict(d)
+    if "engram_layers" in d:
+        d["engram_layers"] = tuple(d["engram_layers"])
     return ModelSpec(attn=AttentionSpec(**d.pop("attn")), moe=MoESpec(**d.pop("moe")), quant=QuantSpec(**d.pop("quant")), **d)
 
 

@@ -164,6 +164,9 @@ class Engine:
             self.dense_kind = weights.layers[0].wo.kind
         else:
             self.dense_kind = weights.layers[0].wo.kind
+        self.engram = getattr(weights, "engram", None)          # n-gram memory (specs with engram_layers)
+        if self.engram is not None and spec.hyper_streams:
+            raise NotImplementedError("the n-gram memory is wired for single-stream stacks (its module gates any number of streams)")
         first_moe = next((l for l in weights.layers if l.w_gate is not None), None)
         self.expert_kind = first_moe.w_gate.kind if first_moe is not None else KIND_BF16
         self.expert_range = expert_range or (0, spec.moe.n_experts)
@@ -249,10 +252,20 @@ class Engine:
         self.graphs.clear()     # views moved: captured graphs are stale
         self.census.invalidate()
 
-    def set_inputs(self, tokens, positions, slot_map, logit_rows, kv_len, q_start, q_len, page_table_rows, state_slots=None):
+    def set_inputs(self, tokens, positions, slot_map, logit_rows, kv_len, q_start, q_len, page_table_rows, state_slots=None, engram_ctx=None):
         """Fill the pinned host block and enqueue ONE host-to-device copy.  `state_slots`: per sequence of the step, the slot of its
-        recurrent state (hybrid stacks with linear-attention layers); default: the sequence's index in the step."""
+        recurrent state (hybrid stacks with linear-attention layers); default: the sequence's index in the step.  `engram_ctx`: per
+        sequence, the (up to three) tokens before its first row of this step - models with an n-gram memory address its tables by the
+        last four tokens, and the addresses of all rows travel in a second copy."""
         T, S = len(tokens), len(kv_len)
+        extra = 0
+        if self.engram is not None:
+            if engram_ctx is None or len(engram_ctx) != S:
+                raise ValueError("this model has an n-gram memory: set_inputs needs engram_ctx (the tokens before each sequence's rows)")
+            import numpy as np
+            from ..ref.engram import context_hashes
+            parts = [context_hashes(self.engram.addr, list(engram_ctx[s]), list(tokens[q_start[s]:q_start[s] + q_len[s]])) for s in range(S)]
+            extra = self.engram.set_hashes(np.concatenate(parts, axis=1))
         self._ensure_meta(T)
         mh = self.mh
         mh["tokens"][:T] = torch.as_tensor(tokens, dtype=torch.int32)
@@ -267,7 +280,7 @@ class Engine:
         for s, row in enumerate(page_table_rows):
             mh["page_table"][s, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
         self.meta_dev.copy_(self.meta_host, non_blocking=True)
-        return self.meta_host.numel() * 4
+        return self.meta_host.numel() * 4 + extra
 
     def set_input_embeds(self, rows, vals: torch.Tensor | None):
         """Rows of the NEXT eager step whose token embedding is replaced by `vals` (bf16 [n, hidden] on this device): the image rows
@@ -363,7 +376,7 @@ class Engine:
         if self.spec.hyper_streams:       # the block's output stays apart: the next boundary spreads it over the streams
             ops.moe_combine(y, rows, wts, shared, None, L.sub, T, k, wait=wait)
             return
-        if nxt is None:
+        if nxt is None or getattr(self, "_next_engram", False):      # an engram layer first adds its memory to the un-normalised rows
             ops.moe_combine(y, rows, wts, shared, L.x, L.x, T, k, wait=wait)
             return
         fp4 = L.xq.kind in FUSED_QUANT_KINDS and self.spec.hidden % 256 == 0      # the quantised operand rides in the same launch
@@ -631,6 +644,11 @@ class Engine:
         for li in range(spec.n_layers):
             lw = self.weights.layer(li)
             self._next_lw = self.weights.layer(li + 1) if li + 1 < spec.n_layers else None
+            self._next_engram = self.engram is not None and (li + 1) in spec.engram_layers
+            if self.engram is not None and li in spec.engram_layers:
+                if self._pre_normed:
+                    raise RuntimeError("engram layer behind a fused combine + norm: its input rows were normalised before the memory could be added")
+                self.launches_per_step += self.engram.apply(spec.engram_layers.index(li), L.x, T)
             with (self.layer_clock.span(f"layer{li}") if timed else contextlib.nullcontext()), (nvtx(f"layer{li}") if self._nvtx else contextlib.nullcontext()):
                 self._attention_layer(li, lw, L, sh)
                 if self._l2_prefetch and self._next_lw is not None and getattr(self._next_lw, "wqkv", None) is not None:
@@ -800,3 +818,5 @@ class Engine:
         if word:
             from ..ops.native import decode_status
             raise RuntimeError(f"device status: {decode_status(word)}")
+        if self.engram is not None:
+            self.engram.check_status()

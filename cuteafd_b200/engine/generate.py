@@ -39,6 +39,7 @@ class BatchGenerator:
         """Runs every prompt through the model (chunked), returns the first generated token of each."""
         eng = self.eng
         self.seqs = [SeqKV() for _ in prompts]
+        self.hist = [list(p) for p in prompts]           # tokens whose rows are in the cache (the n-gram memory looks three back)
         for s, p in zip(self.seqs, prompts):
             s.ensure(self.pool, len(p) + 1)
         eng.reset_state_slots(range(len(prompts)))       # hybrid stacks: sequence i owns recurrent-state slot i
@@ -70,7 +71,8 @@ class BatchGenerator:
                     finals.append((i, len(logit_rows)))
                     logit_rows.append(len(tokens) - 1)
             self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, self._page_rows(seqs),
-                                             state_slots=[i for i, _, _ in batch])
+                                             state_slots=[i for i, _, _ in batch],
+                                             **({"engram_ctx": [prompts[i][max(0, off - 3):off] for i, off, _ in batch]} if getattr(eng, "engram", None) is not None else {}))
             sh = StepShape(T=len(tokens), n_seq=len(batch), max_q_len=max(q_len), n_logits=len(logit_rows), attn_splits=1)
             lane = eng.run(sh, use_graph=use_graph)
             if finals:
@@ -93,7 +95,8 @@ class BatchGenerator:
             slots.append(s.slot(s.length))
             kv_len.append(s.length + 1)
         self.h2d_bytes += eng.set_inputs(tokens, positions, slots, list(range(n)), kv_len, list(range(n)), [1] * n,
-                                         self._page_rows(self.seqs))
+                                         self._page_rows(self.seqs),
+                                         **({"engram_ctx": [h[-3:] for h in self.hist]} if getattr(eng, "engram", None) is not None else {}))
         splits = eng.attn_splits_for(n, 1, max(kv_len))
         return StepShape(T=n, n_seq=n, max_q_len=1, n_logits=n, attn_splits=splits, uniform=True)
 
@@ -101,6 +104,9 @@ class BatchGenerator:
         toks = self._readback(lane, len(self.seqs))
         for s in self.seqs:
             s.length += 1
+        if getattr(self, "hist", None):
+            for h, t in zip(self.hist, self.last):
+                h.append(t)
         self.last = toks
         return toks
 
@@ -125,7 +131,9 @@ class BatchGenerator:
             q_len.append(len(p))
             logit_rows.append(len(tokens) - 1)
         self._prompt_lens = [len(p) for p in prompts]
-        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, self._page_rows(self.seqs))
+        self.hist = [list(p) for p in prompts]
+        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, self._page_rows(self.seqs),
+                                         **({"engram_ctx": [[] for _ in prompts]} if getattr(eng, "engram", None) is not None else {}))
         return StepShape(T=len(tokens), n_seq=len(prompts), max_q_len=max(q_len), n_logits=len(logit_rows), attn_splits=1)
 
     def commit_prefill_all(self, lane) -> list[int]:

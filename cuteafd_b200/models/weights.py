@@ -18,6 +18,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import os
+
 import torch
 
 from ..config import ModelSpec
@@ -31,6 +33,10 @@ def _dense_kind(spec: ModelSpec) -> str:
 def _expert_kind(spec: ModelSpec) -> str:
     return {"bf16": "bf16", "nvfp4": "nvfp4", "mxfp4": "mxfp4"}.get(spec.quant.experts, "bf16")
 
+
+# n-gram memory: rows of a step the module's buffers hold, and where the tables live ("device", or "host": pinned host memory read in place)
+ENGRAM_ROWS = int(os.environ.get("CUTEAFD_ENGRAM_ROWS", "4096"))
+ENGRAM_TABLES = os.environ.get("CUTEAFD_ENGRAM_TABLES", "device")
 
 @dataclass
 class LayerWeights:
@@ -85,6 +91,7 @@ class DeviceWeights:
     layer_map: list = field(default_factory=list)  # layer index -> index into `layers`
     mtp: list = field(default_factory=list)        # [(enorm, hnorm, eh_proj TcWeight, LayerWeights, norm)]
     act_gs: float = 1.0 / 64
+    engram: object | None = None                   # n-gram memory (`models/engram.py::EngramModule`) of specs with engram_layers
     hc_head: tuple | None = None                   # hyper-connections: (fn [4, 4H], scale [3], base [4]) of the head's collapse
 
     def layer(self, i: int) -> LayerWeights:
@@ -144,6 +151,9 @@ class DeviceWeights:
         dw.layer_map = list(range(spec.n_layers))
         if "hc_head_fn" in masters:
             dw.hc_head = tuple(f32(masters[f"hc_head_{k}"]) for k in ("fn", "scale", "base"))
+        if "engram" in masters and spec.engram_layers:
+            from .engram import EngramModule
+            dw.engram = EngramModule(spec.engram_spec(), masters["engram"], device, cap=ENGRAM_ROWS, tables=ENGRAM_TABLES)
         for mw in masters.get("mtp", []):
             dw.mtp.append((f32(mw["enorm"]), f32(mw["hnorm"]), TcWeight.from_master(mw["eh_proj"], "bf16", device),
                            layer_from(mw["layer"]), f32(mw["norm"])))
@@ -185,6 +195,9 @@ class DeviceWeights:
              "layers": [layer_to(self.layer(i)) for i in range(spec.n_layers)]}
         if self.hc_head is not None:
             m["hc_head_fn"], m["hc_head_scale"], m["hc_head_base"] = (x.cpu() for x in self.hc_head)
+        if self.engram is not None:
+            m["engram"] = {"layers": [{"table_q": l["tq"].cpu(), "table_e": l["te"].cpu(), "proj": l["proj"].dequantize()[0], "wq": l["wq"].cpu(),
+                                       "wk": l["wk"].cpu()} for l in self.engram.layers]}
         if self.mtp:
             m["mtp"] = [{"enorm": e.cpu(), "hnorm": h.cpu(), "eh_proj": p.dequantize()[0], "layer": layer_to(l), "norm": n.cpu()}
                         for e, h, p, l, n in self.mtp]
@@ -261,4 +274,8 @@ class DeviceWeights:
             S = spec.hyper_streams
             dw.hc_head = (torch.empty(S, S * h, device=device).normal_(0, 2.0 / (S * h) ** 0.5, generator=gen), torch.full((3,), 0.5, device=device),
                           torch.empty(S, device=device).normal_(0, 0.5, generator=gen))
+        if spec.engram_layers and with_attention:
+            from ..ref.engram import init_engram_weights
+            from .engram import EngramModule
+            dw.engram = EngramModule(spec.engram_spec(), init_engram_weights(spec.engram_spec(), seed + 17), device, cap=ENGRAM_ROWS, tables=ENGRAM_TABLES)
         return dw

@@ -62,6 +62,8 @@ _PROTOS = {
     "cuteafd_short_conv4_peek": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "cuteafd_mhc_boundary": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P],
     "cuteafd_vision_rgb_patches": [P, P, P, I, I, I, I, I, P],
+    "cuteafd_engram_gather": [P, P, P, P, P, I, I, L, P, P],
+    "cuteafd_engram_gate": [P, P, I, P, P, P, I, I, I, P],
     "cuteafd_audio_im2col3": [P, P, I, I, I, P],
     "cuteafd_vision_add_norm": [P, P, I, P, P, P, P, I, I, F, I, P],
     "cuteafd_vision_qkv_rope_store": [P, P, P, P, P, P, P, P, I, I, I, F, P, P],

@@ -166,6 +166,8 @@ class AttnRankEngine(Engine):
         self.tp, self.tp_rank = dep.tp, dep.attn_ranks.index(rank) % dep.tp
         if spec.hyper_streams:
             raise NotImplementedError("hyper-connections run on the single-GPU engine (the lanes carry one residual stream)")
+        if spec.engram_layers:
+            raise NotImplementedError("models with an n-gram memory run on the single-GPU engines (the step inputs of the lanes carry no table addresses)")
         if self.tp > 1 and spec.attn.linear_every:
             raise NotImplementedError("hybrid stacks with linear-attention layers run with attention TP 1 (data-parallel attention ranks)")
         self.group = dep.group_of(rank)

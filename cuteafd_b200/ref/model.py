@@ -97,6 +97,9 @@ def init_weights(spec: ModelSpec, seed: int = 0) -> dict:
         w["hc_head_fn"] = _randn(gen, S, S * spec.hidden, std=2.0 / math.sqrt(S * spec.hidden))
         w["hc_head_scale"] = torch.tensor([0.5, 0.5, 0.5])
         w["hc_head_base"] = _randn(gen, S, std=0.5)
+    if spec.engram_layers:
+        from .engram import init_engram_weights
+        w["engram"] = init_engram_weights(spec.engram_spec(), seed + 17)
     if spec.mtp_layers:
         w["mtp"] = [{"enorm": torch.ones(spec.hidden), "hnorm": torch.ones(spec.hidden),
                      "eh_proj": _randn(gen, spec.hidden, 2 * spec.hidden, std=spec.init_std),
@@ -109,6 +112,7 @@ def init_weights(spec: ModelSpec, seed: int = 0) -> dict:
 class RefCache:
     """Per-sequence KV history: one (k, v, positions) triple per layer ("mtp{i}" for draft layers)."""
     layers: dict = field(default_factory=dict)
+    tokens: list = field(default_factory=list)      # token ids by position (the n-gram memory addresses by the last four)
 
     def append(self, key, k, v, pos):
         if key in self.layers:
@@ -124,9 +128,10 @@ class RefCache:
                 raise NotImplementedError("rows of a linear-attention layer cannot be dropped: the recurrent state has absorbed them")
             keep = p < length
             self.layers[key] = (k[keep], v[keep], p[keep])
+        del self.tokens[length:]
 
     def clone(self) -> "RefCache":
-        return RefCache({k: tuple(t.clone() for t in v) for k, v in self.layers.items()})
+        return RefCache({k: tuple(t.clone() for t in v) for k, v in self.layers.items()}, list(self.tokens))
 
 
 class RefModel:
@@ -245,7 +250,17 @@ class RefModel:
         x = self.w["embed"][tokens.long()].float()
         if self.spec.hyper_streams:
             return self._hyper_hidden_states(x, pos, cache, routes_out)
+        eng_hashes = None
+        if self.spec.engram_layers:
+            from .engram import EngramAddressing, context_hashes, engram_apply
+            espec = self.spec.engram_spec()
+            del cache.tokens[start:]
+            eng_hashes = context_hashes(EngramAddressing(espec), cache.tokens, tokens.tolist())
+            cache.tokens += tokens.tolist()
         for i, lw in enumerate(self.w["layers"]):
+            if eng_hashes is not None and i in self.spec.engram_layers:
+                e = self.spec.engram_layers.index(i)
+                x = engram_apply(espec, self.w["engram"]["layers"][e], x.bfloat16().float()[:, None, :], eng_hashes[e])[:, 0]
             x = self.attention_block(lw, x, pos, cache, i)
             x = self.ffn_block(lw, x, routes_out)
         return x

@@ -149,8 +149,10 @@ class EngineRunner:
             kv_len.append(r.start_pos + n)
             q_len.append(n)
             pages.append(seq.pages)
-        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages,
-                                         **({"state_slots": self._slots_of(rows)} if self._recurrent else {}))
+        extra = {"state_slots": self._slots_of(rows)} if self._recurrent else {}
+        if getattr(eng, "engram", None) is not None:          # n-gram memory: the three tokens before each row run
+            extra["engram_ctx"] = [r.state.tokens[max(0, r.start_pos - 3):r.start_pos] for r in rows]
+        self.h2d_bytes += eng.set_inputs(tokens, positions, slots, logit_rows, kv_len, q_start, q_len, pages, **extra)
         max_q = max(q_len)
         decode_like = max_q <= 8
         # regular decode / verify rounds (every sequence the same number of rows, logits for every row or none) may be cut into
