@@ -634,9 +634,13 @@ class Engine:
         self._ensure_attn_scratch(sh)
         self.launches_per_step = 0
         self._pre_normed = False
-        ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
-        self.launches_per_step += 1
-        self._apply_input_embeds(L.x, T)
+        stage = getattr(self, "stage", None)        # a layer-range split: this engine holds a slice of the stack (parallel/pipeline.py)
+        if stage is None or stage.first:
+            ops.embed_gather(self.md["tokens"][:T], self.weights.embed, L.x, self.status)
+            self.launches_per_step += 1
+            self._apply_input_embeds(L.x, T)
+        else:
+            self.launches_per_step += stage.receive(L.x, T)         # the residual rows arrive from the stage before
         self._hc_pending = "init" if spec.hyper_streams else None
         import contextlib
         from ..utils.trace import nvtx
@@ -654,6 +658,9 @@ class Engine:
                 if self._l2_prefetch and self._next_lw is not None and getattr(self._next_lw, "wqkv", None) is not None:
                     ops.l2_prefetch(self._next_lw.wqkv.data)       # the next layer's first weights ride into L2 under this layer's experts
                 self._moe_layer(lw, L, T)
+        if stage is not None and not stage.last:
+            self.launches_per_step += stage.send(L.x, T)            # hop to the next stage; the head runs on the last one
+            return L
         if spec.hyper_streams:      # close the last block, collapse the streams for the head: hidden rows -> L.x, normalised -> L.xn
             self._hc_boundary(L, T, self.weights.hc_head, self.weights.final_norm, head=True)
         if sh.n_logits:
