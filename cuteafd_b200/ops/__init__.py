@@ -659,3 +659,13 @@ def short_conv4(x, w, carry, slot_of_seq, q_start, q_len, y, *, status=None):
     call("cuteafd_short_conv4", ptr(x), ptr(w), ptr(carry), ptr(slot_of_seq), ptr(q_start), ptr(q_len), ptr(y), slot_of_seq.numel(), y.shape[1],
          x.stride(0), carry.shape[0], ptr(status), stream())
     return y
+
+
+def compress_pool(kv, scores, state, state_slot, q_start, q_len, pos0, out_start, norm_w, out, *, n_seq: int, max_blocks: int, ratio: int,
+                  eps: float = 1e-6):
+    """Softmax pooling of KV candidate rows into one compressed cache row per `ratio` positions (see csrc/compressor.cu): fp32
+    kv / scores [T, D], per-sequence open-block state [slots, 3, D], int32 step descriptors per sequence; rows of the blocks completed
+    in this step land in `out` (bf16 [n, D]) from `out_start[s]` on.  `max_blocks`: the most blocks any sequence touches in the step."""
+    call("cuteafd_compress_pool", ptr(kv), ptr(scores), ptr(state), ptr(state_slot), ptr(q_start), ptr(q_len), ptr(pos0), ptr(out_start),
+         ptr(norm_w), ptr(out), n_seq, max_blocks, kv.shape[1], ratio, eps, stream())
+    return out

@@ -62,6 +62,7 @@ _PROTOS = {
     "cuteafd_short_conv4_peek": [P, P, P, P, P, P, P, I, I, I, I, P, P],
     "cuteafd_mhc_boundary": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P],
     "cuteafd_vision_rgb_patches": [P, P, P, I, I, I, I, I, P],
+    "cuteafd_compress_pool": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, F, P],
     "cuteafd_engram_gather": [P, P, P, P, P, I, I, L, P, P],
     "cuteafd_engram_gate": [P, P, I, P, P, P, I, I, I, P],
     "cuteafd_audio_im2col3": [P, P, I, I, I, P],

@@ -240,3 +240,27 @@ def mhc_mixes(res: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: to
 def mhc_close(res: torch.Tensor, sub: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
     """res'[t, d] = post[t, d] * sub[t] + sum_s comb[t, s, d] * res[t, s]."""
     return post[:, :, None] * sub[:, None, :].float() + torch.einsum("tsd,tsh->tdh", comb, res.float())
+
+
+def compress_pool(kv: torch.Tensor, scores: torch.Tensor, ratio: int, norm_w: torch.Tensor, eps: float, pos0: int = 0, state=None):
+    """Learned KV compressor (CSA / HCA / CED caches): blocks of `ratio` consecutive positions pooled per channel with a softmax over
+    their scores, rounded to bf16, RMS-normalised and scaled.  kv, scores: fp32 [T, D] rows of positions pos0 .. pos0 + T - 1;
+    `state` = (max, sum, weighted sum) [3, D] of a block an earlier call left open.  Returns (rows of the blocks completed here [n, D],
+    state of the block left open or None).  Reference: native/families/deepseek_v41/cuda/v41_compressor.cu (`pool_kernel`)."""
+    T, D = kv.shape
+    mx, l, acc = (state[0].clone(), state[1].clone(), state[2].clone()) if state is not None else (
+        torch.full((D,), float("-inf")), torch.zeros(D), torch.zeros(D))
+    if state is None and pos0 % ratio:
+        raise ValueError("a step that starts inside a block needs the block's state")
+    out = []
+    for t in range(T):
+        nm = torch.maximum(mx, scores[t])
+        r = torch.where(torch.isinf(mx), torch.zeros_like(mx), torch.exp(mx - nm))
+        e = torch.exp(scores[t] - nm)
+        l, acc, mx = l * r + e, acc * r + e * kv[t], nm
+        if (pos0 + t + 1) % ratio == 0:
+            pooled = (acc / l).to(torch.bfloat16).float()
+            out.append(pooled * torch.rsqrt(pooled.pow(2).mean() + eps) * norm_w)
+            mx, l, acc = torch.full((D,), float("-inf")), torch.zeros(D), torch.zeros(D)
+    open_block = (pos0 + T) % ratio != 0
+    return (torch.stack(out) if out else torch.zeros(0, D)), (torch.stack([mx, l, acc]) if open_block else None)

@@ -850,3 +850,44 @@ def test_cluster_capacity_queries():
     assert caps[0] == sm and all(a >= b for a, b in zip(caps, caps[1:])) and all(1 <= c <= sm // (i + 1) for i, c in enumerate(caps))
     f8 = [ops.fp8_cluster_capacity(16, s, 7168) for s in range(1, 9)]
     assert all(a >= b for a, b in zip(f8, f8[1:])) and all(1 <= c <= 2 * sm // (i + 1) for i, c in enumerate(f8))
+
+
+@pytest.mark.parametrize("ratio,D", [(4, 512), (2, 64), (128, 128)])
+def test_compress_pool_matches_oracle_across_steps(ratio, D):
+    """KV compressor: two sequences fed in uneven steps (a prefill chunk, then chunks that start and stop inside blocks, then single
+    tokens); the rows completed by each step and the carried open-block state must match the oracle's one-shot pooling."""
+    from cuteafd_b200.ref.ops import compress_pool as ref_pool
+    g = torch.Generator().manual_seed(ratio)
+    lens = [3 * ratio + 5, 2 * ratio + 1]
+    kv = [torch.randn(n, D, generator=g) for n in lens]
+    sc = [torch.randn(n, D, generator=g) * 2 for n in lens]
+    w = 1 + 0.1 * torch.randn(D, generator=g)
+    want = [ref_pool(kv[i], sc[i], ratio, w, 1e-6)[0] for i in range(2)]
+    state = torch.zeros(4, 3, D, dtype=torch.float32, device=DEV)
+    slots = torch.tensor([2, 0], dtype=torch.int32, device=DEV)
+    wd = w.to(DEV)
+    done, got = [0, 0], [[], []]
+    plan = [[ratio + 2, 1], [ratio - 1, ratio], [1, 0], [lens[0] - 2 * ratio - 2, lens[1] - ratio - 1]]
+    for step in plan:
+        rows_kv = torch.cat([kv[i][done[i]:done[i] + step[i]] for i in range(2)]).to(DEV)
+        rows_sc = torch.cat([sc[i][done[i]:done[i] + step[i]] for i in range(2)]).to(DEV)
+        q_start = [0, step[0]]
+        n_out = [(done[i] + step[i]) // ratio - done[i] // ratio for i in range(2)]
+        blocks = [((done[i] + step[i] - 1) // ratio - done[i] // ratio + 1) if step[i] else 0 for i in range(2)]
+        out = torch.zeros(max(1, sum(n_out)), D, dtype=torch.bfloat16, device=DEV)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        ops.compress_pool(rows_kv, rows_sc, state, slots, i32(q_start), i32(step), i32(done), i32([0, n_out[0]]), wd, out, n_seq=2,
+                          max_blocks=max(blocks), ratio=ratio)
+        torch.cuda.synchronize()
+        o = 0
+        for i in range(2):
+            got[i].append(out[o:o + n_out[i]].float().cpu())
+            o += n_out[i]
+            done[i] += step[i]
+    assert done == lens
+    for i in range(2):
+        rows = torch.cat(got[i])
+        assert rows.shape == want[i].shape
+        assert float((rows - want[i]).abs().max()) < 0.03 * float(want[i].abs().max()), f"sequence {i}"
+    _, st = ref_pool(kv[0], sc[0], ratio, w, 1e-6)
+    assert torch.allclose(state[2].cpu()[1:], st[1:], rtol=2e-3, atol=2e-3)          # running sum and weighted sum of the open block

@@ -236,3 +236,26 @@ def test_hybrid_layer_pattern_facts_and_config_detection():
     w2 = {**w, "layers": [{k: v for k, v in l.items() if k != "sink"} for l in w["layers"]]}
     b, _ = RefModel(full, w2).forward(toks, 0, RefCache())
     assert not torch.allclose(a[-1], b[-1], atol=1e-4)
+
+
+def test_compressor_pooling_is_chunk_invariant_and_softmax_weighted():
+    import torch
+
+    from cuteafd_b200.ref.ops import compress_pool
+    g = torch.Generator().manual_seed(0)
+    kv, sc, w = torch.randn(23, 64, generator=g), torch.randn(23, 64, generator=g) * 2, 1 + 0.1 * torch.randn(64, generator=g)
+    rows, state = compress_pool(kv, sc, 4, w, 1e-6)
+    assert rows.shape == (5, 64) and state is not None                      # 23 = 5 blocks of 4 + 3 open positions
+    # block 1, channel 7, by hand
+    p = torch.softmax(sc[4:8, 7], 0)
+    pooled = (p * kv[4:8, 7]).sum()
+    full = torch.stack([(torch.softmax(sc[4:8, d], 0) * kv[4:8, d]).sum() for d in range(64)]).bfloat16().float()
+    assert abs(float(full[7]) - float(pooled.bfloat16())) < 1e-6
+    assert torch.allclose(rows[1], full * torch.rsqrt(full.pow(2).mean() + 1e-6) * w, atol=1e-5)
+    # the same rows when the positions arrive as 6 + 1 + 1 + 15
+    got, st, pos = [], None, 0
+    for n in (6, 1, 1, 15):
+        r, st = compress_pool(kv[pos:pos + n], sc[pos:pos + n], 4, w, 1e-6, pos0=pos, state=st)
+        got.append(r)
+        pos += n
+    assert torch.allclose(torch.cat(got), rows, atol=1e-5) and torch.allclose(st, state, atol=1e-5)
