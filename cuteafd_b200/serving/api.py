@@ -720,5 +720,6 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
     if gateway:
         from .gateway_extras import install_gateway_extras
         install_gateway_extras(app, tok=tok, tmpl=tmpl, auth=auth, start_generation=start_generation, collect=collect, loop=loop,
-                               served_name=served_name, search=search, record_path=record_path)
+                               served_name=served_name, search=search, record_path=record_path, build_prompt=build_prompt,
+                               audio=vision is not None and getattr(vision, "audio_tower", None) is not None)
     return app

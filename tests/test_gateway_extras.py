@@ -102,3 +102,59 @@ def test_record_and_replay(tmp_path):
         assert rep["requests"] == 3 and rep["matched"] == 0 and len(rep["mismatches"]) == 3
     finally:
         other.stop()
+
+
+def test_realtime_websocket_takes_microphone_audio_when_an_audio_tower_is_loaded():
+    """`input_audio_buffer.append` / `.commit` turn PCM from the socket into a user item; the response's prompt carries the audio
+    placeholders and the tower's rows, exactly like an `input_audio` part of the chat surface."""
+    import base64
+
+    import numpy as np
+    import torch
+
+    from cuteafd_b200.ref.audio import AudioSpec
+    from cuteafd_b200.serving.vision import VisionFrontEnd
+
+    class FakeAudio:
+        device = None
+        spec = AudioSpec(out_hidden=8, n_mels=16)
+        encodes = 0
+
+        def encode(self, clips):
+            self.encodes += 1
+            return [torch.ones(c.shape[0] // 4, 8, dtype=torch.bfloat16) for c in clips]
+
+    loop = _loop(b"I heard you.")
+    seen = []
+    runner = loop.sched.runner
+    real_run = runner.run
+    runner.run = lambda rows: (seen.extend((r.state.req.embeds, list(r.tokens)) for r in rows), real_run(rows))[1]
+    audio = FakeAudio()
+    try:
+        c = TestClient(build_app(loop, vision=VisionFrontEnd(None, audio_tower=audio, audio_pad_id=250, audio_start_id=251, audio_end_id=252)))
+        pcm = (np.sin(np.arange(24000) * 0.03) * 9000).astype("<i2").tobytes()              # one second at the socket's 24 kHz
+        with c.websocket_connect("/v1/realtime") as ws:
+            assert json.loads(ws.receive_text())["type"] == "session.created"
+            for i in range(0, len(pcm), 16000):
+                ws.send_text(json.dumps({"type": "input_audio_buffer.append", "audio": base64.b64encode(pcm[i:i + 16000]).decode()}))
+            ws.send_text(json.dumps({"type": "input_audio_buffer.commit"}))
+            assert json.loads(ws.receive_text())["type"] == "input_audio_buffer.committed"
+            created = json.loads(ws.receive_text())
+            assert created["type"] == "conversation.item.created" and created["item"]["content"][0]["type"] == "input_audio"
+            ws.send_text(json.dumps({"type": "input_audio_buffer.commit"}))                  # nothing buffered any more
+            assert json.loads(ws.receive_text())["type"] == "error"
+            ws.send_text(json.dumps({"type": "response.create"}))
+            text, done = "", None
+            while done is None:
+                ev = json.loads(ws.receive_text())
+                if ev["type"] == "response.text.delta":
+                    text += ev["delta"]
+                if ev["type"] == "response.done":
+                    done = ev
+            assert text == "I heard you." and done["response"]["status"] == "completed"
+        assert audio.encodes == 1
+        emb, toks = next(s for s in seen if s[0] is not None)
+        assert toks.count(250) == 25 and emb["rows"].shape == (25, 8)                          # 1 s -> 100 frames at 16 kHz -> 25 tokens
+        assert [toks[p] for p in emb["positions"]] == [250] * 25
+    finally:
+        loop.stop()
