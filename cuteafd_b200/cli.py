@@ -117,9 +117,17 @@ def build_serving(a):
     elif a.draft == "mtp" and not recurrent:
         from .serving.mtp_drafter import MtpDrafter
         drafter = MtpDrafter(runner)                           # the model's own MTP module (needs MTP weights)
+    policy = None
+    if getattr(a, "draft_policy", "simple") == "online" and drafter is not None:
+        from .serving.draft_policy import OnlineDraftPolicy
+        m = spec.moe
+        # bytes of one routed expert (gate + up + down) in its stored format, as the price unit of the traffic forecast
+        per_weight = {"bf16": 2.0, "fp8_block128": 1.0}.get(spec.quant.experts, 0.5625)
+        policy = OnlineDraftPolicy(max(a.draft_limit, 1), n_experts=m.n_experts, top_k=m.top_k,
+                                   slice_mb=3 * spec.hidden * m.intermediate * per_weight / 2 ** 20)
     sched = Scheduler(runner, pool, max_seqs=a.max_sequences, prefill_chunk=a.prefill_batch_tokens, decode_share=a.decode_share,
                       prefix=prefix, drafter=drafter, max_draft=a.draft_limit, queue_limit=getattr(a, "http_queue", 64),
-                      queue_wait_s=getattr(a, "queue_wait_s", 0) or None)
+                      queue_wait_s=getattr(a, "queue_wait_s", 0) or None, policy=policy)
     return spec, sched
 
 
@@ -465,6 +473,8 @@ def main(argv=None) -> int:
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.add_argument("--n-micro", type=int, default=0, help="multi-GPU: micro-batches the attention ranks keep in flight (0 = the layout's default)")
     p.add_argument("--vision", default="auto", help="auto (tower of the snapshot, if it has one) | off | random[:DEPTH]")
+    p.add_argument("--draft-policy", default="simple", choices=["simple", "online"],
+                   help="simple: fixed width with an acceptance cut-off; online: lengths of all requests chosen jointly from fitted round costs")
     p.add_argument("--audio", default="off", help="off | random[:DEPTH] (an audio encoder of the Whisper shape with random weights; `input_audio` parts accepted)")
     p.add_argument("--vision-max-patches", type=int, default=16384, help="patches of all images of one request")
     p.add_argument("--vision-max-images", type=int, default=8)

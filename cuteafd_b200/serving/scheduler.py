@@ -226,6 +226,11 @@ class Scheduler:
     def _decode_round(self, states: list[SeqState]):
         rows, budget = [], min(VERIFY_ROWS, self.runner.max_rows)
         plan = []
+        plan_round = getattr(self.policy, "plan_round", None)      # policies that choose all requests' lengths jointly
+        if plan_round is not None and self.drafter is not None:
+            drafting = [st for st in states if st.req.allow_drafts]
+            plan_round([st.req.rid for st in drafting], budget - (len(states) - len(drafting)),
+                       room={st.req.rid: st.req.max_tokens - len(st.out) - 1 for st in drafting})
         for st in states:
             drafts = []
             # Sampled requests verify too: every verify row is sampled with the (seed, position) generator, and a draft is accepted
@@ -265,6 +270,9 @@ class Scheduler:
                 self.spec_trace.record(st.req.rid, len(inputs) - 1, accepted - 1, step_ms)
             self.policy.observe(st.req.rid, len(inputs) - 1, accepted - 1)
             self._emit(st, emitted)
+        observe_round = getattr(self.policy, "observe_round", None)
+        if observe_round is not None:
+            observe_round(len(plan), sum(len(i) for _, i in plan), step_ms, widths={st.req.rid: len(i) - 1 for st, i in plan})
         commit = getattr(self.runner, "commit", None)
         if commit is not None:              # engines with recurrent layers absorb exactly the accepted rows now
             commit(verified)
@@ -321,6 +329,9 @@ class Scheduler:
         forget = getattr(self.runner, "forget", None)
         if forget is not None:
             forget(st)
+        forget = getattr(self.policy, "forget", None)
+        if forget is not None:
+            forget(st.req.rid)
         self.stats["finished"] += 1
         self.recent.append({"rid": st.req.rid, "prompt": len(st.req.prompt), "generated": len(st.out), "cache_hit": st.cache_hit, "reason": reason})
         self._event("finish", rid=st.req.rid, reason=reason, generated=len(st.out))
