@@ -19,7 +19,7 @@ import sys
 
 def cmd_plan(a) -> int:
     from .loader.plan import plan
-    rep = plan(a.model, world=a.gpus, layout=a.layout or a.deployment, files=a.files, pool_tokens=a.pool_tokens, gpu_gib=a.gpu_gib,
+    rep = plan(a.model, world=a.gpus, layout=a.layout or a.deployment, files=a.files, pool_tokens=a.pool_tokens, gpu_gib=a.gpu_gib, stages=a.stages,
                attn_groups=a.attn_groups)
     if a.rank >= 0 and os.path.isdir(a.model):
         from .config import default_deployment
@@ -97,6 +97,16 @@ def build_serving(a):
     else:
         weights = DeviceWeights.random(spec, dev, seed=1)      # named shapes without a snapshot: synthetic weights
     n_pages = a.pool_tokens // 64 if a.pool_tokens else 4096
+    if getattr(a, "gpu_occupancy_percent", 0):
+        # pool sized by the start-up capacity policy from the memory measured now (the weights are already resident); a pool that was
+        # asked for and does not fit is an error, only the default pool is sized down
+        from .serving.capacity import CapacityPolicy, plan_capacity
+        free, total = torch.cuda.mem_get_info(dev)
+        cap = plan_capacity(CapacityPolicy(concurrency=a.max_sequences, target_pool_tokens=a.pool_tokens, gpu_occupancy_percent=a.gpu_occupancy_percent),
+                            total_bytes=total, free_bytes=free, weight_bytes=weights.nbytes(), kv_bytes_per_token=spec.kv_bytes_per_token(),
+                            model_max_context=spec.max_context, weights_loaded=True)
+        print(f"[serve] capacity: {cap.describe()}", file=sys.stderr)
+        n_pages = cap.pool_pages
     eng = Engine(weights, n_pages=n_pages, max_seqs=a.max_sequences, max_pages_per_seq=min(n_pages, a.max_context // 64 + 1))
     pool = PagePool(n_pages)
     runner = attach_pool(EngineRunner(eng, max_rows=a.prefill_batch_tokens), pool)
@@ -445,6 +455,7 @@ def main(argv=None) -> int:
     p.add_argument("--attn-groups", type=int, default=1, help="data-parallel attention groups sharing the expert ranks")
     p.add_argument("--deployment", action="store_true", help="print the typed launch decisions of the layout as JSON")
     p.add_argument("--rank", type=int, default=-1, help="with a snapshot directory: list the files and bytes this rank of the layout reads")
+    p.add_argument("--stages", type=int, default=0, help="plan a layer-range split over this many GPUs (consecutive layer ranges, hidden-state hops)")
     p.add_argument("--json", action="store_true"); p.set_defaults(fn=cmd_plan)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
     p = sub.add_parser("run"); p.add_argument("--config", required=True); p.add_argument("--set", action="append", default=[])
@@ -473,6 +484,8 @@ def main(argv=None) -> int:
     p.add_argument("--layers", type=int, default=0, help="debug: run only the first N layers of a named shape")
     p.add_argument("--n-micro", type=int, default=0, help="multi-GPU: micro-batches the attention ranks keep in flight (0 = the layout's default)")
     p.add_argument("--vision", default="auto", help="auto (tower of the snapshot, if it has one) | off | random[:DEPTH]")
+    p.add_argument("--gpu-occupancy-percent", type=int, default=0,
+                   help="size the KV pool by the capacity policy: share of the device this server may hold (0: --pool-tokens or 4096 pages as given)")
     p.add_argument("--draft-policy", default="simple", choices=["simple", "online"],
                    help="simple: fixed width with an acceptance cut-off; online: lengths of all requests chosen jointly from fitted round costs")
     p.add_argument("--audio", default="off", help="off | random[:DEPTH] (an audio encoder of the Whisper shape with random weights; `input_audio` parts accepted)")

@@ -44,9 +44,9 @@ class Layout:
     notes: list = field(default_factory=list)
 
     def table(self) -> str:
-        lines = [f"{'rank':>4} {'role':<10} {'weights GiB':>12} {'kv GiB':>8} {'work GiB':>9} {'total GiB':>10} {'short GiB':>10}"]
+        lines = [f"{'rank':>4} {'role':<14} {'weights GiB':>12} {'kv GiB':>8} {'work GiB':>9} {'total GiB':>10} {'short GiB':>10}"]
         for r in self.ranks:
-            lines.append(f"{r.rank:>4} {r.role:<10} {r.weight_bytes / GIB:>12.1f} {r.kv_pool / GIB:>8.1f} {r.workspace / GIB:>9.1f} "
+            lines.append(f"{r.rank:>4} {r.role:<14} {r.weight_bytes / GIB:>12.1f} {r.kv_pool / GIB:>8.1f} {r.workspace / GIB:>9.1f} "
                          f"{r.total / GIB:>10.1f} {r.shortfall / GIB:>10.1f}")
         lines.append(f"pool tokens: {self.pool_tokens}   fits: {self.fits}")
         lines += [f"note: {n}" for n in self.notes]
@@ -97,4 +97,48 @@ def solve(spec: ModelSpec, world: int = 8, gpu_bytes: int = 180 * GIB, reserve_b
     if dep.ep and spec.moe.n_experts % dep.ep:
         notes.append(f"{spec.moe.n_experts} experts over {dep.ep} expert ranks: uneven ranges of "
                      f"{spec.moe.n_experts // dep.ep} or {spec.moe.n_experts // dep.ep + 1} experts")
+    return Layout(dep, plans, max(tokens, 0), min(spec.max_context, max(tokens, 0)), fits, notes)
+
+
+def solve_stages(spec: ModelSpec, n_stages: int, gpu_bytes: int = 180 * GIB, reserve_bytes: int = 6 * GIB, workspace_bytes: int = 4 * GIB,
+                 pool_tokens: int = 0, max_batch_rows: int = 4096) -> Layout:
+    """Layer-range split (`parallel/pipeline.py`): consecutive layer ranges, one per GPU; every stage holds all weights of its layers
+    and the KV cache of those layers only; the first stage adds the embedding, the last one the head.  The pool is what the tightest
+    stage can hold.  (Reference: cuteafd-loader/src/placement/residual.rs: layer ranges per device.)"""
+    from ..parallel.pipeline import stage_ranges
+    a = spec.attn
+    ranges = stage_ranges(spec.n_layers, n_stages, max(a.full_every or 1, a.linear_every or 1))
+    wb = spec.weight_bytes()
+    per_layer = (wb["attention"] + wb["shared_experts"] + wb["dense_ffn"] + wb["routed_experts"] + wb["router"]) / spec.n_layers
+    embed = wb["embed_head"] / (1 if spec.tie_embeddings else 2)
+    kv_layer = spec.kv_bytes_per_token() / spec.n_layers
+    act = max_batch_rows * spec.hidden * 2 * 24
+    plans, tokens_fit = [], []
+    for r, (lo, hi) in enumerate(ranges):
+        p = RankPlan(r, f"layers {lo}-{hi - 1}", workspace=workspace_bytes + act + (max_batch_rows * spec.vocab * 4 if r == n_stages - 1 else 0),
+                     reserve=reserve_bytes)
+        p.weights["layers"] = int(per_layer * (hi - lo))
+        if r == 0:
+            p.weights["embedding"] = int(embed)
+        if r == n_stages - 1:
+            p.weights["head"] = int(embed)
+        free = gpu_bytes - p.weight_bytes - p.workspace - p.reserve
+        if free < 0:
+            p.shortfall = -free
+        else:
+            tokens_fit.append(int(free // (kv_layer * (hi - lo))))
+        plans.append(p)
+    fits = all(p.shortfall == 0 for p in plans)
+    auto = min(tokens_fit) if len(tokens_fit) == n_stages else 0
+    tokens = auto if pool_tokens <= 0 else pool_tokens
+    notes = [f"layer-range split over {n_stages} GPUs: one step in flight, hidden rows of {spec.hidden * 2} bytes per token cross each boundary"]
+    if pool_tokens > auto:
+        fits = False
+        notes.append(f"requested pool of {pool_tokens} tokens exceeds the {auto} that fit")
+    tokens -= tokens % 64
+    for p, (lo, hi) in zip(plans, ranges):
+        p.kv_pool = int(max(tokens, 0) * kv_layer * (hi - lo))
+        if p.shortfall:
+            notes.append(f"stage {p.rank} ({p.role}) is short {p.shortfall / GIB:.1f} GiB")
+    dep = Deployment(world=n_stages, attn_ranks=tuple(range(n_stages)), expert_ranks=tuple(range(n_stages)), colocated=True, attn_groups=1)
     return Layout(dep, plans, max(tokens, 0), min(spec.max_context, max(tokens, 0)), fits, notes)

@@ -114,7 +114,7 @@ def files_for_rank(snapshot: str | Path, deployment, rank: int, n_experts: int |
 
 
 def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = False, pool_tokens: int = 0, gpu_gib: int = 180,
-         attn_groups: int = 1) -> PlanReport:
+         attn_groups: int = 1, stages: int = 0) -> PlanReport:
     """`model` is a snapshot directory (config.json + *.safetensors) or one of the named synthetic shapes."""
     problems, hints, counts, flist = [], [], Counter(), []
     p = Path(model)
@@ -160,5 +160,13 @@ def plan(model: str, *, world: int = 8, layout: bool = False, files: bool = Fals
             rep.layout.notes.append(f"{attn_groups} data-parallel attention groups: the pool is per group "
                                     f"({attn_groups * rep.layout.pool_tokens} tokens in total)")
         if not rep.layout.fits:
+            rep.supported = False
+    if stages and spec is not None:         # a layer-range split instead of the attention / expert layout
+        try:
+            rep.layout = placement.solve_stages(spec, stages, gpu_bytes=gpu_gib * placement.GIB, pool_tokens=pool_tokens)
+            if not rep.layout.fits:
+                rep.supported = False
+        except (ValueError, NotImplementedError) as e:
+            rep.problems.append(f"layer-range split: {e}")
             rep.supported = False
     return rep
