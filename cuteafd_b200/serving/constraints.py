@@ -215,6 +215,48 @@ def _int_bounds(schema: dict):
     return lo, hi
 
 
+def _num_bounds(schema: dict):
+    """(low, low is exclusive, high, high is exclusive) of a `number` schema, None for an open side."""
+    lo = hi = None
+    lo_x = hi_x = False
+    for key, excl in (("minimum", False), ("exclusiveMinimum", True)):
+        v = schema.get(key)
+        if isinstance(v, (int, float)) and not isinstance(v, bool) and (lo is None or v > lo or (v == lo and excl)):
+            lo, lo_x = float(v), excl
+    for key, excl in (("maximum", False), ("exclusiveMaximum", True)):
+        v = schema.get(key)
+        if isinstance(v, (int, float)) and not isinstance(v, bool) and (hi is None or v < hi or (v == hi and excl)):
+            hi, hi_x = float(v), excl
+    return lo, lo_x, hi, hi_x
+
+
+def _num_in(v: float, b) -> bool:
+    lo, lo_x, hi, hi_x = b
+    return not (lo is not None and (v < lo or (lo_x and v == lo))) and not (hi is not None and (v > hi or (hi_x and v == hi)))
+
+
+def _num_prefix_ok(text: str, b) -> bool:
+    """Can a decimal typed so far (no exponent) still end inside the bounds?  With k fraction digits typed the values it can grow
+    into lie within one unit of the last place of the typed value, away from zero."""
+    import math
+    lo, lo_x, hi, hi_x = b
+    neg = text.startswith("-")
+    if neg and lo is not None and (lo > 0 or (lo == 0 and lo_x)):          # a minus sign writes a value <= 0
+        return False
+    if not neg and hi is not None and (hi < 0 or (hi == 0 and hi_x)):
+        return False
+    if "." not in text:
+        ilo = None if lo is None else math.trunc(lo)
+        ihi = None if hi is None else math.trunc(hi)
+        return _int_prefix_ok(text, ilo, ihi) or (neg and text in ("-", "-0") and (lo is None or lo < 0) and (hi is None or hi > -1))
+    frac = text.split(".", 1)[1]
+    v = float(text + "0")
+    ulp = 10.0 ** -len(frac)
+    if neg:                                               # reachable values: (v - ulp, v]
+        return not (hi is not None and v - ulp >= hi) and not (lo is not None and v < lo)
+    return not (hi is not None and v > hi) and not (lo is not None and v + ulp <= lo)          # reachable values: [v, v + ulp)
+
+
 def _int_prefix_ok(text: str, lo, hi) -> bool:
     """Can the digits typed so far (optionally after a minus sign) still grow into an integer inside [lo, hi]?"""
     neg = text.startswith("-")
@@ -236,8 +278,10 @@ def _int_prefix_ok(text: str, lo, hi) -> bool:
 class SchemaPrefix:
     """`JsonPrefix` plus a cursor into a JSON schema, for the subset that covers tool arguments and typical
     `response_format` schemas: `type` (also a list of types), `properties`, `required`, `additionalProperties: false`,
-    `items`, string `enum`, `integer` vs `number`, `minimum` / `maximum` (also exclusive) of integers.  Anything else in a schema
-    is ignored (not enforced)."""
+    `items`, `minItems` / `maxItems`, string `enum`, `minLength` / `maxLength` (in code points, escapes counted once), `integer` vs
+    `number`, `minimum` / `maximum` (also exclusive) of integers and of numbers (bounded numbers are written without an exponent and
+    pruned digit by digit, so a value that cannot end inside its bounds is refused at the first digit that rules it out).
+    Anything else in a schema is ignored (not enforced)."""
 
     def __init__(self, schema: dict, root: dict | None = None):
         self.j = JsonPrefix()
@@ -248,11 +292,15 @@ class SchemaPrefix:
         self.pattern: list | None = None  # inside a string value restricted by `pattern`: [compiled regex, typed so far]
         self.integer = False
         self.irange = None                # inside an integer with bounds: [lowest, highest, digits typed so far]
+        self.nrange = None                # inside a number with bounds: [bounds, text typed so far]
+        self.strlen = None                # inside a string with minLength / maxLength: [min, max, code points so far, escape state]
 
     def copy(self) -> "SchemaPrefix":
         c = SchemaPrefix.__new__(SchemaPrefix)
         c.j, c.cur, c.integer, c.root = self.j.copy(), self.cur, self.integer, self.root
         c.irange = None if self.irange is None else list(self.irange)
+        c.nrange = None if self.nrange is None else list(self.nrange)
+        c.strlen = None if self.strlen is None else list(self.strlen)
         c.frames = [[f[0], f[1], set(f[2]), f[3]] for f in self.frames]
         c.enum = None if self.enum is None else [self.enum[0], self.enum[1]]
         c.pattern = None if self.pattern is None else [self.pattern[0], self.pattern[1]]
@@ -261,7 +309,8 @@ class SchemaPrefix:
     def signature(self):
         return (self.j.signature(), tuple((id(f[0]), f[1], frozenset(f[2]), f[3]) for f in self.frames), id(self.cur),
                 None if self.enum is None else self.enum[1], None if self.pattern is None else self.pattern[1], self.integer,
-                None if self.irange is None else tuple(self.irange))
+                None if self.irange is None else tuple(self.irange), None if self.nrange is None else self.nrange[1],
+                None if self.strlen is None else tuple(self.strlen[2:]))
 
     def finished(self) -> bool:
         return self.j.complete and not self.j.stack and self.j.mode == "after"
@@ -297,6 +346,12 @@ class SchemaPrefix:
             lo, hi, typed = self.irange
             if typed in ("", "-") or (lo is not None and int(typed) < lo) or (hi is not None and int(typed) > hi):
                 return False
+        if self.j.complete and self.nrange is not None:
+            try:
+                if not _num_in(float(self.nrange[1]), self.nrange[0]):
+                    return False
+            except ValueError:
+                return False
         return self.j.complete
 
     @staticmethod
@@ -315,7 +370,7 @@ class SchemaPrefix:
         if ch == "{":
             self.frames.append([self.cur, "{", set(), None])
         elif ch == "[":
-            self.frames.append([self.cur, "[", set(), None])
+            self.frames.append([self.cur, "[", set(), 0])        # arrays: the last slot counts the items
             self.cur = self._sub(self.cur.get("items"))
         elif ch == '"':
             e = self.cur.get("enum")
@@ -326,6 +381,10 @@ class SchemaPrefix:
             self.pattern = None
             if self.enum is None and isinstance(pat, str):
                 self.pattern = [_compile_pattern(pat), ""]
+            self.strlen = None
+            lo_n, hi_n = self.cur.get("minLength"), self.cur.get("maxLength")
+            if self.enum is None and self.pattern is None and (isinstance(lo_n, int) or isinstance(hi_n, int)):
+                self.strlen = [lo_n if isinstance(lo_n, int) else 0, hi_n if isinstance(hi_n, int) else None, 0, 0]
         elif ch in "-0123456789":
             self.integer = "integer" in types and "number" not in types
             self.irange = None
@@ -334,6 +393,13 @@ class SchemaPrefix:
                 if lo is not None or hi is not None:
                     self.irange = [lo, hi, ch]
                     if not _int_prefix_ok(ch, lo, hi):
+                        return False
+            self.nrange = None
+            if not self.integer:
+                b = _num_bounds(self.cur)
+                if b[0] is not None or b[2] is not None:
+                    self.nrange = [b, ch]
+                    if not _num_prefix_ok(ch, b):
                         return False
         return True
 
@@ -346,8 +412,13 @@ class SchemaPrefix:
                 return False
             self.frames.pop()
         elif ch == "]" and kind == "[":
+            if isinstance(schema.get("minItems"), int) and self.frames[-1][3] < schema["minItems"]:
+                return False
             self.frames.pop()
         elif ch == "," and kind == "[":
+            if isinstance(schema.get("maxItems"), int) and self.frames[-1][3] >= schema["maxItems"]:
+                return False
+            self.frames[-1][3] += 1
             self.cur = self._sub(schema.get("items"))
         elif ch == "," and kind == "{":
             props = schema.get("properties") if isinstance(schema.get("properties"), dict) else None
@@ -364,8 +435,22 @@ class SchemaPrefix:
                 self.irange = None
                 if typed in ("", "-") or (lo is not None and int(typed) < lo) or (hi is not None and int(typed) > hi):
                     return False
+            if self.nrange is not None:
+                b, typed = self.nrange
+                self.nrange = None
+                try:
+                    if not _num_in(float(typed), b):
+                        return False
+                except ValueError:
+                    return False
         if m == "number" and self.integer and ch in ".eE":
             return False
+        if m == "number" and self.nrange is not None:
+            if ch in "eE+":                                      # bounded numbers are written without an exponent
+                return False
+            self.nrange[1] += ch
+            if not _num_prefix_ok(self.nrange[1], self.nrange[0]):
+                return False
         if m == "number" and self.irange is not None and ch.isdigit():
             self.irange[2] += ch
             if not _int_prefix_ok(self.irange[2], self.irange[0], self.irange[1]):
@@ -407,8 +492,32 @@ class SchemaPrefix:
                 if ch == "\\" or (rx is not None and rx.fullmatch(typed, partial=True) is None):
                     return False
                 self.pattern[1] = typed
+        elif m in ("string", "escape", "hex") and self.strlen is not None:
+            lo_n, hi_n, n, esc = self.strlen
+            if esc == 1:                                         # the character after a backslash
+                esc = 14 if ch == "u" else 0
+                n += 0 if ch == "u" else 1
+            elif esc > 10:                                       # hex digits of a \u escape
+                esc = 0 if esc == 11 else esc - 1
+                n += 1 if esc == 0 else 0
+            elif ch == "\\":
+                esc = 1
+            elif ch == '"':
+                if n < lo_n:
+                    return False
+                self.strlen = None
+                return self.j.feed(ch)
+            else:
+                n += 1
+            if hi_n is not None and n > hi_n:
+                return False
+            self.strlen[2], self.strlen[3] = n, esc
         elif ch not in WS:
             if m in ("value", "value_or_end") and not (m == "value_or_end" and ch == "]"):
+                if m == "value_or_end" and self.frames and self.frames[-1][1] == "[":       # the first item of an array
+                    if self.frames[-1][0].get("maxItems") == 0:
+                        return False
+                    self.frames[-1][3] = 1
                 if not self._start_ok(ch):
                     return False
             elif m == "value_or_end" or (m in ("after", "key_or_end") and ch in "}],"):

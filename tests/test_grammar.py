@@ -131,3 +131,35 @@ def test_integer_bounds_of_a_json_schema():
     assert top.feed_text("4") and not top.complete
     top = SchemaSet({"type": "integer", "minimum": 5, "maximum": 50})
     assert top.feed_text("42") and top.complete and not SchemaSet({"type": "integer", "minimum": 5, "maximum": 50}).feed_text("51")
+
+
+def test_schema_array_sizes_string_lengths_and_number_ranges():
+    from cuteafd_b200.serving.constraints import SchemaSet
+
+    def ok(schema, text, whole=True):
+        s = SchemaSet(schema)
+        r = s.feed_text(text)
+        c = s.complete() if callable(s.complete) else s.complete
+        return r and (c if whole else True)
+
+    sch = {"type": "object", "additionalProperties": False, "required": ["tags", "score"], "properties": {
+        "tags": {"type": "array", "items": {"type": "string", "minLength": 2, "maxLength": 4}, "minItems": 1, "maxItems": 3},
+        "score": {"type": "number", "minimum": 0.5, "exclusiveMaximum": 10}}}
+    assert ok(sch, '{"tags":["ab","abcd"],"score":9.99}')
+    assert not ok(sch, '{"tags":[]', whole=False)                          # fewer than minItems: the bracket cannot close
+    assert not ok(sch, '{"tags":["a"]', whole=False)                       # shorter than minLength: the quote cannot close
+    assert not ok(sch, '{"tags":["abcde', whole=False)                     # the fifth character is refused
+    assert not ok(sch, '{"tags":["ab","cd","ef",', whole=False)            # no comma after maxItems items
+    assert ok(sch, '{"tags":["a\\u00e9"],"score":2}')                      # an escape is one code point
+    assert not ok(sch, '{"tags":["\\n\\n\\n\\n\\n', whole=False)
+    assert ok(sch, '{"tags":["ab"],"score":0.5}') and not ok(sch, '{"tags":["ab"],"score":10}') and ok(sch, '{"tags":["ab"],"score":9.999}')
+    assert not ok(sch, '{"tags":["ab"],"score":0.4', whole=False)          # refused at the digit that rules the value out
+    assert not ok(sch, '{"tags":["ab"],"score":12', whole=False) and not ok(sch, '{"tags":["ab"],"score":1e', whole=False)
+    assert not ok(sch, '{"tags":["ab"],"score":-', whole=False)
+    neg = {"type": "number", "minimum": -2.5, "maximum": -0.25}
+    assert ok(neg, "-0.25") and ok(neg, "-2.5") and ok(neg, "-1") and not ok(neg, "-0.2") and not ok(neg, "-3", whole=False) and not ok(neg, "1", whole=False)
+    assert not ok(neg, "-2.6", whole=False) and ok(neg, "-0.30")
+    empty = {"type": "array", "maxItems": 0}
+    assert ok(empty, "[]") and not ok(empty, "[1", whole=False)
+    nested = {"type": "array", "items": {"type": "array", "items": {"type": "integer"}, "minItems": 2, "maxItems": 2}, "minItems": 1}
+    assert ok(nested, "[[1,2],[3,4]]") and not ok(nested, "[[1]", whole=False) and not ok(nested, "[[1,2,", whole=False)
