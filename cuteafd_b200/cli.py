@@ -211,7 +211,7 @@ def cmd_serve(a) -> int:
         usage = UsageStore(os.path.join(a.usage_dir, "usage.sqlite"))
     try:
         from .utils.thermal import ThermalMonitor
-        thermal = ThermalMonitor()
+        thermal = ThermalMonitor().start()          # background sampler behind the window summaries of /v1/thermal (reads only)
     except Exception:
         thermal = None
     vision = _vision_front_end(a, spec)

@@ -285,7 +285,13 @@ def build_app(loop: ServingLoop, *, model_id: str = "cuteafd-b200", tokenizer=No
 
     @app.get("/v1/thermal")
     async def thermal_ep():
-        return thermal.sample() if thermal is not None else {"available": False}
+        if thermal is None:
+            return {"available": False}
+        s = thermal.sample()
+        if hasattr(thermal, "report"):          # window summaries: was the last minute / ten minutes / two hours throttled, and why
+            now = time.time()
+            s["windows"] = {f"{w}s": thermal.report.window(now - w) for w in (60, 600, 7200)}
+        return s
 
     @app.get("/v1/fabric")
     async def fabric_ep():

@@ -72,3 +72,46 @@ def test_trace_helpers(tmp_path):
     t = SpeculationTrace(str(tmp_path / "spec.jsonl"))
     t.record("r1", 3, 2, 31.0)
     assert json.loads((tmp_path / "spec.jsonl").read_text())["accepted"] == 2
+
+
+def test_throttle_report_windows_and_verdicts():
+    from cuteafd_b200.utils.thermal import ThrottleReport
+    rep = ThrottleReport(keep=100)
+    for t in range(10):                          # ten clean seconds at full clock
+        rep.push(100 + t, sm_mhz=1965, sm_max_mhz=1965, power_w=600.0, temp_c=55, util_pct=95)
+    for t in range(10, 16):                      # six seconds under the power cap
+        rep.push(100 + t, sm_mhz=1350, sm_max_mhz=1965, power_w=1000.0, temp_c=64, util_pct=99, reasons=("sw_power_cap",))
+    rep.push(116, sm_mhz=900, sm_max_mhz=1965, power_w=700.0, temp_c=88, util_pct=99, reasons=("hw_thermal_slowdown", "sw_power_cap"))
+    whole = rep.window(0)
+    assert whole["samples"] == 17 and whole["seconds"] == 16 and whole["verdict"] == "thermal"
+    assert whole["throttle_seconds"] == {"sw_power_cap": 7.0, "hw_thermal_slowdown": 1.0} and whole["reason_share"]["sw_power_cap"] == round(7 / 17, 3)
+    assert whole["sm_mhz_busy"] == {"min": 900, "median": 1965, "max": 1965} and whole["temp_c"]["max"] == 88
+    assert rep.window(100, 109)["verdict"] == "clean" and rep.window(110, 115)["verdict"] == "power_capped"
+    assert rep.window(1000) == {"samples": 0}
+    pinned = ThrottleReport()
+    for t in range(5):
+        pinned.push(t, sm_mhz=1100, sm_max_mhz=1965, util_pct=98)
+    assert pinned.window(0)["verdict"] == "clocks_pinned_low"        # slow under load with no reason active: a leftover clock lock
+    idle = ThrottleReport()
+    for t in range(5):
+        idle.push(t, sm_mhz=300, sm_max_mhz=1965, util_pct=2)
+    assert idle.window(0)["verdict"] == "clean" and idle.window(0)["sm_mhz_busy"] is None
+    small = ThrottleReport(keep=3)
+    for t in range(10):
+        small.push(t)
+    assert small.window(0)["samples"] == 3
+
+
+def test_thermal_monitor_feeds_the_report_and_the_sampler_only_reads():
+    import time as _t
+    nv = FakeNvml()
+    mon = ThermalMonitor(nvml=nv)
+    mon.sample()
+    nv.mask = 0x4
+    mon.sample()
+    s = mon.summary(windows=(60,))
+    assert s["now"]["reasons"] == ["sw_power_cap"] and s["windows"]["60s"]["samples"] == 3 and s["windows"]["60s"]["verdict"] == "power_capped"
+    mon.start(hz=200)
+    _t.sleep(0.1)
+    mon.stop()
+    assert len(mon.report.ring) > 5 and mon._thread is None
