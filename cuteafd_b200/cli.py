@@ -265,6 +265,48 @@ def _vision_front_end(a, spec):
     return VisionFrontEnd(tower, pad_id=int(ids["pad"]), start_id=ids["start"], end_id=ids["end"], max_images=a.vision_max_images, **audio_kw)
 
 
+def cmd_bench_history(a) -> int:
+    """`bench-history add [FILE|-] | list | compare A B | regressions | report [--svg OUT] | matrix`: the SQLite history of measured
+    benchmark lines (reference: cuteafd-bench history / reports / release smoke matrix)."""
+    import json
+    import sys
+    from .bench.history import BenchHistory, smoke_matrix
+    if a.action == "matrix":
+        for row in smoke_matrix():
+            print(f"{row['name']:<34} {row['cmd']}")
+        return 0
+    os.makedirs(os.path.dirname(os.path.abspath(a.db)), exist_ok=True)
+    h = BenchHistory(a.db)
+    if a.action == "add":
+        src = sys.stdin if not a.args or a.args[0] == "-" else open(a.args[0])
+        n = 0
+        for text in src:
+            text = text.strip()
+            if text.startswith("{"):
+                try:
+                    line = json.loads(text)
+                except ValueError:
+                    continue
+                if "metric" in line and "value" in line:
+                    print(f"run {h.add(line, label=a.label, commit_id=a.commit)}: {line['metric']} = {line['value']} {line.get('unit', '')}")
+                    n += 1
+        return 0 if n else 1
+    if a.action == "list":
+        print(h.report_markdown(a.metric or None))
+    elif a.action == "compare":
+        print(json.dumps(h.compare(int(a.args[0]), int(a.args[1]), a.tolerance), indent=1))
+    elif a.action == "regressions":
+        regs = h.latest_regressions(a.tolerance)
+        print(json.dumps(regs, indent=1))
+        return 1 if regs else 0
+    elif a.action == "report":
+        print(h.report_markdown(a.metric or None))
+        if a.svg:
+            open(a.svg, "w").write(h.report_svg(a.metric or "decode_tokens_per_s"))
+            print(f"trend -> {a.svg}")
+    return 0
+
+
 def cmd_usage(a) -> int:
     """`usage clear | clear-log | export-csv | demo`: manage the request history without a browser; `demo` serves
     `/usage` over a synthetic history (no GPU, no model).  Reference: cuteafd-daemon/src/commands/usage.rs."""
@@ -462,6 +504,10 @@ def main(argv=None) -> int:
     p.add_argument("--print", action="store_true"); p.set_defaults(fn=cmd_run, subparsers=sub.choices)
     p = sub.add_parser("fabric"); p.add_argument("--p2p", action="store_true"); p.add_argument("--all-to-all", action="store_true")
     p.add_argument("--sizes", default="", help="comma-separated message sizes in bytes"); p.set_defaults(fn=cmd_fabric)
+    p = sub.add_parser("bench-history"); p.add_argument("action", choices=["add", "list", "compare", "regressions", "report", "matrix"])
+    p.add_argument("args", nargs="*"); p.add_argument("--db", default=os.path.expanduser("~/.cache/cuteafd-b200/bench/history.sqlite"))
+    p.add_argument("--label", default=""); p.add_argument("--commit", default=""); p.add_argument("--metric", default="")
+    p.add_argument("--tolerance", type=float, default=0.02); p.add_argument("--svg", default=""); p.set_defaults(fn=cmd_bench_history)
     p = sub.add_parser("serve")
     p.add_argument("--model", "--snapshot", dest="model", default="tiny"); p.add_argument("--listen", default="127.0.0.1:8000")
     p.add_argument("--device", type=int, default=0); p.add_argument("--max-context", type=int, default=32768)
