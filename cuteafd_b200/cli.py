@@ -462,10 +462,90 @@ def cmd_run(a) -> int:
     except configfile.ConfigError as e:
         print(f"config error: {e}", file=sys.stderr)
         return 2
-    if a.print:
+    if a.print or a.dry_run:
         print("cuteafd " + " ".join(shlex.quote(x) for x in argv))
         return 0
+    if a.restart and a.pidfile:
+        _stop_pidfile(a.pidfile, a.stop_timeout)
+    if a.detach:
+        return _spawn_detached(argv, a.pidfile, a.log)
     return main(argv)
+
+
+def _spawn_detached(argv: list, pidfile: str, log: str) -> int:
+    """Start `cuteafd <argv>` as its own session (process group) with output in `log`, record its pid."""
+    import subprocess
+    if not pidfile:
+        print("--detach needs --pidfile", file=sys.stderr)
+        return 2
+    if _pid_alive(_read_pid(pidfile)):
+        print(f"already running (pid {_read_pid(pidfile)}; use --restart)", file=sys.stderr)
+        return 1
+    out = open(log or os.devnull, "ab")
+    proc = subprocess.Popen([sys.executable, "-m", "cuteafd_b200.cli", *argv], stdout=out, stderr=subprocess.STDOUT, stdin=subprocess.DEVNULL,
+                            start_new_session=True)
+    os.makedirs(os.path.dirname(os.path.abspath(pidfile)), exist_ok=True)
+    with open(pidfile, "w") as f:
+        f.write(str(proc.pid))
+    print(f"started pid {proc.pid}" + (f", log {log}" if log else ""))
+    return 0
+
+
+def _read_pid(pidfile: str) -> int | None:
+    try:
+        return int(open(pidfile).read().strip())
+    except (OSError, ValueError):
+        return None
+
+
+def _pid_alive(pid: int | None) -> bool:
+    if not pid:
+        return False
+    try:
+        os.kill(pid, 0)
+    except OSError:
+        return False
+    try:                                    # a finished child that nobody has waited for still has a pid
+        return open(f"/proc/{pid}/stat").read().split(")")[-1].split()[0] != "Z"
+    except OSError:
+        return True
+
+
+def _stop_pidfile(pidfile: str, timeout_s: float = 20.0) -> str:
+    """Ends exactly the process group recorded in the pid file: SIGTERM, then SIGKILL when it has not gone after `timeout_s`."""
+    import signal
+    import time
+    pid = _read_pid(pidfile)
+    if not _pid_alive(pid):
+        if pid is not None:
+            os.unlink(pidfile)
+        return "not running"
+    for sig, wait in ((signal.SIGTERM, timeout_s), (signal.SIGKILL, 5.0)):
+        try:
+            os.killpg(pid, sig)             # the server was started as the leader of its own session
+        except OSError:
+            try:
+                os.kill(pid, sig)
+            except OSError:
+                break
+        t0 = time.time()
+        while time.time() - t0 < wait:
+            try:
+                os.waitpid(pid, os.WNOHANG)         # reaps it when it is our child; otherwise the poll below sees it go
+            except OSError:
+                pass
+            if not _pid_alive(pid):
+                os.unlink(pidfile)
+                return "stopped" if sig == signal.SIGTERM else "killed"
+            time.sleep(0.05)
+    return "still running"
+
+
+def cmd_stop(a) -> int:
+    """`stop --pidfile FILE`: end the server that `run --detach --pidfile FILE` started (reference: stop.sh beside run.sh)."""
+    res = _stop_pidfile(a.pidfile, a.timeout)
+    print(res)
+    return 0 if res in ("stopped", "killed", "not running") else 1
 
 
 def cmd_quantize(a) -> int:
@@ -501,7 +581,13 @@ def main(argv=None) -> int:
     p.add_argument("--json", action="store_true"); p.set_defaults(fn=cmd_plan)
     p = sub.add_parser("doctor"); p.set_defaults(fn=cmd_doctor)
     p = sub.add_parser("run"); p.add_argument("--config", required=True); p.add_argument("--set", action="append", default=[])
-    p.add_argument("--print", action="store_true"); p.set_defaults(fn=cmd_run, subparsers=sub.choices)
+    p.add_argument("--print", action="store_true"); p.add_argument("--dry-run", action="store_true", help="same as --print")
+    p.add_argument("--detach", action="store_true", help="start in the background as its own process group (needs --pidfile)")
+    p.add_argument("--pidfile", default=""); p.add_argument("--log", default=""); p.add_argument("--restart", action="store_true",
+                                                                                                   help="stop what the pid file names first")
+    p.add_argument("--stop-timeout", type=float, default=20.0); p.set_defaults(fn=cmd_run, subparsers=sub.choices)
+    p = sub.add_parser("stop"); p.add_argument("--pidfile", required=True); p.add_argument("--timeout", type=float, default=20.0)
+    p.set_defaults(fn=cmd_stop)
     p = sub.add_parser("fabric"); p.add_argument("--p2p", action="store_true"); p.add_argument("--all-to-all", action="store_true")
     p.add_argument("--sizes", default="", help="comma-separated message sizes in bytes"); p.set_defaults(fn=cmd_fabric)
     p = sub.add_parser("bench-history"); p.add_argument("action", choices=["add", "list", "compare", "regressions", "report", "matrix"])

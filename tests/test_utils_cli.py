@@ -115,3 +115,38 @@ def test_thermal_monitor_feeds_the_report_and_the_sampler_only_reads():
     _t.sleep(0.1)
     mon.stop()
     assert len(mon.report.ring) > 5 and mon._thread is None
+
+
+def test_run_detach_stop_and_restart(tmp_path):
+    """Operator lifecycle: `run --detach` starts the configured command as its own process group and records the pid, `stop` ends
+    exactly that group, `--restart` replaces it."""
+    import socket
+    import time as _t
+    import urllib.request
+
+    from cuteafd_b200 import cli
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    cfg = tmp_path / "demo.config"
+    cfg.write_text(f"COMMAND=gateway\nLISTEN=127.0.0.1:{port}\n")          # the CPU stand-in server: no GPU, no model
+    pidfile, log = str(tmp_path / "run" / "demo.pid"), str(tmp_path / "demo.log")
+    assert cli.main(["run", "--config", str(cfg), "--dry-run"]) == 0
+    assert cli.main(["stop", "--pidfile", pidfile]) == 0                       # nothing to stop is not an error
+    assert cli.main(["run", "--config", str(cfg), "--detach", "--pidfile", pidfile, "--log", log]) == 0
+    pid = int(open(pidfile).read())
+    up = False
+    for _ in range(200):
+        try:
+            up = urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=0.5).status == 200
+            break
+        except OSError:
+            _t.sleep(0.1)
+    assert up, open(log).read()[-2000:]
+    assert cli.main(["run", "--config", str(cfg), "--detach", "--pidfile", pidfile]) == 1        # refuses a second copy
+    assert cli.main(["run", "--config", str(cfg), "--detach", "--restart", "--pidfile", pidfile, "--log", log, "--stop-timeout", "10"]) == 0
+    pid2 = int(open(pidfile).read())
+    assert pid2 != pid and not cli._pid_alive(pid)
+    assert cli.main(["stop", "--pidfile", pidfile, "--timeout", "10"]) == 0
+    assert not cli._pid_alive(pid2) and not (tmp_path / "run" / "demo.pid").exists()
